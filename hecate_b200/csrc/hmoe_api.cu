@@ -1,0 +1,153 @@
+// The C ABI of libhecate_moe_b200.so (declared in include/hecate_moe.h) and the small stand-alone kernels: combine,
+// dequantise, status readback and the synthetic-data fill.
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include "hmoe_common.cuh"
+#include "hmoe_internal.h"
+
+namespace hmoe {
+
+static thread_local char g_err[256] = "";
+static std::atomic<int64_t> g_launches{0};
+
+int fail(int code, const char* msg)
+{
+    snprintf(g_err, sizeof(g_err), "%s", msg ? msg : "");
+    return code;
+}
+void count_launches(int n) { g_launches += n; }
+
+namespace {
+
+// f += y (+ o) (+ o2), y = 0: the band partials are added in the reference's fixed order ((f + y) + o) + o2
+// (runtime/tier/moe4/moe4.cu:702-717; runtime/tier/cn.cu:3)
+__global__ void __launch_bounds__(256) combine_kernel(float* __restrict__ f, const float* __restrict__ o, float* __restrict__ y,
+                                                      int64_t n, const float* __restrict__ o2)
+{
+    const int64_t i = ((int64_t) blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= n) return;
+    float4 a = *(float4*) (f + i);
+    const float4 c = *(const float4*) (y + i);
+    a.x += c.x; a.y += c.y; a.z += c.z; a.w += c.w;
+    if (o) { const float4 b = *(const float4*) (o + i); a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w; }
+    if (o2) { const float4 b = *(const float4*) (o2 + i); a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w; }
+    *(float4*) (f + i) = a;
+    *(float4*) (y + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+}
+
+// one thread per 16-byte word of packed codes: 4 x 8 codes -> fp16 [N][K] times the scale of (row, column group)
+__global__ void __launch_bounds__(256) dequant_kernel(const uint4* __restrict__ q, const void* __restrict__ sc, int group, int N, int K,
+                                                      __half* __restrict__ out)
+{
+    const int KB = K / 64;
+    const size_t total = (size_t) N / 16 * KB * 32;
+    for (size_t i = (size_t) blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t) gridDim.x * blockDim.x)
+    {
+        const int lane = (int) (i & 31), s = (int) ((i >> 5) & 3), kb = (int) ((i >> 7) % KB), gr = (int) ((i >> 7) / KB);
+        const int g = lane >> 2, qq = lane & 3;
+        const uint4 v = q[i];
+        const uint32_t ww[4] = {v.x, v.y, v.z, v.w};
+        #pragma unroll
+        for (int t = 0; t < 4; ++t)
+            #pragma unroll
+            for (int nib = 0; nib < 8; ++nib)
+            {
+                const int cc = nib >> 2, h = (nib >> 1) & 1, rh = nib & 1;
+                const int row = gr * 64 + s * 16 + rh * 8 + g, k = kb * 64 + t * 16 + h * 8 + qq * 2 + cc;
+                const float scale = group ? bf16_bits_to_float(((const uint16_t*) sc)[(size_t) (k / group) * N + row]) : ((const float*) sc)[row];
+                out[(size_t) row * K + k] = __float2half_rn((float) ((int) ((ww[t] >> (4 * nib)) & 15) - 8) * scale);
+            }
+    }
+}
+
+__device__ __forceinline__ unsigned long long mix64(unsigned long long z)
+{
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+__global__ void __launch_bounds__(256) fill_kernel(unsigned long long* __restrict__ dst, size_t nwords, unsigned long long base)
+{
+    for (size_t i = (size_t) blockIdx.x * blockDim.x + threadIdx.x; i < nwords; i += (size_t) gridDim.x * blockDim.x)
+        dst[i] = mix64(base + i);
+}
+
+}  // namespace
+}  // namespace hmoe
+
+using namespace hmoe;
+
+extern "C" {
+
+int hmoe_version(void) { return 100; }
+const char* hmoe_last_error(void) { return g_err; }
+int64_t hmoe_launch_count(void) { return g_launches.load(); }
+
+size_t hmoe_router_ws_bytes(int R, int E) { return router_ws_bytes(R, E); }
+int hmoe_router(const void* x, int x_dtype, const void* wt, int w_dtype, const float* bias, int R, int H, int E, int topk,
+                float scale, int64_t* sel, void* rw, void* ws, size_t ws_bytes, void* stream)
+{
+    return router_launch(x, x_dtype, wt, w_dtype, bias, R, H, E, topk, scale, sel, rw, ws, ws_bytes, (cudaStream_t) stream);
+}
+
+size_t hmoe_decode_ws_bytes(int H, int I) { return decode_ws_bytes(H, I); }
+int hmoe_decode(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
+                int act_quant, float* y, void* ws, size_t ws_bytes, void* stream)
+{
+    if (!layer) return fail(HMOE_E_ARG, "hmoe_decode: null layer");
+    return decode_launch(layer, x, x_dtype, sel, rw, R, lo, n_local, act_quant, y, ws, ws_bytes, (cudaStream_t) stream);
+}
+
+int hmoe_combine(float* f, const float* o, float* y, int64_t n, const float* o2, void* stream)
+{
+    if (!f || !y || n < 0 || n % 4) return fail(HMOE_E_ARG, "hmoe_combine: f, y and n % 4 == 0 required");
+    if (n == 0) return HMOE_OK;
+    combine_kernel<<<(unsigned) ((n / 4 + 255) / 256), 256, 0, (cudaStream_t) stream>>>(f, o, y, n, o2);
+    count_launches(1);
+    const cudaError_t err = cudaGetLastError();
+    return err == cudaSuccess ? HMOE_OK : fail(HMOE_E_CUDA, cudaGetErrorString(err));
+}
+
+int hmoe_dequant(const void* q, const void* scales, int group, int scale_dtype, int N, int K, void* out_f16, void* stream)
+{
+    if (!q || !scales || !out_f16 || N % 64 || K % 64 || N <= 0 || K <= 0) return fail(HMOE_E_ARG, "hmoe_dequant: N and K must be multiples of 64");
+    if (!(group == 0 && scale_dtype == HMOE_F32) && !(group > 0 && K % group == 0 && scale_dtype == HMOE_BF16))
+        return fail(HMOE_E_ARG, "hmoe_dequant: scales must be fp32 per row (group 0) or bf16 per group");
+    dequant_kernel<<<1024, 256, 0, (cudaStream_t) stream>>>((const uint4*) q, scales, group, N, K, (__half*) out_f16);
+    count_launches(1);
+    const cudaError_t err = cudaGetLastError();
+    return err == cudaSuccess ? HMOE_OK : fail(HMOE_E_CUDA, cudaGetErrorString(err));
+}
+
+int hmoe_ws_status(void* ws, uint32_t* status_out, void* stream)
+{
+    if (!ws || !status_out) return fail(HMOE_E_ARG, "hmoe_ws_status: null pointer");
+    uint32_t v = 0;
+    cudaError_t err = cudaMemcpyAsync(&v, ws, 4, cudaMemcpyDeviceToHost, (cudaStream_t) stream);
+    if (err == cudaSuccess) err = cudaMemsetAsync(ws, 0, 4, (cudaStream_t) stream);
+    if (err == cudaSuccess) err = cudaStreamSynchronize((cudaStream_t) stream);
+    if (err != cudaSuccess) return fail(HMOE_E_CUDA, cudaGetErrorString(err));
+    *status_out = v;
+    if (v & ST_WAIT_TIMEOUT) return fail(HMOE_E_TIMEOUT, "a bounded device-side wait gave up");
+    return HMOE_OK;
+}
+
+int hmoe_fill_bytes(void* dst, size_t nbytes, uint64_t seed, uint64_t stream_id, void* stream)
+{
+    if (!dst || nbytes % 8) return fail(HMOE_E_ARG, "hmoe_fill_bytes: nbytes must be a multiple of 8");
+    if (nbytes == 0) return HMOE_OK;
+    // host-side copy of the generator's first step: base = mix(seed * G + stream_id)
+    unsigned long long z = (unsigned long long) seed * 0x9E3779B97F4A7C15ull + (unsigned long long) stream_id;
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z ^= z >> 31;
+    fill_kernel<<<2048, 256, 0, (cudaStream_t) stream>>>((unsigned long long*) dst, nbytes / 8, z);
+    count_launches(1);
+    const cudaError_t err = cudaGetLastError();
+    return err == cudaSuccess ? HMOE_OK : fail(HMOE_E_CUDA, cudaGetErrorString(err));
+}
+
+}  // extern "C"

@@ -1,0 +1,170 @@
+// Shared device helpers of the MoE expert kernels (sm_100a): bounded mbarrier waits, 1-D bulk copies into shared memory,
+// the int4 -> fp16 fragment conversion and the m16n8k16 MMA wrapper.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace hmoe {
+
+// status word bits written by kernels (device) and read by the host on request
+enum : unsigned { ST_WAIT_TIMEOUT = 1u, ST_BAD_INDEX = 2u };
+
+constexpr int TOPK_MAX = 8;
+constexpr int MAXR = 16;                  // decode rows per call (tokens x (1 + MTP drafts))
+constexpr int MAXS = MAXR * TOPK_MAX + 1; // distinct experts of a decode call + the shared expert
+constexpr int MAXT = MAXS + 2;            // 8-row tiles: one per slot, one more per slot with > 8 rows (at most 2 + shared)
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t) __cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long globaltimer_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait: gives up after about `limit_ns` of wall time, raises the abort flag in shared memory and the timeout bit
+// of the global status word, and returns false. Every waiter checks the abort flag, so after one timeout the whole
+// block drains quickly instead of spinning.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned* status,
+                                          unsigned long long limit_ns = 1000000000ull)
+{
+    unsigned long long t0 = 0;
+    for (uint32_t i = 0;; ++i)
+    {
+        if (mbar_try(bar, parity)) return true;
+        if ((i & 1023u) == 1023u)
+        {
+            if (*abort_flag) return false;
+            const unsigned long long now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > limit_ns) break;
+        }
+    }
+    *abort_flag = 1;
+    if (status) atomicOr(status, ST_WAIT_TIMEOUT);
+    return false;
+}
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// 1-D bulk copy global -> shared (both 16-byte aligned, size a multiple of 16), completion counted on an mbarrier.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ uint4 lds128(uint32_t addr)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint4 ldg128_nc(const void* p)
+{
+    uint4 v;
+    asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+// plain (coherent) 16-byte load, for data written by an earlier kernel of the same call
+__device__ __forceinline__ uint4 ldg128(const void* p)
+{
+    uint4 v;
+    asm volatile("ld.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ void mma_f16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// One 32-bit word of packed codes = the A fragment of one 16-column step for this lane: nibble i holds
+// (column pair member i >> 2, column half (i >> 1) & 1, row half i & 1). Returns the four fp16x2 registers
+// {(row g, k 2q..2q+1), (row g+8, same k), (row g, k 2q+8..), (row g+8, k 2q+8..)} with value code - 8, exactly.
+// (1024 + c is exact in fp16; the nibbles that sit four bits higher give 1024 + 16 c and are brought back by one fused
+// multiply-add with 1/16 and -72.)
+__device__ __forceinline__ void frag_from_codes(uint32_t w, uint32_t* a)
+{
+    const uint32_t MAGIC = 0x64006400u;              // 1024.0 in both halves
+    const uint32_t lo0 = (w & 0x000f000fu) | MAGIC, hi0 = (w & 0x00f000f0u) | MAGIC;
+    const uint32_t w8 = w >> 8;
+    const uint32_t lo1 = (w8 & 0x000f000fu) | MAGIC, hi1 = (w8 & 0x00f000f0u) | MAGIC;
+    const __half2 k1032 = __halves2half2(__ushort_as_half(0x6408), __ushort_as_half(0x6408));   // 1032
+    const __half2 k16th = __halves2half2(__ushort_as_half(0x2c00), __ushort_as_half(0x2c00));   // 1/16
+    const __half2 km72 = __halves2half2(__ushort_as_half(0xd480), __ushort_as_half(0xd480));    // -72
+    __half2 r0 = __hsub2(*reinterpret_cast<const __half2*>(&lo0), k1032);
+    __half2 r1 = __hfma2(*reinterpret_cast<const __half2*>(&hi0), k16th, km72);
+    __half2 r2 = __hsub2(*reinterpret_cast<const __half2*>(&lo1), k1032);
+    __half2 r3 = __hfma2(*reinterpret_cast<const __half2*>(&hi1), k16th, km72);
+    a[0] = *reinterpret_cast<uint32_t*>(&r0); a[1] = *reinterpret_cast<uint32_t*>(&r1);
+    a[2] = *reinterpret_cast<uint32_t*>(&r2); a[3] = *reinterpret_cast<uint32_t*>(&r3);
+}
+
+// position of two-value word p (columns 2p, 2p+1 of a 64-column block) in the activation row order the kernels read:
+// t = p / 8 (16-column step), h = (p % 8) / 4, q = p % 4  ->  q * 8 + t * 2 + h
+__device__ __forceinline__ int frag_pos(int p) { return (p & 3) * 8 + (p >> 3) * 2 + ((p >> 2) & 1); }
+
+__device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_as_float((uint32_t) b << 16); }
+
+// deterministic exp: the same sequence of correctly rounded operations as the CPU checker's routine, so selections that
+// depend on it are reproducible bit for bit
+__device__ __forceinline__ float det_expf(float x)
+{
+    x = fminf(fmaxf(x, -87.f), 88.f);
+    const float t = __fmul_rn(x, 1.44269504088896341f);
+    const float n = rintf(t);
+    float r = __fmaf_rn(n, -0.693145751953125f, x);
+    r = __fmaf_rn(n, -1.42860682030941723212e-6f, r);
+    float p = 1.9875691500e-4f;
+    p = __fmaf_rn(p, r, 1.3981999507e-3f);
+    p = __fmaf_rn(p, r, 8.3334519073e-3f);
+    p = __fmaf_rn(p, r, 4.1665795894e-2f);
+    p = __fmaf_rn(p, r, 1.6666665459e-1f);
+    p = __fmaf_rn(p, r, 5.0000001201e-1f);
+    p = __fmaf_rn(p, __fmul_rn(r, r), r);
+    p = __fadd_rn(p, 1.f);
+    return __fmul_rn(p, __int_as_float(((int) n + 127) << 23));
+}
+
+// Routing of one decode call, built once per call by the prepare kernel and read by the expert kernels.
+// Slots are the distinct selected experts in ascending id order (as the reference's in-kernel route() orders them,
+// runtime/tier/moe4/moe4.cu:86-110), followed by the shared expert if there is one. Each slot lists the rows that picked
+// it; those rows are the columns of its MMA tiles (8 per tile).
+struct Route
+{
+    int m;                         // routed slots
+    int nslots;                    // m + (shared ? 1 : 0)
+    int ntiles;                    // 8-row tiles over all slots
+    int pad;
+    short expert[MAXS];            // local expert id of the slot (-1 = shared)
+    short tile0[MAXS];             // first tile of the slot
+    unsigned char nrows[MAXS];     // rows that picked the slot
+    unsigned char rows[MAXS][MAXR];// their row numbers, ascending; entries >= nrows are 255
+    float w[MAXS][MAXR];           // routing weight per listed row (summed over repeated picks)
+};
+
+}  // namespace hmoe

@@ -1,0 +1,22 @@
+// Internal host-side declarations shared by the translation units of libhecate_moe_b200.so.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+#include "../../include/hecate_moe.h"
+
+namespace hmoe {
+
+// records the message for hmoe_last_error() and returns `code`
+int fail(int code, const char* msg);
+void count_launches(int n);
+
+size_t decode_ws_bytes(int H, int I);
+int decode_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
+                  int act_quant, float* y, void* ws, size_t ws_bytes, cudaStream_t st);
+
+size_t router_ws_bytes(int R, int E);
+int router_launch(const void* x, int x_dtype, const void* wt, int w_dtype, const float* bias, int R, int H, int E, int topk,
+                  float scale, int64_t* sel, void* rw, void* ws, size_t ws_bytes, cudaStream_t st);
+
+}  // namespace hmoe

@@ -1,0 +1,172 @@
+"""Host-side mirror of the reference's operator surface for the MoE expert path, on top of the C ABI.
+
+The functions keep the names, argument order and meaning of the reference's extension modules so that its dispatcher
+(runtime/tier/tier_split.py) could call them unchanged:
+
+    moe4_forward / moe4_scratch / moe4_combine / moe4_dequant   runtime/tier/moe4/moe4.cu:817-911
+    router_fused                                                runtime/core/exl3_router.py:134-146
+
+torch is used for device memory and the current stream only. All compute happens in libhecate_moe_b200.so; a missing
+library is an error, never a fallback.
+"""
+import ctypes as C
+
+import torch
+
+from . import _lib
+from ._lib import BF16, F16, F32, HmoeError, LayerStruct, check, lib, vp
+
+MAX_DECODE_ROWS = 16
+
+
+def _stream(dev):
+    return C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+
+
+def _dt(t):
+    if t.dtype == torch.float16:
+        return F16
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise HmoeError(f"expected fp16 or bf16, got {t.dtype}")
+
+
+def launch_count():
+    return int(lib().hmoe_launch_count())
+
+
+class ExpertTables:
+    """The six device pointer tables of one layer's local experts (as tier_split.py:210-214,246 builds them) plus the
+    optional shared expert. Keeps the weight tensors alive."""
+
+    def __init__(self, H, I, topk, gate, up, down, gate_s, up_s, down_s, group=0, shared=None, device=None):
+        dev = device or gate[0].device
+        self.H, self.I, self.topk, self.group, self.n = H, I, topk, group, len(gate)
+        self.scale_dtype = F32 if group == 0 else BF16
+        want = torch.float32 if group == 0 else torch.bfloat16
+        for s in list(gate_s) + list(up_s) + list(down_s):
+            if s.dtype != want:
+                raise HmoeError(f"scales must be {want} for group {group}")
+        self.keep = [gate, up, down, gate_s, up_s, down_s, shared]
+        tab = lambda ts: torch.tensor([t.data_ptr() for t in ts], dtype=torch.int64, device=dev)
+        self.tabs = {k: tab(v) for k, v in zip(("gate_w", "up_w", "down_w", "gate_s", "up_s", "down_s"),
+                                               (gate, up, down, gate_s, up_s, down_s))}
+        self.shared = shared   # (gq, uq, dq, gs, us, ds) tensors or None
+
+    def struct(self):
+        s = LayerStruct()
+        s.H, s.I, s.n_experts, s.topk, s.group, s.scale_dtype = self.H, self.I, self.n, self.topk, self.group, self.scale_dtype
+        for k, t in self.tabs.items():
+            setattr(s, k, t.data_ptr())
+        if self.shared is not None:
+            for k, t in zip(("sh_gate_w", "sh_up_w", "sh_down_w", "sh_gate_s", "sh_up_s", "sh_down_s"), self.shared):
+                setattr(s, k, t.data_ptr())
+        return s
+
+
+def decode_workspace(H, I, device):
+    """Zero-filled scratch of the decode path (the counterpart of moe4.scratch, moe4.cu:897-902)."""
+    n = lib().hmoe_decode_ws_bytes(C.c_int(H), C.c_int(I))
+    return torch.zeros(n, dtype=torch.uint8, device=device)
+
+
+def decode(tables, x, sel, rw, y, ws, lo=0, n_local=None, act_quant=False):
+    """y[R][H] (fp32) += experts(x) for the rows' selections; R <= 16. Only ids in [lo, lo + n_local) contribute."""
+    R = x.shape[0]
+    if not (x.is_contiguous() and sel.is_contiguous() and rw.is_contiguous() and y.is_contiguous()):
+        raise HmoeError("decode: tensors must be contiguous")
+    if sel.dtype != torch.int64 or rw.dtype != torch.float16 or y.dtype != torch.float32:
+        raise HmoeError("decode: sel int64, rw fp16, y fp32 required")
+    if x.shape[1] != tables.H or sel.shape[1] != tables.topk or y.shape[-1] != tables.H:
+        raise HmoeError("decode: shape")
+    st = tables.struct()
+    check(lib().hmoe_decode(C.byref(st), vp(x), C.c_int(_dt(x)), vp(sel), vp(rw), C.c_int(R), C.c_int(lo),
+                            C.c_int(tables.n if n_local is None else n_local), C.c_int(int(act_quant)), vp(y), vp(ws),
+                            C.c_size_t(ws.numel()), _stream(x.device)))
+    return y
+
+
+def ws_status(ws):
+    out = C.c_uint32(0)
+    check(lib().hmoe_ws_status(vp(ws), C.byref(out), _stream(ws.device)))
+    return out.value
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# reference-named entry points
+
+def moe4_scratch(device, H=6144, I=2048):
+    """moe4.scratch(device) -> five tensors (moe4.cu:897-902). Only the first is used here (the decode workspace); the
+    other four stand in for the reference's gu32 / counters / y32 so call sites can keep unpacking five."""
+    e = torch.zeros(1, dtype=torch.int32, device=device)
+    return [decode_workspace(H, I, device), e, e, e, e]
+
+
+def moe4_forward(x, sel, rw, n_hot, gate_w, up_w, down_w, gate_s, up_s, down_s, act, gu32, ctr_a, y32, ctr_b, y, blocks,
+                 blocks_a, lo, sh_gw=0, sh_uw=0, sh_dw=0, sh_gs=0, sh_us=0, sh_ds=0, xf=0, *, I=2048, group=0, act_quant=False):
+    """moe4.forward with the reference's argument order (moe4.cu:828-833,916-920). gate_w .. down_s are int64 device
+    tables of pointers; `act` is the workspace from moe4_scratch; gu32, ctr_a, y32, ctr_b, blocks, blocks_a are accepted and
+    ignored (this implementation needs no counters and sizes its own grid). Up to 16 rows. The shared expert pointers
+    are int4 in the routed experts' format. xf (pre-ordered input) is not supported."""
+    if xf:
+        raise HmoeError("moe4_forward: fragment-order input (xf) is not supported")
+    R, H = x.shape
+    s = LayerStruct()
+    s.H, s.I, s.n_experts, s.topk, s.group = H, I, int(n_hot), sel.shape[1], group
+    s.scale_dtype = F32 if group == 0 else BF16
+    for k, t in zip(("gate_w", "up_w", "down_w", "gate_s", "up_s", "down_s"), (gate_w, up_w, down_w, gate_s, up_s, down_s)):
+        setattr(s, k, t.data_ptr())
+    for k, p in zip(("sh_gate_w", "sh_up_w", "sh_down_w", "sh_gate_s", "sh_up_s", "sh_down_s"), (sh_gw, sh_uw, sh_dw, sh_gs, sh_us, sh_ds)):
+        setattr(s, k, int(p) or None)
+    if sel.dtype != torch.int64 or not sel.is_contiguous():
+        raise HmoeError("moe4: selection must be contiguous int64")
+    check(lib().hmoe_decode(C.byref(s), vp(x), C.c_int(_dt(x)), vp(sel), vp(rw), C.c_int(R), C.c_int(int(lo)), C.c_int(int(n_hot)),
+                            C.c_int(int(act_quant)), vp(y), vp(act), C.c_size_t(act.numel()), _stream(x.device)))
+
+
+def moe4_combine(f, o_ptr, y, rows, o2_ptr, done_ptr=0):
+    """moe4.combine (moe4.cu:817-824): f += y (+ o) (+ o2); y = 0. done_ptr (a flag another device raises) is not
+    supported: there is no second device behind this path."""
+    if done_ptr:
+        raise HmoeError("moe4_combine: done flag not supported")
+    if f.dtype != torch.float32 or not f.is_contiguous():
+        raise HmoeError("moe4_combine: f must be contiguous fp32")
+    n = int(rows) * f.shape[-1]
+    check(lib().hmoe_combine(vp(f), vp(o_ptr or None), vp(y), C.c_int64(n), vp(o2_ptr or None), _stream(f.device)))
+
+
+def moe4_dequant(q, sc, N, K, group=0):
+    """moe4.dequant(q, sc, N, K) -> fp16 [N][K] (moe4.cu:904-911)."""
+    out = torch.empty((N, K), dtype=torch.float16, device=q.device)
+    check(lib().hmoe_dequant(vp(q), vp(sc), C.c_int(group), C.c_int(F32 if group == 0 else BF16), C.c_int(N), C.c_int(K), vp(out),
+                             _stream(q.device)))
+    return out
+
+
+_router_ws = {}
+
+
+def router_fused(x, wt, bias, logits, ctr, sel, rw, topk, scale):
+    """router_fused(x, wt, bias, logits, ctr, sel, rw, topk, scale) (exl3_router.py:134-146). `logits` and `ctr` (the
+    reference's self-cleaning scratch) are accepted and ignored; any number of rows."""
+    H = x.shape[-1]
+    R = x.numel() // H
+    E = wt.shape[0]
+    need = lib().hmoe_router_ws_bytes(C.c_int(R), C.c_int(E))
+    key = (x.device, )
+    ws = _router_ws.get(key)
+    if ws is None or ws.numel() < need:
+        ws = _router_ws[key] = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=x.device)
+    if not (x.is_contiguous() and wt.is_contiguous()):
+        raise HmoeError("router_fused: shape / dtype")
+    check(lib().hmoe_router(vp(x), C.c_int(_dt(x)), vp(wt), C.c_int(_dt(wt)), vp(bias), C.c_int(R), C.c_int(H), C.c_int(E),
+                            C.c_int(int(topk)), C.c_float(float(scale)), vp(sel), vp(rw), vp(ws), C.c_size_t(ws.numel()),
+                            _stream(x.device)))
+    return sel, rw
+
+
+def fill_bytes(t, seed, stream_id):
+    """Fill a uint8 tensor (numel % 8 == 0) with the synthetic generator's bytes for (seed, stream_id)."""
+    check(lib().hmoe_fill_bytes(vp(t), C.c_size_t(t.numel() * t.element_size()), C.c_uint64(seed), C.c_uint64(stream_id),
+                                _stream(t.device)))
+    return t

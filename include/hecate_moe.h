@@ -1,0 +1,83 @@
+/* hecate_moe.h - C ABI of libhecate_moe_b200.so: the MoE expert hot path of chronarion/hecate for NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes plain pointers and sizes, returns 0 (HMOE_OK) or an error code, never throws, never allocates
+ * device memory and never synchronises the stream unless its comment says so. All device pointers must belong to the
+ * current CUDA device. `stream` is a cudaStream_t passed as void*. hmoe_last_error() returns the message of the calling
+ * thread's last failure. Paths in the comments name the reference interface each entry point replaces (relative to the
+ * reference project's root).
+ *
+ * Weight format (unchanged from the reference): a matrix W[N][K] of 4-bit codes c (value c - 8) packed by
+ * tools/quant/gptq_int4.py:74-77 (pack_u4); see hecate_b200/layout.py for the index formula. Scales are either one fp32
+ * per row (group = 0, scale_dtype = HMOE_F32; the reference's format) or one bf16 per 128 input columns laid out
+ * [K/128][N] (group = 128, scale_dtype = HMOE_BF16). Every weight and scale pointer must be 16-byte aligned.
+ */
+#ifndef HECATE_MOE_H
+#define HECATE_MOE_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { HMOE_OK = 0, HMOE_E_ARG = 1, HMOE_E_CUDA = 2, HMOE_E_TIMEOUT = 3, HMOE_E_WS = 4, HMOE_E_UNSUPPORTED = 5 };
+enum { HMOE_F16 = 0, HMOE_BF16 = 1, HMOE_F32 = 2 };
+
+/* One MoE layer's experts as the reference's loader hands them to its kernels (runtime/tier/tier_split.py:206-246):
+ * six device arrays of n_experts device pointers (int64), one per matrix and per scale tensor, plus the optional shared
+ * expert (all six pointers null = none). gate/up are [I][H], down is [H][I]. */
+typedef struct hmoe_layer
+{
+    int32_t H, I, n_experts, topk;
+    int32_t group;        /* 0 = one scale per row, 128 = one scale per 128 input columns */
+    int32_t scale_dtype;  /* HMOE_F32 with group 0, HMOE_BF16 with group 128 */
+    const int64_t* gate_w; const int64_t* up_w; const int64_t* down_w;
+    const int64_t* gate_s; const int64_t* up_s; const int64_t* down_s;
+    const void* sh_gate_w; const void* sh_up_w; const void* sh_down_w;
+    const void* sh_gate_s; const void* sh_up_s; const void* sh_down_s;
+} hmoe_layer;
+
+int hmoe_version(void);
+const char* hmoe_last_error(void);
+/* Kernels launched by this library in this process so far (for benchmark bookkeeping). */
+int64_t hmoe_launch_count(void);
+
+/* Router: replaces router_fused(x, wt, bias, logits, ctr, sel, rw, topk, scale) (runtime/core/exl3_router.py:134-146) and the
+ * routing_dots contract (docker/patches/exllamav3/block_sparse_mlp_routing.py:253-301) for any number of rows.
+ * x [R][H] and wt [E][H] are fp16 or bf16 (x_dtype / w_dtype), bias fp32 [E] or null. Writes sel int64 [R][topk] (selection
+ * order: descending sigmoid(logit) + bias, ties to the lower expert id) and rw fp16 [R][topk] = act * scale / (sum + 1e-20).
+ * Needs E % 32 == 0, E <= 256, H % 256 == 0, topk <= 8. ws: hmoe_router_ws_bytes(R, E) bytes of device scratch. */
+size_t hmoe_router_ws_bytes(int R, int E);
+int hmoe_router(const void* x, int x_dtype, const void* wt, int w_dtype, const float* bias, int R, int H, int E, int topk,
+                float scale, int64_t* sel, void* rw, void* ws, size_t ws_bytes, void* stream);
+
+/* Decode expert layer: replaces moe4.forward(x, sel, rw, n_hot, tables..., scratch..., y, blocks, blocks_a, lo, shared...)
+ * (runtime/tier/moe4/moe4.cu:828-895) for R <= 16 rows in one pass over the weights. x [R][H] fp16 or bf16; sel int64
+ * [R][topk]; rw fp16 [R][topk]; only ids in [lo, lo + n_local) contribute, entry e - lo of the tables; y fp32 [R][H] is
+ * accumulated into. act_quant = 1 reproduces the reference CPU engine's int8 activation round trips
+ * (runtime/tier/cpuband.cpp:106-111,140-150,200-207); 0 keeps fp16 activations like the reference GPU kernels.
+ * ws: hmoe_decode_ws_bytes(H, I) bytes, zero-filled once before first use (replaces moe4.scratch, moe4.cu:897-902). */
+size_t hmoe_decode_ws_bytes(int H, int I);
+int hmoe_decode(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
+                int act_quant, float* y, void* ws, size_t ws_bytes, void* stream);
+
+/* Combine: replaces moe4.combine(f, o_ptr, y, rows, o2_ptr, done_ptr) (runtime/tier/moe4/moe4.cu:702-717,817-824):
+ * f += y (+ o) (+ o2) in that order, then y = 0. o and o2 may be null. n = rows * H must be a multiple of 4. */
+int hmoe_combine(float* f, const float* o, float* y, int64_t n, const float* o2, void* stream);
+
+/* Dequantise one packed matrix to fp16 [N][K] (value * scale): replaces moe4.dequant(q, sc, N, K)
+ * (runtime/tier/moe4/moe4.cu:679-698,904-911); group / scale_dtype as in hmoe_layer. */
+int hmoe_dequant(const void* q, const void* scales, int group, int scale_dtype, int N, int K, void* out_f16, void* stream);
+
+/* Reads and clears the status word kernels set when a bounded device-side wait gave up or an index was out of range
+ * (synchronises the stream). *status_out: bit 0 = wait timed out, bit 1 = bad index. Returns HMOE_E_TIMEOUT if bit 0 is set. */
+int hmoe_ws_status(void* ws, uint32_t* status_out, void* stream);
+
+/* Synthetic data: fills nbytes (multiple of 8) with the counter-based generator of hecate_b200/synth.py
+ * (word i = mix(mix(seed * G + stream_id) + i)), identical to the numpy implementation. No reference counterpart. */
+int hmoe_fill_bytes(void* dst, size_t nbytes, uint64_t seed, uint64_t stream_id, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
