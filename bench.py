@@ -1,0 +1,301 @@
+#!/usr/bin/env python
+"""Benchmark of the MoE expert hot path on B200: one decode MoE layer call per step.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (the decode configuration of the benchmark definition): hidden 6144, 256 routed experts, top-8 sigmoid/bias router,
+one shared expert, SwiGLU experts gate/up [2048 x 6144] and down [6144 x 2048] in packed int4 with a bf16 scale per 128
+input columns, decode batch of 8 tokens each with one MTP draft = 16 rows. Inputs are synthetic (seeded): codes uniform,
+scales lognormal(-4, 0.5), activations N(0, 1) in bf16, router weight N(0, 0.02) in bf16.
+
+A step = router -> prepare -> gate_up (+ SiLU * up * weight) -> down -> combine into the fp32 layer output. `value` is rows/s
+with inputs resident in HBM; `e2e` is the same call chain fed from pinned host memory with the host<->device copies inside
+the timed region. Consecutive steps use different input batches (8 in a ring), so each step selects a different ~100 of the
+256 experts: about 2 GB of the 4.85 GB layer is streamed per step, far more than the 126 MB L2.
+
+`--impl reference` times the reference's own CPU expert engine (oracle/_ref, built from the reference source) on the host
+cores, on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+H, I, E, TOPK, ROWS = 6144, 2048, 256, 8, 16
+GROUP = 128
+PER_MATRIX = I * H // 2                                  # packed bytes of one matrix
+SCALE_BYTES = (2 * I * (H // GROUP) + H * (I // GROUP)) * 2
+EXPERT_BYTES = 3 * PER_MATRIX + SCALE_BYTES              # 19,464,192
+GATE_UP_BYTES = 2 * PER_MATRIX + 2 * I * (H // GROUP) * 2
+NBATCH = 8
+METRIC = "moe_layer_decode_rows_per_s"
+UNIT = "rows/s"
+WORKLOAD = "decode M=8 tokens x (1 + 1 MTP draft) = 16 rows, H=6144, 256 experts top-8 + shared, int4 g128 bf16 scales"
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index, period=0.02):
+        self.samples, self.reasons, self.stop_flag, self.period = [], set(), False, period
+        self.max_mhz = None
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            self.nv, self.h = nv, nv.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(self.h, nv.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+        self.t = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        nv = self.nv
+        names = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40,
+                 "hw_power_brake_slowdown": 0x80}
+        while not self.stop_flag:
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self.t.start()
+        return self
+
+    def __exit__(self, *a):
+        self.stop_flag = True
+        if self.nv is not None:
+            self.t.join()
+
+    def summary(self):
+        s = self.samples
+        return {"sm_mhz": float(np.median(s)) if s else None, "sm_max_mhz": self.max_mhz, "samples": len(s),
+                "reasons": sorted(self.reasons)}
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+def cpu_reference_arm(steps, warmup, seed=0):
+    """Times the reference CPU engine (or, without it, this repository's restatement) on 8-row jobs of the workload."""
+    from oracle import oracle as O
+    from hecate_b200 import synth
+    cores = os.cpu_count() or 1
+    threads = max(1, min(60, cores - 2))
+    sel, rw = synth.zipf_routing(seed, 0, 8, E, TOPK, 0.0)
+    x = synth.activations(seed, 0, 8, H).astype(np.float16)
+    ids = sorted(set(int(e) for e in sel.reshape(-1)))
+    remap = {e: i for i, e in enumerate(ids)}
+    sel_local = np.vectorize(remap.get)(sel).astype(np.int64)
+    experts = []
+    for e in ids:                       # row-major int4 + one fp32 scale per row: the engine's own format
+        mk = lambda kind, n: synth.rand_bytes(seed, synth.stream_id(0, kind, e), n).reshape(-1)
+        sc = lambda kind, N, K: synth.scales(seed, 0, kind, e, N, K, K)
+        experts.append(O.Expert(mk("gate_q", I * H // 2).reshape(I, H // 2), mk("up_q", I * H // 2).reshape(I, H // 2),
+                                mk("down_q", H * I // 2).reshape(H, I // 2), sc("gate_s", I, H), sc("up_s", I, H),
+                                sc("down_s", H, I), H, I, packed=False))
+    times = []
+    if O.ref_available():
+        kind = "reference"
+        eng = O.RefEngine(experts, 0, threads=threads, core0=0)
+        try:
+            for i in range(warmup + steps):
+                _, dt = eng.job(x, sel_local, rw)
+                if i >= warmup:
+                    times.append(dt)
+        finally:
+            eng.stop()
+    else:
+        kind = "port"
+        threads = O.threads()
+        for i in range(warmup + steps):
+            t0 = time.perf_counter()
+            O.moe_forward(H, I, 0, x, sel_local, rw, 0, experts)
+            if i >= warmup:
+                times.append(time.perf_counter() - t0)
+    t = float(np.median(times))
+    return {"value": 8.0 / t, "unit": UNIT, "cores": threads, "kind": kind, "ms_per_job": t * 1e3,
+            "sample": f"{len(times)} jobs of 8 rows ({len(ids)} distinct routed experts, per-row fp32 scales, no shared expert), "
+                      f"median ISSUE->DONE time"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 50))
+    cb = cpu_reference_arm(steps, max(1, min(args.warmup, 5)))
+    line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+            "warmup": args.warmup, "ms_per_step": cb["ms_per_job"], "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int4 x int8 -> fp32", "data": "synthetic",
+            "config": {"workload": WORKLOAD + " [CPU sample: one 8-row job per step]"},
+            "cpu_baseline": cb, "e2e": {"value": cb["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+def build_layer(dev, seed, experts, torch, moe):
+    """Seeded synthetic experts resident in HBM: `experts` routed experts + one shared expert."""
+    from hecate_b200 import synth
+    n = len(experts)
+    pool = torch.empty((n + 1) * 3 * PER_MATRIX, dtype=torch.uint8, device=dev)
+    moe.fill_bytes(pool, seed, synth.stream_id(0, "gate_q", 0))
+    view = lambda e, k: pool[(e * 3 + k) * PER_MATRIX:(e * 3 + k + 1) * PER_MATRIX]
+    g = torch.Generator(device=dev); g.manual_seed(seed + 1)
+    sc = lambda N, K: (torch.randn(N // 64, K // GROUP, 64, device=dev, generator=g) * 0.5 - 4.0).exp().to(torch.bfloat16)
+    gs = [sc(I, H) for _ in range(n + 1)]; us = [sc(I, H) for _ in range(n + 1)]; ds = [sc(H, I) for _ in range(n + 1)]
+    shared = (view(n, 0), view(n, 1), view(n, 2), gs[n], us[n], ds[n])
+    tabs = moe.ExpertTables(H, I, TOPK, [view(e, 0) for e in range(n)], [view(e, 1) for e in range(n)],
+                            [view(e, 2) for e in range(n)], gs[:n], us[:n], ds[:n], group=GROUP, shared=shared, device=dev)
+    tabs.keep.append(pool)
+    return tabs
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from hecate_b200 import moe, synth
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        from hecate_b200 import ep
+        return ep.bench_decode(args, world, rank, dev)
+    steps, warmup = args.steps, max(3, args.warmup)
+    tabs = build_layer(dev, 0, list(range(E)), torch, moe)
+    wt = torch.from_numpy(synth.router_weight(0, 0, E, H)).to(dev).to(torch.bfloat16)
+    bias = torch.zeros(E, dtype=torch.float32, device=dev)
+    xs_host = [torch.from_numpy(synth.activations(b, 0, ROWS, H)).to(torch.bfloat16).pin_memory() for b in range(NBATCH)]
+    xs = [x.to(dev) for x in xs_host]
+    sel = torch.empty(ROWS, TOPK, dtype=torch.int64, device=dev)
+    rw = torch.empty(ROWS, TOPK, dtype=torch.float16, device=dev)
+    ws = moe.decode_workspace(H, I, dev)
+    y = torch.zeros(ROWS, H, dtype=torch.float32, device=dev)
+    f = torch.zeros(ROWS, H, dtype=torch.float32, device=dev)
+    x_in = torch.empty(ROWS, H, dtype=torch.bfloat16, device=dev)
+    f_host = torch.empty(ROWS, H, dtype=torch.float32).pin_memory()
+
+    def step(x):
+        moe.router_fused(x, wt, bias, None, None, sel, rw, TOPK, 1.0)
+        moe.decode(tabs, x, sel, rw, y, ws)
+        moe.moe4_combine(f, 0, y, ROWS, 0)
+
+    # distinct experts per batch (for the algorithmic byte count)
+    distinct = []
+    for b in range(NBATCH):
+        moe.router_fused(xs[b], wt, bias, None, None, sel, rw, TOPK, 1.0)
+        distinct.append(int(torch.unique(sel).numel()))
+    for i in range(warmup):
+        step(xs[i % NBATCH])
+    torch.cuda.synchronize()
+    moe.set_profiling(True)
+    phase = np.zeros(3)
+    l0 = moe.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as cs:
+        torch.cuda.synchronize()
+        ev0.record()
+        for i in range(steps):
+            step(xs[i % NBATCH])
+        ev1.record()
+        torch.cuda.synchronize()
+        ms = ev0.elapsed_time(ev1)
+        if len(cs.samples) < 5:           # very short runs: keep the same load going so the clock record is not empty
+            t_end = time.time() + 0.4
+            while time.time() < t_end:
+                step(xs[0]); torch.cuda.synchronize()
+    launches = moe.launch_count() - l0
+    # phase durations: a second pass over the same steps, one readback per step (the readback waits for the step)
+    for i in range(steps):
+        step(xs[i % NBATCH])
+        phase += np.array(moe.decode_phase_times())
+    phase /= steps
+    moe.set_profiling(False)
+    status = moe.ws_status(ws)
+    mean_d = float(np.mean([distinct[i % NBATCH] for i in range(steps)]))
+    gate_up_bytes = (mean_d + 1) * GATE_UP_BYTES
+    layer_bytes = (mean_d + 1) * EXPERT_BYTES + E * H * 2 + ROWS * H * 6
+    peak, peak_kind = measured_peaks()
+    achieved = gate_up_bytes / (phase[1] * 1e-3) / 1e9
+    ms_per_step = ms / steps
+
+    # end to end: host buffers in, host buffer out, every step
+    for i in range(3):
+        x_in.copy_(xs_host[i % NBATCH], non_blocking=True); step(x_in); f_host.copy_(f, non_blocking=True)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for i in range(steps):
+        x_in.copy_(xs_host[i % NBATCH], non_blocking=True)
+        step(x_in)
+        f_host.copy_(f, non_blocking=True)
+        torch.cuda.synchronize()
+    e2e_s = (time.perf_counter() - t0) / steps
+
+    cb = cpu_reference_arm(20, 3) if not args.no_cpu else None
+    line = {
+        "metric": METRIC, "value": ROWS / (ms_per_step * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int4 x fp16 -> fp32",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD, "l2": "inputs larger than L2: ~2 GB of weights streamed per step, 8 input batches in a ring",
+                   "distinct_experts_per_step": mean_d},
+        "us_per_layer": ms_per_step * 1e3,
+        "layer_hbm_gbs": layer_bytes / (ms_per_step * 1e-3) / 1e9,
+        "layer_hbm_frac": layer_bytes / (ms_per_step * 1e-3) / 1e9 / peak,
+        "phase_us": {"prepare": phase[0] * 1e3, "gate_up": phase[1] * 1e3, "down": phase[2] * 1e3},
+        "roofline": {"bound": "hbm", "kernel": "decode_gate_up_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
+                     "algorithmic_bytes_per_launch": gate_up_bytes},
+        "e2e": {"value": ROWS / e2e_s, "unit": UNIT, "h2d_bytes_per_step": ROWS * H * 2, "d2h_bytes_per_step": ROWS * H * 4,
+                "us_per_layer": e2e_s * 1e6},
+        "gpu_launches": int(launches), "device_status": int(status), "clocks": cs.summary(),
+    }
+    if cb:
+        line["cpu_baseline"] = cb
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -55,7 +55,8 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint4* __restrict__ 
             {
                 const int cc = nib >> 2, h = (nib >> 1) & 1, rh = nib & 1;
                 const int row = gr * 64 + s * 16 + rh * 8 + g, k = kb * 64 + t * 16 + h * 8 + qq * 2 + cc;
-                const float scale = group ? bf16_bits_to_float(((const uint16_t*) sc)[(size_t) (k / group) * N + row]) : ((const float*) sc)[row];
+                const float scale = group ? bf16_bits_to_float(((const uint16_t*) sc)[((size_t) (row >> 6) * (K / group) + k / group) * 64 + (row & 7) * 8 + ((row & 63) >> 3)])
+                                          : ((const float*) sc)[row];
                 out[(size_t) row * K + k] = __float2half_rn((float) ((int) ((ww[t] >> (4 * nib)) & 15) - 8) * scale);
             }
     }
@@ -99,6 +100,9 @@ int hmoe_decode(const hmoe_layer* layer, const void* x, int x_dtype, const int64
     if (!layer) return fail(HMOE_E_ARG, "hmoe_decode: null layer");
     return decode_launch(layer, x, x_dtype, sel, rw, R, lo, n_local, act_quant, y, ws, ws_bytes, (cudaStream_t) stream);
 }
+
+int hmoe_set_profiling(int on) { return decode_set_profiling(on); }
+int hmoe_decode_phase_times(float* ms3) { return ms3 ? decode_phase_times(ms3) : fail(HMOE_E_ARG, "hmoe_decode_phase_times: null pointer"); }
 
 int hmoe_combine(float* f, const float* o, float* y, int64_t n, const float* o2, void* stream)
 {

@@ -14,7 +14,7 @@ enum : unsigned { ST_WAIT_TIMEOUT = 1u, ST_BAD_INDEX = 2u };
 constexpr int TOPK_MAX = 8;
 constexpr int MAXR = 16;                  // decode rows per call (tokens x (1 + MTP drafts))
 constexpr int MAXS = MAXR * TOPK_MAX + 1; // distinct experts of a decode call + the shared expert
-constexpr int MAXT = MAXS + 2;            // 8-row tiles: one per slot, one more per slot with > 8 rows (at most 2 + shared)
+constexpr int MAXT = MAXR * TOPK_MAX + 2; // 8-row tiles: at most one per pick, two for a 16-row shared expert
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t) __cvta_generic_to_shared(p); }
 
@@ -151,20 +151,19 @@ __device__ __forceinline__ float det_expf(float x)
 }
 
 // Routing of one decode call, built once per call by the prepare kernel and read by the expert kernels.
-// Slots are the distinct selected experts in ascending id order (as the reference's in-kernel route() orders them,
-// runtime/tier/moe4/moe4.cu:86-110), followed by the shared expert if there is one. Each slot lists the rows that picked
-// it; those rows are the columns of its MMA tiles (8 per tile).
+// The distinct selected experts are taken in ascending id order (as the reference's in-kernel route() orders them,
+// runtime/tier/moe4/moe4.cu:86-110), followed by the shared expert if there is one. Each expert's rows are cut into
+// tiles of <= 8 rows: a tile is the unit the expert kernels work on (its rows are the 8 columns of the MMAs). An expert
+// picked by more than 8 rows therefore appears as two tiles and is streamed twice (the second pass hits L2).
 struct Route
 {
-    int m;                         // routed slots
-    int nslots;                    // m + (shared ? 1 : 0)
-    int ntiles;                    // 8-row tiles over all slots
-    int pad;
-    short expert[MAXS];            // local expert id of the slot (-1 = shared)
-    short tile0[MAXS];             // first tile of the slot
-    unsigned char nrows[MAXS];     // rows that picked the slot
-    unsigned char rows[MAXS][MAXR];// their row numbers, ascending; entries >= nrows are 255
-    float w[MAXS][MAXR];           // routing weight per listed row (summed over repeated picks)
+    int m;                          // distinct routed experts
+    int ntiles;
+    int pad[2];
+    short expert[MAXT];             // local expert id of the tile (-1 = shared)
+    unsigned char nrows[MAXT];      // rows in the tile (1..8)
+    unsigned char rows[MAXT][8];    // their row numbers, ascending; entries >= nrows repeat the first row
+    float w[MAXT][8];               // routing weight per listed row (summed over repeated picks), 0 beyond nrows
 };
 
 }  // namespace hmoe

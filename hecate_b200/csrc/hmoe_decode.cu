@@ -3,20 +3,21 @@
 // Replaces the reference's moe4 decode kernels (runtime/tier/moe4/moe4.cu:361-676: moe4_a_kernel, moe4_act_kernel,
 // moe4_b_kernel and their in-kernel route()) behind the same operator surface: packed int4 experts in the reference's
 // fragment order, routing as (sel, rw), fp32 output accumulated into y. Differences by design: 16 rows in one pass over
-// the weights, a scale per 128 input columns (or the reference's scale per row), an int4 shared expert as one more slot.
+// the weights, a scale per 128 input columns (or the reference's scale per row), an int4 shared expert as one more expert.
 //
 // Three launches per call:
-//   prepare : one block per row rewrites x as fp16 in the column order the MMAs read (optionally after the CPU engine's
-//             int8 round trip), one more block builds the Route (distinct experts, their rows and weights).
-//   gate_up : persistent blocks, one per SM. A work item is (slot, 64-row group of the expert's gate and up matrices);
-//             items are dealt out as contiguous ranges. One producer thread streams the item's packed codes into a
-//             shared-memory ring with 1-D bulk copies (16 KB gate + 16 KB up per stage, mbarrier completion); eight
-//             consumer warps (four per matrix, each owning every fourth 128-column group) turn the codes into fp16 MMA
-//             fragments in registers and run m16n8k16 MMAs against only the rows that picked the expert. The block then
-//             reduces the eight partial tiles through shared memory, applies SiLU(g) * u * routing weight and writes the
-//             result as the next kernel's MMA operand.
-//   down    : same streaming structure over (64-row group of the output, slot) items, slot fastest, so that a block adds
-//             every slot's contribution to a 64-column slice of y in shared memory and issues one fp32 reduction to global
+//   prepare : one block per row rewrites x as fp16 in the column order the MMAs read (in the int8 mode: the CPU engine's
+//             int8 codes as fp16 integers plus a scale per 32 columns), one more block builds the Route: the distinct
+//             experts, each with the <= 8 rows that picked it as one tile.
+//   gate_up : persistent blocks, one per SM, 16 warps. A work item is (tile, 64-row group of the expert's gate and up
+//             matrices); items are dealt out as contiguous ranges. Lane 0 of warp 0 keeps a four-stage shared-memory ring
+//             full with 1-D bulk copies of the packed codes (16 KB gate + 16 KB up per stage, mbarrier completion). Warp w
+//             owns 64-column block 8 s + w % 8 of stage s of matrix w / 8: it turns the codes into fp16 MMA fragments in
+//             registers and runs m16n8k16 MMAs against the tile's rows, whose fragments and scales it prefetches into
+//             registers one stage ahead. At the end of an item the block reduces the sixteen partial tiles through shared
+//             memory, applies SiLU(g) * u * routing weight and writes the result as the next kernel's MMA operand.
+//   down    : same streaming structure over (64-row group of the output, tile) items, tile fastest, so that a block adds
+//             every tile's contribution to a 64-column slice of y in shared memory and issues one fp32 reduction to global
 //             memory per slice.
 // Both streaming kernels are bound by HBM: algorithmic bytes per call are (distinct experts + shared) x the expert's
 // packed size plus scales.
@@ -27,11 +28,11 @@ namespace hmoe {
 
 namespace {
 
-constexpr int CW = 8;                    // consumer warps
-constexpr int NTHREADS = (CW + 1) * 32;  // + one producer warp
-constexpr int STAGE_BYTES = 32768;
+constexpr int CW = 16;                   // warps per block
+constexpr int NTHREADS = CW * 32;
+constexpr int STAGE_BYTES = 32768;       // 16 units of 64 rows x 64 columns
 constexpr int NSTAGE = 4;
-constexpr int RED_FLOATS = 2 * 4 * 64 * 16;   // gate_up partial tiles: [matrix][k quarter][64 rows][16 columns]
+constexpr int RED_FLOATS = CW * 64 * 8;  // gate_up partial tiles: [warp][64 rows][8 columns]
 constexpr int YACC_FLOATS = MAXR * 64;
 
 struct SmemLayout
@@ -43,13 +44,11 @@ struct SmemLayout
     static constexpr int total = flags + 16;
 };
 
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory"); }
-
 // ---------------------------------------------------------------------------------------------------------------------
 // prepare
 __global__ void __launch_bounds__(256) decode_prepare_kernel(const void* __restrict__ x, int x_bf16, const int64_t* __restrict__ sel,
     const __half* __restrict__ rw, int R, int H, int topk, int lo, int n_local, int has_shared, int act_quant,
-    __half* __restrict__ xf, Route* __restrict__ route)
+    __half* __restrict__ xf, float* __restrict__ xscale, Route* __restrict__ route)
 {
     const int tid = threadIdx.x;
     if ((int) blockIdx.x < R)
@@ -72,14 +71,16 @@ __global__ void __launch_bounds__(256) decode_prepare_kernel(const void* __restr
             }
             if (act_quant)
             {
-                // the CPU engine's activation format (runtime/tier/cpuband.cpp:106-111): int8 with a scale per 32 values
+                // the CPU engine's activation format (runtime/tier/cpuband.cpp:106-111): int8 with a scale per 32 values.
+                // The codes themselves go to the MMAs (exact in fp16), the scale is applied to the fp32 sums.
                 float m = 0.f;
                 #pragma unroll
                 for (int k = 0; k < 32; ++k) m = fmaxf(m, fabsf(v[k]));
                 const float s = m > 0.f ? __fdiv_rn(m, 127.f) : 1.f;
                 const float inv = __fdiv_rn(1.f, s);
                 #pragma unroll
-                for (int k = 0; k < 32; ++k) v[k] = __fmul_rn((float) __float2int_rn(__fmul_rn(v[k], inv)), s);
+                for (int k = 0; k < 32; ++k) v[k] = (float) __float2int_rn(__fmul_rn(v[k], inv));
+                xscale[(size_t) r * (H / 32) + gi] = s;
             }
             const int kb = gi >> 1, p0 = (gi & 1) * 16;
             uint32_t* dst = (uint32_t*) (xf + (size_t) r * H + kb * 64);
@@ -92,9 +93,12 @@ __global__ void __launch_bounds__(256) decode_prepare_kernel(const void* __restr
         }
         return;
     }
-    // routing block
+    // routing block: slot = distinct expert (ascending id), then the shared expert; tiles of <= 8 rows per slot
     __shared__ int flag[256];
-    __shared__ short slot_of[256];
+    __shared__ short slot_e[MAXS];
+    __shared__ unsigned char s_n[MAXS], s_rows[MAXS][MAXR];
+    __shared__ float s_w[MAXS][MAXR];
+    __shared__ short s_tile0[MAXS];
     __shared__ int m_sh;
     for (int i = tid; i < 256; i += blockDim.x) flag[i] = 0;
     __syncthreads();
@@ -107,228 +111,180 @@ __global__ void __launch_bounds__(256) decode_prepare_kernel(const void* __restr
     if (tid == 0)
     {
         int m = 0;
-        for (int e = 0; e < n_local; ++e) if (flag[e]) { slot_of[e] = (short) m; route->expert[m] = (short) e; ++m; }
-        if (has_shared) route->expert[m] = -1;
+        for (int e = 0; e < n_local; ++e) if (flag[e]) slot_e[m++] = (short) e;
         m_sh = m;
-        route->m = m; route->nslots = m + (has_shared ? 1 : 0); route->pad = 0;
+        if (has_shared) slot_e[m] = -1;
     }
     __syncthreads();
-    const int m = m_sh;
-    for (int j = tid; j < m + (has_shared ? 1 : 0); j += blockDim.x)
+    const int m = m_sh, ns = m + (has_shared ? 1 : 0);
+    for (int j = tid; j < ns; j += blockDim.x)
     {
         int n = 0;
         if (j < m)
         {
-            const int e = route->expert[j];
+            const int e = slot_e[j];
             for (int r = 0; r < R; ++r)
             {
                 float ws = 0.f; bool hit = false;
                 for (int k = 0; k < topk; ++k)
                     if ((int) (sel[r * topk + k] - lo) == e) { ws += __half2float(rw[r * topk + k]); hit = true; }
-                if (hit) { route->rows[j][n] = (unsigned char) r; route->w[j][n] = ws; ++n; }
+                if (hit) { s_rows[j][n] = (unsigned char) r; s_w[j][n] = ws; ++n; }
             }
         }
         else
-            for (int r = 0; r < R; ++r) { route->rows[j][n] = (unsigned char) r; route->w[j][n] = 1.f; ++n; }
-        route->nrows[j] = (unsigned char) n;
-        for (int i = n; i < MAXR; ++i) { route->rows[j][i] = 255; route->w[j][i] = 0.f; }
+            for (int r = 0; r < R; ++r) { s_rows[j][n] = (unsigned char) r; s_w[j][n] = 1.f; ++n; }
+        s_n[j] = (unsigned char) n;
     }
     __syncthreads();
     if (tid == 0)
     {
         int t = 0;
-        for (int j = 0; j < m + (has_shared ? 1 : 0); ++j) { route->tile0[j] = (short) t; t += (route->nrows[j] + 7) / 8; }
-        route->ntiles = t;
+        for (int j = 0; j < ns; ++j) { s_tile0[j] = (short) t; t += (s_n[j] + 7) / 8; }
+        route->m = m; route->ntiles = t; route->pad[0] = route->pad[1] = 0;
     }
+    __syncthreads();
+    for (int j = tid; j < ns; j += blockDim.x)
+        for (int b = 0; b * 8 < s_n[j]; ++b)
+        {
+            const int t = s_tile0[j] + b, n = s_n[j] - b * 8 < 8 ? s_n[j] - b * 8 : 8;
+            route->expert[t] = slot_e[j]; route->nrows[t] = (unsigned char) n;
+            for (int i = 0; i < 8; ++i)
+            {
+                route->rows[t][i] = s_rows[j][b * 8 + (i < n ? i : 0)];
+                route->w[t][i] = i < n ? s_w[j][b * 8 + i] : 0.f;
+            }
+        }
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// One consumer warp's share of one ring stage: `nkb` (1 or 2) 64-column blocks of a 64-row group, i.e. one 128-column
-// scale group. wsm = shared address of the warp's first 2 KB unit; xrow[nt] = this lane's activation row for tile nt
-// (already offset to the first of the blocks and to the lane's 32-byte chunk). Adds into acc[strip][nt][4].
-template <int NT, bool GROUPED>
-__device__ __forceinline__ void consume_group(uint32_t wsm, int nkb, const char* const* xrow, const uint16_t* sc, int sc_ok,
-                                              float (*acc)[NT][4], int lane)
+// What a warp needs from global memory for one 64-column block, fetched one ring stage ahead.
+struct Pre
 {
-    float part[4][NT][4];
-    uint16_t sb[8];
-    if (GROUPED)
-    {
-        // scales of rows strip*16 + g and + 8 for this 128-column group (bf16)
-        #pragma unroll
-        for (int s = 0; s < 4; ++s) { sb[2 * s] = sc_ok ? __ldg(sc + s * 16) : (uint16_t) 0; sb[2 * s + 1] = sc_ok ? __ldg(sc + s * 16 + 8) : (uint16_t) 0; }
-        #pragma unroll
-        for (int s = 0; s < 4; ++s)
-            #pragma unroll
-            for (int nt = 0; nt < NT; ++nt)
-                #pragma unroll
-                for (int i = 0; i < 4; ++i) part[s][nt][i] = 0.f;
-    }
-    for (int kbi = 0; kbi < nkb; ++kbi)
-    {
-        uint4 w4[4];
-        #pragma unroll
-        for (int s = 0; s < 4; ++s) w4[s] = lds128(wsm + kbi * 2048 + s * 512 + lane * 16);
-        uint32_t bx[NT][8];
-        #pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
-        {
-            const uint4 b0 = ldg128(xrow[nt] + kbi * 128), b1 = ldg128(xrow[nt] + kbi * 128 + 16);
-            bx[nt][0] = b0.x; bx[nt][1] = b0.y; bx[nt][2] = b0.z; bx[nt][3] = b0.w;
-            bx[nt][4] = b1.x; bx[nt][5] = b1.y; bx[nt][6] = b1.z; bx[nt][7] = b1.w;
-        }
-        #pragma unroll
-        for (int s = 0; s < 4; ++s)
-        {
-            const uint32_t ww[4] = {w4[s].x, w4[s].y, w4[s].z, w4[s].w};
-            #pragma unroll
-            for (int t = 0; t < 4; ++t)
-            {
-                uint32_t a[4];
-                frag_from_codes(ww[t], a);
-                #pragma unroll
-                for (int nt = 0; nt < NT; ++nt)
-                    mma_f16(GROUPED ? part[s][nt] : acc[s][nt], a, bx[nt][2 * t], bx[nt][2 * t + 1]);
-            }
-        }
-    }
-    if (GROUPED)
-    {
-        #pragma unroll
-        for (int s = 0; s < 4; ++s)
-        {
-            const float s0 = bf16_bits_to_float(sb[2 * s]), s1 = bf16_bits_to_float(sb[2 * s + 1]);
-            #pragma unroll
-            for (int nt = 0; nt < NT; ++nt)
-            {
-                acc[s][nt][0] = fmaf(s0, part[s][nt][0], acc[s][nt][0]); acc[s][nt][1] = fmaf(s0, part[s][nt][1], acc[s][nt][1]);
-                acc[s][nt][2] = fmaf(s1, part[s][nt][2], acc[s][nt][2]); acc[s][nt][3] = fmaf(s1, part[s][nt][3], acc[s][nt][3]);
-            }
-        }
-    }
-}
+    uint32_t bx[8];         // activation fragments of this lane's tile row: word 2t + h of 16-column step t
+    uint4 sc;               // GROUPED: bf16 scales of rows strip*16 + g (low half of word `strip`) and + 8 (high half)
+    float2 sx[2];           // Q8: activation scales of the block's two 32-column halves for tile columns 2q and 2q + 1
+};
 
 struct DecodeArgs
 {
-    int H, I, group, act_quant;
+    int H, I;
     const int64_t* gate_w; const int64_t* up_w; const int64_t* down_w;
     const int64_t* gate_s; const int64_t* up_s; const int64_t* down_s;
     const void* sh_gw; const void* sh_uw; const void* sh_dw; const void* sh_gs; const void* sh_us; const void* sh_ds;
     const Route* route;
     const __half* xf;      // [R][H] prepared rows
+    const float* xscale;   // [R][H/32] (Q8)
     __half* act;           // [tiles][8][I] gate_up output = down input
+    float* ascale;         // [tiles][8][I/32] (Q8)
     float* y;              // [R][H]
     unsigned* status;
 };
 
-// ---------------------------------------------------------------------------------------------------------------------
-// gate_up
-template <int NT, bool GROUPED>
-__device__ __forceinline__ void gate_up_item(const DecodeArgs& a, int slot, int gr, int e, uint32_t ring, uint32_t full0, uint32_t empty0,
-                                             float* red, volatile int* abort_flag, uint32_t& it, int warp, int lane)
+// One 64-column block of a 64-row group: 4 strips x 4 steps of MMAs on the tile, added into acc with the scales applied.
+template <bool GROUPED, bool Q8>
+__device__ __forceinline__ void consume_block(uint32_t wsm, const Pre& pr, float (*acc)[4], int lane)
 {
-    const int KB = a.H / 64, S = (KB + 7) / 8;
-    const int mat = warp >> 2, kq = warp & 3, g = lane >> 2, q = lane & 3;
-    const Route* rt = a.route;
-    const int nrows = rt->nrows[slot];
-    float acc[4][NT][4];
+    uint4 w4[4];
+    #pragma unroll
+    for (int s = 0; s < 4; ++s) w4[s] = lds128(wsm + s * 512 + lane * 16);
+    const uint32_t scw[4] = {pr.sc.x, pr.sc.y, pr.sc.z, pr.sc.w};
     #pragma unroll
     for (int s = 0; s < 4; ++s)
-        #pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
-            #pragma unroll
-            for (int i = 0; i < 4; ++i) acc[s][nt][i] = 0.f;
-    const char* xbase[NT];
-    #pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
     {
-        int r = rt->rows[slot][nt * 8 + g];
-        if (r == 255) r = rt->rows[slot][0];
-        xbase[nt] = (const char*) (a.xf + (size_t) r * a.H) + q * 32;
-    }
-    const uint16_t* scb = nullptr;
-    if (GROUPED)
-    {
-        const void* sp = e >= 0 ? (const void*) (mat ? a.up_s[e] : a.gate_s[e]) : (mat ? a.sh_us : a.sh_gs);
-        scb = (const uint16_t*) sp + gr * 64 + g;      // + kg * I + strip * 16 (+ 8)
-    }
-    for (int s = 0; s < S; ++s, ++it)
-    {
-        const uint32_t st = it % NSTAGE, par = (it / NSTAGE) & 1;
-        if (!mbar_wait(full0 + st * 8, par, abort_flag, a.status)) return;
-        const int kb = 8 * s + 2 * kq;
-        if (kb < KB)
+        const uint32_t ww[4] = {w4[s].x, w4[s].y, w4[s].z, w4[s].w};
+        float s0 = 1.f, s1 = 1.f;
+        if (GROUPED) { s0 = __uint_as_float(scw[s] << 16); s1 = __uint_as_float(scw[s] & 0xffff0000u); }
+        if (!GROUPED && !Q8)
         {
-            const int nkb = KB - kb < 2 ? KB - kb : 2;
-            const char* xr[NT];
             #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) xr[nt] = xbase[nt] + kb * 128;
-            consume_group<NT, GROUPED>(ring + st * STAGE_BYTES + mat * (STAGE_BYTES / 2) + 2 * kq * 2048, nkb, xr,
-                                       scb + (size_t) (kb >> 1) * a.I, 1, acc, lane);
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(empty0 + st * 8);
-    }
-    // partial tiles -> shared memory: red[mat][kq][row][col], col stride CP
-    constexpr int CP = 8 * NT;
-    float* rp = red + (mat * 4 + kq) * 64 * CP;
-    #pragma unroll
-    for (int s = 0; s < 4; ++s)
-        #pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
-        {
-            *(float2*) (rp + (s * 16 + g) * CP + nt * 8 + 2 * q) = make_float2(acc[s][nt][0], acc[s][nt][1]);
-            *(float2*) (rp + (s * 16 + g + 8) * CP + nt * 8 + 2 * q) = make_float2(acc[s][nt][2], acc[s][nt][3]);
-        }
-    consumer_sync();
-    // act = silu(gate) * up * routing weight; this warp handles column `warp` (+ 8) of the tile, each lane two rows
-    const int n0 = 2 * lane;
-    float sg0 = 1.f, sg1 = 1.f, su0 = 1.f, su1 = 1.f;
-    if (!GROUPED)
-    {
-        const float* gsp = e >= 0 ? (const float*) a.gate_s[e] : (const float*) a.sh_gs;
-        const float* usp = e >= 0 ? (const float*) a.up_s[e] : (const float*) a.sh_us;
-        sg0 = __ldg(gsp + gr * 64 + n0); sg1 = __ldg(gsp + gr * 64 + n0 + 1);
-        su0 = __ldg(usp + gr * 64 + n0); su1 = __ldg(usp + gr * 64 + n0 + 1);
-    }
-    #pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
-    {
-        const int col = nt * 8 + warp;
-        float v0 = 0.f, v1 = 0.f;
-        if (col < nrows)
-        {
-            float g0 = 0.f, g1 = 0.f, u0 = 0.f, u1 = 0.f;
-            #pragma unroll
-            for (int k = 0; k < 4; ++k)
+            for (int t = 0; t < 4; ++t)
             {
-                g0 += red[((0 * 4 + k) * 64 + n0) * CP + col]; g1 += red[((0 * 4 + k) * 64 + n0 + 1) * CP + col];
-                u0 += red[((1 * 4 + k) * 64 + n0) * CP + col]; u1 += red[((1 * 4 + k) * 64 + n0 + 1) * CP + col];
+                uint32_t a[4];
+                frag_from_codes(ww[t], a);
+                mma_f16(acc[s], a, pr.bx[2 * t], pr.bx[2 * t + 1]);
             }
-            g0 *= sg0; g1 *= sg1; u0 *= su0; u1 *= su1;
-            const float wr = rt->w[slot][col];
-            v0 = g0 / (1.f + expf(-g0)) * u0 * wr;
-            v1 = g1 / (1.f + expf(-g1)) * u1 * wr;
         }
-        if (a.act_quant)
+        else if (!Q8)
         {
-            // second int8 round trip of the CPU engine (cpuband.cpp:200-207): groups of 32 consecutive outputs = 16 lanes
-            float m = fmaxf(fabsf(v0), fabsf(v1));
+            float part[4] = {0.f, 0.f, 0.f, 0.f};
             #pragma unroll
-            for (int o = 8; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-            const float s = m > 0.f ? __fdiv_rn(m, 127.f) : 1.f;
-            const float inv = __fdiv_rn(1.f, s);
-            v0 = __fmul_rn((float) __float2int_rn(__fmul_rn(v0, inv)), s);
-            v1 = __fmul_rn((float) __float2int_rn(__fmul_rn(v1, inv)), s);
+            for (int t = 0; t < 4; ++t)
+            {
+                uint32_t a[4];
+                frag_from_codes(ww[t], a);
+                mma_f16(part, a, pr.bx[2 * t], pr.bx[2 * t + 1]);
+            }
+            acc[s][0] = fmaf(s0, part[0], acc[s][0]); acc[s][1] = fmaf(s0, part[1], acc[s][1]);
+            acc[s][2] = fmaf(s1, part[2], acc[s][2]); acc[s][3] = fmaf(s1, part[3], acc[s][3]);
         }
-        const __half2 h = __floats2half2_rn(v0, v1);
-        uint32_t* dst = (uint32_t*) (a.act + ((size_t) (rt->tile0[slot] + nt) * 8 + warp) * a.I + gr * 64);
-        dst[frag_pos(lane)] = *(const uint32_t*) &h;
+        else
+        {
+            // int8 activations: exact integer sums per 32 columns, then one multiply by (activation scale x weight scale)
+            #pragma unroll
+            for (int hf = 0; hf < 2; ++hf)
+            {
+                float part[4] = {0.f, 0.f, 0.f, 0.f};
+                #pragma unroll
+                for (int t = 2 * hf; t < 2 * hf + 2; ++t)
+                {
+                    uint32_t a[4];
+                    frag_from_codes(ww[t], a);
+                    mma_f16(part, a, pr.bx[2 * t], pr.bx[2 * t + 1]);
+                }
+                const float x0 = hf ? pr.sx[0].y : pr.sx[0].x, x1 = hf ? pr.sx[1].y : pr.sx[1].x;
+                acc[s][0] = fmaf(part[0], x0 * s0, acc[s][0]); acc[s][1] = fmaf(part[1], x1 * s0, acc[s][1]);
+                acc[s][2] = fmaf(part[2], x0 * s1, acc[s][2]); acc[s][3] = fmaf(part[3], x1 * s1, acc[s][3]);
+            }
+        }
     }
-    consumer_sync();
 }
 
-template <bool GROUPED>
+// what a lane keeps about the item it is working on
+struct Item
+{
+    int tile, gr, e, nrows;
+    const char* xb;         // this lane's activation row, offset to its 32-byte chunk of block 0
+    const float* xs[2];     // Q8: activation scale rows of tile columns 2q, 2q + 1
+    const char* sc;         // GROUPED: scale words of this lane's rows for the item's 64-row group (column group 0)
+};
+
+template <bool GROUPED, bool Q8>
+__device__ __forceinline__ void prefetch(const Item& it, int kb, int KB, Pre& pr)
+{
+    if (kb >= KB) return;
+    const uint4 b0 = ldg128(it.xb + kb * 128), b1 = ldg128(it.xb + kb * 128 + 16);
+    pr.bx[0] = b0.x; pr.bx[1] = b0.y; pr.bx[2] = b0.z; pr.bx[3] = b0.w;
+    pr.bx[4] = b1.x; pr.bx[5] = b1.y; pr.bx[6] = b1.z; pr.bx[7] = b1.w;
+    if (Q8) { pr.sx[0] = *(const float2*) (it.xs[0] + 2 * kb); pr.sx[1] = *(const float2*) (it.xs[1] + 2 * kb); }
+    if (GROUPED) pr.sc = ldg128_nc(it.sc + (size_t) (kb >> 1) * 128);
+}
+
+// The block's stream of ring stages. Lane 0 of warp 0 is the producer: `fill` issues the copies of stage number i.
+// Keeps up to NSTAGE stages in flight; blocks only if the stage the consumers need next has not been issued.
+template <typename Fill>
+__device__ __forceinline__ bool produce(uint32_t& issued, uint32_t total, uint32_t it, uint32_t empty0, volatile int* abort_flag,
+                                        unsigned* status, Fill fill)
+{
+    while (issued < total && issued < it + NSTAGE)
+    {
+        if (issued >= NSTAGE)
+        {
+            const uint32_t bar = empty0 + (issued % NSTAGE) * 8, par = ((issued / NSTAGE) - 1) & 1;
+            if (!mbar_try(bar, par))
+            {
+                if (issued > it) return true;                       // enough in flight for now, try again next stage
+                if (!mbar_wait(bar, par, abort_flag, status)) return false;
+            }
+        }
+        fill(issued);
+        ++issued;
+    }
+    return true;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// gate_up
+template <bool GROUPED, bool Q8>
 __global__ void __launch_bounds__(NTHREADS, 1) decode_gate_up_kernel(const DecodeArgs a)
 {
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -346,121 +302,119 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_gate_up_kernel(const Decod
     __syncthreads();
     const Route* rt = a.route;
     const int NG = a.I / 64, KB = a.H / 64, S = (KB + 7) / 8;
-    const int P = rt->nslots * NG;
+    const int P = rt->ntiles * NG;
     const int p0 = (int) ((long long) P * blockIdx.x / gridDim.x), p1 = (int) ((long long) P * (blockIdx.x + 1) / gridDim.x);
-    if (warp == CW)
-    {
-        if (lane == 0)
+    const int mat = warp >> 3, kw = warp & 7, g = lane >> 2, q = lane & 3;
+    const uint32_t total = (uint32_t) (p1 - p0) * S;
+    uint32_t issued = 0;
+    auto fill = [&](uint32_t i) {
+        const int p = p0 + (int) (i / S), s = (int) (i % S);
+        const int tile = p / NG, gr = p % NG, e = rt->expert[tile];
+        const char* gw = (const char*) (e >= 0 ? (const void*) a.gate_w[e] : a.sh_gw) + ((size_t) gr * KB + 8 * s) * 2048;
+        const char* uw = (const char*) (e >= 0 ? (const void*) a.up_w[e] : a.sh_uw) + ((size_t) gr * KB + 8 * s) * 2048;
+        const uint32_t st = i % NSTAGE, bytes = (KB - 8 * s < 8 ? KB - 8 * s : 8) * 2048;
+        mbar_expect_tx(full0 + st * 8, 2 * bytes);
+        bulk_g2s(ring + st * STAGE_BYTES, gw, bytes, full0 + st * 8);
+        bulk_g2s(ring + st * STAGE_BYTES + STAGE_BYTES / 2, uw, bytes, full0 + st * 8);
+    };
+    auto load_item = [&](int p) {
+        Item it;
+        it.tile = p / NG; it.gr = p % NG; it.e = rt->expert[it.tile]; it.nrows = rt->nrows[it.tile];
+        it.xb = (const char*) (a.xf + (size_t) rt->rows[it.tile][g] * a.H) + q * 32;
+        if (Q8)
         {
-            uint32_t it = 0;
-            bool ok = true;
-            for (int p = p0; p < p1 && ok; ++p)
-            {
-                const int slot = p / NG, gr = p % NG, e = rt->expert[slot];
-                const char* gw = (const char*) (e >= 0 ? (const void*) a.gate_w[e] : a.sh_gw) + (size_t) gr * KB * 2048;
-                const char* uw = (const char*) (e >= 0 ? (const void*) a.up_w[e] : a.sh_uw) + (size_t) gr * KB * 2048;
-                for (int s = 0; s < S; ++s, ++it)
-                {
-                    const uint32_t st = it % NSTAGE;
-                    if (it >= NSTAGE && !mbar_wait(empty0 + st * 8, ((it / NSTAGE) - 1) & 1, abort_flag, a.status)) { ok = false; break; }
-                    const int nkb = KB - 8 * s < 8 ? KB - 8 * s : 8;
-                    const uint32_t bytes = nkb * 2048;
-                    mbar_expect_tx(full0 + st * 8, 2 * bytes);
-                    bulk_g2s(ring + st * STAGE_BYTES, gw + (size_t) s * 16384, bytes, full0 + st * 8);
-                    bulk_g2s(ring + st * STAGE_BYTES + STAGE_BYTES / 2, uw + (size_t) s * 16384, bytes, full0 + st * 8);
-                }
-            }
+            it.xs[0] = a.xscale + (size_t) rt->rows[it.tile][2 * q] * (a.H / 32);
+            it.xs[1] = a.xscale + (size_t) rt->rows[it.tile][2 * q + 1] * (a.H / 32);
         }
-    }
-    else
+        if (GROUPED)
+        {
+            const void* sp = it.e >= 0 ? (const void*) (mat ? a.up_s[it.e] : a.gate_s[it.e]) : (mat ? a.sh_us : a.sh_gs);
+            it.sc = (const char*) sp + ((size_t) it.gr * (a.H / 128) * 64 + g * 8) * 2;
+        }
+        return it;
+    };
+    if (p0 < p1)
     {
+        if (threadIdx.x == 0) produce(issued, total, 0, empty0, abort_flag, a.status, fill);
+        float acc[4][4];
+        #pragma unroll
+        for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+        Item cur = load_item(p0);
+        Pre pc;
+        prefetch<GROUPED, Q8>(cur, kw, KB, pc);
         uint32_t it = 0;
-        for (int p = p0; p < p1; ++p)
+        int p = p0, s = 0;
+        while (p < p1)
         {
-            const int slot = p / NG, gr = p % NG, e = rt->expert[slot];
-            if (rt->nrows[slot] > 8) gate_up_item<2, GROUPED>(a, slot, gr, e, ring, full0, empty0, red, abort_flag, it, warp, lane);
-            else gate_up_item<1, GROUPED>(a, slot, gr, e, ring, full0, empty0, red, abort_flag, it, warp, lane);
-            if (*abort_flag) break;
+            int np = p, ns = s + 1;
+            if (ns == S) { ns = 0; np = p + 1; }
+            Item nxt = cur;
+            Pre pn = pc;
+            if (np < p1)
+            {
+                if (ns == 0) nxt = load_item(np);
+                prefetch<GROUPED, Q8>(nxt, 8 * ns + kw, KB, pn);
+            }
+            if (threadIdx.x == 0) produce(issued, total, it, empty0, abort_flag, a.status, fill);   // a failure raises the abort flag
+            __syncwarp();
+            const uint32_t st = it % NSTAGE;
+            if (!mbar_wait(full0 + st * 8, (it / NSTAGE) & 1, abort_flag, a.status)) break;
+            if (8 * s + kw < KB)
+                consume_block<GROUPED, Q8>(ring + st * STAGE_BYTES + mat * (STAGE_BYTES / 2) + kw * 2048, pc, acc, lane);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty0 + st * 8);
+            ++it;
+            if (s == S - 1)
+            {
+                // partial tiles -> shared memory: red[warp][row][8 columns]
+                float* rp = red + warp * 64 * 8;
+                #pragma unroll
+                for (int ss = 0; ss < 4; ++ss)
+                {
+                    *(float2*) (rp + (ss * 16 + g) * 8 + 2 * q) = make_float2(acc[ss][0], acc[ss][1]);
+                    *(float2*) (rp + (ss * 16 + g + 8) * 8 + 2 * q) = make_float2(acc[ss][2], acc[ss][3]);
+                    acc[ss][0] = acc[ss][1] = acc[ss][2] = acc[ss][3] = 0.f;
+                }
+                __syncthreads();
+                // act = silu(gate) * up * routing weight. Warp w: tile column w / 2, rows 32 (w % 2) + lane of the group.
+                const int n = (warp & 1) * 32 + lane, col = warp >> 1;
+                float v = 0.f;
+                if (col < cur.nrows)
+                {
+                    float gg = 0.f, uu = 0.f;
+                    #pragma unroll
+                    for (int k = 0; k < 8; ++k) { gg += red[(k * 64 + n) * 8 + col]; uu += red[((8 + k) * 64 + n) * 8 + col]; }
+                    if (!GROUPED)
+                    {
+                        const float* gsp = cur.e >= 0 ? (const float*) a.gate_s[cur.e] : (const float*) a.sh_gs;
+                        const float* usp = cur.e >= 0 ? (const float*) a.up_s[cur.e] : (const float*) a.sh_us;
+                        gg *= __ldg(gsp + cur.gr * 64 + n); uu *= __ldg(usp + cur.gr * 64 + n);
+                    }
+                    v = gg / (1.f + expf(-gg)) * uu * rt->w[cur.tile][col];
+                }
+                const size_t row = (size_t) cur.tile * 8 + col;
+                if (Q8)
+                {
+                    // second int8 round trip of the CPU engine (cpuband.cpp:200-207): 32 consecutive outputs = this warp
+                    float m = fabsf(v);
+                    #pragma unroll
+                    for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+                    const float sc = m > 0.f ? __fdiv_rn(m, 127.f) : 1.f;
+                    v = (float) __float2int_rn(__fmul_rn(v, __fdiv_rn(1.f, sc)));
+                    if (lane == 0) a.ascale[row * (a.I / 32) + cur.gr * 2 + (warp & 1)] = sc;
+                }
+                a.act[row * a.I + cur.gr * 64 + frag_pos(n >> 1) * 2 + (n & 1)] = __float2half_rn(v);
+                __syncthreads();
+            }
+            cur = nxt; pc = pn; p = np; s = ns;
         }
     }
-    // Leave only when every copy this block issued has landed (a timed-out consumer may still have copies in flight):
-    // the producer thread drains the stages it filled but nobody consumed.
     __syncthreads();
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
 // down
-template <int NT, bool GROUPED>
-__device__ __forceinline__ void down_item(const DecodeArgs& a, int slot, int gr, int e, uint32_t ring, uint32_t full0, uint32_t empty0,
-                                          float* yacc, volatile int* abort_flag, uint32_t& it, int warp, int lane)
-{
-    const int KB = a.I / 64, S = (KB + 15) / 16;
-    const int g = lane >> 2, q = lane & 3;
-    const Route* rt = a.route;
-    const int nrows = rt->nrows[slot];
-    float acc[4][NT][4];
-    #pragma unroll
-    for (int s = 0; s < 4; ++s)
-        #pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
-            #pragma unroll
-            for (int i = 0; i < 4; ++i) acc[s][nt][i] = 0.f;
-    const char* xbase[NT];
-    #pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
-        xbase[nt] = (const char*) (a.act + ((size_t) (rt->tile0[slot] + nt) * 8 + g) * a.I) + q * 32;
-    const uint16_t* scb = nullptr;
-    if (GROUPED)
-    {
-        const void* sp = e >= 0 ? (const void*) a.down_s[e] : a.sh_ds;
-        scb = (const uint16_t*) sp + gr * 64 + g;
-    }
-    for (int s = 0; s < S; ++s, ++it)
-    {
-        const uint32_t st = it % NSTAGE, par = (it / NSTAGE) & 1;
-        if (!mbar_wait(full0 + st * 8, par, abort_flag, a.status)) return;
-        const int kb = 16 * s + 2 * warp;
-        if (kb < KB)
-        {
-            const int nkb = KB - kb < 2 ? KB - kb : 2;
-            const char* xr[NT];
-            #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) xr[nt] = xbase[nt] + kb * 128;
-            consume_group<NT, GROUPED>(ring + st * STAGE_BYTES + 2 * warp * 2048, nkb, xr, scb + (size_t) (kb >> 1) * a.H, 1, acc, lane);
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(empty0 + st * 8);
-    }
-    float sd[8];
-    #pragma unroll
-    for (int s = 0; s < 8; ++s) sd[s] = 1.f;
-    if (!GROUPED)
-    {
-        const float* dsp = e >= 0 ? (const float*) a.down_s[e] : (const float*) a.sh_ds;
-        #pragma unroll
-        for (int s = 0; s < 4; ++s) { sd[2 * s] = __ldg(dsp + gr * 64 + s * 16 + g); sd[2 * s + 1] = __ldg(dsp + gr * 64 + s * 16 + g + 8); }
-    }
-    // add this warp's partial (its share of the columns) into the block's slice accumulator, real row by real row
-    #pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
-        #pragma unroll
-        for (int c = 0; c < 2; ++c)
-        {
-            const int col = nt * 8 + 2 * q + c;
-            if (col < nrows)
-            {
-                float* yr = yacc + (int) rt->rows[slot][col] * 64;
-                #pragma unroll
-                for (int s = 0; s < 4; ++s)
-                {
-                    atomicAdd(yr + s * 16 + g, acc[s][nt][c] * sd[2 * s]);
-                    atomicAdd(yr + s * 16 + g + 8, acc[s][nt][2 + c] * sd[2 * s + 1]);
-                }
-            }
-        }
-}
-
-template <bool GROUPED>
+template <bool GROUPED, bool Q8>
 __global__ void __launch_bounds__(NTHREADS, 1) decode_down_kernel(const DecodeArgs a, int R)
 {
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -479,51 +433,106 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_down_kernel(const DecodeAr
     __syncthreads();
     const Route* rt = a.route;
     const int NG = a.H / 64, KB = a.I / 64, S = (KB + 15) / 16;
-    const int ns = rt->nslots;
-    const int P = ns * NG;
+    const int nt = rt->ntiles;
+    const int P = nt * NG;
     const int p0 = (int) ((long long) P * blockIdx.x / gridDim.x), p1 = (int) ((long long) P * (blockIdx.x + 1) / gridDim.x);
-    if (warp == CW)
-    {
-        if (lane == 0)
+    const int g = lane >> 2, q = lane & 3;
+    const uint32_t total = (uint32_t) (p1 - p0) * S;
+    uint32_t issued = 0;
+    auto fill = [&](uint32_t i) {
+        const int p = p0 + (int) (i / S), s = (int) (i % S);
+        const int gr = p / nt, tile = p % nt, e = rt->expert[tile];
+        const char* dw = (const char*) (e >= 0 ? (const void*) a.down_w[e] : a.sh_dw) + ((size_t) gr * KB + 16 * s) * 2048;
+        const uint32_t st = i % NSTAGE, bytes = (KB - 16 * s < 16 ? KB - 16 * s : 16) * 2048;
+        mbar_expect_tx(full0 + st * 8, bytes);
+        bulk_g2s(ring + st * STAGE_BYTES, dw, bytes, full0 + st * 8);
+    };
+    auto load_item = [&](int p) {
+        Item it;
+        it.gr = p / nt; it.tile = p % nt; it.e = rt->expert[it.tile]; it.nrows = rt->nrows[it.tile];
+        const size_t trow = (size_t) it.tile * 8;
+        it.xb = (const char*) (a.act + (trow + g) * a.I) + q * 32;
+        if (Q8) { it.xs[0] = a.ascale + (trow + 2 * q) * (a.I / 32); it.xs[1] = a.ascale + (trow + 2 * q + 1) * (a.I / 32); }
+        if (GROUPED)
         {
-            uint32_t it = 0;
-            bool ok = true;
-            for (int p = p0; p < p1 && ok; ++p)
-            {
-                const int gr = p / ns, slot = p % ns, e = rt->expert[slot];
-                const char* dw = (const char*) (e >= 0 ? (const void*) a.down_w[e] : a.sh_dw) + (size_t) gr * KB * 2048;
-                for (int s = 0; s < S; ++s, ++it)
-                {
-                    const uint32_t st = it % NSTAGE;
-                    if (it >= NSTAGE && !mbar_wait(empty0 + st * 8, ((it / NSTAGE) - 1) & 1, abort_flag, a.status)) { ok = false; break; }
-                    const int nkb = KB - 16 * s < 16 ? KB - 16 * s : 16;
-                    mbar_expect_tx(full0 + st * 8, nkb * 2048);
-                    bulk_g2s(ring + st * STAGE_BYTES, dw + (size_t) s * 32768, nkb * 2048, full0 + st * 8);
-                }
-            }
+            const void* sp = it.e >= 0 ? (const void*) a.down_s[it.e] : a.sh_ds;
+            it.sc = (const char*) sp + ((size_t) it.gr * (a.I / 128) * 64 + g * 8) * 2;
         }
-    }
-    else
+        return it;
+    };
+    if (p0 < p1)
     {
+        if (threadIdx.x == 0) produce(issued, total, 0, empty0, abort_flag, a.status, fill);
+        float acc[4][4];
+        #pragma unroll
+        for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+        Item cur = load_item(p0);
+        Pre pc;
+        prefetch<GROUPED, Q8>(cur, warp, KB, pc);
         uint32_t it = 0;
-        for (int p = p0; p < p1; ++p)
+        int p = p0, s = 0;
+        while (p < p1)
         {
-            const int gr = p / ns, slot = p % ns, e = rt->expert[slot];
-            if (rt->nrows[slot] > 8) down_item<2, GROUPED>(a, slot, gr, e, ring, full0, empty0, yacc, abort_flag, it, warp, lane);
-            else down_item<1, GROUPED>(a, slot, gr, e, ring, full0, empty0, yacc, abort_flag, it, warp, lane);
-            if (*abort_flag) break;
-            if (p + 1 == p1 || (p + 1) / ns != gr)
+            int np = p, ns = s + 1;
+            if (ns == S) { ns = 0; np = p + 1; }
+            Item nxt = cur;
+            Pre pn = pc;
+            if (np < p1)
             {
-                // the slice of y this block has been adding into is complete: one fp32 reduction per element to global
-                consumer_sync();
-                for (int i = threadIdx.x; i < R * 64; i += CW * 32)
-                {
-                    const float v = yacc[i];
-                    if (v != 0.f) atomicAdd(a.y + (size_t) (i >> 6) * a.H + gr * 64 + (i & 63), v);
-                    yacc[i] = 0.f;
-                }
-                consumer_sync();
+                if (ns == 0) nxt = load_item(np);
+                prefetch<GROUPED, Q8>(nxt, 16 * ns + warp, KB, pn);
             }
+            if (threadIdx.x == 0) produce(issued, total, it, empty0, abort_flag, a.status, fill);   // a failure raises the abort flag
+            __syncwarp();
+            const uint32_t st = it % NSTAGE;
+            if (!mbar_wait(full0 + st * 8, (it / NSTAGE) & 1, abort_flag, a.status)) break;
+            if (16 * s + warp < KB) consume_block<GROUPED, Q8>(ring + st * STAGE_BYTES + warp * 2048, pc, acc, lane);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty0 + st * 8);
+            ++it;
+            if (s == S - 1)
+            {
+                float sd[8];
+                #pragma unroll
+                for (int i = 0; i < 8; ++i) sd[i] = 1.f;
+                if (!GROUPED)
+                {
+                    const float* dsp = cur.e >= 0 ? (const float*) a.down_s[cur.e] : (const float*) a.sh_ds;
+                    #pragma unroll
+                    for (int ss = 0; ss < 4; ++ss) { sd[2 * ss] = __ldg(dsp + cur.gr * 64 + ss * 16 + g); sd[2 * ss + 1] = __ldg(dsp + cur.gr * 64 + ss * 16 + g + 8); }
+                }
+                // add this warp's share of the tile's contribution into the block's slice of y, real row by real row
+                #pragma unroll
+                for (int c = 0; c < 2; ++c)
+                {
+                    const int col = 2 * q + c;
+                    if (col < cur.nrows)
+                    {
+                        float* yr = yacc + (int) rt->rows[cur.tile][col] * 64;
+                        #pragma unroll
+                        for (int ss = 0; ss < 4; ++ss)
+                        {
+                            atomicAdd(yr + ss * 16 + g, acc[ss][c] * sd[2 * ss]);
+                            atomicAdd(yr + ss * 16 + g + 8, acc[ss][2 + c] * sd[2 * ss + 1]);
+                        }
+                    }
+                }
+                #pragma unroll
+                for (int ss = 0; ss < 4; ++ss) acc[ss][0] = acc[ss][1] = acc[ss][2] = acc[ss][3] = 0.f;
+                if (np >= p1 || np / nt != cur.gr)
+                {
+                    // the slice of y this block has been adding into is complete: one fp32 reduction per element to global
+                    __syncthreads();
+                    for (int i = threadIdx.x; i < R * 64; i += NTHREADS)
+                    {
+                        const float v = yacc[i];
+                        if (v != 0.f) atomicAdd(a.y + (size_t) (i >> 6) * a.H + cur.gr * 64 + (i & 63), v);
+                        yacc[i] = 0.f;
+                    }
+                    __syncthreads();
+                }
+            }
+            cur = nxt; pc = pn; p = np; s = ns;
         }
     }
     __syncthreads();
@@ -533,17 +542,62 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_down_kernel(const DecodeAr
 
 // ---------------------------------------------------------------------------------------------------------------------
 // host side
+static size_t up256(size_t b) { return (b + 255) / 256 * 256; }
+
 size_t decode_ws_bytes(int H, int I)
 {
-    size_t b = 0;
-    b += 256;                                            // status word + padding
-    b += (sizeof(Route) + 255) / 256 * 256;
-    b += (size_t) MAXR * H * 2;                          // xf
-    b += (size_t) MAXT * 8 * I * 2;                      // act
-    return (b + 255) / 256 * 256;
+    size_t b = 256;                                      // status word + padding
+    b += up256(sizeof(Route));
+    b += up256((size_t) MAXR * H * 2);                   // xf
+    b += up256((size_t) MAXR * (H / 32) * 4);            // xscale
+    b += up256((size_t) MAXT * 8 * I * 2);               // act
+    b += up256((size_t) MAXT * 8 * (I / 32) * 4);        // ascale
+    return b;
 }
 
 static int g_sms = 0;
+
+// Optional phase timing: when switched on, every decode call records four events (before prepare, after prepare, after
+// gate_up, after down) on the caller's stream into a ring, read back by decode_phase_times().
+static bool g_prof = false;
+static cudaEvent_t g_ev[4];
+static bool g_ev_made = false;
+
+int decode_set_profiling(int on)
+{
+    if (on && !g_ev_made)
+    {
+        for (int i = 0; i < 4; ++i)
+            if (cudaEventCreate(&g_ev[i]) != cudaSuccess) return fail(HMOE_E_CUDA, "hmoe_set_profiling: cudaEventCreate failed");
+        g_ev_made = true;
+    }
+    g_prof = on != 0;
+    return HMOE_OK;
+}
+
+int decode_phase_times(float* ms3)
+{
+    if (!g_ev_made) return fail(HMOE_E_ARG, "hmoe_decode_phase_times: profiling was never switched on");
+    if (cudaEventSynchronize(g_ev[3]) != cudaSuccess) return fail(HMOE_E_CUDA, "hmoe_decode_phase_times: no timed call");
+    for (int i = 0; i < 3; ++i)
+        if (cudaEventElapsedTime(ms3 + i, g_ev[i], g_ev[i + 1]) != cudaSuccess) return fail(HMOE_E_CUDA, "hmoe_decode_phase_times: elapsed");
+    return HMOE_OK;
+}
+
+template <bool G, bool Q>
+static void launch_pair(int grid, const DecodeArgs& a, int R, cudaStream_t st, bool first)
+{
+    if (g_prof) cudaEventRecord(g_ev[1], st);
+    if (first)
+    {
+        cudaFuncSetAttribute(decode_gate_up_kernel<G, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout::total);
+        cudaFuncSetAttribute(decode_down_kernel<G, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout::total);
+    }
+    decode_gate_up_kernel<G, Q><<<grid, NTHREADS, SmemLayout::total, st>>>(a);
+    if (g_prof) cudaEventRecord(g_ev[2], st);
+    decode_down_kernel<G, Q><<<grid, NTHREADS, SmemLayout::total, st>>>(a, R);
+    if (g_prof) cudaEventRecord(g_ev[3], st);
+}
 
 int decode_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
                   int act_quant, float* y, void* ws, size_t ws_bytes, cudaStream_t st)
@@ -558,33 +612,35 @@ int decode_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t
     if (x_dtype != HMOE_F16 && x_dtype != HMOE_BF16) return fail(HMOE_E_ARG, "hmoe_decode: x must be fp16 or bf16");
     if (ws_bytes < decode_ws_bytes(H, I)) return fail(HMOE_E_WS, "hmoe_decode: workspace too small");
     if (!x || !sel || !rw || !y || !ws) return fail(HMOE_E_ARG, "hmoe_decode: null pointer");
+    static bool first[4] = {true, true, true, true};
     if (g_sms == 0)
     {
         int dev = 0; cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev);
-        cudaFuncSetAttribute(decode_gate_up_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout::total);
-        cudaFuncSetAttribute(decode_gate_up_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout::total);
-        cudaFuncSetAttribute(decode_down_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout::total);
-        cudaFuncSetAttribute(decode_down_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout::total);
     }
     char* w = (char*) ws;
     unsigned* status = (unsigned*) w; w += 256;
-    Route* route = (Route*) w; w += (sizeof(Route) + 255) / 256 * 256;
-    __half* xf = (__half*) w; w += (size_t) MAXR * H * 2;
-    __half* act = (__half*) w;
+    Route* route = (Route*) w; w += up256(sizeof(Route));
+    __half* xf = (__half*) w; w += up256((size_t) MAXR * H * 2);
+    float* xscale = (float*) w; w += up256((size_t) MAXR * (H / 32) * 4);
+    __half* act = (__half*) w; w += up256((size_t) MAXT * 8 * I * 2);
+    float* ascale = (float*) w;
     const int has_shared = L->sh_gate_w != nullptr;
+    if (g_prof) cudaEventRecord(g_ev[0], st);
     decode_prepare_kernel<<<R + 1, 256, 0, st>>>(x, x_dtype == HMOE_BF16, sel, (const __half*) rw, R, H, L->topk, lo, n_local, has_shared,
-                                                 act_quant, xf, route);
+                                                 act_quant, xf, xscale, route);
     DecodeArgs a;
-    a.H = H; a.I = I; a.group = L->group; a.act_quant = act_quant;
+    a.H = H; a.I = I;
     a.gate_w = L->gate_w; a.up_w = L->up_w; a.down_w = L->down_w; a.gate_s = L->gate_s; a.up_s = L->up_s; a.down_s = L->down_s;
     a.sh_gw = L->sh_gate_w; a.sh_uw = L->sh_up_w; a.sh_dw = L->sh_down_w; a.sh_gs = L->sh_gate_s; a.sh_us = L->sh_up_s; a.sh_ds = L->sh_down_s;
-    a.route = route; a.xf = xf; a.act = act; a.y = y; a.status = status;
+    a.route = route; a.xf = xf; a.xscale = xscale; a.act = act; a.ascale = ascale; a.y = y; a.status = status;
     const int grid = g_sms;
-    if (L->group) decode_gate_up_kernel<true><<<grid, NTHREADS, SmemLayout::total, st>>>(a);
-    else decode_gate_up_kernel<false><<<grid, NTHREADS, SmemLayout::total, st>>>(a);
-    if (L->group) decode_down_kernel<true><<<grid, NTHREADS, SmemLayout::total, st>>>(a, R);
-    else decode_down_kernel<false><<<grid, NTHREADS, SmemLayout::total, st>>>(a, R);
+    const int v = (L->group ? 2 : 0) + (act_quant ? 1 : 0);
+    if (v == 0) launch_pair<false, false>(grid, a, R, st, first[0]);
+    else if (v == 1) launch_pair<false, true>(grid, a, R, st, first[1]);
+    else if (v == 2) launch_pair<true, false>(grid, a, R, st, first[2]);
+    else launch_pair<true, true>(grid, a, R, st, first[3]);
+    first[v] = false;
     count_launches(3);
     const cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) return fail(HMOE_E_CUDA, cudaGetErrorString(err));

@@ -15,6 +15,9 @@ size_t decode_ws_bytes(int H, int I);
 int decode_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
                   int act_quant, float* y, void* ws, size_t ws_bytes, cudaStream_t st);
 
+int decode_set_profiling(int on);
+int decode_phase_times(float* ms3);
+
 size_t router_ws_bytes(int R, int E);
 int router_launch(const void* x, int x_dtype, const void* wt, int w_dtype, const float* bias, int R, int H, int E, int topk,
                   float scale, int64_t* sel, void* rw, void* ws, size_t ws_bytes, cudaStream_t st);

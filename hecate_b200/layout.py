@@ -9,8 +9,9 @@ holds row n = gr*64 + s*16 + rh*8 + g and column k = kb*64 + t*16 + h*8 + q*2 + 
 ((gr*KB + kb)*4 + s)*32 + lane with lane = g*4 + q is what lane `lane` of a warp feeds to four m16n8k16 MMAs (one 32-bit
 word per 16 columns). 64 rows x 64 columns form one contiguous 2 KB unit and all units of a 64-row group are contiguous.
 
-Scales: float [K/G][N] (column-group major) in bf16 for the group-quantised format, or fp32 [N] for the reference's
-one-scale-per-row format.
+Scales: fp32 [N] for the reference's one-scale-per-row format. For the group-quantised format the logical tensor is
+[K/G][N]; on the device it is stored bf16 [N/64][K/G][64] with row r of a 64-row group at position (r % 8) * 8 + r / 8
+(`group_scales_device_order`), so one 16-byte load gives an MMA lane the scales of its eight rows.
 """
 import numpy as np
 
@@ -53,3 +54,17 @@ def frag_order_row(v):
     K = v.shape[-1]
     w = v.reshape(*v.shape[:-1], K // 64, 4, 2, 4, 2)            # kb t h q pair
     return w.swapaxes(-4, -2).swapaxes(-3, -2).reshape(v.shape)  # kb q t h pair
+
+
+def group_scales_device_order(s):
+    """logical scales [K/G][N] -> device order [N/64][K/G][64] (row r of a group at (r % 8) * 8 + r // 8)."""
+    s = np.asarray(s)
+    KG, N = s.shape
+    t = s.reshape(KG, N // 64, 8, 8)                 # kg, gr, j (= r // 8), g (= r % 8)
+    return np.ascontiguousarray(t.transpose(1, 0, 3, 2)).reshape(N // 64, KG, 64)
+
+
+def group_scales_logical(d, N):
+    """inverse of group_scales_device_order: [N/64][K/G][64] -> [K/G][N]."""
+    d = np.asarray(d).reshape(N // 64, -1, 8, 8)     # gr, kg, g, j
+    return np.ascontiguousarray(d.transpose(1, 0, 3, 2)).reshape(-1, N)

@@ -86,6 +86,17 @@ def decode(tables, x, sel, rw, y, ws, lo=0, n_local=None, act_quant=False):
     return y
 
 
+def set_profiling(on):
+    check(lib().hmoe_set_profiling(C.c_int(int(on))))
+
+
+def decode_phase_times():
+    """ms of (prepare, gate_up, down) of the last decode call made with profiling on (waits for it)."""
+    out = (C.c_float * 3)()
+    check(lib().hmoe_decode_phase_times(out))
+    return tuple(out)
+
+
 def ws_status(ws):
     out = C.c_uint32(0)
     check(lib().hmoe_ws_status(vp(ws), C.byref(out), _stream(ws.device)))

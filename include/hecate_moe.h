@@ -8,8 +8,10 @@
  *
  * Weight format (unchanged from the reference): a matrix W[N][K] of 4-bit codes c (value c - 8) packed by
  * tools/quant/gptq_int4.py:74-77 (pack_u4); see hecate_b200/layout.py for the index formula. Scales are either one fp32
- * per row (group = 0, scale_dtype = HMOE_F32; the reference's format) or one bf16 per 128 input columns laid out
- * [K/128][N] (group = 128, scale_dtype = HMOE_BF16). Every weight and scale pointer must be 16-byte aligned.
+ * per row (group = 0, scale_dtype = HMOE_F32; the reference's format) or one bf16 per 128 input columns (group = 128,
+ * scale_dtype = HMOE_BF16) stored [N/64][K/128][64]: the 64 scales of a 64-row group and one column group are contiguous,
+ * row r of the group at position (r % 8) * 8 + r / 8, so that one 16-byte load gives a lane the eight rows it feeds to the
+ * MMAs (hecate_b200/layout.py: group_scales_device_order). Every weight and scale pointer must be 16-byte aligned.
  */
 #ifndef HECATE_MOE_H
 #define HECATE_MOE_H
@@ -60,6 +62,13 @@ int hmoe_router(const void* x, int x_dtype, const void* wt, int w_dtype, const f
 size_t hmoe_decode_ws_bytes(int H, int I);
 int hmoe_decode(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
                 int act_quant, float* y, void* ws, size_t ws_bytes, void* stream);
+
+/* Phase timing of the decode path (no reference counterpart; the reference uses compile-time ablation macros,
+ * runtime/tier/moe4/moe4.cu:6-10). With profiling on, each hmoe_decode call records CUDA events between its three kernels
+ * on the caller's stream; hmoe_decode_phase_times waits for the last timed call and returns the durations in ms of
+ * {prepare, gate_up, down}. The first switch-on creates the events (allocates; call it outside stream capture). */
+int hmoe_set_profiling(int on);
+int hmoe_decode_phase_times(float* ms3);
 
 /* Combine: replaces moe4.combine(f, o_ptr, y, rows, o2_ptr, done_ptr) (runtime/tier/moe4/moe4.cu:702-717,817-824):
  * f += y (+ o) (+ o2) in that order, then y = 0. o and o2 may be null. n = rows * H must be a multiple of 4. */

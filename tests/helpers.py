@@ -28,7 +28,9 @@ class HostLayer:
         from hecate_b200 import moe
         sdt = torch.float32 if self.group == 0 else torch.bfloat16
         q = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device)
-        s = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device).to(sdt).contiguous()
+        from hecate_b200 import layout
+        dev_order = (lambda a: a.reshape(-1)) if self.group == 0 else layout.group_scales_device_order
+        s = lambda a: torch.from_numpy(np.ascontiguousarray(dev_order(a))).to(device).to(sdt).contiguous()
         cols = {k: [] for k in ("gq", "uq", "dq", "gs", "us", "ds")}
         for d in self.ex:
             for k in cols:

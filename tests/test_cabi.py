@@ -1,0 +1,37 @@
+"""The C ABI library loads without a GPU and exports every function that include/hecate_moe.h declares."""
+import ctypes
+import os
+import re
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, "include", "hecate_moe.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(hmoe_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_all_declared_symbols():
+    from hecate_b200 import _lib
+    L = _lib.lib()
+    names = declared_functions()
+    assert "hmoe_decode" in names and "hmoe_router" in names and len(names) >= 10
+    for n in names:
+        assert hasattr(L, n), f"{n} declared in include/hecate_moe.h but not exported"
+
+
+def test_host_only_entry_points():
+    from hecate_b200 import _lib
+    L = _lib.lib()
+    assert L.hmoe_version() >= 100
+    assert L.hmoe_decode_ws_bytes(ctypes.c_int(6144), ctypes.c_int(2048)) > 4_000_000
+    assert L.hmoe_router_ws_bytes(ctypes.c_int(16), ctypes.c_int(256)) >= 16 * 256 * 4
+    # argument errors are reported as codes with a message, never thrown
+    rc = L.hmoe_combine(None, None, None, ctypes.c_int64(4), None, None)
+    assert rc == 1 and b"hmoe_combine" in L.hmoe_last_error()
+
+
+def test_layer_struct_matches_header():
+    from hecate_b200 import _lib
+    assert ctypes.sizeof(_lib.LayerStruct) == 6 * 4 + 12 * 8

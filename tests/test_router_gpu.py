@@ -1,0 +1,46 @@
+"""The CUDA router selects the same experts and writes the same fp16 weights as the CPU checker, bit for bit."""
+import numpy as np
+import pytest
+
+from hecate_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(oracle, R, H, E, topk, xbf, wbf, bias_sigma, scale, seed):
+    import torch
+    from hecate_b200 import moe
+    dev = torch.device("cuda:0")
+    x = synth.activations(seed, 0, R, H); w = synth.router_weight(seed, 0, E, H)
+    bias = synth.router_bias(seed, 0, E, bias_sigma) if bias_sigma is not None else None
+    xt = torch.from_numpy(x).to(dev).to(torch.bfloat16 if xbf else torch.float16)
+    wt = torch.from_numpy(w).to(dev).to(torch.bfloat16 if wbf else torch.float16)
+    sel = torch.empty(R, topk, dtype=torch.int64, device=dev); rw = torch.empty(R, topk, dtype=torch.float16, device=dev)
+    moe.router_fused(xt, wt, None if bias is None else torch.from_numpy(bias).to(dev), None, None, sel, rw, topk, scale)
+    bits = lambda t: t.cpu().view(torch.int16).numpy().view(np.uint16)
+    osel, orw = oracle.router(bits(xt), xbf, bits(wt), wbf, bias, topk, scale)
+    assert np.array_equal(osel, sel.cpu().numpy())
+    assert np.array_equal(orw.view(np.uint16), bits(rw))
+
+
+@pytest.mark.parametrize("R", [1, 2, 8, 16, 33])
+def test_router_bit_exact_benchmark_shape(oracle, R):
+    _run(oracle, R, 6144, 256, 8, 1, 1, 0.0, 1.0, seed=R)
+
+
+@pytest.mark.parametrize("xbf,wbf", [(0, 0), (0, 1), (1, 0)])
+def test_router_dtypes_bias_scale(oracle, xbf, wbf):
+    _run(oracle, 5, 1024, 64, 6, xbf, wbf, 0.1, 2.5, seed=7)
+    _run(oracle, 3, 256, 32, 8, xbf, wbf, None, 1.0, seed=8)
+
+
+def test_router_large_rows(oracle):
+    _run(oracle, 1000, 512, 128, 8, 1, 1, 0.05, 1.0, seed=9)
+
+
+def test_fill_matches_numpy_generator():
+    import torch
+    from hecate_b200 import moe
+    t = torch.empty(8192, dtype=torch.uint8, device="cuda:0")
+    moe.fill_bytes(t, 5, synth.stream_id(2, "down_q", 17))
+    assert np.array_equal(t.cpu().numpy(), synth.rand_bytes(5, synth.stream_id(2, "down_q", 17), 8192))
