@@ -166,11 +166,11 @@ def build_layer(dev, seed, experts, torch, moe):
     moe.fill_bytes(pool, seed, synth.stream_id(0, "gate_q", 0))
     view = lambda e, k: pool[(e * 3 + k) * PER_MATRIX:(e * 3 + k + 1) * PER_MATRIX]
     g = torch.Generator(device=dev); g.manual_seed(seed + 1)
-    sc = lambda N, K: (torch.randn(N // 64, K // GROUP, 64, device=dev, generator=g) * 0.5 - 4.0).exp().to(torch.bfloat16)
-    gs = [sc(I, H) for _ in range(n + 1)]; us = [sc(I, H) for _ in range(n + 1)]; ds = [sc(H, I) for _ in range(n + 1)]
+    sc = lambda N, K: (torch.randn(n + 1, N // 64, K // GROUP, 64, device=dev, generator=g) * 0.5 - 4.0).exp().to(torch.bfloat16)
+    gs, us, ds = sc(I, H), sc(I, H), sc(H, I)          # device order [N/64][K/128][64] per expert
     shared = (view(n, 0), view(n, 1), view(n, 2), gs[n], us[n], ds[n])
     tabs = moe.ExpertTables(H, I, TOPK, [view(e, 0) for e in range(n)], [view(e, 1) for e in range(n)],
-                            [view(e, 2) for e in range(n)], gs[:n], us[:n], ds[:n], group=GROUP, shared=shared, device=dev)
+                            [view(e, 2) for e in range(n)], list(gs[:n]), list(us[:n]), list(ds[:n]), group=GROUP, shared=shared, device=dev)
     tabs.keep.append(pool)
     return tabs
 
@@ -191,6 +191,7 @@ def run_ours(args):
         from hecate_b200 import ep
         return ep.bench_decode(args, world, rank, dev)
     steps, warmup = args.steps, max(3, args.warmup)
+    E = args.experts
     tabs = build_layer(dev, 0, list(range(E)), torch, moe)
     wt = torch.from_numpy(synth.router_weight(0, 0, E, H)).to(dev).to(torch.bfloat16)
     bias = torch.zeros(E, dtype=torch.float32, device=dev)
@@ -265,7 +266,7 @@ def run_ours(args):
         "metric": METRIC, "value": ROWS / (ms_per_step * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int4 x fp16 -> fp32",
         "data": "synthetic",
-        "config": {"workload": WORKLOAD, "l2": "inputs larger than L2: ~2 GB of weights streamed per step, 8 input batches in a ring",
+        "config": {"workload": WORKLOAD if E == 256 else WORKLOAD + f" [reduced to {E} experts]", "l2": "inputs larger than L2: ~2 GB of weights streamed per step, 8 input batches in a ring",
                    "distinct_experts_per_step": mean_d},
         "us_per_layer": ms_per_step * 1e3,
         "layer_hbm_gbs": layer_bytes / (ms_per_step * 1e-3) / 1e9,
@@ -290,6 +291,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--experts", type=int, default=E, help="routed experts resident (256 = the benchmark; fewer only for profiling)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
