@@ -37,6 +37,14 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity)
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
+// try_wait that lets the hardware park the thread for up to `hint_ns` before it reports failure (fewer polls issued)
+__device__ __forceinline__ bool mbar_try_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns)
+{
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity), "r"(hint_ns) : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ unsigned long long globaltimer_ns()
 {
     unsigned long long t;
@@ -49,11 +57,12 @@ __device__ __forceinline__ unsigned long long globaltimer_ns()
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned* status,
                                           unsigned long long limit_ns = 1000000000ull)
 {
+    if (mbar_try(bar, parity)) return true;
     unsigned long long t0 = 0;
     for (uint32_t i = 0;; ++i)
     {
-        if (mbar_try(bar, parity)) return true;
-        if ((i & 1023u) == 1023u)
+        if (mbar_try_hint(bar, parity, 20000u)) return true;
+        if ((i & 63u) == 63u)
         {
             if (*abort_flag) return false;
             const unsigned long long now = globaltimer_ns();
@@ -97,7 +106,7 @@ __device__ __forceinline__ uint4 ldg128(const void* p)
 
 __device__ __forceinline__ void mma_f16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1)
 {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }

@@ -30,17 +30,19 @@ namespace {
 
 constexpr int CW = 16;                   // warps per block
 constexpr int NTHREADS = CW * 32;
-constexpr int STAGE_BYTES = 32768;       // 16 units of 64 rows x 64 columns
-constexpr int NSTAGE = 4;
-constexpr int RED_FLOATS = CW * 64 * 8;  // gate_up partial tiles: [warp][64 rows][8 columns]
+constexpr int STAGE_BYTES = 65536;       // 32 units of 64 rows x 64 columns
+constexpr int NSTAGE = 3;
+constexpr int NBUF = 4;                  // gate_up partial-sum buffers in rotation (a warp runs at most NSTAGE items ahead)
+constexpr int GU_FLOATS = 2 * 64 * 8;    // [matrix][64 rows][8 tile columns]
 constexpr int YACC_FLOATS = MAXR * 64;
 
 struct SmemLayout
 {
     static constexpr int ring = 0;
-    static constexpr int red = NSTAGE * STAGE_BYTES;                  // gate_up: RED_FLOATS floats; down: YACC_FLOATS floats
-    static constexpr int bars = red + RED_FLOATS * 4;                 // full[NSTAGE], empty[NSTAGE]
-    static constexpr int flags = bars + 2 * NSTAGE * 8;
+    static constexpr int gu = NSTAGE * STAGE_BYTES;                   // gate_up: NBUF x GU_FLOATS; down: YACC_FLOATS
+    static constexpr int bars = gu + NBUF * GU_FLOATS * 4;            // full[NSTAGE]
+    static constexpr int cnt = bars + NSTAGE * 8;                     // NBUF item arrival counters, NSTAGE stage-free counters
+    static constexpr int flags = cnt + (NBUF + NSTAGE) * 4;
     static constexpr int total = flags + 16;
 };
 
@@ -157,12 +159,13 @@ __global__ void __launch_bounds__(256) decode_prepare_kernel(const void* __restr
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// What a warp needs from global memory for one 64-column block, fetched one ring stage ahead.
+// What a warp needs from global memory for its two 64-column blocks (one 128-column scale group) of a ring stage,
+// fetched one stage ahead.
 struct Pre
 {
-    uint32_t bx[8];         // activation fragments of this lane's tile row: word 2t + h of 16-column step t
+    uint32_t bx[2][8];      // activation fragments of this lane's tile row per block: word 2t + h of 16-column step t
     uint4 sc;               // GROUPED: bf16 scales of rows strip*16 + g (low half of word `strip`) and + 8 (high half)
-    float2 sx[2];           // Q8: activation scales of the block's two 32-column halves for tile columns 2q and 2q + 1
+    float4 sx[2];           // Q8: activation scales of the group's four 32-column quarters for tile columns 2q and 2q + 1
 };
 
 struct DecodeArgs
@@ -180,61 +183,59 @@ struct DecodeArgs
     unsigned* status;
 };
 
-// One 64-column block of a 64-row group: 4 strips x 4 steps of MMAs on the tile, added into acc with the scales applied.
+// Two 64-column blocks (one scale group) of a 64-row group: 4 strips x 8 steps of MMAs on the tile, added into acc with
+// the scales applied. wsm = shared address of the first block's 2 KB unit; the second follows it.
 template <bool GROUPED, bool Q8>
-__device__ __forceinline__ void consume_block(uint32_t wsm, const Pre& pr, float (*acc)[4], int lane)
+__device__ __forceinline__ void consume_group(uint32_t wsm, const Pre& pr, float (*acc)[4], int lane)
 {
-    uint4 w4[4];
-    #pragma unroll
-    for (int s = 0; s < 4; ++s) w4[s] = lds128(wsm + s * 512 + lane * 16);
     const uint32_t scw[4] = {pr.sc.x, pr.sc.y, pr.sc.z, pr.sc.w};
+    const float sxa[4] = {pr.sx[0].x, pr.sx[0].y, pr.sx[0].z, pr.sx[0].w}, sxb[4] = {pr.sx[1].x, pr.sx[1].y, pr.sx[1].z, pr.sx[1].w};
+    // The four strips' sums are independent MMA chains; the steps are interleaved across strips so that consecutive MMAs
+    // never wait on each other.
+    float part[4][4];
     #pragma unroll
-    for (int s = 0; s < 4; ++s)
+    for (int s = 0; s < 4; ++s) part[s][0] = part[s][1] = part[s][2] = part[s][3] = 0.f;
+    #pragma unroll
+    for (int blk = 0; blk < 2; ++blk)
     {
-        const uint32_t ww[4] = {w4[s].x, w4[s].y, w4[s].z, w4[s].w};
-        float s0 = 1.f, s1 = 1.f;
-        if (GROUPED) { s0 = __uint_as_float(scw[s] << 16); s1 = __uint_as_float(scw[s] & 0xffff0000u); }
-        if (!GROUPED && !Q8)
+        uint4 w4[4];
+        #pragma unroll
+        for (int s = 0; s < 4; ++s) w4[s] = lds128(wsm + blk * 2048 + s * 512 + lane * 16);
+        #pragma unroll
+        for (int t = 0; t < 4; ++t)
         {
             #pragma unroll
-            for (int t = 0; t < 4; ++t)
+            for (int s = 0; s < 4; ++s)
             {
+                const uint32_t w = t == 0 ? w4[s].x : t == 1 ? w4[s].y : t == 2 ? w4[s].z : w4[s].w;
                 uint32_t a[4];
-                frag_from_codes(ww[t], a);
-                mma_f16(acc[s], a, pr.bx[2 * t], pr.bx[2 * t + 1]);
+                frag_from_codes(w, a);
+                mma_f16((GROUPED || Q8) ? part[s] : acc[s], a, pr.bx[blk][2 * t], pr.bx[blk][2 * t + 1]);
             }
-        }
-        else if (!Q8)
-        {
-            float part[4] = {0.f, 0.f, 0.f, 0.f};
-            #pragma unroll
-            for (int t = 0; t < 4; ++t)
+            if (Q8 && (t & 1))
             {
-                uint32_t a[4];
-                frag_from_codes(ww[t], a);
-                mma_f16(part, a, pr.bx[2 * t], pr.bx[2 * t + 1]);
-            }
-            acc[s][0] = fmaf(s0, part[0], acc[s][0]); acc[s][1] = fmaf(s0, part[1], acc[s][1]);
-            acc[s][2] = fmaf(s1, part[2], acc[s][2]); acc[s][3] = fmaf(s1, part[3], acc[s][3]);
-        }
-        else
-        {
-            // int8 activations: exact integer sums per 32 columns, then one multiply by (activation scale x weight scale)
-            #pragma unroll
-            for (int hf = 0; hf < 2; ++hf)
-            {
-                float part[4] = {0.f, 0.f, 0.f, 0.f};
+                // int8 activations: the sums of 32 columns are exact integers; one multiply by (activation scale x weight scale)
+                const int qt = blk * 2 + (t >> 1);
                 #pragma unroll
-                for (int t = 2 * hf; t < 2 * hf + 2; ++t)
+                for (int s = 0; s < 4; ++s)
                 {
-                    uint32_t a[4];
-                    frag_from_codes(ww[t], a);
-                    mma_f16(part, a, pr.bx[2 * t], pr.bx[2 * t + 1]);
+                    float s0 = 1.f, s1 = 1.f;
+                    if (GROUPED) { s0 = __uint_as_float(scw[s] << 16); s1 = __uint_as_float(scw[s] & 0xffff0000u); }
+                    acc[s][0] = fmaf(part[s][0], sxa[qt] * s0, acc[s][0]); acc[s][1] = fmaf(part[s][1], sxb[qt] * s0, acc[s][1]);
+                    acc[s][2] = fmaf(part[s][2], sxa[qt] * s1, acc[s][2]); acc[s][3] = fmaf(part[s][3], sxb[qt] * s1, acc[s][3]);
+                    part[s][0] = part[s][1] = part[s][2] = part[s][3] = 0.f;
                 }
-                const float x0 = hf ? pr.sx[0].y : pr.sx[0].x, x1 = hf ? pr.sx[1].y : pr.sx[1].x;
-                acc[s][0] = fmaf(part[0], x0 * s0, acc[s][0]); acc[s][1] = fmaf(part[1], x1 * s0, acc[s][1]);
-                acc[s][2] = fmaf(part[2], x0 * s1, acc[s][2]); acc[s][3] = fmaf(part[3], x1 * s1, acc[s][3]);
             }
+        }
+    }
+    if (GROUPED && !Q8)
+    {
+        #pragma unroll
+        for (int s = 0; s < 4; ++s)
+        {
+            const float s0 = __uint_as_float(scw[s] << 16), s1 = __uint_as_float(scw[s] & 0xffff0000u);
+            acc[s][0] = fmaf(s0, part[s][0], acc[s][0]); acc[s][1] = fmaf(s0, part[s][1], acc[s][1]);
+            acc[s][2] = fmaf(s1, part[s][2], acc[s][2]); acc[s][3] = fmaf(s1, part[s][3], acc[s][3]);
         }
     }
 }
@@ -248,38 +249,38 @@ struct Item
     const char* sc;         // GROUPED: scale words of this lane's rows for the item's 64-row group (column group 0)
 };
 
+// kb = first of the warp's two blocks (even)
 template <bool GROUPED, bool Q8>
 __device__ __forceinline__ void prefetch(const Item& it, int kb, int KB, Pre& pr)
 {
     if (kb >= KB) return;
     const uint4 b0 = ldg128(it.xb + kb * 128), b1 = ldg128(it.xb + kb * 128 + 16);
-    pr.bx[0] = b0.x; pr.bx[1] = b0.y; pr.bx[2] = b0.z; pr.bx[3] = b0.w;
-    pr.bx[4] = b1.x; pr.bx[5] = b1.y; pr.bx[6] = b1.z; pr.bx[7] = b1.w;
-    if (Q8) { pr.sx[0] = *(const float2*) (it.xs[0] + 2 * kb); pr.sx[1] = *(const float2*) (it.xs[1] + 2 * kb); }
+    const uint4 b2 = ldg128(it.xb + kb * 128 + 128), b3 = ldg128(it.xb + kb * 128 + 144);
+    pr.bx[0][0] = b0.x; pr.bx[0][1] = b0.y; pr.bx[0][2] = b0.z; pr.bx[0][3] = b0.w;
+    pr.bx[0][4] = b1.x; pr.bx[0][5] = b1.y; pr.bx[0][6] = b1.z; pr.bx[0][7] = b1.w;
+    pr.bx[1][0] = b2.x; pr.bx[1][1] = b2.y; pr.bx[1][2] = b2.z; pr.bx[1][3] = b2.w;
+    pr.bx[1][4] = b3.x; pr.bx[1][5] = b3.y; pr.bx[1][6] = b3.z; pr.bx[1][7] = b3.w;
+    if (Q8) { pr.sx[0] = *(const float4*) (it.xs[0] + 2 * kb); pr.sx[1] = *(const float4*) (it.xs[1] + 2 * kb); }
     if (GROUPED) pr.sc = ldg128_nc(it.sc + (size_t) (kb >> 1) * 128);
 }
 
-// The block's stream of ring stages. Lane 0 of warp 0 is the producer: `fill` issues the copies of stage number i.
-// Keeps up to NSTAGE stages in flight; blocks only if the stage the consumers need next has not been issued.
+// The ring is refilled by whichever warp frees a stage last: after its last read of stage number `it` a warp bumps the
+// stage's counter, and the warp that brings it to CW issues the copies of stage number it + NSTAGE into the same slot.
+// No thread ever waits for a free slot.
 template <typename Fill>
-__device__ __forceinline__ bool produce(uint32_t& issued, uint32_t total, uint32_t it, uint32_t empty0, volatile int* abort_flag,
-                                        unsigned* status, Fill fill)
+__device__ __forceinline__ void release_stage(int* free_cnt, uint32_t it, uint32_t total, int lane, Fill fill)
 {
-    while (issued < total && issued < it + NSTAGE)
+    __syncwarp();
+    if (lane == 0)
     {
-        if (issued >= NSTAGE)
+        __threadfence_block();
+        if (atomicAdd(free_cnt + it % NSTAGE, 1) == CW - 1)
         {
-            const uint32_t bar = empty0 + (issued % NSTAGE) * 8, par = ((issued / NSTAGE) - 1) & 1;
-            if (!mbar_try(bar, par))
-            {
-                if (issued > it) return true;                       // enough in flight for now, try again next stage
-                if (!mbar_wait(bar, par, abort_flag, status)) return false;
-            }
+            free_cnt[it % NSTAGE] = 0;
+            __threadfence_block();
+            if (it + NSTAGE < total) fill(it + NSTAGE);
         }
-        fill(issued);
-        ++issued;
     }
-    return true;
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -289,30 +290,33 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_gate_up_kernel(const Decod
 {
     extern __shared__ __align__(1024) unsigned char smem[];
     const uint32_t sbase = smem_u32(smem);
-    const uint32_t ring = sbase + SmemLayout::ring, full0 = sbase + SmemLayout::bars, empty0 = full0 + NSTAGE * 8;
-    float* red = (float*) (smem + SmemLayout::red);
+    const uint32_t ring = sbase + SmemLayout::ring, full0 = sbase + SmemLayout::bars;
+    float* gu = (float*) (smem + SmemLayout::gu);
+    int* cnt = (int*) (smem + SmemLayout::cnt);
+    int* free_cnt = cnt + NBUF;
     volatile int* abort_flag = (volatile int*) (smem + SmemLayout::flags);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0)
     {
-        for (int i = 0; i < NSTAGE; ++i) { mbar_init(full0 + i * 8, 1); mbar_init(empty0 + i * 8, CW); }
+        for (int i = 0; i < NSTAGE; ++i) mbar_init(full0 + i * 8, 1);
+        for (int i = 0; i < NBUF + NSTAGE; ++i) cnt[i] = 0;
         *abort_flag = 0;
         fence_barrier_init();
     }
+    for (int i = threadIdx.x; i < NBUF * GU_FLOATS; i += NTHREADS) gu[i] = 0.f;
     __syncthreads();
     const Route* rt = a.route;
-    const int NG = a.I / 64, KB = a.H / 64, S = (KB + 7) / 8;
+    const int NG = a.I / 64, KB = a.H / 64, S = (KB + 15) / 16;
     const int P = rt->ntiles * NG;
     const int p0 = (int) ((long long) P * blockIdx.x / gridDim.x), p1 = (int) ((long long) P * (blockIdx.x + 1) / gridDim.x);
     const int mat = warp >> 3, kw = warp & 7, g = lane >> 2, q = lane & 3;
     const uint32_t total = (uint32_t) (p1 - p0) * S;
-    uint32_t issued = 0;
     auto fill = [&](uint32_t i) {
         const int p = p0 + (int) (i / S), s = (int) (i % S);
         const int tile = p / NG, gr = p % NG, e = rt->expert[tile];
-        const char* gw = (const char*) (e >= 0 ? (const void*) a.gate_w[e] : a.sh_gw) + ((size_t) gr * KB + 8 * s) * 2048;
-        const char* uw = (const char*) (e >= 0 ? (const void*) a.up_w[e] : a.sh_uw) + ((size_t) gr * KB + 8 * s) * 2048;
-        const uint32_t st = i % NSTAGE, bytes = (KB - 8 * s < 8 ? KB - 8 * s : 8) * 2048;
+        const char* gw = (const char*) (e >= 0 ? (const void*) a.gate_w[e] : a.sh_gw) + ((size_t) gr * KB + 16 * s) * 2048;
+        const char* uw = (const char*) (e >= 0 ? (const void*) a.up_w[e] : a.sh_uw) + ((size_t) gr * KB + 16 * s) * 2048;
+        const uint32_t st = i % NSTAGE, bytes = (KB - 16 * s < 16 ? KB - 16 * s : 16) * 2048;
         mbar_expect_tx(full0 + st * 8, 2 * bytes);
         bulk_g2s(ring + st * STAGE_BYTES, gw, bytes, full0 + st * 8);
         bulk_g2s(ring + st * STAGE_BYTES + STAGE_BYTES / 2, uw, bytes, full0 + st * 8);
@@ -335,78 +339,84 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_gate_up_kernel(const Decod
     };
     if (p0 < p1)
     {
-        if (threadIdx.x == 0) produce(issued, total, 0, empty0, abort_flag, a.status, fill);
+        if (threadIdx.x == 0)
+            for (uint32_t i = 0; i < NSTAGE && i < total; ++i) fill(i);
         float acc[4][4];
         #pragma unroll
         for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
         Item cur = load_item(p0);
         Pre pc;
-        prefetch<GROUPED, Q8>(cur, kw, KB, pc);
+        prefetch<GROUPED, Q8>(cur, 2 * kw, KB, pc);
         uint32_t it = 0;
-        int p = p0, s = 0;
-        while (p < p1)
+        bool alive = true;
+        for (int p = p0; p < p1 && alive; ++p)
         {
-            int np = p, ns = s + 1;
-            if (ns == S) { ns = 0; np = p + 1; }
             Item nxt = cur;
-            Pre pn = pc;
-            if (np < p1)
+            for (int s = 0; s < S; ++s, ++it)
             {
-                if (ns == 0) nxt = load_item(np);
-                prefetch<GROUPED, Q8>(nxt, 8 * ns + kw, KB, pn);
+                Pre pn = pc;
+                if (s + 1 < S) prefetch<GROUPED, Q8>(cur, 16 * (s + 1) + 2 * kw, KB, pn);
+                else if (p + 1 < p1) { nxt = load_item(p + 1); prefetch<GROUPED, Q8>(nxt, 2 * kw, KB, pn); }
+                const uint32_t st = it % NSTAGE;
+                if (!mbar_wait(full0 + st * 8, (it / NSTAGE) & 1, abort_flag, a.status)) { alive = false; break; }
+                if (16 * s + 2 * kw < KB)
+                    consume_group<GROUPED, Q8>(ring + st * STAGE_BYTES + mat * (STAGE_BYTES / 2) + kw * 4096, pc, acc, lane);
+                release_stage(free_cnt, it, total, lane, fill);
+                pc = pn;
             }
-            if (threadIdx.x == 0) produce(issued, total, it, empty0, abort_flag, a.status, fill);   // a failure raises the abort flag
-            __syncwarp();
-            const uint32_t st = it % NSTAGE;
-            if (!mbar_wait(full0 + st * 8, (it / NSTAGE) & 1, abort_flag, a.status)) break;
-            if (8 * s + kw < KB)
-                consume_block<GROUPED, Q8>(ring + st * STAGE_BYTES + mat * (STAGE_BYTES / 2) + kw * 2048, pc, acc, lane);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(empty0 + st * 8);
-            ++it;
-            if (s == S - 1)
+            if (!alive) break;
+            // This warp's partial tile joins the item's sums in shared memory; the last warp to arrive finishes the item.
+            const int b = (p - p0) % NBUF;
+            float* gb = gu + b * GU_FLOATS + mat * 512;
+            #pragma unroll
+            for (int ss = 0; ss < 4; ++ss)
             {
-                // partial tiles -> shared memory: red[warp][row][8 columns]
-                float* rp = red + warp * 64 * 8;
-                #pragma unroll
-                for (int ss = 0; ss < 4; ++ss)
+                atomicAdd(gb + (ss * 16 + g) * 8 + 2 * q, acc[ss][0]); atomicAdd(gb + (ss * 16 + g) * 8 + 2 * q + 1, acc[ss][1]);
+                atomicAdd(gb + (ss * 16 + g + 8) * 8 + 2 * q, acc[ss][2]); atomicAdd(gb + (ss * 16 + g + 8) * 8 + 2 * q + 1, acc[ss][3]);
+                acc[ss][0] = acc[ss][1] = acc[ss][2] = acc[ss][3] = 0.f;
+            }
+            __syncwarp();
+            int last = 0;
+            if (lane == 0) { __threadfence_block(); last = atomicAdd(cnt + b, 1) == CW - 1; }
+            last = __shfl_sync(0xffffffffu, last, 0);
+            if (last)
+            {
+                __threadfence_block();
+                // act = silu(gate) * up * routing weight for the 64 rows x 8 tile columns of the item
+                float* g0 = gu + b * GU_FLOATS;
+                #pragma unroll 1
+                for (int i = 0; i < 16; ++i)
                 {
-                    *(float2*) (rp + (ss * 16 + g) * 8 + 2 * q) = make_float2(acc[ss][0], acc[ss][1]);
-                    *(float2*) (rp + (ss * 16 + g + 8) * 8 + 2 * q) = make_float2(acc[ss][2], acc[ss][3]);
-                    acc[ss][0] = acc[ss][1] = acc[ss][2] = acc[ss][3] = 0.f;
-                }
-                __syncthreads();
-                // act = silu(gate) * up * routing weight. Warp w: tile column w / 2, rows 32 (w % 2) + lane of the group.
-                const int n = (warp & 1) * 32 + lane, col = warp >> 1;
-                float v = 0.f;
-                if (col < cur.nrows)
-                {
-                    float gg = 0.f, uu = 0.f;
-                    #pragma unroll
-                    for (int k = 0; k < 8; ++k) { gg += red[(k * 64 + n) * 8 + col]; uu += red[((8 + k) * 64 + n) * 8 + col]; }
-                    if (!GROUPED)
+                    const int col = i >> 1, n = (i & 1) * 32 + lane;
+                    float v = 0.f;
+                    if (col < cur.nrows)
                     {
-                        const float* gsp = cur.e >= 0 ? (const float*) a.gate_s[cur.e] : (const float*) a.sh_gs;
-                        const float* usp = cur.e >= 0 ? (const float*) a.up_s[cur.e] : (const float*) a.sh_us;
-                        gg *= __ldg(gsp + cur.gr * 64 + n); uu *= __ldg(usp + cur.gr * 64 + n);
+                        float gg = g0[n * 8 + col], uu = g0[512 + n * 8 + col];
+                        if (!GROUPED)
+                        {
+                            const float* gsp = cur.e >= 0 ? (const float*) a.gate_s[cur.e] : (const float*) a.sh_gs;
+                            const float* usp = cur.e >= 0 ? (const float*) a.up_s[cur.e] : (const float*) a.sh_us;
+                            gg *= __ldg(gsp + cur.gr * 64 + n); uu *= __ldg(usp + cur.gr * 64 + n);
+                        }
+                        v = gg / (1.f + expf(-gg)) * uu * rt->w[cur.tile][col];
                     }
-                    v = gg / (1.f + expf(-gg)) * uu * rt->w[cur.tile][col];
+                    const size_t row = (size_t) cur.tile * 8 + col;
+                    if (Q8)
+                    {
+                        // second int8 round trip of the CPU engine (cpuband.cpp:200-207): 32 consecutive outputs = this warp
+                        float m = fabsf(v);
+                        #pragma unroll
+                        for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+                        const float sc = m > 0.f ? __fdiv_rn(m, 127.f) : 1.f;
+                        v = (float) __float2int_rn(__fmul_rn(v, __fdiv_rn(1.f, sc)));
+                        if (lane == 0) a.ascale[row * (a.I / 32) + cur.gr * 2 + (i & 1)] = sc;
+                    }
+                    a.act[row * a.I + cur.gr * 64 + frag_pos(n >> 1) * 2 + (n & 1)] = __float2half_rn(v);
                 }
-                const size_t row = (size_t) cur.tile * 8 + col;
-                if (Q8)
-                {
-                    // second int8 round trip of the CPU engine (cpuband.cpp:200-207): 32 consecutive outputs = this warp
-                    float m = fabsf(v);
-                    #pragma unroll
-                    for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-                    const float sc = m > 0.f ? __fdiv_rn(m, 127.f) : 1.f;
-                    v = (float) __float2int_rn(__fmul_rn(v, __fdiv_rn(1.f, sc)));
-                    if (lane == 0) a.ascale[row * (a.I / 32) + cur.gr * 2 + (warp & 1)] = sc;
-                }
-                a.act[row * a.I + cur.gr * 64 + frag_pos(n >> 1) * 2 + (n & 1)] = __float2half_rn(v);
-                __syncthreads();
+                for (int i = lane; i < GU_FLOATS; i += 32) g0[i] = 0.f;
+                if (lane == 0) cnt[b] = 0;
             }
-            cur = nxt; pc = pn; p = np; s = ns;
+            cur = nxt;
         }
     }
     __syncthreads();
@@ -419,31 +429,32 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_down_kernel(const DecodeAr
 {
     extern __shared__ __align__(1024) unsigned char smem[];
     const uint32_t sbase = smem_u32(smem);
-    const uint32_t ring = sbase + SmemLayout::ring, full0 = sbase + SmemLayout::bars, empty0 = full0 + NSTAGE * 8;
-    float* yacc = (float*) (smem + SmemLayout::red);
+    const uint32_t ring = sbase + SmemLayout::ring, full0 = sbase + SmemLayout::bars;
+    float* yacc = (float*) (smem + SmemLayout::gu);
+    int* free_cnt = (int*) (smem + SmemLayout::cnt) + NBUF;
     volatile int* abort_flag = (volatile int*) (smem + SmemLayout::flags);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0)
     {
-        for (int i = 0; i < NSTAGE; ++i) { mbar_init(full0 + i * 8, 1); mbar_init(empty0 + i * 8, CW); }
+        for (int i = 0; i < NSTAGE; ++i) mbar_init(full0 + i * 8, 1);
+        for (int i = 0; i < NSTAGE; ++i) free_cnt[i] = 0;
         *abort_flag = 0;
         fence_barrier_init();
     }
     for (int i = threadIdx.x; i < YACC_FLOATS; i += blockDim.x) yacc[i] = 0.f;
     __syncthreads();
     const Route* rt = a.route;
-    const int NG = a.H / 64, KB = a.I / 64, S = (KB + 15) / 16;
+    const int NG = a.H / 64, KB = a.I / 64, S = (KB + 31) / 32;
     const int nt = rt->ntiles;
     const int P = nt * NG;
     const int p0 = (int) ((long long) P * blockIdx.x / gridDim.x), p1 = (int) ((long long) P * (blockIdx.x + 1) / gridDim.x);
     const int g = lane >> 2, q = lane & 3;
     const uint32_t total = (uint32_t) (p1 - p0) * S;
-    uint32_t issued = 0;
     auto fill = [&](uint32_t i) {
         const int p = p0 + (int) (i / S), s = (int) (i % S);
         const int gr = p / nt, tile = p % nt, e = rt->expert[tile];
-        const char* dw = (const char*) (e >= 0 ? (const void*) a.down_w[e] : a.sh_dw) + ((size_t) gr * KB + 16 * s) * 2048;
-        const uint32_t st = i % NSTAGE, bytes = (KB - 16 * s < 16 ? KB - 16 * s : 16) * 2048;
+        const char* dw = (const char*) (e >= 0 ? (const void*) a.down_w[e] : a.sh_dw) + ((size_t) gr * KB + 32 * s) * 2048;
+        const uint32_t st = i % NSTAGE, bytes = (KB - 32 * s < 32 ? KB - 32 * s : 32) * 2048;
         mbar_expect_tx(full0 + st * 8, bytes);
         bulk_g2s(ring + st * STAGE_BYTES, dw, bytes, full0 + st * 8);
     };
@@ -462,77 +473,71 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_down_kernel(const DecodeAr
     };
     if (p0 < p1)
     {
-        if (threadIdx.x == 0) produce(issued, total, 0, empty0, abort_flag, a.status, fill);
+        if (threadIdx.x == 0)
+            for (uint32_t i = 0; i < NSTAGE && i < total; ++i) fill(i);
         float acc[4][4];
         #pragma unroll
         for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
         Item cur = load_item(p0);
         Pre pc;
-        prefetch<GROUPED, Q8>(cur, warp, KB, pc);
+        prefetch<GROUPED, Q8>(cur, 2 * warp, KB, pc);
         uint32_t it = 0;
-        int p = p0, s = 0;
-        while (p < p1)
+        bool alive = true;
+        for (int p = p0; p < p1 && alive; ++p)
         {
-            int np = p, ns = s + 1;
-            if (ns == S) { ns = 0; np = p + 1; }
             Item nxt = cur;
-            Pre pn = pc;
-            if (np < p1)
+            for (int s = 0; s < S; ++s, ++it)
             {
-                if (ns == 0) nxt = load_item(np);
-                prefetch<GROUPED, Q8>(nxt, 16 * ns + warp, KB, pn);
+                Pre pn = pc;
+                if (s + 1 < S) prefetch<GROUPED, Q8>(cur, 32 * (s + 1) + 2 * warp, KB, pn);
+                else if (p + 1 < p1) { nxt = load_item(p + 1); prefetch<GROUPED, Q8>(nxt, 2 * warp, KB, pn); }
+                const uint32_t st = it % NSTAGE;
+                if (!mbar_wait(full0 + st * 8, (it / NSTAGE) & 1, abort_flag, a.status)) { alive = false; break; }
+                if (32 * s + 2 * warp < KB) consume_group<GROUPED, Q8>(ring + st * STAGE_BYTES + warp * 4096, pc, acc, lane);
+                release_stage(free_cnt, it, total, lane, fill);
+                pc = pn;
             }
-            if (threadIdx.x == 0) produce(issued, total, it, empty0, abort_flag, a.status, fill);   // a failure raises the abort flag
-            __syncwarp();
-            const uint32_t st = it % NSTAGE;
-            if (!mbar_wait(full0 + st * 8, (it / NSTAGE) & 1, abort_flag, a.status)) break;
-            if (16 * s + warp < KB) consume_block<GROUPED, Q8>(ring + st * STAGE_BYTES + warp * 2048, pc, acc, lane);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(empty0 + st * 8);
-            ++it;
-            if (s == S - 1)
+            if (!alive) break;
+            float sd[8];
+            #pragma unroll
+            for (int i = 0; i < 8; ++i) sd[i] = 1.f;
+            if (!GROUPED)
             {
-                float sd[8];
+                const float* dsp = cur.e >= 0 ? (const float*) a.down_s[cur.e] : (const float*) a.sh_ds;
                 #pragma unroll
-                for (int i = 0; i < 8; ++i) sd[i] = 1.f;
-                if (!GROUPED)
+                for (int ss = 0; ss < 4; ++ss) { sd[2 * ss] = __ldg(dsp + cur.gr * 64 + ss * 16 + g); sd[2 * ss + 1] = __ldg(dsp + cur.gr * 64 + ss * 16 + g + 8); }
+            }
+            // add this warp's share of the tile's contribution into the block's slice of y, real row by real row
+            #pragma unroll
+            for (int c = 0; c < 2; ++c)
+            {
+                const int col = 2 * q + c;
+                if (col < cur.nrows)
                 {
-                    const float* dsp = cur.e >= 0 ? (const float*) a.down_s[cur.e] : (const float*) a.sh_ds;
+                    float* yr = yacc + (int) rt->rows[cur.tile][col] * 64;
                     #pragma unroll
-                    for (int ss = 0; ss < 4; ++ss) { sd[2 * ss] = __ldg(dsp + cur.gr * 64 + ss * 16 + g); sd[2 * ss + 1] = __ldg(dsp + cur.gr * 64 + ss * 16 + g + 8); }
-                }
-                // add this warp's share of the tile's contribution into the block's slice of y, real row by real row
-                #pragma unroll
-                for (int c = 0; c < 2; ++c)
-                {
-                    const int col = 2 * q + c;
-                    if (col < cur.nrows)
+                    for (int ss = 0; ss < 4; ++ss)
                     {
-                        float* yr = yacc + (int) rt->rows[cur.tile][col] * 64;
-                        #pragma unroll
-                        for (int ss = 0; ss < 4; ++ss)
-                        {
-                            atomicAdd(yr + ss * 16 + g, acc[ss][c] * sd[2 * ss]);
-                            atomicAdd(yr + ss * 16 + g + 8, acc[ss][2 + c] * sd[2 * ss + 1]);
-                        }
+                        atomicAdd(yr + ss * 16 + g, acc[ss][c] * sd[2 * ss]);
+                        atomicAdd(yr + ss * 16 + g + 8, acc[ss][2 + c] * sd[2 * ss + 1]);
                     }
-                }
-                #pragma unroll
-                for (int ss = 0; ss < 4; ++ss) acc[ss][0] = acc[ss][1] = acc[ss][2] = acc[ss][3] = 0.f;
-                if (np >= p1 || np / nt != cur.gr)
-                {
-                    // the slice of y this block has been adding into is complete: one fp32 reduction per element to global
-                    __syncthreads();
-                    for (int i = threadIdx.x; i < R * 64; i += NTHREADS)
-                    {
-                        const float v = yacc[i];
-                        if (v != 0.f) atomicAdd(a.y + (size_t) (i >> 6) * a.H + cur.gr * 64 + (i & 63), v);
-                        yacc[i] = 0.f;
-                    }
-                    __syncthreads();
                 }
             }
-            cur = nxt; pc = pn; p = np; s = ns;
+            #pragma unroll
+            for (int ss = 0; ss < 4; ++ss) acc[ss][0] = acc[ss][1] = acc[ss][2] = acc[ss][3] = 0.f;
+            if (p + 1 >= p1 || (p + 1) / nt != cur.gr)
+            {
+                // the slice of y this block has been adding into is complete: one fp32 reduction per element to global
+                __syncthreads();
+                for (int i = threadIdx.x; i < R * 64; i += NTHREADS)
+                {
+                    const float v = yacc[i];
+                    if (v != 0.f) atomicAdd(a.y + (size_t) (i >> 6) * a.H + cur.gr * 64 + (i & 63), v);
+                    yacc[i] = 0.f;
+                }
+                __syncthreads();
+            }
+            cur = nxt;
         }
     }
     __syncthreads();
