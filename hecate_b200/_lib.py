@@ -7,7 +7,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "csrc", "libhecate_moe_b200.so")
+# HECATE_MOE_LIB selects another build of the same library (e.g. a debug or experimental build)
+LIB_PATH = os.environ.get("HECATE_MOE_LIB") or os.path.join(_HERE, "csrc", "libhecate_moe_b200.so")
 _lib = None
 
 F16, BF16, F32 = 0, 1, 2

@@ -118,19 +118,18 @@ __device__ __forceinline__ void mma_f16(float* c, const uint32_t* a, uint32_t b0
 // multiply-add with 1/16 and -72.)
 __device__ __forceinline__ void frag_from_codes(uint32_t w, uint32_t* a)
 {
-    const uint32_t MAGIC = 0x64006400u;              // 1024.0 in both halves
-    const uint32_t lo0 = (w & 0x000f000fu) | MAGIC, hi0 = (w & 0x00f000f0u) | MAGIC;
+    // Written as PTX with plain 32-bit immediates: half2 constants built through the cuda_fp16 helpers are re-materialised
+    // at every use (measured: six extra integer instructions per word).
     const uint32_t w8 = w >> 8;
-    const uint32_t lo1 = (w8 & 0x000f000fu) | MAGIC, hi1 = (w8 & 0x00f000f0u) | MAGIC;
-    const __half2 k1032 = __halves2half2(__ushort_as_half(0x6408), __ushort_as_half(0x6408));   // 1032
-    const __half2 k16th = __halves2half2(__ushort_as_half(0x2c00), __ushort_as_half(0x2c00));   // 1/16
-    const __half2 km72 = __halves2half2(__ushort_as_half(0xd480), __ushort_as_half(0xd480));    // -72
-    __half2 r0 = __hsub2(*reinterpret_cast<const __half2*>(&lo0), k1032);
-    __half2 r1 = __hfma2(*reinterpret_cast<const __half2*>(&hi0), k16th, km72);
-    __half2 r2 = __hsub2(*reinterpret_cast<const __half2*>(&lo1), k1032);
-    __half2 r3 = __hfma2(*reinterpret_cast<const __half2*>(&hi1), k16th, km72);
-    a[0] = *reinterpret_cast<uint32_t*>(&r0); a[1] = *reinterpret_cast<uint32_t*>(&r1);
-    a[2] = *reinterpret_cast<uint32_t*>(&r2); a[3] = *reinterpret_cast<uint32_t*>(&r3);
+    uint32_t lo0, hi0, lo1, hi1;
+    asm("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xea;" : "=r"(lo0) : "r"(w));     // (w & mask) | 1024.0 in both halves
+    asm("lop3.b32 %0, %1, 0x00f000f0, 0x64006400, 0xea;" : "=r"(hi0) : "r"(w));
+    asm("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xea;" : "=r"(lo1) : "r"(w8));
+    asm("lop3.b32 %0, %1, 0x00f000f0, 0x64006400, 0xea;" : "=r"(hi1) : "r"(w8));
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(a[0]) : "r"(lo0), "r"(0x64086408u));                            // - 1032
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(a[1]) : "r"(hi0), "r"(0x2c002c00u), "r"(0xd480d480u));   // / 16 - 72
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(a[2]) : "r"(lo1), "r"(0x64086408u));
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(a[3]) : "r"(hi1), "r"(0x2c002c00u), "r"(0xd480d480u));
 }
 
 // position of two-value word p (columns 2p, 2p+1 of a 64-column block) in the activation row order the kernels read:

@@ -188,6 +188,9 @@ struct DecodeArgs
 template <bool GROUPED, bool Q8>
 __device__ __forceinline__ void consume_group(uint32_t wsm, const Pre& pr, float (*acc)[4], int lane)
 {
+#if defined(HMOE_EXP) && HMOE_EXP == 1
+    { const uint4 v = lds128(wsm + lane * 16); acc[0][0] += __uint_as_float(v.x) * __uint_as_float(pr.bx[0][0] ^ pr.sc.x); return; }
+#endif
     const uint32_t scw[4] = {pr.sc.x, pr.sc.y, pr.sc.z, pr.sc.w};
     const float sxa[4] = {pr.sx[0].x, pr.sx[0].y, pr.sx[0].z, pr.sx[0].w}, sxb[4] = {pr.sx[1].x, pr.sx[1].y, pr.sx[1].z, pr.sx[1].w};
     // The four strips' sums are independent MMA chains; the steps are interleaved across strips so that consecutive MMAs
@@ -210,7 +213,11 @@ __device__ __forceinline__ void consume_group(uint32_t wsm, const Pre& pr, float
                 const uint32_t w = t == 0 ? w4[s].x : t == 1 ? w4[s].y : t == 2 ? w4[s].z : w4[s].w;
                 uint32_t a[4];
                 frag_from_codes(w, a);
+#if defined(HMOE_EXP) && HMOE_EXP == 2
+                part[s][0] += __uint_as_float(a[0] ^ a[1] ^ a[2] ^ a[3] ^ pr.bx[blk][2 * t] ^ pr.bx[blk][2 * t + 1]);
+#else
                 mma_f16((GROUPED || Q8) ? part[s] : acc[s], a, pr.bx[blk][2 * t], pr.bx[blk][2 * t + 1]);
+#endif
             }
             if (Q8 && (t & 1))
             {
@@ -349,6 +356,54 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_gate_up_kernel(const Decod
         prefetch<GROUPED, Q8>(cur, 2 * kw, KB, pc);
         uint32_t it = 0;
         bool alive = true;
+        // Finishing an item: warp w owns tile column w / 2 and rows 32 (w % 2) + lane of the 64-row group. It waits (bounded)
+        // until all CW partial tiles of the item are in, reads its gate / up sums, clears them for the buffer's next use and
+        // writes act = silu(gate) * up * routing weight as the down kernel's MMA operand. A warp does this one ring stage
+        // after it delivered its own partial, before it frees that stage, so a buffer is never reused too early: a warp
+        // can run at most NSTAGE stages (<= NSTAGE items) ahead of the slowest one and NBUF > NSTAGE.
+        Item prev = cur; bool have_prev = false; int prev_idx = 0;
+        auto finish_item = [&](const Item& pi, int idx) {
+            const int b = idx % NBUF, target = CW * (idx / NBUF + 1);
+            volatile int* c = cnt + b;
+            if (*c < target)
+            {
+                const unsigned long long t0 = globaltimer_ns();
+                while (*c < target)
+                    if (globaltimer_ns() - t0 > 1000000000ull) { *abort_flag = 1; atomicOr(a.status, ST_WAIT_TIMEOUT); break; }
+            }
+            __threadfence_block();
+            const int col = warp >> 1, n = (warp & 1) * 32 + lane;
+            float* g0 = gu + b * GU_FLOATS;
+            float gg = g0[n * 8 + col], uu = g0[512 + n * 8 + col];
+            g0[n * 8 + col] = 0.f; g0[512 + n * 8 + col] = 0.f;
+            float v = 0.f;
+#if defined(HMOE_EXP) && HMOE_EXP == 3
+            if (false)
+#else
+            if (col < pi.nrows)
+#endif
+            {
+                if (!GROUPED)
+                {
+                    const float* gsp = pi.e >= 0 ? (const float*) a.gate_s[pi.e] : (const float*) a.sh_gs;
+                    const float* usp = pi.e >= 0 ? (const float*) a.up_s[pi.e] : (const float*) a.sh_us;
+                    gg *= __ldg(gsp + pi.gr * 64 + n); uu *= __ldg(usp + pi.gr * 64 + n);
+                }
+                v = gg / (1.f + expf(-gg)) * uu * rt->w[pi.tile][col];
+            }
+            const size_t row = (size_t) pi.tile * 8 + col;
+            if (Q8)
+            {
+                // second int8 round trip of the CPU engine (cpuband.cpp:200-207): 32 consecutive outputs = this warp
+                float m = fabsf(v);
+                #pragma unroll
+                for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+                const float sc = m > 0.f ? __fdiv_rn(m, 127.f) : 1.f;
+                v = (float) __float2int_rn(__fmul_rn(v, __fdiv_rn(1.f, sc)));
+                if (lane == 0) a.ascale[row * (a.I / 32) + pi.gr * 2 + (warp & 1)] = sc;
+            }
+            a.act[row * a.I + pi.gr * 64 + frag_pos(n >> 1) * 2 + (n & 1)] = __float2half_rn(v);
+        };
         for (int p = p0; p < p1 && alive; ++p)
         {
             Item nxt = cur;
@@ -361,11 +416,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_gate_up_kernel(const Decod
                 if (!mbar_wait(full0 + st * 8, (it / NSTAGE) & 1, abort_flag, a.status)) { alive = false; break; }
                 if (16 * s + 2 * kw < KB)
                     consume_group<GROUPED, Q8>(ring + st * STAGE_BYTES + mat * (STAGE_BYTES / 2) + kw * 4096, pc, acc, lane);
+                if (s == 0 && have_prev) { finish_item(prev, prev_idx); have_prev = false; }
                 release_stage(free_cnt, it, total, lane, fill);
                 pc = pn;
             }
             if (!alive) break;
-            // This warp's partial tile joins the item's sums in shared memory; the last warp to arrive finishes the item.
+            // This warp's partial tile joins the item's sums in shared memory (buffer b, counted arrivals). Every warp later
+            // finishes its own 32 outputs of the item (see finish_item) once all sixteen partials are in.
             const int b = (p - p0) % NBUF;
             float* gb = gu + b * GU_FLOATS + mat * 512;
             #pragma unroll
@@ -376,48 +433,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_gate_up_kernel(const Decod
                 acc[ss][0] = acc[ss][1] = acc[ss][2] = acc[ss][3] = 0.f;
             }
             __syncwarp();
-            int last = 0;
-            if (lane == 0) { __threadfence_block(); last = atomicAdd(cnt + b, 1) == CW - 1; }
-            last = __shfl_sync(0xffffffffu, last, 0);
-            if (last)
-            {
-                __threadfence_block();
-                // act = silu(gate) * up * routing weight for the 64 rows x 8 tile columns of the item
-                float* g0 = gu + b * GU_FLOATS;
-                #pragma unroll 1
-                for (int i = 0; i < 16; ++i)
-                {
-                    const int col = i >> 1, n = (i & 1) * 32 + lane;
-                    float v = 0.f;
-                    if (col < cur.nrows)
-                    {
-                        float gg = g0[n * 8 + col], uu = g0[512 + n * 8 + col];
-                        if (!GROUPED)
-                        {
-                            const float* gsp = cur.e >= 0 ? (const float*) a.gate_s[cur.e] : (const float*) a.sh_gs;
-                            const float* usp = cur.e >= 0 ? (const float*) a.up_s[cur.e] : (const float*) a.sh_us;
-                            gg *= __ldg(gsp + cur.gr * 64 + n); uu *= __ldg(usp + cur.gr * 64 + n);
-                        }
-                        v = gg / (1.f + expf(-gg)) * uu * rt->w[cur.tile][col];
-                    }
-                    const size_t row = (size_t) cur.tile * 8 + col;
-                    if (Q8)
-                    {
-                        // second int8 round trip of the CPU engine (cpuband.cpp:200-207): 32 consecutive outputs = this warp
-                        float m = fabsf(v);
-                        #pragma unroll
-                        for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-                        const float sc = m > 0.f ? __fdiv_rn(m, 127.f) : 1.f;
-                        v = (float) __float2int_rn(__fmul_rn(v, __fdiv_rn(1.f, sc)));
-                        if (lane == 0) a.ascale[row * (a.I / 32) + cur.gr * 2 + (i & 1)] = sc;
-                    }
-                    a.act[row * a.I + cur.gr * 64 + frag_pos(n >> 1) * 2 + (n & 1)] = __float2half_rn(v);
-                }
-                for (int i = lane; i < GU_FLOATS; i += 32) g0[i] = 0.f;
-                if (lane == 0) cnt[b] = 0;
-            }
+            if (lane == 0) { __threadfence_block(); atomicAdd(cnt + b, 1); }
+            prev = cur; have_prev = true; prev_idx = p - p0;
             cur = nxt;
         }
+        if (alive && have_prev) finish_item(prev, prev_idx);
     }
     __syncthreads();
 }
