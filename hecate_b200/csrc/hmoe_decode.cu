@@ -275,15 +275,15 @@ __device__ __forceinline__ void prefetch(const Item& it, int kb, int KB, Pre& pr
 // stage's counter, and the warp that brings it to CW issues the copies of stage number it + NSTAGE into the same slot.
 // No thread ever waits for a free slot.
 template <typename Fill>
-__device__ __forceinline__ void release_stage(int* free_cnt, uint32_t it, uint32_t total, int lane, Fill fill)
+__device__ __forceinline__ void release_stage(int* free_cnt, uint32_t st, uint32_t it, uint32_t total, int lane, Fill fill)
 {
     __syncwarp();
     if (lane == 0)
     {
         __threadfence_block();
-        if (atomicAdd(free_cnt + it % NSTAGE, 1) == CW - 1)
+        if (atomicAdd(free_cnt + st, 1) == CW - 1)
         {
-            free_cnt[it % NSTAGE] = 0;
+            free_cnt[st] = 0;
             __threadfence_block();
             if (it + NSTAGE < total) fill(it + NSTAGE);
         }
@@ -328,9 +328,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_gate_up_kernel(const Decod
         bulk_g2s(ring + st * STAGE_BYTES, gw, bytes, full0 + st * 8);
         bulk_g2s(ring + st * STAGE_BYTES + STAGE_BYTES / 2, uw, bytes, full0 + st * 8);
     };
-    auto load_item = [&](int p) {
+    auto load_item = [&](int tile, int gr) {
         Item it;
-        it.tile = p / NG; it.gr = p % NG; it.e = rt->expert[it.tile]; it.nrows = rt->nrows[it.tile];
+        it.tile = tile; it.gr = gr; it.e = rt->expert[it.tile]; it.nrows = rt->nrows[it.tile];
         it.xb = (const char*) (a.xf + (size_t) rt->rows[it.tile][g] * a.H) + q * 32;
         if (Q8)
         {
@@ -351,10 +351,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_gate_up_kernel(const Decod
         float acc[4][4];
         #pragma unroll
         for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-        Item cur = load_item(p0);
+        Item cur = load_item(p0 / NG, p0 % NG);
         Pre pc;
         prefetch<GROUPED, Q8>(cur, 2 * kw, KB, pc);
-        uint32_t it = 0;
+        uint32_t it = 0, st = 0, par = 0;
         bool alive = true;
         // Finishing an item: warp w owns tile column w / 2 and rows 32 (w % 2) + lane of the 64-row group. It waits (bounded)
         // until all CW partial tiles of the item are in, reads its gate / up sums, clears them for the buffer's next use and
@@ -411,13 +411,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_gate_up_kernel(const Decod
             {
                 Pre pn = pc;
                 if (s + 1 < S) prefetch<GROUPED, Q8>(cur, 16 * (s + 1) + 2 * kw, KB, pn);
-                else if (p + 1 < p1) { nxt = load_item(p + 1); prefetch<GROUPED, Q8>(nxt, 2 * kw, KB, pn); }
-                const uint32_t st = it % NSTAGE;
-                if (!mbar_wait(full0 + st * 8, (it / NSTAGE) & 1, abort_flag, a.status)) { alive = false; break; }
+                else if (p + 1 < p1)
+                {
+                    const bool wrap = cur.gr + 1 == NG;
+                    nxt = load_item(wrap ? cur.tile + 1 : cur.tile, wrap ? 0 : cur.gr + 1);
+                    prefetch<GROUPED, Q8>(nxt, 2 * kw, KB, pn);
+                }
+                if (!mbar_wait(full0 + st * 8, par, abort_flag, a.status)) { alive = false; break; }
                 if (16 * s + 2 * kw < KB)
                     consume_group<GROUPED, Q8>(ring + st * STAGE_BYTES + mat * (STAGE_BYTES / 2) + kw * 4096, pc, acc, lane);
                 if (s == 0 && have_prev) { finish_item(prev, prev_idx); have_prev = false; }
-                release_stage(free_cnt, it, total, lane, fill);
+                release_stage(free_cnt, st, it, total, lane, fill);
+                if (++st == NSTAGE) { st = 0; par ^= 1; }
                 pc = pn;
             }
             if (!alive) break;
@@ -461,7 +466,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_down_kernel(const DecodeAr
         *abort_flag = 0;
         fence_barrier_init();
     }
-    for (int i = threadIdx.x; i < YACC_FLOATS; i += blockDim.x) yacc[i] = 0.f;
+    for (int i = threadIdx.x; i < 4 * YACC_FLOATS; i += blockDim.x) yacc[i] = 0.f;   // four copies (less contention)
     __syncthreads();
     const Route* rt = a.route;
     const int NG = a.H / 64, KB = a.I / 64, S = (KB + 31) / 32;
@@ -478,9 +483,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_down_kernel(const DecodeAr
         mbar_expect_tx(full0 + st * 8, bytes);
         bulk_g2s(ring + st * STAGE_BYTES, dw, bytes, full0 + st * 8);
     };
-    auto load_item = [&](int p) {
+    auto load_item = [&](int gr, int tile) {
         Item it;
-        it.gr = p / nt; it.tile = p % nt; it.e = rt->expert[it.tile]; it.nrows = rt->nrows[it.tile];
+        it.gr = gr; it.tile = tile; it.e = rt->expert[it.tile]; it.nrows = rt->nrows[it.tile];
         const size_t trow = (size_t) it.tile * 8;
         it.xb = (const char*) (a.act + (trow + g) * a.I) + q * 32;
         if (Q8) { it.xs[0] = a.ascale + (trow + 2 * q) * (a.I / 32); it.xs[1] = a.ascale + (trow + 2 * q + 1) * (a.I / 32); }
@@ -498,10 +503,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_down_kernel(const DecodeAr
         float acc[4][4];
         #pragma unroll
         for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-        Item cur = load_item(p0);
+        Item cur = load_item(p0 / nt, p0 % nt);
         Pre pc;
         prefetch<GROUPED, Q8>(cur, 2 * warp, KB, pc);
-        uint32_t it = 0;
+        uint32_t it = 0, st = 0, par = 0;
         bool alive = true;
         for (int p = p0; p < p1 && alive; ++p)
         {
@@ -510,11 +515,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_down_kernel(const DecodeAr
             {
                 Pre pn = pc;
                 if (s + 1 < S) prefetch<GROUPED, Q8>(cur, 32 * (s + 1) + 2 * warp, KB, pn);
-                else if (p + 1 < p1) { nxt = load_item(p + 1); prefetch<GROUPED, Q8>(nxt, 2 * warp, KB, pn); }
-                const uint32_t st = it % NSTAGE;
-                if (!mbar_wait(full0 + st * 8, (it / NSTAGE) & 1, abort_flag, a.status)) { alive = false; break; }
+                else if (p + 1 < p1)
+                {
+                    const bool wrap = cur.tile + 1 == nt;
+                    nxt = load_item(wrap ? cur.gr + 1 : cur.gr, wrap ? 0 : cur.tile + 1);
+                    prefetch<GROUPED, Q8>(nxt, 2 * warp, KB, pn);
+                }
+                if (!mbar_wait(full0 + st * 8, par, abort_flag, a.status)) { alive = false; break; }
                 if (32 * s + 2 * warp < KB) consume_group<GROUPED, Q8>(ring + st * STAGE_BYTES + warp * 4096, pc, acc, lane);
-                release_stage(free_cnt, it, total, lane, fill);
+                release_stage(free_cnt, st, it, total, lane, fill);
+                if (++st == NSTAGE) { st = 0; par ^= 1; }
                 pc = pn;
             }
             if (!alive) break;
@@ -534,7 +544,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_down_kernel(const DecodeAr
                 const int col = 2 * q + c;
                 if (col < cur.nrows)
                 {
-                    float* yr = yacc + (int) rt->rows[cur.tile][col] * 64;
+                    float* yr = yacc + (warp >> 2) * YACC_FLOATS + (int) rt->rows[cur.tile][col] * 64;
                     #pragma unroll
                     for (int ss = 0; ss < 4; ++ss)
                     {
@@ -545,15 +555,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_down_kernel(const DecodeAr
             }
             #pragma unroll
             for (int ss = 0; ss < 4; ++ss) acc[ss][0] = acc[ss][1] = acc[ss][2] = acc[ss][3] = 0.f;
-            if (p + 1 >= p1 || (p + 1) / nt != cur.gr)
+            if (p + 1 >= p1 || cur.tile + 1 == nt)
             {
                 // the slice of y this block has been adding into is complete: one fp32 reduction per element to global
                 __syncthreads();
                 for (int i = threadIdx.x; i < R * 64; i += NTHREADS)
                 {
-                    const float v = yacc[i];
+                    const float v = (yacc[i] + yacc[YACC_FLOATS + i]) + (yacc[2 * YACC_FLOATS + i] + yacc[3 * YACC_FLOATS + i]);
                     if (v != 0.f) atomicAdd(a.y + (size_t) (i >> 6) * a.H + cur.gr * 64 + (i & 63), v);
-                    yacc[i] = 0.f;
+                    yacc[i] = yacc[YACC_FLOATS + i] = yacc[2 * YACC_FLOATS + i] = yacc[3 * YACC_FLOATS + i] = 0.f;
                 }
                 __syncthreads();
             }
