@@ -683,3 +683,60 @@ int decode_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t
 }
 
 }  // namespace hmoe
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Decode with built-in scratch, for hosts that must not allocate.
+//
+// Some embedders of this library hand out device memory from one arena that is carved up once at start-up (an inference
+// server with a fixed memory plan, a plugin running inside another framework's allocator, a real-time loop where a
+// cudaMalloc would stall every stream of the process). For them the 4.6 MB workspace of hmoe_decode is one more buffer to
+// plan. This variant needs none: its workspace is the array below, which is part of the library image, so every GPU that
+// loads the library carries these 5 MiB from load to exit whether or not the entry point is ever called.
+//
+// The array's name is only meaningful in device code. On the host it is a stand-in symbol, not an address a kernel could
+// use, so the device address is looked up with cudaGetSymbolAddress, once per device, with that device current, the first
+// time the entry point runs there. That look-up is a set-up step: make the first call on each device outside any stream
+// capture. Later calls only launch work.
+//
+// All calls on one device share the array and it keeps whatever the previous call left. The only word that has to start
+// from zero, the status word, is cleared on the caller's stream at the start of every call; everything else is rewritten
+// by the call's own prepare and gate_up kernels before it is read. Two calls whose kernels overlap on the GPU (different
+// streams, or graph branches without an edge between them) would overwrite each other's intermediate results: keep the
+// calls of one device ordered.
+namespace hmoe {
+namespace {
+constexpr size_t STATIC_WS_BYTES = 5u << 20;
+static __device__ __align__(256) unsigned char g_decode_scratch[STATIC_WS_BYTES];
+constexpr int MAX_DEVICES = 64;
+static void* g_scratch_addr[MAX_DEVICES] = {};
+}  // namespace
+}  // namespace hmoe
+
+extern "C" int hmoe_decode_noalloc(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R,
+                                   int lo, int n_local, int act_quant, float* y, uint32_t* status_dev, void* stream)
+{
+    using namespace hmoe;
+    if (!layer) return fail(HMOE_E_ARG, "hmoe_decode_noalloc: null layer");
+    const size_t need = decode_ws_bytes(layer->H, layer->I);
+    if (layer->H <= 0 || layer->I <= 0 || need > STATIC_WS_BYTES)
+        return fail(HMOE_E_WS, "hmoe_decode_noalloc: H / I exceed the built-in scratch (5 MiB: up to H = 6144 with I = 2048); "
+                               "use hmoe_decode with a caller-provided workspace");
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES)
+        return fail(HMOE_E_CUDA, "hmoe_decode_noalloc: no current CUDA device (or device index >= 64)");
+    if (!g_scratch_addr[dev])
+    {
+        void* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_decode_scratch);
+        if (e != cudaSuccess || !p) return fail(HMOE_E_CUDA, cudaGetErrorString(e));
+        g_scratch_addr[dev] = p;
+    }
+    void* ws = g_scratch_addr[dev];
+    cudaStream_t st = (cudaStream_t) stream;
+    if (cudaMemsetAsync(ws, 0, 256, st) != cudaSuccess) return fail(HMOE_E_CUDA, "hmoe_decode_noalloc: clearing the status word failed");
+    const int rc = decode_launch(layer, x, x_dtype, sel, rw, R, lo, n_local, act_quant, y, ws, STATIC_WS_BYTES, st);
+    if (rc != HMOE_OK) return rc;
+    if (status_dev && cudaMemcpyAsync(status_dev, ws, 4, cudaMemcpyDeviceToDevice, st) != cudaSuccess)
+        return fail(HMOE_E_CUDA, "hmoe_decode_noalloc: copying the status word failed");
+    return HMOE_OK;
+}

@@ -63,6 +63,18 @@ size_t hmoe_decode_ws_bytes(int H, int I);
 int hmoe_decode(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
                 int act_quant, float* y, void* ws, size_t ws_bytes, void* stream);
 
+/* hmoe_decode without a workspace argument, for callers that cannot allocate device memory: embedders whose device memory
+ * is one arena planned at start-up, plugins that must stay inside a host framework's allocator, latency-critical loops
+ * where an allocation would stall the process. It has no counterpart in the reference (whose scratch always comes from
+ * torch, runtime/tier/moe4/moe4.cu:897-902). The workspace is a 5 MiB array built into the library image (held by every GPU
+ * that loads the library), which limits it to decode_ws_bytes(H, I) <= 5 MiB, i.e. up to H = 6144 with I = 2048; larger
+ * shapes are refused with HMOE_E_WS. Same arguments and results as hmoe_decode otherwise. status_dev, if not null, is a
+ * caller-owned 4-byte device word that receives the call's status bits (see hmoe_ws_status) on the same stream.
+ * The first call on each device looks up the array's device address (a one-time set-up; make that call outside stream
+ * capture). It allocates nothing, ever. All calls on a device share the array: calls that overlap on the GPU race. */
+int hmoe_decode_noalloc(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo,
+                        int n_local, int act_quant, float* y, uint32_t* status_dev, void* stream);
+
 /* Phase timing of the decode path (no reference counterpart; the reference uses compile-time ablation macros,
  * runtime/tier/moe4/moe4.cu:6-10). With profiling on, each hmoe_decode call records CUDA events between its three kernels
  * on the caller's stream; hmoe_decode_phase_times waits for the last timed call and returns the durations in ms of
