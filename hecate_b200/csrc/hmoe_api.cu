@@ -101,6 +101,22 @@ int hmoe_decode(const hmoe_layer* layer, const void* x, int x_dtype, const int64
     return decode_launch(layer, x, x_dtype, sel, rw, R, lo, n_local, act_quant, y, ws, ws_bytes, (cudaStream_t) stream);
 }
 
+size_t hmoe_prefill_ws_bytes(int R, int topk, int n_local, int H, int I) { return prefill_ws_bytes(R, topk, n_local, H, I); }
+int hmoe_prefill(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
+                 int act_quant, float* out, void* ws, size_t ws_bytes, void* stream)
+{
+    if (!layer) return fail(HMOE_E_ARG, "hmoe_prefill: null layer");
+    return prefill_launch(layer, x, x_dtype, sel, rw, R, lo, n_local, act_quant, out, ws, ws_bytes, (cudaStream_t) stream);
+}
+size_t hmoe_permute_ws_bytes(int R, int topk, int n_local) { return permute_ws_bytes(R, topk, n_local); }
+int hmoe_permute(const int64_t* sel, const void* rw, int R, int topk, int lo, int n_local, int shared_rows, int bm, int balance,
+                 int32_t* order, int32_t* tok, int32_t* eid, float* wt, int32_t* counts, int32_t* rbt, int32_t* plan, void* ws, size_t ws_bytes,
+                 void* stream)
+{
+    return permute_launch(sel, rw, R, topk, lo, n_local, shared_rows, bm, balance, order, tok, eid, wt, counts, rbt, plan, ws, ws_bytes,
+                          (cudaStream_t) stream);
+}
+
 int hmoe_set_profiling(int on) { return decode_set_profiling(on); }
 int hmoe_decode_phase_times(float* ms3) { return ms3 ? decode_phase_times(ms3) : fail(HMOE_E_ARG, "hmoe_decode_phase_times: null pointer"); }
 

@@ -1,0 +1,623 @@
+// Prefill path of the MoE expert layer (hundreds to tens of thousands of rows), sm_100a: token permutation on the device
+// and two grouped GEMMs on the tcgen05 tensor cores with the int4 weights dequantised on the way into shared memory.
+//
+// Replaces, behind the same operator surface (packed int4 experts in the reference's fragment order, (sel, rw) routing, fp32
+// output added into `out`):
+//   * the host-side permutation of runtime/tier/tier_split.py:404-412,433-455 (stable argsort by expert id, bincount with a
+//     host sync, numpy row blocks from runtime/tier/rtx_split.py:236-255 copied to the device per group) by three small
+//     kernels with no host synchronisation: histogram per 1024-pick chunk, scan + balanced row-block table, stable scatter;
+//   * gather_kernel / p4t_gu_kernel / p4t_gemm_kernel of runtime/tier/moe4/moe4t.cu:113-433 by the kernels below.
+//
+// GEMM orientation: D[channel][pick] = W[channel][k] . X[pick][k]: the weights are the M = 128 operand, the picks of one
+// row block (<= 256, one expert) the N operand, fp32 accumulators in tensor memory. Per 64-column stage:
+//   warps 0-7  read the packed codes of the tile straight from global memory (16 bytes per lane, the stored fragment order),
+//              turn them into fp16 (times the bf16 group scale in the group format) and store them as a K-major,
+//              128-byte-swizzled operand tile (4-byte stores, conflict free);
+//   warp 8     one thread loads the row block's 256 x 64 input tile with one 2-D TMA copy (128-byte swizzle, rows beyond the
+//              array zero-filled);
+//   warp 9     one thread issues tcgen05.mma (M 128, N = picks rounded up to 16, K 16) four times per matrix and commits the
+//              stage back to the producers.
+// gate_up keeps two accumulators (gate, up: 2 x 256 columns) over the same input tile and its epilogue writes
+// act = SiLU(g) * u * routing weight in fp16; down adds scale * sum into out[token] with coalesced fp32 reductions.
+// Blocks are persistent (one per SM) over (row block, channel tile) items, channel tile fastest, so the blocks working at
+// the same time share one input tile and one expert's weights through L2.
+// Every wait is bounded (see mbar_wait); tensor memory is released by the warp that allocated it on every path.
+#include <cuda.h>
+#include "hmoe_common.cuh"
+#include "hmoe_internal.h"
+
+namespace hmoe {
+namespace {
+
+constexpr int TM = 128, TN = 256, TK = 64;
+constexpr int PF_THREADS = 320;                 // warps 0-7 dequantise / epilogue, 8 TMA, 9 MMA
+constexpr int CHUNK = 1024;                     // picks per permutation block (one warp)
+
+// ---------------------------------------------------------------------------------------------------------------------
+// permutation
+struct Plan
+{
+    int total;          // routed local picks + shared rows
+    int nrb;            // row blocks
+    int pad[2];
+};
+
+// per 1024-pick chunk: how many picks of each local expert
+__global__ void __launch_bounds__(32) permute_hist_kernel(const int64_t* __restrict__ sel, int P, int lo, int n_local, int* __restrict__ block_hist)
+{
+    __shared__ int hist[256];
+    const int lane = threadIdx.x, base = blockIdx.x * CHUNK;
+    for (int e = lane; e < n_local; e += 32) hist[e] = 0;
+    __syncwarp();
+    for (int i = base + lane; i < base + CHUNK && i < P; i += 32)
+    {
+        const int64_t e = sel[i] - lo;
+        if (e >= 0 && e < n_local) atomicAdd(&hist[(int) e], 1);
+    }
+    __syncwarp();
+    for (int e = lane; e < n_local; e += 32) block_hist[(size_t) blockIdx.x * n_local + e] = hist[e];
+}
+
+// one block: chunk offsets per expert, expert offsets, the shared expert's segment, balanced row blocks
+// (runtime/tier/rtx_split.py:236-255 with one pick group: experts without picks emit nothing, an expert's blocks get
+// near-equal sizes when `balance`, {expert, first pick, picks, 0})
+__global__ void __launch_bounds__(256) permute_scan_kernel(int* __restrict__ block_hist, int nblocks, int n_local, int shared_rows, int bm,
+                                                          int balance, int* __restrict__ counts, int* __restrict__ offs, int* __restrict__ rbt,
+                                                          Plan* __restrict__ plan)
+{
+    __shared__ int cnt[257], off[258], rb0[258];
+    const int t = threadIdx.x;
+    const int ne = n_local + (shared_rows > 0 ? 1 : 0);
+    for (int e = t; e < n_local; e += blockDim.x)
+    {
+        int run = 0;
+        for (int b = 0; b < nblocks; ++b) { const int v = block_hist[(size_t) b * n_local + e]; block_hist[(size_t) b * n_local + e] = run; run += v; }
+        cnt[e] = run;
+    }
+    if (t == 0 && shared_rows > 0) cnt[n_local] = shared_rows;
+    __syncthreads();
+    if (t == 0)
+    {
+        int o = 0, r = 0;
+        for (int e = 0; e < ne; ++e) { off[e] = o; rb0[e] = r; o += cnt[e]; r += (cnt[e] + bm - 1) / bm; }
+        off[ne] = o; rb0[ne] = r;
+        plan->total = o; plan->nrb = r; plan->pad[0] = plan->pad[1] = 0;
+    }
+    __syncthreads();
+    for (int e = t; e <= ne; e += blockDim.x) { offs[e] = off[e]; if (e < ne) counts[e] = cnt[e]; }
+    for (int e = t; e < ne; e += blockDim.x)
+    {
+        const int c = cnt[e], nb = (c + bm - 1) / bm;
+        for (int k = 0; k < nb; ++k)
+        {
+            int rows, start;
+            if (balance) { const int base = c / nb, extra = c % nb; rows = base + (k < extra ? 1 : 0); start = k * base + (k < extra ? k : extra); }
+            else { rows = c - bm * k < bm ? c - bm * k : bm; start = bm * k; }
+            int* r = rbt + 4 * (rb0[e] + k);
+            r[0] = e; r[1] = off[e] + start; r[2] = rows; r[3] = 0;
+        }
+    }
+}
+
+// stable scatter: pick i goes to offs[e] + (picks of e in earlier chunks) + (picks of e earlier in this chunk)
+__global__ void __launch_bounds__(32) permute_scatter_kernel(const int64_t* __restrict__ sel, const __half* __restrict__ rw, int P, int topk,
+    int lo, int n_local, int shared_rows, const int* __restrict__ block_hist, const int* __restrict__ offs, int nblocks,
+    int* __restrict__ order, int* __restrict__ tok, int* __restrict__ eid, float* __restrict__ wt)
+{
+    const int lane = threadIdx.x;
+    if ((int) blockIdx.x >= nblocks)
+    {
+        // the shared expert's rows: every row once, in order, weight 1
+        const int base = ((int) blockIdx.x - nblocks) * CHUNK, o = offs[n_local];
+        for (int r = base + lane; r < base + CHUNK && r < shared_rows; r += 32) { tok[o + r] = r; eid[o + r] = n_local; wt[o + r] = 1.f; if (order) order[o + r] = -1; }
+        return;
+    }
+    __shared__ int seen[256];
+    for (int e = lane; e < n_local; e += 32) seen[e] = 0;
+    __syncwarp();
+    const int base = blockIdx.x * CHUNK;
+    for (int i0 = base; i0 < base + CHUNK && i0 < P; i0 += 32)
+    {
+        const int i = i0 + lane;
+        int e = -1;
+        if (i < P) { const int64_t v = sel[i] - lo; if (v >= 0 && v < n_local) e = (int) v; }
+        const unsigned same = __match_any_sync(0xffffffffu, e);
+        if (e >= 0)
+        {
+            const int rank = __popc(same & ((1u << lane) - 1u));
+            const int pos = offs[e] + block_hist[(size_t) blockIdx.x * n_local + e] + seen[e] + rank;
+            if (order) order[pos] = i;
+            tok[pos] = i / topk; eid[pos] = e; wt[pos] = __half2float(rw[i]);
+        }
+        __syncwarp();
+        if (e >= 0 && (same >> lane) == 1u) seen[e] += __popc(same);      // the highest lane of each group updates the count
+        __syncwarp();
+    }
+}
+
+// xg[pos][H] = fp16(x[tok[pos]]), optionally after the CPU engine's int8 round trip (runtime/tier/cpuband.cpp:106-111)
+__global__ void __launch_bounds__(192) gather_kernel(const void* __restrict__ x, int x_bf16, const int* __restrict__ tok, const Plan* __restrict__ plan,
+                                                     int H, int act_quant, __half* __restrict__ xg)
+{
+    const int pos = blockIdx.x;
+    if (pos >= plan->total) return;
+    const int r = tok[pos];
+    for (int gi = threadIdx.x; gi < H / 32; gi += blockDim.x)
+    {
+        float v[32];
+        if (x_bf16)
+        {
+            const uint4* p = (const uint4*) ((const uint16_t*) x + (size_t) r * H + gi * 32);
+            #pragma unroll
+            for (int j = 0; j < 4; ++j)
+            {
+                const uint4 u = p[j]; const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+                #pragma unroll
+                for (int k = 0; k < 4; ++k) { v[j * 8 + 2 * k] = __uint_as_float(w[k] << 16); v[j * 8 + 2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u); }
+            }
+        }
+        else
+        {
+            const uint4* p = (const uint4*) ((const __half*) x + (size_t) r * H + gi * 32);
+            #pragma unroll
+            for (int j = 0; j < 4; ++j)
+            {
+                const uint4 u = p[j]; const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+                #pragma unroll
+                for (int k = 0; k < 4; ++k) { const float2 f = __half22float2(*(const __half2*) &w[k]); v[j * 8 + 2 * k] = f.x; v[j * 8 + 2 * k + 1] = f.y; }
+            }
+        }
+        if (act_quant)
+        {
+            float m = 0.f;
+            #pragma unroll
+            for (int k = 0; k < 32; ++k) m = fmaxf(m, fabsf(v[k]));
+            const float s = m > 0.f ? __fdiv_rn(m, 127.f) : 1.f, inv = __fdiv_rn(1.f, s);
+            #pragma unroll
+            for (int k = 0; k < 32; ++k) v[k] = __fmul_rn((float) __float2int_rn(__fmul_rn(v[k], inv)), s);
+        }
+        uint4* d = (uint4*) (xg + (size_t) pos * H + gi * 32);
+        #pragma unroll
+        for (int j = 0; j < 4; ++j)
+        {
+            uint32_t w[4];
+            #pragma unroll
+            for (int k = 0; k < 4; ++k) { const __half2 h = __floats2half2_rn(v[j * 8 + 2 * k], v[j * 8 + 2 * k + 1]); w[k] = *(const uint32_t*) &h; }
+            d[j] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// tcgen05 helpers
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// shared-memory operand descriptor: K-major tile, 128-byte swizzle, rows of 128 bytes, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr)
+{
+    return (uint64_t) ((addr & 0x3FFFFu) >> 4) | ((uint64_t) 1 << 16) | ((uint64_t) (1024 >> 4) << 32) | ((uint64_t) 1 << 46) | ((uint64_t) 2 << 61);
+}
+__device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+                 ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r)
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+                 "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+                   "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+                   "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+                   "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]) : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"((uint64_t) map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) { asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory"); }
+
+struct GemmArgs
+{
+    int K, N;                 // reduction length and output channels of the matrix (gate_up: K = H, N = I; down: K = I, N = H)
+    int grouped;              // bf16 scale per 128 columns (else fp32 per row)
+    int act_quant;
+    const int64_t* w0; const int64_t* w1;     // pointer tables of the matrix (gate, up) or (down, -)
+    const int64_t* s0; const int64_t* s1;     // scale tables
+    const void* sh_w0; const void* sh_w1; const void* sh_s0; const void* sh_s1;   // shared expert (expert id n_local)
+    int n_local;
+    const Plan* plan; const int* rbt; const int* tok; const float* wt;
+    __half* act;              // gate_up: output [pos][I]
+    float* out;               // down: output [R][H], added into
+    unsigned* status;
+};
+
+// One 16-row x 64-column strip of packed codes (one 16-byte word per lane) -> 16 fp16x2 values stored into the K-major
+// 128-byte-swizzled operand tile. r8 = index of the strip's first 8-row group in the tile; the lane's rows are g and g + 8.
+__device__ __forceinline__ void store_strip(uint32_t tile, int r8, int g, int q, const uint4& w, uint32_t s_lo, uint32_t s_hi, bool scaled)
+{
+    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+    const uint32_t row0 = tile + r8 * 1024 + g * 128 + 4 * q, row1 = row0 + 1024;
+    #pragma unroll
+    for (int t = 0; t < 4; ++t)
+    {
+        uint32_t a[4];
+        frag_from_codes(ww[t], a);
+        if (scaled)
+        {
+            asm("mul.f16x2 %0, %0, %1;" : "+r"(a[0]) : "r"(s_lo)); asm("mul.f16x2 %0, %0, %1;" : "+r"(a[2]) : "r"(s_lo));
+            asm("mul.f16x2 %0, %0, %1;" : "+r"(a[1]) : "r"(s_hi)); asm("mul.f16x2 %0, %0, %1;" : "+r"(a[3]) : "r"(s_hi));
+        }
+        const uint32_t c0 = (uint32_t) (((2 * t) ^ g) << 4), c1 = (uint32_t) (((2 * t + 1) ^ g) << 4);
+        sts32(row0 + c0, a[0]); sts32(row1 + c0, a[1]); sts32(row0 + c1, a[2]); sts32(row1 + c1, a[3]);
+    }
+}
+
+// bf16 pair (rows g, g + 8 of a strip) -> two fp16x2 broadcast registers
+__device__ __forceinline__ void scale_pair(uint32_t bf2, uint32_t& s_lo, uint32_t& s_hi)
+{
+    const __half2 lo = __float2half2_rn(__uint_as_float(bf2 << 16)), hi = __float2half2_rn(__uint_as_float(bf2 & 0xffff0000u));
+    s_lo = *(const uint32_t*) &lo; s_hi = *(const uint32_t*) &hi;
+}
+
+template <int NMAT>
+struct PfSmem
+{
+    static constexpr int STAGES = NMAT == 2 ? 3 : 4;
+    static constexpr int A_BYTES = TM * TK * 2;             // 16 KB per matrix
+    static constexpr int B_BYTES = TN * TK * 2;             // 32 KB
+    static constexpr int STAGE = NMAT * A_BYTES + B_BYTES;
+    static constexpr int bars = STAGES * STAGE;             // full_a[S], full_b[S], empty[S], done, tmem_free
+    static constexpr int misc = bars + (3 * STAGES + 2) * 8;
+    static constexpr int total = misc + 32 + 1024;          // + slack to align the base to 1024
+};
+
+// NMAT = 2: gate and up over one input tile, SiLU epilogue. NMAT = 1: down, scatter-add epilogue.
+template <int NMAT>
+__global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap, const GemmArgs a)
+{
+    using L = PfSmem<NMAT>;
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t sbase = (raw + 1023u) & ~1023u;
+    unsigned char* smem = smem_raw + (sbase - raw);
+    const uint32_t full_a = sbase + L::bars, full_b = full_a + L::STAGES * 8, empty = full_b + L::STAGES * 8,
+                   done = empty + L::STAGES * 8, tmem_free = done + 8;
+    uint32_t* tmem_slot = (uint32_t*) (smem + L::misc);
+    volatile int* abort_flag = (volatile int*) (smem + L::misc + 8);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int TMEM_COLS = NMAT == 2 ? 512 : 256;
+
+    if (threadIdx.x == 0)
+    {
+        for (int i = 0; i < L::STAGES; ++i) { mbar_init(full_a + i * 8, 8); mbar_init(full_b + i * 8, 1); mbar_init(empty + i * 8, 1); }
+        mbar_init(done, 1); mbar_init(tmem_free, 8);
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 9)
+    {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    const int KB = a.K / 64, NCT = a.N / TM;
+    const int nitems = a.plan->nrb * NCT;
+    uint32_t it = 0;                               // stage counter of this thread's role
+    uint32_t tile_n = 0;                           // tiles done (phase of done / tmem_free)
+
+    for (int item = blockIdx.x; item < nitems; item += gridDim.x, ++tile_n)
+    {
+        if (*abort_flag) break;
+        const int rb = item / NCT, ct = item % NCT;
+        const int e = a.rbt[4 * rb], pos0 = a.rbt[4 * rb + 1], n = a.rbt[4 * rb + 2];
+        const uint32_t n16 = (uint32_t) ((n + 15) & ~15);
+        if (warp < 8)
+        {
+            // ---- dequantise: this warp's strips of every stage
+            const int g = lane >> 2, q = lane & 3;
+            int mat, u0, strip, nsb;                                   // nsb strip-blocks per stage for this warp
+            if (NMAT == 2) { mat = warp >> 2; strip = warp & 3; u0 = 0; nsb = 2; }
+            else { mat = 0; strip = warp & 3; u0 = warp >> 2; nsb = 1; }
+            const void* wp = e < a.n_local ? (const void*) (mat ? a.w1[e] : a.w0[e]) : (mat ? a.sh_w1 : a.sh_w0);
+            const void* sp = e < a.n_local ? (const void*) (mat ? a.s1[e] : a.s0[e]) : (mat ? a.sh_s1 : a.sh_s0);
+            // 64-row groups 2 ct and 2 ct + 1 of the matrix; strip-block b of this warp is unit u0 + b
+            const char* wbase = (const char*) wp + ((size_t) (2 * ct + u0) * KB * 4 + strip) * 512 + lane * 16;
+            const size_t unit_stride = (size_t) KB * 2048;
+            const char* sbase_p = (const char*) sp + ((size_t) (2 * ct + u0) * (a.K / 128) * 64 + g * 8 + 2 * strip) * 2;
+            const size_t sunit_stride = (size_t) (a.K / 128) * 128;
+            uint4 wq[2];
+            #pragma unroll
+            for (int b = 0; b < 2; ++b) if (b < nsb) wq[b] = ldg128_nc(wbase + b * unit_stride);
+            bool ok = true;
+            for (int kb = 0; kb < KB; ++kb, ++it)
+            {
+                const uint32_t s = it % L::STAGES;
+                uint4 wc[2] = {wq[0], wq[1]};
+                uint32_t sc[2] = {0, 0};
+                if (a.grouped)
+                {
+                    #pragma unroll
+                    for (int b = 0; b < 2; ++b) if (b < nsb) sc[b] = __ldg((const uint32_t*) (sbase_p + b * sunit_stride + (size_t) (kb >> 1) * 128));
+                }
+                if (kb + 1 < KB)
+                {
+                    #pragma unroll
+                    for (int b = 0; b < 2; ++b) if (b < nsb) wq[b] = ldg128_nc(wbase + b * unit_stride + (size_t) (kb + 1) * 2048);
+                }
+                if (it >= (uint32_t) L::STAGES && !mbar_wait(empty + s * 8, ((it / L::STAGES) - 1) & 1, abort_flag, a.status)) { ok = false; break; }
+                const uint32_t tile = sbase + s * L::STAGE + mat * L::A_BYTES;
+                #pragma unroll
+                for (int b = 0; b < 2; ++b)
+                    if (b < nsb)
+                    {
+                        uint32_t s_lo = 0, s_hi = 0;
+                        if (a.grouped) scale_pair(sc[b], s_lo, s_hi);
+                        store_strip(tile, (u0 + b) * 8 + strip * 2, g, q, wc[b], s_lo, s_hi, a.grouped != 0);
+                    }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full_a + s * 8);
+            }
+            // ---- epilogue: warp w reads tensor-memory lanes 32 (w % 4) .. + 31 (channels), columns 128 (w / 4) .. + 127 (picks)
+            if (ok && mbar_wait(done, tile_n & 1, abort_flag, a.status))
+            {
+                tc_fence_after();
+                const int lq = warp & 3, chalf = warp >> 2;
+                const int ch = ct * TM + lq * 32 + lane;
+                float sc0 = 1.f, sc1 = 1.f;
+                if (!a.grouped)
+                {
+                    const void* s0p = e < a.n_local ? (const void*) a.s0[e] : a.sh_s0;
+                    sc0 = __ldg((const float*) s0p + ch);
+                    if (NMAT == 2) { const void* s1p = e < a.n_local ? (const void*) a.s1[e] : a.sh_s1; sc1 = __ldg((const float*) s1p + ch); }
+                }
+                for (int c0 = chalf * 128; c0 < chalf * 128 + 128 && c0 < (int) n16; c0 += 32)
+                {
+                    uint32_t r0[32], r1[32];
+                    tmem_ld32(tmem + ((uint32_t) (lq * 32) << 16) + c0, r0);
+                    if (NMAT == 2) tmem_ld32(tmem + ((uint32_t) (lq * 32) << 16) + 256 + c0, r1);
+                    tmem_ld_wait();
+                    if (NMAT == 2)
+                    {
+                        #pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                        {
+                            const int p = c0 + j;
+                            if (p < n)
+                            {
+                                const float gg = __uint_as_float(r0[j]) * sc0, uu = __uint_as_float(r1[j]) * sc1;
+                                float v = gg / (1.f + expf(-gg)) * uu * a.wt[pos0 + p];
+                                if (a.act_quant)
+                                {
+                                    // second int8 round trip of the CPU engine: 32 consecutive channels = this warp
+                                    float m = fabsf(v);
+                                    #pragma unroll
+                                    for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+                                    const float s = m > 0.f ? __fdiv_rn(m, 127.f) : 1.f;
+                                    v = __fmul_rn((float) __float2int_rn(__fmul_rn(v, __fdiv_rn(1.f, s))), s);
+                                }
+                                a.act[(size_t) (pos0 + p) * a.N + ch] = __float2half_rn(v);
+                            }
+                        }
+                    }
+                    else
+                    {
+                        #pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                        {
+                            const int p = c0 + j;
+                            if (p < n) atomicAdd(a.out + (size_t) a.tok[pos0 + p] * a.N + ch, __uint_as_float(r0[j]) * sc0);
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tmem_free);
+            }
+        }
+        else if (warp == 8)
+        {
+            if (lane == 0)
+                for (int kb = 0; kb < KB; ++kb, ++it)
+                {
+                    const uint32_t s = it % L::STAGES;
+                    if (it >= (uint32_t) L::STAGES && !mbar_wait(empty + s * 8, ((it / L::STAGES) - 1) & 1, abort_flag, a.status)) break;
+                    mbar_expect_tx(full_b + s * 8, L::B_BYTES);
+                    tma_load_2d(sbase + s * L::STAGE + NMAT * L::A_BYTES, &tmap, kb * 64, pos0, full_b + s * 8);
+                }
+        }
+        else
+        {
+            if (lane == 0)
+            {
+                const uint32_t idesc = (1u << 4) | ((n16 >> 3) << 17) | ((uint32_t) (TM >> 4) << 24);
+                bool ok = tile_n == 0 || mbar_wait(tmem_free, (tile_n - 1) & 1, abort_flag, a.status);
+                if (ok) tc_fence_after();
+                for (int kb = 0; kb < KB && ok; ++kb, ++it)
+                {
+                    const uint32_t s = it % L::STAGES, ph = (it / L::STAGES) & 1;
+                    if (!mbar_wait(full_a + s * 8, ph, abort_flag, a.status) || !mbar_wait(full_b + s * 8, ph, abort_flag, a.status)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t at = sbase + s * L::STAGE, bt = at + NMAT * L::A_BYTES;
+                    #pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                    {
+                        const uint64_t bd = smem_desc_sw128(bt + k * 32);
+                        mma_f16_ss(tmem, smem_desc_sw128(at + k * 32), bd, idesc, (kb | k) != 0);
+                        if (NMAT == 2) mma_f16_ss(tmem + 256, smem_desc_sw128(at + L::A_BYTES + k * 32), bd, idesc, (kb | k) != 0);
+                    }
+                    tc_commit(empty + s * 8);
+                }
+                if (ok) tc_commit(done);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 9)
+    {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+typedef CUresult (*encode_fn_t)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+encode_fn_t encode_fn()
+{
+    static encode_fn_t f = nullptr;
+    if (!f)
+    {
+        void* p = nullptr; cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess) f = (encode_fn_t) p;
+    }
+    return f;
+}
+
+// row-major fp16 [rows][K] in tiles of 64 columns x 256 rows, 128-byte swizzle
+bool make_map(CUtensorMap* m, const void* ptr, int K, size_t rows)
+{
+    encode_fn_t f = encode_fn();
+    if (!f) return false;
+    cuuint64_t dims[2] = {(cuuint64_t) K, (cuuint64_t) rows};
+    cuuint64_t strides[1] = {(cuuint64_t) K * 2};
+    cuuint32_t box[2] = {TK, TN}, es[2] = {1, 1};
+    return f(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*) ptr, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+size_t up256(size_t b) { return (b + 255) / 256 * 256; }
+
+struct WsLayout
+{
+    size_t status, plan, counts, offs, hist, order, tok, eid, wt, rbt, xg, act, total;
+    int nblocks, rows_cap, maxrb;
+};
+
+WsLayout ws_layout(int R, int topk, int n_local, int H, int I, int bm)
+{
+    WsLayout w;
+    const size_t P = (size_t) R * topk;
+    w.nblocks = (int) ((P + CHUNK - 1) / CHUNK);
+    w.rows_cap = (int) (P + R);
+    w.maxrb = (int) ((P + R) / bm + n_local + 2);
+    size_t o = 0;
+    w.status = o; o += 256;
+    w.plan = o; o += 256;
+    w.counts = o; o += up256((size_t) (n_local + 2) * 4);
+    w.offs = o; o += up256((size_t) (n_local + 3) * 4);
+    w.hist = o; o += up256((size_t) w.nblocks * (n_local > 0 ? n_local : 1) * 4);
+    w.order = o; o += up256((size_t) w.rows_cap * 4);
+    w.tok = o; o += up256((size_t) w.rows_cap * 4);
+    w.eid = o; o += up256((size_t) w.rows_cap * 4);
+    w.wt = o; o += up256((size_t) w.rows_cap * 4);
+    w.rbt = o; o += up256((size_t) w.maxrb * 16);
+    w.xg = o; o += up256((size_t) w.rows_cap * H * 2);
+    w.act = o; o += up256((size_t) w.rows_cap * I * 2);
+    w.total = o;
+    return w;
+}
+
+int run_permute(const int64_t* sel, const void* rw, int R, int topk, int lo, int n_local, int shared_rows, int bm, int balance,
+                int* counts, int* offs, int* hist, int nblocks, int* order, int* tok, int* eid, float* wt, int* rbt, Plan* plan, cudaStream_t st)
+{
+    const int P = R * topk;
+    permute_hist_kernel<<<nblocks, 32, 0, st>>>(sel, P, lo, n_local, hist);
+    permute_scan_kernel<<<1, 256, 0, st>>>(hist, nblocks, n_local, shared_rows, bm, balance, counts, offs, rbt, plan);
+    const int sb = shared_rows > 0 ? (shared_rows + CHUNK - 1) / CHUNK : 0;
+    permute_scatter_kernel<<<nblocks + sb, 32, 0, st>>>(sel, (const __half*) rw, P, topk, lo, n_local, shared_rows, hist, offs, nblocks, order, tok, eid, wt);
+    count_launches(3);
+    return cudaGetLastError() == cudaSuccess ? HMOE_OK : fail(HMOE_E_CUDA, "hmoe_permute: launch failed");
+}
+
+}  // namespace
+
+size_t prefill_ws_bytes(int R, int topk, int n_local, int H, int I) { return ws_layout(R, topk, n_local, H, I, TN).total; }
+
+int permute_launch(const int64_t* sel, const void* rw, int R, int topk, int lo, int n_local, int shared_rows, int bm, int balance,
+                   int32_t* order, int32_t* tok, int32_t* eid, float* wt, int32_t* counts, int32_t* rbt, int32_t* plan2, void* ws, size_t ws_bytes,
+                   cudaStream_t st)
+{
+    if (R < 1 || topk < 1 || n_local < 1 || n_local > 256 || bm < 1) return fail(HMOE_E_ARG, "hmoe_permute: needs R >= 1, 1 <= n_local <= 256, bm >= 1");
+    if (!sel || !rw || !tok || !eid || !wt || !counts || !rbt || !plan2 || !ws) return fail(HMOE_E_ARG, "hmoe_permute: null pointer");
+    const size_t P = (size_t) R * topk;
+    const int nblocks = (int) ((P + CHUNK - 1) / CHUNK);
+    const size_t need = up256((size_t) nblocks * n_local * 4) + up256((size_t) (n_local + 3) * 4);
+    if (ws_bytes < need) return fail(HMOE_E_WS, "hmoe_permute: workspace too small");
+    int* hist = (int*) ws;
+    int* offs = (int*) ((char*) ws + up256((size_t) nblocks * n_local * 4));
+    return run_permute(sel, rw, R, topk, lo, n_local, shared_rows, bm, balance, counts, offs, hist, nblocks, order, tok, eid, wt, rbt, (Plan*) plan2, st);
+}
+
+size_t permute_ws_bytes(int R, int topk, int n_local)
+{
+    const size_t P = (size_t) R * topk;
+    const int nblocks = (int) ((P + CHUNK - 1) / CHUNK);
+    return up256((size_t) nblocks * n_local * 4) + up256((size_t) (n_local + 3) * 4);
+}
+
+int prefill_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
+                   int act_quant, float* out, void* ws, size_t ws_bytes, cudaStream_t st)
+{
+    const int H = L->H, I = L->I;
+    if (R < 1) return fail(HMOE_E_ARG, "hmoe_prefill: rows must be >= 1");
+    if (L->topk < 1 || L->topk > TOPK_MAX) return fail(HMOE_E_ARG, "hmoe_prefill: topk must be 1..8");
+    if (H % 128 || I % 128 || H < 128 || I < 128) return fail(HMOE_E_ARG, "hmoe_prefill: H and I must be multiples of 128");
+    if (n_local < 1 || n_local > 256) return fail(HMOE_E_ARG, "hmoe_prefill: 1..256 local experts");
+    if (!(L->group == 0 && L->scale_dtype == HMOE_F32) && !(L->group == 128 && L->scale_dtype == HMOE_BF16))
+        return fail(HMOE_E_ARG, "hmoe_prefill: scales must be fp32 per row (group 0) or bf16 per 128 columns");
+    if (x_dtype != HMOE_F16 && x_dtype != HMOE_BF16) return fail(HMOE_E_ARG, "hmoe_prefill: x must be fp16 or bf16");
+    if (!x || !sel || !rw || !out || !ws) return fail(HMOE_E_ARG, "hmoe_prefill: null pointer");
+    const WsLayout w = ws_layout(R, L->topk, n_local, H, I, TN);
+    if (ws_bytes < w.total) return fail(HMOE_E_WS, "hmoe_prefill: workspace too small");
+    static int sms = 0;
+    static bool attr = false;
+    if (!attr)
+    {
+        int dev = 0; cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        cudaFuncSetAttribute(prefill_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfSmem<2>::total);
+        cudaFuncSetAttribute(prefill_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfSmem<1>::total);
+        attr = true;
+    }
+    char* b = (char*) ws;
+    unsigned* status = (unsigned*) (b + w.status);
+    Plan* plan = (Plan*) (b + w.plan);
+    int* counts = (int*) (b + w.counts); int* offs = (int*) (b + w.offs); int* hist = (int*) (b + w.hist);
+    int* order = (int*) (b + w.order); int* tok = (int*) (b + w.tok); int* eid = (int*) (b + w.eid); float* wt = (float*) (b + w.wt);
+    int* rbt = (int*) (b + w.rbt);
+    __half* xg = (__half*) (b + w.xg); __half* act = (__half*) (b + w.act);
+    const int has_shared = L->sh_gate_w != nullptr;
+    int rc = run_permute(sel, rw, R, L->topk, lo, n_local, has_shared ? R : 0, TN, 1, counts, offs, hist, w.nblocks, order, tok, eid, wt, rbt, plan, st);
+    if (rc) return rc;
+    gather_kernel<<<w.rows_cap, 192, 0, st>>>(x, x_dtype == HMOE_BF16, tok, plan, H, act_quant, xg);
+    CUtensorMap mx, ma;
+    if (!make_map(&mx, xg, H, (size_t) w.rows_cap) || !make_map(&ma, act, I, (size_t) w.rows_cap)) return fail(HMOE_E_CUDA, "hmoe_prefill: cuTensorMapEncodeTiled failed");
+    GemmArgs g;
+    g.grouped = L->group != 0; g.act_quant = act_quant; g.n_local = n_local;
+    g.plan = plan; g.rbt = rbt; g.tok = tok; g.wt = wt; g.act = act; g.out = out; g.status = status;
+    g.K = H; g.N = I; g.w0 = L->gate_w; g.w1 = L->up_w; g.s0 = L->gate_s; g.s1 = L->up_s;
+    g.sh_w0 = L->sh_gate_w; g.sh_w1 = L->sh_up_w; g.sh_s0 = L->sh_gate_s; g.sh_s1 = L->sh_up_s;
+    prefill_gemm_kernel<2><<<sms, PF_THREADS, PfSmem<2>::total, st>>>(mx, g);
+    g.K = I; g.N = H; g.w0 = L->down_w; g.w1 = nullptr; g.s0 = L->down_s; g.s1 = nullptr;
+    g.sh_w0 = L->sh_down_w; g.sh_w1 = nullptr; g.sh_s0 = L->sh_down_s; g.sh_s1 = nullptr;
+    prefill_gemm_kernel<1><<<sms, PF_THREADS, PfSmem<1>::total, st>>>(ma, g);
+    count_launches(3);
+    const cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) return fail(HMOE_E_CUDA, cudaGetErrorString(err));
+    return HMOE_OK;
+}
+
+}  // namespace hmoe

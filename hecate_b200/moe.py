@@ -86,6 +86,46 @@ def decode(tables, x, sel, rw, y, ws, lo=0, n_local=None, act_quant=False):
     return y
 
 
+def prefill_workspace(R, topk, n_local, H, I, device):
+    n = lib().hmoe_prefill_ws_bytes(C.c_int(R), C.c_int(topk), C.c_int(n_local), C.c_int(H), C.c_int(I))
+    return torch.zeros(n, dtype=torch.uint8, device=device)
+
+
+def prefill(tables, x, sel, rw, out, ws, lo=0, n_local=None, act_quant=False):
+    """out[R][H] (fp32) += experts(x) for any number of rows: permutation on the device, then the two grouped tcgen05 GEMMs
+    (the counterpart of tier_split._prefill_gb300 + moe4t.forward, tier_split.py:427-462, moe4t.cu:498-524)."""
+    R = x.shape[0]
+    if not (x.is_contiguous() and sel.is_contiguous() and rw.is_contiguous() and out.is_contiguous()):
+        raise HmoeError("prefill: tensors must be contiguous")
+    if sel.dtype != torch.int64 or rw.dtype != torch.float16 or out.dtype != torch.float32:
+        raise HmoeError("prefill: sel int64, rw fp16, out fp32 required")
+    st = tables.struct()
+    check(lib().hmoe_prefill(C.byref(st), vp(x), C.c_int(_dt(x)), vp(sel), vp(rw), C.c_int(R), C.c_int(lo),
+                             C.c_int(tables.n if n_local is None else n_local), C.c_int(int(act_quant)), vp(out), vp(ws),
+                             C.c_size_t(ws.numel()), _stream(x.device)))
+    return out
+
+
+def permute(sel, rw, n_local, lo=0, shared_rows=0, bm=256, balance=True):
+    """Device permutation of the picks (stable sort by expert id) and the row-block table. Returns a dict of tensors:
+    order, tok, eid, wt, counts, rbt (first `nrb` rows valid), total, nrb."""
+    R, topk = sel.shape
+    dev = sel.device
+    cap = R * topk + shared_rows
+    maxrb = cap // bm + n_local + 2
+    i32 = lambda n: torch.zeros(n, dtype=torch.int32, device=dev)
+    order, tok, eid, wt = i32(cap), i32(cap), i32(cap), torch.zeros(cap, dtype=torch.float32, device=dev)
+    counts, rbt, plan = i32(n_local + 1), i32(maxrb * 4), i32(4)
+    nb = lib().hmoe_permute_ws_bytes(C.c_int(R), C.c_int(topk), C.c_int(n_local))
+    ws = torch.zeros(nb, dtype=torch.uint8, device=dev)
+    check(lib().hmoe_permute(vp(sel), vp(rw), C.c_int(R), C.c_int(topk), C.c_int(lo), C.c_int(n_local), C.c_int(shared_rows),
+                             C.c_int(bm), C.c_int(int(balance)), vp(order), vp(tok), vp(eid), vp(wt), vp(counts), vp(rbt), vp(plan), vp(ws),
+                             C.c_size_t(nb), _stream(dev)))
+    total, nrb = (int(v) for v in plan[:2].cpu())
+    return dict(order=order[:total], tok=tok[:total], eid=eid[:total], wt=wt[:total], counts=counts, rbt=rbt.view(-1, 4)[:nrb],
+                total=total, nrb=nrb)
+
+
 def set_profiling(on):
     check(lib().hmoe_set_profiling(C.c_int(int(on))))
 

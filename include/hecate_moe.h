@@ -63,6 +63,30 @@ size_t hmoe_decode_ws_bytes(int H, int I);
 int hmoe_decode(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
                 int act_quant, float* y, void* ws, size_t ws_bytes, void* stream);
 
+/* Prefill permutation on the device: replaces the host-side code of runtime/tier/tier_split.py:404-412,433-455 (stable argsort
+ * of the flattened selection by expert id, bincount with a host sync) and pick_groups (runtime/tier/rtx_split.py:236-255, one
+ * pick group) with three kernels and no synchronisation. Picks with ids outside [lo, lo + n_local) are dropped.
+ * Outputs (device, caller-owned): order int32 [R*topk] (flat pick index, may be null), tok int32 [R*topk + shared_rows]
+ * (= order / topk), eid int32 (local expert id; n_local for the shared expert's rows), wt fp32, counts int32 [n_local + 1],
+ * rbt int32 [maxrb][4] = {expert, first pick, picks <= bm, 0} with maxrb >= (R*topk + shared_rows) / bm + n_local + 2,
+ * plan int32 [4] = {picks kept + shared rows, row blocks, 0, 0}. shared_rows > 0 appends a segment "every row once, weight 1"
+ * as expert n_local. balance != 0: an expert's blocks get near-equal sizes. ws: hmoe_permute_ws_bytes bytes. */
+size_t hmoe_permute_ws_bytes(int R, int topk, int n_local);
+int hmoe_permute(const int64_t* sel, const void* rw, int R, int topk, int lo, int n_local, int shared_rows, int bm, int balance,
+                 int32_t* order, int32_t* tok, int32_t* eid, float* wt, int32_t* counts, int32_t* rbt, int32_t* plan, void* ws, size_t ws_bytes,
+                 void* stream);
+
+/* Prefill expert layer: replaces moe4t.forward / moe4p.forward(x, tok, eid, wt, rbt, gw, uw, dw, gs, us, ds, gu, ar, d, out)
+ * (runtime/tier/moe4/moe4t.cu:498-524, moe4p.cu:220-245) together with the permutation above, for any number of rows:
+ * permute -> gather -> grouped gate+up GEMM with SiLU * up * weight epilogue -> grouped down GEMM whose epilogue adds
+ * scale * sum into out[token] (fp32 [R][H], added into: zero it first for a plain result). tcgen05 tensor cores, fp16
+ * operands, fp32 accumulation. act_quant = 1 rounds activations through the CPU engine's int8 format (values, not exact
+ * integer arithmetic: see DESIGN.md). Other arguments as hmoe_decode. ws: hmoe_prefill_ws_bytes bytes (holds the gathered
+ * inputs and the intermediate activations: (R*topk + R) * (H + I) * 2 bytes plus small tables). */
+size_t hmoe_prefill_ws_bytes(int R, int topk, int n_local, int H, int I);
+int hmoe_prefill(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
+                 int act_quant, float* out, void* ws, size_t ws_bytes, void* stream);
+
 /* hmoe_decode without a workspace argument, for callers that cannot allocate device memory: embedders whose device memory
  * is one arena planned at start-up, plugins that must stay inside a host framework's allocator, latency-critical loops
  * where an allocation would stall the process. It has no counterpart in the reference (whose scratch always comes from
