@@ -10,12 +10,12 @@
 //
 // GEMM orientation: D[channel][pick] = W[channel][k] . X[pick][k]: the weights are the M = 128 operand, the picks of one
 // row block (<= 256, one expert) the N operand, fp32 accumulators in tensor memory. Per 64-column stage:
-//   warps 0-7  read the packed codes of the tile straight from global memory (16 bytes per lane, the stored fragment order),
+//   warps 0-15 read the packed codes of the tile straight from global memory (16 bytes per lane, the stored fragment order),
 //              turn them into fp16 (times the bf16 group scale in the group format) and store them as a K-major,
 //              128-byte-swizzled operand tile (4-byte stores, conflict free);
-//   warp 8     one thread loads the row block's 256 x 64 input tile with one 2-D TMA copy (128-byte swizzle, rows beyond the
+//   warp 16    one thread loads the row block's 256 x 64 input tile with one 2-D TMA copy (128-byte swizzle, rows beyond the
 //              array zero-filled);
-//   warp 9     one thread issues tcgen05.mma (M 128, N = picks rounded up to 16, K 16) four times per matrix and commits the
+//   warp 17    one thread issues tcgen05.mma (M 128, N = picks rounded up to 16, K 16) four times per matrix and commits the
 //              stage back to the producers.
 // gate_up keeps two accumulators (gate, up: 2 x 256 columns) over the same input tile and its epilogue writes
 // act = SiLU(g) * u * routing weight in fp16; down adds scale * sum into out[token] with coalesced fp32 reductions.
@@ -30,7 +30,8 @@ namespace hmoe {
 namespace {
 
 constexpr int TM = 128, TN = 256, TK = 64;
-constexpr int PF_THREADS = 320;                 // warps 0-7 dequantise / epilogue, 8 TMA, 9 MMA
+constexpr int NDQ = 16;                         // dequantise / epilogue warps
+constexpr int PF_THREADS = (NDQ + 2) * 32;      // + warp NDQ: TMA, warp NDQ + 1: MMA
 constexpr int CHUNK = 1024;                     // picks per permutation block (one warp)
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -296,12 +297,12 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
 
     if (threadIdx.x == 0)
     {
-        for (int i = 0; i < L::STAGES; ++i) { mbar_init(full_a + i * 8, 8); mbar_init(full_b + i * 8, 1); mbar_init(empty + i * 8, 1); }
-        mbar_init(done, 1); mbar_init(tmem_free, 8);
+        for (int i = 0; i < L::STAGES; ++i) { mbar_init(full_a + i * 8, NMAT == 2 ? NDQ : NDQ / 2); mbar_init(full_b + i * 8, 1); mbar_init(empty + i * 8, 1); }
+        mbar_init(done, 1); mbar_init(tmem_free, NDQ);
         *abort_flag = 0;
         fence_barrier_init();
     }
-    if (warp == 9)
+    if (warp == NDQ + 1)
     {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -313,7 +314,6 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
 
     const int KB = a.K / 64, NCT = a.N / TM;
     const int nitems = a.plan->nrb * NCT;
-    uint32_t it = 0;                               // stage counter of this thread's role
     uint32_t tile_n = 0;                           // tiles done (phase of done / tmem_free)
 
     for (int item = blockIdx.x; item < nitems; item += gridDim.x, ++tile_n)
@@ -322,58 +322,44 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
         const int rb = item / NCT, ct = item % NCT;
         const int e = a.rbt[4 * rb], pos0 = a.rbt[4 * rb + 1], n = a.rbt[4 * rb + 2];
         const uint32_t n16 = (uint32_t) ((n + 15) & ~15);
-        if (warp < 8)
+        if (warp < NDQ)
         {
-            // ---- dequantise: this warp's strips of every stage
+            // ---- dequantise: one 16-row strip of one 64-row unit per warp and stage. gate_up: 2 matrices x 2 units x 4 strips =
+            // 16 strip-blocks per stage, one per warp. down: 8 strip-blocks per stage; warps 0-7 take the even stages, warps
+            // 8-15 the odd ones. The packed words are fetched two stages ahead.
             const int g = lane >> 2, q = lane & 3;
-            int mat, u0, strip, nsb;                                   // nsb strip-blocks per stage for this warp
-            if (NMAT == 2) { mat = warp >> 2; strip = warp & 3; u0 = 0; nsb = 2; }
-            else { mat = 0; strip = warp & 3; u0 = warp >> 2; nsb = 1; }
+            const int strip = warp & 3, unit = (warp >> 2) & 1, mat = NMAT == 2 ? warp >> 3 : 0;
+            const int kb0 = NMAT == 2 ? 0 : warp >> 3, kstep = NMAT == 2 ? 1 : 2;
             const void* wp = e < a.n_local ? (const void*) (mat ? a.w1[e] : a.w0[e]) : (mat ? a.sh_w1 : a.sh_w0);
             const void* sp = e < a.n_local ? (const void*) (mat ? a.s1[e] : a.s0[e]) : (mat ? a.sh_s1 : a.sh_s0);
-            // 64-row groups 2 ct and 2 ct + 1 of the matrix; strip-block b of this warp is unit u0 + b
-            const char* wbase = (const char*) wp + ((size_t) (2 * ct + u0) * KB * 4 + strip) * 512 + lane * 16;
-            const size_t unit_stride = (size_t) KB * 2048;
-            const char* sbase_p = (const char*) sp + ((size_t) (2 * ct + u0) * (a.K / 128) * 64 + g * 8 + 2 * strip) * 2;
-            const size_t sunit_stride = (size_t) (a.K / 128) * 128;
-            uint4 wq[2];
-            #pragma unroll
-            for (int b = 0; b < 2; ++b) if (b < nsb) wq[b] = ldg128_nc(wbase + b * unit_stride);
+            const char* wbase = (const char*) wp + ((size_t) (2 * ct + unit) * KB * 4 + strip) * 512 + lane * 16;
+            const char* sbase_p = (const char*) sp + ((size_t) (2 * ct + unit) * (a.K / 128) * 64 + g * 8 + 2 * strip) * 2;
+            uint4 w0 = make_uint4(0, 0, 0, 0), w1 = w0;
+            if (kb0 < KB) w0 = ldg128_nc(wbase + (size_t) kb0 * 2048);
+            if (kb0 + kstep < KB) w1 = ldg128_nc(wbase + (size_t) (kb0 + kstep) * 2048);
+            const uint32_t it0 = tile_n * (uint32_t) KB;
             bool ok = true;
-            for (int kb = 0; kb < KB; ++kb, ++it)
+            for (int kb = kb0; kb < KB; kb += kstep)
             {
-                const uint32_t s = it % L::STAGES;
-                uint4 wc[2] = {wq[0], wq[1]};
-                uint32_t sc[2] = {0, 0};
-                if (a.grouped)
-                {
-                    #pragma unroll
-                    for (int b = 0; b < 2; ++b) if (b < nsb) sc[b] = __ldg((const uint32_t*) (sbase_p + b * sunit_stride + (size_t) (kb >> 1) * 128));
-                }
-                if (kb + 1 < KB)
-                {
-                    #pragma unroll
-                    for (int b = 0; b < 2; ++b) if (b < nsb) wq[b] = ldg128_nc(wbase + b * unit_stride + (size_t) (kb + 1) * 2048);
-                }
-                if (it >= (uint32_t) L::STAGES && !mbar_wait(empty + s * 8, ((it / L::STAGES) - 1) & 1, abort_flag, a.status)) { ok = false; break; }
-                const uint32_t tile = sbase + s * L::STAGE + mat * L::A_BYTES;
-                #pragma unroll
-                for (int b = 0; b < 2; ++b)
-                    if (b < nsb)
-                    {
-                        uint32_t s_lo = 0, s_hi = 0;
-                        if (a.grouped) scale_pair(sc[b], s_lo, s_hi);
-                        store_strip(tile, (u0 + b) * 8 + strip * 2, g, q, wc[b], s_lo, s_hi, a.grouped != 0);
-                    }
+                const uint32_t gi = it0 + kb, s = gi % L::STAGES;
+                const uint4 wc = w0;
+                w0 = w1;
+                if (kb + 2 * kstep < KB) w1 = ldg128_nc(wbase + (size_t) (kb + 2 * kstep) * 2048);
+                uint32_t sc = 0;
+                if (a.grouped) sc = __ldg((const uint32_t*) (sbase_p + (size_t) (kb >> 1) * 128));
+                if (gi >= (uint32_t) L::STAGES && !mbar_wait(empty + s * 8, ((gi / L::STAGES) - 1) & 1, abort_flag, a.status)) { ok = false; break; }
+                uint32_t s_lo = 0, s_hi = 0;
+                if (a.grouped) scale_pair(sc, s_lo, s_hi);
+                store_strip(sbase + s * L::STAGE + mat * L::A_BYTES, unit * 8 + strip * 2, g, q, wc, s_lo, s_hi, a.grouped != 0);
                 fence_proxy_async();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(full_a + s * 8);
             }
-            // ---- epilogue: warp w reads tensor-memory lanes 32 (w % 4) .. + 31 (channels), columns 128 (w / 4) .. + 127 (picks)
+            // ---- epilogue: warp w reads tensor-memory lanes 32 (w % 4) .. + 31 (channels), columns 64 (w / 4) .. + 63 (picks)
             if (ok && mbar_wait(done, tile_n & 1, abort_flag, a.status))
             {
                 tc_fence_after();
-                const int lq = warp & 3, chalf = warp >> 2;
+                const int lq = warp & 3, cq = warp >> 2;
                 const int ch = ct * TM + lq * 32 + lane;
                 float sc0 = 1.f, sc1 = 1.f;
                 if (!a.grouped)
@@ -382,7 +368,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
                     sc0 = __ldg((const float*) s0p + ch);
                     if (NMAT == 2) { const void* s1p = e < a.n_local ? (const void*) a.s1[e] : a.sh_s1; sc1 = __ldg((const float*) s1p + ch); }
                 }
-                for (int c0 = chalf * 128; c0 < chalf * 128 + 128 && c0 < (int) n16; c0 += 32)
+                for (int c0 = cq * 64; c0 < cq * 64 + 64 && c0 < (int) n16; c0 += 32)
                 {
                     uint32_t r0[32], r1[32];
                     tmem_ld32(tmem + ((uint32_t) (lq * 32) << 16) + c0, r0);
@@ -426,12 +412,12 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
                 if (lane == 0) mbar_arrive(tmem_free);
             }
         }
-        else if (warp == 8)
+        else if (warp == NDQ)
         {
             if (lane == 0)
-                for (int kb = 0; kb < KB; ++kb, ++it)
+                for (int kb = 0; kb < KB; ++kb)
                 {
-                    const uint32_t s = it % L::STAGES;
+                    const uint32_t it = tile_n * (uint32_t) KB + kb, s = it % L::STAGES;
                     if (it >= (uint32_t) L::STAGES && !mbar_wait(empty + s * 8, ((it / L::STAGES) - 1) & 1, abort_flag, a.status)) break;
                     mbar_expect_tx(full_b + s * 8, L::B_BYTES);
                     tma_load_2d(sbase + s * L::STAGE + NMAT * L::A_BYTES, &tmap, kb * 64, pos0, full_b + s * 8);
@@ -444,9 +430,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
                 const uint32_t idesc = (1u << 4) | ((n16 >> 3) << 17) | ((uint32_t) (TM >> 4) << 24);
                 bool ok = tile_n == 0 || mbar_wait(tmem_free, (tile_n - 1) & 1, abort_flag, a.status);
                 if (ok) tc_fence_after();
-                for (int kb = 0; kb < KB && ok; ++kb, ++it)
+                for (int kb = 0; kb < KB && ok; ++kb)
                 {
-                    const uint32_t s = it % L::STAGES, ph = (it / L::STAGES) & 1;
+                    const uint32_t it = tile_n * (uint32_t) KB + kb, s = it % L::STAGES, ph = (it / L::STAGES) & 1;
                     if (!mbar_wait(full_a + s * 8, ph, abort_flag, a.status) || !mbar_wait(full_b + s * 8, ph, abort_flag, a.status)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t at = sbase + s * L::STAGE, bt = at + NMAT * L::A_BYTES;
@@ -465,7 +451,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 9)
+    if (warp == NDQ + 1)
     {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
