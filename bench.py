@@ -150,7 +150,7 @@ def run_reference(args):
     steps = max(1, min(args.steps, 50))
     cb = cpu_reference_arm(steps, max(1, min(args.warmup, 5)))
     line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
-            "warmup": args.warmup, "ms_per_step": cb["ms_per_job"], "higher_is_better": True, "scaling": "weak",
+            "warmup": args.warmup, "ms_per_step": cb["ms_per_job"], "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "int4 x int8 -> fp32", "data": "synthetic",
             "config": {"workload": WORKLOAD + " [CPU sample: one 8-row job per step]"},
             "cpu_baseline": cb, "e2e": {"value": cb["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
@@ -264,7 +264,7 @@ def run_ours(args):
     cb = cpu_reference_arm(20, 3) if not args.no_cpu else None
     line = {
         "metric": METRIC, "value": ROWS / (ms_per_step * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": steps, "warmup": warmup,
-        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int4 x fp16 -> fp32",
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int4 x fp16 -> fp32",
         "data": "synthetic",
         "config": {"workload": WORKLOAD if E == 256 else WORKLOAD + f" [reduced to {E} experts]", "l2": "inputs larger than L2: ~2 GB of weights streamed per step, 8 input batches in a ring",
                    "distinct_experts_per_step": mean_d},

@@ -120,6 +120,13 @@ int hmoe_permute(const int64_t* sel, const void* rw, int R, int topk, int lo, in
 int hmoe_set_profiling(int on) { return decode_set_profiling(on); }
 int hmoe_decode_phase_times(float* ms3) { return ms3 ? decode_phase_times(ms3) : fail(HMOE_E_ARG, "hmoe_decode_phase_times: null pointer"); }
 
+int hmoe_decode_ep(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
+                   int act_quant, float* y, void* ws, size_t ws_bytes, int shared_mod, int shared_rem, void* stream)
+{
+    if (!layer) return fail(HMOE_E_ARG, "hmoe_decode_ep: null layer");
+    return decode_launch(layer, x, x_dtype, sel, rw, R, lo, n_local, act_quant, y, ws, ws_bytes, (cudaStream_t) stream, shared_mod, shared_rem);
+}
+
 int hmoe_combine(float* f, const float* o, float* y, int64_t n, const float* o2, void* stream)
 {
     if (!f || !y || n < 0 || n % 4) return fail(HMOE_E_ARG, "hmoe_combine: f, y and n % 4 == 0 required");

@@ -50,7 +50,7 @@ struct SmemLayout
 // prepare
 __global__ void __launch_bounds__(256) decode_prepare_kernel(const void* __restrict__ x, int x_bf16, const int64_t* __restrict__ sel,
     const __half* __restrict__ rw, int R, int H, int topk, int lo, int n_local, int has_shared, int act_quant,
-    __half* __restrict__ xf, float* __restrict__ xscale, Route* __restrict__ route)
+    __half* __restrict__ xf, float* __restrict__ xscale, Route* __restrict__ route, int sh_mod, int sh_rem)
 {
     const int tid = threadIdx.x;
     if ((int) blockIdx.x < R)
@@ -134,7 +134,10 @@ __global__ void __launch_bounds__(256) decode_prepare_kernel(const void* __restr
             }
         }
         else
-            for (int r = 0; r < R; ++r) { s_rows[j][n] = (unsigned char) r; s_w[j][n] = 1.f; ++n; }
+        {
+            // the shared expert takes every row with weight 1; under expert parallelism only rows r % sh_mod == sh_rem here
+            for (int r = 0; r < R; ++r) if (r % sh_mod == sh_rem) { s_rows[j][n] = (unsigned char) r; s_w[j][n] = 1.f; ++n; }
+        }
         s_n[j] = (unsigned char) n;
     }
     __syncthreads();
@@ -635,8 +638,9 @@ static void launch_pair(int grid, const DecodeArgs& a, int R, cudaStream_t st, b
 }
 
 int decode_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
-                  int act_quant, float* y, void* ws, size_t ws_bytes, cudaStream_t st)
+                  int act_quant, float* y, void* ws, size_t ws_bytes, cudaStream_t st, int sh_mod, int sh_rem)
 {
+    if (sh_mod < 1 || sh_rem < 0 || sh_rem >= sh_mod) return fail(HMOE_E_ARG, "hmoe_decode: shared-row split must satisfy 0 <= rem < mod");
     const int H = L->H, I = L->I;
     if (R < 1 || R > MAXR) return fail(HMOE_E_ARG, "hmoe_decode: rows must be 1..16");
     if (L->topk < 1 || L->topk > TOPK_MAX) return fail(HMOE_E_ARG, "hmoe_decode: topk must be 1..8");
@@ -663,7 +667,7 @@ int decode_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t
     const int has_shared = L->sh_gate_w != nullptr;
     if (g_prof) cudaEventRecord(g_ev[0], st);
     decode_prepare_kernel<<<R + 1, 256, 0, st>>>(x, x_dtype == HMOE_BF16, sel, (const __half*) rw, R, H, L->topk, lo, n_local, has_shared,
-                                                 act_quant, xf, xscale, route);
+                                                 act_quant, xf, xscale, route, sh_mod, sh_rem);
     DecodeArgs a;
     a.H = H; a.I = I;
     a.gate_w = L->gate_w; a.up_w = L->up_w; a.down_w = L->down_w; a.gate_s = L->gate_s; a.up_s = L->up_s; a.down_s = L->down_s;

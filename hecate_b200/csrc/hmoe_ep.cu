@@ -1,0 +1,138 @@
+// Expert-parallel exchange over NVLink peer memory for the decode path.
+//
+// The reference has no expert parallelism; its closest relative is the band mailbox: every band gets all rows plus
+// (sel, rw), ignores foreign expert ids (runtime/tier/moe4/moe4.cu:93) and hands back an fp32 partial that the combine adds
+// in a fixed order (runtime/tier/moe4/moe4.cu:702-717; slot + ISSUE / DONE flags in runtime/tier/rtx_graph.py:105-134).
+// Here the bands are the GPUs of one box: rank r owns experts [r E / W, (r + 1) E / W), every rank sees the step's <= 16 rows
+// (decode "dispatch" = the rows are replicated, each rank filters by expert id), computes its partial with the decode kernels
+// into its slot of a symmetric buffer, and the combine is one kernel per rank that
+//   1. raises this rank's generation flag in every peer's memory (st.release.sys over NVLink),
+//   2. waits, bounded, until every peer's flag in local memory has reached the generation,
+//   3. reads every rank's partial (peer loads) and adds them to the layer output in rank order, the same order on every
+//      rank, so all ranks hold bit-identical results,
+//   4. clears the slot of the other parity for the step after next.
+// Two slots alternate by step parity: a peer signals generation g + 1 only after its reads of generation g are done, so
+// passing the wait for g + 1 proves nobody still reads the slot that step g + 2 will reuse.
+#include <cstring>
+#include "hmoe_common.cuh"
+#include "hmoe_internal.h"
+
+namespace hmoe {
+namespace {
+
+struct EpArgs
+{
+    int rank, world;
+    float* slots[8];          // slots[p] = base of rank p's two partial slots (peer pointers; own pointer for p == rank)
+    unsigned* flags[8];       // flags[p] = base of rank p's flag array [world]
+};
+
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p)
+{
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ float4 ld_peer(const float4* p)
+{
+    float4 v;
+    asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
+__global__ void __launch_bounds__(256) ep_combine_kernel(const EpArgs a, unsigned gen, float* __restrict__ f, int n, size_t slot_floats,
+                                                         unsigned* __restrict__ status)
+{
+    __shared__ int ok_sh;
+    const int parity = gen & 1;
+    if (blockIdx.x == 0 && threadIdx.x < a.world) st_release_sys(a.flags[threadIdx.x] + a.rank, gen);
+    if (threadIdx.x == 0)
+    {
+        int ok = 1;
+        const unsigned long long t0 = globaltimer_ns();
+        for (int p = 0; p < a.world && ok; ++p)
+            while ((int) (ld_acquire_sys(a.flags[a.rank] + p) - gen) < 0)
+                if (globaltimer_ns() - t0 > 2000000000ull) { ok = 0; atomicOr(status, ST_WAIT_TIMEOUT); break; }
+        ok_sh = ok;
+    }
+    __syncthreads();
+    if (!ok_sh) return;
+    for (int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += gridDim.x * blockDim.x * 4)
+    {
+        float4 acc = *(float4*) (f + i);
+        for (int p = 0; p < a.world; ++p)
+        {
+            const float4 v = ld_peer((const float4*) (a.slots[p] + (size_t) parity * slot_floats + i));
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        *(float4*) (f + i) = acc;
+        *(float4*) (a.slots[a.rank] + (size_t) (parity ^ 1) * slot_floats + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+}
+
+}  // namespace
+
+int ep_combine_launch(int rank, int world, void* const* slots, void* const* flags, unsigned gen, float* f, int rows, int H, size_t slot_floats,
+                      unsigned* status, cudaStream_t st)
+{
+    if (world < 1 || world > 8 || rank < 0 || rank >= world) return fail(HMOE_E_ARG, "hmoe_ep_combine: world must be 1..8");
+    const int n = rows * H;
+    if (!f || !slots || !flags || !status || n <= 0 || n % 4 || (size_t) n > slot_floats) return fail(HMOE_E_ARG, "hmoe_ep_combine: sizes");
+    EpArgs a;
+    a.rank = rank; a.world = world;
+    for (int p = 0; p < 8; ++p) { a.slots[p] = p < world ? (float*) slots[p] : nullptr; a.flags[p] = p < world ? (unsigned*) flags[p] : nullptr; }
+    const int blocks = (n / 4 + 255) / 256 < 96 ? (n / 4 + 255) / 256 : 96;
+    ep_combine_kernel<<<blocks, 256, 0, st>>>(a, gen, f, n, slot_floats, status);
+    count_launches(1);
+    const cudaError_t err = cudaGetLastError();
+    return err == cudaSuccess ? HMOE_OK : fail(HMOE_E_CUDA, cudaGetErrorString(err));
+}
+
+}  // namespace hmoe
+
+using namespace hmoe;
+
+extern "C" {
+
+int hmoe_ep_alloc(size_t bytes, void** ptr)
+{
+    if (!ptr || bytes == 0) return fail(HMOE_E_ARG, "hmoe_ep_alloc: arguments");
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e == cudaSuccess) e = cudaMemset(p, 0, bytes);
+    if (e != cudaSuccess) return fail(HMOE_E_CUDA, cudaGetErrorString(e));
+    *ptr = p;
+    return HMOE_OK;
+}
+int hmoe_ep_free(void* ptr) { return cudaFree(ptr) == cudaSuccess ? HMOE_OK : fail(HMOE_E_CUDA, "hmoe_ep_free: cudaFree failed"); }
+int hmoe_ep_export(void* ptr, unsigned char* handle64)
+{
+    if (!ptr || !handle64) return fail(HMOE_E_ARG, "hmoe_ep_export: arguments");
+    cudaIpcMemHandle_t h;
+    const cudaError_t e = cudaIpcGetMemHandle(&h, ptr);
+    if (e != cudaSuccess) return fail(HMOE_E_CUDA, cudaGetErrorString(e));
+    static_assert(sizeof(h) == 64, "ipc handle size");
+    memcpy(handle64, &h, 64);
+    return HMOE_OK;
+}
+int hmoe_ep_open(const unsigned char* handle64, void** ptr)
+{
+    if (!ptr || !handle64) return fail(HMOE_E_ARG, "hmoe_ep_open: arguments");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    void* p = nullptr;
+    const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return fail(HMOE_E_CUDA, cudaGetErrorString(e));
+    *ptr = p;
+    return HMOE_OK;
+}
+int hmoe_ep_close(void* ptr) { return cudaIpcCloseMemHandle(ptr) == cudaSuccess ? HMOE_OK : fail(HMOE_E_CUDA, "hmoe_ep_close failed"); }
+
+int hmoe_ep_combine(int rank, int world, void* const* slots, void* const* flags, uint32_t gen, float* f, int rows, int H, size_t slot_floats,
+                    uint32_t* status, void* stream)
+{
+    return ep_combine_launch(rank, world, slots, flags, gen, f, rows, H, slot_floats, status, (cudaStream_t) stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,197 @@
+"""Expert-parallel decode over the GPUs of one box: one process per GPU (torch.distributed for the set-up plumbing), experts
+split by contiguous id ranges, the step's rows replicated on every rank, partial outputs combined over NVLink peer memory
+by `hmoe_ep_combine` (or, as the baseline, by an NCCL all-reduce).
+
+The reference has no expert parallelism; the shape kept from it is its band split: every band receives all rows with
+(sel, rw), ignores foreign ids and returns an fp32 partial that is added in a fixed order (runtime/tier/tier_split.py:3-11,
+runtime/tier/moe4/moe4.cu:93,702-717).
+"""
+import ctypes as C
+import json
+import os
+import time
+
+import numpy as np
+
+from . import moe
+from ._lib import check, lib, vp
+
+MAX_ROWS = 16
+
+
+def shard_plan(rank, world, n_experts):
+    """Which part of a layer rank `rank` of `world` serves: experts [lo, lo + n_local) and, of the shared expert, the rows
+    r with r % shared_mod == shared_rem."""
+    if n_experts % world:
+        raise ValueError("the number of experts must be a multiple of the world size")
+    n_local = n_experts // world
+    return dict(lo=rank * n_local, n_local=n_local, shared_mod=world, shared_rem=rank)
+
+
+class PeerBuffers:
+    """Symmetric buffers of the combine: per rank two fp32 partial slots [MAX_ROWS * H] and `world` generation flags,
+    allocated with cudaMalloc by the library, exported with CUDA IPC and opened by every peer."""
+
+    def __init__(self, rank, world, H, device, dist):
+        import torch
+        self.rank, self.world, self.H = rank, world, H
+        self.slot_floats = MAX_ROWS * H
+        self.bytes = 2 * self.slot_floats * 4 + 256
+        p = C.c_void_p()
+        check(lib().hmoe_ep_alloc(C.c_size_t(self.bytes), C.byref(p)))
+        self.own = p.value
+        h = (C.c_ubyte * 64)()
+        check(lib().hmoe_ep_export(C.c_void_p(self.own), h))
+        handles = [None] * world
+        dist.all_gather_object(handles, bytes(h))
+        self.base = []
+        for r in range(world):
+            if r == rank:
+                self.base.append(self.own)
+            else:
+                q = C.c_void_p()
+                check(lib().hmoe_ep_open((C.c_ubyte * 64).from_buffer_copy(handles[r]), C.byref(q)))
+                self.base.append(q.value)
+        self.slots = (C.c_void_p * world)(*self.base)
+        self.flags = (C.c_void_p * world)(*[b + 2 * self.slot_floats * 4 for b in self.base])
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.gen = 0
+        dist.barrier()
+
+    def slot_ptr(self, gen):
+        return self.own + (gen & 1) * self.slot_floats * 4
+
+    def close(self):
+        for r, b in enumerate(self.base):
+            if r != self.rank:
+                lib().hmoe_ep_close(C.c_void_p(b))
+        lib().hmoe_ep_free(C.c_void_p(self.own))
+
+
+class EpDecoder:
+    """One rank's side of an expert-parallel decode layer."""
+
+    def __init__(self, rank, world, tables, n_experts, device, dist, use_peer=True):
+        self.rank, self.world, self.tabs, self.dev, self.dist = rank, world, tables, device, dist
+        self.plan = shard_plan(rank, world, n_experts)
+        assert tables.n == self.plan["n_local"]
+        self.ws = moe.decode_workspace(tables.H, tables.I, device)
+        self.use_peer = use_peer and world > 1
+        self.peer = PeerBuffers(rank, world, tables.H, device, dist) if self.use_peer else None
+        import torch
+        self.y = torch.zeros(MAX_ROWS, tables.H, dtype=torch.float32, device=device)
+        self.struct = tables.struct()
+
+    def step(self, x, sel, rw, f):
+        """f[R][H] (fp32) += the layer's output for rows x with global routing (sel, rw); identical on every rank."""
+        import torch
+        R = x.shape[0]
+        st = C.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)
+        pl = self.plan
+        if self.use_peer:
+            self.peer.gen += 1
+            g = self.peer.gen
+            check(lib().hmoe_decode_ep(C.byref(self.struct), vp(x), C.c_int(moe._dt(x)), vp(sel), vp(rw), C.c_int(R), C.c_int(pl["lo"]),
+                                       C.c_int(pl["n_local"]), C.c_int(0), C.c_void_p(self.peer.slot_ptr(g)), vp(self.ws),
+                                       C.c_size_t(self.ws.numel()), C.c_int(pl["shared_mod"]), C.c_int(pl["shared_rem"]), st))
+            check(lib().hmoe_ep_combine(C.c_int(self.rank), C.c_int(self.world), self.peer.slots, self.peer.flags, C.c_uint32(g), vp(f),
+                                        C.c_int(R), C.c_int(self.tabs.H), C.c_size_t(self.peer.slot_floats), vp(self.peer.status), st))
+        else:
+            y = self.y[:R]
+            check(lib().hmoe_decode_ep(C.byref(self.struct), vp(x), C.c_int(moe._dt(x)), vp(sel), vp(rw), C.c_int(R), C.c_int(pl["lo"]),
+                                       C.c_int(pl["n_local"]), C.c_int(0), vp(y), vp(self.ws), C.c_size_t(self.ws.numel()),
+                                       C.c_int(pl["shared_mod"]), C.c_int(pl["shared_rem"]), st))
+            if self.world > 1:
+                self.dist.all_reduce(y)
+            moe.moe4_combine(f, 0, y, R, 0)
+        return f
+
+    def status(self):
+        import torch
+        torch.cuda.synchronize(self.dev)
+        s = moe.ws_status(self.ws)
+        if self.peer is not None:
+            s |= int(self.peer.status.item())
+        return s
+
+
+def bench_decode(args, world, rank, dev):
+    """bench.py's N > 1 arm: the decode configuration with the 256 experts split over `world` GPUs, the 16 rows replicated
+    (strong scaling: the global batch is fixed), combine over peer memory; the NCCL all-reduce variant is timed beside it."""
+    import torch
+    import torch.distributed as dist
+    import bench as B
+    from . import synth
+    E, H, I, TOPK, ROWS, NBATCH = B.E, B.H, B.I, B.TOPK, B.ROWS, B.NBATCH
+    steps, warmup = args.steps, max(3, args.warmup)
+    pl = shard_plan(rank, world, E)
+    tabs = B.build_layer(dev, 100 + rank, list(range(pl["lo"], pl["lo"] + pl["n_local"])), torch, moe)
+    wt = torch.from_numpy(synth.router_weight(0, 0, E, H)).to(dev).to(torch.bfloat16)
+    bias = torch.zeros(E, dtype=torch.float32, device=dev)
+    xs = [torch.from_numpy(synth.activations(b, 0, ROWS, H)).to(torch.bfloat16).to(dev) for b in range(NBATCH)]
+    xs_host = [x.cpu().pin_memory() for x in xs]
+    sel = torch.empty(ROWS, TOPK, dtype=torch.int64, device=dev)
+    rw = torch.empty(ROWS, TOPK, dtype=torch.float16, device=dev)
+    f = torch.zeros(ROWS, H, dtype=torch.float32, device=dev)
+    f_host = torch.empty(ROWS, H, dtype=torch.float32).pin_memory()
+    x_in = torch.empty(ROWS, H, dtype=torch.bfloat16, device=dev)
+    results = {}
+    for mode in ("nccl", "peer"):
+        dec = EpDecoder(rank, world, tabs, E, dev, dist, use_peer=(mode == "peer"))
+
+        def step(x):
+            moe.router_fused(x, wt, bias, None, None, sel, rw, TOPK, 1.0)
+            dec.step(x, sel, rw, f)
+
+        for i in range(warmup):
+            step(xs[i % NBATCH])
+        torch.cuda.synchronize(); dist.barrier()
+        l0 = moe.launch_count()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with B.ClockSampler(dev.index) as cs:
+            torch.cuda.synchronize(); dist.barrier()
+            ev0.record()
+            for i in range(steps):
+                step(xs[i % NBATCH])
+            ev1.record()
+            torch.cuda.synchronize(); dist.barrier()
+        ms = torch.tensor([ev0.elapsed_time(ev1) / steps], device=dev)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        launches = moe.launch_count() - l0
+        t0 = time.perf_counter()
+        n2 = min(steps, 200)
+        for i in range(n2):
+            x_in.copy_(xs_host[i % NBATCH], non_blocking=True); step(x_in); f_host.copy_(f, non_blocking=True); torch.cuda.synchronize()
+        e2e = torch.tensor([(time.perf_counter() - t0) / n2], device=dev)
+        dist.all_reduce(e2e, op=dist.ReduceOp.MAX)
+        st = torch.tensor([dec.status()], device=dev); dist.all_reduce(st, op=dist.ReduceOp.MAX)
+        results[mode] = dict(ms=float(ms.item()), e2e=float(e2e.item()), launches=int(launches), status=int(st.item()), clocks=cs.summary())
+        if dec.peer is not None:
+            dist.barrier(); dec.peer.close()
+    # load balance of the last batch: distinct local experts per rank
+    d_local = torch.tensor([float(((sel >= pl["lo"]) & (sel < pl["lo"] + pl["n_local"])).nonzero().shape[0] and
+                                  torch.unique(sel[(sel >= pl["lo"]) & (sel < pl["lo"] + pl["n_local"])]).numel())], device=dev)
+    d_all = [torch.zeros_like(d_local) for _ in range(world)]
+    dist.all_gather(d_all, d_local)
+    if rank == 0:
+        r = results["peer"]
+        dl = [float(t.item()) for t in d_all]
+        peak, kind = B.measured_peaks()
+        bytes_rank_max = (max(dl) + 1) * B.EXPERT_BYTES + E * H * 2
+        print(json.dumps({
+            "metric": B.METRIC, "value": ROWS / (r["ms"] * 1e-3), "unit": B.UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": r["ms"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int4 x fp16 -> fp32",
+            "data": "synthetic",
+            "config": {"workload": B.WORKLOAD + f"; experts split over {world} GPUs ({pl['n_local']} each), rows replicated, "
+                                                "combine over NVLink peer memory",
+                       "l2": "inputs larger than L2: 8 input batches in a ring, each step streams different experts"},
+            "us_per_layer": r["ms"] * 1e3, "nccl_allreduce_us_per_layer": results["nccl"]["ms"] * 1e3,
+            "distinct_local_experts_last_step": dl, "load_imbalance_max_over_mean": max(dl) / (sum(dl) / len(dl)),
+            "combine_bytes_per_rank": (world - 1) * ROWS * H * 4, "dispatch_bytes_per_rank": 0,
+            "roofline": {"bound": "hbm", "kernel": "decode kernels of the most loaded rank (whole call)", "achieved": bytes_rank_max / (r["ms"] * 1e-3) / 1e9,
+                         "peak": peak, "unit": "GB/s", "frac": bytes_rank_max / (r["ms"] * 1e-3) / 1e9 / peak, "peak_kind": kind, "traffic": None},
+            "e2e": {"value": ROWS / r["e2e"], "unit": B.UNIT, "h2d_bytes_per_step": ROWS * H * 2, "d2h_bytes_per_step": ROWS * H * 4,
+                    "us_per_layer": r["e2e"] * 1e6},
+            "gpu_launches": r["launches"], "device_status": max(r["status"], results["nccl"]["status"]), "clocks": r["clocks"]}))
+    dist.barrier()
+    dist.destroy_process_group()

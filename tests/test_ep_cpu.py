@@ -1,0 +1,61 @@
+"""Expert-parallel host logic on CPU ranks (gloo, world size 2): the expert ranges and the shared-row split cover the layer
+exactly once, and partials summed over ranks equal the single-rank result."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_shard_plan_covers_everything_once():
+    from hecate_b200.ep import shard_plan
+    for world in (1, 2, 4, 8):
+        seen = np.zeros(256, dtype=int)
+        rows = np.zeros(16, dtype=int)
+        for r in range(world):
+            p = shard_plan(r, world, 256)
+            seen[p["lo"]:p["lo"] + p["n_local"]] += 1
+            rows[[i for i in range(16) if i % p["shared_mod"] == p["shared_rem"]]] += 1
+        assert (seen == 1).all() and (rows == 1).all()
+    with pytest.raises(ValueError):
+        shard_plan(0, 3, 256)
+
+
+def _rank_main(rank, world, port, out_path):
+    sys.path.insert(0, ROOT); sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import torch
+    import torch.distributed as dist
+    from helpers import HostLayer
+    from hecate_b200 import synth
+    from hecate_b200.ep import shard_plan
+    from oracle import oracle as O
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    H, I, E, R = 256, 128, 8, 6
+    hl = HostLayer(0, 0, H, I, range(E), 128, True)
+    ex, sh = hl.oracle_experts(O)
+    x = synth.activations(1, 0, R, H).astype(np.float16)
+    sel, rw = synth.zipf_routing(2, 0, R, E, 8, 0.0)
+    p = shard_plan(rank, world, E)
+    # this rank's partial: its experts for all rows, the shared expert for its rows only (as hmoe_decode_ep computes it)
+    part = O.moe_forward(H, I, 128, x, sel, rw, p["lo"], ex[p["lo"]:p["lo"] + p["n_local"]], None, mode=1)
+    mine = [r for r in range(R) if r % p["shared_mod"] == p["shared_rem"]]
+    none = np.full((len(mine), 8), 10 ** 6, dtype=np.int64)
+    part[mine] += O.moe_forward(H, I, 128, x[mine], none, rw[mine], 0, [], sh, mode=1)
+    t = torch.from_numpy(part.astype(np.float64))
+    dist.all_reduce(t)
+    if rank == 0:
+        full = O.moe_forward(H, I, 128, x, sel, rw, 0, ex, sh, mode=1)
+        np.save(out_path, np.stack([t.numpy(), full.astype(np.float64)]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_partials_over_two_gloo_ranks_equal_single_rank(tmp_path):
+    import torch.multiprocessing as mp
+    out = str(tmp_path / "ep.npy")
+    port = 29500 + os.getpid() % 2000
+    mp.spawn(_rank_main, args=(2, port, out), nprocs=2, join=True)
+    got, full = np.load(out)
+    assert np.abs(got - full).max() <= 1e-5 * np.abs(full).max()

@@ -1,0 +1,104 @@
+"""Expert-parallel decode on GPUs: the peer-memory combine against the single-GPU result (needs 2 GPUs, else skipped), and
+the bounded wait of the combine kernel when a peer never signals (1 GPU, no fault: the kernel gives up and reports it)."""
+import ctypes as C
+import os
+import sys
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_combine_wait_is_bounded_and_reported():
+    """A 'peer' whose flag nobody ever raises: the combine kernel waits about two seconds, sets the status bit, adds
+    nothing, and the context stays usable."""
+    import torch
+    from hecate_b200 import moe
+    from hecate_b200._lib import lib, vp
+    dev = torch.device("cuda:0")
+    H, rows = 256, 4
+    slot_floats = 16 * H
+    own = torch.zeros(2 * slot_floats + 64, dtype=torch.float32, device=dev)
+    dead = torch.zeros(2 * slot_floats + 64, dtype=torch.float32, device=dev)      # stands in for a peer that never arrives
+    own[:rows * H] = 1.0
+    slots = (C.c_void_p * 2)(own.data_ptr(), dead.data_ptr())
+    flags = (C.c_void_p * 2)(own.data_ptr() + 2 * slot_floats * 4, dead.data_ptr() + 2 * slot_floats * 4)
+    f = torch.zeros(rows, H, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    rc = lib().hmoe_ep_combine(C.c_int(0), C.c_int(2), slots, flags, C.c_uint32(2), vp(f), C.c_int(rows), C.c_int(H), C.c_size_t(slot_floats),
+                               vp(status), C.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) & 1 == 1                       # the wait gave up
+    assert float(f.abs().max()) == 0.0                       # and nothing was combined
+    status.zero_()
+    # the same call with the peer's flag raised completes and sums both slots (generation 2 -> slot 0)
+    own_flags = own[2 * slot_floats:].view(torch.int32); own_flags[1] = 2
+    dead[:rows * H] = 0.5
+    rc = lib().hmoe_ep_combine(C.c_int(0), C.c_int(2), slots, flags, C.c_uint32(2), vp(f), C.c_int(rows), C.c_int(H), C.c_size_t(slot_floats),
+                               vp(status), C.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+    torch.cuda.synchronize()
+    assert rc == 0 and int(status.item()) == 0
+    assert torch.allclose(f, torch.full_like(f, 1.5))
+
+
+def _rank_main(rank, world, port, out_path):
+    sys.path.insert(0, ROOT); sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import torch
+    import torch.distributed as dist
+    from helpers import HostLayer
+    from hecate_b200 import moe, synth
+    from hecate_b200.ep import EpDecoder, shard_plan
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world, device_id=dev)
+    H, I, E, R = 512, 256, 16, 16
+    p = shard_plan(rank, world, E)
+    local = HostLayer(0, 0, H, I, range(p["lo"], p["lo"] + p["n_local"]), 128, True).upload(dev)
+    x = torch.from_numpy(synth.activations(1, 0, R, H)).to(dev).half()
+    res = {}
+    for mode in (True, False):
+        dec = EpDecoder(rank, world, local, E, dev, dist, use_peer=mode)
+        outs = []
+        for stepi in range(4):                                # several steps: both slots and the generation logic get used
+            sel, rw = synth.zipf_routing(10 + stepi, 0, R, E, 8, 0.0)
+            f = torch.zeros(R, H, device=dev)
+            dec.step(x, torch.from_numpy(sel).to(dev), torch.from_numpy(rw).to(dev), f)
+            outs.append(f)
+        assert dec.status() == 0
+        res[mode] = torch.stack(outs)
+        if dec.peer is not None:
+            dist.barrier(); dec.peer.close()
+    # all ranks hold the same bits after the peer combine (fixed rank order)
+    mine = res[True].clone()
+    others = [torch.zeros_like(mine) for _ in range(world)]
+    dist.all_gather(others, mine)
+    same = all(torch.equal(o, mine) for o in others)
+    if rank == 0:
+        full = HostLayer(0, 0, H, I, range(E), 128, True).upload(dev)
+        ws = moe.decode_workspace(H, I, dev)
+        refs = []
+        for stepi in range(4):
+            sel, rw = synth.zipf_routing(10 + stepi, 0, R, E, 8, 0.0)
+            y = torch.zeros(R, H, device=dev)
+            moe.decode(full, x, torch.from_numpy(sel).to(dev), torch.from_numpy(rw).to(dev), y, ws)
+            refs.append(y)
+        ref = torch.stack(refs)
+        np.save(out_path, np.array([float(same), float((res[True] - ref).norm() / ref.norm()), float((res[False] - ref).norm() / ref.norm())]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_gpu_peer_combine_matches_single_gpu(tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    out = str(tmp_path / "ep.npy")
+    mp.spawn(_rank_main, args=(2, 29600 + os.getpid() % 2000, out), nprocs=2, join=True)
+    same, err_peer, err_nccl = np.load(out)
+    assert same == 1.0
+    assert err_peer < 1e-3 and err_nccl < 1e-3
