@@ -59,17 +59,20 @@ __global__ void __launch_bounds__(256) decode_prepare_kernel(const void* __restr
         for (int gi = tid; gi < H / 32; gi += blockDim.x)
         {
             float v[32];
-            if (x_bf16)
             {
-                const uint16_t* p = (const uint16_t*) x + (size_t) r * H + gi * 32;
+                const uint4* p = (const uint4*) ((const uint16_t*) x + (size_t) r * H + gi * 32);
                 #pragma unroll
-                for (int k = 0; k < 32; ++k) v[k] = bf16_bits_to_float(p[k]);
-            }
-            else
-            {
-                const __half* p = (const __half*) x + (size_t) r * H + gi * 32;
-                #pragma unroll
-                for (int k = 0; k < 32; ++k) v[k] = __half2float(p[k]);
+                for (int j = 0; j < 4; ++j)
+                {
+                    const uint4 u = p[j];
+                    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+                    #pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                    {
+                        if (x_bf16) { v[j * 8 + 2 * k] = __uint_as_float(w[k] << 16); v[j * 8 + 2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u); }
+                        else { const float2 f = __half22float2(*(const __half2*) &w[k]); v[j * 8 + 2 * k] = f.x; v[j * 8 + 2 * k + 1] = f.y; }
+                    }
+                }
             }
             if (act_quant)
             {
@@ -102,20 +105,29 @@ __global__ void __launch_bounds__(256) decode_prepare_kernel(const void* __restr
     __shared__ float s_w[MAXS][MAXR];
     __shared__ short s_tile0[MAXS];
     __shared__ int m_sh;
+    __shared__ short s_sel[MAXR * TOPK_MAX];
+    __shared__ float s_rw[MAXR * TOPK_MAX];
+    __shared__ int wcount[8];
     for (int i = tid; i < 256; i += blockDim.x) flag[i] = 0;
     __syncthreads();
     for (int i = tid; i < R * topk; i += blockDim.x)
     {
         const int64_t e = sel[i] - lo;
-        if (e >= 0 && e < n_local) flag[(int) e] = 1;
+        const bool in = e >= 0 && e < n_local;
+        s_sel[i] = in ? (short) e : (short) -1;
+        s_rw[i] = __half2float(rw[i]);
+        if (in) flag[(int) e] = 1;
     }
     __syncthreads();
-    if (tid == 0)
     {
-        int m = 0;
-        for (int e = 0; e < n_local; ++e) if (flag[e]) slot_e[m++] = (short) e;
-        m_sh = m;
-        if (has_shared) slot_e[m] = -1;
+        // distinct experts in ascending order: one flag per thread, ballots per warp, prefix over the eight warps
+        const unsigned b = __ballot_sync(0xffffffffu, flag[tid] != 0);
+        if ((tid & 31) == 0) wcount[tid >> 5] = __popc(b);
+        __syncthreads();
+        int before = 0, m = 0;
+        for (int w = 0; w < 8; ++w) { if (w < (tid >> 5)) before += wcount[w]; m += wcount[w]; }
+        if (flag[tid]) slot_e[before + __popc(b & ((1u << (tid & 31)) - 1u))] = (short) tid;
+        if (tid == 0) { m_sh = m; if (has_shared) slot_e[m] = -1; }
     }
     __syncthreads();
     const int m = m_sh, ns = m + (has_shared ? 1 : 0);
@@ -129,7 +141,7 @@ __global__ void __launch_bounds__(256) decode_prepare_kernel(const void* __restr
             {
                 float ws = 0.f; bool hit = false;
                 for (int k = 0; k < topk; ++k)
-                    if ((int) (sel[r * topk + k] - lo) == e) { ws += __half2float(rw[r * topk + k]); hit = true; }
+                    if (s_sel[r * topk + k] == e) { ws += s_rw[r * topk + k]; hit = true; }
                 if (hit) { s_rows[j][n] = (unsigned char) r; s_w[j][n] = ws; ++n; }
             }
         }

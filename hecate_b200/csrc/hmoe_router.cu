@@ -11,7 +11,7 @@ namespace hmoe {
 namespace {
 
 constexpr int RW = 8;     // warps per block = experts per block
-constexpr int RR = 8;     // rows per block
+constexpr int RR = 4;     // rows per block
 
 template <bool BF>
 __device__ __forceinline__ void widen8(const uint4& v, float* f)
@@ -44,17 +44,29 @@ __global__ void __launch_bounds__(RW * 32) router_logits_kernel(const uint16_t* 
     #pragma unroll
     for (int r = 0; r < RR; ++r) acc[r] = 0.f;
     const uint16_t* w = wt + (size_t) e * H;
-    for (int k = lane * 8; k < H; k += 256)
+    // four 256-column steps per trip with their weight loads issued first; the additions stay in column order
+    for (int k0 = lane * 8; k0 < H; k0 += 1024)
     {
-        float wf[8];
-        widen8<WBF>(ldg128_nc(w + k), wf);
+        uint4 wv[4];
         #pragma unroll
-        for (int r = 0; r < RR; ++r)
+        for (int u = 0; u < 4; ++u) wv[u] = k0 + u * 256 < H ? ldg128_nc(w + k0 + u * 256) : make_uint4(0, 0, 0, 0);
+        #pragma unroll
+        for (int u = 0; u < 4; ++u)
         {
-            float xf[8];
-            widen8<XBF>(*(const uint4*) (xs + r * H + k), xf);
-            #pragma unroll
-            for (int j = 0; j < 8; ++j) acc[r] = __fmaf_rn(xf[j], wf[j], acc[r]);
+            const int k = k0 + u * 256;
+            if (k < H)
+            {
+                float wf[8];
+                widen8<WBF>(wv[u], wf);
+                #pragma unroll
+                for (int r = 0; r < RR; ++r)
+                {
+                    float xf[8];
+                    widen8<XBF>(*(const uint4*) (xs + r * H + k), xf);
+                    #pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[r] = __fmaf_rn(xf[j], wf[j], acc[r]);
+                }
+            }
         }
     }
     #pragma unroll
