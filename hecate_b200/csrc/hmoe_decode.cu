@@ -35,14 +35,15 @@ constexpr int NSTAGE = 3;
 constexpr int NBUF = 4;                  // gate_up partial-sum buffers in rotation (a warp runs at most NSTAGE items ahead)
 constexpr int GU_FLOATS = 2 * 64 * 8;    // [matrix][64 rows][8 tile columns]
 constexpr int YACC_FLOATS = MAXR * 64;
+constexpr int YCOPIES = 8;                // copies of the down kernel's output slice (two warps share one)
 
 struct SmemLayout
 {
     static constexpr int ring = 0;
     static constexpr int gu = NSTAGE * STAGE_BYTES;                   // gate_up: NBUF x GU_FLOATS; down: YACC_FLOATS
-    static constexpr int bars = gu + NBUF * GU_FLOATS * 4;            // full[NSTAGE]
-    static constexpr int cnt = bars + NSTAGE * 8;                     // NBUF item arrival counters, NSTAGE stage-free counters
-    static constexpr int flags = cnt + (NBUF + NSTAGE) * 4;
+    static constexpr int bars = gu + (NBUF * GU_FLOATS > YCOPIES * YACC_FLOATS ? NBUF * GU_FLOATS : YCOPIES * YACC_FLOATS) * 4;   // full[NSTAGE][CW]
+    static constexpr int cnt = bars + NSTAGE * CW * 8;                // NBUF arrival counters, NBUF completion counters
+    static constexpr int flags = cnt + (2 * NBUF + NSTAGE) * 4;      // + down: NSTAGE stage-free counters
     static constexpr int total = flags + 16;
 };
 
@@ -286,25 +287,9 @@ __device__ __forceinline__ void prefetch(const Item& it, int kb, int KB, Pre& pr
     if (GROUPED) pr.sc = ldg128_nc(it.sc + (size_t) (kb >> 1) * 128);
 }
 
-// The ring is refilled by whichever warp frees a stage last: after its last read of stage number `it` a warp bumps the
-// stage's counter, and the warp that brings it to CW issues the copies of stage number it + NSTAGE into the same slot.
-// No thread ever waits for a free slot.
-template <typename Fill>
-__device__ __forceinline__ void release_stage(int* free_cnt, uint32_t st, uint32_t it, uint32_t total, int lane, Fill fill)
-{
-    __syncwarp();
-    if (lane == 0)
-    {
-        __threadfence_block();
-        if (atomicAdd(free_cnt + st, 1) == CW - 1)
-        {
-            free_cnt[st] = 0;
-            __threadfence_block();
-            if (it + NSTAGE < total) fill(it + NSTAGE);
-        }
-    }
-}
-
+// Each warp owns a private three-slot ring of 4 KB (its two 64-column blocks of a stage) with one mbarrier per slot. When it
+// has read a slot, its lane 0 at once issues the 1-D bulk copy of the data it will need three stages later into that slot,
+// so the warps stream independently: nobody waits for the slowest warp of a stage and no slot ever waits to be freed.
 // ---------------------------------------------------------------------------------------------------------------------
 // gate_up
 template <bool GROUPED, bool Q8>
@@ -315,13 +300,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_gate_up_kernel(const Decod
     const uint32_t ring = sbase + SmemLayout::ring, full0 = sbase + SmemLayout::bars;
     float* gu = (float*) (smem + SmemLayout::gu);
     int* cnt = (int*) (smem + SmemLayout::cnt);
-    int* free_cnt = cnt + NBUF;
     volatile int* abort_flag = (volatile int*) (smem + SmemLayout::flags);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0)
     {
-        for (int i = 0; i < NSTAGE; ++i) mbar_init(full0 + i * 8, 1);
-        for (int i = 0; i < NBUF + NSTAGE; ++i) cnt[i] = 0;
+        for (int i = 0; i < NSTAGE * CW; ++i) mbar_init(full0 + i * 8, 1);
+        for (int i = 0; i < 2 * NBUF; ++i) cnt[i] = 0;
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -332,16 +316,28 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_gate_up_kernel(const Decod
     const int P = rt->ntiles * NG;
     const int p0 = (int) ((long long) P * blockIdx.x / gridDim.x), p1 = (int) ((long long) P * (blockIdx.x + 1) / gridDim.x);
     const int mat = warp >> 3, kw = warp & 7, g = lane >> 2, q = lane & 3;
-    const uint32_t total = (uint32_t) (p1 - p0) * S;
-    auto fill = [&](uint32_t i) {
-        const int p = p0 + (int) (i / S), s = (int) (i % S);
-        const int tile = p / NG, gr = p % NG, e = rt->expert[tile];
-        const char* gw = (const char*) (e >= 0 ? (const void*) a.gate_w[e] : a.sh_gw) + ((size_t) gr * KB + 16 * s) * 2048;
-        const char* uw = (const char*) (e >= 0 ? (const void*) a.up_w[e] : a.sh_uw) + ((size_t) gr * KB + 16 * s) * 2048;
-        const uint32_t st = i % NSTAGE, bytes = (KB - 16 * s < 16 ? KB - 16 * s : 16) * 2048;
-        mbar_expect_tx(full0 + st * 8, 2 * bytes);
-        bulk_g2s(ring + st * STAGE_BYTES, gw, bytes, full0 + st * 8);
-        bulk_g2s(ring + st * STAGE_BYTES + STAGE_BYTES / 2, uw, bytes, full0 + st * 8);
+    // fill cursor of this warp: the next stage to request is stage f_s of item (f_tile, f_gr); f_src = its matrix's packed codes
+    int f_tile = p0 / NG, f_gr = p0 % NG, f_s = 0, f_left = p1 - p0;
+    auto item_src = [&](int tile, int gr) {
+        const int e = rt->expert[tile];
+        return (const char*) (e >= 0 ? (const void*) (mat ? a.up_w[e] : a.gate_w[e]) : (mat ? a.sh_uw : a.sh_gw)) + (size_t) gr * KB * 2048;
+    };
+    const char* f_src = p0 < p1 ? item_src(f_tile, f_gr) : nullptr;      // looked up when the cursor enters an item, used a stage later
+    auto fill_next = [&](uint32_t slot) {
+        if (f_left <= 0) return;
+        const int kb = 16 * f_s + 2 * kw;
+        if (kb < KB)
+        {
+            const uint32_t bar = full0 + (slot * CW + warp) * 8;
+            mbar_expect_tx(bar, 4096);
+            bulk_g2s(ring + slot * STAGE_BYTES + warp * 4096, f_src + (size_t) kb * 2048, 4096, bar);
+        }
+        if (++f_s == S)
+        {
+            f_s = 0; --f_left;
+            if (++f_gr == NG) { f_gr = 0; ++f_tile; }
+            if (f_left > 0) f_src = item_src(f_tile, f_gr);
+        }
     };
     auto load_item = [&](int tile, int gr) {
         Item it;
@@ -361,8 +357,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_gate_up_kernel(const Decod
     };
     if (p0 < p1)
     {
-        if (threadIdx.x == 0)
-            for (uint32_t i = 0; i < NSTAGE && i < total; ++i) fill(i);
+        if (lane == 0)
+            for (uint32_t i = 0; i < NSTAGE; ++i) fill_next(i);
         float acc[4][4];
         #pragma unroll
         for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
@@ -374,8 +370,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_gate_up_kernel(const Decod
         // Finishing an item: warp w owns tile column w / 2 and rows 32 (w % 2) + lane of the 64-row group. It waits (bounded)
         // until all CW partial tiles of the item are in, reads its gate / up sums, clears them for the buffer's next use and
         // writes act = silu(gate) * up * routing weight as the down kernel's MMA operand. A warp does this one ring stage
-        // after it delivered its own partial, before it frees that stage, so a buffer is never reused too early: a warp
-        // can run at most NSTAGE stages (<= NSTAGE items) ahead of the slowest one and NBUF > NSTAGE.
+        // after it delivered its own partial; it
+        // counts itself done afterwards, and no warp adds a later item's partial into the buffer before all sixteen are done
+        // with the buffer's previous item (the warps stream independently and may drift apart).
         Item prev = cur; bool have_prev = false; int prev_idx = 0;
         auto finish_item = [&](const Item& pi, int idx) {
             const int b = idx % NBUF, target = CW * (idx / NBUF + 1);
@@ -418,6 +415,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_gate_up_kernel(const Decod
                 if (lane == 0) a.ascale[row * (a.I / 32) + pi.gr * 2 + (warp & 1)] = sc;
             }
             a.act[row * a.I + pi.gr * 64 + frag_pos(n >> 1) * 2 + (n & 1)] = __float2half_rn(v);
+            __syncwarp();
+            if (lane == 0) { __threadfence_block(); atomicAdd(cnt + NBUF + b, 1); }
         };
         for (int p = p0; p < p1 && alive; ++p)
         {
@@ -432,11 +431,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_gate_up_kernel(const Decod
                     nxt = load_item(wrap ? cur.tile + 1 : cur.tile, wrap ? 0 : cur.gr + 1);
                     prefetch<GROUPED, Q8>(nxt, 2 * kw, KB, pn);
                 }
-                if (!mbar_wait(full0 + st * 8, par, abort_flag, a.status)) { alive = false; break; }
                 if (16 * s + 2 * kw < KB)
-                    consume_group<GROUPED, Q8>(ring + st * STAGE_BYTES + mat * (STAGE_BYTES / 2) + kw * 4096, pc, acc, lane);
+                {
+                    if (!mbar_wait(full0 + (st * CW + warp) * 8, par, abort_flag, a.status)) { alive = false; break; }
+                    consume_group<GROUPED, Q8>(ring + st * STAGE_BYTES + warp * 4096, pc, acc, lane);
+                }
+                __syncwarp();
+                if (lane == 0) fill_next(st);
                 if (s == 0 && have_prev) { finish_item(prev, prev_idx); have_prev = false; }
-                release_stage(free_cnt, st, it, total, lane, fill);
                 if (++st == NSTAGE) { st = 0; par ^= 1; }
                 pc = pn;
             }
@@ -444,6 +446,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_gate_up_kernel(const Decod
             // This warp's partial tile joins the item's sums in shared memory (buffer b, counted arrivals). Every warp later
             // finishes its own 32 outputs of the item (see finish_item) once all sixteen partials are in.
             const int b = (p - p0) % NBUF;
+            {
+                volatile int* dc = cnt + NBUF + b;
+                const int need = CW * ((p - p0) / NBUF);                  // completions of the buffer's earlier items
+                if (*dc < need)
+                {
+                    const unsigned long long t0 = globaltimer_ns();
+                    while (*dc < need)
+                        if (globaltimer_ns() - t0 > 1000000000ull) { *abort_flag = 1; atomicOr(a.status, ST_WAIT_TIMEOUT); break; }
+                }
+                __threadfence_block();
+            }
             float* gb = gu + b * GU_FLOATS + mat * 512;
             #pragma unroll
             for (int ss = 0; ss < 4; ++ss)
@@ -462,6 +475,25 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_gate_up_kernel(const Decod
     __syncthreads();
 }
 
+// down's ring is shared by the block and refilled by whichever warp frees a stage last: after its last read of stage number `it` a warp bumps the
+// stage's counter, and the warp that brings it to CW issues the copies of stage number it + NSTAGE into the same slot.
+// No thread ever waits for a free slot.
+template <typename Fill>
+__device__ __forceinline__ void release_stage(int* free_cnt, uint32_t st, uint32_t it, uint32_t total, int lane, Fill fill)
+{
+    __syncwarp();
+    if (lane == 0)
+    {
+        __threadfence_block();
+        if (atomicAdd(free_cnt + st, 1) == CW - 1)
+        {
+            free_cnt[st] = 0;
+            __threadfence_block();
+            if (it + NSTAGE < total) fill(it + NSTAGE);
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------------------------
 // down
 template <bool GROUPED, bool Q8>
@@ -471,7 +503,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_down_kernel(const DecodeAr
     const uint32_t sbase = smem_u32(smem);
     const uint32_t ring = sbase + SmemLayout::ring, full0 = sbase + SmemLayout::bars;
     float* yacc = (float*) (smem + SmemLayout::gu);
-    int* free_cnt = (int*) (smem + SmemLayout::cnt) + NBUF;
+    int* free_cnt = (int*) (smem + SmemLayout::cnt) + 2 * NBUF;
     volatile int* abort_flag = (volatile int*) (smem + SmemLayout::flags);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0)
