@@ -175,6 +175,26 @@ def build_layer(dev, seed, experts, torch, moe):
     return tabs
 
 
+def make_graphed(step, xs, torch, moe, use_graph):
+    """Returns (run(batch_index), kernels launched per step). With graphs: one captured graph per input batch."""
+    l0 = moe.launch_count()
+    step(xs[0])
+    per_step = moe.launch_count() - l0
+    if not use_graph:
+        return (lambda b: step(xs[b])), per_step
+    graphs = []
+    try:
+        for x in xs:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                step(x)
+            graphs.append(g)
+    except Exception as e:                      # capture refused: run eagerly, say so
+        print(f"graph capture failed ({e}); running eagerly", file=sys.stderr)
+        return (lambda b: step(xs[b])), per_step
+    return (lambda b: graphs[b].replay()), per_step
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -218,23 +238,28 @@ def run_ours(args):
     for i in range(warmup):
         step(xs[i % NBATCH])
     torch.cuda.synchronize()
-    moe.set_profiling(True)
+    # One CUDA graph per input batch (the reference runs its decode forward as captured graphs too, runtime/core/exl3_vgraph.py):
+    # a step allocates nothing, does not synchronise and its launch shapes do not depend on the routing.
+    run_step, launches_per_step = make_graphed(step, xs, torch, moe, not args.no_graph)
+    for i in range(warmup):
+        run_step(i % NBATCH)
+    torch.cuda.synchronize()
     phase = np.zeros(3)
-    l0 = moe.launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as cs:
         torch.cuda.synchronize()
         ev0.record()
         for i in range(steps):
-            step(xs[i % NBATCH])
+            run_step(i % NBATCH)
         ev1.record()
         torch.cuda.synchronize()
         ms = ev0.elapsed_time(ev1)
         if len(cs.samples) < 5:           # very short runs: keep the same load going so the clock record is not empty
             t_end = time.time() + 0.4
             while time.time() < t_end:
-                step(xs[0]); torch.cuda.synchronize()
-    launches = moe.launch_count() - l0
+                run_step(0); torch.cuda.synchronize()
+    launches = launches_per_step * steps
+    moe.set_profiling(True)
     # phase durations: a second pass over the same steps, one readback per step (the readback waits for the step)
     for i in range(steps):
         step(xs[i % NBATCH])
@@ -266,7 +291,7 @@ def run_ours(args):
         "metric": METRIC, "value": ROWS / (ms_per_step * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int4 x fp16 -> fp32",
         "data": "synthetic",
-        "config": {"workload": WORKLOAD if E == 256 else WORKLOAD + f" [reduced to {E} experts]", "l2": "inputs larger than L2: ~2 GB of weights streamed per step, 8 input batches in a ring",
+        "config": {"workload": WORKLOAD if E == 256 else WORKLOAD + f" [reduced to {E} experts]", "launch": "eager" if args.no_graph else "cuda graph per input batch", "l2": "inputs larger than L2: ~2 GB of weights streamed per step, 8 input batches in a ring",
                    "distinct_experts_per_step": mean_d},
         "us_per_layer": ms_per_step * 1e3,
         "layer_hbm_gbs": layer_bytes / (ms_per_step * 1e-3) / 1e9,
@@ -358,6 +383,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-graph", action="store_true", help="launch the step's kernels eagerly instead of replaying CUDA graphs")
     ap.add_argument("--mode", default="decode", choices=["decode", "prefill"], help="decode (default, the headline) or prefill")
     ap.add_argument("--rows", type=int, default=8192, help="prefill rows")
     ap.add_argument("--zipf", type=float, default=1.1, help="prefill expert popularity exponent (0 = uniform)")

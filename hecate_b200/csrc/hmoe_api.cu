@@ -121,10 +121,12 @@ int hmoe_set_profiling(int on) { return decode_set_profiling(on); }
 int hmoe_decode_phase_times(float* ms3) { return ms3 ? decode_phase_times(ms3) : fail(HMOE_E_ARG, "hmoe_decode_phase_times: null pointer"); }
 
 int hmoe_decode_ep(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
-                   int act_quant, float* y, void* ws, size_t ws_bytes, int shared_mod, int shared_rem, void* stream)
+                   int act_quant, float* y, void* ws, size_t ws_bytes, int shared_mod, int shared_rem, uint32_t* gen, size_t slot_floats,
+                   void* stream)
 {
     if (!layer) return fail(HMOE_E_ARG, "hmoe_decode_ep: null layer");
-    return decode_launch(layer, x, x_dtype, sel, rw, R, lo, n_local, act_quant, y, ws, ws_bytes, (cudaStream_t) stream, shared_mod, shared_rem);
+    return decode_launch(layer, x, x_dtype, sel, rw, R, lo, n_local, act_quant, y, ws, ws_bytes, (cudaStream_t) stream, shared_mod, shared_rem,
+                         gen, slot_floats);
 }
 
 int hmoe_combine(float* f, const float* o, float* y, int64_t n, const float* o2, void* stream)

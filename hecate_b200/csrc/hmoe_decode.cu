@@ -51,7 +51,7 @@ struct SmemLayout
 // prepare
 __global__ void __launch_bounds__(256) decode_prepare_kernel(const void* __restrict__ x, int x_bf16, const int64_t* __restrict__ sel,
     const __half* __restrict__ rw, int R, int H, int topk, int lo, int n_local, int has_shared, int act_quant,
-    __half* __restrict__ xf, float* __restrict__ xscale, Route* __restrict__ route, int sh_mod, int sh_rem)
+    __half* __restrict__ xf, float* __restrict__ xscale, Route* __restrict__ route, int sh_mod, int sh_rem, unsigned* gen_bump)
 {
     const int tid = threadIdx.x;
     if ((int) blockIdx.x < R)
@@ -159,6 +159,7 @@ __global__ void __launch_bounds__(256) decode_prepare_kernel(const void* __restr
         int t = 0;
         for (int j = 0; j < ns; ++j) { s_tile0[j] = (short) t; t += (s_n[j] + 7) / 8; }
         route->m = m; route->ntiles = t; route->pad[0] = route->pad[1] = 0;
+        if (gen_bump) *gen_bump += 1;          // expert-parallel step counter: selects the partial slot and the combine's generation
     }
     __syncthreads();
     for (int j = tid; j < ns; j += blockDim.x)
@@ -195,7 +196,8 @@ struct DecodeArgs
     const float* xscale;   // [R][H/32] (Q8)
     __half* act;           // [tiles][8][I] gate_up output = down input
     float* ascale;         // [tiles][8][I/32] (Q8)
-    float* y;              // [R][H]
+    float* y;              // [R][H] (expert-parallel: base of two slots, the step's slot is chosen by *gen_ptr & 1)
+    const unsigned* gen_ptr; size_t slot_stride;
     unsigned* status;
 };
 
@@ -503,6 +505,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_down_kernel(const DecodeAr
     const uint32_t sbase = smem_u32(smem);
     const uint32_t ring = sbase + SmemLayout::ring, full0 = sbase + SmemLayout::bars;
     float* yacc = (float*) (smem + SmemLayout::gu);
+    float* const yout = a.y + (a.gen_ptr ? (size_t) (*a.gen_ptr & 1u) * a.slot_stride : 0);
     int* free_cnt = (int*) (smem + SmemLayout::cnt) + 2 * NBUF;
     volatile int* abort_flag = (volatile int*) (smem + SmemLayout::flags);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -609,7 +612,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_down_kernel(const DecodeAr
                 for (int i = threadIdx.x; i < R * 64; i += NTHREADS)
                 {
                     const float v = (yacc[i] + yacc[YACC_FLOATS + i]) + (yacc[2 * YACC_FLOATS + i] + yacc[3 * YACC_FLOATS + i]);
-                    if (v != 0.f) atomicAdd(a.y + (size_t) (i >> 6) * a.H + cur.gr * 64 + (i & 63), v);
+                    if (v != 0.f) atomicAdd(yout + (size_t) (i >> 6) * a.H + cur.gr * 64 + (i & 63), v);
                     yacc[i] = yacc[YACC_FLOATS + i] = yacc[2 * YACC_FLOATS + i] = yacc[3 * YACC_FLOATS + i] = 0.f;
                 }
                 __syncthreads();
@@ -682,7 +685,7 @@ static void launch_pair(int grid, const DecodeArgs& a, int R, cudaStream_t st, b
 }
 
 int decode_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
-                  int act_quant, float* y, void* ws, size_t ws_bytes, cudaStream_t st, int sh_mod, int sh_rem)
+                  int act_quant, float* y, void* ws, size_t ws_bytes, cudaStream_t st, int sh_mod, int sh_rem, unsigned* gen_ptr, size_t slot_stride)
 {
     if (sh_mod < 1 || sh_rem < 0 || sh_rem >= sh_mod) return fail(HMOE_E_ARG, "hmoe_decode: shared-row split must satisfy 0 <= rem < mod");
     const int H = L->H, I = L->I;
@@ -711,12 +714,13 @@ int decode_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t
     const int has_shared = L->sh_gate_w != nullptr;
     if (g_prof) cudaEventRecord(g_ev[0], st);
     decode_prepare_kernel<<<R + 1, 256, 0, st>>>(x, x_dtype == HMOE_BF16, sel, (const __half*) rw, R, H, L->topk, lo, n_local, has_shared,
-                                                 act_quant, xf, xscale, route, sh_mod, sh_rem);
+                                                 act_quant, xf, xscale, route, sh_mod, sh_rem, gen_ptr);
     DecodeArgs a;
     a.H = H; a.I = I;
     a.gate_w = L->gate_w; a.up_w = L->up_w; a.down_w = L->down_w; a.gate_s = L->gate_s; a.up_s = L->up_s; a.down_s = L->down_s;
     a.sh_gw = L->sh_gate_w; a.sh_uw = L->sh_up_w; a.sh_dw = L->sh_down_w; a.sh_gs = L->sh_gate_s; a.sh_us = L->sh_up_s; a.sh_ds = L->sh_down_s;
     a.route = route; a.xf = xf; a.xscale = xscale; a.act = act; a.ascale = ascale; a.y = y; a.status = status;
+    a.gen_ptr = gen_ptr; a.slot_stride = slot_stride;
     const int grid = g_sms;
     const int v = (L->group ? 2 : 0) + (act_quant ? 1 : 0);
     if (v == 0) launch_pair<false, false>(grid, a, R, st, first[0]);

@@ -6,6 +6,8 @@
 // Here the bands are the GPUs of one box: rank r owns experts [r E / W, (r + 1) E / W), every rank sees the step's <= 16 rows
 // (decode "dispatch" = the rows are replicated, each rank filters by expert id), computes its partial with the decode kernels
 // into its slot of a symmetric buffer, and the combine is one kernel per rank that
+// The step number (generation) lives in device memory: the step's prepare kernel bumps it, the down kernel picks the slot
+// gen % 2 and the combine reads it, so a step has no host-side state and can be captured in a CUDA graph.
 //   1. raises this rank's generation flag in every peer's memory (st.release.sys over NVLink),
 //   2. waits, bounded, until every peer's flag in local memory has reached the generation,
 //   3. reads every rank's partial (peer loads) and adds them to the layer output in rank order, the same order on every
@@ -41,10 +43,11 @@ __device__ __forceinline__ float4 ld_peer(const float4* p)
     return v;
 }
 
-__global__ void __launch_bounds__(256) ep_combine_kernel(const EpArgs a, unsigned gen, float* __restrict__ f, int n, size_t slot_floats,
-                                                         unsigned* __restrict__ status)
+__global__ void __launch_bounds__(256) ep_combine_kernel(const EpArgs a, const unsigned* __restrict__ gen_ptr, float* __restrict__ f, int n,
+                                                         size_t slot_floats, unsigned* __restrict__ status)
 {
     __shared__ int ok_sh;
+    const unsigned gen = *gen_ptr;            // bumped by this step's prepare kernel, stable for the rest of the step
     const int parity = gen & 1;
     if (blockIdx.x == 0 && threadIdx.x < a.world) st_release_sys(a.flags[threadIdx.x] + a.rank, gen);
     if (threadIdx.x == 0)
@@ -73,12 +76,12 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(const EpArgs a, unsigne
 
 }  // namespace
 
-int ep_combine_launch(int rank, int world, void* const* slots, void* const* flags, unsigned gen, float* f, int rows, int H, size_t slot_floats,
+int ep_combine_launch(int rank, int world, void* const* slots, void* const* flags, const unsigned* gen, float* f, int rows, int H, size_t slot_floats,
                       unsigned* status, cudaStream_t st)
 {
     if (world < 1 || world > 8 || rank < 0 || rank >= world) return fail(HMOE_E_ARG, "hmoe_ep_combine: world must be 1..8");
     const int n = rows * H;
-    if (!f || !slots || !flags || !status || n <= 0 || n % 4 || (size_t) n > slot_floats) return fail(HMOE_E_ARG, "hmoe_ep_combine: sizes");
+    if (!f || !slots || !flags || !status || !gen || n <= 0 || n % 4 || (size_t) n > slot_floats) return fail(HMOE_E_ARG, "hmoe_ep_combine: sizes");
     EpArgs a;
     a.rank = rank; a.world = world;
     for (int p = 0; p < 8; ++p) { a.slots[p] = p < world ? (float*) slots[p] : nullptr; a.flags[p] = p < world ? (unsigned*) flags[p] : nullptr; }
@@ -129,7 +132,7 @@ int hmoe_ep_open(const unsigned char* handle64, void** ptr)
 }
 int hmoe_ep_close(void* ptr) { return cudaIpcCloseMemHandle(ptr) == cudaSuccess ? HMOE_OK : fail(HMOE_E_CUDA, "hmoe_ep_close failed"); }
 
-int hmoe_ep_combine(int rank, int world, void* const* slots, void* const* flags, uint32_t gen, float* f, int rows, int H, size_t slot_floats,
+int hmoe_ep_combine(int rank, int world, void* const* slots, void* const* flags, const uint32_t* gen, float* f, int rows, int H, size_t slot_floats,
                     uint32_t* status, void* stream)
 {
     return ep_combine_launch(rank, world, slots, flags, gen, f, rows, H, slot_floats, status, (cudaStream_t) stream);

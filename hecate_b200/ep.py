@@ -36,7 +36,7 @@ class PeerBuffers:
         import torch
         self.rank, self.world, self.H = rank, world, H
         self.slot_floats = MAX_ROWS * H
-        self.bytes = 2 * self.slot_floats * 4 + 256
+        self.bytes = 2 * self.slot_floats * 4 + 512          # two slots, `world` flags (256 B), the generation word (256 B)
         p = C.c_void_p()
         check(lib().hmoe_ep_alloc(C.c_size_t(self.bytes), C.byref(p)))
         self.own = p.value
@@ -55,11 +55,8 @@ class PeerBuffers:
         self.slots = (C.c_void_p * world)(*self.base)
         self.flags = (C.c_void_p * world)(*[b + 2 * self.slot_floats * 4 for b in self.base])
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
-        self.gen = 0
+        self.gen_ptr = self.own + 2 * self.slot_floats * 4 + 256
         dist.barrier()
-
-    def slot_ptr(self, gen):
-        return self.own + (gen & 1) * self.slot_floats * 4
 
     def close(self):
         for r, b in enumerate(self.base):
@@ -89,18 +86,17 @@ class EpDecoder:
         st = C.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)
         pl = self.plan
         if self.use_peer:
-            self.peer.gen += 1
-            g = self.peer.gen
             check(lib().hmoe_decode_ep(C.byref(self.struct), vp(x), C.c_int(moe._dt(x)), vp(sel), vp(rw), C.c_int(R), C.c_int(pl["lo"]),
-                                       C.c_int(pl["n_local"]), C.c_int(0), C.c_void_p(self.peer.slot_ptr(g)), vp(self.ws),
-                                       C.c_size_t(self.ws.numel()), C.c_int(pl["shared_mod"]), C.c_int(pl["shared_rem"]), st))
-            check(lib().hmoe_ep_combine(C.c_int(self.rank), C.c_int(self.world), self.peer.slots, self.peer.flags, C.c_uint32(g), vp(f),
-                                        C.c_int(R), C.c_int(self.tabs.H), C.c_size_t(self.peer.slot_floats), vp(self.peer.status), st))
+                                       C.c_int(pl["n_local"]), C.c_int(0), C.c_void_p(self.peer.own), vp(self.ws),
+                                       C.c_size_t(self.ws.numel()), C.c_int(pl["shared_mod"]), C.c_int(pl["shared_rem"]),
+                                       C.c_void_p(self.peer.gen_ptr), C.c_size_t(self.peer.slot_floats), st))
+            check(lib().hmoe_ep_combine(C.c_int(self.rank), C.c_int(self.world), self.peer.slots, self.peer.flags, C.c_void_p(self.peer.gen_ptr),
+                                        vp(f), C.c_int(R), C.c_int(self.tabs.H), C.c_size_t(self.peer.slot_floats), vp(self.peer.status), st))
         else:
             y = self.y[:R]
             check(lib().hmoe_decode_ep(C.byref(self.struct), vp(x), C.c_int(moe._dt(x)), vp(sel), vp(rw), C.c_int(R), C.c_int(pl["lo"]),
                                        C.c_int(pl["n_local"]), C.c_int(0), vp(y), vp(self.ws), C.c_size_t(self.ws.numel()),
-                                       C.c_int(pl["shared_mod"]), C.c_int(pl["shared_rem"]), st))
+                                       C.c_int(pl["shared_mod"]), C.c_int(pl["shared_rem"]), None, C.c_size_t(0), st))
             if self.world > 1:
                 self.dist.all_reduce(y)
             moe.moe4_combine(f, 0, y, R, 0)
@@ -146,18 +142,21 @@ def bench_decode(args, world, rank, dev):
         for i in range(warmup):
             step(xs[i % NBATCH])
         torch.cuda.synchronize(); dist.barrier()
-        l0 = moe.launch_count()
+        run_step, per_step = B.make_graphed(step, xs, torch, moe, (not args.no_graph) and mode == "peer")
+        for i in range(warmup):
+            run_step(i % NBATCH)
+        torch.cuda.synchronize(); dist.barrier()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with B.ClockSampler(dev.index) as cs:
             torch.cuda.synchronize(); dist.barrier()
             ev0.record()
             for i in range(steps):
-                step(xs[i % NBATCH])
+                run_step(i % NBATCH)
             ev1.record()
             torch.cuda.synchronize(); dist.barrier()
         ms = torch.tensor([ev0.elapsed_time(ev1) / steps], device=dev)
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        launches = moe.launch_count() - l0
+        launches = per_step * steps
         t0 = time.perf_counter()
         n2 = min(steps, 200)
         for i in range(n2):

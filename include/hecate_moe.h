@@ -67,20 +67,23 @@ int hmoe_decode(const hmoe_layer* layer, const void* x, int x_dtype, const int64
  * over unlike processors that all receive every row and ignore foreign ids, runtime/tier/tier_split.py:3-11, moe4.cu:93, and
  * adds their fp32 partials in a fixed order, moe4.cu:702-717; these entry points do the same over NVLink peer memory).
  * hmoe_decode_ep = hmoe_decode where the shared expert only takes rows r with r % shared_mod == shared_rem (each rank serves
- * its share of the rows; experts are split by lo / n_local). hmoe_ep_alloc / export / open / close manage the symmetric
- * buffers (cudaMalloc + CUDA IPC; set-up time only). hmoe_ep_combine(rank, world, slots, flags, gen, f, rows, H, slot_floats,
- * status, stream): slots[p] / flags[p] are rank p's buffers as seen from this process (own pointers for p == rank): two fp32
- * partial slots of slot_floats each (this step's partial in slot gen % 2, zero-filled initially) and `world` uint32 flags.
- * It publishes generation gen (1, 2, 3, ... one per step, same on all ranks), waits at most 2 s for all peers, adds all
- * ranks' partials to f in rank order and clears the other slot. A wait that gives up sets bit 0 of *status (device word). */
+ * its share of the rows; experts are split by lo / n_local), y is the base of this rank's two partial slots (slot_floats
+ * apart) and gen a device word: the call adds 1 to *gen and writes its partial into slot *gen % 2. hmoe_ep_alloc / export /
+ * open / close manage the symmetric buffers (cudaMalloc + CUDA IPC; set-up time only). hmoe_ep_combine(rank, world, slots,
+ * flags, gen, f, rows, H, slot_floats, status, stream): slots[p] / flags[p] are rank p's buffers as seen from this process (own
+ * pointers for p == rank): two zero-initialised fp32 slots and `world` uint32 flags. It reads the generation g from *gen,
+ * publishes it to every peer, waits at most 2 s until all peers have published g, adds all ranks' partials of slot g % 2 to f
+ * in rank order and clears the other slot. All ranks must make the same sequence of steps. A wait that gives up sets bit 0 of
+ * *status (device word). Neither call keeps host-side state, so a step can be captured in a CUDA graph. */
 int hmoe_decode_ep(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
-                   int act_quant, float* y, void* ws, size_t ws_bytes, int shared_mod, int shared_rem, void* stream);
+                   int act_quant, float* y, void* ws, size_t ws_bytes, int shared_mod, int shared_rem, uint32_t* gen, size_t slot_floats,
+                   void* stream);
 int hmoe_ep_alloc(size_t bytes, void** ptr);
 int hmoe_ep_free(void* ptr);
 int hmoe_ep_export(void* ptr, unsigned char* handle64);
 int hmoe_ep_open(const unsigned char* handle64, void** ptr);
 int hmoe_ep_close(void* ptr);
-int hmoe_ep_combine(int rank, int world, void* const* slots, void* const* flags, uint32_t gen, float* f, int rows, int H, size_t slot_floats,
+int hmoe_ep_combine(int rank, int world, void* const* slots, void* const* flags, const uint32_t* gen, float* f, int rows, int H, size_t slot_floats,
                     uint32_t* status, void* stream);
 
 /* Prefill permutation on the device: replaces the host-side code of runtime/tier/tier_split.py:404-412,433-455 (stable argsort

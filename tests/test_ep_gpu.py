@@ -27,7 +27,8 @@ def test_combine_wait_is_bounded_and_reported():
     flags = (C.c_void_p * 2)(own.data_ptr() + 2 * slot_floats * 4, dead.data_ptr() + 2 * slot_floats * 4)
     f = torch.zeros(rows, H, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
-    rc = lib().hmoe_ep_combine(C.c_int(0), C.c_int(2), slots, flags, C.c_uint32(2), vp(f), C.c_int(rows), C.c_int(H), C.c_size_t(slot_floats),
+    gen = torch.full((1,), 2, dtype=torch.int32, device=dev)               # the step counter lives in device memory
+    rc = lib().hmoe_ep_combine(C.c_int(0), C.c_int(2), slots, flags, vp(gen), vp(f), C.c_int(rows), C.c_int(H), C.c_size_t(slot_floats),
                                vp(status), C.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
     assert rc == 0
     torch.cuda.synchronize()
@@ -37,7 +38,7 @@ def test_combine_wait_is_bounded_and_reported():
     # the same call with the peer's flag raised completes and sums both slots (generation 2 -> slot 0)
     own_flags = own[2 * slot_floats:].view(torch.int32); own_flags[1] = 2
     dead[:rows * H] = 0.5
-    rc = lib().hmoe_ep_combine(C.c_int(0), C.c_int(2), slots, flags, C.c_uint32(2), vp(f), C.c_int(rows), C.c_int(H), C.c_size_t(slot_floats),
+    rc = lib().hmoe_ep_combine(C.c_int(0), C.c_int(2), slots, flags, vp(gen), vp(f), C.c_int(rows), C.c_int(H), C.c_size_t(slot_floats),
                                vp(status), C.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
     torch.cuda.synchronize()
     assert rc == 0 and int(status.item()) == 0
