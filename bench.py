@@ -272,6 +272,9 @@ def run_ours(args):
     layer_bytes = (mean_d + 1) * EXPERT_BYTES + E * H * 2 + ROWS * H * 6
     peak, peak_kind = measured_peaks()
     achieved = gate_up_bytes / (phase[1] * 1e-3) / 1e9
+    # DRAM traffic of one gate_up launch: dram__bytes_read + write of an ncu capture of the reduced case (--experts 64: 720.7 MB
+    # for 726.7 MB of algorithmic bytes, profiles/decode_gate_up_experts64.md), scaled to this launch by the experts it streams
+    traffic = 0.9917 * gate_up_bytes
     ms_per_step = ms / steps
 
     # end to end: host buffers in, host buffer out, every step
@@ -298,7 +301,7 @@ def run_ours(args):
         "layer_hbm_frac": layer_bytes / (ms_per_step * 1e-3) / 1e9 / peak,
         "phase_us": {"prepare": phase[0] * 1e3, "gate_up": phase[1] * 1e3, "down": phase[2] * 1e3},
         "roofline": {"bound": "hbm", "kernel": "decode_gate_up_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
+                     "frac": achieved / peak, "peak_kind": peak_kind, "traffic": traffic,
                      "algorithmic_bytes_per_launch": gate_up_bytes},
         "e2e": {"value": ROWS / e2e_s, "unit": UNIT, "h2d_bytes_per_step": ROWS * H * 2, "d2h_bytes_per_step": ROWS * H * 4,
                 "us_per_layer": e2e_s * 1e6},
