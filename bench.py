@@ -323,6 +323,12 @@ def run_prefill(args):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+        from hecate_b200 import ep
+        return ep.bench_prefill(args, world, int(os.environ.get("RANK", "0")), dev)
     E, R = args.experts, args.rows
     steps, warmup = min(args.steps, 200), max(3, min(args.warmup, 10))
     tabs = build_layer(dev, 0, list(range(E)), torch, moe)

@@ -108,6 +108,20 @@ int hmoe_prefill(const hmoe_layer* layer, const void* x, int x_dtype, const int6
     if (!layer) return fail(HMOE_E_ARG, "hmoe_prefill: null layer");
     return prefill_launch(layer, x, x_dtype, sel, rw, R, lo, n_local, act_quant, out, ws, ws_bytes, (cudaStream_t) stream);
 }
+int hmoe_prefill_ep(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
+                    int act_quant, float* out, void* ws, size_t ws_bytes, int shared_row0, int shared_rows, void* stream)
+{
+    if (!layer) return fail(HMOE_E_ARG, "hmoe_prefill_ep: null layer");
+    if (shared_rows < 0) return fail(HMOE_E_ARG, "hmoe_prefill_ep: shared_rows must be >= 0");
+    return prefill_launch(layer, x, x_dtype, sel, rw, R, lo, n_local, act_quant, out, ws, ws_bytes, (cudaStream_t) stream, shared_row0, shared_rows);
+}
+size_t hmoe_prefill_sorted_ws_bytes(int npos, int H, int I) { return prefill_sorted_ws_bytes(npos, H, I); }
+int hmoe_prefill_sorted(const hmoe_layer* layer, const void* x, int x_dtype, const int32_t* tok, const float* wt, const int32_t* rbt, int nrb,
+                        int npos, int n_local, int act_quant, float* out, void* ws, size_t ws_bytes, void* stream)
+{
+    if (!layer) return fail(HMOE_E_ARG, "hmoe_prefill_sorted: null layer");
+    return prefill_sorted_launch(layer, x, x_dtype, tok, wt, rbt, nrb, npos, n_local, act_quant, out, ws, ws_bytes, (cudaStream_t) stream);
+}
 size_t hmoe_permute_ws_bytes(int R, int topk, int n_local) { return permute_ws_bytes(R, topk, n_local); }
 int hmoe_permute(const int64_t* sel, const void* rw, int R, int topk, int lo, int n_local, int shared_rows, int bm, int balance,
                  int32_t* order, int32_t* tok, int32_t* eid, float* wt, int32_t* counts, int32_t* rbt, int32_t* plan, void* ws, size_t ws_bytes,

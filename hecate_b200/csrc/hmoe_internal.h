@@ -25,7 +25,10 @@ int router_launch(const void* x, int x_dtype, const void* wt, int w_dtype, const
 
 size_t prefill_ws_bytes(int R, int topk, int n_local, int H, int I);
 int prefill_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
-                   int act_quant, float* out, void* ws, size_t ws_bytes, cudaStream_t st);
+                   int act_quant, float* out, void* ws, size_t ws_bytes, cudaStream_t st, int shared_row0 = 0, int shared_rows = -1);
+size_t prefill_sorted_ws_bytes(int npos, int H, int I);
+int prefill_sorted_launch(const hmoe_layer* L, const void* x, int x_dtype, const int32_t* tok, const float* wt, const int32_t* rbt, int nrb,
+                          int npos, int n_local, int act_quant, float* out, void* ws, size_t ws_bytes, cudaStream_t st);
 size_t permute_ws_bytes(int R, int topk, int n_local);
 int permute_launch(const int64_t* sel, const void* rw, int R, int topk, int lo, int n_local, int shared_rows, int bm, int balance,
                    int32_t* order, int32_t* tok, int32_t* eid, float* wt, int32_t* counts, int32_t* rbt, int32_t* plan2, void* ws, size_t ws_bytes,

@@ -102,7 +102,7 @@ __global__ void __launch_bounds__(256) permute_scan_kernel(int* __restrict__ blo
 
 // stable scatter: pick i goes to offs[e] + (picks of e in earlier chunks) + (picks of e earlier in this chunk)
 __global__ void __launch_bounds__(32) permute_scatter_kernel(const int64_t* __restrict__ sel, const __half* __restrict__ rw, int P, int topk,
-    int lo, int n_local, int shared_rows, const int* __restrict__ block_hist, const int* __restrict__ offs, int nblocks,
+    int lo, int n_local, int shared_rows, int shared_row0, const int* __restrict__ block_hist, const int* __restrict__ offs, int nblocks,
     int* __restrict__ order, int* __restrict__ tok, int* __restrict__ eid, float* __restrict__ wt)
 {
     const int lane = threadIdx.x;
@@ -110,7 +110,7 @@ __global__ void __launch_bounds__(32) permute_scatter_kernel(const int64_t* __re
     {
         // the shared expert's rows: every row once, in order, weight 1
         const int base = ((int) blockIdx.x - nblocks) * CHUNK, o = offs[n_local];
-        for (int r = base + lane; r < base + CHUNK && r < shared_rows; r += 32) { tok[o + r] = r; eid[o + r] = n_local; wt[o + r] = 1.f; if (order) order[o + r] = -1; }
+        for (int r = base + lane; r < base + CHUNK && r < shared_rows; r += 32) { tok[o + r] = shared_row0 + r; eid[o + r] = n_local; wt[o + r] = 1.f; if (order) order[o + r] = -1; }
         return;
     }
     __shared__ int seen[256];
@@ -516,14 +516,14 @@ WsLayout ws_layout(int R, int topk, int n_local, int H, int I, int bm)
     return w;
 }
 
-int run_permute(const int64_t* sel, const void* rw, int R, int topk, int lo, int n_local, int shared_rows, int bm, int balance,
+int run_permute(const int64_t* sel, const void* rw, int R, int topk, int lo, int n_local, int shared_rows, int shared_row0, int bm, int balance,
                 int* counts, int* offs, int* hist, int nblocks, int* order, int* tok, int* eid, float* wt, int* rbt, Plan* plan, cudaStream_t st)
 {
     const int P = R * topk;
     permute_hist_kernel<<<nblocks, 32, 0, st>>>(sel, P, lo, n_local, hist);
     permute_scan_kernel<<<1, 256, 0, st>>>(hist, nblocks, n_local, shared_rows, bm, balance, counts, offs, rbt, plan);
     const int sb = shared_rows > 0 ? (shared_rows + CHUNK - 1) / CHUNK : 0;
-    permute_scatter_kernel<<<nblocks + sb, 32, 0, st>>>(sel, (const __half*) rw, P, topk, lo, n_local, shared_rows, hist, offs, nblocks, order, tok, eid, wt);
+    permute_scatter_kernel<<<nblocks + sb, 32, 0, st>>>(sel, (const __half*) rw, P, topk, lo, n_local, shared_rows, shared_row0, hist, offs, nblocks, order, tok, eid, wt);
     count_launches(3);
     return cudaGetLastError() == cudaSuccess ? HMOE_OK : fail(HMOE_E_CUDA, "hmoe_permute: launch failed");
 }
@@ -531,6 +531,57 @@ int run_permute(const int64_t* sel, const void* rw, int R, int topk, int lo, int
 }  // namespace
 
 size_t prefill_ws_bytes(int R, int topk, int n_local, int H, int I) { return ws_layout(R, topk, n_local, H, I, TN).total; }
+
+namespace {
+__global__ void set_plan_kernel(Plan* plan, int total, int nrb) { plan->total = total; plan->nrb = nrb; plan->pad[0] = plan->pad[1] = 0; }
+}
+
+// The reference's calling convention (moe4t.forward, runtime/tier/moe4/moe4t.cu:498-524): the caller has already sorted the
+// picks by expert (tok, wt in that order) and built the row-block table; npos picks, nrb row blocks of <= 256 picks.
+size_t prefill_sorted_ws_bytes(int npos, int H, int I) { return 512 + up256((size_t) npos * H * 2) + up256((size_t) npos * I * 2); }
+
+int prefill_sorted_launch(const hmoe_layer* L, const void* x, int x_dtype, const int32_t* tok, const float* wt, const int32_t* rbt, int nrb,
+                          int npos, int n_local, int act_quant, float* out, void* ws, size_t ws_bytes, cudaStream_t st)
+{
+    const int H = L->H, I = L->I;
+    if (npos < 0 || nrb < 0) return fail(HMOE_E_ARG, "hmoe_prefill_sorted: sizes");
+    if (npos == 0 || nrb == 0) return HMOE_OK;
+    if (H % 128 || I % 128 || H < 128 || I < 128) return fail(HMOE_E_ARG, "hmoe_prefill_sorted: H and I must be multiples of 128");
+    if (!(L->group == 0 && L->scale_dtype == HMOE_F32) && !(L->group == 128 && L->scale_dtype == HMOE_BF16))
+        return fail(HMOE_E_ARG, "hmoe_prefill_sorted: scales must be fp32 per row (group 0) or bf16 per 128 columns");
+    if (x_dtype != HMOE_F16 && x_dtype != HMOE_BF16) return fail(HMOE_E_ARG, "hmoe_prefill_sorted: x must be fp16 or bf16");
+    if (!x || !tok || !wt || !rbt || !out || !ws) return fail(HMOE_E_ARG, "hmoe_prefill_sorted: null pointer");
+    if (ws_bytes < prefill_sorted_ws_bytes(npos, H, I)) return fail(HMOE_E_WS, "hmoe_prefill_sorted: workspace too small");
+    static int sms = 0;
+    if (!sms)
+    {
+        int dev = 0; cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        cudaFuncSetAttribute(prefill_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfSmem<2>::total);
+        cudaFuncSetAttribute(prefill_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfSmem<1>::total);
+    }
+    char* b = (char*) ws;
+    unsigned* status = (unsigned*) b;
+    Plan* plan = (Plan*) (b + 256);
+    __half* xg = (__half*) (b + 512);
+    __half* act = (__half*) (b + 512 + up256((size_t) npos * H * 2));
+    set_plan_kernel<<<1, 1, 0, st>>>(plan, npos, nrb);
+    gather_kernel<<<npos, 192, 0, st>>>(x, x_dtype == HMOE_BF16, tok, plan, H, act_quant, xg);
+    CUtensorMap mx, ma;
+    if (!make_map(&mx, xg, H, (size_t) npos) || !make_map(&ma, act, I, (size_t) npos)) return fail(HMOE_E_CUDA, "hmoe_prefill_sorted: cuTensorMapEncodeTiled failed");
+    GemmArgs g;
+    g.grouped = L->group != 0; g.act_quant = act_quant; g.n_local = n_local;
+    g.plan = plan; g.rbt = rbt; g.tok = tok; g.wt = wt; g.act = act; g.out = out; g.status = status;
+    g.K = H; g.N = I; g.w0 = L->gate_w; g.w1 = L->up_w; g.s0 = L->gate_s; g.s1 = L->up_s;
+    g.sh_w0 = L->sh_gate_w; g.sh_w1 = L->sh_up_w; g.sh_s0 = L->sh_gate_s; g.sh_s1 = L->sh_up_s;
+    prefill_gemm_kernel<2><<<sms, PF_THREADS, PfSmem<2>::total, st>>>(mx, g);
+    g.K = I; g.N = H; g.w0 = L->down_w; g.w1 = nullptr; g.s0 = L->down_s; g.s1 = nullptr;
+    g.sh_w0 = L->sh_down_w; g.sh_w1 = nullptr; g.sh_s0 = L->sh_down_s; g.sh_s1 = nullptr;
+    prefill_gemm_kernel<1><<<sms, PF_THREADS, PfSmem<1>::total, st>>>(ma, g);
+    count_launches(4);
+    const cudaError_t err = cudaGetLastError();
+    return err == cudaSuccess ? HMOE_OK : fail(HMOE_E_CUDA, cudaGetErrorString(err));
+}
 
 int permute_launch(const int64_t* sel, const void* rw, int R, int topk, int lo, int n_local, int shared_rows, int bm, int balance,
                    int32_t* order, int32_t* tok, int32_t* eid, float* wt, int32_t* counts, int32_t* rbt, int32_t* plan2, void* ws, size_t ws_bytes,
@@ -544,7 +595,7 @@ int permute_launch(const int64_t* sel, const void* rw, int R, int topk, int lo, 
     if (ws_bytes < need) return fail(HMOE_E_WS, "hmoe_permute: workspace too small");
     int* hist = (int*) ws;
     int* offs = (int*) ((char*) ws + up256((size_t) nblocks * n_local * 4));
-    return run_permute(sel, rw, R, topk, lo, n_local, shared_rows, bm, balance, counts, offs, hist, nblocks, order, tok, eid, wt, rbt, (Plan*) plan2, st);
+    return run_permute(sel, rw, R, topk, lo, n_local, shared_rows, 0, bm, balance, counts, offs, hist, nblocks, order, tok, eid, wt, rbt, (Plan*) plan2, st);
 }
 
 size_t permute_ws_bytes(int R, int topk, int n_local)
@@ -555,8 +606,10 @@ size_t permute_ws_bytes(int R, int topk, int n_local)
 }
 
 int prefill_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
-                   int act_quant, float* out, void* ws, size_t ws_bytes, cudaStream_t st)
+                   int act_quant, float* out, void* ws, size_t ws_bytes, cudaStream_t st, int shared_row0, int shared_rows)
 {
+    if (shared_rows < 0) { shared_row0 = 0; shared_rows = R; }          // default: the shared expert takes every row
+    if (shared_row0 < 0 || shared_row0 + shared_rows > R) return fail(HMOE_E_ARG, "hmoe_prefill: shared row range outside the rows");
     const int H = L->H, I = L->I;
     if (R < 1) return fail(HMOE_E_ARG, "hmoe_prefill: rows must be >= 1");
     if (L->topk < 1 || L->topk > TOPK_MAX) return fail(HMOE_E_ARG, "hmoe_prefill: topk must be 1..8");
@@ -586,7 +639,8 @@ int prefill_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_
     int* rbt = (int*) (b + w.rbt);
     __half* xg = (__half*) (b + w.xg); __half* act = (__half*) (b + w.act);
     const int has_shared = L->sh_gate_w != nullptr;
-    int rc = run_permute(sel, rw, R, L->topk, lo, n_local, has_shared ? R : 0, TN, 1, counts, offs, hist, w.nblocks, order, tok, eid, wt, rbt, plan, st);
+    int rc = run_permute(sel, rw, R, L->topk, lo, n_local, has_shared ? shared_rows : 0, shared_row0, TN, 1, counts, offs, hist, w.nblocks, order, tok, eid, wt,
+                         rbt, plan, st);
     if (rc) return rc;
     gather_kernel<<<w.rows_cap, 192, 0, st>>>(x, x_dtype == HMOE_BF16, tok, plan, H, act_quant, xg);
     CUtensorMap mx, ma;

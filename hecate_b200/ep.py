@@ -111,6 +111,100 @@ class EpDecoder:
         return s
 
 
+class EpPrefill:
+    """Expert-parallel prefill, collectives by NCCL: the ranks' token slices are all-gathered (dispatch), every rank runs the
+    grouped GEMMs for its experts over all tokens (ids outside [lo, lo + n_local) are dropped by the permutation) plus the
+    shared expert for its own tokens, and a reduce-scatter returns each rank its tokens' sums (combine)."""
+
+    def __init__(self, rank, world, tables, n_experts, rows_per_rank, device, dist):
+        import torch
+        self.rank, self.world, self.tabs, self.dev, self.dist, self.rpr = rank, world, tables, device, dist, rows_per_rank
+        self.plan = shard_plan(rank, world, n_experts)
+        R = rows_per_rank * world
+        self.R = R
+        self.ws = moe.prefill_workspace(R, tables.topk, tables.n, tables.H, tables.I, device)
+        self.x_all = torch.empty(R, tables.H, dtype=torch.bfloat16, device=device)
+        self.sel_all = torch.empty(R, tables.topk, dtype=torch.int64, device=device)
+        self.rw_all = torch.empty(R, tables.topk, dtype=torch.float16, device=device)
+        self.partial = torch.empty(R, tables.H, dtype=torch.float32, device=device)
+        self.struct = tables.struct()
+
+    def step(self, x, sel, rw, out):
+        """x bf16 [R/W][H], sel, rw: this rank's tokens; out fp32 [R/W][H] receives their MoE output."""
+        import torch
+        d, pl = self.dist, self.plan
+        if self.world > 1:
+            d.all_gather_into_tensor(self.x_all, x); d.all_gather_into_tensor(self.sel_all, sel); d.all_gather_into_tensor(self.rw_all, rw)
+        else:
+            self.x_all.copy_(x); self.sel_all.copy_(sel); self.rw_all.copy_(rw)
+        self.partial.zero_()
+        st = C.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)
+        check(lib().hmoe_prefill_ep(C.byref(self.struct), vp(self.x_all), C.c_int(moe._dt(self.x_all)), vp(self.sel_all), vp(self.rw_all),
+                                    C.c_int(self.R), C.c_int(pl["lo"]), C.c_int(pl["n_local"]), C.c_int(0), vp(self.partial), vp(self.ws),
+                                    C.c_size_t(self.ws.numel()), C.c_int(self.rank * self.rpr), C.c_int(self.rpr), st))
+        if self.world > 1:
+            d.reduce_scatter_tensor(out, self.partial)
+        else:
+            out.copy_(self.partial)
+        return out
+
+
+def bench_prefill(args, world, rank, dev):
+    """bench.py --mode prefill for N > 1: args.rows tokens in total, split over the ranks; uniform or Zipf routing."""
+    import torch
+    import torch.distributed as dist
+    import bench as B
+    from . import synth
+    E, H, I, TOPK = B.E, B.H, B.I, B.TOPK
+    R = args.rows
+    rpr = R // world
+    pl = shard_plan(rank, world, E)
+    tabs = B.build_layer(dev, 100 + rank, list(range(pl["lo"], pl["lo"] + pl["n_local"])), torch, moe)
+    steps, warmup = min(args.steps, 50), max(3, min(args.warmup, 5))
+    sel_all, rw_all = synth.zipf_routing(10, 0, R, E, TOPK, args.zipf)
+    x = torch.from_numpy(synth.activations(rank, 0, rpr, H)).to(torch.bfloat16).to(dev)
+    sel = torch.from_numpy(sel_all[rank * rpr:(rank + 1) * rpr]).to(dev); rw = torch.from_numpy(rw_all[rank * rpr:(rank + 1) * rpr]).to(dev)
+    out = torch.empty(rpr, H, dtype=torch.float32, device=dev)
+    ep = EpPrefill(rank, world, tabs, E, rpr, dev, dist)
+    for _ in range(warmup):
+        ep.step(x, sel, rw, out)
+    torch.cuda.synchronize(); dist.barrier()
+    l0 = moe.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with B.ClockSampler(dev.index) as cs:
+        torch.cuda.synchronize(); dist.barrier()
+        ev0.record()
+        for _ in range(steps):
+            ep.step(x, sel, rw, out)
+        ev1.record()
+        torch.cuda.synchronize(); dist.barrier()
+    ms = torch.tensor([ev0.elapsed_time(ev1) / steps], device=dev)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    launches = moe.launch_count() - l0
+    st = torch.tensor([moe.ws_status(ep.ws)], device=dev); dist.all_reduce(st, op=dist.ReduceOp.MAX)
+    picks = np.array([int(((sel_all >= r * pl["n_local"]) & (sel_all < (r + 1) * pl["n_local"])).sum()) for r in range(world)])
+    if rank == 0:
+        flop = 2.0 * (TOPK * R + R) * (3 * I * H)
+        t = float(ms.item()) * 1e-3
+        peaks = json.load(open(os.path.join(B.ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(B.ROOT, "MEASURED_PEAKS.json")) else {}
+        peak = float(peaks.get("bf16_tflops_sustained", 1400.0)) * world
+        print(json.dumps({
+            "metric": "moe_prefill_expert_gemm_tflops", "value": flop / t / 1e12, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
+            "warmup": warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "int4 -> fp16 x fp16 -> fp32 (tcgen05)", "data": "synthetic",
+            "config": {"workload": f"prefill M={R} tokens over {world} GPUs ({rpr} each), Zipf({args.zipf}) top-8 over {E} experts + shared, "
+                                   f"experts split {pl['n_local']} per GPU, all-gather dispatch + reduce-scatter combine (NCCL)",
+                       "l2": "inputs larger than L2"},
+            "tokens_per_s": R / t,
+            "dispatch_bytes_per_rank": (world - 1) * rpr * (H * 2 + TOPK * 10), "combine_bytes_per_rank": (world - 1) * rpr * H * 4,
+            "picks_per_rank": picks.tolist(), "load_imbalance_max_over_mean": float(picks.max() / picks.mean()),
+            "roofline": {"bound": "tensor", "kernel": "whole step incl. collectives", "achieved": flop / t / 1e12, "peak": peak, "unit": "TFLOP/s",
+                         "frac": flop / t / 1e12 / peak, "peak_kind": "measured (sustained) x n_gpus", "traffic": None},
+            "gpu_launches": int(launches), "device_status": int(st.item()), "clocks": cs.summary()}))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def bench_decode(args, world, rank, dev):
     """bench.py's N > 1 arm: the decode configuration with the 256 experts split over `world` GPUs, the 16 rows replicated
     (strong scaling: the global batch is fixed), combine over peer memory; the NCCL all-reduce variant is timed beside it."""

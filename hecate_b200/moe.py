@@ -106,6 +106,37 @@ def prefill(tables, x, sel, rw, out, ws, lo=0, n_local=None, act_quant=False):
     return out
 
 
+def moe4t_scratch(device, npos, H=6144, I=2048):
+    """moe4t.scratch(device, npos) -> [gu, ar, d] (moe4t.cu:490-495). Here one workspace tensor stands for all three (it holds
+    the gathered inputs and the intermediate activations); the other two entries keep call sites that unpack three working."""
+    n = lib().hmoe_prefill_sorted_ws_bytes(C.c_int(int(npos)), C.c_int(H), C.c_int(I))
+    e = torch.zeros(1, dtype=torch.uint8, device=device)
+    return [torch.zeros(n, dtype=torch.uint8, device=device), e, e]
+
+
+def moe4t_forward(x, tok, eid, wt, rbt, gw, uw, dw, gs, us, ds, gu, ar, d, out, *, I=2048, group=0, act_quant=False):
+    """moe4t.forward / moe4p.forward with the reference's argument order (moe4t.cu:498-500): x fp16/bf16 [rows][H], tok / eid
+    int32 [npos] and wt fp32 [npos] in sorted-pick order, rbt int32 [nrb][4] on the device, six int64 pointer tables, the
+    workspace from moe4t_scratch as `gu` (`ar`, `d` ignored), out fp32 [rows][H] added into. eid is not read: the expert of a
+    pick is the expert of its row block."""
+    npos, nrb, H = int(tok.numel()), int(rbt.shape[0]), x.shape[1]
+    if npos == 0:
+        return
+    if tok.dtype != torch.int32 or wt.dtype != torch.float32 or rbt.dtype != torch.int32 or out.dtype != torch.float32:
+        raise HmoeError("moe4t: shapes")
+    s = LayerStruct()
+    s.H, s.I, s.n_experts, s.topk, s.group = H, I, int(gw.numel()), 8, group
+    s.scale_dtype = F32 if group == 0 else BF16
+    for k, t in zip(("gate_w", "up_w", "down_w", "gate_s", "up_s", "down_s"), (gw, uw, dw, gs, us, ds)):
+        setattr(s, k, t.data_ptr())
+    check(lib().hmoe_prefill_sorted(C.byref(s), vp(x), C.c_int(_dt(x)), vp(tok), vp(wt), vp(rbt.contiguous()), C.c_int(nrb), C.c_int(npos),
+                                    C.c_int(int(gw.numel())), C.c_int(int(act_quant)), vp(out), vp(gu), C.c_size_t(gu.numel()),
+                                    _stream(x.device)))
+
+
+moe4p_forward, moe4p_scratch = moe4t_forward, moe4t_scratch
+
+
 def permute(sel, rw, n_local, lo=0, shared_rows=0, bm=256, balance=True):
     """Device permutation of the picks (stable sort by expert id) and the row-block table. Returns a dict of tensors:
     order, tok, eid, wt, counts, rbt (first `nrb` rows valid), total, nrb."""

@@ -110,6 +110,21 @@ size_t hmoe_prefill_ws_bytes(int R, int topk, int n_local, int H, int I);
 int hmoe_prefill(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
                  int act_quant, float* out, void* ws, size_t ws_bytes, void* stream);
 
+/* hmoe_prefill for one rank of an expert-parallel group (no reference counterpart): experts split by lo / n_local as above;
+ * the shared expert is applied to rows [shared_row0, shared_row0 + shared_rows) only (the rank's own tokens). */
+int hmoe_prefill_ep(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
+                    int act_quant, float* out, void* ws, size_t ws_bytes, int shared_row0, int shared_rows, void* stream);
+
+/* The same two grouped GEMMs with the reference's calling convention, for callers that keep the reference's host-side
+ * permutation: replaces moe4t.forward / moe4p.forward(x, tok, eid, wt, rbt, gw, uw, dw, gs, us, ds, gu, ar, d, out)
+ * (runtime/tier/moe4/moe4t.cu:498-524). tok int32 [npos] (token of each sorted pick), wt fp32 [npos], rbt int32 [nrb][4] =
+ * {expert, first pick, picks <= 256, 0}, all on the device; the expert of a pick is taken from its row block (eid is not
+ * needed). Expert ids >= n_local select the shared expert. ws: hmoe_prefill_sorted_ws_bytes(npos, H, I) (replaces
+ * moe4t.scratch, moe4t.cu:490-495). */
+size_t hmoe_prefill_sorted_ws_bytes(int npos, int H, int I);
+int hmoe_prefill_sorted(const hmoe_layer* layer, const void* x, int x_dtype, const int32_t* tok, const float* wt, const int32_t* rbt, int nrb,
+                        int npos, int n_local, int act_quant, float* out, void* ws, size_t ws_bytes, void* stream);
+
 /* hmoe_decode without a workspace argument, for callers that cannot allocate device memory: embedders whose device memory
  * is one arena planned at start-up, plugins that must stay inside a host framework's allocator, latency-critical loops
  * where an allocation would stall the process. It has no counterpart in the reference (whose scratch always comes from

@@ -160,3 +160,25 @@ def test_prefill_matches_decode_at_full_shape(dev):
     y = torch.zeros(16, H, device=dev)
     moe.decode(tabs, x[rows].contiguous(), st[rows].contiguous(), rt[rows].contiguous(), y, wsd)
     assert errors(out[rows].cpu().numpy(), y.cpu().numpy())[2] < 1e-3
+
+
+def test_reference_calling_convention_moe4t_forward(oracle, dev):
+    """moe4t_forward with tok / wt / rbt prepared on the host exactly as the reference's dispatcher does
+    (tier_split.py:433-457: stable argsort, bincount, pick_groups with 256-pick balanced blocks)."""
+    import torch
+    from hecate_b200 import moe
+    H, I, E, R = 256, 128, 8, 500
+    hl = HostLayer(0, 0, H, I, range(E), 0, False)
+    tabs = hl.upload(dev)
+    x = synth.activations(1, 0, R, H).astype(np.float16)
+    sel, rw = synth.zipf_routing(2, 0, R, E, 8, 1.1)
+    order, tok, eid, wt, counts = oracle.permute(sel, rw, E)
+    rbt = oracle.row_blocks(counts, 256, True)
+    ex, _ = hl.oracle_experts(oracle)
+    ref = oracle.moe_forward(H, I, 0, x, sel, rw, 0, ex, None, mode=1)
+    scr = moe.moe4t_scratch(dev, len(tok), H, I)
+    out = torch.zeros(R, H, device=dev)
+    t = tabs.tabs
+    T = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    moe.moe4t_forward(T(x), T(tok), T(eid), T(wt), T(rbt), t["gate_w"], t["up_w"], t["down_w"], t["gate_s"], t["up_s"], t["down_s"], *scr, out, I=I)
+    assert errors(out.cpu().numpy(), ref)[2] < NORM_REL_EXACT
