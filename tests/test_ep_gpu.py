@@ -103,3 +103,47 @@ def test_two_gpu_peer_combine_matches_single_gpu(tmp_path):
     same, err_peer, err_nccl = np.load(out)
     assert same == 1.0
     assert err_peer < 1e-3 and err_nccl < 1e-3
+
+
+def _prefill_rank_main(rank, world, port, out_path):
+    sys.path.insert(0, ROOT); sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import torch
+    import torch.distributed as dist
+    from helpers import HostLayer
+    from hecate_b200 import moe, synth
+    from hecate_b200.ep import EpPrefill, shard_plan
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world, device_id=dev)
+    H, I, E, R = 256, 128, 8, 320
+    rpr = R // world
+    p = shard_plan(rank, world, E)
+    local = HostLayer(0, 0, H, I, range(p["lo"], p["lo"] + p["n_local"]), 128, True).upload(dev)
+    xa = synth.activations(1, 0, R, H); sel, rw = synth.zipf_routing(2, 0, R, E, 8, 1.1)
+    sl = slice(rank * rpr, (rank + 1) * rpr)
+    ep = EpPrefill(rank, world, local, E, rpr, dev, dist)
+    out = torch.empty(rpr, H, device=dev)
+    ep.step(torch.from_numpy(xa[sl]).to(dev).to(torch.bfloat16), torch.from_numpy(sel[sl]).to(dev), torch.from_numpy(rw[sl]).to(dev), out)
+    assert moe.ws_status(ep.ws) == 0
+    gathered = [torch.empty_like(out) for _ in range(world)]
+    dist.all_gather(gathered, out)
+    if rank == 0:
+        full = HostLayer(0, 0, H, I, range(E), 128, True).upload(dev)
+        ws = moe.prefill_workspace(R, 8, E, H, I, dev)
+        ref = torch.zeros(R, H, device=dev)
+        moe.prefill(full, torch.from_numpy(xa).to(dev).to(torch.bfloat16), torch.from_numpy(sel).to(dev), torch.from_numpy(rw).to(dev), ref, ws)
+        got = torch.cat(gathered)
+        np.save(out_path, np.array([float((got - ref).norm() / ref.norm())]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_gpu_prefill_matches_single_gpu(tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    out = str(tmp_path / "epp.npy")
+    mp.spawn(_prefill_rank_main, args=(2, 29700 + os.getpid() % 2000, out), nprocs=2, join=True)
+    assert np.load(out)[0] < 1e-3
