@@ -334,19 +334,30 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
             const void* sp = e < a.n_local ? (const void*) (mat ? a.s1[e] : a.s0[e]) : (mat ? a.sh_s1 : a.sh_s0);
             const char* wbase = (const char*) wp + ((size_t) (2 * ct + unit) * KB * 4 + strip) * 512 + lane * 16;
             const char* sbase_p = (const char*) sp + ((size_t) (2 * ct + unit) * (a.K / 128) * 64 + g * 8 + 2 * strip) * 2;
-            uint4 w0 = make_uint4(0, 0, 0, 0), w1 = w0;
-            if (kb0 < KB) w0 = ldg128_nc(wbase + (size_t) kb0 * 2048);
-            if (kb0 + kstep < KB) w1 = ldg128_nc(wbase + (size_t) (kb0 + kstep) * 2048);
+            // packed words and scale pairs of the next NPF of this warp's stages, in flight while the current one is converted
+            constexpr int NPF = 4;
+            uint4 wq[NPF]; uint32_t sq[NPF];
+            #pragma unroll
+            for (int i = 0; i < NPF; ++i)
+            {
+                const int kbi = kb0 + i * kstep;
+                wq[i] = kbi < KB ? ldg128_nc(wbase + (size_t) kbi * 2048) : make_uint4(0, 0, 0, 0);
+                sq[i] = (a.grouped && kbi < KB) ? __ldg((const uint32_t*) (sbase_p + (size_t) (kbi >> 1) * 128)) : 0u;
+            }
             const uint32_t it0 = tile_n * (uint32_t) KB;
             bool ok = true;
             for (int kb = kb0; kb < KB; kb += kstep)
             {
                 const uint32_t gi = it0 + kb, s = gi % L::STAGES;
-                const uint4 wc = w0;
-                w0 = w1;
-                if (kb + 2 * kstep < KB) w1 = ldg128_nc(wbase + (size_t) (kb + 2 * kstep) * 2048);
-                uint32_t sc = 0;
-                if (a.grouped) sc = __ldg((const uint32_t*) (sbase_p + (size_t) (kb >> 1) * 128));
+                const uint4 wc = wq[0];
+                const uint32_t sc = sq[0];
+                #pragma unroll
+                for (int i = 0; i + 1 < NPF; ++i) { wq[i] = wq[i + 1]; sq[i] = sq[i + 1]; }
+                {
+                    const int kbn = kb + NPF * kstep;
+                    wq[NPF - 1] = kbn < KB ? ldg128_nc(wbase + (size_t) kbn * 2048) : make_uint4(0, 0, 0, 0);
+                    sq[NPF - 1] = (a.grouped && kbn < KB) ? __ldg((const uint32_t*) (sbase_p + (size_t) (kbn >> 1) * 128)) : 0u;
+                }
                 if (gi >= (uint32_t) L::STAGES && !mbar_wait(empty + s * 8, ((gi / L::STAGES) - 1) & 1, abort_flag, a.status)) { ok = false; break; }
                 uint32_t s_lo = 0, s_hi = 0;
                 if (a.grouped) scale_pair(sc, s_lo, s_hi);
