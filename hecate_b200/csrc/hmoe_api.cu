@@ -101,7 +101,7 @@ int hmoe_decode(const hmoe_layer* layer, const void* x, int x_dtype, const int64
     return decode_launch(layer, x, x_dtype, sel, rw, R, lo, n_local, act_quant, y, ws, ws_bytes, (cudaStream_t) stream);
 }
 
-size_t hmoe_prefill_ws_bytes(int R, int topk, int n_local, int H, int I) { return prefill_ws_bytes(R, topk, n_local, H, I); }
+size_t hmoe_prefill_ws_bytes(int R, int topk, int n_local, int H, int I, int act_quant) { return prefill_ws_bytes(R, topk, n_local, H, I, act_quant); }
 int hmoe_prefill(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
                  int act_quant, float* out, void* ws, size_t ws_bytes, void* stream)
 {
@@ -115,7 +115,7 @@ int hmoe_prefill_ep(const hmoe_layer* layer, const void* x, int x_dtype, const i
     if (shared_rows < 0) return fail(HMOE_E_ARG, "hmoe_prefill_ep: shared_rows must be >= 0");
     return prefill_launch(layer, x, x_dtype, sel, rw, R, lo, n_local, act_quant, out, ws, ws_bytes, (cudaStream_t) stream, shared_row0, shared_rows);
 }
-size_t hmoe_prefill_sorted_ws_bytes(int npos, int H, int I) { return prefill_sorted_ws_bytes(npos, H, I); }
+size_t hmoe_prefill_sorted_ws_bytes(int npos, int H, int I, int act_quant) { return prefill_sorted_ws_bytes(npos, H, I, act_quant); }
 int hmoe_prefill_sorted(const hmoe_layer* layer, const void* x, int x_dtype, const int32_t* tok, const float* wt, const int32_t* rbt, int nrb,
                         int npos, int n_local, int act_quant, float* out, void* ws, size_t ws_bytes, void* stream)
 {

@@ -177,14 +177,24 @@ __global__ void __launch_bounds__(192) gather_kernel(const void* __restrict__ x,
             #pragma unroll
             for (int k = 0; k < 32; ++k) v[k] = __fmul_rn((float) __float2int_rn(__fmul_rn(v[k], inv)), s);
         }
-        uint4* d = (uint4*) (xg + (size_t) pos * H + gi * 32);
+        const size_t rowlen = act_quant ? 2 * (size_t) H : (size_t) H;       // int8 mode: [hi | lo] halves, code x scale kept to ~22 bits
+        uint4* d = (uint4*) (xg + (size_t) pos * rowlen + gi * 32);
+        uint4* dl = (uint4*) (xg + (size_t) pos * rowlen + H + gi * 32);
         #pragma unroll
         for (int j = 0; j < 4; ++j)
         {
-            uint32_t w[4];
+            uint32_t w[4], wl[4];
             #pragma unroll
-            for (int k = 0; k < 4; ++k) { const __half2 h = __floats2half2_rn(v[j * 8 + 2 * k], v[j * 8 + 2 * k + 1]); w[k] = *(const uint32_t*) &h; }
+            for (int k = 0; k < 4; ++k)
+            {
+                const __half2 h = __floats2half2_rn(v[j * 8 + 2 * k], v[j * 8 + 2 * k + 1]);
+                w[k] = *(const uint32_t*) &h;
+                const float2 f = __half22float2(h);
+                const __half2 l = __floats2half2_rn(v[j * 8 + 2 * k] - f.x, v[j * 8 + 2 * k + 1] - f.y);
+                wl[k] = *(const uint32_t*) &l;
+            }
             d[j] = make_uint4(w[0], w[1], w[2], w[3]);
+            if (act_quant) dl[j] = make_uint4(wl[0], wl[1], wl[2], wl[3]);
         }
     }
 }
@@ -229,6 +239,7 @@ struct GemmArgs
     int K, N;                 // reduction length and output channels of the matrix (gate_up: K = H, N = I; down: K = I, N = H)
     int grouped;              // bf16 scale per 128 columns (else fp32 per row)
     int act_quant;
+    int kfold;                // 1, or 2 in the int8 mode: the inputs are [hi | lo] halves over 2 K columns, the weights are walked twice
     const int64_t* w0; const int64_t* w1;     // pointer tables of the matrix (gate, up) or (down, -)
     const int64_t* s0; const int64_t* s1;     // scale tables
     const void* sh_w0; const void* sh_w1; const void* sh_s0; const void* sh_s1;   // shared expert (expert id n_local)
@@ -312,7 +323,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    const int KB = a.K / 64, NCT = a.N / TM;
+    const int KB = a.K / 64, KBT = KB * a.kfold, NCT = a.N / TM;     // KB 64-column blocks of the weights, KBT ring stages per tile
     const int nitems = a.plan->nrb * NCT;
     uint32_t tile_n = 0;                           // tiles done (phase of done / tmem_free)
 
@@ -341,12 +352,13 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
             for (int i = 0; i < NPF; ++i)
             {
                 const int kbi = kb0 + i * kstep;
-                wq[i] = kbi < KB ? ldg128_nc(wbase + (size_t) kbi * 2048) : make_uint4(0, 0, 0, 0);
-                sq[i] = (a.grouped && kbi < KB) ? __ldg((const uint32_t*) (sbase_p + (size_t) (kbi >> 1) * 128)) : 0u;
+                const int kbw = kbi >= KB ? kbi - KB : kbi;            // second pass over the weights for the lo halves
+                wq[i] = kbi < KBT ? ldg128_nc(wbase + (size_t) kbw * 2048) : make_uint4(0, 0, 0, 0);
+                sq[i] = (a.grouped && kbi < KBT) ? __ldg((const uint32_t*) (sbase_p + (size_t) (kbw >> 1) * 128)) : 0u;
             }
-            const uint32_t it0 = tile_n * (uint32_t) KB;
+            const uint32_t it0 = tile_n * (uint32_t) KBT;
             bool ok = true;
-            for (int kb = kb0; kb < KB; kb += kstep)
+            for (int kb = kb0; kb < KBT; kb += kstep)
             {
                 const uint32_t gi = it0 + kb, s = gi % L::STAGES;
                 const uint4 wc = wq[0];
@@ -354,9 +366,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
                 #pragma unroll
                 for (int i = 0; i + 1 < NPF; ++i) { wq[i] = wq[i + 1]; sq[i] = sq[i + 1]; }
                 {
-                    const int kbn = kb + NPF * kstep;
-                    wq[NPF - 1] = kbn < KB ? ldg128_nc(wbase + (size_t) kbn * 2048) : make_uint4(0, 0, 0, 0);
-                    sq[NPF - 1] = (a.grouped && kbn < KB) ? __ldg((const uint32_t*) (sbase_p + (size_t) (kbn >> 1) * 128)) : 0u;
+                    const int kbn = kb + NPF * kstep, kbw = kbn >= KB ? kbn - KB : kbn;
+                    wq[NPF - 1] = kbn < KBT ? ldg128_nc(wbase + (size_t) kbw * 2048) : make_uint4(0, 0, 0, 0);
+                    sq[NPF - 1] = (a.grouped && kbn < KBT) ? __ldg((const uint32_t*) (sbase_p + (size_t) (kbw >> 1) * 128)) : 0u;
                 }
                 if (gi >= (uint32_t) L::STAGES && !mbar_wait(empty + s * 8, ((gi / L::STAGES) - 1) & 1, abort_flag, a.status)) { ok = false; break; }
                 uint32_t s_lo = 0, s_hi = 0;
@@ -403,8 +415,13 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
                                     for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
                                     const float s = m > 0.f ? __fdiv_rn(m, 127.f) : 1.f;
                                     v = __fmul_rn((float) __float2int_rn(__fmul_rn(v, __fdiv_rn(1.f, s))), s);
+                                    // code x scale does not fit fp16: keep it as hi + lo halves, the down GEMM walks both
+                                    const __half hi = __float2half_rn(v);
+                                    a.act[(size_t) (pos0 + p) * (2 * a.N) + ch] = hi;
+                                    a.act[(size_t) (pos0 + p) * (2 * a.N) + a.N + ch] = __float2half_rn(v - __half2float(hi));
                                 }
-                                a.act[(size_t) (pos0 + p) * a.N + ch] = __float2half_rn(v);
+                                else
+                                    a.act[(size_t) (pos0 + p) * a.N + ch] = __float2half_rn(v);
                             }
                         }
                     }
@@ -426,9 +443,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
         else if (warp == NDQ)
         {
             if (lane == 0)
-                for (int kb = 0; kb < KB; ++kb)
+                for (int kb = 0; kb < KBT; ++kb)
                 {
-                    const uint32_t it = tile_n * (uint32_t) KB + kb, s = it % L::STAGES;
+                    const uint32_t it = tile_n * (uint32_t) KBT + kb, s = it % L::STAGES;
                     if (it >= (uint32_t) L::STAGES && !mbar_wait(empty + s * 8, ((it / L::STAGES) - 1) & 1, abort_flag, a.status)) break;
                     mbar_expect_tx(full_b + s * 8, L::B_BYTES);
                     tma_load_2d(sbase + s * L::STAGE + NMAT * L::A_BYTES, &tmap, kb * 64, pos0, full_b + s * 8);
@@ -441,9 +458,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
                 const uint32_t idesc = (1u << 4) | ((n16 >> 3) << 17) | ((uint32_t) (TM >> 4) << 24);
                 bool ok = tile_n == 0 || mbar_wait(tmem_free, (tile_n - 1) & 1, abort_flag, a.status);
                 if (ok) tc_fence_after();
-                for (int kb = 0; kb < KB && ok; ++kb)
+                for (int kb = 0; kb < KBT && ok; ++kb)
                 {
-                    const uint32_t it = tile_n * (uint32_t) KB + kb, s = it % L::STAGES, ph = (it / L::STAGES) & 1;
+                    const uint32_t it = tile_n * (uint32_t) KBT + kb, s = it % L::STAGES, ph = (it / L::STAGES) & 1;
                     if (!mbar_wait(full_a + s * 8, ph, abort_flag, a.status) || !mbar_wait(full_b + s * 8, ph, abort_flag, a.status)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t at = sbase + s * L::STAGE, bt = at + NMAT * L::A_BYTES;
@@ -503,7 +520,7 @@ struct WsLayout
     int nblocks, rows_cap, maxrb;
 };
 
-WsLayout ws_layout(int R, int topk, int n_local, int H, int I, int bm)
+WsLayout ws_layout(int R, int topk, int n_local, int H, int I, int bm, int kfold = 1)
 {
     WsLayout w;
     const size_t P = (size_t) R * topk;
@@ -521,8 +538,8 @@ WsLayout ws_layout(int R, int topk, int n_local, int H, int I, int bm)
     w.eid = o; o += up256((size_t) w.rows_cap * 4);
     w.wt = o; o += up256((size_t) w.rows_cap * 4);
     w.rbt = o; o += up256((size_t) w.maxrb * 16);
-    w.xg = o; o += up256((size_t) w.rows_cap * H * 2);
-    w.act = o; o += up256((size_t) w.rows_cap * I * 2);
+    w.xg = o; o += up256((size_t) w.rows_cap * H * 2 * kfold);
+    w.act = o; o += up256((size_t) w.rows_cap * I * 2 * kfold);
     w.total = o;
     return w;
 }
@@ -541,7 +558,7 @@ int run_permute(const int64_t* sel, const void* rw, int R, int topk, int lo, int
 
 }  // namespace
 
-size_t prefill_ws_bytes(int R, int topk, int n_local, int H, int I) { return ws_layout(R, topk, n_local, H, I, TN).total; }
+size_t prefill_ws_bytes(int R, int topk, int n_local, int H, int I, int act_quant) { return ws_layout(R, topk, n_local, H, I, TN, act_quant ? 2 : 1).total; }
 
 namespace {
 __global__ void set_plan_kernel(Plan* plan, int total, int nrb) { plan->total = total; plan->nrb = nrb; plan->pad[0] = plan->pad[1] = 0; }
@@ -549,7 +566,11 @@ __global__ void set_plan_kernel(Plan* plan, int total, int nrb) { plan->total = 
 
 // The reference's calling convention (moe4t.forward, runtime/tier/moe4/moe4t.cu:498-524): the caller has already sorted the
 // picks by expert (tok, wt in that order) and built the row-block table; npos picks, nrb row blocks of <= 256 picks.
-size_t prefill_sorted_ws_bytes(int npos, int H, int I) { return 512 + up256((size_t) npos * H * 2) + up256((size_t) npos * I * 2); }
+size_t prefill_sorted_ws_bytes(int npos, int H, int I, int act_quant)
+{
+    const int f = act_quant ? 2 : 1;
+    return 512 + up256((size_t) npos * H * 2 * f) + up256((size_t) npos * I * 2 * f);
+}
 
 int prefill_sorted_launch(const hmoe_layer* L, const void* x, int x_dtype, const int32_t* tok, const float* wt, const int32_t* rbt, int nrb,
                           int npos, int n_local, int act_quant, float* out, void* ws, size_t ws_bytes, cudaStream_t st)
@@ -562,7 +583,8 @@ int prefill_sorted_launch(const hmoe_layer* L, const void* x, int x_dtype, const
         return fail(HMOE_E_ARG, "hmoe_prefill_sorted: scales must be fp32 per row (group 0) or bf16 per 128 columns");
     if (x_dtype != HMOE_F16 && x_dtype != HMOE_BF16) return fail(HMOE_E_ARG, "hmoe_prefill_sorted: x must be fp16 or bf16");
     if (!x || !tok || !wt || !rbt || !out || !ws) return fail(HMOE_E_ARG, "hmoe_prefill_sorted: null pointer");
-    if (ws_bytes < prefill_sorted_ws_bytes(npos, H, I)) return fail(HMOE_E_WS, "hmoe_prefill_sorted: workspace too small");
+    const int kf = act_quant ? 2 : 1;
+    if (ws_bytes < prefill_sorted_ws_bytes(npos, H, I, act_quant)) return fail(HMOE_E_WS, "hmoe_prefill_sorted: workspace too small");
     static int sms = 0;
     if (!sms)
     {
@@ -575,13 +597,13 @@ int prefill_sorted_launch(const hmoe_layer* L, const void* x, int x_dtype, const
     unsigned* status = (unsigned*) b;
     Plan* plan = (Plan*) (b + 256);
     __half* xg = (__half*) (b + 512);
-    __half* act = (__half*) (b + 512 + up256((size_t) npos * H * 2));
+    __half* act = (__half*) (b + 512 + up256((size_t) npos * H * 2 * kf));
     set_plan_kernel<<<1, 1, 0, st>>>(plan, npos, nrb);
     gather_kernel<<<npos, 192, 0, st>>>(x, x_dtype == HMOE_BF16, tok, plan, H, act_quant, xg);
     CUtensorMap mx, ma;
-    if (!make_map(&mx, xg, H, (size_t) npos) || !make_map(&ma, act, I, (size_t) npos)) return fail(HMOE_E_CUDA, "hmoe_prefill_sorted: cuTensorMapEncodeTiled failed");
+    if (!make_map(&mx, xg, H * kf, (size_t) npos) || !make_map(&ma, act, I * kf, (size_t) npos)) return fail(HMOE_E_CUDA, "hmoe_prefill_sorted: cuTensorMapEncodeTiled failed");
     GemmArgs g;
-    g.grouped = L->group != 0; g.act_quant = act_quant; g.n_local = n_local;
+    g.grouped = L->group != 0; g.act_quant = act_quant; g.n_local = n_local; g.kfold = kf;
     g.plan = plan; g.rbt = rbt; g.tok = tok; g.wt = wt; g.act = act; g.out = out; g.status = status;
     g.K = H; g.N = I; g.w0 = L->gate_w; g.w1 = L->up_w; g.s0 = L->gate_s; g.s1 = L->up_s;
     g.sh_w0 = L->sh_gate_w; g.sh_w1 = L->sh_up_w; g.sh_s0 = L->sh_gate_s; g.sh_s1 = L->sh_up_s;
@@ -630,8 +652,9 @@ int prefill_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_
         return fail(HMOE_E_ARG, "hmoe_prefill: scales must be fp32 per row (group 0) or bf16 per 128 columns");
     if (x_dtype != HMOE_F16 && x_dtype != HMOE_BF16) return fail(HMOE_E_ARG, "hmoe_prefill: x must be fp16 or bf16");
     if (!x || !sel || !rw || !out || !ws) return fail(HMOE_E_ARG, "hmoe_prefill: null pointer");
-    const WsLayout w = ws_layout(R, L->topk, n_local, H, I, TN);
-    if (ws_bytes < w.total) return fail(HMOE_E_WS, "hmoe_prefill: workspace too small");
+    const int kf = act_quant ? 2 : 1;
+    const WsLayout w = ws_layout(R, L->topk, n_local, H, I, TN, kf);
+    if (ws_bytes < w.total) return fail(HMOE_E_WS, "hmoe_prefill: workspace too small (the int8 mode needs hmoe_prefill_ws_bytes(..., act_quant = 1))");
     static int sms = 0;
     static bool attr = false;
     if (!attr)
@@ -655,9 +678,9 @@ int prefill_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_
     if (rc) return rc;
     gather_kernel<<<w.rows_cap, 192, 0, st>>>(x, x_dtype == HMOE_BF16, tok, plan, H, act_quant, xg);
     CUtensorMap mx, ma;
-    if (!make_map(&mx, xg, H, (size_t) w.rows_cap) || !make_map(&ma, act, I, (size_t) w.rows_cap)) return fail(HMOE_E_CUDA, "hmoe_prefill: cuTensorMapEncodeTiled failed");
+    if (!make_map(&mx, xg, H * kf, (size_t) w.rows_cap) || !make_map(&ma, act, I * kf, (size_t) w.rows_cap)) return fail(HMOE_E_CUDA, "hmoe_prefill: cuTensorMapEncodeTiled failed");
     GemmArgs g;
-    g.grouped = L->group != 0; g.act_quant = act_quant; g.n_local = n_local;
+    g.grouped = L->group != 0; g.act_quant = act_quant; g.n_local = n_local; g.kfold = kf;
     g.plan = plan; g.rbt = rbt; g.tok = tok; g.wt = wt; g.act = act; g.out = out; g.status = status;
     g.K = H; g.N = I; g.w0 = L->gate_w; g.w1 = L->up_w; g.s0 = L->gate_s; g.s1 = L->up_s;
     g.sh_w0 = L->sh_gate_w; g.sh_w1 = L->sh_up_w; g.sh_s0 = L->sh_gate_s; g.sh_s1 = L->sh_up_s;

@@ -86,8 +86,8 @@ def decode(tables, x, sel, rw, y, ws, lo=0, n_local=None, act_quant=False):
     return y
 
 
-def prefill_workspace(R, topk, n_local, H, I, device):
-    n = lib().hmoe_prefill_ws_bytes(C.c_int(R), C.c_int(topk), C.c_int(n_local), C.c_int(H), C.c_int(I))
+def prefill_workspace(R, topk, n_local, H, I, device, act_quant=False):
+    n = lib().hmoe_prefill_ws_bytes(C.c_int(R), C.c_int(topk), C.c_int(n_local), C.c_int(H), C.c_int(I), C.c_int(int(act_quant)))
     return torch.zeros(n, dtype=torch.uint8, device=device)
 
 
@@ -106,10 +106,10 @@ def prefill(tables, x, sel, rw, out, ws, lo=0, n_local=None, act_quant=False):
     return out
 
 
-def moe4t_scratch(device, npos, H=6144, I=2048):
+def moe4t_scratch(device, npos, H=6144, I=2048, act_quant=False):
     """moe4t.scratch(device, npos) -> [gu, ar, d] (moe4t.cu:490-495). Here one workspace tensor stands for all three (it holds
     the gathered inputs and the intermediate activations); the other two entries keep call sites that unpack three working."""
-    n = lib().hmoe_prefill_sorted_ws_bytes(C.c_int(int(npos)), C.c_int(H), C.c_int(I))
+    n = lib().hmoe_prefill_sorted_ws_bytes(C.c_int(int(npos)), C.c_int(H), C.c_int(I), C.c_int(int(act_quant)))
     e = torch.zeros(1, dtype=torch.uint8, device=device)
     return [torch.zeros(n, dtype=torch.uint8, device=device), e, e]
 

@@ -103,10 +103,11 @@ int hmoe_permute(const int64_t* sel, const void* rw, int R, int topk, int lo, in
  * (runtime/tier/moe4/moe4t.cu:498-524, moe4p.cu:220-245) together with the permutation above, for any number of rows:
  * permute -> gather -> grouped gate+up GEMM with SiLU * up * weight epilogue -> grouped down GEMM whose epilogue adds
  * scale * sum into out[token] (fp32 [R][H], added into: zero it first for a plain result). tcgen05 tensor cores, fp16
- * operands, fp32 accumulation. act_quant = 1 rounds activations through the CPU engine's int8 format (values, not exact
- * integer arithmetic: see DESIGN.md). Other arguments as hmoe_decode. ws: hmoe_prefill_ws_bytes bytes (holds the gathered
- * inputs and the intermediate activations: (R*topk + R) * (H + I) * 2 bytes plus small tables). */
-size_t hmoe_prefill_ws_bytes(int R, int topk, int n_local, int H, int I);
+ * operands, fp32 accumulation. act_quant = 1 reproduces the CPU engine's int8 activation round trips: code x scale is carried
+ * as an fp16 hi + lo pair and the weights are walked twice (twice the tensor-core work; a parity mode, not the fast path).
+ * Other arguments as hmoe_decode. ws: hmoe_prefill_ws_bytes(..., act_quant) bytes (holds the gathered inputs and the
+ * intermediate activations: (R*topk + R) * (H + I) * 2 bytes, twice that in the int8 mode, plus small tables). */
+size_t hmoe_prefill_ws_bytes(int R, int topk, int n_local, int H, int I, int act_quant);
 int hmoe_prefill(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
                  int act_quant, float* out, void* ws, size_t ws_bytes, void* stream);
 
@@ -121,7 +122,7 @@ int hmoe_prefill_ep(const hmoe_layer* layer, const void* x, int x_dtype, const i
  * {expert, first pick, picks <= 256, 0}, all on the device; the expert of a pick is taken from its row block (eid is not
  * needed). Expert ids >= n_local select the shared expert. ws: hmoe_prefill_sorted_ws_bytes(npos, H, I) (replaces
  * moe4t.scratch, moe4t.cu:490-495). */
-size_t hmoe_prefill_sorted_ws_bytes(int npos, int H, int I);
+size_t hmoe_prefill_sorted_ws_bytes(int npos, int H, int I, int act_quant);
 int hmoe_prefill_sorted(const hmoe_layer* layer, const void* x, int x_dtype, const int32_t* tok, const float* wt, const int32_t* rbt, int nrb,
                         int npos, int n_local, int act_quant, float* out, void* ws, size_t ws_bytes, void* stream);
 

@@ -42,6 +42,14 @@ class HostLayer:
                                 group=self.group, shared=shared, device=device)
 
 
+def int8_close(e):
+    """Gate of the int8-mode results on small layers, e = errors(...). Integer sums are exact and a typical result is 1e-7
+    from the CPU engine's, but the fp32 scale sums and expf differ from the CPU's by ulps, which can move one intermediate
+    value across a rounding boundary of its int8 code: one code (1/127 of its group's maximum) on one pick shifts that
+    row's outputs by up to ~2e-3 of the output range in a layer this small. More than a few such flips fails."""
+    return e[0] < 5e-3 and e[1] < 3e-4
+
+
 def errors(got, ref):
     """(max-rel, mean-abs, norm-rel), the first two normalised: max|a-b| / max|b| and mean|a-b| / mean|b|."""
     got = np.asarray(got, dtype=np.float64); ref = np.asarray(ref, dtype=np.float64)

@@ -10,8 +10,7 @@ pytestmark = pytest.mark.gpu
 
 NORM_REL_EXACT = 2e-3      # the reference GPU kernels' own gate against an exact evaluation (tools/quant/test_moe4_rtx.py:70)
 MAX_REL = 1e-2             # the benchmark definition's bar against the CPU engine, max|a-b| / max|b|
-MEAN_ABS_PREFILL = 3e-3    # mean|a-b| / mean|b| reached by the prefill path in the int8 mode (values rounded to fp16, not exact
-                           # integer arithmetic like the decode path, which meets 1e-3): see DESIGN.md
+MEAN_ABS = 1e-3            # the same definition's bar on mean|a-b| / mean|b|; the int8 mode carries code x scale as fp16 hi + lo
 
 
 @pytest.fixture(scope="module")
@@ -64,7 +63,7 @@ def _prefill(oracle, dev, H, I, E, R, group, shared, aq, zipf, seed=0, lo=0, n_l
     ex, sh = hl.oracle_experts(oracle)
     n_local = E if n_local is None else n_local
     ref = oracle.moe_forward(H, I, group, x, sel, rw, lo, ex[:n_local], sh, mode=0 if aq else 1)
-    ws = moe.prefill_workspace(R, 8, n_local, H, I, dev)
+    ws = moe.prefill_workspace(R, 8, n_local, H, I, dev, act_quant=aq)
     out = torch.zeros(R, H, device=dev)
     moe.prefill(tabs, torch.from_numpy(x).to(dev), torch.from_numpy(sel).to(dev), torch.from_numpy(rw).to(dev), out, ws, lo=lo,
                 n_local=n_local, act_quant=aq)
@@ -82,7 +81,13 @@ def test_prefill_exact_mode_small(oracle, dev, group, R, zipf, shared):
 @pytest.mark.parametrize("group", [0, 128])
 def test_prefill_int8_mode(oracle, dev, group):
     e = _prefill(oracle, dev, 512, 256, 16, 700, group, True, True, 1.1)
-    assert e[0] < MAX_REL and e[1] < MEAN_ABS_PREFILL, e
+    assert e[0] < MAX_REL and e[1] < MEAN_ABS, e
+
+
+def test_prefill_int8_mode_full_width(oracle, dev):
+    """The benchmark's widths (6144 x 2048), few experts and rows so that the CPU checker finishes in seconds."""
+    e = _prefill(oracle, dev, 6144, 2048, 8, 64, 128, True, True, 0.0)
+    assert e[0] < MAX_REL and e[1] < MEAN_ABS, e
 
 
 def test_prefill_band_filter(oracle, dev):
