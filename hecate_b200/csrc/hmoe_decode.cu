@@ -623,6 +623,177 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_down_kernel(const DecodeAr
     __syncthreads();
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// down, for I <= 2048 (at most 32 blocks of 64 input columns per output row)
+//
+// Items are (tile, 64-row group of the output) with the row group fastest: a block walks an expert's matrix in address
+// order, and the tile, hence the activations, stays the same over a long run of items. Warp w = (kq = w / 4, strip = w % 4)
+// owns 16 output rows and a quarter of the input columns (U <= 8 blocks): its activation fragments for those columns live
+// in registers for the whole tile, so the inner loop reads nothing but the ring. The four warps of a column quarter share a
+// ring of NSTAGE slots of 16 KB (their quarter of the item, contiguous in memory); the warp that frees a slot last issues
+// the copy of the item NSTAGE ahead into it. Each warp ends an item with its 16 rows x (real tile columns) partial sums,
+// which go to y as fp32 reductions in global memory: four per output element (one per column quarter), nothing is kept in
+// shared memory between items and no warp waits for another except through the ring.
+template <bool GROUPED, bool Q8>
+__global__ void __launch_bounds__(NTHREADS, 1) decode_down_resident_kernel(const DecodeArgs a)
+{
+    extern __shared__ __align__(1024) unsigned char smem[];
+    constexpr int SLOT = STAGE_BYTES / 4;
+    const uint32_t sbase = smem_u32(smem);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, kq = warp >> 2, s = warp & 3, g = lane >> 2, q = lane & 3;
+    const uint32_t ring = sbase + SmemLayout::ring + kq * NSTAGE * SLOT, full0 = sbase + SmemLayout::bars + kq * NSTAGE * 8;
+    int* free_cnt = (int*) (smem + SmemLayout::gu) + kq * NSTAGE;
+    volatile int* abort_flag = (volatile int*) (smem + SmemLayout::flags);
+    float* const yout = a.y + (a.gen_ptr ? (size_t) (*a.gen_ptr & 1u) * a.slot_stride : 0);
+    if (threadIdx.x == 0)
+    {
+        for (int i = 0; i < 4 * NSTAGE; ++i) { mbar_init(sbase + SmemLayout::bars + i * 8, 1); ((int*) (smem + SmemLayout::gu))[i] = 0; }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    __syncthreads();
+    const Route* rt = a.route;
+    const int NG = a.H / 64, KB = a.I / 64, U = 2 * ((KB + 7) / 8);
+    const int nu = KB - kq * U < 0 ? 0 : (KB - kq * U < U ? KB - kq * U : U);       // this quarter's blocks (even)
+    const int nt = rt->ntiles, P = nt * NG;
+    const int p0 = (int) ((long long) P * blockIdx.x / gridDim.x), p1 = (int) ((long long) P * (blockIdx.x + 1) / gridDim.x);
+    const int total = p1 - p0;
+    if (total > 0 && nu > 0)
+    {
+        auto fill = [&](int i) {
+            const int p = p0 + i, t = p / NG, r = p % NG, e = rt->expert[t];
+            const char* src = (const char*) (e >= 0 ? (const void*) a.down_w[e] : a.sh_dw) + ((size_t) r * KB + kq * U) * 2048;
+            const uint32_t slot = (uint32_t) i % NSTAGE;
+            mbar_expect_tx(full0 + slot * 8, nu * 2048);
+            bulk_g2s(ring + slot * SLOT, src, nu * 2048, full0 + slot * 8);
+        };
+        if (s == 0 && lane == 0)
+            for (int i = 0; i < NSTAGE && i < total; ++i) fill(i);
+        uint32_t bfr[8][8];                   // activation fragments of this lane's tile row: block u, word 2t + h of 16-column step t
+        int nrows = 0, rowA = 0, rowB = 0;
+        const char* scp = nullptr; const float* sdp = nullptr; const float* xsA = nullptr; const float* xsB = nullptr;
+        auto enter_tile = [&](int tile) {
+            const int e = rt->expert[tile];
+            nrows = rt->nrows[tile]; rowA = rt->rows[tile][2 * q]; rowB = rt->rows[tile][2 * q + 1];
+            const char* xb = (const char*) (a.act + ((size_t) tile * 8 + g) * a.I) + (size_t) kq * U * 128 + q * 32;
+            #pragma unroll
+            for (int u = 0; u < 8; ++u)
+            {
+                uint4 v0 = make_uint4(0, 0, 0, 0), v1 = v0;
+                if (u < nu) { v0 = ldg128(xb + u * 128); v1 = ldg128(xb + u * 128 + 16); }
+                bfr[u][0] = v0.x; bfr[u][1] = v0.y; bfr[u][2] = v0.z; bfr[u][3] = v0.w;
+                bfr[u][4] = v1.x; bfr[u][5] = v1.y; bfr[u][6] = v1.z; bfr[u][7] = v1.w;
+            }
+            if (Q8) { xsA = a.ascale + ((size_t) tile * 8 + 2 * q) * (a.I / 32) + kq * U * 2; xsB = xsA + a.I / 32; }
+            const void* sp = e >= 0 ? (const void*) a.down_s[e] : a.sh_ds;
+            if (GROUPED) scp = (const char*) sp + ((size_t) (kq * U / 2) * 64 + g * 8 + 2 * s) * 2;
+            else sdp = (const float*) sp + s * 16 + g;
+        };
+        // scales of this warp's rows for one item: GROUPED, word j = bf16 pair (row strip*16 + g, + 8) of 128-column group j
+        auto load_scales = [&](int gr, uint32_t* sc, float* sd) {
+            if (GROUPED)
+            {
+                #pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (2 * j < nu) sc[j] = __ldg((const uint32_t*) (scp + ((size_t) gr * (a.I / 128) + j) * 128));
+            }
+            else { sd[0] = __ldg(sdp + gr * 64); sd[1] = __ldg(sdp + gr * 64 + 8); }
+        };
+        int tile = p0 / NG, gr = p0 % NG;
+        enter_tile(tile);
+        uint32_t sc[4] = {0, 0, 0, 0};
+        float sd[2] = {1.f, 1.f};
+        load_scales(gr, sc, sd);
+        uint32_t st = 0, par = 0;
+        for (int i = 0; i < total; ++i)
+        {
+            uint32_t scn[4] = {0, 0, 0, 0};
+            float sdn[2] = {1.f, 1.f};
+            const bool same_tile = gr + 1 < NG;
+            if (same_tile && i + 1 < total) load_scales(gr + 1, scn, sdn);          // one item ahead
+            if (!mbar_wait(full0 + st * 8, par, abort_flag, a.status)) break;
+            const uint32_t wsm = ring + st * SLOT + s * 512 + lane * 16;
+            float acc[4] = {0.f, 0.f, 0.f, 0.f}, pa[4] = {0.f, 0.f, 0.f, 0.f}, pb[4] = {0.f, 0.f, 0.f, 0.f};
+            #pragma unroll
+            for (int j = 0; j < 4; ++j)
+            {
+                if (2 * j >= nu) break;
+                float s0 = 1.f, s1 = 1.f;
+                if (GROUPED) { s0 = __uint_as_float(sc[j] << 16); s1 = __uint_as_float(sc[j] & 0xffff0000u); }
+                #pragma unroll
+                for (int uu = 0; uu < 2; ++uu)
+                {
+                    const int u = 2 * j + uu;
+                    const uint4 w4 = lds128(wsm + u * 2048);
+                    float2 sxa = make_float2(1.f, 1.f), sxb = sxa;
+                    if (Q8) { sxa = *(const float2*) (xsA + 2 * u); sxb = *(const float2*) (xsB + 2 * u); }
+                    #pragma unroll
+                    for (int t = 0; t < 4; ++t)
+                    {
+                        const uint32_t w = t == 0 ? w4.x : t == 1 ? w4.y : t == 2 ? w4.z : w4.w;
+                        uint32_t af[4];
+                        frag_from_codes(w, af);
+                        // two independent MMA chains: in the int8 mode one per 32 columns (exact integer sums), else alternating steps
+                        mma_f16((Q8 ? (t >> 1) : (t & 1)) ? pb : pa, af, bfr[u][2 * t], bfr[u][2 * t + 1]);
+                    }
+                    if (Q8)
+                    {
+                        acc[0] = fmaf(pa[0], sxa.x * s0, acc[0]); acc[1] = fmaf(pa[1], sxb.x * s0, acc[1]);
+                        acc[2] = fmaf(pa[2], sxa.x * s1, acc[2]); acc[3] = fmaf(pa[3], sxb.x * s1, acc[3]);
+                        acc[0] = fmaf(pb[0], sxa.y * s0, acc[0]); acc[1] = fmaf(pb[1], sxb.y * s0, acc[1]);
+                        acc[2] = fmaf(pb[2], sxa.y * s1, acc[2]); acc[3] = fmaf(pb[3], sxb.y * s1, acc[3]);
+                        #pragma unroll
+                        for (int k = 0; k < 4; ++k) pa[k] = pb[k] = 0.f;
+                    }
+                }
+                if (GROUPED && !Q8)
+                {
+                    acc[0] = fmaf(s0, pa[0] + pb[0], acc[0]); acc[1] = fmaf(s0, pa[1] + pb[1], acc[1]);
+                    acc[2] = fmaf(s1, pa[2] + pb[2], acc[2]); acc[3] = fmaf(s1, pa[3] + pb[3], acc[3]);
+                    #pragma unroll
+                    for (int k = 0; k < 4; ++k) pa[k] = pb[k] = 0.f;
+                }
+            }
+            if (!GROUPED && !Q8)
+            {
+                #pragma unroll
+                for (int k = 0; k < 4; ++k) acc[k] = pa[k] + pb[k];
+            }
+            // the slot is read: the last of the quarter's four warps to say so refills it
+            __syncwarp();
+            if (lane == 0)
+            {
+                __threadfence_block();
+                if (atomicAdd(free_cnt + st, 1) == 3)
+                {
+                    free_cnt[st] = 0;
+                    __threadfence_block();
+                    if (i + NSTAGE < total) fill(i + NSTAGE);
+                }
+            }
+            // this warp's 16 rows of the real tile columns join y
+            float* const yc = yout + gr * 64 + s * 16 + g;
+            if (2 * q < nrows) { atomicAdd(yc + (size_t) rowA * a.H, acc[0] * sd[0]); atomicAdd(yc + (size_t) rowA * a.H + 8, acc[2] * sd[1]); }
+            if (2 * q + 1 < nrows) { atomicAdd(yc + (size_t) rowB * a.H, acc[1] * sd[0]); atomicAdd(yc + (size_t) rowB * a.H + 8, acc[3] * sd[1]); }
+            if (++st == NSTAGE) { st = 0; par ^= 1; }
+            if (same_tile)
+            {
+                ++gr;
+                #pragma unroll
+                for (int j = 0; j < 4; ++j) sc[j] = scn[j];
+                sd[0] = sdn[0]; sd[1] = sdn[1];
+            }
+            else if (i + 1 < total)
+            {
+                gr = 0; ++tile;
+                enter_tile(tile);
+                load_scales(gr, sc, sd);
+            }
+        }
+    }
+    __syncthreads();
+}
+
 }  // namespace
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -677,10 +848,12 @@ static void launch_pair(int grid, const DecodeArgs& a, int R, cudaStream_t st, b
     {
         cudaFuncSetAttribute(decode_gate_up_kernel<G, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout::total);
         cudaFuncSetAttribute(decode_down_kernel<G, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout::total);
+        cudaFuncSetAttribute(decode_down_resident_kernel<G, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout::total);
     }
     decode_gate_up_kernel<G, Q><<<grid, NTHREADS, SmemLayout::total, st>>>(a);
     if (g_prof) cudaEventRecord(g_ev[2], st);
-    decode_down_kernel<G, Q><<<grid, NTHREADS, SmemLayout::total, st>>>(a, R);
+    if (a.I <= 2048) decode_down_resident_kernel<G, Q><<<grid, NTHREADS, SmemLayout::total, st>>>(a);
+    else decode_down_kernel<G, Q><<<grid, NTHREADS, SmemLayout::total, st>>>(a, R);
     if (g_prof) cudaEventRecord(g_ev[3], st);
 }
 
