@@ -172,6 +172,8 @@ struct Route
     unsigned char nrows[MAXT];      // rows in the tile (1..8)
     unsigned char rows[MAXT][8];    // their row numbers, ascending; entries >= nrows repeat the first row
     float w[MAXT][8];               // routing weight per listed row (summed over repeated picks), 0 beyond nrows
+    short rowbase[MAXT];            // number of real rows in the tiles before this one (row index of the tile's first row in
+                                    // the per-pick buffers; at most rows * (topk + 1) real rows per call)
 };
 
 }  // namespace hmoe

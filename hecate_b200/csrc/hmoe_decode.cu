@@ -51,12 +51,15 @@ struct SmemLayout
 // prepare
 __global__ void __launch_bounds__(256) decode_prepare_kernel(const void* __restrict__ x, int x_bf16, const int64_t* __restrict__ sel,
     const __half* __restrict__ rw, int R, int H, int topk, int lo, int n_local, int has_shared, int act_quant,
-    __half* __restrict__ xf, float* __restrict__ xscale, Route* __restrict__ route, int sh_mod, int sh_rem, unsigned* gen_bump)
+    __half* __restrict__ xf, float* __restrict__ xscale, Route* __restrict__ route, int sh_mod, int sh_rem, unsigned* gen_bump,
+    float4* __restrict__ gzero, int gzero_n)
 {
     const int tid = threadIdx.x;
     if ((int) blockIdx.x < R)
     {
         const int r = blockIdx.x;
+        // this row's share of the gate / up sums is cleared for the streaming kernels' reductions (gzero_n float4 per row block)
+        for (int i = tid; i < gzero_n; i += blockDim.x) gzero[(size_t) r * gzero_n + i] = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int gi = tid; gi < H / 32; gi += blockDim.x)
         {
             float v[32];
@@ -104,7 +107,7 @@ __global__ void __launch_bounds__(256) decode_prepare_kernel(const void* __restr
     __shared__ short slot_e[MAXS];
     __shared__ unsigned char s_n[MAXS], s_rows[MAXS][MAXR];
     __shared__ float s_w[MAXS][MAXR];
-    __shared__ short s_tile0[MAXS];
+    __shared__ short s_tile0[MAXS], s_rb[MAXS];
     __shared__ int m_sh;
     __shared__ short s_sel[MAXR * TOPK_MAX];
     __shared__ float s_rw[MAXR * TOPK_MAX];
@@ -156,8 +159,8 @@ __global__ void __launch_bounds__(256) decode_prepare_kernel(const void* __restr
     __syncthreads();
     if (tid == 0)
     {
-        int t = 0;
-        for (int j = 0; j < ns; ++j) { s_tile0[j] = (short) t; t += (s_n[j] + 7) / 8; }
+        int t = 0, rb = 0;
+        for (int j = 0; j < ns; ++j) { s_tile0[j] = (short) t; s_rb[j] = (short) rb; t += (s_n[j] + 7) / 8; rb += s_n[j]; }
         route->m = m; route->ntiles = t; route->pad[0] = route->pad[1] = 0;
         if (gen_bump) *gen_bump += 1;          // expert-parallel step counter: selects the partial slot and the combine's generation
     }
@@ -166,7 +169,7 @@ __global__ void __launch_bounds__(256) decode_prepare_kernel(const void* __restr
         for (int b = 0; b * 8 < s_n[j]; ++b)
         {
             const int t = s_tile0[j] + b, n = s_n[j] - b * 8 < 8 ? s_n[j] - b * 8 : 8;
-            route->expert[t] = slot_e[j]; route->nrows[t] = (unsigned char) n;
+            route->expert[t] = slot_e[j]; route->nrows[t] = (unsigned char) n; route->rowbase[t] = (short) (s_rb[j] + b * 8);
             for (int i = 0; i < 8; ++i)
             {
                 route->rows[t][i] = s_rows[j][b * 8 + (i < n ? i : 0)];
@@ -196,6 +199,7 @@ struct DecodeArgs
     const float* xscale;   // [R][H/32] (Q8)
     __half* act;           // [tiles][8][I] gate_up output = down input
     float* ascale;         // [tiles][8][I/32] (Q8)
+    float* G;              // I <= 2048 path: [pick rows][gate | up][I] fp32 sums (shares memory with act)
     float* y;              // [R][H] (expert-parallel: base of two slots, the step's slot is chosen by *gen_ptr & 1)
     const unsigned* gen_ptr; size_t slot_stride;
     unsigned* status;
@@ -204,13 +208,14 @@ struct DecodeArgs
 // Two 64-column blocks (one scale group) of a 64-row group: 4 strips x 8 steps of MMAs on the tile, added into acc with
 // the scales applied. wsm = shared address of the first block's 2 KB unit; the second follows it.
 template <bool GROUPED, bool Q8>
-__device__ __forceinline__ void consume_group(uint32_t wsm, const Pre& pr, float (*acc)[4], int lane)
+__device__ __forceinline__ void consume_group(uint32_t wsm, const uint32_t (&bx)[2][8], const uint4 sc, const float4 sx0, const float4 sx1,
+                                              float (*acc)[4], int lane)
 {
 #if defined(HMOE_EXP) && HMOE_EXP == 1
-    { const uint4 v = lds128(wsm + lane * 16); acc[0][0] += __uint_as_float(v.x) * __uint_as_float(pr.bx[0][0] ^ pr.sc.x); return; }
+    { const uint4 v = lds128(wsm + lane * 16); acc[0][0] += __uint_as_float(v.x) * __uint_as_float(bx[0][0] ^ sc.x); return; }
 #endif
-    const uint32_t scw[4] = {pr.sc.x, pr.sc.y, pr.sc.z, pr.sc.w};
-    const float sxa[4] = {pr.sx[0].x, pr.sx[0].y, pr.sx[0].z, pr.sx[0].w}, sxb[4] = {pr.sx[1].x, pr.sx[1].y, pr.sx[1].z, pr.sx[1].w};
+    const uint32_t scw[4] = {sc.x, sc.y, sc.z, sc.w};
+    const float sxa[4] = {sx0.x, sx0.y, sx0.z, sx0.w}, sxb[4] = {sx1.x, sx1.y, sx1.z, sx1.w};
     // The four strips' sums are independent MMA chains; the steps are interleaved across strips so that consecutive MMAs
     // never wait on each other.
     float part[4][4];
@@ -232,9 +237,9 @@ __device__ __forceinline__ void consume_group(uint32_t wsm, const Pre& pr, float
                 uint32_t a[4];
                 frag_from_codes(w, a);
 #if defined(HMOE_EXP) && HMOE_EXP == 2
-                part[s][0] += __uint_as_float(a[0] ^ a[1] ^ a[2] ^ a[3] ^ pr.bx[blk][2 * t] ^ pr.bx[blk][2 * t + 1]);
+                part[s][0] += __uint_as_float(a[0] ^ a[1] ^ a[2] ^ a[3] ^ bx[blk][2 * t] ^ bx[blk][2 * t + 1]);
 #else
-                mma_f16((GROUPED || Q8) ? part[s] : acc[s], a, pr.bx[blk][2 * t], pr.bx[blk][2 * t + 1]);
+                mma_f16((GROUPED || Q8) ? part[s] : acc[s], a, bx[blk][2 * t], bx[blk][2 * t + 1]);
 #endif
             }
             if (Q8 && (t & 1))
@@ -436,7 +441,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_gate_up_kernel(const Decod
                 if (16 * s + 2 * kw < KB)
                 {
                     if (!mbar_wait(full0 + (st * CW + warp) * 8, par, abort_flag, a.status)) { alive = false; break; }
-                    consume_group<GROUPED, Q8>(ring + st * STAGE_BYTES + warp * 4096, pc, acc, lane);
+                    consume_group<GROUPED, Q8>(ring + st * STAGE_BYTES + warp * 4096, pc.bx, pc.sc, pc.sx[0], pc.sx[1], acc, lane);
                 }
                 __syncwarp();
                 if (lane == 0) fill_next(st);
@@ -572,7 +577,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_down_kernel(const DecodeAr
                     prefetch<GROUPED, Q8>(nxt, 2 * warp, KB, pn);
                 }
                 if (!mbar_wait(full0 + st * 8, par, abort_flag, a.status)) { alive = false; break; }
-                if (32 * s + 2 * warp < KB) consume_group<GROUPED, Q8>(ring + st * STAGE_BYTES + warp * 4096, pc, acc, lane);
+                if (32 * s + 2 * warp < KB) consume_group<GROUPED, Q8>(ring + st * STAGE_BYTES + warp * 4096, pc.bx, pc.sc, pc.sx[0], pc.sx[1], acc, lane);
                 release_stage(free_cnt, st, it, total, lane, fill);
                 if (++st == NSTAGE) { st = 0; par ^= 1; }
                 pc = pn;
@@ -624,170 +629,281 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_down_kernel(const DecodeAr
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// down, for I <= 2048 (at most 32 blocks of 64 input columns per output row)
+// The streaming kernel of the H <= 6144, I <= 2048 path, used twice per call: gate_up (DOWN = false) and down (DOWN = true).
 //
-// Items are (tile, 64-row group of the output) with the row group fastest: a block walks an expert's matrix in address
-// order, and the tile, hence the activations, stays the same over a long run of items. Warp w = (kq = w / 4, strip = w % 4)
-// owns 16 output rows and a quarter of the input columns (U <= 8 blocks): its activation fragments for those columns live
-// in registers for the whole tile, so the inner loop reads nothing but the ring. The four warps of a column quarter share a
-// ring of NSTAGE slots of 16 KB (their quarter of the item, contiguous in memory); the warp that frees a slot last issues
-// the copy of the item NSTAGE ahead into it. Each warp ends an item with its 16 rows x (real tile columns) partial sums,
-// which go to y as fp32 reductions in global memory: four per output element (one per column quarter), nothing is kept in
-// shared memory between items and no warp waits for another except through the ring.
-template <bool GROUPED, bool Q8>
-__global__ void __launch_bounds__(NTHREADS, 1) decode_down_resident_kernel(const DecodeArgs a)
+// An item is (tile, matrix, 64-row group of the output): 64 rows x all K input columns of codes (gate_up: 192 KB for
+// K = 6144, down: 64 KB). Items are dealt out to the blocks as contiguous ranges with the row group fastest, then the
+// matrix (gate, up), then the tile, so a block walks the matrices in address order and stays with one tile - one set of
+// activations - for a long time. The K columns are cut into KC chunks of 2048; warp w owns the 128 columns
+// [2048 kc + 128 w, + 128) of every chunk: one scale group, 4 KB of codes, contiguous in memory. Its activation fragments
+// for those columns (16 registers per chunk) stay in registers for the whole tile, so the inner loop reads nothing but
+// shared memory. Every warp has a private ring of NSTAGE slots (4 KB of codes + the 128 bytes of bf16 scales of the same
+// 64 rows x 128 columns), each with its own mbarrier; when the warp has read a slot its lane 0 at once issues the copies
+// for the slot's next use, so the warps stream independently and no warp ever waits for another.
+// A warp ends an item with a 64 x 8 partial tile over its KC x 128 columns; the real tile columns are added to the result
+// with fp32 reductions in global memory (sixteen per output element, one per warp):
+//   gate_up -> G[pick row][gate | up][I]  (zeroed by the prepare kernel; pick row = Route::rowbase[tile] + tile column)
+//   down    -> y[row][H]
+// Between the two launches nothing else runs: the down kernel turns G into its own MMA operand when it enters a tile
+// (SiLU(gate) * up * routing weight, in the int8 mode followed by the CPU engine's second int8 round trip).
+__device__ __forceinline__ void red_add(float* p, float v)
+{
+    asm volatile("red.global.add.f32 [%0], %1;" ::"l"(__cvta_generic_to_global(p)), "f"(v) : "memory");
+}
+
+struct StreamSmem
+{
+    static constexpr int SLOT = 4096 + 128;
+    static constexpr int bars = NSTAGE * CW * SLOT;
+    static constexpr int flags = bars + NSTAGE * CW * 8;
+    static constexpr int total = flags + 16;
+};
+
+template <bool GROUPED, bool Q8, bool DOWN, int KC>
+__global__ void __launch_bounds__(NTHREADS, 1) decode_stream_kernel(const DecodeArgs a)
 {
     extern __shared__ __align__(1024) unsigned char smem[];
-    constexpr int SLOT = STAGE_BYTES / 4;
+    constexpr int SLOT = StreamSmem::SLOT;
     const uint32_t sbase = smem_u32(smem);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, kq = warp >> 2, s = warp & 3, g = lane >> 2, q = lane & 3;
-    const uint32_t ring = sbase + SmemLayout::ring + kq * NSTAGE * SLOT, full0 = sbase + SmemLayout::bars + kq * NSTAGE * 8;
-    int* free_cnt = (int*) (smem + SmemLayout::gu) + kq * NSTAGE;
-    volatile int* abort_flag = (volatile int*) (smem + SmemLayout::flags);
-    float* const yout = a.y + (a.gen_ptr ? (size_t) (*a.gen_ptr & 1u) * a.slot_stride : 0);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
+    const uint32_t ring = sbase + warp * SLOT, full0 = sbase + StreamSmem::bars + warp * 8;      // slot st: + st * CW * SLOT / + st * CW * 8
+    volatile int* abort_flag = (volatile int*) (smem + StreamSmem::flags);
     if (threadIdx.x == 0)
     {
-        for (int i = 0; i < 4 * NSTAGE; ++i) { mbar_init(sbase + SmemLayout::bars + i * 8, 1); ((int*) (smem + SmemLayout::gu))[i] = 0; }
+        for (int i = 0; i < NSTAGE * CW; ++i) mbar_init(sbase + StreamSmem::bars + i * 8, 1);
         *abort_flag = 0;
         fence_barrier_init();
     }
     __syncthreads();
     const Route* rt = a.route;
-    const int NG = a.H / 64, KB = a.I / 64, U = 2 * ((KB + 7) / 8);
-    const int nu = KB - kq * U < 0 ? 0 : (KB - kq * U < U ? KB - kq * U : U);       // this quarter's blocks (even)
-    const int nt = rt->ntiles, P = nt * NG;
+    const int K = DOWN ? a.I : a.H, N = DOWN ? a.H : a.I;          // input columns and output rows of one matrix
+    const int KB = K / 64, NG = N / 64, J = DOWN ? NG : 2 * NG;
+    const int P = rt->ntiles * J;
     const int p0 = (int) ((long long) P * blockIdx.x / gridDim.x), p1 = (int) ((long long) P * (blockIdx.x + 1) / gridDim.x);
-    const int total = p1 - p0;
-    if (total > 0 && nu > 0)
+    float* const out0 = DOWN ? a.y + (a.gen_ptr ? (size_t) (*a.gen_ptr & 1u) * a.slot_stride : 0) : a.G;
+    if (p0 < p1 && 2 * warp < KB)
     {
-        auto fill = [&](int i) {
-            const int p = p0 + i, t = p / NG, r = p % NG, e = rt->expert[t];
-            const char* src = (const char*) (e >= 0 ? (const void*) a.down_w[e] : a.sh_dw) + ((size_t) r * KB + kq * U) * 2048;
-            const uint32_t slot = (uint32_t) i % NSTAGE;
-            mbar_expect_tx(full0 + slot * 8, nu * 2048);
-            bulk_g2s(ring + slot * SLOT, src, nu * 2048, full0 + slot * 8);
+        // ---- fill cursor (lane 0): the next slot to request is chunk f_kc of item (f_tile, f_j)
+        int f_p = p0, f_tile = p0 / J, f_j = p0 % J, f_kc = 0;
+        const char* f_w = nullptr; const char* f_s = nullptr;
+        auto fill_next = [&](uint32_t slot) {
+            if (f_p >= p1) return;
+            const int mat = (!DOWN && f_j >= NG) ? 1 : 0, gr = f_j - mat * NG;
+            if (f_w == nullptr || (gr == 0 && f_kc == 0))
+            {
+                const int e = rt->expert[f_tile];
+                const void* w = DOWN ? (e >= 0 ? (const void*) a.down_w[e] : a.sh_dw)
+                                     : (mat ? (e >= 0 ? (const void*) a.up_w[e] : a.sh_uw) : (e >= 0 ? (const void*) a.gate_w[e] : a.sh_gw));
+                f_w = (const char*) w + (size_t) warp * 4096;
+                if (GROUPED)
+                {
+                    const void* sc = DOWN ? (e >= 0 ? (const void*) a.down_s[e] : a.sh_ds)
+                                          : (mat ? (e >= 0 ? (const void*) a.up_s[e] : a.sh_us) : (e >= 0 ? (const void*) a.gate_s[e] : a.sh_gs));
+                    f_s = (const char*) sc + (size_t) warp * 128;
+                }
+            }
+            const uint32_t bar = full0 + slot * CW * 8, dst = ring + slot * CW * SLOT;
+            mbar_expect_tx(bar, GROUPED ? SLOT : 4096);
+            bulk_g2s(dst, f_w + ((size_t) gr * KB + f_kc * 32) * 2048, 4096, bar);
+            if (GROUPED) bulk_g2s(dst + 4096, f_s + ((size_t) gr * (K / 128) + f_kc * 16) * 128, 128, bar);
+            if (++f_kc == KC || f_kc * 32 + 2 * warp >= KB)
+            {
+                f_kc = 0; ++f_p;
+                if (++f_j == J) { f_j = 0; ++f_tile; f_w = nullptr; }
+            }
         };
-        if (s == 0 && lane == 0)
-            for (int i = 0; i < NSTAGE && i < total; ++i) fill(i);
-        uint32_t bfr[8][8];                   // activation fragments of this lane's tile row: block u, word 2t + h of 16-column step t
-        int nrows = 0, rowA = 0, rowB = 0;
-        const char* scp = nullptr; const float* sdp = nullptr; const float* xsA = nullptr; const float* xsB = nullptr;
+        if (lane == 0)
+            for (uint32_t i = 0; i < NSTAGE; ++i) fill_next(i);
+
+        // ---- consume (all lanes)
+        uint32_t bx[KC][2][8];                  // the tile's activation fragments of this warp's columns
+        float4 sx[KC][2];                       // Q8: their scales per 32 columns for tile columns 2q and 2q + 1
+        #pragma unroll
+        for (int kc = 0; kc < KC; ++kc) sx[kc][0] = sx[kc][1] = make_float4(1.f, 1.f, 1.f, 1.f);
+        int nrows = 0;
+        float* outA = nullptr; float* outB = nullptr;         // result rows of tile columns 2q and 2q + 1, at this lane's row g
+        const float* sdp[2] = {nullptr, nullptr};             // !GROUPED: per-row scales, at this lane's row g
         auto enter_tile = [&](int tile) {
             const int e = rt->expert[tile];
-            nrows = rt->nrows[tile]; rowA = rt->rows[tile][2 * q]; rowB = rt->rows[tile][2 * q + 1];
-            const char* xb = (const char*) (a.act + ((size_t) tile * 8 + g) * a.I) + (size_t) kq * U * 128 + q * 32;
-            #pragma unroll
-            for (int u = 0; u < 8; ++u)
+            nrows = rt->nrows[tile];
+            if (!DOWN)
             {
-                uint4 v0 = make_uint4(0, 0, 0, 0), v1 = v0;
-                if (u < nu) { v0 = ldg128(xb + u * 128); v1 = ldg128(xb + u * 128 + 16); }
-                bfr[u][0] = v0.x; bfr[u][1] = v0.y; bfr[u][2] = v0.z; bfr[u][3] = v0.w;
-                bfr[u][4] = v1.x; bfr[u][5] = v1.y; bfr[u][6] = v1.z; bfr[u][7] = v1.w;
-            }
-            if (Q8) { xsA = a.ascale + ((size_t) tile * 8 + 2 * q) * (a.I / 32) + kq * U * 2; xsB = xsA + a.I / 32; }
-            const void* sp = e >= 0 ? (const void*) a.down_s[e] : a.sh_ds;
-            if (GROUPED) scp = (const char*) sp + ((size_t) (kq * U / 2) * 64 + g * 8 + 2 * s) * 2;
-            else sdp = (const float*) sp + s * 16 + g;
-        };
-        // scales of this warp's rows for one item: GROUPED, word j = bf16 pair (row strip*16 + g, + 8) of 128-column group j
-        auto load_scales = [&](int gr, uint32_t* sc, float* sd) {
-            if (GROUPED)
-            {
+                const char* xb = (const char*) (a.xf + (size_t) rt->rows[tile][g] * a.H) + (size_t) warp * 256 + q * 32;
                 #pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    if (2 * j < nu) sc[j] = __ldg((const uint32_t*) (scp + ((size_t) gr * (a.I / 128) + j) * 128));
-            }
-            else { sd[0] = __ldg(sdp + gr * 64); sd[1] = __ldg(sdp + gr * 64 + 8); }
-        };
-        int tile = p0 / NG, gr = p0 % NG;
-        enter_tile(tile);
-        uint32_t sc[4] = {0, 0, 0, 0};
-        float sd[2] = {1.f, 1.f};
-        load_scales(gr, sc, sd);
-        uint32_t st = 0, par = 0;
-        for (int i = 0; i < total; ++i)
-        {
-            uint32_t scn[4] = {0, 0, 0, 0};
-            float sdn[2] = {1.f, 1.f};
-            const bool same_tile = gr + 1 < NG;
-            if (same_tile && i + 1 < total) load_scales(gr + 1, scn, sdn);          // one item ahead
-            if (!mbar_wait(full0 + st * 8, par, abort_flag, a.status)) break;
-            const uint32_t wsm = ring + st * SLOT + s * 512 + lane * 16;
-            float acc[4] = {0.f, 0.f, 0.f, 0.f}, pa[4] = {0.f, 0.f, 0.f, 0.f}, pb[4] = {0.f, 0.f, 0.f, 0.f};
-            #pragma unroll
-            for (int j = 0; j < 4; ++j)
-            {
-                if (2 * j >= nu) break;
-                float s0 = 1.f, s1 = 1.f;
-                if (GROUPED) { s0 = __uint_as_float(sc[j] << 16); s1 = __uint_as_float(sc[j] & 0xffff0000u); }
-                #pragma unroll
-                for (int uu = 0; uu < 2; ++uu)
+                for (int kc = 0; kc < KC; ++kc)
                 {
-                    const int u = 2 * j + uu;
-                    const uint4 w4 = lds128(wsm + u * 2048);
-                    float2 sxa = make_float2(1.f, 1.f), sxb = sxa;
-                    if (Q8) { sxa = *(const float2*) (xsA + 2 * u); sxb = *(const float2*) (xsB + 2 * u); }
-                    #pragma unroll
-                    for (int t = 0; t < 4; ++t)
+                    uint4 b0 = make_uint4(0, 0, 0, 0), b1 = b0, b2 = b0, b3 = b0;
+                    if (kc * 32 + 2 * warp < KB)
                     {
-                        const uint32_t w = t == 0 ? w4.x : t == 1 ? w4.y : t == 2 ? w4.z : w4.w;
-                        uint32_t af[4];
-                        frag_from_codes(w, af);
-                        // two independent MMA chains: in the int8 mode one per 32 columns (exact integer sums), else alternating steps
-                        mma_f16((Q8 ? (t >> 1) : (t & 1)) ? pb : pa, af, bfr[u][2 * t], bfr[u][2 * t + 1]);
+                        const char* xk = xb + kc * 4096;
+                        b0 = ldg128(xk); b1 = ldg128(xk + 16); b2 = ldg128(xk + 128); b3 = ldg128(xk + 144);
+                        if (Q8)
+                        {
+                            sx[kc][0] = *(const float4*) (a.xscale + (size_t) rt->rows[tile][2 * q] * (a.H / 32) + 64 * kc + 4 * warp);
+                            sx[kc][1] = *(const float4*) (a.xscale + (size_t) rt->rows[tile][2 * q + 1] * (a.H / 32) + 64 * kc + 4 * warp);
+                        }
                     }
-                    if (Q8)
+                    bx[kc][0][0] = b0.x; bx[kc][0][1] = b0.y; bx[kc][0][2] = b0.z; bx[kc][0][3] = b0.w;
+                    bx[kc][0][4] = b1.x; bx[kc][0][5] = b1.y; bx[kc][0][6] = b1.z; bx[kc][0][7] = b1.w;
+                    bx[kc][1][0] = b2.x; bx[kc][1][1] = b2.y; bx[kc][1][2] = b2.z; bx[kc][1][3] = b2.w;
+                    bx[kc][1][4] = b3.x; bx[kc][1][5] = b3.y; bx[kc][1][6] = b3.z; bx[kc][1][7] = b3.w;
+                }
+                const size_t rb = (size_t) rt->rowbase[tile] + 2 * q;
+                outA = a.G + rb * 2 * a.I + g; outB = outA + 2 * a.I;
+                if (!GROUPED)
+                {
+                    sdp[0] = (const float*) (e >= 0 ? (const void*) a.gate_s[e] : a.sh_gs) + g;
+                    sdp[1] = (const float*) (e >= 0 ? (const void*) a.up_s[e] : a.sh_us) + g;
+                }
+            }
+            else
+            {
+                // this lane's operand words: tile column g, columns 128 w + 64 blk + 16 t + 8 h + 2 q (+ 1) -> word [blk][2t + h]
+                float v[2][8][2];
+                if (g < nrows)
+                {
+                    const float* gp = a.G + ((size_t) rt->rowbase[tile] + g) * 2 * a.I + (size_t) warp * 128 + 2 * q;
+                    const float wt = rt->w[tile][g];
+                    #pragma unroll
+                    for (int blk = 0; blk < 2; ++blk)
                     {
-                        acc[0] = fmaf(pa[0], sxa.x * s0, acc[0]); acc[1] = fmaf(pa[1], sxb.x * s0, acc[1]);
-                        acc[2] = fmaf(pa[2], sxa.x * s1, acc[2]); acc[3] = fmaf(pa[3], sxb.x * s1, acc[3]);
-                        acc[0] = fmaf(pb[0], sxa.y * s0, acc[0]); acc[1] = fmaf(pb[1], sxb.y * s0, acc[1]);
-                        acc[2] = fmaf(pb[2], sxa.y * s1, acc[2]); acc[3] = fmaf(pb[3], sxb.y * s1, acc[3]);
+                        float2 gg[8], uu[8];                    // all loads of the block first, then the arithmetic
                         #pragma unroll
-                        for (int k = 0; k < 4; ++k) pa[k] = pb[k] = 0.f;
+                        for (int wd = 0; wd < 8; ++wd)
+                        {
+                            const int col = blk * 64 + (wd >> 1) * 16 + (wd & 1) * 8;
+                            gg[wd] = __ldcg((const float2*) (gp + col)); uu[wd] = __ldcg((const float2*) (gp + a.I + col));
+                        }
+                        #pragma unroll
+                        for (int wd = 0; wd < 8; ++wd)
+                        {
+                            // fp16 operands: the fast exponential is far inside their rounding; the int8 mode follows the CPU engine
+                            v[blk][wd][0] = gg[wd].x / (1.f + (Q8 ? expf(-gg[wd].x) : __expf(-gg[wd].x))) * uu[wd].x * wt;
+                            v[blk][wd][1] = gg[wd].y / (1.f + (Q8 ? expf(-gg[wd].y) : __expf(-gg[wd].y))) * uu[wd].y * wt;
+                        }
                     }
                 }
-                if (GROUPED && !Q8)
+                else
                 {
-                    acc[0] = fmaf(s0, pa[0] + pb[0], acc[0]); acc[1] = fmaf(s0, pa[1] + pb[1], acc[1]);
-                    acc[2] = fmaf(s1, pa[2] + pb[2], acc[2]); acc[3] = fmaf(s1, pa[3] + pb[3], acc[3]);
                     #pragma unroll
-                    for (int k = 0; k < 4; ++k) pa[k] = pb[k] = 0.f;
+                    for (int blk = 0; blk < 2; ++blk)
+                        #pragma unroll
+                        for (int wd = 0; wd < 8; ++wd) v[blk][wd][0] = v[blk][wd][1] = 0.f;
                 }
-            }
-            if (!GROUPED && !Q8)
-            {
-                #pragma unroll
-                for (int k = 0; k < 4; ++k) acc[k] = pa[k] + pb[k];
-            }
-            // the slot is read: the last of the quarter's four warps to say so refills it
-            __syncwarp();
-            if (lane == 0)
-            {
-                __threadfence_block();
-                if (atomicAdd(free_cnt + st, 1) == 3)
+                if (Q8)
                 {
-                    free_cnt[st] = 0;
-                    __threadfence_block();
-                    if (i + NSTAGE < total) fill(i + NSTAGE);
+                    // second int8 round trip of the CPU engine (cpuband.cpp:200-207): 32 consecutive values = words 4 hf .. 4 hf + 3
+                    // of a block over the four lanes of this tile column
+                    float sc[4];
+                    #pragma unroll
+                    for (int blk = 0; blk < 2; ++blk)
+                        #pragma unroll
+                        for (int hf = 0; hf < 2; ++hf)
+                        {
+                            float m = 0.f;
+                            #pragma unroll
+                            for (int wd = 4 * hf; wd < 4 * hf + 4; ++wd) m = fmaxf(m, fmaxf(fabsf(v[blk][wd][0]), fabsf(v[blk][wd][1])));
+                            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+                            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+                            const float s = m > 0.f ? __fdiv_rn(m, 127.f) : 1.f, inv = __fdiv_rn(1.f, s);
+                            #pragma unroll
+                            for (int wd = 4 * hf; wd < 4 * hf + 4; ++wd)
+                            {
+                                v[blk][wd][0] = (float) __float2int_rn(__fmul_rn(v[blk][wd][0], inv));
+                                v[blk][wd][1] = (float) __float2int_rn(__fmul_rn(v[blk][wd][1], inv));
+                            }
+                            sc[blk * 2 + hf] = s;
+                        }
+                    // the MMA results of this lane are tile columns 2q and 2q + 1: fetch their scales
+                    float sa[4], sb[4];
+                    #pragma unroll
+                    for (int k = 0; k < 4; ++k) { sa[k] = __shfl_sync(0xffffffffu, sc[k], 8 * q); sb[k] = __shfl_sync(0xffffffffu, sc[k], 8 * q + 4); }
+                    sx[0][0] = make_float4(sa[0], sa[1], sa[2], sa[3]); sx[0][1] = make_float4(sb[0], sb[1], sb[2], sb[3]);
+                }
+                #pragma unroll
+                for (int blk = 0; blk < 2; ++blk)
+                    #pragma unroll
+                    for (int wd = 0; wd < 8; ++wd)
+                    {
+                        const __half2 h = __floats2half2_rn(v[blk][wd][0], v[blk][wd][1]);
+                        bx[0][blk][wd] = *(const uint32_t*) &h;
+                    }
+                outA = out0 + (size_t) rt->rows[tile][2 * q] * a.H + g; outB = out0 + (size_t) rt->rows[tile][2 * q + 1] * a.H + g;
+                if (!GROUPED) sdp[0] = (const float*) (e >= 0 ? (const void*) a.down_s[e] : a.sh_ds) + g;
+            }
+        };
+        // !GROUPED: the eight per-row scales of this lane's rows for item jj, applied to the finished sums
+        auto load_row_scales = [&](int jj, float* sd) {
+            const int mat = (!DOWN && jj >= NG) ? 1 : 0, gr = jj - mat * NG;
+            #pragma unroll
+            for (int i = 0; i < 8; ++i) sd[i] = __ldg(sdp[mat] + gr * 64 + i * 8);
+        };
+        float sd[8];
+        #pragma unroll
+        for (int i = 0; i < 8; ++i) sd[i] = 1.f;
+        float acc[4][4];
+        #pragma unroll
+        for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+        uint32_t st = 0, par = 0;
+        int tile = p0 / J, j = p0 % J;
+        enter_tile(tile);
+        if (!GROUPED) load_row_scales(j, sd);
+        bool alive = true;
+        for (int p = p0; p < p1 && alive; ++p)
+        {
+            float sdn[8];
+            #pragma unroll
+            for (int k = 0; k < 8; ++k) sdn[k] = 1.f;
+            const bool same_tile = j + 1 < J;
+            if (!GROUPED && same_tile && p + 1 < p1) load_row_scales(j + 1, sdn);          // one item ahead
+            #pragma unroll
+            for (int kc = 0; kc < KC; ++kc)
+            {
+                if (kc * 32 + 2 * warp < KB)
+                {
+                    if (!mbar_wait(full0 + st * CW * 8, par, abort_flag, a.status)) { alive = false; break; }
+                    const uint32_t slot = ring + st * CW * SLOT;
+                    uint4 sc = make_uint4(0, 0, 0, 0);
+                    if (GROUPED) sc = lds128(slot + 4096 + g * 16);
+                    consume_group<GROUPED, Q8>(slot, bx[kc], sc, sx[kc][0], sx[kc][1], acc, lane);
+                    __syncwarp();
+                    if (lane == 0) fill_next(st);
+                    if (++st == NSTAGE) { st = 0; par ^= 1; }
                 }
             }
-            // this warp's 16 rows of the real tile columns join y
-            float* const yc = yout + gr * 64 + s * 16 + g;
-            if (2 * q < nrows) { atomicAdd(yc + (size_t) rowA * a.H, acc[0] * sd[0]); atomicAdd(yc + (size_t) rowA * a.H + 8, acc[2] * sd[1]); }
-            if (2 * q + 1 < nrows) { atomicAdd(yc + (size_t) rowB * a.H, acc[1] * sd[0]); atomicAdd(yc + (size_t) rowB * a.H + 8, acc[3] * sd[1]); }
-            if (++st == NSTAGE) { st = 0; par ^= 1; }
+            if (!alive) break;
+            // this warp's partial sums of the real tile columns join the result
+            #pragma unroll
+            for (int c = 0; c < 2; ++c)
+            {
+#if defined(HMOE_EXP) && HMOE_EXP == 6
+                if (acc[0][c] == 123.456f)
+#else
+                if (2 * q + c < nrows)
+#endif
+                {
+                    float* yr = (c ? outB : outA) + j * 64;
+                    #pragma unroll
+                    for (int ss = 0; ss < 4; ++ss)
+                    {
+                        red_add(yr + ss * 16, acc[ss][c] * sd[2 * ss]);
+                        red_add(yr + ss * 16 + 8, acc[ss][2 + c] * sd[2 * ss + 1]);
+                    }
+                }
+            }
+            #pragma unroll
+            for (int ss = 0; ss < 4; ++ss) acc[ss][0] = acc[ss][1] = acc[ss][2] = acc[ss][3] = 0.f;
             if (same_tile)
             {
-                ++gr;
+                ++j;
                 #pragma unroll
-                for (int j = 0; j < 4; ++j) sc[j] = scn[j];
-                sd[0] = sdn[0]; sd[1] = sdn[1];
+                for (int k = 0; k < 8; ++k) sd[k] = sdn[k];
             }
-            else if (i + 1 < total)
+            else if (p + 1 < p1)
             {
-                gr = 0; ++tile;
+                j = 0; ++tile;
                 enter_tile(tile);
-                load_scales(gr, sc, sd);
+                if (!GROUPED) load_row_scales(j, sd);
             }
         }
     }
@@ -840,6 +956,14 @@ int decode_phase_times(float* ms3)
     return HMOE_OK;
 }
 
+template <bool G, bool Q, int KC>
+static void launch_stream_gate_up(int grid, const DecodeArgs& a, cudaStream_t st)
+{
+    static bool first = true;
+    if (first) { cudaFuncSetAttribute(decode_stream_kernel<G, Q, false, KC>, cudaFuncAttributeMaxDynamicSharedMemorySize, StreamSmem::total); first = false; }
+    decode_stream_kernel<G, Q, false, KC><<<grid, NTHREADS, StreamSmem::total, st>>>(a);
+}
+
 template <bool G, bool Q>
 static void launch_pair(int grid, const DecodeArgs& a, int R, cudaStream_t st, bool first)
 {
@@ -848,11 +972,15 @@ static void launch_pair(int grid, const DecodeArgs& a, int R, cudaStream_t st, b
     {
         cudaFuncSetAttribute(decode_gate_up_kernel<G, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout::total);
         cudaFuncSetAttribute(decode_down_kernel<G, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout::total);
-        cudaFuncSetAttribute(decode_down_resident_kernel<G, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout::total);
+        cudaFuncSetAttribute(decode_stream_kernel<G, Q, true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, StreamSmem::total);
     }
-    decode_gate_up_kernel<G, Q><<<grid, NTHREADS, SmemLayout::total, st>>>(a);
+    const bool resident = a.I <= 2048 && a.H <= 6144;      // the activation fragments of a tile fit in registers
+    if (!resident) decode_gate_up_kernel<G, Q><<<grid, NTHREADS, SmemLayout::total, st>>>(a);
+    else if (a.H <= 2048) launch_stream_gate_up<G, Q, 1>(grid, a, st);
+    else if (a.H <= 4096) launch_stream_gate_up<G, Q, 2>(grid, a, st);
+    else launch_stream_gate_up<G, Q, 3>(grid, a, st);
     if (g_prof) cudaEventRecord(g_ev[2], st);
-    if (a.I <= 2048) decode_down_resident_kernel<G, Q><<<grid, NTHREADS, SmemLayout::total, st>>>(a);
+    if (resident) decode_stream_kernel<G, Q, true, 1><<<grid, NTHREADS, StreamSmem::total, st>>>(a);
     else decode_down_kernel<G, Q><<<grid, NTHREADS, SmemLayout::total, st>>>(a, R);
     if (g_prof) cudaEventRecord(g_ev[3], st);
 }
@@ -887,12 +1015,13 @@ int decode_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t
     const int has_shared = L->sh_gate_w != nullptr;
     if (g_prof) cudaEventRecord(g_ev[0], st);
     decode_prepare_kernel<<<R + 1, 256, 0, st>>>(x, x_dtype == HMOE_BF16, sel, (const __half*) rw, R, H, L->topk, lo, n_local, has_shared,
-                                                 act_quant, xf, xscale, route, sh_mod, sh_rem, gen_ptr);
+                                                 act_quant, xf, xscale, route, sh_mod, sh_rem, gen_ptr,
+                                                 (float4*) act, (I <= 2048 && H <= 6144) ? (L->topk + 1) * 2 * I / 4 : 0);
     DecodeArgs a;
     a.H = H; a.I = I;
     a.gate_w = L->gate_w; a.up_w = L->up_w; a.down_w = L->down_w; a.gate_s = L->gate_s; a.up_s = L->up_s; a.down_s = L->down_s;
     a.sh_gw = L->sh_gate_w; a.sh_uw = L->sh_up_w; a.sh_dw = L->sh_down_w; a.sh_gs = L->sh_gate_s; a.sh_us = L->sh_up_s; a.sh_ds = L->sh_down_s;
-    a.route = route; a.xf = xf; a.xscale = xscale; a.act = act; a.ascale = ascale; a.y = y; a.status = status;
+    a.route = route; a.xf = xf; a.xscale = xscale; a.act = act; a.ascale = ascale; a.G = (float*) act; a.y = y; a.status = status;
     a.gen_ptr = gen_ptr; a.slot_stride = slot_stride;
     const int grid = g_sms;
     const int v = (L->group ? 2 : 0) + (act_quant ? 1 : 0);
