@@ -758,76 +758,54 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_stream_kernel(const Decode
             }
             else
             {
-                // this lane's operand words: tile column g, columns 128 w + 64 blk + 16 t + 8 h + 2 q (+ 1) -> word [blk][2t + h]
-                float v[2][8][2];
-                if (g < nrows)
-                {
-                    const float* gp = a.G + ((size_t) rt->rowbase[tile] + g) * 2 * a.I + (size_t) warp * 128 + 2 * q;
-                    const float wt = rt->w[tile][g];
-                    #pragma unroll
-                    for (int blk = 0; blk < 2; ++blk)
-                    {
-                        float2 gg[8], uu[8];                    // all loads of the block first, then the arithmetic
-                        #pragma unroll
-                        for (int wd = 0; wd < 8; ++wd)
-                        {
-                            const int col = blk * 64 + (wd >> 1) * 16 + (wd & 1) * 8;
-                            gg[wd] = __ldcg((const float2*) (gp + col)); uu[wd] = __ldcg((const float2*) (gp + a.I + col));
-                        }
-                        #pragma unroll
-                        for (int wd = 0; wd < 8; ++wd)
-                        {
-                            // fp16 operands: the fast exponential is far inside their rounding; the int8 mode follows the CPU engine
-                            v[blk][wd][0] = gg[wd].x / (1.f + (Q8 ? expf(-gg[wd].x) : __expf(-gg[wd].x))) * uu[wd].x * wt;
-                            v[blk][wd][1] = gg[wd].y / (1.f + (Q8 ? expf(-gg[wd].y) : __expf(-gg[wd].y))) * uu[wd].y * wt;
-                        }
-                    }
-                }
-                else
-                {
-                    #pragma unroll
-                    for (int blk = 0; blk < 2; ++blk)
-                        #pragma unroll
-                        for (int wd = 0; wd < 8; ++wd) v[blk][wd][0] = v[blk][wd][1] = 0.f;
-                }
-                if (Q8)
-                {
-                    // second int8 round trip of the CPU engine (cpuband.cpp:200-207): 32 consecutive values = words 4 hf .. 4 hf + 3
-                    // of a block over the four lanes of this tile column
-                    float sc[4];
-                    #pragma unroll
-                    for (int blk = 0; blk < 2; ++blk)
-                        #pragma unroll
-                        for (int hf = 0; hf < 2; ++hf)
-                        {
-                            float m = 0.f;
-                            #pragma unroll
-                            for (int wd = 4 * hf; wd < 4 * hf + 4; ++wd) m = fmaxf(m, fmaxf(fabsf(v[blk][wd][0]), fabsf(v[blk][wd][1])));
-                            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-                            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
-                            const float s = m > 0.f ? __fdiv_rn(m, 127.f) : 1.f, inv = __fdiv_rn(1.f, s);
-                            #pragma unroll
-                            for (int wd = 4 * hf; wd < 4 * hf + 4; ++wd)
-                            {
-                                v[blk][wd][0] = (float) __float2int_rn(__fmul_rn(v[blk][wd][0], inv));
-                                v[blk][wd][1] = (float) __float2int_rn(__fmul_rn(v[blk][wd][1], inv));
-                            }
-                            sc[blk * 2 + hf] = s;
-                        }
-                    // the MMA results of this lane are tile columns 2q and 2q + 1: fetch their scales
-                    float sa[4], sb[4];
-                    #pragma unroll
-                    for (int k = 0; k < 4; ++k) { sa[k] = __shfl_sync(0xffffffffu, sc[k], 8 * q); sb[k] = __shfl_sync(0xffffffffu, sc[k], 8 * q + 4); }
-                    sx[0][0] = make_float4(sa[0], sa[1], sa[2], sa[3]); sx[0][1] = make_float4(sb[0], sb[1], sb[2], sb[3]);
-                }
+                // The operand of tile column t is computed by the whole warp, lane L taking columns 2L, 2L + 1 of each of the
+                // warp's two blocks (= word L of the block), and handed to the lanes g == t in the order the MMAs read:
+                // word [blk][2t' + h] of lane (g, q) is word 8t' + 4h + q of the block.
                 #pragma unroll
                 for (int blk = 0; blk < 2; ++blk)
                     #pragma unroll
-                    for (int wd = 0; wd < 8; ++wd)
+                    for (int wd = 0; wd < 8; ++wd) bx[0][blk][wd] = 0u;
+                float sa[4] = {1.f, 1.f, 1.f, 1.f}, sb[4] = {1.f, 1.f, 1.f, 1.f};
+                const float* gp = a.G + (size_t) rt->rowbase[tile] * 2 * a.I + (size_t) warp * 128 + 2 * lane;
+                for (int t = 0; t < nrows; ++t, gp += 2 * a.I)
+                {
+                    const float2 g0 = __ldcg((const float2*) gp), g1 = __ldcg((const float2*) (gp + 64));
+                    const float2 u0 = __ldcg((const float2*) (gp + a.I)), u1 = __ldcg((const float2*) (gp + a.I + 64));
+                    const float wt = rt->w[tile][t];
+                    // fp16 operands: the fast exponential is far inside their rounding; the int8 mode follows the CPU engine
+                    float v[2][2];
+                    v[0][0] = g0.x / (1.f + (Q8 ? expf(-g0.x) : __expf(-g0.x))) * u0.x * wt;
+                    v[0][1] = g0.y / (1.f + (Q8 ? expf(-g0.y) : __expf(-g0.y))) * u0.y * wt;
+                    v[1][0] = g1.x / (1.f + (Q8 ? expf(-g1.x) : __expf(-g1.x))) * u1.x * wt;
+                    v[1][1] = g1.y / (1.f + (Q8 ? expf(-g1.y) : __expf(-g1.y))) * u1.y * wt;
+                    #pragma unroll
+                    for (int blk = 0; blk < 2; ++blk)
                     {
-                        const __half2 h = __floats2half2_rn(v[blk][wd][0], v[blk][wd][1]);
-                        bx[0][blk][wd] = *(const uint32_t*) &h;
+                        if (Q8)
+                        {
+                            // second int8 round trip of the CPU engine (cpuband.cpp:200-207): 32 consecutive values = 16 lanes
+                            float m = fmaxf(fabsf(v[blk][0]), fabsf(v[blk][1]));
+                            #pragma unroll
+                            for (int o = 8; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+                            const float sc = m > 0.f ? __fdiv_rn(m, 127.f) : 1.f, inv = __fdiv_rn(1.f, sc);
+                            v[blk][0] = (float) __float2int_rn(__fmul_rn(v[blk][0], inv));
+                            v[blk][1] = (float) __float2int_rn(__fmul_rn(v[blk][1], inv));
+                            // the MMA results of a lane are tile columns 2q and 2q + 1: those lanes keep this column's scales
+                            const float s_lo = __shfl_sync(0xffffffffu, sc, 0), s_hi = __shfl_sync(0xffffffffu, sc, 16);
+                            if (2 * q == t) { sa[2 * blk] = s_lo; sa[2 * blk + 1] = s_hi; }
+                            if (2 * q + 1 == t) { sb[2 * blk] = s_lo; sb[2 * blk + 1] = s_hi; }
+                        }
+                        const __half2 h = __floats2half2_rn(v[blk][0], v[blk][1]);
+                        const uint32_t word = *(const uint32_t*) &h;
+                        #pragma unroll
+                        for (int wd = 0; wd < 8; ++wd)
+                        {
+                            const uint32_t got = __shfl_sync(0xffffffffu, word, (wd >> 1) * 8 + (wd & 1) * 4 + q);
+                            if (g == t) bx[0][blk][wd] = got;
+                        }
                     }
+                }
+                if (Q8) { sx[0][0] = make_float4(sa[0], sa[1], sa[2], sa[3]); sx[0][1] = make_float4(sb[0], sb[1], sb[2], sb[3]); }
                 outA = out0 + (size_t) rt->rows[tile][2 * q] * a.H + g; outB = out0 + (size_t) rt->rows[tile][2 * q + 1] * a.H + g;
                 if (!GROUPED) sdp[0] = (const float*) (e >= 0 ? (const void*) a.down_s[e] : a.sh_ds) + g;
             }
