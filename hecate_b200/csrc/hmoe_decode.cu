@@ -55,6 +55,7 @@ __global__ void __launch_bounds__(256) decode_prepare_kernel(const void* __restr
     float4* __restrict__ gzero, int gzero_n)
 {
     const int tid = threadIdx.x;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // the next kernel's blocks may set up while this one runs
     if ((int) blockIdx.x < R)
     {
         const int r = blockIdx.x;
@@ -646,6 +647,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_down_kernel(const DecodeAr
 //   down    -> y[row][H]
 // Between the two launches nothing else runs: the down kernel turns G into its own MMA operand when it enters a tile
 // (SiLU(gate) * up * routing weight, in the int8 mode followed by the CPU engine's second int8 round trip).
+// Programmatic dependent launch: a kernel lets the next one in the stream start as its own blocks retire (the next kernel's
+// blocks set up their barriers and request their first weights meanwhile), and the next kernel waits here for the full
+// completion of its predecessor, memory included, before it reads anything the predecessor wrote. Both are no-ops for a
+// kernel launched without the attribute.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ void red_add(float* p, float v)
 {
     asm volatile("red.global.add.f32 [%0], %1;" ::"l"(__cvta_generic_to_global(p)), "f"(v) : "memory");
@@ -668,6 +676,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_stream_kernel(const Decode
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
     const uint32_t ring = sbase + warp * SLOT, full0 = sbase + StreamSmem::bars + warp * 8;      // slot st: + st * CW * SLOT / + st * CW * 8
     volatile int* abort_flag = (volatile int*) (smem + StreamSmem::flags);
+    pdl_launch_dependents();
     if (threadIdx.x == 0)
     {
         for (int i = 0; i < NSTAGE * CW; ++i) mbar_init(sbase + StreamSmem::bars + i * 8, 1);
@@ -675,6 +684,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_stream_kernel(const Decode
         fence_barrier_init();
     }
     __syncthreads();
+    // gate_up follows the prepare kernel, which wrote the route; down follows gate_up, but the route and the weights it
+    // needs to fill its rings are older than that: it waits only before it reads the gate / up sums.
+    if (!DOWN) pdl_wait();
     const Route* rt = a.route;
     const int K = DOWN ? a.I : a.H, N = DOWN ? a.H : a.I;          // input columns and output rows of one matrix
     const int KB = K / 64, NG = N / 64, J = DOWN ? NG : 2 * NG;
@@ -824,6 +836,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_stream_kernel(const Decode
         for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
         uint32_t st = 0, par = 0;
         int tile = p0 / J, j = p0 % J;
+        if (DOWN) pdl_wait();
         enter_tile(tile);
         if (!GROUPED) load_row_scales(j, sd);
         bool alive = true;
@@ -934,12 +947,25 @@ int decode_phase_times(float* ms3)
     return HMOE_OK;
 }
 
+// launch as a programmatic dependent of the previous kernel in the stream (see pdl_wait)
+template <typename Kern>
+static void launch_dependent(Kern kern, int grid, const DecodeArgs& a, cudaStream_t st)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(NTHREADS); cfg.dynamicSmemBytes = StreamSmem::total; cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = g_prof ? 0 : 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, kern, a);
+}
+
 template <bool G, bool Q, int KC>
 static void launch_stream_gate_up(int grid, const DecodeArgs& a, cudaStream_t st)
 {
     static bool first = true;
     if (first) { cudaFuncSetAttribute(decode_stream_kernel<G, Q, false, KC>, cudaFuncAttributeMaxDynamicSharedMemorySize, StreamSmem::total); first = false; }
-    decode_stream_kernel<G, Q, false, KC><<<grid, NTHREADS, StreamSmem::total, st>>>(a);
+    launch_dependent(decode_stream_kernel<G, Q, false, KC>, grid, a, st);
 }
 
 template <bool G, bool Q>
@@ -958,7 +984,7 @@ static void launch_pair(int grid, const DecodeArgs& a, int R, cudaStream_t st, b
     else if (a.H <= 4096) launch_stream_gate_up<G, Q, 2>(grid, a, st);
     else launch_stream_gate_up<G, Q, 3>(grid, a, st);
     if (g_prof) cudaEventRecord(g_ev[2], st);
-    if (resident) decode_stream_kernel<G, Q, true, 1><<<grid, NTHREADS, StreamSmem::total, st>>>(a);
+    if (resident) launch_dependent(decode_stream_kernel<G, Q, true, 1>, grid, a, st);
     else decode_down_kernel<G, Q><<<grid, NTHREADS, SmemLayout::total, st>>>(a, R);
     if (g_prof) cudaEventRecord(g_ev[3], st);
 }

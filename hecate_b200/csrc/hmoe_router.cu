@@ -4,6 +4,8 @@
 // sigmoid uses a fixed polynomial exp, so the selected experts are reproducible bit for bit by the CPU checker.
 //   logit[r][e]: lane L of a warp sums columns i*256 + L*8 + j (i outer, j inner) with fused multiply-adds, then five
 //   butterfly steps (xor 16, 8, 4, 2, 1) add the 32 partial sums.
+// One launch: the block that completes a group of four rows last also selects their experts. Router calls that overlap
+// on one device take different counter sets in rotation (sixteen of them).
 #include "hmoe_common.cuh"
 #include "hmoe_internal.h"
 
@@ -25,47 +27,144 @@ __device__ __forceinline__ void widen8(const uint4& v, float* f)
     }
 }
 
-template <bool XBF, bool WBF>
-__global__ void __launch_bounds__(RW * 32) router_logits_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ wt,
-                                                                int R, int H, int E, float* __restrict__ logits)
+constexpr int CTR_SLOTS = 16, CTR_GROUPS = 256;
+// Arrival counters of the row groups, one set per call slot (calls take slots in rotation, so that calls overlapping on
+// one device do not share counters unless more than CTR_SLOTS of them are in flight). Zero when the library is loaded;
+// the block that arrives last puts its counter back to zero.
+static __device__ unsigned g_router_ctr[CTR_SLOTS][CTR_GROUPS];
+
+// These kernels run once per layer on a handful of warps per SM: their duration is a chain of memory latencies, so every
+// group of loads is issued before its first use.
+
+// One warp selects one row: keys and activations of the E <= 256 experts in shared memory (512 words at `scratch`),
+// top-k rounds (max key, then lowest index holding it), weights. fresh: the logits were written by other blocks of the
+// same launch (read them past L1).
+__device__ __noinline__ void topk_row(const float* __restrict__ logits, const float* __restrict__ bias, int r, int E, int topk, float scale,
+                                      int64_t* __restrict__ sel, __half* __restrict__ rw, int lane, bool fresh, float* scratch)
 {
-    extern __shared__ __align__(16) uint16_t xs[];          // [RR][H]
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int r0 = blockIdx.y * RR, nr = R - r0 < RR ? R - r0 : RR;
-    for (int i = threadIdx.x * 8; i < RR * H; i += blockDim.x * 8)
+    float* s_act = scratch; unsigned* s_key = (unsigned*) (scratch + 256);
     {
-        const int r = i / H;
-        *(uint4*) (xs + i) = r < nr ? *(const uint4*) (x + (size_t) (r0 + r) * H + (i % H)) : make_uint4(0, 0, 0, 0);
+        // all of the row's logits and biases are requested before the first is used
+        float l[8], bb[8];
+        #pragma unroll
+        for (int i = 0; i < 8; ++i)
+        {
+            const int e = lane + 32 * i;
+            l[i] = e < E ? (fresh ? __ldcg(logits + (size_t) r * E + e) : logits[(size_t) r * E + e]) : 0.f;
+            bb[i] = (e < E && bias) ? __ldg(bias + e) : 0.f;
+        }
+        #pragma unroll
+        for (int i = 0; i < 8; ++i) { s_act[lane + 32 * i] = l[i]; s_key[lane + 32 * i] = __float_as_uint(bb[i]); }
     }
-    __syncthreads();
+    __syncwarp();
+    #pragma unroll 1
+    for (int e = lane; e < E; e += 32)
+    {
+        const float act = __fdiv_rn(1.f, __fadd_rn(1.f, det_expf(-s_act[e])));
+        const unsigned u = __float_as_uint(__fadd_rn(act, __uint_as_float(s_key[e])));
+        s_act[e] = act; s_key[e] = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    }
+    __syncwarp();
+    float sum = 0.f, mine_w = 0.f; int mine_id = 0;
+    #pragma unroll 1
+    for (int k = 0; k < topk; ++k)
+    {
+        unsigned lk = 0u; int li = lane;
+        #pragma unroll 1
+        for (int e = lane; e < E; e += 32) { const unsigned key = s_key[e]; if (key > lk) { lk = key; li = e; } }
+        const unsigned m = __reduce_max_sync(0xffffffffu, lk);
+        const unsigned bi = __reduce_min_sync(0xffffffffu, lk == m ? (unsigned) li : 0xffffffffu);
+        const float a = s_act[bi];
+        __syncwarp();
+        if (lane == 0) s_key[bi] = 0u;
+        __syncwarp();
+        sum = __fadd_rn(sum, a);
+        if (lane == k) { mine_w = a; mine_id = (int) bi; }
+    }
+    if (lane < topk)
+    {
+        sel[(size_t) r * topk + lane] = mine_id;
+        rw[(size_t) r * topk + lane] = __float2half_rn(__fdiv_rn(__fmul_rn(mine_w, scale), __fadd_rn(sum, 1e-20f)));
+    }
+}
+
+// Block (bx, by): experts 8 bx .. 8 bx + 7 (one per warp) x rows 4 by .. 4 by + 3, the columns in chunks of at most HC.
+// Lane 0 of every warp brings the chunk of its expert's weight row into shared memory with one bulk copy, so all of a
+// chunk's bytes are requested at once; meanwhile the block stages its rows as fp32 (two 16-byte halves per lane and step,
+// halves of all lanes side by side: conflict-free). The sums then run from shared memory in the fixed order.
+// With FUSED, the block that finishes a row group last (counted in g_router_ctr) also selects the group's experts.
+constexpr int HC = 6144;
+
+template <bool XBF, bool WBF, bool FUSED>
+__global__ void __launch_bounds__(RW * 32) router_logits_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ wt,
+                                                                int R, int H, int E, float* __restrict__ logits,
+                                                                const float* __restrict__ bias, int topk, float scale,
+                                                                int64_t* __restrict__ sel, __half* __restrict__ rw, int slot)
+{
+    extern __shared__ __align__(128) unsigned char rsm[];
+    __shared__ int s_last;
+    __shared__ int s_abort;
+    __shared__ __align__(8) unsigned long long s_bar[RW];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int hc = H < HC ? H : HC;                              // chunk length, a multiple of 256
+    float* xs = (float*) rsm;                                    // [RR][hc] fp32, see above
+    const uint32_t wsm = smem_u32(rsm) + RR * hc * 4 + warp * hc * 2, bar = smem_u32(&s_bar[warp]);
+    const int r0 = blockIdx.y * RR, nr = R - r0 < RR ? R - r0 : RR;
     const int e = blockIdx.x * RW + warp;
-    if (e >= E) return;
+    const uint16_t* w = wt + (size_t) (e < E ? e : 0) * H;
+    if (lane == 0) { mbar_init(bar, 1); fence_barrier_init(); }
+    if (threadIdx.x == 0) s_abort = 0;
+    __syncthreads();
     float acc[RR];
     #pragma unroll
     for (int r = 0; r < RR; ++r) acc[r] = 0.f;
-    const uint16_t* w = wt + (size_t) e * H;
-    // four 256-column steps per trip with their weight loads issued first; the additions stay in column order
-    for (int k0 = lane * 8; k0 < H; k0 += 1024)
+    uint32_t par = 0;
+    #pragma unroll 1
+    for (int c0 = 0; c0 < H; c0 += hc, par ^= 1)
     {
-        uint4 wv[4];
-        #pragma unroll
-        for (int u = 0; u < 4; ++u) wv[u] = k0 + u * 256 < H ? ldg128_nc(w + k0 + u * 256) : make_uint4(0, 0, 0, 0);
-        #pragma unroll
-        for (int u = 0; u < 4; ++u)
+        const int cl = H - c0 < hc ? H - c0 : hc;
+        if (c0 > 0) __syncthreads();                             // everyone is done with the previous chunk
+        if (lane == 0) { mbar_expect_tx(bar, cl * 2); bulk_g2s(wsm, w + c0, cl * 2, bar); }
+        #pragma unroll 1
+        for (int i0 = threadIdx.x * 8; i0 < RR * cl; i0 += RW * 32 * 8 * 6)
         {
-            const int k = k0 + u * 256;
-            if (k < H)
+            uint4 v[6];                                          // six loads in flight per thread
+            #pragma unroll
+            for (int u = 0; u < 6; ++u)
             {
-                float wf[8];
-                widen8<WBF>(wv[u], wf);
-                #pragma unroll
-                for (int r = 0; r < RR; ++r)
+                const int i = i0 + u * RW * 32 * 8, r = i / cl, c = i - r * cl;
+                v[u] = (i < RR * cl && r < nr) ? *(const uint4*) (x + (size_t) (r0 + r) * H + c0 + c) : make_uint4(0, 0, 0, 0);
+            }
+            #pragma unroll
+            for (int u = 0; u < 6; ++u)
+            {
+                const int i = i0 + u * RW * 32 * 8, r = i / cl, c = i - r * cl;
+                if (i < RR * cl)
                 {
-                    float xf[8];
-                    widen8<XBF>(*(const uint4*) (xs + r * H + k), xf);
-                    #pragma unroll
-                    for (int j = 0; j < 8; ++j) acc[r] = __fmaf_rn(xf[j], wf[j], acc[r]);
+                    float f[8];
+                    widen8<XBF>(v[u], f);
+                    float* d = xs + r * hc + (c & ~255) + ((c & 255) >> 3) * 4;
+                    *(float4*) d = make_float4(f[0], f[1], f[2], f[3]);
+                    *(float4*) (d + 128) = make_float4(f[4], f[5], f[6], f[7]);
                 }
+            }
+        }
+        __syncthreads();
+        if (!mbar_wait(bar, par, &s_abort, nullptr)) return;
+        #pragma unroll 2
+        for (int k = 0; k < cl; k += 256)
+        {
+            float wf[8];
+            widen8<WBF>(lds128(wsm + (k + lane * 8) * 2), wf);
+            const float* xk = xs + k + lane * 4;
+            #pragma unroll
+            for (int r = 0; r < RR; ++r)
+            {
+                const float4 a = *(const float4*) (xk + r * hc), b = *(const float4*) (xk + r * hc + 128);
+                acc[r] = __fmaf_rn(a.x, wf[0], acc[r]); acc[r] = __fmaf_rn(a.y, wf[1], acc[r]);
+                acc[r] = __fmaf_rn(a.z, wf[2], acc[r]); acc[r] = __fmaf_rn(a.w, wf[3], acc[r]);
+                acc[r] = __fmaf_rn(b.x, wf[4], acc[r]); acc[r] = __fmaf_rn(b.y, wf[5], acc[r]);
+                acc[r] = __fmaf_rn(b.z, wf[6], acc[r]); acc[r] = __fmaf_rn(b.w, wf[7], acc[r]);
             }
         }
     }
@@ -75,53 +174,45 @@ __global__ void __launch_bounds__(RW * 32) router_logits_kernel(const uint16_t* 
         float a = acc[r];
         #pragma unroll
         for (int o = 16; o; o >>= 1) a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, o));
-        if (lane == 0 && r < nr) logits[(size_t) (r0 + r) * E + e] = a;
+        if (lane == 0 && r < nr && e < E) logits[(size_t) (r0 + r) * E + e] = a;
     }
+    if (!FUSED) return;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0)
+    {
+        unsigned* c = &g_router_ctr[slot][blockIdx.y];
+        const unsigned old = atomicAdd(c, 1u);
+        s_last = old == gridDim.x - 1;
+        if (s_last) *c = 0u;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (warp < nr) topk_row(logits, bias, r0 + warp, E, topk, scale, sel, rw, lane, true, xs + warp * 512);
 }
 
-// one warp per row: keys, top-k rounds (max key, then lowest index holding it), weights
 __global__ void __launch_bounds__(256) router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int R, int E,
                                                          int topk, float scale, int64_t* __restrict__ sel, __half* __restrict__ rw)
 {
-    const int lane = threadIdx.x & 31, r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (r >= R) return;
-    unsigned key[8]; float act[8];
-    #pragma unroll
-    for (int i = 0; i < 8; ++i)
+    __shared__ float scratch[8 * 512];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, r = blockIdx.x * 8 + warp;
+    if (r < R) topk_row(logits, bias, r, E, topk, scale, sel, rw, lane, false, scratch + warp * 512);
+}
+
+template <bool XBF, bool WBF>
+void launch_logits(dim3 grid, size_t smem, cudaStream_t st, bool fused, const uint16_t* x, const uint16_t* wt, int R, int H, int E,
+                   float* logits, const float* bias, int topk, float scale, int64_t* sel, __half* rw, int slot)
+{
+    static bool attr = false;
+    if (!attr)
     {
-        const int e = lane + 32 * i;
-        if (e < E)
-        {
-            const float l = logits[(size_t) r * E + e];
-            act[i] = __fdiv_rn(1.f, __fadd_rn(1.f, det_expf(-l)));
-            const unsigned u = __float_as_uint(__fadd_rn(act[i], bias ? bias[e] : 0.f));
-            key[i] = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-        }
-        else { act[i] = 0.f; key[i] = 0u; }
+        cudaFuncSetAttribute(router_logits_kernel<XBF, WBF, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(router_logits_kernel<XBF, WBF, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        attr = true;
     }
-    float sum = 0.f, mine_w = 0.f; int mine_id = 0;
-    for (int k = 0; k < topk; ++k)
-    {
-        unsigned lk = 0u; int li = 0;
-        #pragma unroll
-        for (int i = 0; i < 8; ++i) if (key[i] > lk) { lk = key[i]; li = i; }
-        const unsigned m = __reduce_max_sync(0xffffffffu, lk);
-        const unsigned bi = __reduce_min_sync(0xffffffffu, lk == m ? (unsigned) (lane + 32 * li) : 0xffffffffu);
-        float a = 0.f;
-        if ((int) (bi & 31) == lane)
-        {
-            #pragma unroll
-            for (int i = 0; i < 8; ++i) if (i == (int) (bi >> 5)) { a = act[i]; key[i] = 0u; }
-        }
-        a = __shfl_sync(0xffffffffu, a, bi & 31);
-        sum = __fadd_rn(sum, a);
-        if (lane == k) { mine_w = a; mine_id = (int) bi; }
-    }
-    if (lane < topk)
-    {
-        sel[(size_t) r * topk + lane] = mine_id;
-        rw[(size_t) r * topk + lane] = __float2half_rn(__fdiv_rn(__fmul_rn(mine_w, scale), __fadd_rn(sum, 1e-20f)));
-    }
+    if (fused) router_logits_kernel<XBF, WBF, true><<<grid, RW * 32, smem, st>>>(x, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot);
+    else router_logits_kernel<XBF, WBF, false><<<grid, RW * 32, smem, st>>>(x, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot);
 }
 
 }  // namespace
@@ -137,27 +228,23 @@ int router_launch(const void* x, int x_dtype, const void* wt, int w_dtype, const
         return fail(HMOE_E_ARG, "hmoe_router: x and wt must be fp16 or bf16");
     if (!x || !wt || !sel || !rw || !ws) return fail(HMOE_E_ARG, "hmoe_router: null pointer");
     if (ws_bytes < router_ws_bytes(R, E)) return fail(HMOE_E_WS, "hmoe_router: workspace too small");
-    const size_t smem = (size_t) RR * H * 2;
-    if (smem > 200 * 1024) return fail(HMOE_E_ARG, "hmoe_router: H too large");
+    const int hc = H < HC ? H : HC;
+    const size_t smem = (size_t) RR * (hc > 512 ? hc : 512) * 4 + (size_t) RW * hc * 2;    // rows as fp32 (reused as the selection's scratch) + weight rows
     const dim3 grid((E + RW - 1) / RW, (R + RR - 1) / RR);
     float* logits = (float*) ws;
     const uint16_t* xp = (const uint16_t*) x; const uint16_t* wp = (const uint16_t*) wt;
-    static bool attr = false;
-    if (!attr)
-    {
-        cudaFuncSetAttribute(router_logits_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        cudaFuncSetAttribute(router_logits_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        cudaFuncSetAttribute(router_logits_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        cudaFuncSetAttribute(router_logits_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        attr = true;
-    }
+    // Up to CTR_GROUPS row groups the selection runs in the same launch (the last block of a row group does it); beyond,
+    // a second kernel selects.
+    const bool fused = (int) grid.y <= CTR_GROUPS;
+    static unsigned calls = 0;
+    const int slot = (int) (calls++ % CTR_SLOTS);
     const bool xb = x_dtype == HMOE_BF16, wb = w_dtype == HMOE_BF16;
-    if (!xb && !wb) router_logits_kernel<false, false><<<grid, RW * 32, smem, st>>>(xp, wp, R, H, E, logits);
-    else if (!xb && wb) router_logits_kernel<false, true><<<grid, RW * 32, smem, st>>>(xp, wp, R, H, E, logits);
-    else if (xb && !wb) router_logits_kernel<true, false><<<grid, RW * 32, smem, st>>>(xp, wp, R, H, E, logits);
-    else router_logits_kernel<true, true><<<grid, RW * 32, smem, st>>>(xp, wp, R, H, E, logits);
-    router_topk_kernel<<<(R + 7) / 8, 256, 0, st>>>(logits, bias, R, E, topk, scale, sel, (__half*) rw);
-    count_launches(2);
+    if (!xb && !wb) launch_logits<false, false>(grid, smem, st, fused, xp, wp, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot);
+    else if (!xb && wb) launch_logits<false, true>(grid, smem, st, fused, xp, wp, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot);
+    else if (xb && !wb) launch_logits<true, false>(grid, smem, st, fused, xp, wp, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot);
+    else launch_logits<true, true>(grid, smem, st, fused, xp, wp, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot);
+    if (!fused) router_topk_kernel<<<(R + 7) / 8, 256, 0, st>>>(logits, bias, R, E, topk, scale, sel, (__half*) rw);
+    count_launches(fused ? 1 : 2);
     const cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) return fail(HMOE_E_CUDA, cudaGetErrorString(err));
     return HMOE_OK;
