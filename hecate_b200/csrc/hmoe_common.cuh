@@ -15,6 +15,7 @@ constexpr int TOPK_MAX = 8;
 constexpr int MAXR = 16;                  // decode rows per call (tokens x (1 + MTP drafts))
 constexpr int MAXS = MAXR * TOPK_MAX + 1; // distinct experts of a decode call + the shared expert
 constexpr int MAXT = MAXR * TOPK_MAX + 2; // 8-row tiles: at most one per pick, two for a 16-row shared expert
+constexpr int MAXB = 256;                 // blocks of a streaming kernel (one per SM)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t) __cvta_generic_to_shared(p); }
 
@@ -174,6 +175,7 @@ struct Route
     float w[MAXT][8];               // routing weight per listed row (summed over repeated picks), 0 beyond nrows
     short rowbase[MAXT];            // number of real rows in the tiles before this one (row index of the tile's first row in
                                     // the per-pick buffers; at most rows * (topk + 1) real rows per call)
+    int split[2][MAXB + 1];         // streaming kernels (0 gate_up, 1 down): block b works on items [split[b], split[b + 1])
 };
 
 }  // namespace hmoe

@@ -52,7 +52,7 @@ struct SmemLayout
 __global__ void __launch_bounds__(256) decode_prepare_kernel(const void* __restrict__ x, int x_bf16, const int64_t* __restrict__ sel,
     const __half* __restrict__ rw, int R, int H, int topk, int lo, int n_local, int has_shared, int act_quant,
     __half* __restrict__ xf, float* __restrict__ xscale, Route* __restrict__ route, int sh_mod, int sh_rem, unsigned* gen_bump,
-    float4* __restrict__ gzero, int gzero_n)
+    float4* __restrict__ gzero, int gzero_n, int I, int nblocks)
 {
     const int tid = threadIdx.x;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // the next kernel's blocks may set up while this one runs
@@ -109,6 +109,8 @@ __global__ void __launch_bounds__(256) decode_prepare_kernel(const void* __restr
     __shared__ unsigned char s_n[MAXS], s_rows[MAXS][MAXR];
     __shared__ float s_w[MAXS][MAXR];
     __shared__ short s_tile0[MAXS], s_rb[MAXS];
+    __shared__ unsigned char s_tn[MAXT];
+    __shared__ int s_cum[2][MAXT + 1];
     __shared__ int m_sh;
     __shared__ short s_sel[MAXR * TOPK_MAX];
     __shared__ float s_rw[MAXR * TOPK_MAX];
@@ -171,12 +173,41 @@ __global__ void __launch_bounds__(256) decode_prepare_kernel(const void* __restr
         {
             const int t = s_tile0[j] + b, n = s_n[j] - b * 8 < 8 ? s_n[j] - b * 8 : 8;
             route->expert[t] = slot_e[j]; route->nrows[t] = (unsigned char) n; route->rowbase[t] = (short) (s_rb[j] + b * 8);
+            s_tn[t] = (unsigned char) n;
             for (int i = 0; i < 8; ++i)
             {
                 route->rows[t][i] = s_rows[j][b * 8 + (i < n ? i : 0)];
                 route->w[t][i] = i < n ? s_w[j][b * 8 + i] : 0.f;
             }
         }
+    __syncthreads();
+    // Item ranges of the streaming kernels' blocks. The kernels are bound by HBM, but an item of a tile with many real rows
+    // issues more reductions and runs a little longer (measured: 8 rows against 1, +20 % in down, under +1 % in gate_up); the
+    // ranges are cut at equal cost so that the blocks that get the 16-row shared expert do not finish last.
+    const int nt = route->ntiles;
+    if (tid == 0 || tid == 32)
+    {
+        const int k = tid >> 5, J = k ? H / 64 : 2 * (I / 64);
+        int c = 0;
+        for (int t = 0; t < nt; ++t) { s_cum[k][t] = c; c += J * (k ? 100 + 3 * s_tn[t] : 400 + s_tn[t]); }
+        s_cum[k][nt] = c;
+    }
+    __syncthreads();
+    for (int i = tid; i < 2 * (nblocks + 1); i += blockDim.x)
+    {
+        const int k = i / (nblocks + 1), b = i % (nblocks + 1), J = k ? H / 64 : 2 * (I / 64);
+        int p = nt * J;
+        if (b < nblocks && nt > 0)
+        {
+            const int target = (int) ((long long) s_cum[k][nt] * b / nblocks);
+            int lo = 0, hi = nt - 1;                    // last tile whose start is <= target
+            while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (s_cum[k][mid] <= target) lo = mid; else hi = mid - 1; }
+            const int item = k ? 100 + 3 * s_tn[lo] : 400 + s_tn[lo];
+            int off = (target - s_cum[k][lo]) / item;
+            p = lo * J + (off < J ? off : J);
+        }
+        if (b <= MAXB) route->split[k][b] = p;
+    }
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -200,6 +231,7 @@ struct DecodeArgs
     const float* xscale;   // [R][H/32] (Q8)
     __half* act;           // [tiles][8][I] gate_up output = down input
     float* ascale;         // [tiles][8][I/32] (Q8)
+    unsigned long long* dbg;
     float* G;              // I <= 2048 path: [pick rows][gate | up][I] fp32 sums (shares memory with act)
     float* y;              // [R][H] (expert-parallel: base of two slots, the step's slot is chosen by *gen_ptr & 1)
     const unsigned* gen_ptr; size_t slot_stride;
@@ -676,6 +708,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_stream_kernel(const Decode
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
     const uint32_t ring = sbase + warp * SLOT, full0 = sbase + StreamSmem::bars + warp * 8;      // slot st: + st * CW * SLOT / + st * CW * 8
     volatile int* abort_flag = (volatile int*) (smem + StreamSmem::flags);
+#if defined(HMOE_EXP) && HMOE_EXP == 8
+    if (threadIdx.x == 0) a.dbg[(DOWN * 148 + blockIdx.x) * 4 + 0] = globaltimer_ns();
+#endif
     pdl_launch_dependents();
     if (threadIdx.x == 0)
     {
@@ -690,8 +725,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_stream_kernel(const Decode
     const Route* rt = a.route;
     const int K = DOWN ? a.I : a.H, N = DOWN ? a.H : a.I;          // input columns and output rows of one matrix
     const int KB = K / 64, NG = N / 64, J = DOWN ? NG : 2 * NG;
-    const int P = rt->ntiles * J;
-    const int p0 = (int) ((long long) P * blockIdx.x / gridDim.x), p1 = (int) ((long long) P * (blockIdx.x + 1) / gridDim.x);
+    const int p0 = rt->split[DOWN][blockIdx.x], p1 = rt->split[DOWN][blockIdx.x + 1];      // cut at equal cost by the prepare kernel
     float* const out0 = DOWN ? a.y + (a.gen_ptr ? (size_t) (*a.gen_ptr & 1u) * a.slot_stride : 0) : a.G;
     if (p0 < p1 && 2 * warp < KB)
     {
@@ -837,6 +871,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_stream_kernel(const Decode
         uint32_t st = 0, par = 0;
         int tile = p0 / J, j = p0 % J;
         if (DOWN) pdl_wait();
+#if defined(HMOE_EXP) && HMOE_EXP == 8
+        if (threadIdx.x == 0) a.dbg[(DOWN * 148 + blockIdx.x) * 4 + 1] = globaltimer_ns();
+#endif
         enter_tile(tile);
         if (!GROUPED) load_row_scales(j, sd);
         bool alive = true;
@@ -899,6 +936,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_stream_kernel(const Decode
         }
     }
     __syncthreads();
+#if defined(HMOE_EXP) && HMOE_EXP == 8
+    if (threadIdx.x == 0) a.dbg[(DOWN * 148 + blockIdx.x) * 4 + 2] = globaltimer_ns();
+#endif
 }
 
 }  // namespace
@@ -1020,14 +1060,14 @@ int decode_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t
     if (g_prof) cudaEventRecord(g_ev[0], st);
     decode_prepare_kernel<<<R + 1, 256, 0, st>>>(x, x_dtype == HMOE_BF16, sel, (const __half*) rw, R, H, L->topk, lo, n_local, has_shared,
                                                  act_quant, xf, xscale, route, sh_mod, sh_rem, gen_ptr,
-                                                 (float4*) act, (I <= 2048 && H <= 6144) ? (L->topk + 1) * 2 * I / 4 : 0);
+                                                 (float4*) act, (I <= 2048 && H <= 6144) ? (L->topk + 1) * 2 * I / 4 : 0, I, g_sms < MAXB ? g_sms : MAXB);
     DecodeArgs a;
     a.H = H; a.I = I;
     a.gate_w = L->gate_w; a.up_w = L->up_w; a.down_w = L->down_w; a.gate_s = L->gate_s; a.up_s = L->up_s; a.down_s = L->down_s;
     a.sh_gw = L->sh_gate_w; a.sh_uw = L->sh_up_w; a.sh_dw = L->sh_down_w; a.sh_gs = L->sh_gate_s; a.sh_us = L->sh_up_s; a.sh_ds = L->sh_down_s;
-    a.route = route; a.xf = xf; a.xscale = xscale; a.act = act; a.ascale = ascale; a.G = (float*) act; a.y = y; a.status = status;
+    a.route = route; a.xf = xf; a.xscale = xscale; a.act = act; a.ascale = ascale; a.G = (float*) act; a.dbg = (unsigned long long*) ((char*) ws + decode_ws_bytes(H, I) - 16384); a.y = y; a.status = status;
     a.gen_ptr = gen_ptr; a.slot_stride = slot_stride;
-    const int grid = g_sms;
+    const int grid = g_sms < MAXB ? g_sms : MAXB;
     const int v = (L->group ? 2 : 0) + (act_quant ? 1 : 0);
     if (v == 0) launch_pair<false, false>(grid, a, R, st, first[0]);
     else if (v == 1) launch_pair<false, true>(grid, a, R, st, first[1]);
