@@ -103,110 +103,140 @@ __global__ void __launch_bounds__(256) decode_prepare_kernel(const void* __restr
         }
         return;
     }
-    // routing block: slot = distinct expert (ascending id), then the shared expert; tiles of <= 8 rows per slot
-    __shared__ int flag[256];
+    // routing block: slot = distinct expert (ascending id), then the shared expert; tiles of <= 8 rows per slot.
+    // Everything is done in parallel with block-wide prefix sums: this block is the critical path of the call (the
+    // streaming kernel's blocks are already resident and wait for it).
+    __shared__ short slot_of[256];                        // local expert id -> slot, -1 if not picked
     __shared__ short slot_e[MAXS];
-    __shared__ unsigned char s_n[MAXS], s_rows[MAXS][MAXR];
+    __shared__ unsigned s_mask[MAXS];                     // rows of the slot, one bit each
+    __shared__ unsigned char s_rows[MAXS][MAXR];
     __shared__ float s_w[MAXS][MAXR];
-    __shared__ short s_tile0[MAXS], s_rb[MAXS];
-    __shared__ unsigned char s_tn[MAXT];
+    __shared__ int s_scan[4][256];                        // per slot: tiles, rows, cost in gate_up, cost in down (then their prefix sums)
     __shared__ int s_cum[2][MAXT + 1];
-    __shared__ int m_sh;
     __shared__ short s_sel[MAXR * TOPK_MAX];
     __shared__ float s_rw[MAXR * TOPK_MAX];
     __shared__ int wcount[8];
-    for (int i = tid; i < 256; i += blockDim.x) flag[i] = 0;
+    __shared__ int m_sh;
+    const int NP = R * topk;
+    slot_of[tid] = 0;                                      // used as the picked flag first
+    if (tid < MAXS) s_mask[tid] = 0u;
     __syncthreads();
-    for (int i = tid; i < R * topk; i += blockDim.x)
+    if (tid < NP)
     {
-        const int64_t e = sel[i] - lo;
+        const int64_t e = sel[tid] - lo;
         const bool in = e >= 0 && e < n_local;
-        s_sel[i] = in ? (short) e : (short) -1;
-        s_rw[i] = __half2float(rw[i]);
-        if (in) flag[(int) e] = 1;
+        s_sel[tid] = in ? (short) e : (short) -1;
+        s_rw[tid] = __half2float(rw[tid]);
+        if (in) slot_of[(int) e] = 1;
     }
     __syncthreads();
     {
         // distinct experts in ascending order: one flag per thread, ballots per warp, prefix over the eight warps
-        const unsigned b = __ballot_sync(0xffffffffu, flag[tid] != 0);
-        if ((tid & 31) == 0) wcount[tid >> 5] = __popc(b);
+        const bool picked = slot_of[tid] != 0;
+        const unsigned bl = __ballot_sync(0xffffffffu, picked);
+        if ((tid & 31) == 0) wcount[tid >> 5] = __popc(bl);
         __syncthreads();
         int before = 0, m = 0;
         for (int w = 0; w < 8; ++w) { if (w < (tid >> 5)) before += wcount[w]; m += wcount[w]; }
-        if (flag[tid]) slot_e[before + __popc(b & ((1u << (tid & 31)) - 1u))] = (short) tid;
+        const int slot = before + __popc(bl & ((1u << (tid & 31)) - 1u));
+        slot_of[tid] = picked ? (short) slot : (short) -1;
+        if (picked) slot_e[slot] = (short) tid;
         if (tid == 0) { m_sh = m; if (has_shared) slot_e[m] = -1; }
     }
     __syncthreads();
     const int m = m_sh, ns = m + (has_shared ? 1 : 0);
-    for (int j = tid; j < ns; j += blockDim.x)
+    // one thread per pick: the first pick of an expert in its row owns the (slot, row) pair and the summed weight
+    int my_slot = -1, my_row = 0; float my_w = 0.f;
+    if (tid < NP && s_sel[tid] >= 0)
     {
-        int n = 0;
-        if (j < m)
+        const int r = tid / topk, k = tid - r * topk, e = s_sel[tid];
+        bool first = true;
+        for (int k2 = 0; k2 < k; ++k2) first &= s_sel[r * topk + k2] != e;
+        if (first)
         {
-            const int e = slot_e[j];
-            for (int r = 0; r < R; ++r)
-            {
-                float ws = 0.f; bool hit = false;
-                for (int k = 0; k < topk; ++k)
-                    if (s_sel[r * topk + k] == e) { ws += s_rw[r * topk + k]; hit = true; }
-                if (hit) { s_rows[j][n] = (unsigned char) r; s_w[j][n] = ws; ++n; }
-            }
+            for (int k2 = k; k2 < topk; ++k2) if (s_sel[r * topk + k2] == e) my_w += s_rw[r * topk + k2];
+            my_slot = slot_of[e]; my_row = r;
+            atomicOr(&s_mask[my_slot], 1u << r);
         }
-        else
-        {
-            // the shared expert takes every row with weight 1; under expert parallelism only rows r % sh_mod == sh_rem here
-            for (int r = 0; r < R; ++r) if (r % sh_mod == sh_rem) { s_rows[j][n] = (unsigned char) r; s_w[j][n] = 1.f; ++n; }
-        }
-        s_n[j] = (unsigned char) n;
+    }
+    // the shared expert takes every row with weight 1; under expert parallelism only rows r % sh_mod == sh_rem here
+    if (has_shared && tid >= 128 && tid < 128 + R && (tid - 128) % sh_mod == sh_rem) atomicOr(&s_mask[m], 1u << (tid - 128));
+    __syncthreads();
+    if (my_slot >= 0)
+    {
+        const int pos = __popc(s_mask[my_slot] & ((1u << my_row) - 1u));
+        s_rows[my_slot][pos] = (unsigned char) my_row; s_w[my_slot][pos] = my_w;
+    }
+    if (has_shared && tid >= 128 && tid < 128 + R && (tid - 128) % sh_mod == sh_rem)
+    {
+        const int pos = __popc(s_mask[m] & ((1u << (tid - 128)) - 1u));
+        s_rows[m][pos] = (unsigned char) (tid - 128); s_w[m][pos] = 1.f;
+    }
+    // Per slot: tiles, rows, and the cost of its items in the two streaming kernels. The kernels are bound by HBM, but an
+    // item of a tile with many real rows issues more reductions and runs a little longer (measured: 8 rows against 1,
+    // +20 % in down, under +1 % in gate_up); the blocks' item ranges are cut at equal cost so that the blocks that get the
+    // 16-row shared expert do not finish last.
+    const int J0 = 2 * (I / 64), J1 = H / 64;
+    {
+        const int n = tid < ns ? __popc(s_mask[tid]) : 0, full = n >> 3, rest = n & 7;
+        s_scan[0][tid] = (n + 7) >> 3;
+        s_scan[1][tid] = n;
+        s_scan[2][tid] = J0 * (full * (400 + 8) + (rest ? 400 + rest : 0));
+        s_scan[3][tid] = J1 * (full * (100 + 3 * 8) + (rest ? 100 + 3 * rest : 0));
     }
     __syncthreads();
+    int incl[4];
+    #pragma unroll 1
+    for (int o = 1; o < 256; o <<= 1)                      // inclusive prefix sums of the four columns
+    {
+        #pragma unroll
+        for (int c = 0; c < 4; ++c) incl[c] = s_scan[c][tid] + (tid >= o ? s_scan[c][tid - o] : 0);
+        __syncthreads();
+        #pragma unroll
+        for (int c = 0; c < 4; ++c) s_scan[c][tid] = incl[c];
+        __syncthreads();
+    }
+    const int nt = s_scan[0][255];
     if (tid == 0)
     {
-        int t = 0, rb = 0;
-        for (int j = 0; j < ns; ++j) { s_tile0[j] = (short) t; s_rb[j] = (short) rb; t += (s_n[j] + 7) / 8; rb += s_n[j]; }
-        route->m = m; route->ntiles = t; route->pad[0] = route->pad[1] = 0;
+        route->m = m; route->ntiles = nt; route->pad[0] = route->pad[1] = 0;
+        s_cum[0][nt] = s_scan[2][255]; s_cum[1][nt] = s_scan[3][255];
         if (gen_bump) *gen_bump += 1;          // expert-parallel step counter: selects the partial slot and the combine's generation
     }
-    __syncthreads();
-    for (int j = tid; j < ns; j += blockDim.x)
-        for (int b = 0; b * 8 < s_n[j]; ++b)
+    if (tid < ns)
+    {
+        const int n = __popc(s_mask[tid]);
+        int t = incl[0] - ((n + 7) >> 3), rb = incl[1] - n;
+        int c0 = incl[2] - J0 * ((n >> 3) * 408 + ((n & 7) ? 400 + (n & 7) : 0)), c1 = incl[3] - J1 * ((n >> 3) * 124 + ((n & 7) ? 100 + 3 * (n & 7) : 0));
+        for (int b8 = 0; b8 < n; b8 += 8, ++t)
         {
-            const int t = s_tile0[j] + b, n = s_n[j] - b * 8 < 8 ? s_n[j] - b * 8 : 8;
-            route->expert[t] = slot_e[j]; route->nrows[t] = (unsigned char) n; route->rowbase[t] = (short) (s_rb[j] + b * 8);
-            s_tn[t] = (unsigned char) n;
+            const int nn = n - b8 < 8 ? n - b8 : 8;
+            route->expert[t] = slot_e[tid]; route->nrows[t] = (unsigned char) nn; route->rowbase[t] = (short) (rb + b8);
             for (int i = 0; i < 8; ++i)
             {
-                route->rows[t][i] = s_rows[j][b * 8 + (i < n ? i : 0)];
-                route->w[t][i] = i < n ? s_w[j][b * 8 + i] : 0.f;
+                route->rows[t][i] = s_rows[tid][b8 + (i < nn ? i : 0)];
+                route->w[t][i] = i < nn ? s_w[tid][b8 + i] : 0.f;
             }
+            s_cum[0][t] = c0; s_cum[1][t] = c1;
+            s_scan[0][t] = nn;                 // rows of tile t (the tile counts are no longer needed: every thread holds its own)
+            c0 += J0 * (400 + nn); c1 += J1 * (100 + 3 * nn);
         }
-    __syncthreads();
-    // Item ranges of the streaming kernels' blocks. The kernels are bound by HBM, but an item of a tile with many real rows
-    // issues more reductions and runs a little longer (measured: 8 rows against 1, +20 % in down, under +1 % in gate_up); the
-    // ranges are cut at equal cost so that the blocks that get the 16-row shared expert do not finish last.
-    const int nt = route->ntiles;
-    if (tid == 0 || tid == 32)
-    {
-        const int k = tid >> 5, J = k ? H / 64 : 2 * (I / 64);
-        int c = 0;
-        for (int t = 0; t < nt; ++t) { s_cum[k][t] = c; c += J * (k ? 100 + 3 * s_tn[t] : 400 + s_tn[t]); }
-        s_cum[k][nt] = c;
     }
     __syncthreads();
     for (int i = tid; i < 2 * (nblocks + 1); i += blockDim.x)
     {
-        const int k = i / (nblocks + 1), b = i % (nblocks + 1), J = k ? H / 64 : 2 * (I / 64);
+        const int k = i / (nblocks + 1), b = i % (nblocks + 1), J = k ? J1 : J0;
         int p = nt * J;
         if (b < nblocks && nt > 0)
         {
             const int target = (int) ((long long) s_cum[k][nt] * b / nblocks);
-            int lo = 0, hi = nt - 1;                    // last tile whose start is <= target
-            while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (s_cum[k][mid] <= target) lo = mid; else hi = mid - 1; }
-            const int item = k ? 100 + 3 * s_tn[lo] : 400 + s_tn[lo];
-            int off = (target - s_cum[k][lo]) / item;
-            p = lo * J + (off < J ? off : J);
+            int lo2 = 0, hi = nt - 1;                    // last tile whose start is <= target
+            while (lo2 < hi) { const int mid = (lo2 + hi + 1) >> 1; if (s_cum[k][mid] <= target) lo2 = mid; else hi = mid - 1; }
+            const int item = k ? 100 + 3 * s_scan[0][lo2] : 400 + s_scan[0][lo2];
+            const int off = (target - s_cum[k][lo2]) / item;
+            p = lo2 * J + (off < J ? off : J);
         }
-        if (b <= MAXB) route->split[k][b] = p;
+        route->split[k][b] = p;
     }
 }
 
