@@ -991,33 +991,45 @@ size_t decode_ws_bytes(int H, int I)
 static int g_sms = 0;
 
 // Optional phase timing: when switched on, every decode call records four events (before prepare, after prepare, after
-// gate_up, after down) on the caller's stream into a ring, read back by decode_phase_times().
+// gate_up, after down) on the caller's stream into a ring of PROF_RING sets; decode_phase_times() averages the sets recorded
+// since profiling was switched on (at most the last PROF_RING calls). Programmatic dependent launch is off meanwhile.
+constexpr int PROF_RING = 32;
 static bool g_prof = false;
-static cudaEvent_t g_ev[4];
+static cudaEvent_t g_ev[PROF_RING][4];
 static bool g_ev_made = false;
+static unsigned g_prof_calls = 0;
 
 int decode_set_profiling(int on)
 {
     if (on && !g_ev_made)
     {
-        for (int i = 0; i < 4; ++i)
-            if (cudaEventCreate(&g_ev[i]) != cudaSuccess) return fail(HMOE_E_CUDA, "hmoe_set_profiling: cudaEventCreate failed");
+        for (int i = 0; i < PROF_RING * 4; ++i)
+            if (cudaEventCreate(&g_ev[i / 4][i % 4]) != cudaSuccess) return fail(HMOE_E_CUDA, "hmoe_set_profiling: cudaEventCreate failed");
         g_ev_made = true;
     }
+    if (on && !g_prof) g_prof_calls = 0;
     g_prof = on != 0;
     return HMOE_OK;
 }
 
 int decode_phase_times(float* ms3)
 {
-    if (!g_ev_made) return fail(HMOE_E_ARG, "hmoe_decode_phase_times: profiling was never switched on");
-    if (cudaEventSynchronize(g_ev[3]) != cudaSuccess) return fail(HMOE_E_CUDA, "hmoe_decode_phase_times: no timed call");
-    for (int i = 0; i < 3; ++i)
-        if (cudaEventElapsedTime(ms3 + i, g_ev[i], g_ev[i + 1]) != cudaSuccess) return fail(HMOE_E_CUDA, "hmoe_decode_phase_times: elapsed");
+    if (!g_ev_made || g_prof_calls == 0) return fail(HMOE_E_ARG, "hmoe_decode_phase_times: no call was timed");
+    const unsigned n = g_prof_calls < PROF_RING ? g_prof_calls : PROF_RING;
+    ms3[0] = ms3[1] = ms3[2] = 0.f;
+    for (unsigned s = 0; s < n; ++s)
+    {
+        if (cudaEventSynchronize(g_ev[s][3]) != cudaSuccess) return fail(HMOE_E_CUDA, "hmoe_decode_phase_times: no timed call");
+        for (int i = 0; i < 3; ++i)
+        {
+            float ms = 0.f;
+            if (cudaEventElapsedTime(&ms, g_ev[s][i], g_ev[s][i + 1]) != cudaSuccess) return fail(HMOE_E_CUDA, "hmoe_decode_phase_times: elapsed");
+            ms3[i] += ms / n;
+        }
+    }
     return HMOE_OK;
 }
 
-// launch as a programmatic dependent of the previous kernel in the stream (see pdl_wait)
 template <typename Kern>
 static void launch_dependent(Kern kern, int grid, const DecodeArgs& a, cudaStream_t st)
 {
@@ -1041,7 +1053,8 @@ static void launch_stream_gate_up(int grid, const DecodeArgs& a, cudaStream_t st
 template <bool G, bool Q>
 static void launch_pair(int grid, const DecodeArgs& a, int R, cudaStream_t st, bool first)
 {
-    if (g_prof) cudaEventRecord(g_ev[1], st);
+    cudaEvent_t* ev = g_ev[g_prof_calls % PROF_RING];
+    if (g_prof) cudaEventRecord(ev[1], st);
     if (first)
     {
         cudaFuncSetAttribute(decode_gate_up_kernel<G, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout::total);
@@ -1053,10 +1066,10 @@ static void launch_pair(int grid, const DecodeArgs& a, int R, cudaStream_t st, b
     else if (a.H <= 2048) launch_stream_gate_up<G, Q, 1>(grid, a, st);
     else if (a.H <= 4096) launch_stream_gate_up<G, Q, 2>(grid, a, st);
     else launch_stream_gate_up<G, Q, 3>(grid, a, st);
-    if (g_prof) cudaEventRecord(g_ev[2], st);
+    if (g_prof) cudaEventRecord(ev[2], st);
     if (resident) launch_dependent(decode_stream_kernel<G, Q, true, 1>, grid, a, st);
     else decode_down_kernel<G, Q><<<grid, NTHREADS, SmemLayout::total, st>>>(a, R);
-    if (g_prof) cudaEventRecord(g_ev[3], st);
+    if (g_prof) { cudaEventRecord(ev[3], st); ++g_prof_calls; }
 }
 
 int decode_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
@@ -1087,7 +1100,7 @@ int decode_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t
     __half* act = (__half*) w; w += up256((size_t) MAXT * 8 * I * 2);
     float* ascale = (float*) w;
     const int has_shared = L->sh_gate_w != nullptr;
-    if (g_prof) cudaEventRecord(g_ev[0], st);
+    if (g_prof) cudaEventRecord(g_ev[g_prof_calls % PROF_RING][0], st);
     decode_prepare_kernel<<<R + 1, 256, 0, st>>>(x, x_dtype == HMOE_BF16, sel, (const __half*) rw, R, H, L->topk, lo, n_local, has_shared,
                                                  act_quant, xf, xscale, route, sh_mod, sh_rem, gen_ptr,
                                                  (float4*) act, (I <= 2048 && H <= 6144) ? (L->topk + 1) * 2 * I / 4 : 0, I, g_sms < MAXB ? g_sms : MAXB);

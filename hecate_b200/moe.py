@@ -162,7 +162,8 @@ def set_profiling(on):
 
 
 def decode_phase_times():
-    """ms of (prepare, gate_up, down) of the last decode call made with profiling on (waits for it)."""
+    """ms of (prepare, gate_up, down), averaged over the decode calls made since profiling was switched on (at most the last
+    32; waits for them)."""
     out = (C.c_float * 3)()
     check(lib().hmoe_decode_phase_times(out))
     return tuple(out)

@@ -140,8 +140,10 @@ int hmoe_decode_noalloc(const hmoe_layer* layer, const void* x, int x_dtype, con
 
 /* Phase timing of the decode path (no reference counterpart; the reference uses compile-time ablation macros,
  * runtime/tier/moe4/moe4.cu:6-10). With profiling on, each hmoe_decode call records CUDA events between its three kernels
- * on the caller's stream; hmoe_decode_phase_times waits for the last timed call and returns the durations in ms of
- * {prepare, gate_up, down}. The first switch-on creates the events (allocates; call it outside stream capture). */
+ * on the caller's stream, into a ring of 32 sets; hmoe_decode_phase_times waits for them and returns the durations in ms
+ * of {prepare, gate_up, down} averaged over the calls made since profiling was switched on (at most the last 32). While
+ * profiling is on the kernels are launched without programmatic overlap, so each duration is that of the kernel alone.
+ * The first switch-on creates the events (allocates; call it outside stream capture). */
 int hmoe_set_profiling(int on);
 int hmoe_decode_phase_times(float* ms3);
 
