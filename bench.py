@@ -273,9 +273,9 @@ def run_ours(args):
     layer_bytes = (mean_d + 1) * EXPERT_BYTES + E * H * 2 + ROWS * H * 6
     peak, peak_kind = measured_peaks()
     achieved = gate_up_bytes / (phase[1] * 1e-3) / 1e9
-    # DRAM traffic of one gate_up launch: dram__bytes_read + write of an ncu capture of the reduced case (--experts 64: 720.7 MB
-    # for 726.7 MB of algorithmic bytes, profiles/decode_gate_up_experts64.md), scaled to this launch by the experts it streams
-    traffic = 0.9917 * gate_up_bytes
+    # DRAM traffic of one gate_up launch: dram__bytes_read + write of an ncu capture of the reduced case (--experts 64: 709.4 MB
+    # for 722.3 MB of algorithmic bytes, profiles/decode_stream_kernels_experts64.md), scaled to this launch by the experts it streams
+    traffic = 0.982 * gate_up_bytes
     ms_per_step = ms / steps
 
     # end to end: host buffers in, host buffer out, every step. The host->device copy of the step's rows, the layer call and
