@@ -226,6 +226,12 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r)
                    "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
                    "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]) : "r"(taddr));
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r)
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+                   "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]) : "r"(taddr));
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar)
 {
@@ -285,8 +291,8 @@ struct PfSmem
     static constexpr int A_BYTES = TM * TK * 2;             // 16 KB per matrix
     static constexpr int B_BYTES = TN * TK * 2;             // 32 KB
     static constexpr int STAGE = NMAT * A_BYTES + B_BYTES;
-    static constexpr int bars = STAGES * STAGE;             // full_a[S], full_b[S], empty[S], done, tmem_free
-    static constexpr int misc = bars + (3 * STAGES + 2) * 8;
+    static constexpr int bars = STAGES * STAGE;             // full_a[S], full_b[S], empty[S], done[2], tmem_free[2]
+    static constexpr int misc = bars + (3 * STAGES + 4) * 8;
     static constexpr int total = misc + 32 + 1024;          // + slack to align the base to 1024
 };
 
@@ -300,16 +306,18 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
     const uint32_t sbase = (raw + 1023u) & ~1023u;
     unsigned char* smem = smem_raw + (sbase - raw);
     const uint32_t full_a = sbase + L::bars, full_b = full_a + L::STAGES * 8, empty = full_b + L::STAGES * 8,
-                   done = empty + L::STAGES * 8, tmem_free = done + 8;
+                   done = empty + L::STAGES * 8, tmem_free = done + 2 * 8;      // done[NACC], tmem_free[NACC]
     uint32_t* tmem_slot = (uint32_t*) (smem + L::misc);
     volatile int* abort_flag = (volatile int*) (smem + L::misc + 8);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    constexpr int TMEM_COLS = NMAT == 2 ? 512 : 256;
+    // Accumulators in tensor memory: gate + up fill all 512 columns; down needs 256 and keeps two sets, so the MMAs of the
+    // next tile run while this tile's sums are read out.
+    constexpr int TMEM_COLS = 512, NACC = NMAT == 2 ? 1 : 2;
 
     if (threadIdx.x == 0)
     {
         for (int i = 0; i < L::STAGES; ++i) { mbar_init(full_a + i * 8, NMAT == 2 ? NDQ : NDQ / 2); mbar_init(full_b + i * 8, 1); mbar_init(empty + i * 8, 1); }
-        mbar_init(done, 1); mbar_init(tmem_free, NDQ);
+        for (int i = 0; i < 2; ++i) { mbar_init(done + i * 8, 1); mbar_init(tmem_free + i * 8, NDQ); }
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -325,28 +333,104 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
 
     const int KB = a.K / 64, KBT = KB * a.kfold, NCT = a.N / TM;     // KB 64-column blocks of the weights, KBT ring stages per tile
     const int nitems = a.plan->nrb * NCT;
-    uint32_t tile_n = 0;                           // tiles done (phase of done / tmem_free)
 
-    for (int item = blockIdx.x; item < nitems; item += gridDim.x, ++tile_n)
+    if (warp < NDQ)
     {
-        if (*abort_flag) break;
-        const int rb = item / NCT, ct = item % NCT;
-        const int e = a.rbt[4 * rb], pos0 = a.rbt[4 * rb + 1], n = a.rbt[4 * rb + 2];
-        const uint32_t n16 = (uint32_t) ((n + 15) & ~15);
-        if (warp < NDQ)
+        // ---- dequantise: one 16-row strip of one 64-row unit per warp and stage. gate_up: 2 matrices x 2 units x 4 strips =
+        // 16 strip-blocks per stage, one per warp. down: 8 strip-blocks per stage; warps 0-7 take the even stages, warps
+        // 8-15 the odd ones. The packed words are fetched NPF of the warp's stages ahead. The warps also read out the
+        // finished sums (epilogue), but LEAD of their stages late: by then the ring holds the first stages of the next tile, so
+        // the MMA thread has work (down, second accumulator set) or can restart at once (gate_up) while the sums are read.
+        const int g = lane >> 2, q = lane & 3;
+        const int strip = warp & 3, unit = (warp >> 2) & 1, mat = NMAT == 2 ? warp >> 3 : 0;
+        const int kb0 = NMAT == 2 ? 0 : warp >> 3, kstep = NMAT == 2 ? 1 : 2;
+        constexpr int NPF = 4;
+#ifdef PF_LEAD
+        constexpr int LEAD = PF_LEAD;
+#else
+        constexpr int LEAD = NMAT == 2 ? 2 : 1;                  // own stages of the next tile produced before the epilogue
+#endif
+        struct Tile { int e, pos0, n, ct; uint32_t tile_n; };
+        Tile pend; bool have_pend = false;
+        bool ok = true;
+        auto epilogue = [&](const Tile& t) {
+
+            // warp w reads tensor-memory lanes 32 (w % 4) .. + 31 (channels), columns 64 (w / 4) .. + 63 (picks)
+            const uint32_t acc = (uint32_t) (t.tile_n % NACC);
+            if (!mbar_wait(done + acc * 8, (t.tile_n / NACC) & 1, abort_flag, a.status)) { ok = false; return; }
+            tc_fence_after();
+            const uint32_t n16 = (uint32_t) ((t.n + 15) & ~15);
+            const int lq = warp & 3, cq = warp >> 2;
+            const int ch = t.ct * TM + lq * 32 + lane;
+            const uint32_t tacc = tmem + acc * 256 + ((uint32_t) (lq * 32) << 16);
+            float sc0 = 1.f, sc1 = 1.f;
+            if (!a.grouped)
+            {
+                const void* s0p = t.e < a.n_local ? (const void*) a.s0[t.e] : a.sh_s0;
+                sc0 = __ldg((const float*) s0p + ch);
+                if (NMAT == 2) { const void* s1p = t.e < a.n_local ? (const void*) a.s1[t.e] : a.sh_s1; sc1 = __ldg((const float*) s1p + ch); }
+            }
+            for (int c0 = cq * 64; c0 < cq * 64 + 64 && c0 < (int) n16; c0 += 16)
+            {
+                uint32_t r0[16], r1[16];                 // 16 columns at a time: the streaming loop's prefetched words stay in registers
+                tmem_ld16(tacc + c0, r0);
+                if (NMAT == 2) tmem_ld16(tacc + 256 + c0, r1);
+                tmem_ld_wait();
+                if (NMAT == 2)
+                {
+                    #pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                    {
+                        const int p = c0 + j;
+                        if (p < t.n)
+                        {
+                            const float gg = __uint_as_float(r0[j]) * sc0, uu = __uint_as_float(r1[j]) * sc1;
+                            float v = gg / (1.f + expf(-gg)) * uu * a.wt[t.pos0 + p];
+                            if (a.act_quant)
+                            {
+                                // second int8 round trip of the CPU engine: 32 consecutive channels = this warp
+                                float m = fabsf(v);
+                                #pragma unroll
+                                for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+                                const float sq8 = m > 0.f ? __fdiv_rn(m, 127.f) : 1.f;
+                                v = __fmul_rn((float) __float2int_rn(__fmul_rn(v, __fdiv_rn(1.f, sq8))), sq8);
+                                // code x scale does not fit fp16: keep it as hi + lo halves, the down GEMM walks both
+                                const __half hi = __float2half_rn(v);
+                                a.act[(size_t) (t.pos0 + p) * (2 * a.N) + ch] = hi;
+                                a.act[(size_t) (t.pos0 + p) * (2 * a.N) + a.N + ch] = __float2half_rn(v - __half2float(hi));
+                            }
+                            else
+                                a.act[(size_t) (t.pos0 + p) * a.N + ch] = __float2half_rn(v);
+                        }
+                    }
+                }
+                else
+                {
+                    #pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                    {
+                        const int p = c0 + j;
+                        if (p < t.n) atomicAdd(a.out + (size_t) a.tok[t.pos0 + p] * a.N + ch, __uint_as_float(r0[j]) * sc0);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tmem_free + acc * 8);
+        };
+
+        uint32_t tile_n = 0;
+        for (int item = blockIdx.x; item < nitems && ok; item += gridDim.x, ++tile_n)
         {
-            // ---- dequantise: one 16-row strip of one 64-row unit per warp and stage. gate_up: 2 matrices x 2 units x 4 strips =
-            // 16 strip-blocks per stage, one per warp. down: 8 strip-blocks per stage; warps 0-7 take the even stages, warps
-            // 8-15 the odd ones. The packed words are fetched two stages ahead.
-            const int g = lane >> 2, q = lane & 3;
-            const int strip = warp & 3, unit = (warp >> 2) & 1, mat = NMAT == 2 ? warp >> 3 : 0;
-            const int kb0 = NMAT == 2 ? 0 : warp >> 3, kstep = NMAT == 2 ? 1 : 2;
-            const void* wp = e < a.n_local ? (const void*) (mat ? a.w1[e] : a.w0[e]) : (mat ? a.sh_w1 : a.sh_w0);
-            const void* sp = e < a.n_local ? (const void*) (mat ? a.s1[e] : a.s0[e]) : (mat ? a.sh_s1 : a.sh_s0);
-            const char* wbase = (const char*) wp + ((size_t) (2 * ct + unit) * KB * 4 + strip) * 512 + lane * 16;
-            const char* sbase_p = (const char*) sp + ((size_t) (2 * ct + unit) * (a.K / 128) * 64 + g * 8 + 2 * strip) * 2;
+            if (*abort_flag) { ok = false; break; }
+            const int rb = item / NCT;
+            Tile cur;
+            cur.ct = item % NCT; cur.e = a.rbt[4 * rb]; cur.pos0 = a.rbt[4 * rb + 1]; cur.n = a.rbt[4 * rb + 2]; cur.tile_n = tile_n;
+            const void* wp = cur.e < a.n_local ? (const void*) (mat ? a.w1[cur.e] : a.w0[cur.e]) : (mat ? a.sh_w1 : a.sh_w0);
+            const void* sp = cur.e < a.n_local ? (const void*) (mat ? a.s1[cur.e] : a.s0[cur.e]) : (mat ? a.sh_s1 : a.sh_s0);
+            const char* wbase = (const char*) wp + ((size_t) (2 * cur.ct + unit) * KB * 4 + strip) * 512 + lane * 16;
+            const char* sbase_p = (const char*) sp + ((size_t) (2 * cur.ct + unit) * (a.K / 128) * 64 + g * 8 + 2 * strip) * 2;
             // packed words and scale pairs of the next NPF of this warp's stages, in flight while the current one is converted
-            constexpr int NPF = 4;
             uint4 wq[NPF]; uint32_t sq[NPF];
             #pragma unroll
             for (int i = 0; i < NPF; ++i)
@@ -357,7 +441,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
                 sq[i] = (a.grouped && kbi < KBT) ? __ldg((const uint32_t*) (sbase_p + (size_t) (kbw >> 1) * 128)) : 0u;
             }
             const uint32_t it0 = tile_n * (uint32_t) KBT;
-            bool ok = true;
+            int produced = 0;
             for (int kb = kb0; kb < KBT; kb += kstep)
             {
                 const uint32_t gi = it0 + kb, s = gi % L::STAGES;
@@ -377,87 +461,48 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
                 fence_proxy_async();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(full_a + s * 8);
+                if (++produced == LEAD && have_pend) { epilogue(pend); have_pend = false; if (!ok) break; }
             }
-            // ---- epilogue: warp w reads tensor-memory lanes 32 (w % 4) .. + 31 (channels), columns 64 (w / 4) .. + 63 (picks)
-            if (ok && mbar_wait(done, tile_n & 1, abort_flag, a.status))
-            {
-                tc_fence_after();
-                const int lq = warp & 3, cq = warp >> 2;
-                const int ch = ct * TM + lq * 32 + lane;
-                float sc0 = 1.f, sc1 = 1.f;
-                if (!a.grouped)
-                {
-                    const void* s0p = e < a.n_local ? (const void*) a.s0[e] : a.sh_s0;
-                    sc0 = __ldg((const float*) s0p + ch);
-                    if (NMAT == 2) { const void* s1p = e < a.n_local ? (const void*) a.s1[e] : a.sh_s1; sc1 = __ldg((const float*) s1p + ch); }
-                }
-                for (int c0 = cq * 64; c0 < cq * 64 + 64 && c0 < (int) n16; c0 += 32)
-                {
-                    uint32_t r0[32], r1[32];
-                    tmem_ld32(tmem + ((uint32_t) (lq * 32) << 16) + c0, r0);
-                    if (NMAT == 2) tmem_ld32(tmem + ((uint32_t) (lq * 32) << 16) + 256 + c0, r1);
-                    tmem_ld_wait();
-                    if (NMAT == 2)
-                    {
-                        #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                        {
-                            const int p = c0 + j;
-                            if (p < n)
-                            {
-                                const float gg = __uint_as_float(r0[j]) * sc0, uu = __uint_as_float(r1[j]) * sc1;
-                                float v = gg / (1.f + expf(-gg)) * uu * a.wt[pos0 + p];
-                                if (a.act_quant)
-                                {
-                                    // second int8 round trip of the CPU engine: 32 consecutive channels = this warp
-                                    float m = fabsf(v);
-                                    #pragma unroll
-                                    for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-                                    const float s = m > 0.f ? __fdiv_rn(m, 127.f) : 1.f;
-                                    v = __fmul_rn((float) __float2int_rn(__fmul_rn(v, __fdiv_rn(1.f, s))), s);
-                                    // code x scale does not fit fp16: keep it as hi + lo halves, the down GEMM walks both
-                                    const __half hi = __float2half_rn(v);
-                                    a.act[(size_t) (pos0 + p) * (2 * a.N) + ch] = hi;
-                                    a.act[(size_t) (pos0 + p) * (2 * a.N) + a.N + ch] = __float2half_rn(v - __half2float(hi));
-                                }
-                                else
-                                    a.act[(size_t) (pos0 + p) * a.N + ch] = __float2half_rn(v);
-                            }
-                        }
-                    }
-                    else
-                    {
-                        #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                        {
-                            const int p = c0 + j;
-                            if (p < n) atomicAdd(a.out + (size_t) a.tok[pos0 + p] * a.N + ch, __uint_as_float(r0[j]) * sc0);
-                        }
-                    }
-                }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(tmem_free);
-            }
+            if (!ok) break;
+            if (have_pend) { epilogue(pend); have_pend = false; }       // tiles with fewer than LEAD stages per warp
+            pend = cur; have_pend = true;
         }
-        else if (warp == NDQ)
+        if (ok && have_pend) epilogue(pend);
+    }
+    else if (warp == NDQ)
+    {
+        if (lane == 0)
         {
-            if (lane == 0)
+            uint32_t tile_n = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; item < nitems && ok; item += gridDim.x, ++tile_n)
+            {
+                const int pos0 = a.rbt[4 * (item / NCT) + 1];
                 for (int kb = 0; kb < KBT; ++kb)
                 {
                     const uint32_t it = tile_n * (uint32_t) KBT + kb, s = it % L::STAGES;
-                    if (it >= (uint32_t) L::STAGES && !mbar_wait(empty + s * 8, ((it / L::STAGES) - 1) & 1, abort_flag, a.status)) break;
+                    if (it >= (uint32_t) L::STAGES && !mbar_wait(empty + s * 8, ((it / L::STAGES) - 1) & 1, abort_flag, a.status)) { ok = false; break; }
                     mbar_expect_tx(full_b + s * 8, L::B_BYTES);
                     tma_load_2d(sbase + s * L::STAGE + NMAT * L::A_BYTES, &tmap, kb * 64, pos0, full_b + s * 8);
                 }
+            }
         }
-        else
+    }
+    else
+    {
+        if (lane == 0)
         {
-            if (lane == 0)
+            uint32_t tile_n = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; item < nitems && ok; item += gridDim.x, ++tile_n)
             {
+                const int n = a.rbt[4 * (item / NCT) + 2];
+                const uint32_t n16 = (uint32_t) ((n + 15) & ~15);
                 const uint32_t idesc = (1u << 4) | ((n16 >> 3) << 17) | ((uint32_t) (TM >> 4) << 24);
-                bool ok = tile_n == 0 || mbar_wait(tmem_free, (tile_n - 1) & 1, abort_flag, a.status);
-                if (ok) tc_fence_after();
+                const uint32_t acc = tile_n % NACC, tacc = tmem + acc * 256;
+                // the accumulator set is free once the tile that used it last has been read out
+                if (tile_n >= (uint32_t) NACC && !mbar_wait(tmem_free + acc * 8, ((tile_n / NACC) - 1) & 1, abort_flag, a.status)) break;
+                tc_fence_after();
                 for (int kb = 0; kb < KBT && ok; ++kb)
                 {
                     const uint32_t it = tile_n * (uint32_t) KBT + kb, s = it % L::STAGES, ph = (it / L::STAGES) & 1;
@@ -468,12 +513,12 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
                     for (int k = 0; k < 4; ++k)
                     {
                         const uint64_t bd = smem_desc_sw128(bt + k * 32);
-                        mma_f16_ss(tmem, smem_desc_sw128(at + k * 32), bd, idesc, (kb | k) != 0);
-                        if (NMAT == 2) mma_f16_ss(tmem + 256, smem_desc_sw128(at + L::A_BYTES + k * 32), bd, idesc, (kb | k) != 0);
+                        mma_f16_ss(tacc, smem_desc_sw128(at + k * 32), bd, idesc, (kb | k) != 0);
+                        if (NMAT == 2) mma_f16_ss(tacc + 256, smem_desc_sw128(at + L::A_BYTES + k * 32), bd, idesc, (kb | k) != 0);
                     }
                     tc_commit(empty + s * 8);
                 }
-                if (ok) tc_commit(done);
+                if (ok) tc_commit(done + acc * 8);
             }
         }
     }
