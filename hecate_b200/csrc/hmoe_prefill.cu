@@ -344,7 +344,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
         const int g = lane >> 2, q = lane & 3;
         const int strip = warp & 3, unit = (warp >> 2) & 1, mat = NMAT == 2 ? warp >> 3 : 0;
         const int kb0 = NMAT == 2 ? 0 : warp >> 3, kstep = NMAT == 2 ? 1 : 2;
-        constexpr int NPF = NMAT == 2 ? 4 : 8;             // down: short stages (one matrix) and short tiles, so a deeper queue
+        constexpr int NPF = 4;
         // own stages of the next tile produced before the epilogue: gate_up fills its whole ring (all three slots held the
         // finished tile's last stages, so none of them waits for the next tile's MMAs); down, whose warps take alternate stages and
         // whose MMAs are not held back by the read-out, does best with one (measured: 3/1 7.42 ms, 2/1 7.60, 3/2 7.84)
