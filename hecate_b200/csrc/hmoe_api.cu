@@ -115,6 +115,16 @@ int hmoe_prefill_ep(const hmoe_layer* layer, const void* x, int x_dtype, const i
     if (shared_rows < 0) return fail(HMOE_E_ARG, "hmoe_prefill_ep: shared_rows must be >= 0");
     return prefill_launch(layer, x, x_dtype, sel, rw, R, lo, n_local, act_quant, out, ws, ws_bytes, (cudaStream_t) stream, shared_row0, shared_rows);
 }
+int hmoe_prefill_ep_peer(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
+                         int act_quant, void* const* out_peer, int world, int rows_per_rank, void* ws, size_t ws_bytes, int shared_row0,
+                         int shared_rows, void* stream)
+{
+    if (!layer) return fail(HMOE_E_ARG, "hmoe_prefill_ep_peer: null layer");
+    if (!out_peer) return fail(HMOE_E_ARG, "hmoe_prefill_ep_peer: null output table");
+    return prefill_launch(layer, x, x_dtype, sel, rw, R, lo, n_local, act_quant, nullptr, ws, ws_bytes, (cudaStream_t) stream, shared_row0, shared_rows,
+                          out_peer, world, rows_per_rank);
+}
+
 size_t hmoe_prefill_sorted_ws_bytes(int npos, int H, int I, int act_quant) { return prefill_sorted_ws_bytes(npos, H, I, act_quant); }
 int hmoe_prefill_sorted(const hmoe_layer* layer, const void* x, int x_dtype, const int32_t* tok, const float* wt, const int32_t* rbt, int nrb,
                         int npos, int n_local, int act_quant, float* out, void* ws, size_t ws_bytes, void* stream)

@@ -74,7 +74,35 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(const EpArgs a, const u
     }
 }
 
+// Barrier over the ranks through the same flags: raise generation `gen` in every peer's memory, wait (bounded) until every
+// peer has raised it here. What a rank wrote into peer memory before this kernel (in stream order) is complete when the
+// peers pass the barrier: the flag is stored with release semantics at system scope after a system-wide fence.
+__global__ void __launch_bounds__(32) ep_barrier_kernel(const EpArgs a, unsigned gen, unsigned* __restrict__ status)
+{
+    __threadfence_system();
+    if ((int) threadIdx.x < a.world) st_release_sys(a.flags[threadIdx.x] + a.rank, gen);
+    if ((int) threadIdx.x < a.world)
+    {
+        const unsigned long long t0 = globaltimer_ns();
+        while ((int) (ld_acquire_sys(a.flags[a.rank] + threadIdx.x) - gen) < 0)
+            if (globaltimer_ns() - t0 > 2000000000ull) { atomicOr(status, ST_WAIT_TIMEOUT); break; }
+    }
+    __threadfence_system();
+}
+
 }  // namespace
+
+int ep_barrier_launch(int rank, int world, void* const* flags, unsigned gen, unsigned* status, cudaStream_t st)
+{
+    if (world < 1 || world > 8 || rank < 0 || rank >= world || !flags || !status) return fail(HMOE_E_ARG, "hmoe_ep_barrier: arguments");
+    EpArgs a;
+    a.rank = rank; a.world = world;
+    for (int p = 0; p < 8; ++p) { a.slots[p] = nullptr; a.flags[p] = p < world ? (unsigned*) flags[p] : nullptr; }
+    ep_barrier_kernel<<<1, 32, 0, st>>>(a, gen, status);
+    count_launches(1);
+    const cudaError_t err = cudaGetLastError();
+    return err == cudaSuccess ? HMOE_OK : fail(HMOE_E_CUDA, cudaGetErrorString(err));
+}
 
 int ep_combine_launch(int rank, int world, void* const* slots, void* const* flags, const unsigned* gen, float* f, int rows, int H, size_t slot_floats,
                       unsigned* status, cudaStream_t st)
@@ -136,6 +164,23 @@ int hmoe_ep_combine(int rank, int world, void* const* slots, void* const* flags,
                     uint32_t* status, void* stream)
 {
     return ep_combine_launch(rank, world, slots, flags, gen, f, rows, H, slot_floats, status, (cudaStream_t) stream);
+}
+
+int hmoe_ep_memset(void* ptr, int value, size_t bytes, void* stream)
+{
+    if (!ptr) return fail(HMOE_E_ARG, "hmoe_ep_memset: null pointer");
+    return cudaMemsetAsync(ptr, value, bytes, (cudaStream_t) stream) == cudaSuccess ? HMOE_OK : fail(HMOE_E_CUDA, "hmoe_ep_memset: cudaMemsetAsync failed");
+}
+int hmoe_ep_copy(void* dst, const void* src, size_t bytes, void* stream)
+{
+    if (!dst || !src) return fail(HMOE_E_ARG, "hmoe_ep_copy: null pointer");
+    return cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, (cudaStream_t) stream) == cudaSuccess ? HMOE_OK
+                                                                                                           : fail(HMOE_E_CUDA, "hmoe_ep_copy: cudaMemcpyAsync failed");
+}
+
+int hmoe_ep_barrier(int rank, int world, void* const* flags, uint32_t gen, uint32_t* status, void* stream)
+{
+    return ep_barrier_launch(rank, world, flags, gen, status, (cudaStream_t) stream);
 }
 
 }  // extern "C"

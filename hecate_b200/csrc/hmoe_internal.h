@@ -25,7 +25,9 @@ int router_launch(const void* x, int x_dtype, const void* wt, int w_dtype, const
 
 size_t prefill_ws_bytes(int R, int topk, int n_local, int H, int I, int act_quant);
 int prefill_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
-                   int act_quant, float* out, void* ws, size_t ws_bytes, cudaStream_t st, int shared_row0 = 0, int shared_rows = -1);
+                   int act_quant, float* out, void* ws, size_t ws_bytes, cudaStream_t st, int shared_row0 = 0, int shared_rows = -1,
+                   void* const* out_peer = nullptr, int world = 1, int rows_per_rank = 0);
+int ep_barrier_launch(int rank, int world, void* const* flags, unsigned gen, unsigned* status, cudaStream_t st);
 size_t prefill_sorted_ws_bytes(int npos, int H, int I, int act_quant);
 int prefill_sorted_launch(const hmoe_layer* L, const void* x, int x_dtype, const int32_t* tok, const float* wt, const int32_t* rbt, int nrb,
                           int npos, int n_local, int act_quant, float* out, void* ws, size_t ws_bytes, cudaStream_t st);

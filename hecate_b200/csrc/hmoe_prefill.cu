@@ -253,6 +253,8 @@ struct GemmArgs
     const Plan* plan; const int* rbt; const int* tok; const float* wt;
     __half* act;              // gate_up: output [pos][I]
     float* out;               // down: output [R][H], added into
+    float* out_peer[8];       // expert parallel, combine over peer memory: row t belongs to rank t / rows_per_rank and is added
+    int rows_per_rank;        //   into out_peer[rank][(t % rows_per_rank)][H] (peer pointers over NVLink); 0 = off
     unsigned* status;
 };
 
@@ -409,7 +411,13 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
                     for (int j = 0; j < 16; ++j)
                     {
                         const int p = c0 + j;
-                        if (p < t.n) atomicAdd(a.out + (size_t) a.tok[t.pos0 + p] * a.N + ch, __uint_as_float(r0[j]) * sc0);
+                        if (p < t.n)
+                        {
+                            const int tk = a.tok[t.pos0 + p];
+                            float* dst = a.out + (size_t) tk * a.N;
+                            if (a.rows_per_rank) { const int pr = tk / a.rows_per_rank; dst = a.out_peer[pr] + (size_t) (tk - pr * a.rows_per_rank) * a.N; }
+                            atomicAdd(dst + ch, __uint_as_float(r0[j]) * sc0);
+                        }
                     }
                 }
             }
@@ -649,6 +657,8 @@ int prefill_sorted_launch(const hmoe_layer* L, const void* x, int x_dtype, const
     GemmArgs g;
     g.grouped = L->group != 0; g.act_quant = act_quant; g.n_local = n_local; g.kfold = kf;
     g.plan = plan; g.rbt = rbt; g.tok = tok; g.wt = wt; g.act = act; g.out = out; g.status = status;
+    g.rows_per_rank = 0;
+    for (int p = 0; p < 8; ++p) g.out_peer[p] = nullptr;
     g.K = H; g.N = I; g.w0 = L->gate_w; g.w1 = L->up_w; g.s0 = L->gate_s; g.s1 = L->up_s;
     g.sh_w0 = L->sh_gate_w; g.sh_w1 = L->sh_up_w; g.sh_s0 = L->sh_gate_s; g.sh_s1 = L->sh_up_s;
     prefill_gemm_kernel<2><<<sms, PF_THREADS, PfSmem<2>::total, st>>>(mx, g);
@@ -683,9 +693,12 @@ size_t permute_ws_bytes(int R, int topk, int n_local)
 }
 
 int prefill_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
-                   int act_quant, float* out, void* ws, size_t ws_bytes, cudaStream_t st, int shared_row0, int shared_rows)
+                   int act_quant, float* out, void* ws, size_t ws_bytes, cudaStream_t st, int shared_row0, int shared_rows,
+                   void* const* out_peer, int world, int rows_per_rank)
 {
-    if (shared_rows < 0) { shared_row0 = 0; shared_rows = R; }          // default: the shared expert takes every row
+    if (shared_rows < 0) { shared_row0 = 0; shared_rows = R; }
+    if (out_peer && (world < 1 || world > 8 || rows_per_rank < 1 || (long long) world * rows_per_rank < R))
+        return fail(HMOE_E_ARG, "hmoe_prefill_ep_peer: world must be 1..8 and world * rows_per_rank must cover the rows");          // default: the shared expert takes every row
     if (shared_row0 < 0 || shared_row0 + shared_rows > R) return fail(HMOE_E_ARG, "hmoe_prefill: shared row range outside the rows");
     const int H = L->H, I = L->I;
     if (R < 1) return fail(HMOE_E_ARG, "hmoe_prefill: rows must be >= 1");
@@ -695,7 +708,7 @@ int prefill_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_
     if (!(L->group == 0 && L->scale_dtype == HMOE_F32) && !(L->group == 128 && L->scale_dtype == HMOE_BF16))
         return fail(HMOE_E_ARG, "hmoe_prefill: scales must be fp32 per row (group 0) or bf16 per 128 columns");
     if (x_dtype != HMOE_F16 && x_dtype != HMOE_BF16) return fail(HMOE_E_ARG, "hmoe_prefill: x must be fp16 or bf16");
-    if (!x || !sel || !rw || !out || !ws) return fail(HMOE_E_ARG, "hmoe_prefill: null pointer");
+    if (!x || !sel || !rw || (!out && !out_peer) || !ws) return fail(HMOE_E_ARG, "hmoe_prefill: null pointer");
     const int kf = act_quant ? 2 : 1;
     const WsLayout w = ws_layout(R, L->topk, n_local, H, I, TN, kf);
     if (ws_bytes < w.total) return fail(HMOE_E_WS, "hmoe_prefill: workspace too small (the int8 mode needs hmoe_prefill_ws_bytes(..., act_quant = 1))");
@@ -726,6 +739,8 @@ int prefill_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_
     GemmArgs g;
     g.grouped = L->group != 0; g.act_quant = act_quant; g.n_local = n_local; g.kfold = kf;
     g.plan = plan; g.rbt = rbt; g.tok = tok; g.wt = wt; g.act = act; g.out = out; g.status = status;
+    g.rows_per_rank = out_peer ? rows_per_rank : 0;
+    for (int p = 0; p < 8; ++p) g.out_peer[p] = (out_peer && p < world) ? (float*) out_peer[p] : nullptr;
     g.K = H; g.N = I; g.w0 = L->gate_w; g.w1 = L->up_w; g.s0 = L->gate_s; g.s1 = L->up_s;
     g.sh_w0 = L->sh_gate_w; g.sh_w1 = L->sh_up_w; g.sh_s0 = L->sh_gate_s; g.sh_s1 = L->sh_up_s;
     prefill_gemm_kernel<2><<<sms, PF_THREADS, PfSmem<2>::total, st>>>(mx, g);

@@ -32,10 +32,10 @@ class PeerBuffers:
     """Symmetric buffers of the combine: per rank two fp32 partial slots [MAX_ROWS * H] and `world` generation flags,
     allocated with cudaMalloc by the library, exported with CUDA IPC and opened by every peer."""
 
-    def __init__(self, rank, world, H, device, dist):
+    def __init__(self, rank, world, H, device, dist, slot_floats=None):
         import torch
         self.rank, self.world, self.H = rank, world, H
-        self.slot_floats = MAX_ROWS * H
+        self.slot_floats = MAX_ROWS * H if slot_floats is None else (slot_floats + 63) // 64 * 64
         self.bytes = 2 * self.slot_floats * 4 + 512          # two slots, `world` flags (256 B), the generation word (256 B)
         p = C.c_void_p()
         check(lib().hmoe_ep_alloc(C.c_size_t(self.bytes), C.byref(p)))
@@ -112,11 +112,13 @@ class EpDecoder:
 
 
 class EpPrefill:
-    """Expert-parallel prefill, collectives by NCCL: the ranks' token slices are all-gathered (dispatch), every rank runs the
-    grouped GEMMs for its experts over all tokens (ids outside [lo, lo + n_local) are dropped by the permutation) plus the
-    shared expert for its own tokens, and a reduce-scatter returns each rank its tokens' sums (combine)."""
+    """Expert-parallel prefill. Dispatch: the ranks' token slices are all-gathered (NCCL); every rank runs the grouped GEMMs
+    for its experts over all tokens (ids outside [lo, lo + n_local) are dropped by the permutation) plus the shared expert
+    for its own tokens. Combine, use_peer = True: the down GEMM adds every row's sums straight into the output of the rank
+    that owns the row, over NVLink peer memory, and a flag barrier ends the step. use_peer = False (the baseline): a local
+    full-size partial and an NCCL reduce-scatter."""
 
-    def __init__(self, rank, world, tables, n_experts, rows_per_rank, device, dist):
+    def __init__(self, rank, world, tables, n_experts, rows_per_rank, device, dist, use_peer=True):
         import torch
         self.rank, self.world, self.tabs, self.dev, self.dist, self.rpr = rank, world, tables, device, dist, rows_per_rank
         self.plan = shard_plan(rank, world, n_experts)
@@ -126,19 +128,40 @@ class EpPrefill:
         self.x_all = torch.empty(R, tables.H, dtype=torch.bfloat16, device=device)
         self.sel_all = torch.empty(R, tables.topk, dtype=torch.int64, device=device)
         self.rw_all = torch.empty(R, tables.topk, dtype=torch.float16, device=device)
-        self.partial = torch.empty(R, tables.H, dtype=torch.float32, device=device)
+        self.use_peer = use_peer and world > 1
         self.struct = tables.struct()
+        self.gen = 0
+        if self.use_peer:
+            # one slot of the symmetric buffer is this rank's output [rows_per_rank][H]; the flags serve the barrier
+            self.peer = PeerBuffers(rank, world, tables.H, device, dist, slot_floats=rows_per_rank * tables.H)
+            self.out_tab = (C.c_void_p * world)(*self.peer.base)
+        else:
+            self.peer = None
+            self.partial = torch.empty(R, tables.H, dtype=torch.float32, device=device)
 
     def step(self, x, sel, rw, out):
         """x bf16 [R/W][H], sel, rw: this rank's tokens; out fp32 [R/W][H] receives their MoE output."""
         import torch
         d, pl = self.dist, self.plan
+        st = C.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)
+        nbytes = self.rpr * self.tabs.H * 4
+        if self.use_peer:
+            # own output cleared before the step's first collective: when the all-gather returns on a peer, this rank has passed it
+            check(lib().hmoe_ep_memset(C.c_void_p(self.peer.own), C.c_int(0), C.c_size_t(nbytes), st))
         if self.world > 1:
             d.all_gather_into_tensor(self.x_all, x); d.all_gather_into_tensor(self.sel_all, sel); d.all_gather_into_tensor(self.rw_all, rw)
         else:
             self.x_all.copy_(x); self.sel_all.copy_(sel); self.rw_all.copy_(rw)
+        if self.use_peer:
+            self.gen += 1
+            check(lib().hmoe_prefill_ep_peer(C.byref(self.struct), vp(self.x_all), C.c_int(moe._dt(self.x_all)), vp(self.sel_all), vp(self.rw_all),
+                                             C.c_int(self.R), C.c_int(pl["lo"]), C.c_int(pl["n_local"]), C.c_int(0), self.out_tab,
+                                             C.c_int(self.world), C.c_int(self.rpr), vp(self.ws), C.c_size_t(self.ws.numel()),
+                                             C.c_int(self.rank * self.rpr), C.c_int(self.rpr), st))
+            check(lib().hmoe_ep_barrier(C.c_int(self.rank), C.c_int(self.world), self.peer.flags, C.c_uint32(self.gen), vp(self.peer.status), st))
+            check(lib().hmoe_ep_copy(vp(out), C.c_void_p(self.peer.own), C.c_size_t(nbytes), st))
+            return out
         self.partial.zero_()
-        st = C.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)
         check(lib().hmoe_prefill_ep(C.byref(self.struct), vp(self.x_all), C.c_int(moe._dt(self.x_all)), vp(self.sel_all), vp(self.rw_all),
                                     C.c_int(self.R), C.c_int(pl["lo"]), C.c_int(pl["n_local"]), C.c_int(0), vp(self.partial), vp(self.ws),
                                     C.c_size_t(self.ws.numel()), C.c_int(self.rank * self.rpr), C.c_int(self.rpr), st))
@@ -147,6 +170,14 @@ class EpPrefill:
         else:
             out.copy_(self.partial)
         return out
+
+    def status(self):
+        import torch
+        torch.cuda.synchronize(self.dev)
+        s = moe.ws_status(self.ws)
+        if self.peer is not None:
+            s |= int(self.peer.status.item())
+        return s
 
 
 def bench_prefill(args, world, rank, dev):
@@ -165,23 +196,34 @@ def bench_prefill(args, world, rank, dev):
     x = torch.from_numpy(synth.activations(rank, 0, rpr, H)).to(torch.bfloat16).to(dev)
     sel = torch.from_numpy(sel_all[rank * rpr:(rank + 1) * rpr]).to(dev); rw = torch.from_numpy(rw_all[rank * rpr:(rank + 1) * rpr]).to(dev)
     out = torch.empty(rpr, H, dtype=torch.float32, device=dev)
-    ep = EpPrefill(rank, world, tabs, E, rpr, dev, dist)
-    for _ in range(warmup):
-        ep.step(x, sel, rw, out)
-    torch.cuda.synchronize(); dist.barrier()
-    l0 = moe.launch_count()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with B.ClockSampler(dev.index) as cs:
-        torch.cuda.synchronize(); dist.barrier()
-        ev0.record()
-        for _ in range(steps):
+    times = {}
+    st_all = 0
+    launches = 0
+    for mode in ("nccl", "peer"):
+        ep = EpPrefill(rank, world, tabs, E, rpr, dev, dist, use_peer=(mode == "peer"))
+        for _ in range(warmup):
             ep.step(x, sel, rw, out)
-        ev1.record()
         torch.cuda.synchronize(); dist.barrier()
-    ms = torch.tensor([ev0.elapsed_time(ev1) / steps], device=dev)
-    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    launches = moe.launch_count() - l0
-    st = torch.tensor([moe.ws_status(ep.ws)], device=dev); dist.all_reduce(st, op=dist.ReduceOp.MAX)
+        l0 = moe.launch_count()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with B.ClockSampler(dev.index) as cs:
+            torch.cuda.synchronize(); dist.barrier()
+            ev0.record()
+            for _ in range(steps):
+                ep.step(x, sel, rw, out)
+            ev1.record()
+            torch.cuda.synchronize(); dist.barrier()
+        ms = torch.tensor([ev0.elapsed_time(ev1) / steps], device=dev)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        times[mode] = float(ms.item())
+        launches = moe.launch_count() - l0
+        st = torch.tensor([ep.status()], device=dev); dist.all_reduce(st, op=dist.ReduceOp.MAX)
+        st_all |= int(st.item())
+        if ep.peer is not None:
+            dist.barrier(); ep.peer.close()
+        del ep
+    ms = torch.tensor([times["peer"]], device=dev)
+    st = torch.tensor([st_all], device=dev)
     picks = np.array([int(((sel_all >= r * pl["n_local"]) & (sel_all < (r + 1) * pl["n_local"])).sum()) for r in range(world)])
     if rank == 0:
         flop = 2.0 * (TOPK * R + R) * (3 * I * H)
@@ -193,9 +235,9 @@ def bench_prefill(args, world, rank, dev):
             "warmup": warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "int4 -> fp16 x fp16 -> fp32 (tcgen05)", "data": "synthetic",
             "config": {"workload": f"prefill M={R} tokens over {world} GPUs ({rpr} each), Zipf({args.zipf}) top-8 over {E} experts + shared, "
-                                   f"experts split {pl['n_local']} per GPU, all-gather dispatch + reduce-scatter combine (NCCL)",
+                                   f"experts split {pl['n_local']} per GPU, all-gather dispatch (NCCL), combine fused into the down GEMM over NVLink peer memory",
                        "l2": "inputs larger than L2"},
-            "tokens_per_s": R / t,
+            "tokens_per_s": R / t, "nccl_reduce_scatter_ms_per_step": times["nccl"],
             "dispatch_bytes_per_rank": (world - 1) * rpr * (H * 2 + TOPK * 10), "combine_bytes_per_rank": (world - 1) * rpr * H * 4,
             "picks_per_rank": picks.tolist(), "load_imbalance_max_over_mean": float(picks.max() / picks.mean()),
             "roofline": {"bound": "tensor", "kernel": "whole step incl. collectives", "achieved": flop / t / 1e12, "peak": peak, "unit": "TFLOP/s",

@@ -116,6 +116,23 @@ int hmoe_prefill(const hmoe_layer* layer, const void* x, int x_dtype, const int6
 int hmoe_prefill_ep(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
                     int act_quant, float* out, void* ws, size_t ws_bytes, int shared_row0, int shared_rows, void* stream);
 
+/* hmoe_prefill_ep with the combine fused into the down GEMM (no reference counterpart): row t of the R = world * rows_per_rank
+ * gathered rows belongs to rank t / rows_per_rank, and its sums are added straight into that rank's output
+ * out_peer[rank][t % rows_per_rank][H] with fp32 reductions over NVLink peer memory (out_peer: host array of `world` device
+ * pointers, the own one and the peers' opened with hmoe_ep_open). Every rank zeroes its own output before the step's first
+ * collective and calls hmoe_ep_barrier after this call; its output is complete when the barrier has passed.
+ * hmoe_ep_barrier: raises generation `gen` (a number that grows by one per step) in every peer's flag array (flags[p] =
+ * rank p's array of `world` words, zero at start) and waits, at most 2 s, until every peer has raised it here; on a
+ * time-out bit 0 of *status is set and the kernel returns. */
+int hmoe_prefill_ep_peer(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
+                         int act_quant, void* const* out_peer, int world, int rows_per_rank, void* ws, size_t ws_bytes, int shared_row0,
+                         int shared_rows, void* stream);
+int hmoe_ep_barrier(int rank, int world, void* const* flags, uint32_t gen, uint32_t* status, void* stream);
+/* Stream-ordered memset / device-to-device copy for memory obtained from hmoe_ep_alloc (which the host language may have no
+ * tensor for). */
+int hmoe_ep_memset(void* ptr, int value, size_t bytes, void* stream);
+int hmoe_ep_copy(void* dst, const void* src, size_t bytes, void* stream);
+
 /* The same two grouped GEMMs with the reference's calling convention, for callers that keep the reference's host-side
  * permutation: replaces moe4t.forward / moe4p.forward(x, tok, eid, wt, rbt, gw, uw, dw, gs, us, ds, gu, ar, d, out)
  * (runtime/tier/moe4/moe4t.cu:498-524). tok int32 [npos] (token of each sorted pick), wt fp32 [npos], rbt int32 [nrb][4] =

@@ -10,6 +10,8 @@ Writes
                      from its source text
   layout.npz         bytes written by the reference's pack_u4 (tools/quant/gptq_int4.py:74-77) and codes recovered by its
                      _unpack_moe4 / _rowmajor_i4 (runtime/tier/tier_split.py:98-106), executed from their source text
+  quant.npz          scales chosen by the reference's per-row recipe scales_mse (tools/quant/gptq_int4.py:62-71, with its
+                     candidate list U4F, :38), executed from its source text on a seeded matrix (`--only quant` writes just this)
 No reference source is copied: the functions are compiled from the files where they lie at generation time only.
 """
 import ast
@@ -66,8 +68,37 @@ def _function_from(path, name, glb):
     raise KeyError(name)
 
 
+def _assignment_from(path, name, glb):
+    tree = ast.parse(open(path).read())
+    for node in tree.body:
+        if isinstance(node, ast.Assign) and any(isinstance(t, ast.Name) and t.id == name for t in node.targets):
+            exec(compile(ast.Module(body=[node], type_ignores=[]), path, "exec"), glb)
+            return glb[name]
+    raise KeyError(name)
+
+
+def quant_matrix():
+    """The seeded matrix of quant.npz: 24 rows x 256 columns, rows of very different magnitude."""
+    w = synth.normal(21, 5150, 24 * 256).reshape(24, 256).astype(np.float32)
+    return w * (10.0 ** np.linspace(-3, 1, 24, dtype=np.float32))[:, None]
+
+
+def write_quant():
+    import torch
+    path = os.path.join(REF, "tools/quant/gptq_int4.py")
+    glb = {"torch": torch, "dev": "cpu"}
+    _assignment_from(path, "U4F", glb)
+    scales_mse = _function_from(path, "scales_mse", glb)
+    W = quant_matrix()
+    s = scales_mse(torch.from_numpy(W)).numpy()
+    np.savez_compressed(os.path.join(HERE, "quant.npz"), scales=s, u4f=glb["U4F"].numpy())
+    print("quant.npz written")
+
+
 def main():
     import torch
+    if "--only" in sys.argv and sys.argv[sys.argv.index("--only") + 1] == "quant":
+        return write_quant()
     build.build_oracle(); assert build.build_ref(), "needs the reference tree"
     # 1. engine jobs
     ex = job_experts()
@@ -106,6 +137,7 @@ def main():
     assert np.array_equal(unpack(torch.from_numpy(q), N, K).numpy(), codes)
     rm = rowmajor(torch.from_numpy(q), N, K).numpy()
     np.savez_compressed(os.path.join(HERE, "layout.npz"), codes=codes, packed=q, rowmajor=rm)
+    write_quant()
     print("golden fixtures written")
 
 

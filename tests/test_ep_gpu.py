@@ -122,19 +122,26 @@ def _prefill_rank_main(rank, world, port, out_path):
     local = HostLayer(0, 0, H, I, range(p["lo"], p["lo"] + p["n_local"]), 128, True).upload(dev)
     xa = synth.activations(1, 0, R, H); sel, rw = synth.zipf_routing(2, 0, R, E, 8, 1.1)
     sl = slice(rank * rpr, (rank + 1) * rpr)
-    ep = EpPrefill(rank, world, local, E, rpr, dev, dist)
-    out = torch.empty(rpr, H, device=dev)
-    ep.step(torch.from_numpy(xa[sl]).to(dev).to(torch.bfloat16), torch.from_numpy(sel[sl]).to(dev), torch.from_numpy(rw[sl]).to(dev), out)
-    assert moe.ws_status(ep.ws) == 0
+    errs = []
+    outs = {}
+    for use_peer in (False, True):
+        ep = EpPrefill(rank, world, local, E, rpr, dev, dist, use_peer=use_peer)
+        out = torch.empty(rpr, H, device=dev)
+        for _ in range(2):                     # twice: the second step reuses the zeroed peer buffer and the next barrier generation
+            ep.step(torch.from_numpy(xa[sl]).to(dev).to(torch.bfloat16), torch.from_numpy(sel[sl]).to(dev), torch.from_numpy(rw[sl]).to(dev), out)
+        assert ep.status() == 0
+        outs[use_peer] = out
     gathered = [torch.empty_like(out) for _ in range(world)]
-    dist.all_gather(gathered, out)
+    dist.all_gather(gathered, outs[True])
+    gathered_nccl = [torch.empty_like(out) for _ in range(world)]
+    dist.all_gather(gathered_nccl, outs[False])
     if rank == 0:
         full = HostLayer(0, 0, H, I, range(E), 128, True).upload(dev)
         ws = moe.prefill_workspace(R, 8, E, H, I, dev)
         ref = torch.zeros(R, H, device=dev)
         moe.prefill(full, torch.from_numpy(xa).to(dev).to(torch.bfloat16), torch.from_numpy(sel).to(dev), torch.from_numpy(rw).to(dev), ref, ws)
-        got = torch.cat(gathered)
-        np.save(out_path, np.array([float((got - ref).norm() / ref.norm())]))
+        got = torch.cat(gathered); got_nccl = torch.cat(gathered_nccl)
+        np.save(out_path, np.array([float((got - ref).norm() / ref.norm()), float((got_nccl - ref).norm() / ref.norm())]))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -146,4 +153,5 @@ def test_two_gpu_prefill_matches_single_gpu(tmp_path):
     import torch.multiprocessing as mp
     out = str(tmp_path / "epp.npy")
     mp.spawn(_prefill_rank_main, args=(2, 29700 + os.getpid() % 2000, out), nprocs=2, join=True)
-    assert np.load(out)[0] < 1e-3
+    e = np.load(out)
+    assert e[0] < 1e-3 and e[1] < 1e-3, e        # peer-memory combine, NCCL reduce-scatter combine
