@@ -218,6 +218,21 @@ def moe4_combine(f, o_ptr, y, rows, o2_ptr, done_ptr=0):
     check(lib().hmoe_combine(vp(f), vp(o_ptr or None), vp(y), C.c_int64(n), vp(o2_ptr or None), _stream(f.device)))
 
 
+def combine_norm(f, o_ptr, y, rows, o2_ptr, done_ptr, r, w, xn, eps, cbias=0.0, cscale=1.0):
+    """combine_norm (runtime/tier/cn.cu:190-210): the layer's combine fused into the next layer's input norm. f fp32 [rows][H]
+    or None; y the accumulator (zeroed here); r fp32 residual, updated in place; w the norm weight (fp16 / bf16 [H]); xn fp16
+    out. done_ptr (a flag another device raises) is not supported."""
+    if done_ptr:
+        raise HmoeError("combine_norm: done flag not supported")
+    if r.dtype != torch.float32 or xn.dtype != torch.float16 or not (r.is_contiguous() and xn.is_contiguous() and w.is_contiguous()):
+        raise HmoeError("combine_norm: shapes / dtypes")
+    Hn = r.shape[-1]
+    if w.numel() != Hn or xn.shape[-1] != Hn or y.shape[-1] != Hn:
+        raise HmoeError("combine_norm: shapes / dtypes")
+    check(lib().hmoe_combine_norm(vp(f), vp(o_ptr or None), vp(y), vp(o2_ptr or None), vp(r), vp(w), C.c_int(_dt(w)), vp(xn), C.c_int(int(rows)),
+                                  C.c_int(Hn), C.c_float(eps), C.c_float(cbias), C.c_float(cscale), _stream(r.device)))
+
+
 def moe4_dequant(q, sc, N, K, group=0):
     """moe4.dequant(q, sc, N, K) -> fp16 [N][K] (moe4.cu:904-911)."""
     out = torch.empty((N, K), dtype=torch.float16, device=q.device)

@@ -168,6 +168,13 @@ int hmoe_decode_phase_times(float* ms3);
  * f += y (+ o) (+ o2) in that order, then y = 0. o and o2 may be null. n = rows * H must be a multiple of 4. */
 int hmoe_combine(float* f, const float* o, float* y, int64_t n, const float* o2, void* stream);
 
+/* The combine fused into the next layer's input norm: replaces combine_norm(f, o_ptr, y, rows, o2_ptr, done_ptr, r, w, xn, eps,
+ * cbias, cscale) (runtime/tier/cn.cu:50-105,190-210). Per row: a = ((f + y) + o) + o2 (f, o, o2 may be null), y = 0,
+ * r += a (fp32 residual [rows][H], in place), xn = fp16(r * (w + cbias) * rsqrt(mean(r^2) + eps) * cscale), w fp16 or bf16 [H].
+ * Same column ownership and summation order as the reference kernel. H % 4 == 0, H <= 16384. f is not written. */
+int hmoe_combine_norm(const float* f, const float* o, float* y, const float* o2, float* r, const void* w, int w_dtype, void* xn, int rows, int H,
+                      float eps, float cbias, float cscale, void* stream);
+
 /* Dequantise one packed matrix to fp16 [N][K] (value * scale): replaces moe4.dequant(q, sc, N, K)
  * (runtime/tier/moe4/moe4.cu:679-698,904-911); group / scale_dtype as in hmoe_layer. */
 int hmoe_dequant(const void* q, const void* scales, int group, int scale_dtype, int N, int K, void* out_f16, void* stream);

@@ -189,3 +189,41 @@ class RefEngine:
 
     def stop(self):
         self.mod.stop()
+
+
+def combine_norm(f, o, y, o2, r, w, eps, cbias=0.0, cscale=1.0, threads=1024):
+    """CPU restatement of the combine fused into the next input norm (runtime/tier/cn.cu:50-105), float32 throughout and in the
+    kernel's order: a = ((f + y) + o) + o2; r' = a + r; per thread t the squares of float4 columns t, t + 1024, ... are added
+    with fused multiply-adds (x, y, z, w in turn), the 32 lanes of a warp are summed by a butterfly (xor 16 .. 1), the 32 warp
+    sums by a second one; xn = fp16(r' * (w + cbias) * (rsqrt(sum / H + eps) * cscale)). Returns (r', xn, sum of squares).
+    f, o, o2 may be None; w float32 [H] (the fp16 / bf16 weight widened). The reciprocal square root here is exact; the GPU's
+    is a 2-ulp approximation, so xn may differ in its last bit."""
+    y = np.asarray(y, dtype=np.float32)
+    rows, H = y.shape
+    a = np.zeros_like(y) if f is None else np.asarray(f, dtype=np.float32).copy()
+    a = a + y
+    if o is not None:
+        a = a + np.asarray(o, dtype=np.float32)
+    if o2 is not None:
+        a = a + np.asarray(o2, dtype=np.float32)
+    rn = (a + np.asarray(r, dtype=np.float32)).astype(np.float32)
+    cols = H // 4
+    sums = np.zeros((rows, threads), dtype=np.float32)
+    fma = lambda x, s: (x.astype(np.float64) * x.astype(np.float64) + s.astype(np.float64)).astype(np.float32)
+    for k in range((cols + threads - 1) // threads):
+        c = np.arange(threads) + k * threads
+        ok = c < cols
+        for j in range(4):
+            x = np.zeros((rows, threads), dtype=np.float32)
+            x[:, ok] = rn[:, 4 * c[ok] + j]
+            sums = np.where(ok[None, :], fma(x, sums), sums)
+    def butterfly(v):                      # v [rows][n_groups][32]
+        for off in (16, 8, 4, 2, 1):
+            v = (v + v[..., np.arange(32) ^ off]).astype(np.float32)
+        return v
+    warp = butterfly(sums.reshape(rows, threads // 32, 32))[..., 0]                 # [rows][32 warps]
+    total = butterfly(warp.reshape(rows, 1, 32))[:, 0, 0]
+    rmf = (np.float32(1.0) / np.sqrt((total / np.float32(H) + np.float32(eps)).astype(np.float32), dtype=np.float32)).astype(np.float32) * np.float32(cscale)
+    ww = (np.asarray(w, dtype=np.float32) + np.float32(cbias)).astype(np.float32) if cbias != 0.0 else np.asarray(w, dtype=np.float32)
+    xn = ((rn * ww[None, :]).astype(np.float32) * rmf[:, None]).astype(np.float32).astype(np.float16)
+    return rn, xn, total
