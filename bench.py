@@ -400,6 +400,9 @@ def main():
     ap.add_argument("--mode", default="decode", choices=["decode", "prefill"], help="decode (default, the headline) or prefill")
     ap.add_argument("--rows", type=int, default=8192, help="prefill rows")
     ap.add_argument("--zipf", type=float, default=1.1, help="prefill expert popularity exponent (0 = uniform)")
+    ap.add_argument("--placement", default="auto", choices=["auto", "contiguous", "balanced"],
+                    help="N > 1 prefill: expert -> GPU map; auto = balanced by load when --zipf > 0")
+    ap.add_argument("--extra-slots", type=int, default=0, help="N > 1 prefill, balanced placement: slots for copies of the hottest experts")
     ap.add_argument("--experts", type=int, default=E, help="routed experts resident (256 = the benchmark; fewer only for profiling)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -189,10 +189,23 @@ def bench_prefill(args, world, rank, dev):
     E, H, I, TOPK = B.E, B.H, B.I, B.TOPK
     R = args.rows
     rpr = R // world
-    pl = shard_plan(rank, world, E)
-    tabs = B.build_layer(dev, 100 + rank, list(range(pl["lo"], pl["lo"] + pl["n_local"])), torch, moe)
     steps, warmup = min(args.steps, 50), max(3, min(args.warmup, 5))
     sel_all, rw_all = synth.zipf_routing(10, 0, R, E, TOPK, args.zipf)
+    # Placement: "contiguous" = expert e on GPU e // (E / world); "balanced" = experts dealt to the GPUs by load
+    # (hecate_b200.placement.balance) from the pick counts of ANOTHER sample of the same popularity (the routing log of an
+    # earlier chunk), optionally with extra slots for copies of the hottest experts. The selection is then expressed in router
+    # positions, as a router with permuted weight rows would emit it.
+    from . import placement as PL
+    want = getattr(args, "placement", "auto")
+    use_plan = want == "balanced" or (want == "auto" and args.zipf > 0)
+    base_imb = PL.contiguous(PL.pick_counts(sel_all, E), world).imbalance()
+    if use_plan:
+        cal, _ = synth.zipf_routing(11, 0, R, E, TOPK, args.zipf)
+        plan = PL.balance(PL.pick_counts(cal, E), world, extra_slots=getattr(args, "extra_slots", 0))
+        sel_all = PL.positions(sel_all, plan)
+        E = len(plan.perm)
+    pl = shard_plan(rank, world, E)
+    tabs = B.build_layer(dev, 100 + rank, list(range(pl["lo"], pl["lo"] + pl["n_local"])), torch, moe)
     x = torch.from_numpy(synth.activations(rank, 0, rpr, H)).to(torch.bfloat16).to(dev)
     sel = torch.from_numpy(sel_all[rank * rpr:(rank + 1) * rpr]).to(dev); rw = torch.from_numpy(rw_all[rank * rpr:(rank + 1) * rpr]).to(dev)
     out = torch.empty(rpr, H, dtype=torch.float32, device=dev)
@@ -235,11 +248,13 @@ def bench_prefill(args, world, rank, dev):
             "warmup": warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "int4 -> fp16 x fp16 -> fp32 (tcgen05)", "data": "synthetic",
             "config": {"workload": f"prefill M={R} tokens over {world} GPUs ({rpr} each), Zipf({args.zipf}) top-8 over {E} experts + shared, "
-                                   f"experts split {pl['n_local']} per GPU, all-gather dispatch (NCCL), combine fused into the down GEMM over NVLink peer memory",
+                                   f"{pl['n_local']} expert slots per GPU ({'placed by load from a calibration sample' if use_plan else 'contiguous ids'}), "
+                                   f"all-gather dispatch (NCCL), combine fused into the down GEMM over NVLink peer memory",
                        "l2": "inputs larger than L2"},
             "tokens_per_s": R / t, "nccl_reduce_scatter_ms_per_step": times["nccl"],
             "dispatch_bytes_per_rank": (world - 1) * rpr * (H * 2 + TOPK * 10), "combine_bytes_per_rank": (world - 1) * rpr * H * 4,
             "picks_per_rank": picks.tolist(), "load_imbalance_max_over_mean": float(picks.max() / picks.mean()),
+            "load_imbalance_contiguous_placement": base_imb,
             "roofline": {"bound": "tensor", "kernel": "whole step incl. collectives", "achieved": flop / t / 1e12, "peak": peak, "unit": "TFLOP/s",
                          "frac": flop / t / 1e12 / peak, "peak_kind": "measured (sustained) x n_gpus", "traffic": None},
             "gpu_launches": int(launches), "device_status": int(st.item()), "clocks": cs.summary()}))
