@@ -127,6 +127,14 @@ def test_full_shape(oracle, dev, group, aq):
         assert e[2] < NORM_REL_EXACT, e
 
 
+@pytest.mark.parametrize("H,I", [(6272, 256), (512, 2176)])
+def test_shapes_beyond_the_register_resident_path(oracle, dev, H, I):
+    """H > 6144 or I > 2048: a tile's activation fragments no longer fit in registers and the call takes the kernels that
+    fetch them stage by stage."""
+    (got,), ref = run_case(oracle, dev, H, I, 8, 11, 128, True, True, seed=5)
+    assert int8_close(errors(got, ref)), errors(got, ref)
+
+
 def test_accumulates_into_y_and_combine(oracle, dev):
     import torch
     from hecate_b200 import moe
