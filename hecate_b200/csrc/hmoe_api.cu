@@ -158,6 +158,14 @@ int hmoe_router(const void* x, int x_dtype, const void* wt, int w_dtype, const f
     return router_launch(x, x_dtype, wt, w_dtype, bias, R, H, E, topk, scale, sel, rw, ws, ws_bytes, (cudaStream_t) stream);
 }
 
+int hmoe_norm_router(const float* y, const float* r, float* r_out, const void* nw, int nw_dtype, void* xn, const void* wt, int w_dtype,
+                     const float* bias, int R, int H, int E, int topk, float scale, float eps, float cbias, float cscale, int64_t* sel, void* rw,
+                     void* ws, size_t ws_bytes, void* stream)
+{
+    return norm_router_launch(y, r, r_out, nw, nw_dtype, xn, wt, w_dtype, bias, R, H, E, topk, scale, eps, cbias, cscale, sel, rw, ws, ws_bytes,
+                              (cudaStream_t) stream);
+}
+
 size_t hmoe_decode_ws_bytes(int H, int I) { return decode_ws_bytes(H, I); }
 int hmoe_decode(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
                 int act_quant, float* y, void* ws, size_t ws_bytes, void* stream)

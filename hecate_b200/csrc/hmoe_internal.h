@@ -23,6 +23,10 @@ size_t router_ws_bytes(int R, int E);
 int router_launch(const void* x, int x_dtype, const void* wt, int w_dtype, const float* bias, int R, int H, int E, int topk,
                   float scale, int64_t* sel, void* rw, void* ws, size_t ws_bytes, cudaStream_t st);
 
+int norm_router_launch(const float* y, const float* r, float* r_out, const void* nw, int nw_dtype, void* xn, const void* wt, int w_dtype,
+                       const float* bias, int R, int H, int E, int topk, float scale, float eps, float cbias, float cscale, int64_t* sel, void* rw,
+                       void* ws, size_t ws_bytes, cudaStream_t st);
+
 size_t prefill_ws_bytes(int R, int topk, int n_local, int H, int I, int act_quant);
 int prefill_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
                    int act_quant, float* out, void* ws, size_t ws_bytes, cudaStream_t st, int shared_row0 = 0, int shared_rows = -1,

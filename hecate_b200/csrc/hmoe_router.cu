@@ -95,11 +95,20 @@ __device__ __noinline__ void topk_row(const float* __restrict__ logits, const fl
 // With FUSED, the block that finishes a row group last (counted in g_router_ctr) also selects the group's experts.
 constexpr int HC = 6144;
 
-template <bool XBF, bool WBF, bool FUSED>
+// NORM (the norm + router fusion, one chunk only): the rows come as the fp32 residual r (+ y); the block computes
+// r' = r + y, the sum of squares of every row in the order of the stand-alone norm kernel (1024 virtual threads, float4
+// columns t and t + 1024, butterflies), xn = fp16(r' * (w + cbias) * rsqrt(mean + eps) * cscale), and routes on xn, which is
+// what a norm kernel followed by the router would do bit for bit. Blocks bx == 0 write r' and xn.
+struct NormArgs
+{
+    const float* r; const float* y; float* r_out; const uint16_t* nw; __half* xn; float eps, cbias, cscale; int nw_bf16;
+};
+
+template <bool XBF, bool WBF, bool FUSED, bool NORM>
 __global__ void __launch_bounds__(RW * 32) router_logits_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ wt,
                                                                 int R, int H, int E, float* __restrict__ logits,
                                                                 const float* __restrict__ bias, int topk, float scale,
-                                                                int64_t* __restrict__ sel, __half* __restrict__ rw, int slot)
+                                                                int64_t* __restrict__ sel, __half* __restrict__ rw, int slot, const NormArgs na)
 {
     extern __shared__ __align__(128) unsigned char rsm[];
     __shared__ int s_last;
@@ -125,6 +134,80 @@ __global__ void __launch_bounds__(RW * 32) router_logits_kernel(const uint16_t* 
         const int cl = H - c0 < hc ? H - c0 : hc;
         if (c0 > 0) __syncthreads();                             // everyone is done with the previous chunk
         if (lane == 0) { mbar_expect_tx(bar, cl * 2); bulk_g2s(wsm, w + c0, cl * 2, bar); }
+        if (NORM)
+        {
+            __shared__ float vsums[32];
+            const int cols = H / 4, t = threadIdx.x;
+            #pragma unroll 1
+            for (int rr = 0; rr < RR; ++rr)
+            {
+                float4 v[4][2];                                   // virtual thread t + 256 k, float4 columns vt and vt + 1024
+                float ps[4];
+                #pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    #pragma unroll
+                    for (int j = 0; j < 2; ++j)
+                    {
+                        const int c = t + 256 * k + 1024 * j;
+                        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (rr < nr && c < cols)
+                        {
+                            const size_t i = (size_t) (r0 + rr) * H + 4 * (size_t) c;
+                            a = *(const float4*) (na.r + i);
+                            if (na.y) { const float4 b = *(const float4*) (na.y + i); a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w; }
+                        }
+                        v[k][j] = a;
+                    }
+                #pragma unroll
+                for (int k = 0; k < 4; ++k)
+                {
+                    float sq = 0.f;
+                    #pragma unroll
+                    for (int j = 0; j < 2; ++j)
+                        if (t + 256 * k + 1024 * j < cols)
+                        {
+                            const float4 a = v[k][j];
+                            sq = fmaf(a.x, a.x, sq); sq = fmaf(a.y, a.y, sq); sq = fmaf(a.z, a.z, sq); sq = fmaf(a.w, a.w, sq);
+                        }
+                    #pragma unroll
+                    for (int off = 16; off > 0; off >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, off);
+                    ps[k] = sq;
+                }
+                __syncthreads();                                  // vsums free (previous row read)
+                if (lane == 0) { vsums[warp] = ps[0]; vsums[warp + 8] = ps[1]; vsums[warp + 16] = ps[2]; vsums[warp + 24] = ps[3]; }
+                __syncthreads();
+                float tot = vsums[lane];
+                #pragma unroll
+                for (int off = 16; off > 0; off >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, off);
+                const float rmf = rsqrtf(tot / (float) H + na.eps) * na.cscale;
+                #pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    #pragma unroll
+                    for (int j = 0; j < 2; ++j)
+                    {
+                        const int c = t + 256 * k + 1024 * j;
+                        if (c >= cols) continue;
+                        float4 a = v[k][j], w4;
+                        const uint2 u = *(const uint2*) (na.nw + 4 * c);
+                        if (na.nw_bf16) w4 = make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u), __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u));
+                        else { const float2 p = __half22float2(*(const __half2*) &u.x), q2 = __half22float2(*(const __half2*) &u.y); w4 = make_float4(p.x, p.y, q2.x, q2.y); }
+                        if (na.cbias != 0.f) { w4.x += na.cbias; w4.y += na.cbias; w4.z += na.cbias; w4.w += na.cbias; }
+                        const __half2 h0 = __halves2half2(__float2half_rn(a.x * w4.x * rmf), __float2half_rn(a.y * w4.y * rmf));
+                        const __half2 h1 = __halves2half2(__float2half_rn(a.z * w4.z * rmf), __float2half_rn(a.w * w4.w * rmf));
+                        const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+                        const int col = 4 * c;
+                        *(float4*) (xs + rr * hc + (col & ~255) + ((col & 255) >> 3) * 4 + (c & 1) * 128) = make_float4(f0.x, f0.y, f1.x, f1.y);
+                        if (blockIdx.x == 0 && rr < nr)
+                        {
+                            const size_t i = (size_t) (r0 + rr) * H + col;
+                            uint2 o; o.x = *(const uint32_t*) &h0; o.y = *(const uint32_t*) &h1;
+                            *(uint2*) (na.xn + i) = o;
+                            if (na.r_out) *(float4*) (na.r_out + i) = a;
+                        }
+                    }
+            }
+        }
+        else
         #pragma unroll 1
         for (int i0 = threadIdx.x * 8; i0 < RR * cl; i0 += RW * 32 * 8 * 6)
         {
@@ -207,12 +290,28 @@ void launch_logits(dim3 grid, size_t smem, cudaStream_t st, bool fused, const ui
     static bool attr = false;
     if (!attr)
     {
-        cudaFuncSetAttribute(router_logits_kernel<XBF, WBF, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        cudaFuncSetAttribute(router_logits_kernel<XBF, WBF, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(router_logits_kernel<XBF, WBF, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(router_logits_kernel<XBF, WBF, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         attr = true;
     }
-    if (fused) router_logits_kernel<XBF, WBF, true><<<grid, RW * 32, smem, st>>>(x, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot);
-    else router_logits_kernel<XBF, WBF, false><<<grid, RW * 32, smem, st>>>(x, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot);
+    const NormArgs na = {};
+    if (fused) router_logits_kernel<XBF, WBF, true, false><<<grid, RW * 32, smem, st>>>(x, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot, na);
+    else router_logits_kernel<XBF, WBF, false, false><<<grid, RW * 32, smem, st>>>(x, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot, na);
+}
+
+template <bool WBF>
+void launch_norm_router(dim3 grid, size_t smem, cudaStream_t st, bool fused, const uint16_t* wt, int R, int H, int E, float* logits,
+                        const float* bias, int topk, float scale, int64_t* sel, __half* rw, int slot, const NormArgs& na)
+{
+    static bool attr = false;
+    if (!attr)
+    {
+        cudaFuncSetAttribute(router_logits_kernel<false, WBF, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(router_logits_kernel<false, WBF, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        attr = true;
+    }
+    if (fused) router_logits_kernel<false, WBF, true, true><<<grid, RW * 32, smem, st>>>(nullptr, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot, na);
+    else router_logits_kernel<false, WBF, false, true><<<grid, RW * 32, smem, st>>>(nullptr, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot, na);
 }
 
 }  // namespace
@@ -243,6 +342,34 @@ int router_launch(const void* x, int x_dtype, const void* wt, int w_dtype, const
     else if (!xb && wb) launch_logits<false, true>(grid, smem, st, fused, xp, wp, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot);
     else if (xb && !wb) launch_logits<true, false>(grid, smem, st, fused, xp, wp, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot);
     else launch_logits<true, true>(grid, smem, st, fused, xp, wp, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot);
+    if (!fused) router_topk_kernel<<<(R + 7) / 8, 256, 0, st>>>(logits, bias, R, E, topk, scale, sel, (__half*) rw);
+    count_launches(fused ? 1 : 2);
+    const cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) return fail(HMOE_E_CUDA, cudaGetErrorString(err));
+    return HMOE_OK;
+}
+
+int norm_router_launch(const float* y, const float* r, float* r_out, const void* nw, int nw_dtype, void* xn, const void* wt, int w_dtype,
+                       const float* bias, int R, int H, int E, int topk, float scale, float eps, float cbias, float cscale, int64_t* sel, void* rw,
+                       void* ws, size_t ws_bytes, cudaStream_t st)
+{
+    if (R < 1 || E < 32 || E > 256 || E % 32 || H % 256 || H < 256 || H > HC || topk < 1 || topk > TOPK_MAX || topk > E)
+        return fail(HMOE_E_ARG, "hmoe_norm_router: needs R >= 1, E % 32 == 0, E <= 256, H % 256 == 0, H <= 6144, topk <= 8");
+    if ((nw_dtype != HMOE_F16 && nw_dtype != HMOE_BF16) || (w_dtype != HMOE_F16 && w_dtype != HMOE_BF16))
+        return fail(HMOE_E_ARG, "hmoe_norm_router: the norm weight and wt must be fp16 or bf16");
+    if (!r || !nw || !xn || !wt || !sel || !rw || !ws || r_out == r || (y && r_out == y)) return fail(HMOE_E_ARG, "hmoe_norm_router: null pointer, or r_out aliases an input");
+    if (ws_bytes < router_ws_bytes(R, E)) return fail(HMOE_E_WS, "hmoe_norm_router: workspace too small");
+    const size_t smem = (size_t) RR * (H > 512 ? H : 512) * 4 + (size_t) RW * H * 2;
+    const dim3 grid((E + RW - 1) / RW, (R + RR - 1) / RR);
+    const bool fused = (int) grid.y <= CTR_GROUPS;
+    static unsigned calls = 0;
+    const int slot = (int) (calls++ % CTR_SLOTS);
+    NormArgs na;
+    na.r = r; na.y = y; na.r_out = r_out; na.nw = (const uint16_t*) nw; na.xn = (__half*) xn; na.eps = eps; na.cbias = cbias; na.cscale = cscale;
+    na.nw_bf16 = nw_dtype == HMOE_BF16;
+    float* logits = (float*) ws;
+    if (w_dtype == HMOE_BF16) launch_norm_router<true>(grid, smem, st, fused, (const uint16_t*) wt, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot, na);
+    else launch_norm_router<false>(grid, smem, st, fused, (const uint16_t*) wt, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot, na);
     if (!fused) router_topk_kernel<<<(R + 7) / 8, 256, 0, st>>>(logits, bias, R, E, topk, scale, sel, (__half*) rw);
     count_launches(fused ? 1 : 2);
     const cudaError_t err = cudaGetLastError();

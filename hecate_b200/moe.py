@@ -263,6 +263,24 @@ def router_fused(x, wt, bias, logits, ctr, sel, rw, topk, scale):
     return sel, rw
 
 
+def norm_route(y, r, w, xn, wt, bias, sel, rw, topk, scale, eps, cbias=0.0, cscale=1.0, r_out=None):
+    """Residual add + input norm + router in one launch (the reference's norm_route, runtime/core/exl3_normroute.py:16-65, without
+    its hand-off arguments): r' = r + y (y may be None) -> r_out (or dropped), xn = fp16 norm of r', (sel, rw) = router(xn)."""
+    H = r.shape[-1]
+    R = r.numel() // H
+    E = wt.shape[0]
+    need = lib().hmoe_router_ws_bytes(C.c_int(R), C.c_int(E))
+    ws = _router_ws.get((r.device, ))
+    if ws is None or ws.numel() < need:
+        ws = _router_ws[(r.device, )] = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=r.device)
+    if r.dtype != torch.float32 or xn.dtype != torch.float16 or not (r.is_contiguous() and xn.is_contiguous() and wt.is_contiguous() and w.is_contiguous()):
+        raise HmoeError("norm_route: shapes / dtypes")
+    check(lib().hmoe_norm_router(vp(y), vp(r), vp(r_out), vp(w), C.c_int(_dt(w)), vp(xn), vp(wt), C.c_int(_dt(wt)), vp(bias), C.c_int(R), C.c_int(H),
+                                 C.c_int(E), C.c_int(int(topk)), C.c_float(float(scale)), C.c_float(eps), C.c_float(cbias), C.c_float(cscale),
+                                 vp(sel), vp(rw), vp(ws), C.c_size_t(ws.numel()), _stream(r.device)))
+    return sel, rw
+
+
 def fill_bytes(t, seed, stream_id):
     """Fill a uint8 tensor (numel % 8 == 0) with the synthetic generator's bytes for (seed, stream_id)."""
     check(lib().hmoe_fill_bytes(vp(t), C.c_size_t(t.numel() * t.element_size()), C.c_uint64(seed), C.c_uint64(stream_id),

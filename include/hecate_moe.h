@@ -53,6 +53,15 @@ size_t hmoe_router_ws_bytes(int R, int E);
 int hmoe_router(const void* x, int x_dtype, const void* wt, int w_dtype, const float* bias, int R, int H, int E, int topk,
                 float scale, int64_t* sel, void* rw, void* ws, size_t ws_bytes, void* stream);
 
+/* Residual add + input norm + router in one launch: the step the reference fuses as norm_route (runtime/core/exl3_normroute.py:16-65,
+ * runtime/core/nr4_kernel.cuh:121-381). r' = r + y (y may be null), xn = fp16(r' * (nw + cbias) * rsqrt(mean(r'^2) + eps) * cscale),
+ * then hmoe_router on xn. r, y fp32 [R][H] are only read; r' goes to r_out (fp32 [R][H], may be null, must not alias r or y), xn
+ * fp16 [R][H] is the expert layer's input. The sum of squares is taken in the order of hmoe_combine_norm and the router sees the
+ * fp16-rounded xn, so the results equal those of the two separate calls bit for bit. H <= 6144; other limits as hmoe_router. */
+int hmoe_norm_router(const float* y, const float* r, float* r_out, const void* nw, int nw_dtype, void* xn, const void* wt, int w_dtype,
+                     const float* bias, int R, int H, int E, int topk, float scale, float eps, float cbias, float cscale, int64_t* sel, void* rw,
+                     void* ws, size_t ws_bytes, void* stream);
+
 /* Decode expert layer: replaces moe4.forward(x, sel, rw, n_hot, tables..., scratch..., y, blocks, blocks_a, lo, shared...)
  * (runtime/tier/moe4/moe4.cu:828-895) for R <= 16 rows in one pass over the weights. x [R][H] fp16 or bf16; sel int64
  * [R][topk]; rw fp16 [R][topk]; only ids in [lo, lo + n_local) contribute, entry e - lo of the tables; y fp32 [R][H] is

@@ -44,3 +44,30 @@ def test_fill_matches_numpy_generator():
     t = torch.empty(8192, dtype=torch.uint8, device="cuda:0")
     moe.fill_bytes(t, 5, synth.stream_id(2, "down_q", 17))
     assert np.array_equal(t.cpu().numpy(), synth.rand_bytes(5, synth.stream_id(2, "down_q", 17), 8192))
+
+
+@pytest.mark.parametrize("R,H,wbf,with_y", [(16, 6144, True, True), (5, 6144, False, False), (3, 512, True, True), (9, 1024, False, True)])
+def test_norm_route_equals_norm_then_router(R, H, wbf, with_y):
+    """Residual add + norm + router in one launch gives, bit for bit, what the norm kernel followed by the router gives."""
+    import torch
+    from hecate_b200 import moe
+    dev = torch.device("cuda:0")
+    E, topk = 256, 8
+    g = lambda s, n: torch.from_numpy(synth.normal(31, s, n).astype(np.float32)).to(dev)
+    r = g(1, R * H).view(R, H) * 2.0
+    y = g(2, R * H).view(R, H) * 0.5 if with_y else None
+    nw = (1.0 + 0.1 * g(3, H)).to(torch.bfloat16 if wbf else torch.float16)
+    wt = torch.from_numpy(synth.router_weight(4, 0, E, H)).to(dev).to(torch.bfloat16 if wbf else torch.float16)
+    bias = torch.from_numpy(synth.router_bias(4, 0, E, 0.05)).to(dev)
+    # separate: combine_norm (a = y, r += a, xn), then the router on xn
+    r1 = r.clone(); y1 = y.clone() if y is not None else torch.zeros(R, H, device=dev)
+    xn1 = torch.empty(R, H, dtype=torch.float16, device=dev)
+    moe.combine_norm(None, 0, y1, R, 0, 0, r1, nw, xn1, 1e-6, 0.0, 1.0)
+    sel1 = torch.empty(R, topk, dtype=torch.int64, device=dev); rw1 = torch.empty(R, topk, dtype=torch.float16, device=dev)
+    moe.router_fused(xn1, wt, bias, None, None, sel1, rw1, topk, 2.5)
+    # fused
+    xn2 = torch.empty(R, H, dtype=torch.float16, device=dev); r2 = torch.empty(R, H, device=dev)
+    sel2 = torch.empty(R, topk, dtype=torch.int64, device=dev); rw2 = torch.empty(R, topk, dtype=torch.float16, device=dev)
+    moe.norm_route(y, r, nw, xn2, wt, bias, sel2, rw2, topk, 2.5, 1e-6, r_out=r2)
+    assert torch.equal(r2, r1) and torch.equal(xn2, xn1)
+    assert torch.equal(sel2, sel1) and torch.equal(rw2.view(torch.int16), rw1.view(torch.int16))
