@@ -22,7 +22,8 @@ class LayerStruct(C.Structure):
     _fields_ = [("H", C.c_int32), ("I", C.c_int32), ("n_experts", C.c_int32), ("topk", C.c_int32),
                 ("group", C.c_int32), ("scale_dtype", C.c_int32)] + \
                [(n, C.c_void_p) for n in ("gate_w", "up_w", "down_w", "gate_s", "up_s", "down_s",
-                                          "sh_gate_w", "sh_up_w", "sh_down_w", "sh_gate_s", "sh_up_s", "sh_down_s")]
+                                          "sh_gate_w", "sh_up_w", "sh_down_w", "sh_gate_s", "sh_up_s", "sh_down_s")] + \
+               [("shared_format", C.c_int32)]
 
 
 def lib():

@@ -1099,15 +1099,25 @@ int decode_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t
     float* xscale = (float*) w; w += up256((size_t) MAXR * (H / 32) * 4);
     __half* act = (__half*) w; w += up256((size_t) MAXT * 8 * I * 2);
     float* ascale = (float*) w;
-    const int has_shared = L->sh_gate_w != nullptr;
+    const bool sh8 = L->shared_format == 1 && L->sh_gate_w != nullptr;       // the reference's int8 shared expert: its own kernels
+    if (sh8 && !(I <= 2048 && H <= 6144)) return fail(HMOE_E_UNSUPPORTED, "hmoe_decode: the int8 shared expert needs H <= 6144 and I <= 2048");
+    const int has_shared = L->sh_gate_w != nullptr && !sh8;
     if (g_prof) cudaEventRecord(g_ev[g_prof_calls % PROF_RING][0], st);
     decode_prepare_kernel<<<R + 1, 256, 0, st>>>(x, x_dtype == HMOE_BF16, sel, (const __half*) rw, R, H, L->topk, lo, n_local, has_shared,
                                                  act_quant, xf, xscale, route, sh_mod, sh_rem, gen_ptr,
                                                  (float4*) act, (I <= 2048 && H <= 6144) ? (L->topk + 1) * 2 * I / 4 : 0, I, g_sms < MAXB ? g_sms : MAXB);
+    if (sh8)
+    {
+        // its gate / up sums go to the rows of the per-pick buffer behind the routed picks (cleared by the prepare kernel with the rest)
+        const int rc = shared_i8_launch(L, R, sh_mod, sh_rem, xf, (float*) act + (size_t) R * L->topk * 2 * I, y, gen_ptr, slot_stride,
+                                        g_sms < MAXB ? g_sms : MAXB, st);
+        if (rc) return rc;
+    }
     DecodeArgs a;
     a.H = H; a.I = I;
     a.gate_w = L->gate_w; a.up_w = L->up_w; a.down_w = L->down_w; a.gate_s = L->gate_s; a.up_s = L->up_s; a.down_s = L->down_s;
-    a.sh_gw = L->sh_gate_w; a.sh_uw = L->sh_up_w; a.sh_dw = L->sh_down_w; a.sh_gs = L->sh_gate_s; a.sh_us = L->sh_up_s; a.sh_ds = L->sh_down_s;
+    a.sh_gw = sh8 ? nullptr : L->sh_gate_w; a.sh_uw = sh8 ? nullptr : L->sh_up_w; a.sh_dw = sh8 ? nullptr : L->sh_down_w;
+    a.sh_gs = sh8 ? nullptr : L->sh_gate_s; a.sh_us = sh8 ? nullptr : L->sh_up_s; a.sh_ds = sh8 ? nullptr : L->sh_down_s;
     a.route = route; a.xf = xf; a.xscale = xscale; a.act = act; a.ascale = ascale; a.G = (float*) act; a.dbg = (unsigned long long*) ((char*) ws + decode_ws_bytes(H, I) - 16384); a.y = y; a.status = status;
     a.gen_ptr = gen_ptr; a.slot_stride = slot_stride;
     const int grid = g_sms < MAXB ? g_sms : MAXB;

@@ -1,5 +1,6 @@
 // Internal host-side declarations shared by the translation units of libhecate_moe_b200.so.
 #pragma once
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stddef.h>
 #include <stdint.h>
@@ -15,6 +16,9 @@ size_t decode_ws_bytes(int H, int I);
 int decode_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
                   int act_quant, float* y, void* ws, size_t ws_bytes, cudaStream_t st, int sh_mod = 1, int sh_rem = 0,
                   unsigned* gen_ptr = nullptr, size_t slot_stride = 0);
+
+int shared_i8_launch(const hmoe_layer* L, int R, int sh_mod, int sh_rem, const __half* xf, float* gs, float* y, const unsigned* gen_ptr,
+                     size_t slot_stride, int sms, cudaStream_t st);
 
 int decode_set_profiling(int on);
 int decode_phase_times(float* ms3);

@@ -708,6 +708,7 @@ int prefill_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_
     if (!(L->group == 0 && L->scale_dtype == HMOE_F32) && !(L->group == 128 && L->scale_dtype == HMOE_BF16))
         return fail(HMOE_E_ARG, "hmoe_prefill: scales must be fp32 per row (group 0) or bf16 per 128 columns");
     if (x_dtype != HMOE_F16 && x_dtype != HMOE_BF16) return fail(HMOE_E_ARG, "hmoe_prefill: x must be fp16 or bf16");
+    if (L->shared_format != 0 && L->sh_gate_w) return fail(HMOE_E_UNSUPPORTED, "hmoe_prefill: the int8 shared expert is served by the decode path only");
     if (!x || !sel || !rw || (!out && !out_peer) || !ws) return fail(HMOE_E_ARG, "hmoe_prefill: null pointer");
     const int kf = act_quant ? 2 : 1;
     const WsLayout w = ws_layout(R, L->topk, n_local, H, I, TN, kf);

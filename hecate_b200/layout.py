@@ -68,3 +68,22 @@ def group_scales_logical(d, N):
     """inverse of group_scales_device_order: [N/64][K/G][64] -> [K/G][N]."""
     d = np.asarray(d).reshape(N // 64, -1, 8, 8)     # gr, kg, g, j
     return np.ascontiguousarray(d.transpose(1, 0, 3, 2)).reshape(-1, N)
+
+
+def pack_i8(codes):
+    """codes uint8 [N][K] (value = code - 128) -> the reference's dense int8 fragment order, N % 64 == 0, K % 32 == 0
+    (runtime/core/hecate_runtime.py:43-48 with four strips per group): byte
+    ((((((((gr * K/32 + kb) * 4 + s) * 8 + g) * 4 + q) * 2 + t) * 2 + h) * 2 + c) * 2 + rh holds row gr*64 + s*16 + rh*8 + g,
+    column kb*32 + t*16 + h*8 + q*2 + c."""
+    codes = np.asarray(codes, dtype=np.uint8)
+    N, K = codes.shape
+    assert N % 64 == 0 and K % 32 == 0
+    v = codes.reshape(N // 64, 4, 2, 8, K // 32, 2, 2, 4, 2)               # gr, s, rh, g, kb, t, h, q, c
+    return np.ascontiguousarray(v.transpose(0, 4, 1, 3, 7, 5, 6, 8, 2)).reshape(-1)
+
+
+def unpack_i8(q, N, K):
+    """inverse of pack_i8 -> codes uint8 [N][K]."""
+    v = np.asarray(q, dtype=np.uint8).reshape(N // 64, K // 32, 4, 8, 4, 2, 2, 2, 2)   # gr, kb, s, g, q, t, h, c, rh
+    return np.ascontiguousarray(v.transpose(0, 2, 8, 3, 1, 5, 6, 4, 7)).reshape(N, K)
+

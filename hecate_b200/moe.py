@@ -39,7 +39,7 @@ class ExpertTables:
     """The six device pointer tables of one layer's local experts (as tier_split.py:210-214,246 builds them) plus the
     optional shared expert. Keeps the weight tensors alive."""
 
-    def __init__(self, H, I, topk, gate, up, down, gate_s, up_s, down_s, group=0, shared=None, device=None):
+    def __init__(self, H, I, topk, gate, up, down, gate_s, up_s, down_s, group=0, shared=None, device=None, shared_i8=False):
         dev = device or gate[0].device
         self.H, self.I, self.topk, self.group, self.n = H, I, topk, group, len(gate)
         self.scale_dtype = F32 if group == 0 else BF16
@@ -52,12 +52,14 @@ class ExpertTables:
         self.tabs = {k: tab(v) for k, v in zip(("gate_w", "up_w", "down_w", "gate_s", "up_s", "down_s"),
                                                (gate, up, down, gate_s, up_s, down_s))}
         self.shared = shared   # (gq, uq, dq, gs, us, ds) tensors or None
+        self.shared_i8 = bool(shared_i8)   # shared expert in the reference's int8 format (layout.pack_i8, fp32 row scales)
 
     def struct(self):
         s = LayerStruct()
         s.H, s.I, s.n_experts, s.topk, s.group, s.scale_dtype = self.H, self.I, self.n, self.topk, self.group, self.scale_dtype
         for k, t in self.tabs.items():
             setattr(s, k, t.data_ptr())
+        s.shared_format = 1 if (self.shared is not None and self.shared_i8) else 0
         if self.shared is not None:
             for k, t in zip(("sh_gate_w", "sh_up_w", "sh_down_w", "sh_gate_s", "sh_up_s", "sh_down_s"), self.shared):
                 setattr(s, k, t.data_ptr())

@@ -10,6 +10,7 @@ Writes
                      from its source text
   layout.npz         bytes written by the reference's pack_u4 (tools/quant/gptq_int4.py:74-77) and codes recovered by its
                      _unpack_moe4 / _rowmajor_i4 (runtime/tier/tier_split.py:98-106), executed from their source text
+  layout_i8.npz      bytes written by the reference's int8 packer (runtime/core/hecate_runtime.py:43-48), `--only i8`
   quant.npz          scales chosen by the reference's per-row recipe scales_mse (tools/quant/gptq_int4.py:62-71, with its
                      candidate list U4F, :38), executed from its source text on a seeded matrix (`--only quant` writes just this)
 No reference source is copied: the functions are compiled from the files where they lie at generation time only.
@@ -95,10 +96,27 @@ def write_quant():
     print("quant.npz written")
 
 
+def write_layout_i8():
+    """layout_i8.npz: bytes written by the reference's int8 packer _pack and codes recovered by its _codes
+    (runtime/core/hecate_runtime.py:38-48), executed from their source text."""
+    import torch
+    path = os.path.join(REF, "runtime/core/hecate_runtime.py")
+    glb = {"torch": torch}
+    pack = _function_from(path, "_pack", glb)
+    codes_of = _function_from(path, "_codes", glb)
+    N, K = 128, 96
+    codes = synth.rand_bytes(6, 424242, N * K).reshape(N, K).astype(np.uint8)
+    q, spw = pack(torch.from_numpy(codes))
+    assert spw == 4 and np.array_equal(codes_of(q, N, K, spw).numpy(), codes)
+    np.savez_compressed(os.path.join(HERE, "layout_i8.npz"), codes=codes, packed=q.numpy())
+    print("layout_i8.npz written")
+
+
 def main():
     import torch
-    if "--only" in sys.argv and sys.argv[sys.argv.index("--only") + 1] == "quant":
-        return write_quant()
+    if "--only" in sys.argv:
+        what = sys.argv[sys.argv.index("--only") + 1]
+        return write_quant() if what == "quant" else write_layout_i8()
     build.build_oracle(); assert build.build_ref(), "needs the reference tree"
     # 1. engine jobs
     ex = job_experts()
@@ -138,6 +156,7 @@ def main():
     rm = rowmajor(torch.from_numpy(q), N, K).numpy()
     np.savez_compressed(os.path.join(HERE, "layout.npz"), codes=codes, packed=q, rowmajor=rm)
     write_quant()
+    write_layout_i8()
     print("golden fixtures written")
 
 

@@ -34,4 +34,5 @@ def test_host_only_entry_points():
 
 def test_layer_struct_matches_header():
     from hecate_b200 import _lib
-    assert ctypes.sizeof(_lib.LayerStruct) == 6 * 4 + 12 * 8
+    assert ctypes.sizeof(_lib.LayerStruct) == 6 * 4 + 12 * 8 + 8          # six ints, twelve pointers, shared_format + padding
+    assert _lib.LayerStruct.shared_format.offset == 6 * 4 + 12 * 8

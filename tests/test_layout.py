@@ -69,3 +69,11 @@ def test_frag_order_row():
         pos = qq * 8 + t * 2 + h
         assert w[2 * pos] == 2 * p and w[2 * pos + 1] == 2 * p + 1
     assert sorted(w[64:]) == list(range(64, 128))
+
+
+def test_int8_layout_matches_the_reference_packer():
+    """layout_i8.npz holds what the reference's own _pack wrote for seeded codes (tests/golden/make_golden.py)."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "layout_i8.npz"))
+    assert np.array_equal(layout.pack_i8(g["codes"]), g["packed"])
+    assert np.array_equal(layout.unpack_i8(g["packed"], *g["codes"].shape), g["codes"])

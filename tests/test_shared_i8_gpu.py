@@ -1,0 +1,64 @@
+"""The shared expert in the reference's int8 format (dense GEMV fragment order, one fp32 scale per row) beside int4 routed
+experts: the decode result equals the routed experts' result plus an exact evaluation of the int8 expert."""
+import numpy as np
+import pytest
+
+from helpers import HostLayer, errors, random_routing
+from hecate_b200 import layout, synth
+
+pytestmark = pytest.mark.gpu
+NORM_REL_EXACT = 2e-3      # the reference GPU kernels' own gate against an exact evaluation (tools/quant/test_moe4_rtx.py:70)
+
+
+def _int8_expert(seed, H, I):
+    mk = lambda s, N, K: (synth.rand_bytes(seed, s, N * K).reshape(N, K).astype(np.uint8), (np.exp(synth.normal(seed, s + 50, N) * 0.5 - 7.5)).astype(np.float32))
+    return mk(1, I, H), mk(2, I, H), mk(3, H, I)
+
+
+def _shared_exact(x, ex):
+    (gc, gs), (uc, us), (dc, ds) = ex
+    w = lambda c, s: (c.astype(np.float64) - 128.0) * s[:, None].astype(np.float64)
+    xd = x.astype(np.float64)
+    g, u = xd @ w(gc, gs).T, xd @ w(uc, us).T
+    return (g / (1.0 + np.exp(-g)) * u) @ w(dc, ds).T
+
+
+@pytest.mark.parametrize("H,I,R,group", [(256, 128, 5, 128), (512, 256, 16, 0), (6144, 2048, 16, 128), (6144, 2048, 3, 128)])
+def test_int8_shared_expert(oracle, H, I, R, group):
+    import torch
+    from hecate_b200 import moe
+    dev = torch.device("cuda:0")
+    E = 8
+    hl = HostLayer(9, 0, H, I, range(E), group, False)
+    base = hl.upload(dev)
+    ex8 = _int8_expert(13, H, I)
+    up = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    shared = tuple(up(layout.pack_i8(c)) for c, _ in ex8) + tuple(up(s) for _, s in ex8)
+    tabs = moe.ExpertTables(H, I, 8, *[base.keep[i] for i in range(6)], group=group, shared=shared, device=dev, shared_i8=True)
+    x = synth.activations(3, 0, R, H).astype(np.float16); sel, rw = random_routing(4, R, E)
+    ex, _ = hl.oracle_experts(oracle)
+    ref = oracle.moe_forward(H, I, group, x, sel, rw, 0, ex, None, mode=1).astype(np.float64) + _shared_exact(x, ex8)
+    ws = moe.decode_workspace(H, I, dev)
+    for call in range(2):                     # twice on one workspace: the per-pick buffer is cleared by every call
+        y = torch.zeros(R, H, device=dev)
+        moe.decode(tabs, up(x), up(sel), up(rw), y, ws)
+        assert moe.ws_status(ws) == 0
+        assert errors(y.cpu().numpy(), ref)[2] < NORM_REL_EXACT, (call, errors(y.cpu().numpy(), ref))
+
+
+def test_int8_shared_expert_is_decode_only(oracle):
+    import torch
+    from hecate_b200 import moe
+    from hecate_b200._lib import HmoeError
+    dev = torch.device("cuda:0")
+    H, I, E, R = 256, 128, 8, 40
+    hl = HostLayer(9, 0, H, I, range(E), 128, False)
+    base = hl.upload(dev)
+    ex8 = _int8_expert(13, H, I)
+    up = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    shared = tuple(up(layout.pack_i8(c)) for c, _ in ex8) + tuple(up(s) for _, s in ex8)
+    tabs = moe.ExpertTables(H, I, 8, *[base.keep[i] for i in range(6)], group=128, shared=shared, device=dev, shared_i8=True)
+    x = synth.activations(3, 0, R, H).astype(np.float16); sel, rw = random_routing(4, R, E)
+    ws = moe.prefill_workspace(R, 8, E, H, I, dev)
+    with pytest.raises(HmoeError):
+        moe.prefill(tabs, up(x), up(sel), up(rw), torch.zeros(R, H, device=dev), ws)
