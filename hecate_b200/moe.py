@@ -188,11 +188,13 @@ def moe4_scratch(device, H=6144, I=2048):
 
 
 def moe4_forward(x, sel, rw, n_hot, gate_w, up_w, down_w, gate_s, up_s, down_s, act, gu32, ctr_a, y32, ctr_b, y, blocks,
-                 blocks_a, lo, sh_gw=0, sh_uw=0, sh_dw=0, sh_gs=0, sh_us=0, sh_ds=0, xf=0, *, I=2048, group=0, act_quant=False):
+                 blocks_a, lo, sh_gw=0, sh_uw=0, sh_dw=0, sh_gs=0, sh_us=0, sh_ds=0, xf=0, *, I=2048, group=0, act_quant=False,
+                 shared_i8=False):
     """moe4.forward with the reference's argument order (moe4.cu:828-833,916-920). gate_w .. down_s are int64 device
     tables of pointers; `act` is the workspace from moe4_scratch; gu32, ctr_a, y32, ctr_b, blocks, blocks_a are accepted and
     ignored (this implementation needs no counters and sizes its own grid). Up to 16 rows. The shared expert pointers
-    are int4 in the routed experts' format. xf (pre-ordered input) is not supported."""
+    are int4 in the routed experts' format, or with shared_i8 the reference's int8 copies (tier_split.py:495-514). xf
+    (pre-ordered input) is not supported."""
     if xf:
         raise HmoeError("moe4_forward: fragment-order input (xf) is not supported")
     R, H = x.shape
@@ -203,6 +205,7 @@ def moe4_forward(x, sel, rw, n_hot, gate_w, up_w, down_w, gate_s, up_s, down_s, 
         setattr(s, k, t.data_ptr())
     for k, p in zip(("sh_gate_w", "sh_up_w", "sh_down_w", "sh_gate_s", "sh_up_s", "sh_down_s"), (sh_gw, sh_uw, sh_dw, sh_gs, sh_us, sh_ds)):
         setattr(s, k, int(p) or None)
+    s.shared_format = 1 if (shared_i8 and sh_gw) else 0
     if sel.dtype != torch.int64 or not sel.is_contiguous():
         raise HmoeError("moe4: selection must be contiguous int64")
     check(lib().hmoe_decode(C.byref(s), vp(x), C.c_int(_dt(x)), vp(sel), vp(rw), C.c_int(R), C.c_int(int(lo)), C.c_int(int(n_hot)),
