@@ -7,9 +7,10 @@
 //
 // The reference runs this expert inside moe4 as one more slot (runtime/tier/tier_split.py:495-514,553-568;
 // runtime/tier/moe4/moe4.cu:435-440,490-505). Here it is a pair of small kernels beside the routed experts' streaming
-// kernels, because it is 2 % of a step's bytes: every warp takes a contiguous range of units straight from global memory
-// (all of a unit's loads issued before the first is used, the next unit's loads in flight during the MMAs), multiplies them
-// with all rows of the step (two 8-column MMA tiles), and adds its partial sums with fp32 reductions:
+// kernels, because it is 2 % of a step's bytes: every block takes a contiguous range of units straight from global memory,
+// its warps in turn (all of a unit's loads issued before the first is used, the next unit's loads in flight during the MMAs),
+// multiplies them with all rows of the step (two 8-column MMA tiles), sums the warps' partial tiles through shared memory
+// and adds the result with fp32 reductions:
 //   gate_up -> Gs[row][gate | up][I]   (rows R*topk .. of the per-pick buffer the prepare kernel zeroes)
 //   down    -> y[row][H], the operand SiLU(gate) * up computed from Gs on the fly (weight 1)
 // Per-row scales are applied to the partial sums as they leave. Rows outside the step (>= R) and, under expert parallelism,
@@ -20,7 +21,7 @@
 namespace hmoe {
 namespace {
 
-constexpr int SW = 16, STHREADS = SW * 32;
+constexpr int SW = 16, STHREADS = SW * 32, PART = 16 * 65;
 
 // 4 bytes (c0 rh0, c0 rh1, c1 rh0, c1 rh1) -> fp16x2 (row g: c0, c1) and (row g + 8: c0, c1), value code - 128, exactly
 __device__ __forceinline__ void dec_i8(uint32_t w, uint32_t& lo, uint32_t& hi)
@@ -31,6 +32,9 @@ __device__ __forceinline__ void dec_i8(uint32_t w, uint32_t& lo, uint32_t& hi)
     asm("sub.f16x2 %0, %1, %2;" : "=r"(lo) : "r"(h0), "r"(0x64806480u));
     asm("sub.f16x2 %0, %1, %2;" : "=r"(hi) : "r"(h1), "r"(0x64806480u));
 }
+// programmatic dependent launch: let the next kernel's blocks start as this one's retire / wait for the kernel before
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void red_add_f32(float* p, float v)
 {
     asm volatile("red.global.add.f32 [%0], %1;" ::"l"(__cvta_generic_to_global(p)), "f"(v) : "memory");
@@ -67,27 +71,23 @@ __device__ __forceinline__ void unit_mma(const uint4 (&w)[4], const uint32_t (&b
 }
 
 // DOWN = false: units of gate then up, (matrix, 64-row group, 32-column block) with the block fastest. DOWN = true: units of down.
+// A block takes a contiguous range of units and deals them to its warps in turn, so all warps are in the same 64-row group at
+// the same time; where the range leaves a row group (and at its end) the warps' partial tiles are summed through shared memory
+// and one set of reductions leaves the block.
 template <bool DOWN>
-__global__ void __launch_bounds__(STHREADS) shared_i8_kernel(const SharedArgs a)
+__global__ void __launch_bounds__(STHREADS, 1) shared_i8_kernel(const SharedArgs a)
 {
+    extern __shared__ float part[];                       // [SW][16 tile columns][64 rows + 1]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
+    pdl_launch_dependents();
     const int K = DOWN ? a.I : a.H, N = DOWN ? a.H : a.I, KB = K / 32, NG = N / 64;
     const long long total = (long long) (DOWN ? 1 : 2) * NG * KB;
-    const long long nw = (long long) gridDim.x * SW, wid = (long long) blockIdx.x * SW + warp;
-    long long u = total * wid / nw;
-    const long long u1 = total * (wid + 1) / nw;
-    if (u >= u1) return;
-    float* const yout = DOWN ? a.y + (a.gen_ptr ? (size_t) (*a.gen_ptr & 1u) * a.slot_stride : 0) : nullptr;
-    // rows of the two tiles this lane feeds (operand) and receives (results: tile columns 2q, 2q + 1)
-    bool live_b[2], live_c[2][2];
+    const long long U0 = total * blockIdx.x / gridDim.x, U1 = total * (blockIdx.x + 1) / gridDim.x;
+    float* const yout = DOWN ? a.y + (a.gen_ptr ? (size_t) (*a.gen_ptr & 1u) * a.slot_stride : 0) : nullptr;     // gen: written two kernels back
+    // rows of the two tiles this lane feeds (operand)
+    bool live_b[2];
     #pragma unroll
-    for (int j = 0; j < 2; ++j)
-    {
-        const int rb = 8 * j + g;
-        live_b[j] = rb < a.R && rb % a.sh_mod == a.sh_rem;
-        #pragma unroll
-        for (int c = 0; c < 2; ++c) { const int rc = 8 * j + 2 * q + c; live_c[j][c] = rc < a.R && rc % a.sh_mod == a.sh_rem; }
-    }
+    for (int j = 0; j < 2; ++j) { const int rb = 8 * j + g; live_b[j] = rb < a.R && rb % a.sh_mod == a.sh_rem; }
     auto load_w = [&](long long uu, uint4 (&w)[4]) {
         const int kb = (int) (uu % KB), row = (int) (uu / KB);            // row = matrix * NG + 64-row group
         const uint4* base = DOWN ? a.down_w : (row >= NG ? a.up_w : a.gate_w);
@@ -127,48 +127,65 @@ __global__ void __launch_bounds__(STHREADS) shared_i8_kernel(const SharedArgs a)
     for (int s = 0; s < 4; ++s)
         #pragma unroll
         for (int j = 0; j < 2; ++j) acc[s][j][0] = acc[s][j][1] = acc[s][j][2] = acc[s][j][3] = 0.f;
-    auto flush = [&](int row) {                                       // row = matrix * NG + 64-row group of the finished sums
-        const int mat = row >= NG ? 1 : 0, gr = row % NG;
-        const float* sc = (DOWN ? a.down_s : (mat ? a.up_s : a.gate_s)) + gr * 64 + g;
+    // the block's range, one 64-row group (segment) at a time
+    bool waited = false;
+    for (long long seg0 = U0; seg0 < U1;)
+    {
+        const int row = (int) (seg0 / KB);
+        const long long seg1 = (long long) (row + 1) * KB < U1 ? (long long) (row + 1) * KB : U1;
+        long long u = seg0 + warp;
+        uint4 w[4], wn[4];
+        uint32_t b[2][4], bn[2][4];
+        if (u < seg1) load_w(u, w);              // weights do not depend on the kernel before: requested while it drains
+        if (!waited) { pdl_wait(); waited = true; }
+        if (u < seg1) load_b(u, b);
+        for (; u < seg1; u += SW)
+        {
+            const bool more = u + SW < seg1;
+            if (more) { load_w(u + SW, wn); load_b(u + SW, bn); }
+            unit_mma(w, b, acc);
+            if (more)
+            {
+                #pragma unroll
+                for (int s = 0; s < 4; ++s) w[s] = wn[s];
+                #pragma unroll
+                for (int j = 0; j < 2; ++j)
+                    #pragma unroll
+                    for (int i = 0; i < 4; ++i) b[j][i] = bn[j][i];
+            }
+        }
+        // partial tile of this warp -> shared memory [tile column][row of the group, padded to 65], then one sum per output element
+        float* mine = part + warp * PART;
         #pragma unroll
         for (int s = 0; s < 4; ++s)
-        {
-            const float s0 = __ldg(sc + s * 16), s1 = __ldg(sc + s * 16 + 8);
             #pragma unroll
             for (int j = 0; j < 2; ++j)
+            {
                 #pragma unroll
                 for (int c = 0; c < 2; ++c)
                 {
-                    if (live_c[j][c])
-                    {
-                        const int r = 8 * j + 2 * q + c;
-                        float* dst = DOWN ? yout + (size_t) r * a.H + gr * 64 + s * 16 + g
-                                          : a.gs + (size_t) r * 2 * a.I + (size_t) mat * a.I + gr * 64 + s * 16 + g;
-                        red_add_f32(dst, acc[s][j][c] * s0);
-                        red_add_f32(dst + 8, acc[s][j][2 + c] * s1);
-                    }
-                    acc[s][j][c] = 0.f; acc[s][j][2 + c] = 0.f;
+                    mine[(8 * j + 2 * q + c) * 65 + s * 16 + g] = acc[s][j][c];
+                    mine[(8 * j + 2 * q + c) * 65 + s * 16 + g + 8] = acc[s][j][2 + c];
                 }
-        }
-    };
-    uint4 w[4], wn[4];
-    uint32_t b[2][4], bn[2][4];
-    load_w(u, w); load_b(u, b);
-    for (; u < u1; ++u)
-    {
-        const bool more = u + 1 < u1;
-        if (more) { load_w(u + 1, wn); load_b(u + 1, bn); }
-        unit_mma(w, b, acc);
-        if (!more || (u + 1) % KB == 0) flush((int) (u / KB));
-        if (more)
+                acc[s][j][0] = acc[s][j][1] = acc[s][j][2] = acc[s][j][3] = 0.f;
+            }
+        __syncthreads();
+        const int mat = row >= NG ? 1 : 0, gr = row % NG;
+        const float* sc = (DOWN ? a.down_s : (mat ? a.up_s : a.gate_s)) + gr * 64;
+        for (int i = threadIdx.x; i < 1024; i += STHREADS)
         {
-            #pragma unroll
-            for (int s = 0; s < 4; ++s) w[s] = wn[s];
-            #pragma unroll
-            for (int j = 0; j < 2; ++j)
+            const int r = i >> 6, n = i & 63;                        // tile column (row of the step), row of the group: consecutive n per warp
+            if (r < a.R && r % a.sh_mod == a.sh_rem)
+            {
+                float v = 0.f;
                 #pragma unroll
-                for (int i = 0; i < 4; ++i) b[j][i] = bn[j][i];
+                for (int ww = 0; ww < SW; ++ww) v += part[ww * PART + r * 65 + n];
+                float* dst = DOWN ? yout + (size_t) r * a.H + gr * 64 + n : a.gs + (size_t) r * 2 * a.I + (size_t) mat * a.I + gr * 64 + n;
+                red_add_f32(dst, v * __ldg(sc + n));
+            }
         }
+        __syncthreads();
+        seg0 = seg1;
     }
 }
 
@@ -184,8 +201,23 @@ int shared_i8_launch(const hmoe_layer* L, int R, int sh_mod, int sh_rem, const _
     a.gate_w = (const uint4*) L->sh_gate_w; a.up_w = (const uint4*) L->sh_up_w; a.down_w = (const uint4*) L->sh_down_w;
     a.gate_s = (const float*) L->sh_gate_s; a.up_s = (const float*) L->sh_up_s; a.down_s = (const float*) L->sh_down_s;
     a.xf = xf; a.gs = gs; a.y = y; a.gen_ptr = gen_ptr; a.slot_stride = slot_stride;
-    shared_i8_kernel<false><<<sms, STHREADS, 0, st>>>(a);
-    shared_i8_kernel<true><<<sms, STHREADS, 0, st>>>(a);
+    // one block of sixteen warps per SM; both launches are programmatic dependents of the kernel before them
+    static bool attr = false;
+    const size_t smem = (size_t) SW * PART * 4;
+    if (!attr)
+    {
+        cudaFuncSetAttribute(shared_i8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+        cudaFuncSetAttribute(shared_i8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+        attr = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(sms); cfg.blockDim = dim3(STHREADS); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, shared_i8_kernel<false>, a);
+    cudaLaunchKernelEx(&cfg, shared_i8_kernel<true>, a);
     count_launches(2);
     return HMOE_OK;
 }
