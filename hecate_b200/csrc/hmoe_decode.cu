@@ -261,7 +261,6 @@ struct DecodeArgs
     const float* xscale;   // [R][H/32] (Q8)
     __half* act;           // [tiles][8][I] gate_up output = down input
     float* ascale;         // [tiles][8][I/32] (Q8)
-    unsigned long long* dbg;
     float* G;              // I <= 2048 path: [pick rows][gate | up][I] fp32 sums (shares memory with act)
     float* y;              // [R][H] (expert-parallel: base of two slots, the step's slot is chosen by *gen_ptr & 1)
     const unsigned* gen_ptr; size_t slot_stride;
@@ -274,9 +273,6 @@ template <bool GROUPED, bool Q8>
 __device__ __forceinline__ void consume_group(uint32_t wsm, const uint32_t (&bx)[2][8], const uint4 sc, const float4 sx0, const float4 sx1,
                                               float (*acc)[4], int lane)
 {
-#if defined(HMOE_EXP) && HMOE_EXP == 1
-    { const uint4 v = lds128(wsm + lane * 16); acc[0][0] += __uint_as_float(v.x) * __uint_as_float(bx[0][0] ^ sc.x); return; }
-#endif
     const uint32_t scw[4] = {sc.x, sc.y, sc.z, sc.w};
     const float sxa[4] = {sx0.x, sx0.y, sx0.z, sx0.w}, sxb[4] = {sx1.x, sx1.y, sx1.z, sx1.w};
     // The four strips' sums are independent MMA chains; the steps are interleaved across strips so that consecutive MMAs
@@ -299,11 +295,7 @@ __device__ __forceinline__ void consume_group(uint32_t wsm, const uint32_t (&bx)
                 const uint32_t w = t == 0 ? w4[s].x : t == 1 ? w4[s].y : t == 2 ? w4[s].z : w4[s].w;
                 uint32_t a[4];
                 frag_from_codes(w, a);
-#if defined(HMOE_EXP) && HMOE_EXP == 2
-                part[s][0] += __uint_as_float(a[0] ^ a[1] ^ a[2] ^ a[3] ^ bx[blk][2 * t] ^ bx[blk][2 * t + 1]);
-#else
                 mma_f16((GROUPED || Q8) ? part[s] : acc[s], a, bx[blk][2 * t], bx[blk][2 * t + 1]);
-#endif
             }
             if (Q8 && (t & 1))
             {
@@ -459,11 +451,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_gate_up_kernel(const Decod
             float gg = g0[n * 8 + col], uu = g0[512 + n * 8 + col];
             g0[n * 8 + col] = 0.f; g0[512 + n * 8 + col] = 0.f;
             float v = 0.f;
-#if defined(HMOE_EXP) && HMOE_EXP == 3
-            if (false)
-#else
             if (col < pi.nrows)
-#endif
             {
                 if (!GROUPED)
                 {
@@ -738,9 +726,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_stream_kernel(const Decode
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
     const uint32_t ring = sbase + warp * SLOT, full0 = sbase + StreamSmem::bars + warp * 8;      // slot st: + st * CW * SLOT / + st * CW * 8
     volatile int* abort_flag = (volatile int*) (smem + StreamSmem::flags);
-#if defined(HMOE_EXP) && HMOE_EXP == 8
-    if (threadIdx.x == 0) a.dbg[(DOWN * 148 + blockIdx.x) * 4 + 0] = globaltimer_ns();
-#endif
     pdl_launch_dependents();
     if (threadIdx.x == 0)
     {
@@ -901,9 +886,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_stream_kernel(const Decode
         uint32_t st = 0, par = 0;
         int tile = p0 / J, j = p0 % J;
         if (DOWN) pdl_wait();
-#if defined(HMOE_EXP) && HMOE_EXP == 8
-        if (threadIdx.x == 0) a.dbg[(DOWN * 148 + blockIdx.x) * 4 + 1] = globaltimer_ns();
-#endif
         enter_tile(tile);
         if (!GROUPED) load_row_scales(j, sd);
         bool alive = true;
@@ -934,11 +916,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_stream_kernel(const Decode
             #pragma unroll
             for (int c = 0; c < 2; ++c)
             {
-#if defined(HMOE_EXP) && HMOE_EXP == 6
-                if (acc[0][c] == 123.456f)
-#else
                 if (2 * q + c < nrows)
-#endif
                 {
                     float* yr = (c ? outB : outA) + j * 64;
                     #pragma unroll
@@ -966,9 +944,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_stream_kernel(const Decode
         }
     }
     __syncthreads();
-#if defined(HMOE_EXP) && HMOE_EXP == 8
-    if (threadIdx.x == 0) a.dbg[(DOWN * 148 + blockIdx.x) * 4 + 2] = globaltimer_ns();
-#endif
 }
 
 }  // namespace
@@ -1118,7 +1093,7 @@ int decode_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t
     a.gate_w = L->gate_w; a.up_w = L->up_w; a.down_w = L->down_w; a.gate_s = L->gate_s; a.up_s = L->up_s; a.down_s = L->down_s;
     a.sh_gw = sh8 ? nullptr : L->sh_gate_w; a.sh_uw = sh8 ? nullptr : L->sh_up_w; a.sh_dw = sh8 ? nullptr : L->sh_down_w;
     a.sh_gs = sh8 ? nullptr : L->sh_gate_s; a.sh_us = sh8 ? nullptr : L->sh_up_s; a.sh_ds = sh8 ? nullptr : L->sh_down_s;
-    a.route = route; a.xf = xf; a.xscale = xscale; a.act = act; a.ascale = ascale; a.G = (float*) act; a.dbg = (unsigned long long*) ((char*) ws + decode_ws_bytes(H, I) - 16384); a.y = y; a.status = status;
+    a.route = route; a.xf = xf; a.xscale = xscale; a.act = act; a.ascale = ascale; a.G = (float*) act; a.y = y; a.status = status;
     a.gen_ptr = gen_ptr; a.slot_stride = slot_stride;
     const int grid = g_sms < MAXB ? g_sms : MAXB;
     const int v = (L->group ? 2 : 0) + (act_quant ? 1 : 0);
