@@ -5,21 +5,20 @@
 // fragment order, routing as (sel, rw), fp32 output accumulated into y. Differences by design: 16 rows in one pass over
 // the weights, a scale per 128 input columns (or the reference's scale per row), an int4 shared expert as one more expert.
 //
-// Three launches per call:
+// Launches per call:
 //   prepare : one block per row rewrites x as fp16 in the column order the MMAs read (in the int8 mode: the CPU engine's
-//             int8 codes as fp16 integers plus a scale per 32 columns), one more block builds the Route: the distinct
-//             experts, each with the <= 8 rows that picked it as one tile.
-//   gate_up : persistent blocks, one per SM, 16 warps. A work item is (tile, 64-row group of the expert's gate and up
-//             matrices); items are dealt out as contiguous ranges. Lane 0 of warp 0 keeps a four-stage shared-memory ring
-//             full with 1-D bulk copies of the packed codes (16 KB gate + 16 KB up per stage, mbarrier completion). Warp w
-//             owns 64-column block 8 s + w % 8 of stage s of matrix w / 8: it turns the codes into fp16 MMA fragments in
-//             registers and runs m16n8k16 MMAs against the tile's rows, whose fragments and scales it prefetches into
-//             registers one stage ahead. At the end of an item the block reduces the sixteen partial tiles through shared
-//             memory, applies SiLU(g) * u * routing weight and writes the result as the next kernel's MMA operand.
-//   down    : same streaming structure over (64-row group of the output, tile) items, tile fastest, so that a block adds
-//             every tile's contribution to a 64-column slice of y in shared memory and issues one fp32 reduction to global
-//             memory per slice.
-// Both streaming kernels are bound by HBM: algorithmic bytes per call are (distinct experts + shared) x the expert's
+//             int8 codes as fp16 integers plus a scale per 32 columns) and clears the per-pick sums; one more block builds the
+//             Route: the distinct experts, each with the <= 8 rows that picked it as one tile, and the item ranges of the
+//             streaming kernels' blocks.
+//   H <= 6144 and I <= 2048 (the register-resident path, see decode_stream_kernel):
+//     gate_up, down : the same persistent streaming kernel, one block per SM, 16 warps with private rings of 1-D bulk
+//             copies; gate and up sums go to a per-pick fp32 buffer, down turns them into its operand when it enters a tile.
+//   larger shapes (decode_gate_up_kernel, decode_down_kernel): the tile's activation fragments no longer fit in registers
+//             and are fetched stage by stage; gate_up reduces its sixteen partial tiles through shared memory and writes
+//             act = SiLU(gate) * up * weight as fp16, down adds every tile's contribution to a 64-column slice of y in shared
+//             memory.
+//   The reference's int8 shared expert, when the layer has one, runs as two more small kernels (hmoe_shared_i8.cu).
+// All streaming kernels are bound by HBM: algorithmic bytes per call are (distinct experts + shared) x the expert's
 // packed size plus scales.
 #include "hmoe_common.cuh"
 #include "hmoe_internal.h"
