@@ -127,6 +127,14 @@ def test_full_shape(oracle, dev, group, aq):
         assert e[2] < NORM_REL_EXACT, e
 
 
+@pytest.mark.parametrize("aq", [True, False])
+def test_single_token_full_width(oracle, dev, aq):
+    """One token (the reference's own CPU-tier decode case): H = 6144, I = 2048, top-8 of 16 experts + shared."""
+    (got,), ref = run_case(oracle, dev, 6144, 2048, 16, 1, 128, True, aq, seed=7)
+    e = errors(got, ref)
+    assert (e[0] < MAX_REL and e[1] < MEAN_ABS) if aq else e[2] < NORM_REL_EXACT, e
+
+
 @pytest.mark.parametrize("H,I", [(6272, 256), (512, 2176)])
 def test_shapes_beyond_the_register_resident_path(oracle, dev, H, I):
     """H > 6144 or I > 2048: a tile's activation fragments no longer fit in registers and the call takes the kernels that
