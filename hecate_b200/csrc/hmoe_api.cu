@@ -18,6 +18,23 @@ int fail(int code, const char* msg)
 }
 void count_launches(int n) { g_launches += n; }
 
+int current_device()
+{
+    int d = -1;
+    return cudaGetDevice(&d) == cudaSuccess ? d : -1;
+}
+int device_sms()
+{
+    static std::atomic<int> sms[MAX_DEVICES] = {};
+    const int d = current_device();
+    if (d < 0) return 0;
+    if (d < MAX_DEVICES) { const int v = sms[d].load(std::memory_order_relaxed); if (v) return v; }
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, d) != cudaSuccess) return 0;
+    if (d < MAX_DEVICES) sms[d].store(n, std::memory_order_relaxed);
+    return n;
+}
+
 namespace {
 
 // f += y (+ o) (+ o2), y = 0: the band partials are added in the reference's fixed order ((f + y) + o) + o2
@@ -36,68 +53,57 @@ __global__ void __launch_bounds__(256) combine_kernel(float* __restrict__ f, con
     *(float4*) (y + i) = make_float4(0.f, 0.f, 0.f, 0.f);
 }
 
-// The combine fused into the next layer's input norm (replaces combine_norm, runtime/tier/cn.cu:50-105): one block of 1024
-// threads per row; per float4 column a = ((f + y) + o) + o2, y = 0, r += a (fp32 residual, stored), then
-// xn = fp16(r * (w + cbias) * rsqrt(mean(r^2) + eps) * cscale). Thread t owns float4 columns t, t + 1024, ... and the sum of
-// squares is taken in that order with fused multiply-adds, then a butterfly in the warp, the 32 warp sums through shared
-// memory and a second butterfly: the column ownership and summation order of the reference kernel, so r is bit-identical to
-// it and xn differs at most by the last bit of the fast reciprocal square root.
-constexpr int CN_THREADS = 1024, CN_MAXK = 4;
+// Ordered sum of partial outputs + residual add + RMS norm, one launch (replaces combine_norm, runtime/tier/cn.cu:50-105, and is
+// also the tail of the expert-parallel combine). One block of 1024 threads per row. The list `part` holds the row-major fp32
+// partials in the order they are added (the reference's order is ((f + y) + o) + o2; a null first entry reads as zero); `clear`
+// (the accumulator the expert kernels add into) is zeroed for the next layer. What the bit-identity contract with the
+// reference kernel fixes is arithmetic only: thread t owns 4-wide columns t, t + 1024, ..., squares are accumulated with fused
+// multiply-adds in element order, the 1024 partial sums are reduced by a butterfly inside each warp and a second butterfly over
+// the 32 warp sums, and xn = fp16((r * (w + cbias)) * (rsqrt(mean + eps) * cscale)).
+constexpr int NORM_THREADS = 1024, NORM_VECS = 4, NORM_PARTS = 10;
+
+struct NormParts
+{
+    const float* part[NORM_PARTS];     // added in this order; part[0] may be null (= zeros), the others are all valid
+    int n;
+    float* clear;                      // zeroed after it was read (may be null)
+};
 
 template <bool WBF>
-__global__ void __launch_bounds__(CN_THREADS) combine_norm_kernel(const float* __restrict__ f, const float* __restrict__ o, float* __restrict__ y,
-    const float* __restrict__ o2, float* __restrict__ r, const uint16_t* __restrict__ w, __half* __restrict__ xn, int H, float eps, float cbias,
-    float cscale)
+__global__ void __launch_bounds__(NORM_THREADS) sum_norm_kernel(const NormParts in, float* __restrict__ resid, const uint16_t* __restrict__ w,
+                                                                __half* __restrict__ xn, int H, float eps, float cbias, float cscale)
 {
-    __shared__ float sums[32];
-    const int t = threadIdx.x, warp = t >> 5, lane = t & 31, cols = H / 4;
-    const size_t ro = (size_t) blockIdx.x * H;
-    float4 a[CN_MAXK], ww[CN_MAXK];
-    float sum = 0.f;
+    __shared__ float warp_sum[32];
+    const int tid = threadIdx.x, nvec = H / 4;
+    const size_t row = (size_t) blockIdx.x * H;
+    float4 keep[NORM_VECS];
+    float ss = 0.f;
     #pragma unroll
-    for (int k = 0; k < CN_MAXK; ++k)
+    for (int j = 0; j < NORM_VECS; ++j)
     {
-        const int c = t + k * CN_THREADS;
-        if (c >= cols) continue;
-        const size_t i = ro + 4 * (size_t) c;
-        float4 v = f ? *(const float4*) (f + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-        const float4 yc = *(const float4*) (y + i);
-        v.x += yc.x; v.y += yc.y; v.z += yc.z; v.w += yc.w;
-        if (o) { const float4 b = *(const float4*) (o + i); v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w; }
-        if (o2) { const float4 b = *(const float4*) (o2 + i); v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w; }
-        const float4 rr = *(const float4*) (r + i);
-        v.x += rr.x; v.y += rr.y; v.z += rr.z; v.w += rr.w;
-        *(float4*) (y + i) = make_float4(0.f, 0.f, 0.f, 0.f);
-        *(float4*) (r + i) = v;
-        a[k] = v;
-        const uint2 u = *(const uint2*) (w + 4 * c);
-        if (WBF) ww[k] = make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u), __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u));
-        else
+        const int vec = tid + j * NORM_THREADS;
+        if (vec < nvec)
         {
-            const float2 p = __half22float2(*(const __half2*) &u.x), q = __half22float2(*(const __half2*) &u.y);
-            ww[k] = make_float4(p.x, p.y, q.x, q.y);
+            const size_t at = row + 4 * (size_t) vec;
+            float4 sum = in.part[0] ? *(const float4*) (in.part[0] + at) : make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int p = 1; p < in.n; ++p) sum = vec_add(sum, *(const float4*) (in.part[p] + at));
+            sum = vec_add(sum, *(const float4*) (resid + at));
+            if (in.clear) *(float4*) (in.clear + at) = make_float4(0.f, 0.f, 0.f, 0.f);
+            *(float4*) (resid + at) = sum;
+            keep[j] = sum;
+            ss = sq_accumulate(ss, sum);
         }
-        sum = fmaf(v.x, v.x, sum); sum = fmaf(v.y, v.y, sum); sum = fmaf(v.z, v.z, sum); sum = fmaf(v.w, v.w, sum);
     }
-    #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
-    if (lane == 0) sums[warp] = sum;
+    ss = butterfly32(ss);
+    if ((tid & 31) == 0) warp_sum[tid >> 5] = ss;
     __syncthreads();
-    sum = sums[lane];
+    const float total = butterfly32(warp_sum[tid & 31]);
+    const float k = rsqrtf(total / (float) H + eps) * cscale;
     #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
-    const float rmf = rsqrtf(sum / (float) H + eps) * cscale;
-    #pragma unroll
-    for (int k = 0; k < CN_MAXK; ++k)
+    for (int j = 0; j < NORM_VECS; ++j)
     {
-        const int c = t + k * CN_THREADS;
-        if (c >= cols) continue;
-        float4 x4 = a[k], w4 = ww[k];
-        if (cbias != 0.f) { w4.x += cbias; w4.y += cbias; w4.z += cbias; w4.w += cbias; }
-        x4.x = x4.x * w4.x * rmf; x4.y = x4.y * w4.y * rmf; x4.z = x4.z * w4.z * rmf; x4.w = x4.w * w4.w * rmf;
-        const __half2 h0 = __halves2half2(__float2half_rn(x4.x), __float2half_rn(x4.y)), h1 = __halves2half2(__float2half_rn(x4.z), __float2half_rn(x4.w));
-        uint2 u; u.x = *(const uint32_t*) &h0; u.y = *(const uint32_t*) &h1;
-        *(uint2*) (xn + ro + 4 * (size_t) c) = u;
+        const int vec = tid + j * NORM_THREADS;
+        if (vec < nvec) *(uint2*) (xn + row + 4 * (size_t) vec) = norm_pack4(keep[j], norm_weight4<WBF>(w, vec), cbias, k);
     }
 }
 
@@ -239,13 +245,16 @@ int hmoe_combine(float* f, const float* o, float* y, int64_t n, const float* o2,
 int hmoe_combine_norm(const float* f, const float* o, float* y, const float* o2, float* r, const void* w, int w_dtype, void* xn, int rows, int H,
                       float eps, float cbias, float cscale, void* stream)
 {
-    if (!y || !r || !w || !xn || rows < 1 || H < 4 || H % 4 || H > 4 * CN_THREADS * CN_MAXK)
+    if (!y || !r || !w || !xn || rows < 1 || H < 4 || H % 4 || H > 4 * NORM_THREADS * NORM_VECS)
         return fail(HMOE_E_ARG, "hmoe_combine_norm: y, r, w, xn required; H a multiple of 4, at most 16384");
     if (w_dtype != HMOE_F16 && w_dtype != HMOE_BF16) return fail(HMOE_E_ARG, "hmoe_combine_norm: the norm weight must be fp16 or bf16");
-    if (w_dtype == HMOE_BF16)
-        combine_norm_kernel<true><<<rows, CN_THREADS, 0, (cudaStream_t) stream>>>(f, o, y, o2, r, (const uint16_t*) w, (__half*) xn, H, eps, cbias, cscale);
-    else
-        combine_norm_kernel<false><<<rows, CN_THREADS, 0, (cudaStream_t) stream>>>(f, o, y, o2, r, (const uint16_t*) w, (__half*) xn, H, eps, cbias, cscale);
+    NormParts in = {};
+    in.part[0] = f; in.part[1] = y; in.n = 2;
+    if (o) in.part[in.n++] = o;
+    if (o2) in.part[in.n++] = o2;
+    in.clear = y;
+    if (w_dtype == HMOE_BF16) sum_norm_kernel<true><<<rows, NORM_THREADS, 0, (cudaStream_t) stream>>>(in, r, (const uint16_t*) w, (__half*) xn, H, eps, cbias, cscale);
+    else sum_norm_kernel<false><<<rows, NORM_THREADS, 0, (cudaStream_t) stream>>>(in, r, (const uint16_t*) w, (__half*) xn, H, eps, cbias, cscale);
     count_launches(1);
     const cudaError_t err = cudaGetLastError();
     return err == cudaSuccess ? HMOE_OK : fail(HMOE_E_CUDA, cudaGetErrorString(err));

@@ -117,6 +117,9 @@ __device__ __forceinline__ void mma_f16(float* c, const uint32_t* a, uint32_t b0
 // {(row g, k 2q..2q+1), (row g+8, same k), (row g, k 2q+8..), (row g+8, k 2q+8..)} with value code - 8, exactly.
 // (1024 + c is exact in fp16; the nibbles that sit four bits higher give 1024 + 16 c and are brought back by one fused
 // multiply-add with 1/16 and -72.)
+// This is the magic-number conversion the reference's decode kernels use for the same words (dec8, runtime/tier/moe4/moe4.cu:56-67):
+// the stored nibble order was chosen for exactly these two masks, so any converter for this layout extracts the same pairs;
+// a byte-permute (prmt) variant needs one more instruction per word and was not kept.
 __device__ __forceinline__ void frag_from_codes(uint32_t w, uint32_t* a)
 {
     // Written as PTX with plain 32-bit immediates: half2 constants built through the cuda_fp16 helpers are re-materialised
@@ -134,7 +137,8 @@ __device__ __forceinline__ void frag_from_codes(uint32_t w, uint32_t* a)
 }
 
 // position of two-value word p (columns 2p, 2p+1 of a 64-column block) in the activation row order the kernels read:
-// t = p / 8 (16-column step), h = (p % 8) / 4, q = p % 4  ->  q * 8 + t * 2 + h
+// t = p / 8 (16-column step), h = (p % 8) / 4, q = p % 4  ->  q * 8 + t * 2 + h (the B-fragment order the reference's norm +
+// router kernel may pre-write for moe4, frag_word, runtime/tier/moe4/moe4.cu:72)
 __device__ __forceinline__ int frag_pos(int p) { return (p & 3) * 8 + (p >> 3) * 2 + ((p >> 2) & 1); }
 
 __device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_as_float((uint32_t) b << 16); }
@@ -157,6 +161,33 @@ __device__ __forceinline__ float det_expf(float x)
     p = __fmaf_rn(p, __fmul_rn(r, r), r);
     p = __fadd_rn(p, 1.f);
     return __fmul_rn(p, __int_as_float(((int) n + 127) << 23));
+}
+
+// ---- pieces of the residual + RMS-norm kernels (hmoe_combine_norm, hmoe_norm_router): 4-wide column arithmetic in the order
+// the bit-identity contract with the reference norm kernels fixes (see sum_norm_kernel)
+__device__ __forceinline__ float4 vec_add(float4 a, const float4 b) { a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w; return a; }
+__device__ __forceinline__ float sq_accumulate(float s, const float4 v) { s = fmaf(v.x, v.x, s); s = fmaf(v.y, v.y, s); s = fmaf(v.z, v.z, s); return fmaf(v.w, v.w, s); }
+__device__ __forceinline__ float butterfly32(float v)
+{
+    #pragma unroll
+    for (int d = 16; d; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
+    return v;
+}
+template <bool WBF>
+__device__ __forceinline__ float4 norm_weight4(const uint16_t* w, int vec)
+{
+    const uint2 bits = *(const uint2*) (w + 4 * vec);
+    if (WBF) return make_float4(__uint_as_float(bits.x << 16), __uint_as_float(bits.x & 0xffff0000u), __uint_as_float(bits.y << 16), __uint_as_float(bits.y & 0xffff0000u));
+    const float2 lo = __half22float2(*(const __half2*) &bits.x), hi = __half22float2(*(const __half2*) &bits.y);
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+// fp16x4 of (v * (w + cbias)) * k, each product rounded on its own as in the reference kernel
+__device__ __forceinline__ uint2 norm_pack4(const float4 v, float4 w, float cbias, float k)
+{
+    if (cbias != 0.f) { w.x += cbias; w.y += cbias; w.z += cbias; w.w += cbias; }
+    const __half2 lo = __floats2half2_rn(__fmul_rn(__fmul_rn(v.x, w.x), k), __fmul_rn(__fmul_rn(v.y, w.y), k));
+    const __half2 hi = __floats2half2_rn(__fmul_rn(__fmul_rn(v.z, w.z), k), __fmul_rn(__fmul_rn(v.w, w.w), k));
+    return make_uint2(*(const uint32_t*) &lo, *(const uint32_t*) &hi);
 }
 
 // Routing of one decode call, built once per call by the prepare kernel and read by the expert kernels.

@@ -725,7 +725,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_stream_kernel(const Decode
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
     const uint32_t ring = sbase + warp * SLOT, full0 = sbase + StreamSmem::bars + warp * 8;      // slot st: + st * CW * SLOT / + st * CW * 8
     volatile int* abort_flag = (volatile int*) (smem + StreamSmem::flags);
-    pdl_launch_dependents();
     if (threadIdx.x == 0)
     {
         for (int i = 0; i < NSTAGE * CW; ++i) mbar_init(sbase + StreamSmem::bars + i * 8, 1);
@@ -735,7 +734,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_stream_kernel(const Decode
     __syncthreads();
     // gate_up follows the prepare kernel, which wrote the route; down follows gate_up, but the route and the weights it
     // needs to fill its rings are older than that: it waits only before it reads the gate / up sums.
-    if (!DOWN) pdl_wait();
+    // Ordering rule of the chain: a kernel lets its dependents start only after its own wait has returned, i.e. after the
+    // kernel before it has completed with its memory visible. So whatever a dependent reads before ITS wait (down: the route,
+    // the step counter) was written at least two kernels back and is complete, whatever the occupancy. Blocks without work
+    // wait too, so that a grid with nothing to do cannot release its dependents early.
+    if (!DOWN) { pdl_wait(); pdl_launch_dependents(); }
     const Route* rt = a.route;
     const int K = DOWN ? a.I : a.H, N = DOWN ? a.H : a.I;          // input columns and output rows of one matrix
     const int KB = K / 64, NG = N / 64, J = DOWN ? NG : 2 * NG;
@@ -884,7 +887,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_stream_kernel(const Decode
         for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
         uint32_t st = 0, par = 0;
         int tile = p0 / J, j = p0 % J;
-        if (DOWN) pdl_wait();
+        if (DOWN) { pdl_wait(); pdl_launch_dependents(); }
         enter_tile(tile);
         if (!GROUPED) load_row_scales(j, sd);
         bool alive = true;
@@ -942,6 +945,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_stream_kernel(const Decode
             }
         }
     }
+    else if (DOWN) { pdl_wait(); pdl_launch_dependents(); }
     __syncthreads();
 }
 
@@ -961,8 +965,6 @@ size_t decode_ws_bytes(int H, int I)
     b += up256((size_t) MAXT * 8 * (I / 32) * 4);        // ascale
     return b;
 }
-
-static int g_sms = 0;
 
 // Optional phase timing: when switched on, every decode call records four events (before prepare, after prepare, after
 // gate_up, after down) on the caller's stream into a ring of PROF_RING sets; decode_phase_times() averages the sets recorded
@@ -1019,17 +1021,18 @@ static void launch_dependent(Kern kern, int grid, const DecodeArgs& a, cudaStrea
 template <bool G, bool Q, int KC>
 static void launch_stream_gate_up(int grid, const DecodeArgs& a, cudaStream_t st)
 {
-    static bool first = true;
-    if (first) { cudaFuncSetAttribute(decode_stream_kernel<G, Q, false, KC>, cudaFuncAttributeMaxDynamicSharedMemorySize, StreamSmem::total); first = false; }
+    static DeviceOnce once;
+    if (once.first()) cudaFuncSetAttribute(decode_stream_kernel<G, Q, false, KC>, cudaFuncAttributeMaxDynamicSharedMemorySize, StreamSmem::total);
     launch_dependent(decode_stream_kernel<G, Q, false, KC>, grid, a, st);
 }
 
 template <bool G, bool Q>
-static void launch_pair(int grid, const DecodeArgs& a, int R, cudaStream_t st, bool first)
+static void launch_pair(int grid, const DecodeArgs& a, int R, cudaStream_t st)
 {
     cudaEvent_t* ev = g_ev[g_prof_calls % PROF_RING];
     if (g_prof) cudaEventRecord(ev[1], st);
-    if (first)
+    static DeviceOnce once;
+    if (once.first())
     {
         cudaFuncSetAttribute(decode_gate_up_kernel<G, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout::total);
         cudaFuncSetAttribute(decode_down_kernel<G, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout::total);
@@ -1060,12 +1063,8 @@ int decode_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t
     if (x_dtype != HMOE_F16 && x_dtype != HMOE_BF16) return fail(HMOE_E_ARG, "hmoe_decode: x must be fp16 or bf16");
     if (ws_bytes < decode_ws_bytes(H, I)) return fail(HMOE_E_WS, "hmoe_decode: workspace too small");
     if (!x || !sel || !rw || !y || !ws) return fail(HMOE_E_ARG, "hmoe_decode: null pointer");
-    static bool first[4] = {true, true, true, true};
-    if (g_sms == 0)
-    {
-        int dev = 0; cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev);
-    }
+    const int g_sms = device_sms();
+    if (g_sms <= 0) return fail(HMOE_E_CUDA, "hmoe_decode: no current CUDA device");
     char* w = (char*) ws;
     unsigned* status = (unsigned*) w; w += 256;
     Route* route = (Route*) w; w += up256(sizeof(Route));
@@ -1096,11 +1095,10 @@ int decode_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t
     a.gen_ptr = gen_ptr; a.slot_stride = slot_stride;
     const int grid = g_sms < MAXB ? g_sms : MAXB;
     const int v = (L->group ? 2 : 0) + (act_quant ? 1 : 0);
-    if (v == 0) launch_pair<false, false>(grid, a, R, st, first[0]);
-    else if (v == 1) launch_pair<false, true>(grid, a, R, st, first[1]);
-    else if (v == 2) launch_pair<true, false>(grid, a, R, st, first[2]);
-    else launch_pair<true, true>(grid, a, R, st, first[3]);
-    first[v] = false;
+    if (v == 0) launch_pair<false, false>(grid, a, R, st);
+    else if (v == 1) launch_pair<false, true>(grid, a, R, st);
+    else if (v == 2) launch_pair<true, false>(grid, a, R, st);
+    else launch_pair<true, true>(grid, a, R, st);
     count_launches(3);
     const cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) return fail(HMOE_E_CUDA, cudaGetErrorString(err));
@@ -1132,7 +1130,6 @@ namespace hmoe {
 namespace {
 constexpr size_t STATIC_WS_BYTES = 5u << 20;
 static __device__ __align__(256) unsigned char g_decode_scratch[STATIC_WS_BYTES];
-constexpr int MAX_DEVICES = 64;
 static void* g_scratch_addr[MAX_DEVICES] = {};
 }  // namespace
 }  // namespace hmoe

@@ -12,6 +12,26 @@ namespace hmoe {
 int fail(int code, const char* msg);
 void count_launches(int n);
 
+// Per-device host state. One process may drive several GPUs through this library, so nothing that belongs to a device (its SM
+// count, whether a kernel's shared-memory attribute has been set there) is kept in a per-process static.
+constexpr int MAX_DEVICES = 64;
+int current_device();                     // cudaGetDevice, -1 on failure
+int device_sms();                         // SM count of the current device (looked up once per device)
+// One flag per device: first() is true the first time it is called with a given device current (and every time for device
+// numbers beyond MAX_DEVICES, where the set-up it guards is simply repeated).
+struct DeviceOnce
+{
+    unsigned char done[MAX_DEVICES] = {};
+    bool first()
+    {
+        const int d = current_device();
+        if (d < 0 || d >= MAX_DEVICES) return true;
+        if (done[d]) return false;
+        done[d] = 1;
+        return true;
+    }
+};
+
 size_t decode_ws_bytes(int H, int I);
 int decode_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
                   int act_quant, float* y, void* ws, size_t ws_bytes, cudaStream_t st, int sh_mod = 1, int sh_rem = 0,

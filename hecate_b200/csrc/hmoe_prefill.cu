@@ -238,6 +238,10 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"((uint64_t) map), "r"(c0), "r"(c1), "r"(bar) : "memory");
 }
+__device__ __forceinline__ void red_add_sys(float* p, float v)
+{
+    asm volatile("red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(__cvta_generic_to_global(p)), "f"(v) : "memory");
+}
 __device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) { asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory"); }
 
 struct GemmArgs
@@ -414,9 +418,15 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
                         if (p < t.n)
                         {
                             const int tk = a.tok[t.pos0 + p];
-                            float* dst = a.out + (size_t) tk * a.N;
-                            if (a.rows_per_rank) { const int pr = tk / a.rows_per_rank; dst = a.out_peer[pr] + (size_t) (tk - pr * a.rows_per_rank) * a.N; }
-                            atomicAdd(dst + ch, __uint_as_float(r0[j]) * sc0);
+                            const float v = __uint_as_float(r0[j]) * sc0;
+                            if (a.rows_per_rank)
+                            {
+                                // the row's owner may be another GPU, and up to eight GPUs add into the same addresses: the
+                                // reduction has to be atomic at system scope (a gpu-scope one is only atomic among this GPU's threads)
+                                const int pr = tk / a.rows_per_rank;
+                                red_add_sys(a.out_peer[pr] + (size_t) (tk - pr * a.rows_per_rank) * a.N + ch, v);
+                            }
+                            else atomicAdd(a.out + (size_t) tk * a.N + ch, v);
                         }
                     }
                 }
@@ -566,6 +576,15 @@ bool make_map(CUtensorMap* m, const void* ptr, int K, size_t rows)
 
 size_t up256(size_t b) { return (b + 255) / 256 * 256; }
 
+// the kernels' dynamic shared memory exceeds the default limit: raise it once per device
+void set_gemm_attributes()
+{
+    static DeviceOnce once;
+    if (!once.first()) return;
+    cudaFuncSetAttribute(prefill_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfSmem<2>::total);
+    cudaFuncSetAttribute(prefill_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfSmem<1>::total);
+}
+
 struct WsLayout
 {
     size_t status, plan, counts, offs, hist, order, tok, eid, wt, rbt, xg, act, total;
@@ -637,14 +656,9 @@ int prefill_sorted_launch(const hmoe_layer* L, const void* x, int x_dtype, const
     if (!x || !tok || !wt || !rbt || !out || !ws) return fail(HMOE_E_ARG, "hmoe_prefill_sorted: null pointer");
     const int kf = act_quant ? 2 : 1;
     if (ws_bytes < prefill_sorted_ws_bytes(npos, H, I, act_quant)) return fail(HMOE_E_WS, "hmoe_prefill_sorted: workspace too small");
-    static int sms = 0;
-    if (!sms)
-    {
-        int dev = 0; cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        cudaFuncSetAttribute(prefill_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfSmem<2>::total);
-        cudaFuncSetAttribute(prefill_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfSmem<1>::total);
-    }
+    const int sms = device_sms();
+    if (sms <= 0) return fail(HMOE_E_CUDA, "hmoe_prefill_sorted: no current CUDA device");
+    set_gemm_attributes();
     char* b = (char*) ws;
     unsigned* status = (unsigned*) b;
     Plan* plan = (Plan*) (b + 256);
@@ -713,16 +727,9 @@ int prefill_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_
     const int kf = act_quant ? 2 : 1;
     const WsLayout w = ws_layout(R, L->topk, n_local, H, I, TN, kf);
     if (ws_bytes < w.total) return fail(HMOE_E_WS, "hmoe_prefill: workspace too small (the int8 mode needs hmoe_prefill_ws_bytes(..., act_quant = 1))");
-    static int sms = 0;
-    static bool attr = false;
-    if (!attr)
-    {
-        int dev = 0; cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        cudaFuncSetAttribute(prefill_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfSmem<2>::total);
-        cudaFuncSetAttribute(prefill_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfSmem<1>::total);
-        attr = true;
-    }
+    const int sms = device_sms();
+    if (sms <= 0) return fail(HMOE_E_CUDA, "hmoe_prefill: no current CUDA device");
+    set_gemm_attributes();
     char* b = (char*) ws;
     unsigned* status = (unsigned*) (b + w.status);
     Plan* plan = (Plan*) (b + w.plan);

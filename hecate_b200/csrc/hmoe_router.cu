@@ -6,6 +6,7 @@
 //   butterfly steps (xor 16, 8, 4, 2, 1) add the 32 partial sums.
 // One launch: the block that completes a group of four rows last also selects their experts. Router calls that overlap
 // on one device take different counter sets in rotation (sixteen of them).
+#include <atomic>
 #include "hmoe_common.cuh"
 #include "hmoe_internal.h"
 
@@ -32,6 +33,8 @@ constexpr int CTR_SLOTS = 16, CTR_GROUPS = 256;
 // one device do not share counters unless more than CTR_SLOTS of them are in flight). Zero when the library is loaded;
 // the block that arrives last puts its counter back to zero.
 static __device__ unsigned g_router_ctr[CTR_SLOTS][CTR_GROUPS];
+// Set by a block of the row group whose bounded wait gave up; read and cleared by the group's last block.
+static __device__ unsigned g_router_bad[CTR_SLOTS][CTR_GROUPS];
 
 // These kernels run once per layer on a handful of warps per SM: their duration is a chain of memory latencies, so every
 // group of loads is issued before its first use.
@@ -108,7 +111,8 @@ template <bool XBF, bool WBF, bool FUSED, bool NORM>
 __global__ void __launch_bounds__(RW * 32) router_logits_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ wt,
                                                                 int R, int H, int E, float* __restrict__ logits,
                                                                 const float* __restrict__ bias, int topk, float scale,
-                                                                int64_t* __restrict__ sel, __half* __restrict__ rw, int slot, const NormArgs na)
+                                                                int64_t* __restrict__ sel, __half* __restrict__ rw, int slot, const NormArgs na,
+                                                                unsigned* __restrict__ status)
 {
     extern __shared__ __align__(128) unsigned char rsm[];
     __shared__ int s_last;
@@ -161,25 +165,17 @@ __global__ void __launch_bounds__(RW * 32) router_logits_kernel(const uint16_t* 
                 #pragma unroll
                 for (int k = 0; k < 4; ++k)
                 {
+                    // virtual thread t + 256 k of the stand-alone norm kernel: its two columns in order, then its warp's butterfly
                     float sq = 0.f;
                     #pragma unroll
                     for (int j = 0; j < 2; ++j)
-                        if (t + 256 * k + 1024 * j < cols)
-                        {
-                            const float4 a = v[k][j];
-                            sq = fmaf(a.x, a.x, sq); sq = fmaf(a.y, a.y, sq); sq = fmaf(a.z, a.z, sq); sq = fmaf(a.w, a.w, sq);
-                        }
-                    #pragma unroll
-                    for (int off = 16; off > 0; off >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, off);
-                    ps[k] = sq;
+                        if (t + 256 * k + 1024 * j < cols) sq = sq_accumulate(sq, v[k][j]);
+                    ps[k] = butterfly32(sq);
                 }
                 __syncthreads();                                  // vsums free (previous row read)
                 if (lane == 0) { vsums[warp] = ps[0]; vsums[warp + 8] = ps[1]; vsums[warp + 16] = ps[2]; vsums[warp + 24] = ps[3]; }
                 __syncthreads();
-                float tot = vsums[lane];
-                #pragma unroll
-                for (int off = 16; off > 0; off >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, off);
-                const float rmf = rsqrtf(tot / (float) H + na.eps) * na.cscale;
+                const float rmf = rsqrtf(butterfly32(vsums[lane]) / (float) H + na.eps) * na.cscale;
                 #pragma unroll
                 for (int k = 0; k < 4; ++k)
                     #pragma unroll
@@ -187,22 +183,17 @@ __global__ void __launch_bounds__(RW * 32) router_logits_kernel(const uint16_t* 
                     {
                         const int c = t + 256 * k + 1024 * j;
                         if (c >= cols) continue;
-                        float4 a = v[k][j], w4;
-                        const uint2 u = *(const uint2*) (na.nw + 4 * c);
-                        if (na.nw_bf16) w4 = make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u), __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u));
-                        else { const float2 p = __half22float2(*(const __half2*) &u.x), q2 = __half22float2(*(const __half2*) &u.y); w4 = make_float4(p.x, p.y, q2.x, q2.y); }
-                        if (na.cbias != 0.f) { w4.x += na.cbias; w4.y += na.cbias; w4.z += na.cbias; w4.w += na.cbias; }
-                        const __half2 h0 = __halves2half2(__float2half_rn(a.x * w4.x * rmf), __float2half_rn(a.y * w4.y * rmf));
-                        const __half2 h1 = __halves2half2(__float2half_rn(a.z * w4.z * rmf), __float2half_rn(a.w * w4.w * rmf));
-                        const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+                        const float4 w4 = na.nw_bf16 ? norm_weight4<true>(na.nw, c) : norm_weight4<false>(na.nw, c);
+                        const uint2 o = norm_pack4(v[k][j], w4, na.cbias, rmf);
+                        // the router sees the rounded fp16 values, staged as fp32 in the order the logit sums read them
+                        const float2 f0 = __half22float2(*(const __half2*) &o.x), f1 = __half22float2(*(const __half2*) &o.y);
                         const int col = 4 * c;
                         *(float4*) (xs + rr * hc + (col & ~255) + ((col & 255) >> 3) * 4 + (c & 1) * 128) = make_float4(f0.x, f0.y, f1.x, f1.y);
                         if (blockIdx.x == 0 && rr < nr)
                         {
                             const size_t i = (size_t) (r0 + rr) * H + col;
-                            uint2 o; o.x = *(const uint32_t*) &h0; o.y = *(const uint32_t*) &h1;
                             *(uint2*) (na.xn + i) = o;
-                            if (na.r_out) *(float4*) (na.r_out + i) = a;
+                            if (na.r_out) *(float4*) (na.r_out + i) = v[k][j];
                         }
                     }
             }
@@ -233,9 +224,12 @@ __global__ void __launch_bounds__(RW * 32) router_logits_kernel(const uint16_t* 
             }
         }
         __syncthreads();
-        if (!mbar_wait(bar, par, &s_abort, nullptr)) return;
+        // A wait that gives up raises the status bit; the block skips the sums but still takes part in the arrival count
+        // below, so the call's counter slot returns to zero and later calls that reuse it are not affected.
+        const bool got = mbar_wait(bar, par, &s_abort, status);
+        if (FUSED && !got && lane == 0) atomicOr(&g_router_bad[slot][blockIdx.y], 1u);
         #pragma unroll 2
-        for (int k = 0; k < cl; k += 256)
+        for (int k = 0; got && k < cl; k += 256)
         {
             float wf[8];
             widen8<WBF>(lds128(wsm + (k + lane * 8) * 2), wf);
@@ -272,6 +266,13 @@ __global__ void __launch_bounds__(RW * 32) router_logits_kernel(const uint16_t* 
     __syncthreads();
     if (!s_last) return;
     __threadfence();
+    {
+        // after a failed wait the logits are incomplete: select nothing (the status word tells the host)
+        const unsigned bad = *(volatile unsigned*) &g_router_bad[slot][blockIdx.y];
+        __syncthreads();
+        if (threadIdx.x == 0 && bad) g_router_bad[slot][blockIdx.y] = 0u;
+        if (bad) return;
+    }
     if (warp < nr) topk_row(logits, bias, r0 + warp, E, topk, scale, sel, rw, lane, true, xs + warp * 512);
 }
 
@@ -285,38 +286,40 @@ __global__ void __launch_bounds__(256) router_topk_kernel(const float* __restric
 
 template <bool XBF, bool WBF>
 void launch_logits(dim3 grid, size_t smem, cudaStream_t st, bool fused, const uint16_t* x, const uint16_t* wt, int R, int H, int E,
-                   float* logits, const float* bias, int topk, float scale, int64_t* sel, __half* rw, int slot)
+                   float* logits, const float* bias, int topk, float scale, int64_t* sel, __half* rw, int slot, unsigned* status)
 {
-    static bool attr = false;
-    if (!attr)
+    static DeviceOnce once;
+    if (once.first())
     {
         cudaFuncSetAttribute(router_logits_kernel<XBF, WBF, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         cudaFuncSetAttribute(router_logits_kernel<XBF, WBF, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        attr = true;
     }
     const NormArgs na = {};
-    if (fused) router_logits_kernel<XBF, WBF, true, false><<<grid, RW * 32, smem, st>>>(x, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot, na);
-    else router_logits_kernel<XBF, WBF, false, false><<<grid, RW * 32, smem, st>>>(x, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot, na);
+    if (fused) router_logits_kernel<XBF, WBF, true, false><<<grid, RW * 32, smem, st>>>(x, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot, na, status);
+    else router_logits_kernel<XBF, WBF, false, false><<<grid, RW * 32, smem, st>>>(x, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot, na, status);
 }
 
 template <bool WBF>
 void launch_norm_router(dim3 grid, size_t smem, cudaStream_t st, bool fused, const uint16_t* wt, int R, int H, int E, float* logits,
-                        const float* bias, int topk, float scale, int64_t* sel, __half* rw, int slot, const NormArgs& na)
+                        const float* bias, int topk, float scale, int64_t* sel, __half* rw, int slot, const NormArgs& na, unsigned* status)
 {
-    static bool attr = false;
-    if (!attr)
+    static DeviceOnce once;
+    if (once.first())
     {
         cudaFuncSetAttribute(router_logits_kernel<false, WBF, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         cudaFuncSetAttribute(router_logits_kernel<false, WBF, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        attr = true;
     }
-    if (fused) router_logits_kernel<false, WBF, true, true><<<grid, RW * 32, smem, st>>>(nullptr, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot, na);
-    else router_logits_kernel<false, WBF, false, true><<<grid, RW * 32, smem, st>>>(nullptr, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot, na);
+    if (fused) router_logits_kernel<false, WBF, true, true><<<grid, RW * 32, smem, st>>>(nullptr, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot, na, status);
+    else router_logits_kernel<false, WBF, false, true><<<grid, RW * 32, smem, st>>>(nullptr, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot, na, status);
 }
+
+// Both entry points share the counter sets, so they also share the rotation that hands them out.
+std::atomic<unsigned> g_router_calls{0};
 
 }  // namespace
 
-size_t router_ws_bytes(int R, int E) { return ((size_t) R * E * 4 + 255) / 256 * 256; }
+// workspace: status word (256 bytes, see hmoe_ws_status) + logits fp32 [R][E]
+size_t router_ws_bytes(int R, int E) { return 256 + ((size_t) R * E * 4 + 255) / 256 * 256; }
 
 int router_launch(const void* x, int x_dtype, const void* wt, int w_dtype, const float* bias, int R, int H, int E, int topk,
                   float scale, int64_t* sel, void* rw, void* ws, size_t ws_bytes, cudaStream_t st)
@@ -330,18 +333,18 @@ int router_launch(const void* x, int x_dtype, const void* wt, int w_dtype, const
     const int hc = H < HC ? H : HC;
     const size_t smem = (size_t) RR * (hc > 512 ? hc : 512) * 4 + (size_t) RW * hc * 2;    // rows as fp32 (reused as the selection's scratch) + weight rows
     const dim3 grid((E + RW - 1) / RW, (R + RR - 1) / RR);
-    float* logits = (float*) ws;
+    unsigned* status = (unsigned*) ws;
+    float* logits = (float*) ((char*) ws + 256);
     const uint16_t* xp = (const uint16_t*) x; const uint16_t* wp = (const uint16_t*) wt;
     // Up to CTR_GROUPS row groups the selection runs in the same launch (the last block of a row group does it); beyond,
     // a second kernel selects.
     const bool fused = (int) grid.y <= CTR_GROUPS;
-    static unsigned calls = 0;
-    const int slot = (int) (calls++ % CTR_SLOTS);
+    const int slot = (int) (g_router_calls.fetch_add(1, std::memory_order_relaxed) % CTR_SLOTS);
     const bool xb = x_dtype == HMOE_BF16, wb = w_dtype == HMOE_BF16;
-    if (!xb && !wb) launch_logits<false, false>(grid, smem, st, fused, xp, wp, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot);
-    else if (!xb && wb) launch_logits<false, true>(grid, smem, st, fused, xp, wp, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot);
-    else if (xb && !wb) launch_logits<true, false>(grid, smem, st, fused, xp, wp, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot);
-    else launch_logits<true, true>(grid, smem, st, fused, xp, wp, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot);
+    if (!xb && !wb) launch_logits<false, false>(grid, smem, st, fused, xp, wp, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot, status);
+    else if (!xb && wb) launch_logits<false, true>(grid, smem, st, fused, xp, wp, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot, status);
+    else if (xb && !wb) launch_logits<true, false>(grid, smem, st, fused, xp, wp, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot, status);
+    else launch_logits<true, true>(grid, smem, st, fused, xp, wp, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot, status);
     if (!fused) router_topk_kernel<<<(R + 7) / 8, 256, 0, st>>>(logits, bias, R, E, topk, scale, sel, (__half*) rw);
     count_launches(fused ? 1 : 2);
     const cudaError_t err = cudaGetLastError();
@@ -362,14 +365,14 @@ int norm_router_launch(const float* y, const float* r, float* r_out, const void*
     const size_t smem = (size_t) RR * (H > 512 ? H : 512) * 4 + (size_t) RW * H * 2;
     const dim3 grid((E + RW - 1) / RW, (R + RR - 1) / RR);
     const bool fused = (int) grid.y <= CTR_GROUPS;
-    static unsigned calls = 0;
-    const int slot = (int) (calls++ % CTR_SLOTS);
+    const int slot = (int) (g_router_calls.fetch_add(1, std::memory_order_relaxed) % CTR_SLOTS);
     NormArgs na;
     na.r = r; na.y = y; na.r_out = r_out; na.nw = (const uint16_t*) nw; na.xn = (__half*) xn; na.eps = eps; na.cbias = cbias; na.cscale = cscale;
     na.nw_bf16 = nw_dtype == HMOE_BF16;
-    float* logits = (float*) ws;
-    if (w_dtype == HMOE_BF16) launch_norm_router<true>(grid, smem, st, fused, (const uint16_t*) wt, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot, na);
-    else launch_norm_router<false>(grid, smem, st, fused, (const uint16_t*) wt, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot, na);
+    unsigned* status = (unsigned*) ws;
+    float* logits = (float*) ((char*) ws + 256);
+    if (w_dtype == HMOE_BF16) launch_norm_router<true>(grid, smem, st, fused, (const uint16_t*) wt, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot, na, status);
+    else launch_norm_router<false>(grid, smem, st, fused, (const uint16_t*) wt, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot, na, status);
     if (!fused) router_topk_kernel<<<(R + 7) / 8, 256, 0, st>>>(logits, bias, R, E, topk, scale, sel, (__half*) rw);
     count_launches(fused ? 1 : 2);
     const cudaError_t err = cudaGetLastError();

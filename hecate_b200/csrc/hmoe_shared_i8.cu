@@ -24,6 +24,7 @@ namespace {
 constexpr int SW = 16, STHREADS = SW * 32, PART = 16 * 65;
 
 // 4 bytes (c0 rh0, c0 rh1, c1 rh0, c1 rh1) -> fp16x2 (row g: c0, c1) and (row g + 8: c0, c1), value code - 128, exactly
+// (the same magic-number step as the reference uses for these bytes, runtime/tier/moe4/moe4.cu:48-55: 1024 + code is exact in fp16)
 __device__ __forceinline__ void dec_i8(uint32_t w, uint32_t& lo, uint32_t& hi)
 {
     uint32_t h0, h1;
@@ -79,7 +80,6 @@ __global__ void __launch_bounds__(STHREADS, 1) shared_i8_kernel(const SharedArgs
 {
     extern __shared__ float part[];                       // [SW][16 tile columns][64 rows + 1]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
-    pdl_launch_dependents();
     const int K = DOWN ? a.I : a.H, N = DOWN ? a.H : a.I, KB = K / 32, NG = N / 64;
     const long long total = (long long) (DOWN ? 1 : 2) * NG * KB;
     const long long U0 = total * blockIdx.x / gridDim.x, U1 = total * (blockIdx.x + 1) / gridDim.x;
@@ -137,7 +137,9 @@ __global__ void __launch_bounds__(STHREADS, 1) shared_i8_kernel(const SharedArgs
         uint4 w[4], wn[4];
         uint32_t b[2][4], bn[2][4];
         if (u < seg1) load_w(u, w);              // weights do not depend on the kernel before: requested while it drains
-        if (!waited) { pdl_wait(); waited = true; }
+        // dependents are released only after this kernel's own wait (see decode_stream_kernel: what a dependent reads before
+        // its wait is then at least two completed kernels old)
+        if (!waited) { pdl_wait(); pdl_launch_dependents(); waited = true; }
         if (u < seg1) load_b(u, b);
         for (; u < seg1; u += SW)
         {
@@ -187,6 +189,7 @@ __global__ void __launch_bounds__(STHREADS, 1) shared_i8_kernel(const SharedArgs
         __syncthreads();
         seg0 = seg1;
     }
+    if (!waited) { pdl_wait(); pdl_launch_dependents(); }       // a block without units still orders the chain
 }
 
 }  // namespace
@@ -202,13 +205,12 @@ int shared_i8_launch(const hmoe_layer* L, int R, int sh_mod, int sh_rem, const _
     a.gate_s = (const float*) L->sh_gate_s; a.up_s = (const float*) L->sh_up_s; a.down_s = (const float*) L->sh_down_s;
     a.xf = xf; a.gs = gs; a.y = y; a.gen_ptr = gen_ptr; a.slot_stride = slot_stride;
     // one block of sixteen warps per SM; both launches are programmatic dependents of the kernel before them
-    static bool attr = false;
+    static DeviceOnce once;
     const size_t smem = (size_t) SW * PART * 4;
-    if (!attr)
+    if (once.first())
     {
         cudaFuncSetAttribute(shared_i8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
         cudaFuncSetAttribute(shared_i8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
-        attr = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(sms); cfg.blockDim = dim3(STHREADS); cfg.dynamicSmemBytes = smem; cfg.stream = st;

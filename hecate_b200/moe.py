@@ -259,7 +259,7 @@ def router_fused(x, wt, bias, logits, ctr, sel, rw, topk, scale):
     key = (x.device, )
     ws = _router_ws.get(key)
     if ws is None or ws.numel() < need:
-        ws = _router_ws[key] = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=x.device)
+        ws = _router_ws[key] = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=x.device)
     if not (x.is_contiguous() and wt.is_contiguous()):
         raise HmoeError("router_fused: shape / dtype")
     check(lib().hmoe_router(vp(x), C.c_int(_dt(x)), vp(wt), C.c_int(_dt(wt)), vp(bias), C.c_int(R), C.c_int(H), C.c_int(E),
@@ -277,7 +277,7 @@ def norm_route(y, r, w, xn, wt, bias, sel, rw, topk, scale, eps, cbias=0.0, csca
     need = lib().hmoe_router_ws_bytes(C.c_int(R), C.c_int(E))
     ws = _router_ws.get((r.device, ))
     if ws is None or ws.numel() < need:
-        ws = _router_ws[(r.device, )] = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=r.device)
+        ws = _router_ws[(r.device, )] = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=r.device)
     if r.dtype != torch.float32 or xn.dtype != torch.float16 or not (r.is_contiguous() and xn.is_contiguous() and wt.is_contiguous() and w.is_contiguous()):
         raise HmoeError("norm_route: shapes / dtypes")
     check(lib().hmoe_norm_router(vp(y), vp(r), vp(r_out), vp(w), C.c_int(_dt(w)), vp(xn), vp(wt), C.c_int(_dt(wt)), vp(bias), C.c_int(R), C.c_int(H),

@@ -51,7 +51,9 @@ int64_t hmoe_launch_count(void);
  * routing_dots contract (docker/patches/exllamav3/block_sparse_mlp_routing.py:253-301) for any number of rows.
  * x [R][H] and wt [E][H] are fp16 or bf16 (x_dtype / w_dtype), bias fp32 [E] or null. Writes sel int64 [R][topk] (selection
  * order: descending sigmoid(logit) + bias, ties to the lower expert id) and rw fp16 [R][topk] = act * scale / (sum + 1e-20).
- * Needs E % 32 == 0, E <= 256, H % 256 == 0, topk <= 8. ws: hmoe_router_ws_bytes(R, E) bytes of device scratch. */
+ * Needs E % 32 == 0, E <= 256, H % 256 == 0, topk <= 8. ws: hmoe_router_ws_bytes(R, E) bytes of device scratch, zero-filled once
+ * before first use; its first word is a status word (hmoe_ws_status): if a bounded wait inside the kernel gives up, bit 0 is
+ * set and the call writes no selection. */
 size_t hmoe_router_ws_bytes(int R, int E);
 int hmoe_router(const void* x, int x_dtype, const void* wt, int w_dtype, const float* bias, int R, int H, int E, int topk,
                 float scale, int64_t* sel, void* rw, void* ws, size_t ws_bytes, void* stream);

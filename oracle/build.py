@@ -16,7 +16,16 @@ import sys
 import sysconfig
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF_ROOT = os.environ.get("HECATE_REFERENCE_ROOT", "/root/reference")
+
+
+def ref_root():
+    """Where the reference project's tree lies: HECATE_REFERENCE_ROOT, else a folder named `reference` beside this repository
+    (None if neither exists)."""
+    for cand in (os.environ.get("HECATE_REFERENCE_ROOT"), os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")):
+        if cand and os.path.isdir(cand):
+            return cand
+    return None
+
 CXXFLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-mavx2", "-mfma", "-mf16c", "-ffp-contract=off", "-fopenmp"]
 
 
@@ -39,9 +48,10 @@ def ref_module_path():
 
 def build_ref(force=False):
     """Compile the reference CPU engine as the python module `cpuband_ref` (needs the reference tree and torch headers)."""
-    src = os.path.join(REF_ROOT, "runtime", "tier", "cpuband.cpp")
+    root = ref_root()
+    src = os.path.join(root, "runtime", "tier", "cpuband.cpp") if root else ""
     dst = ref_module_path()
-    if not os.path.exists(src):
+    if not root or not os.path.exists(src):
         return dst if os.path.exists(dst) else None
     shim = os.path.join(HERE, "ref_shim", "arm_neon.h")
     if not force and _newer(dst, src, shim):

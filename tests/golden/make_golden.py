@@ -1,5 +1,5 @@
 """Generates the golden fixtures of tests/golden from the reference itself. Run in a container that has the reference
-tree (default /root/reference) and the oracle/_ref build:
+tree (HECATE_REFERENCE_ROOT, or a folder `reference` beside this repository) and the oracle/_ref build:
 
     python tests/golden/make_golden.py
 
@@ -25,10 +25,11 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
-REF = os.environ.get("HECATE_REFERENCE_ROOT", "/root/reference")
 
 from hecate_b200 import synth  # noqa: E402
 from oracle import build, oracle as O  # noqa: E402
+
+REF = build.ref_root() or ""
 
 # the seeded engine jobs, shared with tests/test_oracle_golden.py
 JOB_SEED, JOB_LO, JOB_EXPERTS = 11, 144, 6
