@@ -27,9 +27,24 @@ def test_host_only_entry_points():
     assert L.hmoe_version() >= 100
     assert L.hmoe_decode_ws_bytes(ctypes.c_int(6144), ctypes.c_int(2048)) > 4_000_000
     assert L.hmoe_router_ws_bytes(ctypes.c_int(16), ctypes.c_int(256)) >= 16 * 256 * 4
+    # the built-in scratch of hmoe_decode_noalloc is 5 MiB: the benchmark shape fits, the next larger ones do not
+    five = 5 << 20
+    assert L.hmoe_decode_ws_bytes(ctypes.c_int(6144), ctypes.c_int(2048)) <= five
+    assert L.hmoe_decode_ws_bytes(ctypes.c_int(6144), ctypes.c_int(2304)) > five
+    assert L.hmoe_decode_ws_bytes(ctypes.c_int(8192), ctypes.c_int(2304)) > five
     # argument errors are reported as codes with a message, never thrown
     rc = L.hmoe_combine(None, None, None, ctypes.c_int64(4), None, None)
     assert rc == 1 and b"hmoe_combine" in L.hmoe_last_error()
+
+
+def test_noalloc_size_check_needs_no_gpu():
+    """Shapes beyond the built-in scratch are refused before anything touches a device."""
+    from hecate_b200 import _lib
+    L = _lib.lib()
+    st = _lib.LayerStruct()
+    st.H, st.I, st.n_experts, st.topk, st.group, st.scale_dtype = 6144, 2304, 1, 8, 0, 2
+    rc = L.hmoe_decode_noalloc(ctypes.byref(st), None, 0, None, None, 1, 0, 1, 0, None, None, None)
+    assert rc == 4 and b"built-in scratch" in L.hmoe_last_error()
 
 
 def test_layer_struct_matches_header():

@@ -71,3 +71,34 @@ def test_norm_route_equals_norm_then_router(R, H, wbf, with_y):
     moe.norm_route(y, r, nw, xn2, wt, bias, sel2, rw2, topk, 2.5, 1e-6, r_out=r2)
     assert torch.equal(r2, r1) and torch.equal(xn2, xn1)
     assert torch.equal(sel2, sel1) and torch.equal(rw2.view(torch.int16), rw1.view(torch.int16))
+
+
+@pytest.mark.parametrize("R,H,wbf,with_y,cbias", [(16, 6144, True, True, 0.0), (4, 6144, False, False, 1.0), (7, 1024, True, True, 0.0)])
+def test_norm_route_against_the_checker(oracle, R, H, wbf, with_y, cbias):
+    """hmoe_norm_router against the CPU checker alone (no other kernel of this library involved): the residual sum bit for
+    bit and the normalised rows to one fp16 ulp against the checker's combine_norm restatement; the selection and the fp16
+    weights bit for bit against the checker's router applied to the rows the kernel wrote."""
+    import torch
+    from hecate_b200 import moe
+    dev = torch.device("cuda:0")
+    E, topk, scale = 256, 8, 2.5
+    g = lambda s, n: synth.normal(33, s, n).astype(np.float32)
+    r = g(1, R * H).reshape(R, H) * 2.0
+    y = g(2, R * H).reshape(R, H) * 0.5 if with_y else None
+    nw_t = torch.from_numpy(1.0 + 0.1 * g(3, H)).to(dev).to(torch.bfloat16 if wbf else torch.float16)
+    wt_t = torch.from_numpy(synth.router_weight(5, 0, E, H)).to(dev).to(torch.bfloat16 if wbf else torch.float16)
+    bias = synth.router_bias(5, 0, E, 0.05)
+    xn = torch.empty(R, H, dtype=torch.float16, device=dev); r_out = torch.empty(R, H, device=dev)
+    sel = torch.empty(R, topk, dtype=torch.int64, device=dev); rw = torch.empty(R, topk, dtype=torch.float16, device=dev)
+    moe.norm_route(None if y is None else torch.from_numpy(y).to(dev), torch.from_numpy(r).to(dev), nw_t, xn, wt_t, torch.from_numpy(bias).to(dev),
+                   sel, rw, topk, scale, 1e-6, cbias=cbias, r_out=r_out)
+    torch.cuda.synchronize()
+    rn, xn_ref, _ = oracle.combine_norm(None, None, y if y is not None else np.zeros_like(r), None, r, nw_t.float().cpu().numpy(), 1e-6, cbias, 1.0)
+    assert np.array_equal(r_out.cpu().numpy(), rn)
+    got = xn.cpu().numpy().astype(np.float32)
+    ulp = np.maximum(np.abs(xn_ref.astype(np.float32)), 2.0 ** -14) * 2.0 ** -10
+    assert np.all(np.abs(got - xn_ref.astype(np.float32)) <= ulp)
+    bits = lambda t: t.cpu().view(torch.int16).numpy().view(np.uint16)
+    osel, orw = oracle.router(bits(xn), 0, bits(wt_t), int(wbf), bias, topk, scale)
+    assert np.array_equal(osel, sel.cpu().numpy())
+    assert np.array_equal(orw.view(np.uint16), bits(rw))

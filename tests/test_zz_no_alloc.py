@@ -28,12 +28,15 @@ def _call_noalloc(tabs, x, sel, rw, y, status_dev, act_quant):
                                  C.c_void_p(torch.cuda.current_stream(x.device).cuda_stream))
 
 
-@pytest.mark.parametrize("group,act_quant", [(128, False), (0, True)])
-def test_noalloc_matches_workspace_entry_point_twice(group, act_quant):
+# (512, 256): the register-resident streaming kernels with one column chunk; (512, 2176): a shape that fits the built-in scratch
+# but takes the other pair of kernels (I > 2048); (6144, 2048): the largest shape the scratch holds (three column chunks,
+# 4.7 of the 5 MiB), with a few experts
+@pytest.mark.parametrize("H,I,E,group,act_quant", [(512, 256, 16, 128, False), (512, 256, 16, 0, True), (512, 2176, 8, 128, True),
+                                                   (6144, 2048, 10, 128, False)])
+def test_noalloc_matches_workspace_entry_point_twice(H, I, E, group, act_quant):
     import torch
     from hecate_b200 import moe
     dev = torch.device("cuda:0")
-    H, I, E = 512, 256, 16
     hl = HostLayer(0, 0, H, I, range(E), group, True)
     tabs = hl.upload(dev)
     ws = moe.decode_workspace(H, I, dev)
