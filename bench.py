@@ -1,22 +1,32 @@
 #!/usr/bin/env python
-"""Benchmark of the MoE expert hot path on B200: one decode MoE layer call per step.
+"""Benchmark of the MoE expert hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (the decode configuration of the benchmark definition): hidden 6144, 256 routed experts, top-8 sigmoid/bias router,
-one shared expert, SwiGLU experts gate/up [2048 x 6144] and down [6144 x 2048] in packed int4 with a bf16 scale per 128
-input columns, decode batch of 8 tokens each with one MTP draft = 16 rows. Inputs are synthetic (seeded): codes uniform,
-scales lognormal(-4, 0.5), activations N(0, 1) in bf16, router weight N(0, 0.02) in bf16.
+One MoE layer of the benchmark definition: hidden 6144, 256 routed experts, top-8 sigmoid/bias router, one shared expert,
+SwiGLU experts gate/up [2048 x 6144] and down [6144 x 2048] in packed int4 with a bf16 scale per 128 input columns. Inputs are
+synthetic (seeded): codes uniform, scales lognormal(-4, 0.5), activations N(0, 1) in bf16, router weight N(0, 0.02) in bf16.
 
-A step = router -> prepare -> gate_up (+ SiLU * up * weight) -> down -> combine into the fp32 layer output. `value` is rows/s
-with inputs resident in HBM; `e2e` is the same call chain fed from pinned host memory with the host<->device copies inside
-the timed region. Consecutive steps use different input batches (8 in a ring), so each step selects a different ~100 of the
-256 experts: about 2 GB of the 4.85 GB layer is streamed per step, far more than the 126 MB L2.
+The headline line is the DECODE configuration (8 tokens x (1 + 1 MTP draft) = 16 rows): a step = router -> prepare -> gate_up
+(+ SiLU * up * weight) -> down -> combine into the fp32 layer output. `value` is rows/s with inputs resident in HBM, `e2e` the
+same call chain fed from pinned host memory with the host<->device copies inside the timed region. Consecutive steps use
+different input batches (8 in a ring), so each step streams a different ~2 GB of the 4.85 GB layer, far more than the L2.
+
+The same JSON line carries, as further objects:
+  prefill        N = 1: M = 8192 tokens, Zipf(1.1) expert popularity (permute -> gather -> grouped gate_up GEMM -> grouped down
+                 GEMM on tcgen05); N > 1: M = 32768 tokens expert-parallel with uniform routing, and `prefill_zipf` with Zipf(1.3)
+  parity_check   outputs of THIS layer (a few decode rows, a few prefill tokens, both activation modes) against the CPU checker,
+                 computed outside the timed regions; N > 1: the peer-memory combine against the NCCL arm
+  act_quant      the same steps timed in the mode that reproduces the CPU engine's int8 activation round trips
+  reference_gpu  the reference's own GPU kernels (baseline/_ref, built unchanged for sm_100a) on the same device and inputs, in
+                 their format (fp16 activations, one fp32 scale per row, routed experts only), beside this library in that format
+  cpu_baseline   the reference CPU engine on the host cores (config 2 as two 8-row jobs + the shared expert, and config 1)
 
 `--impl reference` times the reference's own CPU expert engine (oracle/_ref, built from the reference source) on the host
-cores, on a bounded sample of the same workload.
+cores, on a bounded sample of the same workload. `--mode decode|prefill` runs one arm alone (profiling).
 """
 import argparse
+import ctypes as C
 import json
 import os
 import sys
@@ -34,20 +44,29 @@ PER_MATRIX = I * H // 2                                  # packed bytes of one m
 SCALE_BYTES = (2 * I * (H // GROUP) + H * (I // GROUP)) * 2
 EXPERT_BYTES = 3 * PER_MATRIX + SCALE_BYTES              # 19,464,192
 GATE_UP_BYTES = 2 * PER_MATRIX + 2 * I * (H // GROUP) * 2
+PICK_FLOP = 2.0 * 3 * I * H                              # 75,497,472 per (token, expert) pair
 NBATCH = 8
 METRIC = "moe_layer_decode_rows_per_s"
 UNIT = "rows/s"
 WORKLOAD = "decode M=8 tokens x (1 + 1 MTP draft) = 16 rows, H=6144, 256 experts top-8 + shared, int4 g128 bf16 scales"
+# DRAM traffic of one gate_up launch relative to its algorithmic bytes (dram__bytes_read + write of an ncu capture of the reduced
+# case --experts 64; traffic grows in proportion to the experts streamed). Re-derive when the capture is refreshed.
+GATE_UP_TRAFFIC_RATIO = 0.982
+# bars: the benchmark definition's against the CPU engine (int8 activation mode; errors normalised as max|a-b| / max|b| and
+# mean|a-b| / mean|b|) and the reference GPU kernels' own gate (norm-relative, tools/quant/test_moe4_rtx.py:70) otherwise
+MAX_REL, MEAN_ABS, NORM_REL = 1e-2, 1e-3, 2e-3
 
 
-def measured_peaks():
+def peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
         try:
-            return float(json.load(open(p))["hbm_gbs"]), "measured"
+            d = json.load(open(p))
+            return {"hbm": float(d["hbm_gbs"]), "bf16": float(d["bf16_tflops"]), "bf16_sustained": float(d["bf16_tflops_sustained"]),
+                    "kind": "measured"}
         except Exception:
             pass
-    return 6650.0, "fallback"
+    return {"hbm": 6650.0, "bf16": 1590.0, "bf16_sustained": 1400.0, "kind": "fallback"}
 
 
 class ClockSampler:
@@ -99,48 +118,76 @@ class ClockSampler:
                 "reasons": sorted(self.reasons)}
 
 
+def errors(got, ref):
+    """(max-rel, mean-abs, norm-rel), the first two normalised: max|a-b| / max|b| and mean|a-b| / mean|b|."""
+    got = np.asarray(got, dtype=np.float64); ref = np.asarray(ref, dtype=np.float64)
+    d = np.abs(got - ref)
+    return (float(d.max() / max(np.abs(ref).max(), 1e-30)), float(d.mean() / max(np.abs(ref).mean(), 1e-30)),
+            float(np.linalg.norm(got - ref) / max(np.linalg.norm(ref), 1e-30)))
+
+
 # ----------------------------------------------------------------------------------------------------------------------
-def cpu_reference_arm(steps, warmup, seed=0):
-    """Times the reference CPU engine (or, without it, this repository's restatement) on 8-row jobs of the workload."""
+# the reference CPU engine on the host cores
+def cpu_reference_arm(jobs, warmup, seed=0, variants=("avx2", "vnni")):
+    """Times the reference CPU engine (oracle/_ref; without it, this repository's restatement) on the decode workload in the
+    engine's own format (row-major int4, one fp32 scale per row, 8 rows and 8 picks per row and job):
+      config 2  the 16 rows as two 8-row jobs of the routed experts plus, for each, one job that applies the shared expert to the
+                same 8 rows (one pick of weight 1: the engine reads 8 picks per row, so the 9th pick is a job of its own);
+                value = 16 rows / (sum of the four median job times)
+      config 1  one row: a job of its 8 picks plus a one-pick job of the shared expert
+    Routing is uniform random top-8 of 256 (what the seeded router produces); the weights are seeded random bytes."""
     from oracle import oracle as O
     from hecate_b200 import synth
     cores = os.cpu_count() or 1
     threads = max(1, min(60, cores - 2))
-    sel, rw = synth.zipf_routing(seed, 0, 8, E, TOPK, 0.0)
-    x = synth.activations(seed, 0, 8, H).astype(np.float16)
+    sel, rw = synth.zipf_routing(seed, 0, ROWS, E, TOPK, 0.0)
+    x = synth.activations(seed, 0, ROWS, H).astype(np.float16)
     ids = sorted(set(int(e) for e in sel.reshape(-1)))
     remap = {e: i for i, e in enumerate(ids)}
     sel_local = np.vectorize(remap.get)(sel).astype(np.int64)
+    S = len(ids)                                          # local id of the shared expert
+    rng = np.random.default_rng(seed)
     experts = []
-    for e in ids:                       # row-major int4 + one fp32 scale per row: the engine's own format
-        mk = lambda kind, n: synth.rand_bytes(seed, synth.stream_id(0, kind, e), n).reshape(-1)
-        sc = lambda kind, N, K: synth.scales(seed, 0, kind, e, N, K, K)
-        experts.append(O.Expert(mk("gate_q", I * H // 2).reshape(I, H // 2), mk("up_q", I * H // 2).reshape(I, H // 2),
-                                mk("down_q", H * I // 2).reshape(H, I // 2), sc("gate_s", I, H), sc("up_s", I, H),
-                                sc("down_s", H, I), H, I, packed=False))
-    times = []
-    if O.ref_available():
-        kind = "reference"
-        eng = O.RefEngine(experts, 0, threads=threads, core0=0)
+    for _ in range(S + 1):
+        q = lambda N, K: rng.integers(0, 256, size=(N, K // 2), dtype=np.uint8)
+        sc = lambda N: np.exp(-4.0 + 0.5 * rng.standard_normal(N)).astype(np.float32).reshape(1, N)
+        experts.append(O.Expert(q(I, H), q(I, H), q(H, I), sc(I), sc(I), sc(H), H, I, packed=False))
+    sh_sel = np.full((8, TOPK), -1, dtype=np.int64); sh_sel[:, 0] = S
+    sh_rw = np.zeros((8, TOPK), dtype=np.float16); sh_rw[:, 0] = 1.0
+    jobs_c2 = [(x[0:8], sel_local[0:8], rw[0:8]), (x[0:8], sh_sel, sh_rw), (x[8:16], sel_local[8:16], rw[8:16]), (x[8:16], sh_sel, sh_rw)]
+    jobs_c1 = [(x[0:1], sel_local[0:1], rw[0:1]), (x[0:1], sh_sel[0:1], sh_rw[0:1])]
+    out = {"cores": threads, "unit": UNIT, "distinct_routed_experts": S,
+           "sample": f"{jobs} timed repetitions of every job (median ISSUE->DONE time per job, summed): config 2 = two 8-row jobs of the routed "
+                     f"experts ({S} distinct) + two 8-row one-pick jobs of the shared expert; config 1 = one row, 8 picks + the shared expert; "
+                     f"engine format (row-major int4, fp32 scale per row)"}
+
+    def run_engine(variant):
+        eng = O.RefEngine(experts, 0, threads=threads, core0=0, variant=variant)
         try:
-            for i in range(warmup + steps):
-                _, dt = eng.job(x, sel_local, rw)
-                if i >= warmup:
-                    times.append(dt)
+            med = lambda job: float(np.median([eng.job(*job)[1] for _ in range(warmup + jobs)][warmup:]))
+            t2 = [med(j) for j in jobs_c2]
+            t1 = [med(j) for j in jobs_c1]
         finally:
             eng.stop()
+        return {"value": ROWS / sum(t2), "ms_16_rows": sum(t2) * 1e3, "ms_per_job": [t * 1e3 for t in t2],
+                "config1_us_per_token": sum(t1) * 1e6, "config1_rows_per_s": 1.0 / sum(t1)}
+
+    done = {}
+    for v in variants:
+        if O.ref_available(v):
+            done[v] = run_engine(v)
+    if done:
+        best = max(done, key=lambda v: done[v]["value"])
+        out.update(kind="reference", value=done[best]["value"], ms_16_rows=done[best]["ms_16_rows"], variant=best, variants=done,
+                   variant_note="avx2 / vnni / scalar: the AArch64 SDOT and FMLA of the engine's inner loop mapped to AVX2 widening multiply-adds, "
+                                "to one AVX-512-VNNI instruction, or to scalar loops; results are bit-identical")
     else:
-        kind = "port"
-        threads = O.threads()
-        for i in range(warmup + steps):
-            t0 = time.perf_counter()
-            O.moe_forward(H, I, 0, x, sel_local, rw, 0, experts)
-            if i >= warmup:
-                times.append(time.perf_counter() - t0)
-    t = float(np.median(times))
-    return {"value": 8.0 / t, "unit": UNIT, "cores": threads, "kind": kind, "ms_per_job": t * 1e3,
-            "sample": f"{len(times)} jobs of 8 rows ({len(ids)} distinct routed experts, per-row fp32 scales, no shared expert), "
-                      f"median ISSUE->DONE time"}
+        t0 = time.perf_counter()
+        for _ in range(max(1, jobs // 4)):
+            O.moe_forward(H, I, 0, x, sel_local, rw, 0, experts[:S], experts[S])
+        t = (time.perf_counter() - t0) / max(1, jobs // 4)
+        out.update(kind="port", value=ROWS / t, cores=O.threads(), ms_16_rows=t * 1e3)
+    return out
 
 
 def run_reference(args):
@@ -148,31 +195,57 @@ def run_reference(args):
     if rank != 0:
         return
     steps = max(1, min(args.steps, 50))
-    cb = cpu_reference_arm(steps, max(1, min(args.warmup, 5)))
+    cb = cpu_reference_arm(steps, max(1, min(args.warmup, 5)), variants=("avx2", "vnni", "scalar") if args.all_variants else ("avx2", "vnni"))
     line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
-            "warmup": args.warmup, "ms_per_step": cb["ms_per_job"], "higher_is_better": True, "scaling": "strong",
+            "warmup": args.warmup, "ms_per_step": cb["ms_16_rows"], "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "int4 x int8 -> fp32", "data": "synthetic",
-            "config": {"workload": WORKLOAD + " [CPU sample: one 8-row job per step]"},
+            "config": {"workload": WORKLOAD + " [reference CPU engine: two 8-row jobs + the shared expert, fp32 scale per row]"},
             "cpu_baseline": cb, "e2e": {"value": cb["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
 
 # ----------------------------------------------------------------------------------------------------------------------
-def build_layer(dev, seed, experts, torch, moe):
-    """Seeded synthetic experts resident in HBM: `experts` routed experts + one shared expert."""
-    from hecate_b200 import synth
-    n = len(experts)
-    pool = torch.empty((n + 1) * 3 * PER_MATRIX, dtype=torch.uint8, device=dev)
-    moe.fill_bytes(pool, seed, synth.stream_id(0, "gate_q", 0))
-    view = lambda e, k: pool[(e * 3 + k) * PER_MATRIX:(e * 3 + k + 1) * PER_MATRIX]
-    g = torch.Generator(device=dev); g.manual_seed(seed + 1)
-    sc = lambda N, K: (torch.randn(n + 1, N // 64, K // GROUP, 64, device=dev, generator=g) * 0.5 - 4.0).exp().to(torch.bfloat16)
-    gs, us, ds = sc(I, H), sc(I, H), sc(H, I)          # device order [N/64][K/128][64] per expert
-    shared = (view(n, 0), view(n, 1), view(n, 2), gs[n], us[n], ds[n])
-    tabs = moe.ExpertTables(H, I, TOPK, [view(e, 0) for e in range(n)], [view(e, 1) for e in range(n)],
-                            [view(e, 2) for e in range(n)], list(gs[:n]), list(us[:n]), list(ds[:n]), group=GROUP, shared=shared, device=dev)
-    tabs.keep.append(pool)
-    return tabs
+# the layer
+class Layer:
+    """Seeded synthetic experts resident in HBM: n routed experts + one shared expert, in the benchmark's format (bf16 scale per
+    128 columns) and, over the same packed codes, in the reference's format (one fp32 scale per row; routed experts only)."""
+
+    def __init__(self, dev, seed, n, rowscale=False):
+        import torch
+        from hecate_b200 import moe, synth
+        self.n, self.dev = n, dev
+        self.pool = torch.empty((n + 1) * 3 * PER_MATRIX, dtype=torch.uint8, device=dev)
+        moe.fill_bytes(self.pool, seed, synth.stream_id(0, "gate_q", 0))
+        view = self.view
+        g = torch.Generator(device=dev); g.manual_seed(seed + 1)
+        sc = lambda N, K: (torch.randn(n + 1, N // 64, K // GROUP, 64, device=dev, generator=g) * 0.5 - 4.0).exp().to(torch.bfloat16)
+        self.gs, self.us, self.ds = sc(I, H), sc(I, H), sc(H, I)          # device order [N/64][K/128][64] per expert
+        shared = (view(n, 0), view(n, 1), view(n, 2), self.gs[n], self.us[n], self.ds[n])
+        self.tabs = moe.ExpertTables(H, I, TOPK, [view(e, 0) for e in range(n)], [view(e, 1) for e in range(n)],
+                                     [view(e, 2) for e in range(n)], list(self.gs[:n]), list(self.us[:n]), list(self.ds[:n]), group=GROUP,
+                                     shared=shared, device=dev)
+        self.tabs.keep.append(self.pool)
+        self.tabs0 = None
+        if rowscale:
+            rs = lambda N: (torch.randn(n, N, device=dev, generator=g) * 0.5 - 4.0).exp()
+            self.rs = (rs(I), rs(I), rs(H))
+            self.tabs0 = moe.ExpertTables(H, I, TOPK, [view(e, 0) for e in range(n)], [view(e, 1) for e in range(n)],
+                                          [view(e, 2) for e in range(n)], list(self.rs[0]), list(self.rs[1]), list(self.rs[2]), group=0,
+                                          shared=None, device=dev)
+            self.tabs0.keep.append(self.pool)
+
+    def view(self, e, k):
+        return self.pool[(e * 3 + k) * PER_MATRIX:(e * 3 + k + 1) * PER_MATRIX]
+
+    def host_experts(self, O, ids):
+        """Host copies of experts `ids` (n = the shared expert) for the CPU checker, from the device tensors."""
+        from hecate_b200 import layout
+        out = []
+        for e in ids:
+            q = [self.view(e, k).cpu().numpy() for k in range(3)]
+            s = [layout.group_scales_logical(t[e].float().cpu().numpy(), N) for t, N in ((self.gs, I), (self.us, I), (self.ds, H))]
+            out.append(O.Expert(q[0], q[1], q[2], s[0], s[1], s[2], H, I))
+        return out
 
 
 def make_graphed(step, xs, torch, moe, use_graph):
@@ -195,27 +268,37 @@ def make_graphed(step, xs, torch, moe, use_graph):
     return (lambda b: graphs[b].replay()), per_step
 
 
-def run_ours(args):
-    import torch
-    import torch.distributed as dist
-    from hecate_b200 import moe, synth
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-        from hecate_b200 import ep
-        return ep.bench_decode(args, world, rank, dev)
+def timed(torch, run, steps, nb):
+    """ms per step over `steps` calls of run(i % nb), CUDA events on the current stream, synchronised on both sides."""
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    ev0.record()
+    for i in range(steps):
+        run(i % nb)
+    ev1.record()
+    torch.cuda.synchronize()
+    return ev0.elapsed_time(ev1) / steps
+
+
+def oracle_rows(O, layer, x_rows, sel_rows, rw_rows, mode):
+    """The CPU checker's output for a few rows of THIS layer (weights copied back from the device). x_rows float32 (bf16 values)."""
+    ids = sorted(set(int(e) for e in sel_rows.reshape(-1)))
+    remap = {e: i for i, e in enumerate(ids)}
+    loc = np.vectorize(remap.get)(sel_rows).astype(np.int64)
+    hx = layer.host_experts(O, ids + [layer.n])
+    return O.moe_forward(H, I, GROUP, x_rows.astype(np.float16), loc, rw_rows, 0, hx[:-1], hx[-1], mode=mode)
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# N = 1
+def decode_arm(args, dev, layer, torch, moe, synth, O):
     steps, warmup = args.steps, max(3, args.warmup)
-    E = args.experts
-    tabs = build_layer(dev, 0, list(range(E)), torch, moe)
-    wt = torch.from_numpy(synth.router_weight(0, 0, E, H)).to(dev).to(torch.bfloat16)
-    bias = torch.zeros(E, dtype=torch.float32, device=dev)
-    xs_host = [torch.from_numpy(synth.activations(b, 0, ROWS, H)).to(torch.bfloat16).pin_memory() for b in range(NBATCH)]
+    n_exp = layer.n
+    tabs = layer.tabs
+    wt = torch.from_numpy(synth.router_weight(0, 0, n_exp, H)).to(dev).to(torch.bfloat16)
+    bias = torch.zeros(n_exp, dtype=torch.float32, device=dev)
+    xs_np = [synth.activations(b, 0, ROWS, H) for b in range(NBATCH)]
+    xs_host = [torch.from_numpy(x).to(torch.bfloat16).pin_memory() for x in xs_np]
     xs = [x.to(dev) for x in xs_host]
     sel = torch.empty(ROWS, TOPK, dtype=torch.int64, device=dev)
     rw = torch.empty(ROWS, TOPK, dtype=torch.float16, device=dev)
@@ -224,17 +307,18 @@ def run_ours(args):
     f = torch.zeros(ROWS, H, dtype=torch.float32, device=dev)
     x_in = torch.empty(ROWS, H, dtype=torch.bfloat16, device=dev)
     f_host = torch.empty(ROWS, H, dtype=torch.float32).pin_memory()
+    aq = [False]
 
     def step(x):
         moe.router_fused(x, wt, bias, None, None, sel, rw, TOPK, 1.0)
-        moe.decode(tabs, x, sel, rw, y, ws)
+        moe.decode(tabs, x, sel, rw, y, ws, act_quant=aq[0])
         moe.moe4_combine(f, 0, y, ROWS, 0)
 
-    # distinct experts per batch (for the algorithmic byte count)
-    distinct = []
-    for b in range(NBATCH):
+    distinct, routes = [], []
+    for b in range(NBATCH):                  # distinct experts per batch (for the algorithmic byte count) and the routing itself
         moe.router_fused(xs[b], wt, bias, None, None, sel, rw, TOPK, 1.0)
         distinct.append(int(torch.unique(sel).numel()))
+        routes.append((sel.cpu().numpy().copy(), rw.cpu().numpy().copy()))
     for i in range(warmup):
         step(xs[i % NBATCH])
     torch.cuda.synchronize()
@@ -243,40 +327,26 @@ def run_ours(args):
     run_step, launches_per_step = make_graphed(step, xs, torch, moe, not args.no_graph)
     for i in range(warmup):
         run_step(i % NBATCH)
-    torch.cuda.synchronize()
-    phase = np.zeros(3)
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as cs:
-        torch.cuda.synchronize()
-        ev0.record()
-        for i in range(steps):
-            run_step(i % NBATCH)
-        ev1.record()
-        torch.cuda.synchronize()
-        ms = ev0.elapsed_time(ev1)
+    with ClockSampler(dev.index) as cs:
+        ms_per_step = timed(torch, run_step, steps, NBATCH)
         if len(cs.samples) < 5:           # very short runs: keep the same load going so the clock record is not empty
             t_end = time.time() + 0.4
             while time.time() < t_end:
                 run_step(0); torch.cuda.synchronize()
     launches = launches_per_step * steps
-    moe.set_profiling(True)
     # kernel durations: a second pass over the same steps launched eagerly back to back, CUDA events around each kernel on
     # its stream (recorded by the library into a ring); read after the pass
+    moe.set_profiling(True)
     for i in range(min(steps, 32)):
         step(xs[i % NBATCH])
     torch.cuda.synchronize()
     phase = np.array(moe.decode_phase_times())
     moe.set_profiling(False)
-    status = moe.ws_status(ws)
     mean_d = float(np.mean([distinct[i % NBATCH] for i in range(steps)]))
     gate_up_bytes = (mean_d + 1) * GATE_UP_BYTES
-    layer_bytes = (mean_d + 1) * EXPERT_BYTES + E * H * 2 + ROWS * H * 6
-    peak, peak_kind = measured_peaks()
+    layer_bytes = (mean_d + 1) * EXPERT_BYTES + n_exp * H * 2 + ROWS * H * 6
+    pk = peaks()
     achieved = gate_up_bytes / (phase[1] * 1e-3) / 1e9
-    # DRAM traffic of one gate_up launch: dram__bytes_read + write of an ncu capture of the reduced case (--experts 64: 709.4 MB
-    # for 722.3 MB of algorithmic bytes, profiles/decode_stream_kernels_experts64.md), scaled to this launch by the experts it streams
-    traffic = 0.982 * gate_up_bytes
-    ms_per_step = ms / steps
 
     # end to end: host buffers in, host buffer out, every step. The host->device copy of the step's rows, the layer call and
     # the device->host copy of its result are captured as one graph per input batch (the same public calls, replayed), and the
@@ -293,122 +363,434 @@ def run_ours(args):
         torch.cuda.synchronize()
     e2e_s = (time.perf_counter() - t0) / steps
 
-    cb = cpu_reference_arm(20, 3) if not args.no_cpu else None
+    # the parity mode (the CPU engine's int8 activation round trips), timed the same way
+    aq[0] = True
+    run_q, _ = make_graphed(step, xs, torch, moe, not args.no_graph)
+    for i in range(3):
+        run_q(i % NBATCH)
+    ms_q = timed(torch, run_q, steps, NBATCH)
+    aq[0] = False
+
+    # parity on this very layer, outside the timed regions: the router's selection bit for bit, two rows of batch 0 in both modes
+    parity = {}
+    if O is not None:
+        bits = lambda t: t.cpu().view(torch.int16).numpy().view(np.uint16)
+        osel, orw = O.router(bits(xs[0]), 1, bits(wt), 1, None, TOPK, 1.0)
+        s0, w0 = routes[0]
+        parity["router_bit_exact"] = bool(np.array_equal(osel, s0) and np.array_equal(orw.view(np.uint16), w0.view(np.uint16)))
+        rows = [0, 9]
+        for mode_name, q in (("act_quant1_vs_cpu_engine", True), ("act_quant0_vs_exact", False)):
+            y.zero_()
+            moe.decode(tabs, xs[0], torch.from_numpy(s0).to(dev), torch.from_numpy(w0).to(dev), y, ws, act_quant=q)
+            got = y[rows].cpu().numpy(); y.zero_()
+            ref = oracle_rows(O, layer, xs_np[0][rows], s0[rows], w0[rows], 0 if q else 1)
+            e = errors(got, ref)
+            parity[mode_name] = {"max_rel": e[0], "mean_abs": e[1], "norm_rel": e[2], "rows": rows,
+                                 "ok": bool(e[0] < MAX_REL and e[1] < MEAN_ABS) if q else bool(e[2] < NORM_REL)}
+    status = moe.ws_status(ws)
     line = {
         "metric": METRIC, "value": ROWS / (ms_per_step * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int4 x fp16 -> fp32",
         "data": "synthetic",
-        "config": {"workload": WORKLOAD if E == 256 else WORKLOAD + f" [reduced to {E} experts]", "launch": "eager" if args.no_graph else "cuda graph per input batch", "l2": "inputs larger than L2: ~2 GB of weights streamed per step, 8 input batches in a ring",
+        "config": {"workload": WORKLOAD if n_exp == 256 else WORKLOAD + f" [reduced to {n_exp} experts]",
+                   "launch": "eager" if args.no_graph else "cuda graph per input batch",
+                   "l2": "inputs larger than L2: ~2 GB of weights streamed per step, 8 input batches in a ring",
                    "distinct_experts_per_step": mean_d},
         "us_per_layer": ms_per_step * 1e3,
         "layer_hbm_gbs": layer_bytes / (ms_per_step * 1e-3) / 1e9,
-        "layer_hbm_frac": layer_bytes / (ms_per_step * 1e-3) / 1e9 / peak,
+        "layer_hbm_frac": layer_bytes / (ms_per_step * 1e-3) / 1e9 / pk["hbm"],
         "phase_us": {"prepare": phase[0] * 1e3, "gate_up": phase[1] * 1e3, "down": phase[2] * 1e3},
-        "roofline": {"bound": "hbm", "kernel": "decode_stream_kernel (gate_up)", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "peak_kind": peak_kind, "traffic": traffic,
+        "roofline": {"bound": "hbm", "kernel": "decode_stream_kernel (gate_up)", "achieved": achieved, "peak": pk["hbm"], "unit": "GB/s",
+                     "frac": achieved / pk["hbm"], "peak_kind": pk["kind"], "traffic": GATE_UP_TRAFFIC_RATIO * gate_up_bytes,
                      "algorithmic_bytes_per_launch": gate_up_bytes},
         "e2e": {"value": ROWS / e2e_s, "unit": UNIT, "h2d_bytes_per_step": ROWS * H * 2, "d2h_bytes_per_step": ROWS * H * 4,
                 "us_per_layer": e2e_s * 1e6},
+        "act_quant": {"decode_us_per_layer": ms_q * 1e3, "decode_vs_default": ms_q / ms_per_step},
+        "parity_check": {"decode": parity},
         "gpu_launches": int(launches), "device_status": int(status), "clocks": cs.summary(),
     }
-    if cb:
-        line["cpu_baseline"] = cb
-    print(json.dumps(line))
+    return line, dict(wt=wt, bias=bias, xs=xs, routes=routes)
 
 
-def run_prefill(args):
+def prefill_arm(args, dev, layer, torch, moe, synth, O, R=8192, zipf=1.1):
     """Prefill configuration: M = 8192 tokens, Zipf(1.1) expert popularity, top-8 without replacement, + shared expert.
     A step = permute -> gather -> grouped gate_up GEMM (+ SiLU epilogue) -> grouped down GEMM (+ scatter-add epilogue).
     value = TFLOP/s over the algorithmic flops 2 * (8 R + R) * 37,748,736 (padding columns not counted)."""
-    import torch
-    from hecate_b200 import moe, synth
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
-        from hecate_b200 import ep
-        return ep.bench_prefill(args, world, int(os.environ.get("RANK", "0")), dev)
-    E, R = args.experts, args.rows
-    steps, warmup = min(args.steps, 200), max(3, min(args.warmup, 10))
-    tabs = build_layer(dev, 0, list(range(E)), torch, moe)
+    n_exp, tabs = layer.n, layer.tabs
+    steps, warmup = max(1, min(args.steps, 50)), max(3, min(args.warmup, 5))
     NB = 2
-    xs = [torch.from_numpy(synth.activations(b, 0, R, H)).to(torch.bfloat16).to(dev) for b in range(NB)]
-    routes = [synth.zipf_routing(10 + b, 0, R, E, TOPK, args.zipf) for b in range(NB)]
+    xs_np = [synth.activations(20 + b, 0, R, H) for b in range(NB)]
+    xs = [torch.from_numpy(x).to(torch.bfloat16).to(dev) for x in xs_np]
+    routes = [synth.zipf_routing(10 + b, 0, R, n_exp, TOPK, zipf) for b in range(NB)]
     sels = [torch.from_numpy(r[0]).to(dev) for r in routes]; rws = [torch.from_numpy(r[1]).to(dev) for r in routes]
-    ws = moe.prefill_workspace(R, TOPK, E, H, I, dev)
+    ws = moe.prefill_workspace(R, TOPK, n_exp, H, I, dev)
     out = torch.zeros(R, H, dtype=torch.float32, device=dev)
     x_host = xs[0].cpu().pin_memory(); out_host = torch.empty(R, H, dtype=torch.float32).pin_memory()
     x_in = torch.empty_like(xs[0])
+    aq = [False]
+    wsq = [ws]
 
     def step(i):
         out.zero_()
-        moe.prefill(tabs, xs[i % NB], sels[i % NB], rws[i % NB], out, ws)
+        moe.prefill(tabs, xs[i % NB], sels[i % NB], rws[i % NB], out, wsq[0], act_quant=aq[0])
 
     for i in range(warmup):
         step(i)
-    torch.cuda.synchronize()
     l0 = moe.launch_count()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as cs:
-        ev0.record()
-        for i in range(steps):
-            step(i)
-        ev1.record()
-        torch.cuda.synchronize()
-        ms = ev0.elapsed_time(ev1) / steps
+    with ClockSampler(dev.index) as cs:
+        ms = timed(torch, step, steps, NB)
     launches = moe.launch_count() - l0
-    status = moe.ws_status(ws)
+    n2 = max(1, min(steps, 10))
+    torch.cuda.synchronize()
     t0 = time.perf_counter()
-    for i in range(min(steps, 20)):
+    for i in range(n2):
         x_in.copy_(x_host, non_blocking=True); out.zero_()
         moe.prefill(tabs, x_in, sels[0], rws[0], out, ws)
         out_host.copy_(out, non_blocking=True); torch.cuda.synchronize()
-    e2e_s = (time.perf_counter() - t0) / min(steps, 20)
-    flop = 2.0 * (TOPK * R + R) * (3 * I * H)
-    counts = np.bincount(routes[0][0].reshape(-1), minlength=E)
-    peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
-    peak = float(peaks.get("bf16_tflops_sustained", 1400.0)); kind = "measured (sustained)" if peaks else "fallback"
+    e2e_s = (time.perf_counter() - t0) / n2
+    flop = (TOPK * R + R) * PICK_FLOP
+    counts = np.bincount(routes[0][0].reshape(-1), minlength=n_exp)
+    pk = peaks()
     tf = flop / (ms * 1e-3) / 1e12
-    print(json.dumps({
-        "metric": "moe_prefill_expert_gemm_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
-        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int4 -> fp16 x fp16 -> fp32 (tcgen05)",
-        "data": "synthetic",
-        "config": {"workload": f"prefill M={R} tokens, Zipf({args.zipf}) top-8 over {E} experts + shared, H=6144, int4 g128 bf16 scales",
+    res = {
+        "metric": "moe_prefill_expert_gemm_tflops", "value": tf, "unit": "TFLOP/s", "ms_per_step": ms, "steps": steps, "warmup": warmup,
+        "tokens_per_s": R / (ms * 1e-3), "dtype": "int4 -> fp16 x fp16 -> fp32 (tcgen05)",
+        "config": {"workload": f"prefill M={R} tokens, Zipf({zipf}) top-8 over {n_exp} experts + shared, H=6144, int4 g128 bf16 scales",
                    "l2": "inputs larger than L2 (4.85 GB of weights, 0.9 GB gathered inputs)", "max_picks_per_expert": int(counts.max()),
                    "min_picks_per_expert": int(counts.min())},
-        "tokens_per_s": R / (ms * 1e-3),
-        "roofline": {"bound": "tensor", "kernel": "prefill_gemm_kernel<2> + <1> (whole step)", "achieved": tf, "peak": peak, "unit": "TFLOP/s",
-                     "frac": tf / peak, "peak_kind": kind, "traffic": None},
+        "roofline": {"bound": "tensor", "kernel": "prefill_gemm_kernel<2> + <1> (whole step: permute, gather, both grouped GEMMs)",
+                     "achieved": tf, "peak": pk["bf16"], "unit": "TFLOP/s", "frac": tf / pk["bf16"], "peak_kind": pk["kind"] + " burst (bf16_tflops)",
+                     "peak_sustained": pk["bf16_sustained"], "frac_sustained": tf / pk["bf16_sustained"], "traffic": None,
+                     "algorithmic_flop_per_step": flop},
         "e2e": {"value": flop / e2e_s / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": R * H * 2, "d2h_bytes_per_step": R * H * 4,
                 "ms_per_step": e2e_s * 1e3},
-        "gpu_launches": int(launches), "device_status": int(status), "clocks": cs.summary()}))
+        "gpu_launches": int(launches), "clocks": cs.summary()}
+    parity = {}
+    if O is not None:
+        rows = [0, R // 2 + 1, R - 1]
+        for mode_name, q in (("act_quant0_vs_exact", False), ("act_quant1_vs_cpu_engine", True)):
+            if q:
+                wsq[0] = moe.prefill_workspace(R, TOPK, n_exp, H, I, dev, act_quant=True)
+                aq[0] = True
+                step(0); step(0)
+                res["act_quant_ms_per_step"] = timed(torch, step, max(1, min(steps, 5)), NB)
+            step(0)
+            got = out[rows].cpu().numpy()
+            ref = oracle_rows(O, layer, xs_np[0][rows], routes[0][0][rows], routes[0][1][rows], 0 if q else 1)
+            e = errors(got, ref)
+            parity[mode_name] = {"max_rel": e[0], "mean_abs": e[1], "norm_rel": e[2], "rows": rows,
+                                 "ok": bool(e[0] < MAX_REL and e[1] < MEAN_ABS) if q else bool(e[2] < NORM_REL)}
+        res["device_status_act_quant"] = int(moe.ws_status(wsq[0]))
+        aq[0] = False; wsq[0] = ws
+    res["device_status"] = int(moe.ws_status(ws))
+    return res, parity
+
+
+def reference_gpu_arm(args, dev, layer, torch, moe, synth, dec):
+    """The reference's own GPU kernels on this device, through their stock entry points (baseline/ref_gpu.py), and this library
+    on the same inputs in the same format (fp16 activations, one fp32 scale per row, routed experts only)."""
+    from baseline import ref_gpu
+    if not ref_gpu.available("moe4", "moe4t"):
+        return {"unavailable": "baseline/_ref holds no build of the reference GPU kernels"}
+    rg = ref_gpu.RefGpu(dev)
+    tabs0 = layer.tabs0
+    steps = max(3, min(args.steps, 20))
+    res = {"format": "fp16 activations, fp32 scale per row, routed experts only (the reference kernels' format); "
+                     "16 rows = two 8-row moe4 calls (its kernels take <= 8 rows)"}
+    xs16 = [x.to(torch.float16) for x in dec["xs"]]
+    sels = [torch.from_numpy(r[0]).to(dev) for r in dec["routes"]]; rws = [torch.from_numpy(r[1]).to(dev) for r in dec["routes"]]
+    ws = moe.decode_workspace(H, I, dev)
+    y = torch.zeros(ROWS, H, dtype=torch.float32, device=dev); yr = torch.zeros(ROWS, H, dtype=torch.float32, device=dev)
+    for rows in (8, 16):
+        def ours(b):
+            y.zero_(); moe.decode(tabs0, xs16[b][:rows], sels[b][:rows], rws[b][:rows], y[:rows], ws)
+        def theirs(b):
+            rg.decode(tabs0, xs16[b][:rows], sels[b][:rows], rws[b][:rows], yr[:rows])
+        ours(0); theirs(0); torch.cuda.synchronize()
+        e = errors(y[:rows].cpu().numpy(), yr[:rows].cpu().numpy())
+        run_o, _ = make_graphed(ours, list(range(NBATCH)), torch, moe, not args.no_graph)
+        run_t, _ = make_graphed(theirs, list(range(NBATCH)), torch, moe, not args.no_graph)
+        for i in range(3):
+            run_o(i); run_t(i)
+        res[f"decode_{rows}_rows"] = {"reference_us": timed(torch, run_t, steps, NBATCH) * 1e3, "ours_us": timed(torch, run_o, steps, NBATCH) * 1e3,
+                                      "norm_rel_ours_vs_reference": e[2], "ok": bool(e[2] < NORM_REL)}
+    del run_o, run_t
+    R = 8192
+    x = torch.from_numpy(synth.activations(20, 0, R, H)).to(torch.float16).to(dev)
+    s_np, w_np = synth.zipf_routing(10, 0, R, layer.n, TOPK, 1.1)
+    sel, rw = torch.from_numpy(s_np).to(dev), torch.from_numpy(w_np).to(dev)
+    wsp = moe.prefill_workspace(R, TOPK, layer.n, H, I, dev)
+    out = torch.zeros(R, H, dtype=torch.float32, device=dev)
+    keep = [None]
+    def ours_p(i):
+        out.zero_(); moe.prefill(tabs0, x, sel, rw, out, wsp)
+    def theirs_p(i):
+        keep[0] = rg.prefill(tabs0, x, sel, rw)
+    ours_p(0); theirs_p(0); torch.cuda.synchronize()
+    e = errors(out[::64].cpu().numpy(), keep[0][::64].cpu().numpy())
+    for i in range(2):
+        ours_p(i); theirs_p(i)
+    n = max(3, min(steps, 10))
+    t_ref, t_ours = timed(torch, theirs_p, n, 1), timed(torch, ours_p, n, 1)
+    flop = TOPK * R * PICK_FLOP
+    res["prefill_8192_rows"] = {"reference_ms": t_ref, "ours_ms": t_ours, "reference_tflops": flop / (t_ref * 1e-3) / 1e12,
+                                "ours_tflops": flop / (t_ours * 1e-3) / 1e12, "norm_rel_ours_vs_reference": e[2], "ok": bool(e[2] < NORM_REL),
+                                "note": "routed experts only (8 picks per token); the reference arm includes its host-side argsort / bincount "
+                                        "sync and row-block upload, ours its device permutation"}
+    res["device_status"] = int(moe.ws_status(ws)) | int(moe.ws_status(wsp))
+    return res
+
+
+def run_ours(args):
+    import torch
+    from hecate_b200 import moe, synth
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        return run_ep(args, world, rank, dev)
+    O = None
+    if not args.no_check:
+        from oracle import oracle as O
+    layer = Layer(dev, 0, args.experts, rowscale=not args.no_ref_gpu)
+    line = None
+    if args.mode in ("all", "decode"):
+        line, dec = decode_arm(args, dev, layer, torch, moe, synth, O)
+    if args.mode in ("all", "prefill"):
+        pre, par = prefill_arm(args, dev, layer, torch, moe, synth, O, R=args.rows, zipf=args.zipf)
+        if line is None:
+            line = dict(pre, n_gpus=1, higher_is_better=True, scaling="weak", vs_baseline=None, data="synthetic", parity_check={"prefill": par})
+        else:
+            line["prefill"] = pre
+            line["parity_check"]["prefill"] = par
+            line["gpu_launches"] += pre["gpu_launches"]
+            line["device_status"] |= pre["device_status"]
+    if args.mode == "all" and not args.no_ref_gpu:
+        try:
+            line["reference_gpu"] = reference_gpu_arm(args, dev, layer, torch, moe, synth, dec)
+        except Exception as e:                   # the baseline must never take the product's numbers down with it
+            line["reference_gpu"] = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+    if args.mode in ("all", "decode") and not args.no_cpu:
+        del layer
+        torch.cuda.empty_cache()
+        line["cpu_baseline"] = cpu_reference_arm(20, 3)
+    print(json.dumps(line))
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# N > 1: expert parallel
+def run_ep(args, world, rank, dev):
+    """The decode configuration with the 256 experts split over `world` GPUs (strong scaling: the 16-row batch is fixed), and the
+    long-prefill configuration (32768 tokens over the ranks) with uniform and with Zipf(1.3) routing."""
+    import torch
+    import torch.distributed as dist
+    from hecate_b200 import ep, moe, synth
+    from hecate_b200 import placement as PL
+    dist.init_process_group("nccl", device_id=dev)
+    pl = ep.shard_plan(rank, world, E)
+    layer = Layer(dev, 100 + rank, pl["n_local"])
+    tabs = layer.tabs
+    line = None
+    if args.mode in ("all", "decode"):
+        line = ep_decode_arm(args, world, rank, dev, tabs, pl, torch, dist, ep, moe, synth)
+    if args.mode in ("all", "prefill"):
+        R = 32768 if args.mode == "all" else args.rows
+        runs = (("prefill", 0.0), ("prefill_zipf", 1.3)) if args.mode == "all" else (("prefill", args.zipf),)
+        for key, z in runs:
+            res = ep_prefill_arm(args, world, rank, dev, tabs, R, z, torch, dist, ep, moe, synth, PL)
+            if rank == 0:
+                if line is None:
+                    line = dict(res, n_gpus=world, higher_is_better=True, scaling="strong", vs_baseline=None, data="synthetic")
+                else:
+                    line[key] = res
+                    line["gpu_launches"] += res["gpu_launches"]
+                    line["device_status"] |= res["device_status"]
+    if rank == 0:
+        print(json.dumps(line))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def ep_decode_arm(args, world, rank, dev, tabs, pl, torch, dist, ep, moe, synth):
+    steps, warmup = args.steps, max(3, args.warmup)
+    wt = torch.from_numpy(synth.router_weight(0, 0, E, H)).to(dev).to(torch.bfloat16)
+    bias = torch.zeros(E, dtype=torch.float32, device=dev)
+    xs = [torch.from_numpy(synth.activations(b, 0, ROWS, H)).to(torch.bfloat16).to(dev) for b in range(NBATCH)]
+    xs_host = [x.cpu().pin_memory() for x in xs]
+    sel = torch.empty(ROWS, TOPK, dtype=torch.int64, device=dev)
+    rw = torch.empty(ROWS, TOPK, dtype=torch.float16, device=dev)
+    f = torch.zeros(ROWS, H, dtype=torch.float32, device=dev)
+    f_host = torch.empty(ROWS, H, dtype=torch.float32).pin_memory()
+    x_in = torch.empty(ROWS, H, dtype=torch.bfloat16, device=dev)
+    results, outs = {}, {}
+    for mode in ("nccl", "peer"):
+        dec = ep.EpDecoder(rank, world, tabs, E, dev, dist, use_peer=(mode == "peer"))
+
+        def step(x):
+            moe.router_fused(x, wt, bias, None, None, sel, rw, TOPK, 1.0)
+            dec.step(x, sel, rw, f)
+
+        for i in range(warmup):
+            step(xs[i % NBATCH])
+        torch.cuda.synchronize(); dist.barrier()
+        f.zero_(); step(xs[0]); torch.cuda.synchronize()
+        outs[mode] = f.clone(); f.zero_()                   # one step's output, for the cross-check of the two combines
+        dist.barrier()
+        graph = (not args.no_graph) and mode == "peer"      # NCCL calls are left eager
+        run_step, per_step = make_graphed(step, xs, torch, moe, graph)
+        for i in range(warmup):
+            run_step(i % NBATCH)
+        torch.cuda.synchronize(); dist.barrier()
+        with ClockSampler(dev.index) as cs:
+            dist.barrier()
+            t = timed(torch, run_step, steps, NBATCH)
+            dist.barrier()
+        ms = torch.tensor([t], device=dev)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        launches = per_step * steps
+
+        def e2e_step(b):
+            x_in.copy_(xs_host[b], non_blocking=True); step(x_in); f_host.copy_(f, non_blocking=True)
+        run_e2e, _ = make_graphed(e2e_step, list(range(NBATCH)), torch, moe, graph)
+        for i in range(3):
+            run_e2e(i % NBATCH)
+        torch.cuda.synchronize(); dist.barrier()
+        n2 = min(steps, 200)
+        t0 = time.perf_counter()
+        for i in range(n2):
+            run_e2e(i % NBATCH); torch.cuda.synchronize()
+        e2e = torch.tensor([(time.perf_counter() - t0) / n2], device=dev)
+        dist.all_reduce(e2e, op=dist.ReduceOp.MAX)
+        st = torch.tensor([dec.status()], device=dev); dist.all_reduce(st, op=dist.ReduceOp.MAX)
+        results[mode] = dict(ms=float(ms.item()), e2e=float(e2e.item()), launches=int(launches), status=int(st.item()), clocks=cs.summary())
+        del run_step, run_e2e
+        if dec.peer is not None:
+            dist.barrier(); dec.peer.close()
+    # load balance of the last batch: distinct local experts per rank
+    mine = (sel >= pl["lo"]) & (sel < pl["lo"] + pl["n_local"])
+    d_local = torch.tensor([float(torch.unique(sel[mine]).numel()) if bool(mine.any()) else 0.0], device=dev)
+    d_all = [torch.zeros_like(d_local) for _ in range(world)]
+    dist.all_gather(d_all, d_local)
+    e = errors(outs["peer"].cpu().numpy(), outs["nccl"].cpu().numpy())
+    if rank != 0:
+        return None
+    r = results["peer"]
+    dl = [float(t.item()) for t in d_all]
+    pk = peaks()
+    bytes_rank_max = (max(dl) + 1) * EXPERT_BYTES + E * H * 2
+    return {
+        "metric": METRIC, "value": ROWS / (r["ms"] * 1e-3), "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
+        "ms_per_step": r["ms"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int4 x fp16 -> fp32",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD + f"; experts split over {world} GPUs ({pl['n_local']} each), rows replicated, "
+                                          "combine over NVLink peer memory",
+                   "l2": "inputs larger than L2: 8 input batches in a ring, each step streams different experts"},
+        "us_per_layer": r["ms"] * 1e3, "nccl_allreduce_us_per_layer": results["nccl"]["ms"] * 1e3,
+        "distinct_local_experts_last_step": dl, "load_imbalance_max_over_mean": max(dl) / (sum(dl) / len(dl)),
+        "combine_bytes_per_rank": (world - 1) * ROWS * H * 4, "dispatch_bytes_per_rank": 0,
+        "roofline": {"bound": "hbm", "kernel": "decode kernels of the most loaded rank (whole call)", "achieved": bytes_rank_max / (r["ms"] * 1e-3) / 1e9,
+                     "peak": pk["hbm"], "unit": "GB/s", "frac": bytes_rank_max / (r["ms"] * 1e-3) / 1e9 / pk["hbm"], "peak_kind": pk["kind"], "traffic": None},
+        "e2e": {"value": ROWS / r["e2e"], "unit": UNIT, "h2d_bytes_per_step": ROWS * H * 2, "d2h_bytes_per_step": ROWS * H * 4,
+                "us_per_layer": r["e2e"] * 1e6},
+        "parity_check": {"decode": {"peer_combine_vs_nccl_allreduce": {"max_rel": e[0], "mean_abs": e[1], "norm_rel": e[2], "ok": bool(e[2] < 1e-5)}}},
+        "gpu_launches": r["launches"], "device_status": max(r["status"], results["nccl"]["status"]), "clocks": r["clocks"]}
+
+
+def ep_prefill_arm(args, world, rank, dev, tabs, R, zipf, torch, dist, ep, moe, synth, PL):
+    """R tokens in total, split over the ranks; uniform or Zipf routing. Placement: contiguous ids for uniform routing; under
+    skew the experts are dealt to the GPUs by load (hecate_b200.placement.balance) from the pick counts of ANOTHER sample of the
+    same popularity (the routing log of an earlier chunk), and the selection is expressed in router positions, as a router with
+    permuted weight rows would emit it. Both combines (NCCL reduce-scatter, fused into the down GEMM over peer memory) are timed
+    and cross-checked; the line reports the faster."""
+    rpr = R // world
+    steps, warmup = max(1, min(args.steps, 20)), max(3, min(args.warmup, 5))
+    sel_all, rw_all = synth.zipf_routing(10, 0, R, E, TOPK, zipf)
+    want = getattr(args, "placement", "auto")
+    use_plan = want == "balanced" or (want == "auto" and zipf > 0)
+    base_imb = PL.contiguous(PL.pick_counts(sel_all, E), world).imbalance()
+    if use_plan:
+        cal, _ = synth.zipf_routing(11, 0, R, E, TOPK, zipf)
+        plan = PL.balance(PL.pick_counts(cal, E), world, extra_slots=0)
+        sel_all = PL.positions(sel_all, plan)
+    pl = ep.shard_plan(rank, world, E)
+    x = torch.from_numpy(synth.activations(rank, 0, rpr, H)).to(torch.bfloat16).to(dev)
+    sel = torch.from_numpy(sel_all[rank * rpr:(rank + 1) * rpr]).to(dev); rw = torch.from_numpy(rw_all[rank * rpr:(rank + 1) * rpr]).to(dev)
+    out = torch.empty(rpr, H, dtype=torch.float32, device=dev)
+    times, outs = {}, {}
+    st_all = launches = 0
+    for mode in ("nccl", "peer"):
+        p = ep.EpPrefill(rank, world, tabs, E, rpr, dev, dist, use_peer=(mode == "peer"))
+        for _ in range(warmup):
+            p.step(x, sel, rw, out)
+        torch.cuda.synchronize(); dist.barrier()
+        outs[mode] = out[::256].clone()
+        l0 = moe.launch_count()
+        with ClockSampler(dev.index) as cs:
+            dist.barrier()
+            t = timed(torch, lambda i: p.step(x, sel, rw, out), steps, 1)
+            dist.barrier()
+        ms = torch.tensor([t], device=dev)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        times[mode] = float(ms.item())
+        launches = moe.launch_count() - l0
+        st = torch.tensor([p.status()], device=dev); dist.all_reduce(st, op=dist.ReduceOp.MAX)
+        st_all |= int(st.item())
+        if p.peer is not None:
+            dist.barrier(); p.peer.close()
+        del p
+    best = min(times, key=times.get)               # both arms are timed; the line reports the faster one and names it
+    e = torch.tensor(list(errors(outs["peer"].cpu().numpy(), outs["nccl"].cpu().numpy())), device=dev, dtype=torch.float64)
+    dist.all_reduce(e, op=dist.ReduceOp.MAX)
+    picks = np.array([int(((sel_all >= r * pl["n_local"]) & (sel_all < (r + 1) * pl["n_local"])).sum()) for r in range(world)])
+    if rank != 0:
+        return None
+    flop = (TOPK * R + R) * PICK_FLOP
+    t = times[best] * 1e-3
+    pk = peaks()
+    return {
+        "metric": "moe_prefill_expert_gemm_tflops", "value": flop / t / 1e12, "unit": "TFLOP/s", "steps": steps, "warmup": warmup,
+        "ms_per_step": t * 1e3, "dtype": "int4 -> fp16 x fp16 -> fp32 (tcgen05)",
+        "config": {"workload": f"prefill M={R} tokens over {world} GPUs ({rpr} each), Zipf({zipf}) top-8 over {E} experts + shared, "
+                               f"{pl['n_local']} experts per GPU ({'placed by load from a calibration sample' if use_plan else 'contiguous ids'}), "
+                               f"all-gather dispatch (NCCL), combine: " + ("fused into the down GEMM over NVLink peer memory" if best == "peer" else "NCCL reduce-scatter"),
+                   "l2": "inputs larger than L2"},
+        "tokens_per_s": R / t, "nccl_reduce_scatter_ms_per_step": times["nccl"], "peer_combine_ms_per_step": times["peer"],
+        "dispatch_bytes_per_rank": (world - 1) * rpr * (H * 2 + TOPK * 10), "combine_bytes_per_rank": (world - 1) * rpr * H * 4,
+        "picks_per_rank": picks.tolist(), "load_imbalance_max_over_mean": float(picks.max() / picks.mean()),
+        "load_imbalance_contiguous_placement": base_imb,
+        "roofline": {"bound": "tensor", "kernel": "whole step incl. collectives", "achieved": flop / t / 1e12, "peak": pk["bf16"] * world, "unit": "TFLOP/s",
+                     "frac": flop / t / 1e12 / (pk["bf16"] * world), "peak_kind": pk["kind"] + " burst (bf16_tflops) x n_gpus",
+                     "frac_sustained": flop / t / 1e12 / (pk["bf16_sustained"] * world), "traffic": None},
+        "parity_check": {"peer_combine_vs_nccl_reduce_scatter": {"max_rel": float(e[0]), "mean_abs": float(e[1]), "norm_rel": float(e[2]),
+                                                                 "ok": bool(float(e[2]) < 1e-5)}},
+        "gpu_launches": int(launches), "device_status": int(st_all), "clocks": cs.summary()}
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=1000)
-    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--mode", default="all", choices=["all", "decode", "prefill"], help="all (default): the decode headline plus the prefill, "
+                    "parity and baseline objects; decode / prefill: that arm alone")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-check", action="store_true", help="skip the parity checks against the CPU checker")
+    ap.add_argument("--no-ref-gpu", action="store_true", help="skip the reference GPU kernels")
+    ap.add_argument("--all-variants", action="store_true", help="--impl reference: also time the scalar build of the engine")
     ap.add_argument("--no-graph", action="store_true", help="launch the step's kernels eagerly instead of replaying CUDA graphs")
-    ap.add_argument("--mode", default="decode", choices=["decode", "prefill"], help="decode (default, the headline) or prefill")
-    ap.add_argument("--rows", type=int, default=8192, help="prefill rows")
+    ap.add_argument("--rows", type=int, default=8192, help="prefill rows (N = 1, or --mode prefill)")
     ap.add_argument("--zipf", type=float, default=1.1, help="prefill expert popularity exponent (0 = uniform)")
     ap.add_argument("--placement", default="auto", choices=["auto", "contiguous", "balanced"],
-                    help="N > 1 prefill: expert -> GPU map; auto = balanced by load when --zipf > 0")
-    ap.add_argument("--extra-slots", type=int, default=0, help="N > 1 prefill, balanced placement: slots for copies of the hottest experts")
+                    help="N > 1 prefill: expert -> GPU map; auto = balanced by load when the routing is skewed")
     ap.add_argument("--experts", type=int, default=E, help="routed experts resident (256 = the benchmark; fewer only for profiling)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
-    elif args.mode == "prefill":
-        run_prefill(args)
     else:
         run_ours(args)
 

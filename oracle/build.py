@@ -41,16 +41,32 @@ def build_oracle(force=False):
     return dst
 
 
-def ref_module_path():
+# Builds of the reference engine: the same source with three versions of the shim's inner-loop intrinsics (see
+# ref_shim/arm_neon.h). The module name carries the variant, so several can be loaded into one process.
+REF_VARIANTS = {
+    "avx2": ("cpuband_ref", []),
+    "vnni": ("cpuband_ref_vnni", ["-DHMOE_SHIM_VNNI", "-mavx512f", "-mavx512vl", "-mavx512vnni"]),
+    "scalar": ("cpuband_ref_scalar", ["-DHMOE_SHIM_SCALAR", "-fno-tree-vectorize", "-fno-tree-slp-vectorize"]),
+}
+
+
+def ref_module_path(variant="avx2"):
     suffix = sysconfig.get_config_var("EXT_SUFFIX") or ".so"
-    return os.path.join(HERE, "_ref", "cpuband_ref" + suffix)
+    return os.path.join(HERE, "_ref", REF_VARIANTS[variant][0] + suffix)
 
 
-def build_ref(force=False):
-    """Compile the reference CPU engine as the python module `cpuband_ref` (needs the reference tree and torch headers)."""
+def host_has_vnni():
+    try:
+        return "avx512_vnni" in open("/proc/cpuinfo").read()
+    except OSError:
+        return False
+
+
+def build_ref(force=False, variant="avx2"):
+    """Compile the reference CPU engine as a python module (needs the reference tree and torch headers)."""
     root = ref_root()
     src = os.path.join(root, "runtime", "tier", "cpuband.cpp") if root else ""
-    dst = ref_module_path()
+    dst = ref_module_path(variant)
     if not root or not os.path.exists(src):
         return dst if os.path.exists(dst) else None
     shim = os.path.join(HERE, "ref_shim", "arm_neon.h")
@@ -62,14 +78,19 @@ def build_ref(force=False):
     text = text.replace('asm volatile("yield")', "__builtin_ia32_pause()").replace("__fp16", "_Float16")
     inc = [f"-I{p}" for p in ce.include_paths()] + [f"-I{sysconfig.get_paths()['include']}", f"-I{os.path.join(HERE, 'ref_shim')}"]
     libdir = ce.library_paths()[0]
-    cmd = ["g++", "-O3", "-std=c++17", "-fPIC", "-shared", "-mavx2", "-mfma", "-mf16c", "-ffp-contract=off", "-pthread",
-           "-DTORCH_EXTENSION_NAME=cpuband_ref", "-DTORCH_API_INCLUDE_EXTENSION_H", "-D_GLIBCXX_USE_CXX11_ABI=1",
+    name, extra = REF_VARIANTS[variant]
+    cmd = ["g++", "-O3", "-std=c++17", "-fPIC", "-shared", "-mavx2", "-mfma", "-mf16c", "-ffp-contract=off", "-pthread", *extra,
+           f"-DTORCH_EXTENSION_NAME={name}", "-DTORCH_API_INCLUDE_EXTENSION_H", "-D_GLIBCXX_USE_CXX11_ABI=1",
            *inc, "-x", "c++", "-", "-o", dst, f"-L{libdir}", f"-Wl,-rpath,{libdir}",
            "-ltorch_python", "-ltorch", "-ltorch_cpu", "-lc10"]
     subprocess.run(cmd, input=text.encode(), check=True)
     return dst
 
 
+def build_ref_all(force=False):
+    return {v: build_ref(force, v) for v in REF_VARIANTS}
+
+
 if __name__ == "__main__":
     print(build_oracle(force="--force" in sys.argv))
-    print(build_ref(force="--force" in sys.argv))
+    print(build_ref_all(force="--force" in sys.argv))

@@ -134,22 +134,25 @@ def threads():
 # ----------------------------------------------------------------------------------------------------------------------
 # The reference CPU engine itself (oracle/_ref, built from the reference's own source by oracle/build.py)
 
-def ref_available():
+def ref_available(variant="avx2"):
+    """Is the reference engine's build `variant` ("avx2", "vnni", "scalar": oracle/build.py) present and runnable on this host?"""
     from . import build
-    return os.path.exists(build.ref_module_path())
+    if variant == "vnni" and not build.host_has_vnni():
+        return False
+    return os.path.exists(build.ref_module_path(variant))
 
 
 class RefEngine:
     """Drives the reference engine in its legacy (non-slot) mode the way the reference's own test does
     (tools/dev/test_grace_picks.py:25-42): a 256-byte int32 flag block (ISSUE word 0, meta [layer, rows] at byte 64,
     DONE at byte 128), x fp16 [8][6144], sel int64 [8][8], rw fp16 [8][8], out fp32 [8][6144]. H, I and 8 rows are fixed
-    by the engine. One engine per process (its pool is a process-wide singleton)."""
+    by the engine. One engine per build variant and process (its pool is a singleton of the module)."""
     H, I = 6144, 2048
 
-    def __init__(self, experts, lo, threads=8, core0=0):
+    def __init__(self, experts, lo, threads=8, core0=0, variant="avx2"):
         import torch
         from . import build
-        spec = importlib.util.spec_from_file_location("cpuband_ref", build.ref_module_path())
+        spec = importlib.util.spec_from_file_location(build.REF_VARIANTS[variant][0], build.ref_module_path(variant))
         self.mod = importlib.util.module_from_spec(spec)
         spec.loader.exec_module(self.mod)
         self.torch = torch

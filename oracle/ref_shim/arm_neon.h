@@ -2,7 +2,10 @@
 // (runtime/tier/cpuband.cpp) uses, so that its unmodified arithmetic can be compiled and run on an x86-64 host as the
 // parity oracle and the timed CPU baseline. Integer operations are exact; vfmaq_n_f32 is a fused multiply-add like the
 // AArch64 instruction; vaddvq_f32 adds pairwise, (v0 + v1) + (v2 + v3), the order of the AArch64 FADDP sequence.
-// Needs -mavx2 -mfma.
+// Three builds of the two intrinsics in the engine's inner loop (cpuband.cpp:80-104), all bit-identical in their results:
+//   default           vdotq_s32 as widening 16-bit multiply-adds (AVX2), vfmaq_n_f32 as an FMA            needs -mavx2 -mfma
+//   HMOE_SHIM_VNNI    vdotq_s32 as one AVX-512-VNNI dot-product instruction (the x86 counterpart of SDOT)  + -mavx512vl -mavx512vnni
+//   HMOE_SHIM_SCALAR  both as plain scalar loops (a strawman: what the engine costs without SIMD)
 #pragma once
 #include <cstdint>
 #include <immintrin.h>
@@ -27,12 +30,34 @@ static inline int8x16x2_t vzipq_s8(int8x16_t a, int8x16_t b) { return {{{_mm_unp
 // lane i += sum of the four int8 products 4i .. 4i+3
 static inline int32x4_t vdotq_s32(int32x4_t acc, int8x16_t a, int8x16_t b)
 {
+#if defined(HMOE_SHIM_SCALAR)
+    alignas(16) int8_t x[16], y[16]; alignas(16) int32_t c[4];
+    _mm_store_si128((__m128i*) x, a.v); _mm_store_si128((__m128i*) y, b.v); _mm_store_si128((__m128i*) c, acc.v);
+    for (int i = 0; i < 4; ++i)
+        for (int j = 0; j < 4; ++j) c[i] += (int32_t) x[4 * i + j] * (int32_t) y[4 * i + j];
+    return {_mm_load_si128((const __m128i*) c)};
+#elif defined(HMOE_SHIM_VNNI)
+    // vpdpbusd multiplies unsigned by signed bytes: |a| x (b with a's sign). Exact for every a and every b != -128; the engine's
+    // b operands are activation codes in [-127, 127] (cpuband.cpp:106-111) and its a operands int4 values in [-8, 7].
+    return {_mm_dpbusd_epi32(acc.v, _mm_abs_epi8(a.v), _mm_sign_epi8(b.v, a.v))};
+#else
     const __m256i m = _mm256_madd_epi16(_mm256_cvtepi8_epi16(a.v), _mm256_cvtepi8_epi16(b.v));
     const __m128i d = _mm_hadd_epi32(_mm256_castsi256_si128(m), _mm256_extracti128_si256(m, 1));
     return {_mm_add_epi32(acc.v, d)};
+#endif
 }
 static inline float32x4_t vcvtq_f32_s32(int32x4_t a) { return _mm_cvtepi32_ps(a.v); }
-static inline float32x4_t vfmaq_n_f32(float32x4_t acc, float32x4_t a, float s) { return _mm_fmadd_ps(a, _mm_set1_ps(s), acc); }
+static inline float32x4_t vfmaq_n_f32(float32x4_t acc, float32x4_t a, float s)
+{
+#if defined(HMOE_SHIM_SCALAR)
+    alignas(16) float x[4], c[4];
+    _mm_store_ps(x, a); _mm_store_ps(c, acc);
+    for (int i = 0; i < 4; ++i) c[i] = __builtin_fmaf(x[i], s, c[i]);
+    return _mm_load_ps(c);
+#else
+    return _mm_fmadd_ps(a, _mm_set1_ps(s), acc);
+#endif
+}
 static inline float vaddvq_f32(float32x4_t a)
 {
     float v[4]; _mm_storeu_ps(v, a);

@@ -70,16 +70,23 @@ def test_exact_mode_close_to_int8_mode(oracle, experts):
     assert 1e-3 < rel < 3e-2       # the int8 activation round trips cost about 1 % (the reason for the act_quant mode)
 
 
-def test_against_reference_engine_live(oracle, experts):
-    if not oracle.ref_available():
-        pytest.skip("reference engine build not present")
-    eng = oracle.RefEngine(experts, MG.JOB_LO, threads=4)
+@pytest.mark.parametrize("variant", ["avx2", "vnni", "scalar"])
+def test_against_reference_engine_live(oracle, experts, variant):
+    """Every build of the reference engine (the shim's AVX2, AVX-512-VNNI and scalar inner loops) gives the restatement's
+    result bit for bit, and therefore the stored golden outputs: the variants differ in speed only."""
+    if not oracle.ref_available(variant):
+        pytest.skip(f"reference engine build '{variant}' not present (or the host lacks its instructions)")
+    eng = oracle.RefEngine(experts, MG.JOB_LO, threads=4, variant=variant)
     try:
         for j, spec in enumerate(MG.JOBS[:3]):
             x, sel, rw = MG.job_inputs(j + 10, spec)
             ref, _ = eng.job(x, sel, rw)
             got = oracle.moe_forward(6144, 2048, 0, x, sel, rw, MG.JOB_LO, experts)
             assert np.array_equal(ref.view(np.int32), got.view(np.int32))
+        z = np.load(os.path.join(G, "cpuband_jobs.npz"))
+        x, sel, rw = MG.job_inputs(0, MG.JOBS[0])
+        ref, _ = eng.job(x, sel, rw)
+        assert np.array_equal(ref.view(np.int32), z["out0"].view(np.int32))
     finally:
         eng.stop()
 
