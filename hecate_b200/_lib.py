@@ -11,7 +11,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("HECATE_MOE_LIB") or os.path.join(_HERE, "csrc", "libhecate_moe_b200.so")
 _lib = None
 
-F16, BF16, F32 = 0, 1, 2
+F16, BF16, F32, F16_FRAG = 0, 1, 2, 3
 
 
 class HmoeError(RuntimeError):

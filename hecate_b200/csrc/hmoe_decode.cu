@@ -48,7 +48,7 @@ struct SmemLayout
 
 // ---------------------------------------------------------------------------------------------------------------------
 // prepare
-__global__ void __launch_bounds__(256) decode_prepare_kernel(const void* __restrict__ x, int x_bf16, const int64_t* __restrict__ sel,
+__global__ void __launch_bounds__(256) decode_prepare_kernel(const void* __restrict__ x, int x_kind /* 0 fp16, 1 bf16, 2 fp16 in MMA column order */, const int64_t* __restrict__ sel,
     const __half* __restrict__ rw, int R, int H, int topk, int lo, int n_local, int has_shared, int act_quant,
     __half* __restrict__ xf, float* __restrict__ xscale, Route* __restrict__ route, int sh_mod, int sh_rem, unsigned* gen_bump,
     float4* __restrict__ gzero, int gzero_n, int I, int nblocks)
@@ -63,6 +63,20 @@ __global__ void __launch_bounds__(256) decode_prepare_kernel(const void* __restr
         for (int gi = tid; gi < H / 32; gi += blockDim.x)
         {
             float v[32];
+            if (x_kind == 2)
+            {
+                // fp16 rows that already are in the MMA column order (the copy the reference's norm + router kernel can write for
+                // moe4, its xf argument): word p of the 64-column block sits at frag_pos(p)
+                const uint32_t* src = (const uint32_t*) ((const uint16_t*) x + (size_t) r * H + (gi >> 1) * 64);
+                #pragma unroll
+                for (int p = 0; p < 16; ++p)
+                {
+                    const uint32_t w = src[frag_pos((gi & 1) * 16 + p)];
+                    const float2 f = __half22float2(*(const __half2*) &w);
+                    v[2 * p] = f.x; v[2 * p + 1] = f.y;
+                }
+            }
+            else
             {
                 const uint4* p = (const uint4*) ((const uint16_t*) x + (size_t) r * H + gi * 32);
                 #pragma unroll
@@ -73,7 +87,7 @@ __global__ void __launch_bounds__(256) decode_prepare_kernel(const void* __restr
                     #pragma unroll
                     for (int k = 0; k < 4; ++k)
                     {
-                        if (x_bf16) { v[j * 8 + 2 * k] = __uint_as_float(w[k] << 16); v[j * 8 + 2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u); }
+                        if (x_kind == 1) { v[j * 8 + 2 * k] = __uint_as_float(w[k] << 16); v[j * 8 + 2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u); }
                         else { const float2 f = __half22float2(*(const __half2*) &w[k]); v[j * 8 + 2 * k] = f.x; v[j * 8 + 2 * k + 1] = f.y; }
                     }
                 }
@@ -1060,7 +1074,7 @@ int decode_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t
     if (n_local < 0 || n_local > 256) return fail(HMOE_E_ARG, "hmoe_decode: at most 256 local experts");
     if (!(L->group == 0 && L->scale_dtype == HMOE_F32) && !(L->group == 128 && L->scale_dtype == HMOE_BF16))
         return fail(HMOE_E_ARG, "hmoe_decode: scales must be fp32 per row (group 0) or bf16 per 128 columns");
-    if (x_dtype != HMOE_F16 && x_dtype != HMOE_BF16) return fail(HMOE_E_ARG, "hmoe_decode: x must be fp16 or bf16");
+    if (x_dtype != HMOE_F16 && x_dtype != HMOE_BF16 && x_dtype != HMOE_F16_FRAG) return fail(HMOE_E_ARG, "hmoe_decode: x must be fp16 or bf16");
     if (ws_bytes < decode_ws_bytes(H, I)) return fail(HMOE_E_WS, "hmoe_decode: workspace too small");
     if (!x || !sel || !rw || !y || !ws) return fail(HMOE_E_ARG, "hmoe_decode: null pointer");
     const int g_sms = device_sms();
@@ -1076,7 +1090,7 @@ int decode_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t
     if (sh8 && !(I <= 2048 && H <= 6144)) return fail(HMOE_E_UNSUPPORTED, "hmoe_decode: the int8 shared expert needs H <= 6144 and I <= 2048");
     const int has_shared = L->sh_gate_w != nullptr && !sh8;
     if (g_prof) cudaEventRecord(g_ev[g_prof_calls % PROF_RING][0], st);
-    decode_prepare_kernel<<<R + 1, 256, 0, st>>>(x, x_dtype == HMOE_BF16, sel, (const __half*) rw, R, H, L->topk, lo, n_local, has_shared,
+    decode_prepare_kernel<<<R + 1, 256, 0, st>>>(x, x_dtype == HMOE_BF16 ? 1 : (x_dtype == HMOE_F16_FRAG ? 2 : 0), sel, (const __half*) rw, R, H, L->topk, lo, n_local, has_shared,
                                                  act_quant, xf, xscale, route, sh_mod, sh_rem, gen_ptr,
                                                  (float4*) act, (I <= 2048 && H <= 6144) ? (L->topk + 1) * 2 * I / 4 : 0, I, g_sms < MAXB ? g_sms : MAXB);
     if (sh8)

@@ -14,7 +14,7 @@ import ctypes as C
 import torch
 
 from . import _lib
-from ._lib import BF16, F16, F32, HmoeError, LayerStruct, check, lib, vp
+from ._lib import BF16, F16, F16_FRAG, F32, HmoeError, LayerStruct, check, lib, vp
 
 MAX_DECODE_ROWS = 16
 
@@ -112,8 +112,11 @@ def moe4t_scratch(device, npos, H=6144, I=2048, act_quant=False):
     """moe4t.scratch(device, npos) -> [gu, ar, d] (moe4t.cu:490-495). Here one workspace tensor stands for all three (it holds
     the gathered inputs and the intermediate activations); the other two entries keep call sites that unpack three working."""
     n = lib().hmoe_prefill_sorted_ws_bytes(C.c_int(int(npos)), C.c_int(H), C.c_int(I), C.c_int(int(act_quant)))
-    e = torch.zeros(1, dtype=torch.uint8, device=device)
-    return [torch.zeros(n, dtype=torch.uint8, device=device), e, e]
+    # `ar` and `d` are zero-stride views of one element with the reference's shapes, so call sites that reshape them
+    # (d.view(1, ps, H), tier_split.py:459) keep working without the memory
+    ar = torch.zeros(1, dtype=torch.float16, device=device).expand(int(npos), I)
+    d = torch.zeros(1, dtype=torch.float32, device=device).expand(int(npos), H)
+    return [torch.zeros(n, dtype=torch.uint8, device=device), ar, d]
 
 
 def moe4t_forward(x, tok, eid, wt, rbt, gw, uw, dw, gs, us, ds, gu, ar, d, out, *, I=2048, group=0, act_quant=False):
@@ -193,10 +196,10 @@ def moe4_forward(x, sel, rw, n_hot, gate_w, up_w, down_w, gate_s, up_s, down_s, 
     """moe4.forward with the reference's argument order (moe4.cu:828-833,916-920). gate_w .. down_s are int64 device
     tables of pointers; `act` is the workspace from moe4_scratch; gu32, ctr_a, y32, ctr_b, blocks, blocks_a are accepted and
     ignored (this implementation needs no counters and sizes its own grid). Up to 16 rows. The shared expert pointers
-    are int4 in the routed experts' format, or with shared_i8 the reference's int8 copies (tier_split.py:495-514). xf
-    (pre-ordered input) is not supported."""
-    if xf:
-        raise HmoeError("moe4_forward: fragment-order input (xf) is not supported")
+    are int4 in the routed experts' format, or with shared_i8 the reference's int8 copies (tier_split.py:495-514). xf = 1: x
+    is the fp16 copy in the MMA column order that the reference's norm + router kernel writes (moe4.cu:68-72)."""
+    if xf and x.dtype != torch.float16:
+        raise HmoeError("moe4_forward: fragment-order input (xf) must be fp16")
     R, H = x.shape
     s = LayerStruct()
     s.H, s.I, s.n_experts, s.topk, s.group = H, I, int(n_hot), sel.shape[1], group
@@ -208,7 +211,7 @@ def moe4_forward(x, sel, rw, n_hot, gate_w, up_w, down_w, gate_s, up_s, down_s, 
     s.shared_format = 1 if (shared_i8 and sh_gw) else 0
     if sel.dtype != torch.int64 or not sel.is_contiguous():
         raise HmoeError("moe4: selection must be contiguous int64")
-    check(lib().hmoe_decode(C.byref(s), vp(x), C.c_int(_dt(x)), vp(sel), vp(rw), C.c_int(R), C.c_int(int(lo)), C.c_int(int(n_hot)),
+    check(lib().hmoe_decode(C.byref(s), vp(x), C.c_int(F16_FRAG if xf else _dt(x)), vp(sel), vp(rw), C.c_int(R), C.c_int(int(lo)), C.c_int(int(n_hot)),
                             C.c_int(int(act_quant)), vp(y), vp(act), C.c_size_t(act.numel()), _stream(x.device)))
 
 

@@ -23,7 +23,9 @@ extern "C" {
 #endif
 
 enum { HMOE_OK = 0, HMOE_E_ARG = 1, HMOE_E_CUDA = 2, HMOE_E_TIMEOUT = 3, HMOE_E_WS = 4, HMOE_E_UNSUPPORTED = 5 };
-enum { HMOE_F16 = 0, HMOE_BF16 = 1, HMOE_F32 = 2 };
+enum { HMOE_F16 = 0, HMOE_BF16 = 1, HMOE_F32 = 2,
+       HMOE_F16_FRAG = 3 /* hmoe_decode's x only: fp16 rows already in the MMA column order, as the reference's norm + router kernel
+                            writes them for moe4.forward(xf = 1) (runtime/tier/moe4/moe4.cu:68-72, runtime/core/nr4_kernel.cuh:99-118) */ };
 
 /* One MoE layer's experts as the reference's loader hands them to its kernels (runtime/tier/tier_split.py:206-246):
  * six device arrays of n_experts device pointers (int64), one per matrix and per scale tensor, plus the optional shared
@@ -68,7 +70,7 @@ int hmoe_norm_router(const float* y, const float* r, float* r_out, const void* n
                      void* ws, size_t ws_bytes, void* stream);
 
 /* Decode expert layer: replaces moe4.forward(x, sel, rw, n_hot, tables..., scratch..., y, blocks, blocks_a, lo, shared...)
- * (runtime/tier/moe4/moe4.cu:828-895) for R <= 16 rows in one pass over the weights. x [R][H] fp16 or bf16; sel int64
+ * (runtime/tier/moe4/moe4.cu:828-895) for R <= 16 rows in one pass over the weights. x [R][H] fp16 or bf16 (or HMOE_F16_FRAG); sel int64
  * [R][topk]; rw fp16 [R][topk]; only ids in [lo, lo + n_local) contribute, entry e - lo of the tables; y fp32 [R][H] is
  * accumulated into. act_quant = 1 reproduces the reference CPU engine's int8 activation round trips
  * (runtime/tier/cpuband.cpp:106-111,140-150,200-207); 0 keeps fp16 activations like the reference GPU kernels.

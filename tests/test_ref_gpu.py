@@ -62,7 +62,7 @@ def test_router_against_reference_router(ref, R, bias_sigma):
     moe.router_fused(xt, wt, bt, None, None, sel, rw, topk, 2.5)
     torch.cuda.synchronize()
     m = _margins(x, w, bias, topk)
-    print(f"router R={R} bias_sigma={bias_sigma}: min top-{topk}/{topk + 1} key margin per row {np.array2string(m, precision=2)}")
+    print(f"router R={R} bias_sigma={bias_sigma}: top-{topk}/{topk + 1} key margin per row " + " ".join(f"{v:.1e}" for v in m))
     a, b = sel.cpu().numpy(), rsel.cpu().numpy()
     for r in range(R):
         if m[r] < 1e-5:
