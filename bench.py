@@ -609,39 +609,136 @@ def run_ep(args, world, rank, dev):
                     line[key] = res
                     line["gpu_launches"] += res["gpu_launches"]
                     line["device_status"] |= res["device_status"]
+    L = args.layers if args.layers > 0 else (75 if (world == 8 and args.mode == "all") else 0)
+    if L > 0:
+        del layer, tabs
+        torch.cuda.empty_cache()
+        res = stack_arm(args, world, rank, dev, L, torch, dist, ep, moe, synth)
+        if rank == 0:
+            if line is None:
+                line = dict(res, n_gpus=world, higher_is_better=True, scaling="strong", vs_baseline=None, data="synthetic")
+            else:
+                line["stack"] = res
     if rank == 0:
         print(json.dumps(line))
     dist.barrier()
     dist.destroy_process_group()
 
 
+def stack_arm(args, world, rank, dev, L, torch, dist, ep, moe, synth):
+    """The expert stack of a whole model: L MoE layers with per-layer weights and router (layer index in the seed), the experts
+    of every layer split over the GPUs, decode batch of 8 tokens x (1 + 1 draft) = 16 rows that are data-parallel (rank r holds
+    rows r, r + world, ...). Per layer and rank: router on the rank's rows -> dispatch (all-gather of rows, selections, weights over
+    peer memory) -> expert kernels -> combine of the rank's rows over peer memory. One CUDA graph replays all L layers of a step.
+    Successive layers use different input batches, so every layer routes differently."""
+    pl = ep.shard_plan(rank, world, E)
+    layers = [Layer(dev, 1000 + 16 * l + rank, pl["n_local"]) for l in range(L)]
+    g = torch.Generator(device=dev); g.manual_seed(7)
+    wts = [(torch.randn(E, H, device=dev, generator=g) * 0.02).to(torch.bfloat16) for _ in range(L)]
+    bias = torch.zeros(E, dtype=torch.float32, device=dev)
+    dec = ep.EpDecoder(rank, world, layers[0].tabs, E, dev, dist, use_peer=world > 1)
+    own = list(range(rank, ROWS, world))
+    n_own = len(own)
+    NB = 4
+    xs = [torch.from_numpy(synth.activations(b, 0, ROWS, H)).to(torch.bfloat16).to(dev) for b in range(NB + 1)]
+    xo = [x[own].contiguous() for x in xs]
+    sel = torch.empty(max(n_own, 1), TOPK, dtype=torch.int64, device=dev); rw = torch.empty(max(n_own, 1), TOPK, dtype=torch.float16, device=dev)
+    sel16 = torch.empty(ROWS, TOPK, dtype=torch.int64, device=dev); rw16 = torch.empty(ROWS, TOPK, dtype=torch.float16, device=dev)
+    f_own = torch.zeros(max(n_own, 1), H, dtype=torch.float32, device=dev)
+    f = torch.zeros(ROWS, H, dtype=torch.float32, device=dev)
+
+    def step(b):
+        for l in range(L):
+            if world > 1:
+                x = xo[(b + l) % (NB + 1)]
+                if n_own:
+                    moe.router_fused(x, wts[l], bias, None, None, sel, rw, TOPK, 1.0)
+                dec.step_dp(x, sel, rw, f_own, ROWS, tables=layers[l].tabs)
+            else:
+                x = xs[(b + l) % (NB + 1)]
+                moe.router_fused(x, wts[l], bias, None, None, sel16, rw16, TOPK, 1.0)
+                dec.step(x, sel16, rw16, f, tables=layers[l].tabs)
+
+    steps, warmup = max(1, min(args.steps, 20)), 3
+    for i in range(2):
+        step(i)
+    torch.cuda.synchronize(); dist.barrier()
+    run_step, per_step = make_graphed(step, list(range(NB)), torch, moe, not args.no_graph)
+    for i in range(warmup):
+        run_step(i % NB)
+    torch.cuda.synchronize(); dist.barrier()
+    with ClockSampler(dev.index) as cs:
+        dist.barrier()
+        t = timed(torch, run_step, steps, NB)
+        dist.barrier()
+    ms = torch.tensor([t], device=dev)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    st = torch.tensor([dec.status()], device=dev); dist.all_reduce(st, op=dist.ReduceOp.MAX)
+    resident = sum(lay.pool.numel() + 2 * (lay.gs.numel() + lay.us.numel() + lay.ds.numel()) for lay in layers)
+    del run_step
+    if dec.peer is not None:
+        dist.barrier(); dec.peer.close()
+    if rank != 0:
+        return None
+    t = float(ms.item())
+    return {"metric": "moe_stack_decode_us_per_layer", "value": t * 1e3 / L, "unit": "us/layer", "layers": L, "ms_per_step": t, "steps": steps,
+            "warmup": warmup, "tokens_per_s": 8 / (t * 1e-3), "rows_per_s": ROWS / (t * 1e-3), "experts_per_gpu_per_layer": pl["n_local"],
+            "resident_gb_per_gpu": resident / 1e9, "launch": "eager" if args.no_graph else "one cuda graph per step over all layers",
+            "dispatch_bytes_per_rank_per_layer": (world - 1) * n_own * (H * 2 + TOPK * 10) if world > 1 else 0,
+            "combine_bytes_per_rank_per_layer": (world - 1) * n_own * H * 4 if world > 1 else 0,
+            "config": {"workload": f"{L} MoE layers (per-layer random weights and routing from seed), decode M=8 tokens x 2 rows, experts "
+                                   f"split over {world} GPUs, data-parallel tokens with dispatch + combine over NVLink peer memory every layer"},
+            "gpu_launches": int(per_step * steps), "device_status": int(st.item()), "clocks": cs.summary()}
+
+
 def ep_decode_arm(args, world, rank, dev, tabs, pl, torch, dist, ep, moe, synth):
+    """Two arms. "peer" (the headline): the 16 rows are data-parallel (rank r holds rows r, r + world, ...); per step every rank
+    routes its own rows, dispatches them (rows, selections, weights: an all-gather over NVLink peer memory), runs its experts on
+    all rows and brings its own rows' sums back over peer memory. "nccl" (the baseline): rows replicated, router replicated,
+    NCCL all-reduce of the fp32 partials."""
     steps, warmup = args.steps, max(3, args.warmup)
     wt = torch.from_numpy(synth.router_weight(0, 0, E, H)).to(dev).to(torch.bfloat16)
     bias = torch.zeros(E, dtype=torch.float32, device=dev)
     xs = [torch.from_numpy(synth.activations(b, 0, ROWS, H)).to(torch.bfloat16).to(dev) for b in range(NBATCH)]
+    own = list(range(rank, ROWS, world))
+    n_own = len(own)
+    xo = [x[own].contiguous() for x in xs]
+    xo_host = [x.cpu().pin_memory() for x in xo]
     xs_host = [x.cpu().pin_memory() for x in xs]
     sel = torch.empty(ROWS, TOPK, dtype=torch.int64, device=dev)
     rw = torch.empty(ROWS, TOPK, dtype=torch.float16, device=dev)
+    sel_o = torch.empty(max(n_own, 1), TOPK, dtype=torch.int64, device=dev); rw_o = torch.empty(max(n_own, 1), TOPK, dtype=torch.float16, device=dev)
     f = torch.zeros(ROWS, H, dtype=torch.float32, device=dev)
+    f_o = torch.zeros(max(n_own, 1), H, dtype=torch.float32, device=dev)
     f_host = torch.empty(ROWS, H, dtype=torch.float32).pin_memory()
     x_in = torch.empty(ROWS, H, dtype=torch.bfloat16, device=dev)
+    xo_in = torch.empty(max(n_own, 1), H, dtype=torch.bfloat16, device=dev)
     results, outs = {}, {}
+    disp_bytes = 0
     for mode in ("nccl", "peer"):
         dec = ep.EpDecoder(rank, world, tabs, E, dev, dist, use_peer=(mode == "peer"))
+        if mode == "peer":
+            disp_bytes = dec.dispatch_bytes(ROWS)
 
-        def step(x):
-            moe.router_fused(x, wt, bias, None, None, sel, rw, TOPK, 1.0)
-            dec.step(x, sel, rw, f)
+            def step(x):                        # x: this rank's rows
+                if n_own:
+                    moe.router_fused(x, wt, bias, None, None, sel_o, rw_o, TOPK, 1.0)
+                dec.step_dp(x, sel_o, rw_o, f_o, ROWS)
+            inputs, hosts, x_dev, out_dev = xo, xo_host, xo_in, f_o
+        else:
+            def step(x):                        # x: all rows
+                moe.router_fused(x, wt, bias, None, None, sel, rw, TOPK, 1.0)
+                dec.step(x, sel, rw, f)
+            inputs, hosts, x_dev, out_dev = xs, xs_host, x_in, f
 
         for i in range(warmup):
-            step(xs[i % NBATCH])
+            step(inputs[i % NBATCH])
         torch.cuda.synchronize(); dist.barrier()
-        f.zero_(); step(xs[0]); torch.cuda.synchronize()
-        outs[mode] = f.clone(); f.zero_()                   # one step's output, for the cross-check of the two combines
+        out_dev.zero_(); step(inputs[0]); torch.cuda.synchronize()
+        outs[mode] = (f[own] if mode == "nccl" else f_o[:n_own]).clone(); out_dev.zero_()     # this rank's rows of one step, for the cross-check
         dist.barrier()
         graph = (not args.no_graph) and mode == "peer"      # NCCL calls are left eager
-        run_step, per_step = make_graphed(step, xs, torch, moe, graph)
+        run_step, per_step = make_graphed(step, inputs, torch, moe, graph)
         for i in range(warmup):
             run_step(i % NBATCH)
         torch.cuda.synchronize(); dist.barrier()
@@ -654,7 +751,7 @@ def ep_decode_arm(args, world, rank, dev, tabs, pl, torch, dist, ep, moe, synth)
         launches = per_step * steps
 
         def e2e_step(b):
-            x_in.copy_(xs_host[b], non_blocking=True); step(x_in); f_host.copy_(f, non_blocking=True)
+            x_dev.copy_(hosts[b], non_blocking=True); step(x_dev); f_host[:out_dev.shape[0]].copy_(out_dev, non_blocking=True)
         run_e2e, _ = make_graphed(e2e_step, list(range(NBATCH)), torch, moe, graph)
         for i in range(3):
             run_e2e(i % NBATCH)
@@ -670,12 +767,13 @@ def ep_decode_arm(args, world, rank, dev, tabs, pl, torch, dist, ep, moe, synth)
         del run_step, run_e2e
         if dec.peer is not None:
             dist.barrier(); dec.peer.close()
-    # load balance of the last batch: distinct local experts per rank
+    # load balance of the last batch: distinct local experts per rank (sel holds the replicated routing of the nccl arm's last step)
     mine = (sel >= pl["lo"]) & (sel < pl["lo"] + pl["n_local"])
     d_local = torch.tensor([float(torch.unique(sel[mine]).numel()) if bool(mine.any()) else 0.0], device=dev)
     d_all = [torch.zeros_like(d_local) for _ in range(world)]
     dist.all_gather(d_all, d_local)
-    e = errors(outs["peer"].cpu().numpy(), outs["nccl"].cpu().numpy())
+    e = torch.tensor(list(errors(outs["peer"].cpu().numpy(), outs["nccl"].cpu().numpy())) if n_own else [0.0, 0.0, 0.0], device=dev, dtype=torch.float64)
+    dist.all_reduce(e, op=dist.ReduceOp.MAX)
     if rank != 0:
         return None
     r = results["peer"]
@@ -686,17 +784,18 @@ def ep_decode_arm(args, world, rank, dev, tabs, pl, torch, dist, ep, moe, synth)
         "metric": METRIC, "value": ROWS / (r["ms"] * 1e-3), "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": r["ms"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int4 x fp16 -> fp32",
         "data": "synthetic",
-        "config": {"workload": WORKLOAD + f"; experts split over {world} GPUs ({pl['n_local']} each), rows replicated, "
-                                          "combine over NVLink peer memory",
+        "config": {"workload": WORKLOAD + f"; experts split over {world} GPUs ({pl['n_local']} each), tokens data-parallel ({n_own} rows per GPU), "
+                                          "dispatch and combine as an all-to-all over NVLink peer memory",
                    "l2": "inputs larger than L2: 8 input batches in a ring, each step streams different experts"},
         "us_per_layer": r["ms"] * 1e3, "nccl_allreduce_us_per_layer": results["nccl"]["ms"] * 1e3,
         "distinct_local_experts_last_step": dl, "load_imbalance_max_over_mean": max(dl) / (sum(dl) / len(dl)),
-        "combine_bytes_per_rank": (world - 1) * ROWS * H * 4, "dispatch_bytes_per_rank": 0,
+        "combine_bytes_per_rank": (world - 1) * n_own * H * 4, "dispatch_bytes_per_rank": disp_bytes,
         "roofline": {"bound": "hbm", "kernel": "decode kernels of the most loaded rank (whole call)", "achieved": bytes_rank_max / (r["ms"] * 1e-3) / 1e9,
                      "peak": pk["hbm"], "unit": "GB/s", "frac": bytes_rank_max / (r["ms"] * 1e-3) / 1e9 / pk["hbm"], "peak_kind": pk["kind"], "traffic": None},
-        "e2e": {"value": ROWS / r["e2e"], "unit": UNIT, "h2d_bytes_per_step": ROWS * H * 2, "d2h_bytes_per_step": ROWS * H * 4,
-                "us_per_layer": r["e2e"] * 1e6},
-        "parity_check": {"decode": {"peer_combine_vs_nccl_allreduce": {"max_rel": e[0], "mean_abs": e[1], "norm_rel": e[2], "ok": bool(e[2] < 1e-5)}}},
+        "e2e": {"value": ROWS / r["e2e"], "unit": UNIT, "h2d_bytes_per_step": n_own * H * 2, "d2h_bytes_per_step": n_own * H * 4,
+                "us_per_layer": r["e2e"] * 1e6, "note": "per rank: its own rows in, its own rows' result out"},
+        "parity_check": {"decode": {"peer_all_to_all_vs_nccl_allreduce": {"max_rel": float(e[0]), "mean_abs": float(e[1]), "norm_rel": float(e[2]),
+                                                                          "ok": bool(float(e[2]) < 1e-3)}}},
         "gpu_launches": r["launches"], "device_status": max(r["status"], results["nccl"]["status"]), "clocks": r["clocks"]}
 
 
@@ -787,6 +886,7 @@ def main():
     ap.add_argument("--zipf", type=float, default=1.1, help="prefill expert popularity exponent (0 = uniform)")
     ap.add_argument("--placement", default="auto", choices=["auto", "contiguous", "balanced"],
                     help="N > 1 prefill: expert -> GPU map; auto = balanced by load when the routing is skewed")
+    ap.add_argument("--layers", type=int, default=0, help="N > 1: also run a stack of this many MoE layers (default: 75 at 8 GPUs, else none)")
     ap.add_argument("--experts", type=int, default=E, help="routed experts resident (256 = the benchmark; fewer only for profiling)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -43,8 +43,11 @@ __device__ __forceinline__ float4 ld_peer(const float4* p)
     return v;
 }
 
+// own_rows = 0: f [rows][H] += the sum over all rows (every rank ends with the whole batch, bit-identical). own_rows = 1 (tokens
+// are data-parallel: rank r owns rows r, r + world, ...): f [own rows][H] += the sums of this rank's rows only, an eighth of the
+// peer traffic at 8 GPUs; this is the combine half of the all-to-all.
 __global__ void __launch_bounds__(256) ep_combine_kernel(const EpArgs a, const unsigned* __restrict__ gen_ptr, float* __restrict__ f, int n,
-                                                         size_t slot_floats, unsigned* __restrict__ status)
+                                                         size_t slot_floats, unsigned* __restrict__ status, int own_rows, int H)
 {
     __shared__ int ok_sh;
     const unsigned gen = *gen_ptr;            // bumped by this step's prepare kernel, stable for the rest of the step
@@ -63,14 +66,79 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(const EpArgs a, const u
     if (!ok_sh) return;
     for (int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += gridDim.x * blockDim.x * 4)
     {
-        float4 acc = *(float4*) (f + i);
+        *(float4*) (a.slots[a.rank] + (size_t) (parity ^ 1) * slot_floats + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+        int o = i;                                         // position in f
+        if (own_rows)
+        {
+            const int r = i / H;
+            if (r % a.world != a.rank) continue;
+            o = (r / a.world) * H + (i - r * H);
+        }
+        float4 acc = *(float4*) (f + o);
         for (int p = 0; p < a.world; ++p)
         {
             const float4 v = ld_peer((const float4*) (a.slots[p] + (size_t) parity * slot_floats + i));
             acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
-        *(float4*) (f + i) = acc;
-        *(float4*) (a.slots[a.rank] + (size_t) (parity ^ 1) * slot_floats + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+        *(float4*) (f + o) = acc;
+    }
+}
+
+// Decode dispatch: the all-gather half of the all-to-all, over peer memory. Tokens are data-parallel: rank r holds rows
+// r, r + world, ... of the step's R rows (with the selections and weights its own router produced for them). Block p of the
+// kernel stores this rank's rows into rank p's staging area at their global row positions (x as 16-byte words, then sel and
+// rw), raises this rank's flag there with release semantics at system scope, and waits (bounded) until rank p has raised its
+// flag here: when the kernel ends, the local staging area holds all R rows. The step number lives in the staging area's control
+// words (the last block to finish advances it), so a step has no host state. One staging area suffices: a rank reaches its
+// next dispatch only through its combine, which waits for every peer's combine flag, which a peer raises after the kernels
+// that read its staging area.
+struct StageArgs
+{
+    int rank, world;
+    char* stage[8];
+};
+struct StageLayout
+{
+    size_t x, sel, rw, flags, ctl, total;
+    __host__ __device__ StageLayout(int H, int topk)
+    {
+        x = 0; sel = x + (size_t) MAXR * H * 2; rw = sel + (size_t) MAXR * topk * 8; flags = (rw + (size_t) MAXR * topk * 2 + 255) / 256 * 256;
+        ctl = flags + 256; total = ctl + 256;
+    }
+};
+
+__global__ void __launch_bounds__(256) ep_dispatch_kernel(const StageArgs a, const uint4* __restrict__ x_own, const int64_t* __restrict__ sel_own,
+                                                          const uint16_t* __restrict__ rw_own, int R, int H, int topk, unsigned* __restrict__ status)
+{
+    const StageLayout L(H, topk);
+    const int p = blockIdx.x, tid = threadIdx.x;
+    char* dst = a.stage[p];
+    char* own = a.stage[a.rank];
+    unsigned* ctl = (unsigned*) (own + L.ctl);                     // [0] step number, [1] finished blocks of this launch
+    const unsigned g = *(volatile unsigned*) ctl + 1u;            // advanced only after every block of this launch has read it
+    const int n_own = R > a.rank ? (R - a.rank + a.world - 1) / a.world : 0;
+    const int words = H / 8;                                       // 16-byte words per row
+    for (int i = tid; i < n_own * words; i += blockDim.x)
+    {
+        const int j = i / words, c = i - j * words;
+        ((uint4*) (dst + L.x))[(size_t) (a.rank + j * a.world) * words + c] = x_own[(size_t) j * words + c];
+    }
+    for (int i = tid; i < n_own * topk; i += blockDim.x)
+    {
+        const int j = i / topk, k = i - j * topk, r = a.rank + j * a.world;
+        ((int64_t*) (dst + L.sel))[r * topk + k] = sel_own[i];
+        ((uint16_t*) (dst + L.rw))[r * topk + k] = rw_own[i];
+    }
+    __syncthreads();
+    if (tid == 0)
+    {
+        __threadfence_system();
+        st_release_sys((unsigned*) (dst + L.flags) + a.rank, g);
+        const unsigned long long t0 = globaltimer_ns();
+        while ((int) (ld_acquire_sys((const unsigned*) (own + L.flags) + p) - g) < 0)
+            if (globaltimer_ns() - t0 > 2000000000ull) { atomicOr(status, ST_WAIT_TIMEOUT); break; }
+        __threadfence();
+        if (atomicAdd(ctl + 1, 1u) == gridDim.x - 1) { ctl[1] = 0u; *(volatile unsigned*) ctl = g; }
     }
 }
 
@@ -104,8 +172,25 @@ int ep_barrier_launch(int rank, int world, void* const* flags, unsigned gen, uns
     return err == cudaSuccess ? HMOE_OK : fail(HMOE_E_CUDA, cudaGetErrorString(err));
 }
 
+size_t ep_stage_bytes(int H, int topk) { return StageLayout(H, topk).total; }
+
+int ep_dispatch_launch(int rank, int world, void* const* stage, const void* x_own, const int64_t* sel_own, const void* rw_own, int R, int H, int topk,
+                       unsigned* status, cudaStream_t st)
+{
+    if (world < 1 || world > 8 || rank < 0 || rank >= world) return fail(HMOE_E_ARG, "hmoe_ep_dispatch: world must be 1..8");
+    if (!stage || !status || R < 1 || R > MAXR || H % 8 || topk < 1 || topk > TOPK_MAX) return fail(HMOE_E_ARG, "hmoe_ep_dispatch: rows 1..16, H % 8 == 0, topk 1..8");
+    if (R > rank && (!x_own || !sel_own || !rw_own)) return fail(HMOE_E_ARG, "hmoe_ep_dispatch: null pointer");
+    StageArgs a;
+    a.rank = rank; a.world = world;
+    for (int p = 0; p < 8; ++p) a.stage[p] = p < world ? (char*) stage[p] : nullptr;
+    ep_dispatch_kernel<<<world, 256, 0, st>>>(a, (const uint4*) x_own, sel_own, (const uint16_t*) rw_own, R, H, topk, status);
+    count_launches(1);
+    const cudaError_t err = cudaGetLastError();
+    return err == cudaSuccess ? HMOE_OK : fail(HMOE_E_CUDA, cudaGetErrorString(err));
+}
+
 int ep_combine_launch(int rank, int world, void* const* slots, void* const* flags, const unsigned* gen, float* f, int rows, int H, size_t slot_floats,
-                      unsigned* status, cudaStream_t st)
+                      unsigned* status, cudaStream_t st, int own_rows)
 {
     if (world < 1 || world > 8 || rank < 0 || rank >= world) return fail(HMOE_E_ARG, "hmoe_ep_combine: world must be 1..8");
     const int n = rows * H;
@@ -114,7 +199,8 @@ int ep_combine_launch(int rank, int world, void* const* slots, void* const* flag
     a.rank = rank; a.world = world;
     for (int p = 0; p < 8; ++p) { a.slots[p] = p < world ? (float*) slots[p] : nullptr; a.flags[p] = p < world ? (unsigned*) flags[p] : nullptr; }
     const int blocks = (n / 4 + 255) / 256 < 96 ? (n / 4 + 255) / 256 : 96;
-    ep_combine_kernel<<<blocks, 256, 0, st>>>(a, gen, f, n, slot_floats, status);
+    if (H % 4) return fail(HMOE_E_ARG, "hmoe_ep_combine: H must be a multiple of 4");
+    ep_combine_kernel<<<blocks, 256, 0, st>>>(a, gen, f, n, slot_floats, status, own_rows, H);
     count_launches(1);
     const cudaError_t err = cudaGetLastError();
     return err == cudaSuccess ? HMOE_OK : fail(HMOE_E_CUDA, cudaGetErrorString(err));
@@ -163,7 +249,27 @@ int hmoe_ep_close(void* ptr) { return cudaIpcCloseMemHandle(ptr) == cudaSuccess 
 int hmoe_ep_combine(int rank, int world, void* const* slots, void* const* flags, const uint32_t* gen, float* f, int rows, int H, size_t slot_floats,
                     uint32_t* status, void* stream)
 {
-    return ep_combine_launch(rank, world, slots, flags, gen, f, rows, H, slot_floats, status, (cudaStream_t) stream);
+    return ep_combine_launch(rank, world, slots, flags, gen, f, rows, H, slot_floats, status, (cudaStream_t) stream, 0);
+}
+
+int hmoe_ep_combine_own(int rank, int world, void* const* slots, void* const* flags, const uint32_t* gen, float* f_own, int rows, int H,
+                        size_t slot_floats, uint32_t* status, void* stream)
+{
+    return ep_combine_launch(rank, world, slots, flags, gen, f_own, rows, H, slot_floats, status, (cudaStream_t) stream, 1);
+}
+
+size_t hmoe_ep_stage_bytes(int H, int topk) { return ep_stage_bytes(H, topk); }
+int hmoe_ep_stage_offsets(int H, int topk, size_t* x_off, size_t* sel_off, size_t* rw_off)
+{
+    if (!x_off || !sel_off || !rw_off) return fail(HMOE_E_ARG, "hmoe_ep_stage_offsets: null pointer");
+    const StageLayout L(H, topk);
+    *x_off = L.x; *sel_off = L.sel; *rw_off = L.rw;
+    return HMOE_OK;
+}
+int hmoe_ep_dispatch(int rank, int world, void* const* stage, const void* x_own, const int64_t* sel_own, const void* rw_own, int R, int H, int topk,
+                     uint32_t* status, void* stream)
+{
+    return ep_dispatch_launch(rank, world, stage, x_own, sel_own, rw_own, R, H, topk, status, (cudaStream_t) stream);
 }
 
 int hmoe_ep_memset(void* ptr, int value, size_t bytes, void* stream)

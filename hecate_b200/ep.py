@@ -1,6 +1,8 @@
-"""Expert-parallel decode over the GPUs of one box: one process per GPU (torch.distributed for the set-up plumbing), experts
-split by contiguous id ranges, the step's rows replicated on every rank, partial outputs combined over NVLink peer memory
-by `hmoe_ep_combine` (or, as the baseline, by an NCCL all-reduce).
+"""Expert parallelism over the GPUs of one box: one process per GPU (torch.distributed for the set-up plumbing), experts split
+by contiguous id ranges. Decode: either the step's rows are replicated on every rank (`EpDecoder.step`, partial outputs combined
+over NVLink peer memory by `hmoe_ep_combine`, or, as the baseline, by an NCCL all-reduce), or the tokens are data-parallel
+(`EpDecoder.step_dp`): every rank routes its own rows, `hmoe_ep_dispatch` all-gathers rows, selections and weights through peer
+memory, and `hmoe_ep_combine_own` brings back each rank's own rows: the two halves of the all-to-all. Prefill: `EpPrefill`.
 
 The reference has no expert parallelism; the shape kept from it is its band split: every band receives all rows with
 (sel, rw), ignores foreign ids and returns an fp32 partial that is added in a fixed order (runtime/tier/tier_split.py:3-11,
@@ -27,11 +29,14 @@ class PeerBuffers:
     """Symmetric buffers of the combine: per rank two fp32 partial slots [MAX_ROWS * H] and `world` generation flags,
     allocated with cudaMalloc by the library, exported with CUDA IPC and opened by every peer."""
 
-    def __init__(self, rank, world, H, device, dist, slot_floats=None):
+    def __init__(self, rank, world, H, device, dist, slot_floats=None, stage_topk=0):
         import torch
         self.rank, self.world, self.H = rank, world, H
         self.slot_floats = MAX_ROWS * H if slot_floats is None else (slot_floats + 63) // 64 * 64
         self.bytes = 2 * self.slot_floats * 4 + 512          # two slots, `world` flags (256 B), the generation word (256 B)
+        self.stage_off = self.bytes                          # optional: the staging area of the decode dispatch
+        if stage_topk:
+            self.bytes += lib().hmoe_ep_stage_bytes(C.c_int(H), C.c_int(stage_topk))
         p = C.c_void_p()
         check(lib().hmoe_ep_alloc(C.c_size_t(self.bytes), C.byref(p)))
         self.own = p.value
@@ -51,6 +56,11 @@ class PeerBuffers:
         self.flags = (C.c_void_p * world)(*[b + 2 * self.slot_floats * 4 for b in self.base])
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.gen_ptr = self.own + 2 * self.slot_floats * 4 + 256
+        if stage_topk:
+            self.stage = (C.c_void_p * world)(*[b + self.stage_off for b in self.base])
+            offs = [C.c_size_t() for _ in range(3)]
+            check(lib().hmoe_ep_stage_offsets(C.c_int(H), C.c_int(stage_topk), *[C.byref(o) for o in offs]))
+            self.stage_x, self.stage_sel, self.stage_rw = (self.own + self.stage_off + o.value for o in offs)
         dist.barrier()
 
     def close(self):
@@ -69,19 +79,21 @@ class EpDecoder:
         assert tables.n == self.plan["n_local"]
         self.ws = moe.decode_workspace(tables.H, tables.I, device)
         self.use_peer = use_peer and world > 1
-        self.peer = PeerBuffers(rank, world, tables.H, device, dist) if self.use_peer else None
+        self.peer = PeerBuffers(rank, world, tables.H, device, dist, stage_topk=tables.topk) if self.use_peer else None
         import torch
         self.y = torch.zeros(MAX_ROWS, tables.H, dtype=torch.float32, device=device)
         self.struct = tables.struct()
 
-    def step(self, x, sel, rw, f):
-        """f[R][H] (fp32) += the layer's output for rows x with global routing (sel, rw); identical on every rank."""
+    def step(self, x, sel, rw, f, tables=None):
+        """f[R][H] (fp32) += the layer's output for rows x with global routing (sel, rw); identical on every rank. The rows are
+        replicated (every rank passes all of them)."""
         import torch
         R = x.shape[0]
         st = C.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)
         pl = self.plan
+        struct = self.struct if tables is None else tables.struct()
         if self.use_peer:
-            check(lib().hmoe_decode_ep(C.byref(self.struct), vp(x), C.c_int(moe._dt(x)), vp(sel), vp(rw), C.c_int(R), C.c_int(pl["lo"]),
+            check(lib().hmoe_decode_ep(C.byref(struct), vp(x), C.c_int(moe._dt(x)), vp(sel), vp(rw), C.c_int(R), C.c_int(pl["lo"]),
                                        C.c_int(pl["n_local"]), C.c_int(0), C.c_void_p(self.peer.own), vp(self.ws),
                                        C.c_size_t(self.ws.numel()), C.c_int(pl["shared_mod"]), C.c_int(pl["shared_rem"]),
                                        C.c_void_p(self.peer.gen_ptr), C.c_size_t(self.peer.slot_floats), st))
@@ -89,13 +101,43 @@ class EpDecoder:
                                         vp(f), C.c_int(R), C.c_int(self.tabs.H), C.c_size_t(self.peer.slot_floats), vp(self.peer.status), st))
         else:
             y = self.y[:R]
-            check(lib().hmoe_decode_ep(C.byref(self.struct), vp(x), C.c_int(moe._dt(x)), vp(sel), vp(rw), C.c_int(R), C.c_int(pl["lo"]),
+            check(lib().hmoe_decode_ep(C.byref(struct), vp(x), C.c_int(moe._dt(x)), vp(sel), vp(rw), C.c_int(R), C.c_int(pl["lo"]),
                                        C.c_int(pl["n_local"]), C.c_int(0), vp(y), vp(self.ws), C.c_size_t(self.ws.numel()),
                                        C.c_int(pl["shared_mod"]), C.c_int(pl["shared_rem"]), None, C.c_size_t(0), st))
             if self.world > 1:
                 self.dist.all_reduce(y)
             moe.moe4_combine(f, 0, y, R, 0)
         return f
+
+    def own_rows(self, R):
+        """Rows of a step that this rank holds when the tokens are data-parallel: rank, rank + world, ..."""
+        return list(range(self.rank, R, self.world))
+
+    def step_dp(self, x_own, sel_own, rw_own, f_own, R, tables=None):
+        """Data-parallel tokens: x_own [n][H], sel_own, rw_own are this rank's rows (rows rank, rank + world, ... of the step's R
+        rows) with the routing its own router call produced; f_own [n][H] (fp32) += their layer output. Dispatch and combine are
+        the two halves of an all-to-all over NVLink peer memory (hmoe_ep_dispatch, hmoe_ep_combine_own). `tables`: another layer's
+        experts through the same buffers (a stack of layers shares one set)."""
+        import torch
+        if not self.use_peer:
+            raise RuntimeError("step_dp needs the peer-memory buffers")
+        st = C.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)
+        pl, pb = self.plan, self.peer
+        struct = self.struct if tables is None else tables.struct()
+        H, topk = self.tabs.H, self.tabs.topk
+        check(lib().hmoe_ep_dispatch(C.c_int(self.rank), C.c_int(self.world), pb.stage, vp(x_own), vp(sel_own), vp(rw_own), C.c_int(R), C.c_int(H),
+                                     C.c_int(topk), vp(pb.status), st))
+        check(lib().hmoe_decode_ep(C.byref(struct), C.c_void_p(pb.stage_x), C.c_int(moe._dt(x_own)), C.c_void_p(pb.stage_sel), C.c_void_p(pb.stage_rw),
+                                   C.c_int(R), C.c_int(pl["lo"]), C.c_int(pl["n_local"]), C.c_int(0), C.c_void_p(pb.own), vp(self.ws),
+                                   C.c_size_t(self.ws.numel()), C.c_int(pl["shared_mod"]), C.c_int(pl["shared_rem"]), C.c_void_p(pb.gen_ptr),
+                                   C.c_size_t(pb.slot_floats), st))
+        check(lib().hmoe_ep_combine_own(C.c_int(self.rank), C.c_int(self.world), pb.slots, pb.flags, C.c_void_p(pb.gen_ptr), vp(f_own), C.c_int(R),
+                                        C.c_int(H), C.c_size_t(pb.slot_floats), vp(pb.status), st))
+        return f_own
+
+    def dispatch_bytes(self, R, itemsize=2):
+        """Bytes this rank sends to other ranks per step in step_dp (rows, selections, weights)."""
+        return (self.world - 1) * len(self.own_rows(R)) * (self.tabs.H * itemsize + self.tabs.topk * 10)
 
     def status(self):
         import torch

@@ -102,6 +102,24 @@ int hmoe_ep_close(void* ptr);
 int hmoe_ep_combine(int rank, int world, void* const* slots, void* const* flags, const uint32_t* gen, float* f, int rows, int H, size_t slot_floats,
                     uint32_t* status, void* stream);
 
+/* The token exchange of expert-parallel decode as an all-to-all over NVLink peer memory (no reference counterpart as such; the
+ * shape kept is the reference's mailbox: a per-layer slot with the rows, their selections and weights, and an ISSUE flag stored
+ * with release semantics at system scope, runtime/tier/moe4/moe4.cu:719-738, runtime/tier/rtx_graph.py:105-134). Tokens are
+ * data-parallel: of a step's R <= 16 rows, rank r holds rows r, r + world, ... (x_own [n][H] 2-byte elements, sel_own int64
+ * [n][topk], rw_own fp16 [n][topk], compact, produced by the rank's own router call).
+ * hmoe_ep_dispatch: stores the rank's rows into every rank's staging area (stage[p] = rank p's area as seen from this process,
+ * hmoe_ep_stage_bytes(H, topk) bytes from hmoe_ep_alloc, zero at start), raises its flag there and waits, at most 2 s (then bit 0
+ * of *status), until every rank's rows have arrived here. Afterwards the local area holds x [R][H], sel [R][topk], rw [R][topk] at
+ * the offsets hmoe_ep_stage_offsets returns: the inputs of hmoe_decode_ep. All ranks must make the same sequence of steps, each
+ * followed by a combine (which is what makes a single staging area enough).
+ * hmoe_ep_combine_own: hmoe_ep_combine for data-parallel tokens: f_own [n][H] += the sums of this rank's rows only. */
+size_t hmoe_ep_stage_bytes(int H, int topk);
+int hmoe_ep_stage_offsets(int H, int topk, size_t* x_off, size_t* sel_off, size_t* rw_off);
+int hmoe_ep_dispatch(int rank, int world, void* const* stage, const void* x_own, const int64_t* sel_own, const void* rw_own, int R, int H, int topk,
+                     uint32_t* status, void* stream);
+int hmoe_ep_combine_own(int rank, int world, void* const* slots, void* const* flags, const uint32_t* gen, float* f_own, int rows, int H,
+                        size_t slot_floats, uint32_t* status, void* stream);
+
 /* Prefill permutation on the device: replaces the host-side code of runtime/tier/tier_split.py:404-412,433-455 (stable argsort
  * of the flattened selection by expert id, bincount with a host sync) and pick_groups (runtime/tier/rtx_split.py:236-255, one
  * pick group) with three kernels and no synchronisation. Picks with ids outside [lo, lo + n_local) are dropped.

@@ -73,6 +73,20 @@ def _rank_main(rank, world, port, out_path):
         res[mode] = torch.stack(outs)
         if dec.peer is not None:
             dist.barrier(); dec.peer.close()
+    # data-parallel tokens: every rank passes only its own rows (rank, rank + world, ...); dispatch and combine over peer memory
+    dec = EpDecoder(rank, world, local, E, dev, dist, use_peer=True)
+    own = dec.own_rows(R)
+    outs = []
+    for stepi in range(4):
+        sel, rw = synth.zipf_routing(10 + stepi, 0, R, E, 8, 0.0)
+        f_own = torch.zeros(len(own), H, device=dev)
+        dec.step_dp(x[own].contiguous(), torch.from_numpy(sel[own]).to(dev), torch.from_numpy(rw[own]).to(dev), f_own, R)
+        outs.append(f_own)
+    assert dec.status() == 0 and dec.dispatch_bytes(R) == (world - 1) * len(own) * (H * 2 + 80)
+    dp = torch.stack(outs)
+    dist.barrier(); dec.peer.close()
+    dp_err = torch.tensor([float((dp - res[True][:, own]).abs().max() / res[True].abs().max())], device=dev)
+    dist.all_reduce(dp_err, op=dist.ReduceOp.MAX)
     # all ranks hold the same bits after the peer combine (fixed rank order)
     mine = res[True].clone()
     others = [torch.zeros_like(mine) for _ in range(world)]
@@ -88,7 +102,8 @@ def _rank_main(rank, world, port, out_path):
             moe.decode(full, x, torch.from_numpy(sel).to(dev), torch.from_numpy(rw).to(dev), y, ws)
             refs.append(y)
         ref = torch.stack(refs)
-        np.save(out_path, np.array([float(same), float((res[True] - ref).norm() / ref.norm()), float((res[False] - ref).norm() / ref.norm())]))
+        np.save(out_path, np.array([float(same), float((res[True] - ref).norm() / ref.norm()), float((res[False] - ref).norm() / ref.norm()),
+                                    float(dp_err.item())]))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -100,9 +115,10 @@ def test_two_gpu_peer_combine_matches_single_gpu(tmp_path):
     import torch.multiprocessing as mp
     out = str(tmp_path / "ep.npy")
     mp.spawn(_rank_main, args=(2, 29600 + os.getpid() % 2000, out), nprocs=2, join=True)
-    same, err_peer, err_nccl = np.load(out)
+    same, err_peer, err_nccl, err_dp = np.load(out)
     assert same == 1.0
     assert err_peer < 1e-3 and err_nccl < 1e-3
+    assert err_dp < 1e-3                 # dispatched rows give what replicated rows give (the sums differ only in their atomic order)
 
 
 def _prefill_rank_main(rank, world, port, out_path):
@@ -131,6 +147,20 @@ def _prefill_rank_main(rank, world, port, out_path):
             ep.step(torch.from_numpy(xa[sl]).to(dev).to(torch.bfloat16), torch.from_numpy(sel[sl]).to(dev), torch.from_numpy(rw[sl]).to(dev), out)
         assert ep.status() == 0
         outs[use_peer] = out
+    # A placement by load with copies of the hottest experts (hecate_b200.placement): rank r loads the experts at positions
+    # [r * slots, (r + 1) * slots) of the plan, the selection is expressed in positions; the result must be the contiguous one.
+    from hecate_b200 import placement as PL
+    plan = PL.balance(PL.pick_counts(sel, E), world, extra_slots=2)
+    ids = plan.perm[rank * plan.slots:(rank + 1) * plan.slots]
+    placed = HostLayer(0, 0, H, I, ids, 128, True).upload(dev)
+    selp = PL.positions(sel, plan)
+    assert max(len(c) for c in plan.copies) > 1 and plan.imbalance() <= PL.contiguous(PL.pick_counts(sel, E), world).imbalance()
+    ep = EpPrefill(rank, world, placed, len(plan.perm), rpr, dev, dist, use_peer=True)
+    out_p = torch.empty(rpr, H, device=dev)
+    ep.step(torch.from_numpy(xa[sl]).to(dev).to(torch.bfloat16), torch.from_numpy(selp[sl]).to(dev), torch.from_numpy(rw[sl]).to(dev), out_p)
+    assert ep.status() == 0
+    gathered_placed = [torch.empty_like(out_p) for _ in range(world)]
+    dist.all_gather(gathered_placed, out_p)
     gathered = [torch.empty_like(out) for _ in range(world)]
     dist.all_gather(gathered, outs[True])
     gathered_nccl = [torch.empty_like(out) for _ in range(world)]
@@ -140,8 +170,9 @@ def _prefill_rank_main(rank, world, port, out_path):
         ws = moe.prefill_workspace(R, 8, E, H, I, dev)
         ref = torch.zeros(R, H, device=dev)
         moe.prefill(full, torch.from_numpy(xa).to(dev).to(torch.bfloat16), torch.from_numpy(sel).to(dev), torch.from_numpy(rw).to(dev), ref, ws)
-        got = torch.cat(gathered); got_nccl = torch.cat(gathered_nccl)
-        np.save(out_path, np.array([float((got - ref).norm() / ref.norm()), float((got_nccl - ref).norm() / ref.norm())]))
+        got = torch.cat(gathered); got_nccl = torch.cat(gathered_nccl); got_placed = torch.cat(gathered_placed)
+        np.save(out_path, np.array([float((got - ref).norm() / ref.norm()), float((got_nccl - ref).norm() / ref.norm()),
+                                    float((got_placed - ref).norm() / ref.norm())]))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -155,3 +186,4 @@ def test_two_gpu_prefill_matches_single_gpu(tmp_path):
     mp.spawn(_prefill_rank_main, args=(2, 29700 + os.getpid() % 2000, out), nprocs=2, join=True)
     e = np.load(out)
     assert e[0] < 1e-3 and e[1] < 1e-3, e        # peer-memory combine, NCCL reduce-scatter combine
+    assert e[2] < 1e-3, e                         # experts placed by load with copies: same result as contiguous ids
