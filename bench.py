@@ -7,8 +7,8 @@ One MoE layer of the benchmark definition: hidden 6144, 256 routed experts, top-
 SwiGLU experts gate/up [2048 x 6144] and down [6144 x 2048] in packed int4 with a bf16 scale per 128 input columns. Inputs are
 synthetic (seeded): codes uniform, scales lognormal(-4, 0.5), activations N(0, 1) in bf16, router weight N(0, 0.02) in bf16.
 
-The headline line is the DECODE configuration (8 tokens x (1 + 1 MTP draft) = 16 rows): a step = router -> prepare -> gate_up
-(+ SiLU * up * weight) -> down -> combine into the fp32 layer output. `value` is rows/s with inputs resident in HBM, `e2e` the
+The headline line is the DECODE configuration (8 tokens x (1 + 1 MTP draft) = 16 rows): a step = router (whose launch also does the
+expert kernels' set-up) -> gate_up (+ SiLU * up * weight) -> down -> combine into the fp32 layer output. `value` is rows/s with inputs resident in HBM, `e2e` the
 same call chain fed from pinned host memory with the host<->device copies inside the timed region. Consecutive steps use
 different input batches (8 in a ring), so each step streams a different ~2 GB of the 4.85 GB layer, far more than the L2.
 
@@ -310,8 +310,7 @@ def decode_arm(args, dev, layer, torch, moe, synth, O):
     aq = [False]
 
     def step(x):
-        moe.router_fused(x, wt, bias, None, None, sel, rw, TOPK, 1.0)
-        moe.decode(tabs, x, sel, rw, y, ws, act_quant=aq[0])
+        moe.router_decode(tabs, x, wt, bias, sel, rw, 1.0, y, ws, act_quant=aq[0])      # router (+ set-up) -> gate_up -> down
         moe.moe4_combine(f, 0, y, ROWS, 0)
 
     distinct, routes = [], []

@@ -5,6 +5,7 @@
 #include <cstring>
 #include "hmoe_common.cuh"
 #include "hmoe_internal.h"
+#include "hmoe_prepare.cuh"
 
 namespace hmoe {
 
@@ -180,6 +181,19 @@ int hmoe_decode(const hmoe_layer* layer, const void* x, int x_dtype, const int64
     return decode_launch(layer, x, x_dtype, sel, rw, R, lo, n_local, act_quant, y, ws, ws_bytes, (cudaStream_t) stream);
 }
 
+int hmoe_router_decode(const hmoe_layer* layer, const void* x, int x_dtype, const void* wt, int w_dtype, const float* bias, int R, int E, float scale,
+                       int64_t* sel, void* rw, void* router_ws, size_t router_ws_bytes, int lo, int n_local, int act_quant, float* y, void* ws,
+                       size_t ws_bytes, void* stream)
+{
+    if (!layer) return fail(HMOE_E_ARG, "hmoe_router_decode: null layer");
+    PrepArgs pa;
+    int rc = decode_prep_args(layer, x, x_dtype, R, lo, n_local, act_quant, ws, ws_bytes, 1, 0, nullptr, &pa);
+    if (rc) return rc;
+    rc = router_prepare_launch(x, x_dtype, wt, w_dtype, bias, R, layer->H, E, layer->topk, scale, sel, rw, router_ws, router_ws_bytes, pa, (cudaStream_t) stream);
+    if (rc) return rc;
+    return decode_launch(layer, x, x_dtype, sel, rw, R, lo, n_local, act_quant, y, ws, ws_bytes, (cudaStream_t) stream, 1, 0, nullptr, 0, true);
+}
+
 size_t hmoe_prefill_ws_bytes(int R, int topk, int n_local, int H, int I, int act_quant) { return prefill_ws_bytes(R, topk, n_local, H, I, act_quant); }
 int hmoe_prefill(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
                  int act_quant, float* out, void* ws, size_t ws_bytes, void* stream)
@@ -230,6 +244,17 @@ int hmoe_decode_ep(const hmoe_layer* layer, const void* x, int x_dtype, const in
     if (!layer) return fail(HMOE_E_ARG, "hmoe_decode_ep: null layer");
     return decode_launch(layer, x, x_dtype, sel, rw, R, lo, n_local, act_quant, y, ws, ws_bytes, (cudaStream_t) stream, shared_mod, shared_rem,
                          gen, slot_floats);
+}
+
+int hmoe_decode_ep_combine(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
+                           int act_quant, void* ws, size_t ws_bytes, int shared_mod, int shared_rem, uint32_t* gen, size_t slot_floats, int rank,
+                           int world, void* const* slots, void* const* flags, float* f, int own_rows, uint32_t* status, void* stream)
+{
+    if (!layer) return fail(HMOE_E_ARG, "hmoe_decode_ep_combine: null layer");
+    if (!slots || rank < 0 || rank >= world || world > 8) return fail(HMOE_E_ARG, "hmoe_decode_ep_combine: rank / world / slots");
+    EpCombineArgs e = {rank, world, own_rows, slots, flags, f, status};
+    return decode_launch(layer, x, x_dtype, sel, rw, R, lo, n_local, act_quant, (float*) slots[rank], ws, ws_bytes, (cudaStream_t) stream, shared_mod,
+                         shared_rem, gen, slot_floats, false, &e);
 }
 
 int hmoe_combine(float* f, const float* o, float* y, int64_t n, const float* o2, void* stream)

@@ -22,6 +22,7 @@
 // packed size plus scales.
 #include "hmoe_common.cuh"
 #include "hmoe_internal.h"
+#include "hmoe_prepare.cuh"
 
 namespace hmoe {
 
@@ -47,210 +48,16 @@ struct SmemLayout
 };
 
 // ---------------------------------------------------------------------------------------------------------------------
-// prepare
-__global__ void __launch_bounds__(256) decode_prepare_kernel(const void* __restrict__ x, int x_kind /* 0 fp16, 1 bf16, 2 fp16 in MMA column order */, const int64_t* __restrict__ sel,
+// prepare (the device code is in hmoe_prepare.cuh; the router can run it inside its own launch instead)
+__global__ void __launch_bounds__(256) decode_prepare_kernel(const void* __restrict__ x, int x_kind, const int64_t* __restrict__ sel,
     const __half* __restrict__ rw, int R, int H, int topk, int lo, int n_local, int has_shared, int act_quant,
     __half* __restrict__ xf, float* __restrict__ xscale, Route* __restrict__ route, int sh_mod, int sh_rem, unsigned* gen_bump,
     float4* __restrict__ gzero, int gzero_n, int I, int nblocks)
 {
-    const int tid = threadIdx.x;
+    __shared__ RouteSmem S;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // the next kernel's blocks may set up while this one runs
-    if ((int) blockIdx.x < R)
-    {
-        const int r = blockIdx.x;
-        // this row's share of the gate / up sums is cleared for the streaming kernels' reductions (gzero_n float4 per row block)
-        for (int i = tid; i < gzero_n; i += blockDim.x) gzero[(size_t) r * gzero_n + i] = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int gi = tid; gi < H / 32; gi += blockDim.x)
-        {
-            float v[32];
-            if (x_kind == 2)
-            {
-                // fp16 rows that already are in the MMA column order (the copy the reference's norm + router kernel can write for
-                // moe4, its xf argument): word p of the 64-column block sits at frag_pos(p)
-                const uint32_t* src = (const uint32_t*) ((const uint16_t*) x + (size_t) r * H + (gi >> 1) * 64);
-                #pragma unroll
-                for (int p = 0; p < 16; ++p)
-                {
-                    const uint32_t w = src[frag_pos((gi & 1) * 16 + p)];
-                    const float2 f = __half22float2(*(const __half2*) &w);
-                    v[2 * p] = f.x; v[2 * p + 1] = f.y;
-                }
-            }
-            else
-            {
-                const uint4* p = (const uint4*) ((const uint16_t*) x + (size_t) r * H + gi * 32);
-                #pragma unroll
-                for (int j = 0; j < 4; ++j)
-                {
-                    const uint4 u = p[j];
-                    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-                    #pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                    {
-                        if (x_kind == 1) { v[j * 8 + 2 * k] = __uint_as_float(w[k] << 16); v[j * 8 + 2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u); }
-                        else { const float2 f = __half22float2(*(const __half2*) &w[k]); v[j * 8 + 2 * k] = f.x; v[j * 8 + 2 * k + 1] = f.y; }
-                    }
-                }
-            }
-            if (act_quant)
-            {
-                // the CPU engine's activation format (runtime/tier/cpuband.cpp:106-111): int8 with a scale per 32 values.
-                // The codes themselves go to the MMAs (exact in fp16), the scale is applied to the fp32 sums.
-                float m = 0.f;
-                #pragma unroll
-                for (int k = 0; k < 32; ++k) m = fmaxf(m, fabsf(v[k]));
-                const float s = m > 0.f ? __fdiv_rn(m, 127.f) : 1.f;
-                const float inv = __fdiv_rn(1.f, s);
-                #pragma unroll
-                for (int k = 0; k < 32; ++k) v[k] = (float) __float2int_rn(__fmul_rn(v[k], inv));
-                xscale[(size_t) r * (H / 32) + gi] = s;
-            }
-            const int kb = gi >> 1, p0 = (gi & 1) * 16;
-            uint32_t* dst = (uint32_t*) (xf + (size_t) r * H + kb * 64);
-            #pragma unroll
-            for (int p = 0; p < 16; ++p)
-            {
-                const __half2 h = __floats2half2_rn(v[2 * p], v[2 * p + 1]);
-                dst[frag_pos(p0 + p)] = *(const uint32_t*) &h;
-            }
-        }
-        return;
-    }
-    // routing block: slot = distinct expert (ascending id), then the shared expert; tiles of <= 8 rows per slot.
-    // Everything is done in parallel with block-wide prefix sums: this block is the critical path of the call (the
-    // streaming kernel's blocks are already resident and wait for it).
-    __shared__ short slot_of[256];                        // local expert id -> slot, -1 if not picked
-    __shared__ short slot_e[MAXS];
-    __shared__ unsigned s_mask[MAXS];                     // rows of the slot, one bit each
-    __shared__ unsigned char s_rows[MAXS][MAXR];
-    __shared__ float s_w[MAXS][MAXR];
-    __shared__ int s_scan[4][256];                        // per slot: tiles, rows, cost in gate_up, cost in down (then their prefix sums)
-    __shared__ int s_cum[2][MAXT + 1];
-    __shared__ short s_sel[MAXR * TOPK_MAX];
-    __shared__ float s_rw[MAXR * TOPK_MAX];
-    __shared__ int wcount[8];
-    __shared__ int m_sh;
-    const int NP = R * topk;
-    slot_of[tid] = 0;                                      // used as the picked flag first
-    if (tid < MAXS) s_mask[tid] = 0u;
-    __syncthreads();
-    if (tid < NP)
-    {
-        const int64_t e = sel[tid] - lo;
-        const bool in = e >= 0 && e < n_local;
-        s_sel[tid] = in ? (short) e : (short) -1;
-        s_rw[tid] = __half2float(rw[tid]);
-        if (in) slot_of[(int) e] = 1;
-    }
-    __syncthreads();
-    {
-        // distinct experts in ascending order: one flag per thread, ballots per warp, prefix over the eight warps
-        const bool picked = slot_of[tid] != 0;
-        const unsigned bl = __ballot_sync(0xffffffffu, picked);
-        if ((tid & 31) == 0) wcount[tid >> 5] = __popc(bl);
-        __syncthreads();
-        int before = 0, m = 0;
-        for (int w = 0; w < 8; ++w) { if (w < (tid >> 5)) before += wcount[w]; m += wcount[w]; }
-        const int slot = before + __popc(bl & ((1u << (tid & 31)) - 1u));
-        slot_of[tid] = picked ? (short) slot : (short) -1;
-        if (picked) slot_e[slot] = (short) tid;
-        if (tid == 0) { m_sh = m; if (has_shared) slot_e[m] = -1; }
-    }
-    __syncthreads();
-    const int m = m_sh, ns = m + (has_shared ? 1 : 0);
-    // one thread per pick: the first pick of an expert in its row owns the (slot, row) pair and the summed weight
-    int my_slot = -1, my_row = 0; float my_w = 0.f;
-    if (tid < NP && s_sel[tid] >= 0)
-    {
-        const int r = tid / topk, k = tid - r * topk, e = s_sel[tid];
-        bool first = true;
-        for (int k2 = 0; k2 < k; ++k2) first &= s_sel[r * topk + k2] != e;
-        if (first)
-        {
-            for (int k2 = k; k2 < topk; ++k2) if (s_sel[r * topk + k2] == e) my_w += s_rw[r * topk + k2];
-            my_slot = slot_of[e]; my_row = r;
-            atomicOr(&s_mask[my_slot], 1u << r);
-        }
-    }
-    // the shared expert takes every row with weight 1; under expert parallelism only rows r % sh_mod == sh_rem here
-    if (has_shared && tid >= 128 && tid < 128 + R && (tid - 128) % sh_mod == sh_rem) atomicOr(&s_mask[m], 1u << (tid - 128));
-    __syncthreads();
-    if (my_slot >= 0)
-    {
-        const int pos = __popc(s_mask[my_slot] & ((1u << my_row) - 1u));
-        s_rows[my_slot][pos] = (unsigned char) my_row; s_w[my_slot][pos] = my_w;
-    }
-    if (has_shared && tid >= 128 && tid < 128 + R && (tid - 128) % sh_mod == sh_rem)
-    {
-        const int pos = __popc(s_mask[m] & ((1u << (tid - 128)) - 1u));
-        s_rows[m][pos] = (unsigned char) (tid - 128); s_w[m][pos] = 1.f;
-    }
-    // Per slot: tiles, rows, and the cost of its items in the two streaming kernels. The kernels are bound by HBM, but an
-    // item of a tile with many real rows issues more reductions and runs a little longer (measured: 8 rows against 1,
-    // +20 % in down, under +1 % in gate_up); the blocks' item ranges are cut at equal cost so that the blocks that get the
-    // 16-row shared expert do not finish last.
-    const int J0 = 2 * (I / 64), J1 = H / 64;
-    {
-        const int n = tid < ns ? __popc(s_mask[tid]) : 0, full = n >> 3, rest = n & 7;
-        s_scan[0][tid] = (n + 7) >> 3;
-        s_scan[1][tid] = n;
-        s_scan[2][tid] = J0 * (full * (400 + 8) + (rest ? 400 + rest : 0));
-        s_scan[3][tid] = J1 * (full * (100 + 3 * 8) + (rest ? 100 + 3 * rest : 0));
-    }
-    __syncthreads();
-    int incl[4];
-    #pragma unroll 1
-    for (int o = 1; o < 256; o <<= 1)                      // inclusive prefix sums of the four columns
-    {
-        #pragma unroll
-        for (int c = 0; c < 4; ++c) incl[c] = s_scan[c][tid] + (tid >= o ? s_scan[c][tid - o] : 0);
-        __syncthreads();
-        #pragma unroll
-        for (int c = 0; c < 4; ++c) s_scan[c][tid] = incl[c];
-        __syncthreads();
-    }
-    const int nt = s_scan[0][255];
-    if (tid == 0)
-    {
-        route->m = m; route->ntiles = nt; route->pad[0] = route->pad[1] = 0;
-        s_cum[0][nt] = s_scan[2][255]; s_cum[1][nt] = s_scan[3][255];
-        if (gen_bump) *gen_bump += 1;          // expert-parallel step counter: selects the partial slot and the combine's generation
-    }
-    if (tid < ns)
-    {
-        const int n = __popc(s_mask[tid]);
-        int t = incl[0] - ((n + 7) >> 3), rb = incl[1] - n;
-        int c0 = incl[2] - J0 * ((n >> 3) * 408 + ((n & 7) ? 400 + (n & 7) : 0)), c1 = incl[3] - J1 * ((n >> 3) * 124 + ((n & 7) ? 100 + 3 * (n & 7) : 0));
-        for (int b8 = 0; b8 < n; b8 += 8, ++t)
-        {
-            const int nn = n - b8 < 8 ? n - b8 : 8;
-            route->expert[t] = slot_e[tid]; route->nrows[t] = (unsigned char) nn; route->rowbase[t] = (short) (rb + b8);
-            for (int i = 0; i < 8; ++i)
-            {
-                route->rows[t][i] = s_rows[tid][b8 + (i < nn ? i : 0)];
-                route->w[t][i] = i < nn ? s_w[tid][b8 + i] : 0.f;
-            }
-            s_cum[0][t] = c0; s_cum[1][t] = c1;
-            s_scan[0][t] = nn;                 // rows of tile t (the tile counts are no longer needed: every thread holds its own)
-            c0 += J0 * (400 + nn); c1 += J1 * (100 + 3 * nn);
-        }
-    }
-    __syncthreads();
-    for (int i = tid; i < 2 * (nblocks + 1); i += blockDim.x)
-    {
-        const int k = i / (nblocks + 1), b = i % (nblocks + 1), J = k ? J1 : J0;
-        int p = nt * J;
-        if (b < nblocks && nt > 0)
-        {
-            const int target = (int) ((long long) s_cum[k][nt] * b / nblocks);
-            int lo2 = 0, hi = nt - 1;                    // last tile whose start is <= target
-            while (lo2 < hi) { const int mid = (lo2 + hi + 1) >> 1; if (s_cum[k][mid] <= target) lo2 = mid; else hi = mid - 1; }
-            const int item = k ? 100 + 3 * s_scan[0][lo2] : 400 + s_scan[0][lo2];
-            const int off = (target - s_cum[k][lo2]) / item;
-            p = lo2 * J + (off < J ? off : J);
-        }
-        route->split[k][b] = p;
-    }
+    if ((int) blockIdx.x < R) prepare_row(x, x_kind, blockIdx.x, H, act_quant, xf, xscale, gzero, gzero_n, threadIdx.x, blockDim.x);
+    else build_route<false>(S, sel, rw, R, H, I, topk, lo, n_local, has_shared, sh_mod, sh_rem, gen_bump, route, nblocks, threadIdx.x);
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -262,6 +69,80 @@ struct Pre
     uint4 sc;               // GROUPED: bf16 scales of rows strip*16 + g (low half of word `strip`) and + 8 (high half)
     float4 sx[2];           // Q8: activation scales of the group's four 32-column quarters for tile columns 2q and 2q + 1
 };
+
+// The expert-parallel combine, done by the down launch itself when its blocks run out of weights to stream (instead of a kernel
+// of its own after it). The block that finishes last raises this rank's generation in every peer's flag array (release, system
+// scope); every block then waits, bounded, until all peers have raised theirs here, and sums its slice of the peers' partial slots
+// into the layer output in rank order (all rows: identical bits on every rank; or only the rows this rank owns when the tokens
+// are data-parallel), and clears its slice of the other slot for the step after next. Blocks that finish early wait on SMs that
+// would otherwise idle: the tail costs one flag round trip and one round of peer loads after the slowest rank's last weight.
+struct EpTail
+{
+    int rank, world, own_rows, n;     // n = rows * H
+    float* slots[8];                  // slots[p] = rank p's two partial slots as seen from here
+    unsigned* flags[8];               // flags[p] = rank p's flag array [world]
+    float* f;                         // layer output, added into
+    unsigned* done;                   // arrival counter of this launch's blocks (in the workspace, returns to zero)
+    unsigned* status;                 // status word for a wait that gives up
+};
+
+__device__ __forceinline__ void ep_st_release_sys(unsigned* p, unsigned v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ unsigned ep_ld_acquire_sys(const unsigned* p)
+{
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ float4 ep_ld_peer(const float4* p)
+{
+    float4 v;
+    asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
+// called by all threads of every block of the down launch, after the block's last reduction has been issued
+__device__ __forceinline__ void ep_tail_combine(const EpTail& e, unsigned gen, size_t slot_floats, int H)
+{
+    __shared__ int ok_sh;
+    __syncthreads();
+    if (threadIdx.x == 0)
+    {
+        __threadfence();
+        if (atomicAdd(e.done, 1u) == gridDim.x - 1)
+        {
+            *e.done = 0u;
+            __threadfence_system();
+            for (int p = 0; p < e.world; ++p) ep_st_release_sys(e.flags[p] + e.rank, gen);
+        }
+        int ok = 1;
+        const unsigned long long t0 = globaltimer_ns();
+        for (int p = 0; p < e.world && ok; ++p)
+            while ((int) (ep_ld_acquire_sys(e.flags[e.rank] + p) - gen) < 0)
+                if (globaltimer_ns() - t0 > 2000000000ull) { ok = 0; atomicOr(e.status, ST_WAIT_TIMEOUT); break; }
+        ok_sh = ok;
+    }
+    __syncthreads();
+    if (!ok_sh) return;
+    const int parity = gen & 1;
+    for (int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4; i < e.n; i += gridDim.x * blockDim.x * 4)
+    {
+        *(float4*) (e.slots[e.rank] + (size_t) (parity ^ 1) * slot_floats + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+        int o = i;
+        if (e.own_rows)
+        {
+            const int r = i / H;
+            if (r % e.world != e.rank) continue;
+            o = (r / e.world) * H + (i - r * H);
+        }
+        float4 acc = *(float4*) (e.f + o);
+        for (int p = 0; p < e.world; ++p)
+        {
+            const float4 v = ep_ld_peer((const float4*) (e.slots[p] + (size_t) parity * slot_floats + i));
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        *(float4*) (e.f + o) = acc;
+    }
+}
 
 struct DecodeArgs
 {
@@ -278,6 +159,7 @@ struct DecodeArgs
     float* y;              // [R][H] (expert-parallel: base of two slots, the step's slot is chosen by *gen_ptr & 1)
     const unsigned* gen_ptr; size_t slot_stride;
     unsigned* status;
+    EpTail ep;             // expert parallel: the combine over peer memory as the tail of the down launch (world = 0: none)
 };
 
 // Two 64-column blocks (one scale group) of a 64-row group: 4 strips x 8 steps of MMAs on the tile, added into acc with
@@ -961,6 +843,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_stream_kernel(const Decode
     }
     else if (DOWN) { pdl_wait(); pdl_launch_dependents(); }
     __syncthreads();
+    if (DOWN && a.ep.world > 0) ep_tail_combine(a.ep, *a.gen_ptr, a.slot_stride, a.H);
 }
 
 }  // namespace
@@ -1063,8 +946,32 @@ static void launch_pair(int grid, const DecodeArgs& a, int R, cudaStream_t st)
     if (g_prof) { cudaEventRecord(ev[3], st); ++g_prof_calls; }
 }
 
+// The arguments of the set-up step for a call with these parameters (for the router's launch, which can do the step itself).
+int decode_prep_args(const hmoe_layer* L, const void* x, int x_dtype, int R, int lo, int n_local, int act_quant, void* ws, size_t ws_bytes,
+                     int sh_mod, int sh_rem, unsigned* gen_ptr, PrepArgs* pa)
+{
+    const int H = L->H, I = L->I;
+    if (R < 1 || R > MAXR || H % 128 || I % 128 || H < 128 || I < 128 || !ws || ws_bytes < decode_ws_bytes(H, I)) return fail(HMOE_E_ARG, "hmoe_router_decode: shapes or workspace");
+    if (x_dtype != HMOE_F16 && x_dtype != HMOE_BF16) return fail(HMOE_E_ARG, "hmoe_router_decode: x must be fp16 or bf16");
+    const int sms = device_sms();
+    if (sms <= 0) return fail(HMOE_E_CUDA, "hmoe_router_decode: no current CUDA device");
+    char* w = (char*) ws;
+    pa->status = (unsigned*) w; w += 256;
+    pa->route = (Route*) w; w += up256(sizeof(Route));
+    pa->xf = (__half*) w; w += up256((size_t) MAXR * H * 2);
+    pa->xscale = (float*) w; w += up256((size_t) MAXR * (H / 32) * 4);
+    pa->gzero = (float4*) w;
+    pa->gzero_n = (I <= 2048 && H <= 6144) ? (L->topk + 1) * 2 * I / 4 : 0;
+    const bool sh8 = L->shared_format == 1 && L->sh_gate_w != nullptr;
+    pa->x = x; pa->x_kind = x_dtype == HMOE_BF16 ? 1 : 0; pa->act_quant = act_quant;
+    pa->lo = lo; pa->n_local = n_local; pa->has_shared = L->sh_gate_w != nullptr && !sh8; pa->sh_mod = sh_mod; pa->sh_rem = sh_rem;
+    pa->gen_bump = gen_ptr; pa->I = I; pa->nblocks = sms < MAXB ? sms : MAXB;
+    return HMOE_OK;
+}
+
 int decode_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
-                  int act_quant, float* y, void* ws, size_t ws_bytes, cudaStream_t st, int sh_mod, int sh_rem, unsigned* gen_ptr, size_t slot_stride)
+                  int act_quant, float* y, void* ws, size_t ws_bytes, cudaStream_t st, int sh_mod, int sh_rem, unsigned* gen_ptr, size_t slot_stride,
+                  bool prepared, const EpCombineArgs* epc)
 {
     if (sh_mod < 1 || sh_rem < 0 || sh_rem >= sh_mod) return fail(HMOE_E_ARG, "hmoe_decode: shared-row split must satisfy 0 <= rem < mod");
     const int H = L->H, I = L->I;
@@ -1090,7 +997,8 @@ int decode_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t
     if (sh8 && !(I <= 2048 && H <= 6144)) return fail(HMOE_E_UNSUPPORTED, "hmoe_decode: the int8 shared expert needs H <= 6144 and I <= 2048");
     const int has_shared = L->sh_gate_w != nullptr && !sh8;
     if (g_prof) cudaEventRecord(g_ev[g_prof_calls % PROF_RING][0], st);
-    decode_prepare_kernel<<<R + 1, 256, 0, st>>>(x, x_dtype == HMOE_BF16 ? 1 : (x_dtype == HMOE_F16_FRAG ? 2 : 0), sel, (const __half*) rw, R, H, L->topk, lo, n_local, has_shared,
+    // prepared: the router's launch has done the set-up step (hmoe_router_decode)
+    if (!prepared) decode_prepare_kernel<<<R + 1, 256, 0, st>>>(x, x_dtype == HMOE_BF16 ? 1 : (x_dtype == HMOE_F16_FRAG ? 2 : 0), sel, (const __half*) rw, R, H, L->topk, lo, n_local, has_shared,
                                                  act_quant, xf, xscale, route, sh_mod, sh_rem, gen_ptr,
                                                  (float4*) act, (I <= 2048 && H <= 6144) ? (L->topk + 1) * 2 * I / 4 : 0, I, g_sms < MAXB ? g_sms : MAXB);
     if (sh8)
@@ -1107,13 +1015,24 @@ int decode_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t
     a.sh_gs = sh8 ? nullptr : L->sh_gate_s; a.sh_us = sh8 ? nullptr : L->sh_up_s; a.sh_ds = sh8 ? nullptr : L->sh_down_s;
     a.route = route; a.xf = xf; a.xscale = xscale; a.act = act; a.ascale = ascale; a.G = (float*) act; a.y = y; a.status = status;
     a.gen_ptr = gen_ptr; a.slot_stride = slot_stride;
+    a.ep = EpTail();
+    if (epc)
+    {
+        if (!gen_ptr || !(I <= 2048 && H <= 6144)) return fail(HMOE_E_UNSUPPORTED, "hmoe_decode_ep_combine: needs the step counter and H <= 6144, I <= 2048");
+        if (epc->world < 1 || epc->world > 8 || epc->rank < 0 || epc->rank >= epc->world || !epc->f || !epc->slots || !epc->flags || !epc->status || H % 4 ||
+            (size_t) R * H > slot_stride)
+            return fail(HMOE_E_ARG, "hmoe_decode_ep_combine: world 1..8, buffers, rows * H <= slot_floats");
+        a.ep.rank = epc->rank; a.ep.world = epc->world; a.ep.own_rows = epc->own_rows; a.ep.n = R * H; a.ep.f = epc->f;
+        a.ep.done = status + 4; a.ep.status = epc->status;
+        for (int p = 0; p < 8; ++p) { a.ep.slots[p] = p < epc->world ? (float*) epc->slots[p] : nullptr; a.ep.flags[p] = p < epc->world ? (unsigned*) epc->flags[p] : nullptr; }
+    }
     const int grid = g_sms < MAXB ? g_sms : MAXB;
     const int v = (L->group ? 2 : 0) + (act_quant ? 1 : 0);
     if (v == 0) launch_pair<false, false>(grid, a, R, st);
     else if (v == 1) launch_pair<false, true>(grid, a, R, st);
     else if (v == 2) launch_pair<true, false>(grid, a, R, st);
     else launch_pair<true, true>(grid, a, R, st);
-    count_launches(3);
+    count_launches(prepared ? 2 : 3);
     const cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) return fail(HMOE_E_CUDA, cudaGetErrorString(err));
     return HMOE_OK;

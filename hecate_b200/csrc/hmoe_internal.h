@@ -32,10 +32,24 @@ struct DeviceOnce
     }
 };
 
+// the expert-parallel combine as the tail of the down launch (hmoe_decode_ep_combine)
+struct EpCombineArgs
+{
+    int rank, world, own_rows;
+    void* const* slots; void* const* flags;
+    float* f;
+    unsigned* status;
+};
+
 size_t decode_ws_bytes(int H, int I);
 int decode_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
                   int act_quant, float* y, void* ws, size_t ws_bytes, cudaStream_t st, int sh_mod = 1, int sh_rem = 0,
-                  unsigned* gen_ptr = nullptr, size_t slot_stride = 0);
+                  unsigned* gen_ptr = nullptr, size_t slot_stride = 0, bool prepared = false, const struct EpCombineArgs* epc = nullptr);
+struct PrepArgs;
+int decode_prep_args(const hmoe_layer* L, const void* x, int x_dtype, int R, int lo, int n_local, int act_quant, void* ws, size_t ws_bytes,
+                     int sh_mod, int sh_rem, unsigned* gen_ptr, PrepArgs* pa);
+int router_prepare_launch(const void* x, int x_dtype, const void* wt, int w_dtype, const float* bias, int R, int H, int E, int topk, float scale,
+                          int64_t* sel, void* rw, void* ws, size_t ws_bytes, const PrepArgs& pa, cudaStream_t st);
 
 int shared_i8_launch(const hmoe_layer* L, int R, int sh_mod, int sh_rem, const __half* xf, float* gs, float* y, const unsigned* gen_ptr,
                      size_t slot_stride, int sms, cudaStream_t st);

@@ -9,6 +9,7 @@
 #include <atomic>
 #include "hmoe_common.cuh"
 #include "hmoe_internal.h"
+#include "hmoe_prepare.cuh"
 
 namespace hmoe {
 namespace {
@@ -35,6 +36,9 @@ constexpr int CTR_SLOTS = 16, CTR_GROUPS = 256;
 static __device__ unsigned g_router_ctr[CTR_SLOTS][CTR_GROUPS];
 // Set by a block of the row group whose bounded wait gave up; read and cleared by the group's last block.
 static __device__ unsigned g_router_bad[CTR_SLOTS][CTR_GROUPS];
+// PREP: row groups whose selection is complete (the block that completes the last one builds the decode call's Route), and
+// whether any of them failed.
+static __device__ unsigned g_router_groups[CTR_SLOTS], g_router_anybad[CTR_SLOTS];
 
 // These kernels run once per layer on a handful of warps per SM: their duration is a chain of memory latencies, so every
 // group of loads is issued before its first use.
@@ -107,18 +111,33 @@ struct NormArgs
     const float* r; const float* y; float* r_out; const uint16_t* nw; __half* xn; float eps, cbias, cscale; int nw_bf16;
 };
 
-template <bool XBF, bool WBF, bool FUSED, bool NORM>
+// PREP (with FUSED, without NORM): the launch also does the set-up step of the decode call that follows (hmoe_prepare.cuh), so that
+// no separate prepare kernel sits between the router and the expert kernels: one more block per row group (blockIdx.x ==
+// gridDim.x - 1) rewrites the group's rows for the MMAs while the other blocks compute logits, and the block that completes the
+// last row group's selection builds the Route from the selections of all rows.
+template <bool XBF, bool WBF, bool FUSED, bool NORM, bool PREP = false>
 __global__ void __launch_bounds__(RW * 32) router_logits_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ wt,
                                                                 int R, int H, int E, float* __restrict__ logits,
                                                                 const float* __restrict__ bias, int topk, float scale,
                                                                 int64_t* __restrict__ sel, __half* __restrict__ rw, int slot, const NormArgs na,
-                                                                unsigned* __restrict__ status)
+                                                                unsigned* __restrict__ status, const PrepArgs pa)
 {
     extern __shared__ __align__(128) unsigned char rsm[];
     __shared__ int s_last;
     __shared__ int s_abort;
     __shared__ __align__(8) unsigned long long s_bar[RW];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nrouter = PREP ? (int) gridDim.x - 1 : (int) gridDim.x;       // blocks per row group that compute logits
+    if (PREP)
+    {
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");    // the expert kernels' blocks may set up while this one runs
+        if ((int) blockIdx.x == nrouter)
+        {
+            for (int r = blockIdx.y * RR; r < R && r < (int) (blockIdx.y + 1) * RR; ++r)
+                prepare_row(pa.x, pa.x_kind, r, H, pa.act_quant, pa.xf, pa.xscale, pa.gzero, pa.gzero_n, threadIdx.x, RW * 32);
+            return;
+        }
+    }
     const int hc = H < HC ? H : HC;                              // chunk length, a multiple of 256
     float* xs = (float*) rsm;                                    // [RR][hc] fp32, see above
     const uint32_t wsm = smem_u32(rsm) + RR * hc * 4 + warp * hc * 2, bar = smem_u32(&s_bar[warp]);
@@ -260,7 +279,7 @@ __global__ void __launch_bounds__(RW * 32) router_logits_kernel(const uint16_t* 
     {
         unsigned* c = &g_router_ctr[slot][blockIdx.y];
         const unsigned old = atomicAdd(c, 1u);
-        s_last = old == gridDim.x - 1;
+        s_last = old == (unsigned) nrouter - 1;
         if (s_last) *c = 0u;
     }
     __syncthreads();
@@ -270,10 +289,35 @@ __global__ void __launch_bounds__(RW * 32) router_logits_kernel(const uint16_t* 
         // after a failed wait the logits are incomplete: select nothing (the status word tells the host)
         const unsigned bad = *(volatile unsigned*) &g_router_bad[slot][blockIdx.y];
         __syncthreads();
-        if (threadIdx.x == 0 && bad) g_router_bad[slot][blockIdx.y] = 0u;
-        if (bad) return;
+        if (threadIdx.x == 0 && bad) { g_router_bad[slot][blockIdx.y] = 0u; if (PREP) atomicOr(&g_router_anybad[slot], 1u); }
+        if (bad && !PREP) return;
+        if (!bad && warp < nr) topk_row(logits, bias, r0 + warp, E, topk, scale, sel, rw, lane, true, xs + warp * 512);
     }
-    if (warp < nr) topk_row(logits, bias, r0 + warp, E, topk, scale, sel, rw, lane, true, xs + warp * 512);
+    if (!PREP) return;
+    // the selections of this row group are written: count the group; the block that completes the last group builds the Route
+    __syncthreads();
+    if (threadIdx.x == 0)
+    {
+        __threadfence();
+        const unsigned old = atomicAdd(&g_router_groups[slot], 1u);
+        s_last = old == gridDim.y - 1;
+        if (s_last) g_router_groups[slot] = 0u;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const unsigned anybad = *(volatile unsigned*) &g_router_anybad[slot];
+    __syncthreads();
+    if (anybad)
+    {
+        // a wait gave up somewhere in this call: the selections are incomplete. Leave an empty Route (the expert kernels then do
+        // nothing) and tell the host through the decode workspace's status word.
+        if (threadIdx.x == 0) { g_router_anybad[slot] = 0u; atomicOr(pa.status, ST_WAIT_TIMEOUT); pa.route->m = 0; pa.route->ntiles = 0; }
+        for (int i = threadIdx.x; i < 2 * (MAXB + 1); i += RW * 32) pa.route->split[i / (MAXB + 1)][i % (MAXB + 1)] = 0;
+        return;
+    }
+    build_route<true>(*(RouteSmem*) (rsm + RW * 512 * 4), sel, rw, R, H, pa.I, topk, pa.lo, pa.n_local, pa.has_shared, pa.sh_mod, pa.sh_rem,
+                      pa.gen_bump, pa.route, pa.nblocks, threadIdx.x);
 }
 
 __global__ void __launch_bounds__(256) router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int R, int E,
@@ -295,8 +339,8 @@ void launch_logits(dim3 grid, size_t smem, cudaStream_t st, bool fused, const ui
         cudaFuncSetAttribute(router_logits_kernel<XBF, WBF, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     }
     const NormArgs na = {};
-    if (fused) router_logits_kernel<XBF, WBF, true, false><<<grid, RW * 32, smem, st>>>(x, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot, na, status);
-    else router_logits_kernel<XBF, WBF, false, false><<<grid, RW * 32, smem, st>>>(x, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot, na, status);
+    if (fused) router_logits_kernel<XBF, WBF, true, false><<<grid, RW * 32, smem, st>>>(x, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot, na, status, PrepArgs());
+    else router_logits_kernel<XBF, WBF, false, false><<<grid, RW * 32, smem, st>>>(x, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot, na, status, PrepArgs());
 }
 
 template <bool WBF>
@@ -309,12 +353,22 @@ void launch_norm_router(dim3 grid, size_t smem, cudaStream_t st, bool fused, con
         cudaFuncSetAttribute(router_logits_kernel<false, WBF, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         cudaFuncSetAttribute(router_logits_kernel<false, WBF, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     }
-    if (fused) router_logits_kernel<false, WBF, true, true><<<grid, RW * 32, smem, st>>>(nullptr, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot, na, status);
-    else router_logits_kernel<false, WBF, false, true><<<grid, RW * 32, smem, st>>>(nullptr, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot, na, status);
+    if (fused) router_logits_kernel<false, WBF, true, true><<<grid, RW * 32, smem, st>>>(nullptr, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot, na, status, PrepArgs());
+    else router_logits_kernel<false, WBF, false, true><<<grid, RW * 32, smem, st>>>(nullptr, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot, na, status, PrepArgs());
 }
 
 // Both entry points share the counter sets, so they also share the rotation that hands them out.
 std::atomic<unsigned> g_router_calls{0};
+
+template <bool XBF, bool WBF>
+void launch_logits_prep(dim3 grid, size_t smem, cudaStream_t st, const uint16_t* x, const uint16_t* wt, int R, int H, int E, float* logits,
+                        const float* bias, int topk, float scale, int64_t* sel, __half* rw, int slot, unsigned* status, const PrepArgs& pa)
+{
+    static DeviceOnce once;
+    if (once.first()) cudaFuncSetAttribute(router_logits_kernel<XBF, WBF, true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    const NormArgs na = {};
+    router_logits_kernel<XBF, WBF, true, false, true><<<grid, RW * 32, smem, st>>>(x, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot, na, status, pa);
+}
 
 }  // namespace
 
@@ -347,6 +401,36 @@ int router_launch(const void* x, int x_dtype, const void* wt, int w_dtype, const
     else launch_logits<true, true>(grid, smem, st, fused, xp, wp, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot, status);
     if (!fused) router_topk_kernel<<<(R + 7) / 8, 256, 0, st>>>(logits, bias, R, E, topk, scale, sel, (__half*) rw);
     count_launches(fused ? 1 : 2);
+    const cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) return fail(HMOE_E_CUDA, cudaGetErrorString(err));
+    return HMOE_OK;
+}
+
+// The router with the decode call's set-up step inside its launch: `pa` comes from decode_prep_args.
+int router_prepare_launch(const void* x, int x_dtype, const void* wt, int w_dtype, const float* bias, int R, int H, int E, int topk, float scale,
+                          int64_t* sel, void* rw, void* ws, size_t ws_bytes, const PrepArgs& pa, cudaStream_t st)
+{
+    if (R < 1 || R > MAXR || E < 32 || E > 256 || E % 32 || H % 256 || H < 256 || topk < 1 || topk > TOPK_MAX || topk > E)
+        return fail(HMOE_E_ARG, "hmoe_router_decode: needs 1 <= R <= 16, E % 32 == 0, E <= 256, H % 256 == 0, topk <= 8");
+    if ((x_dtype != HMOE_F16 && x_dtype != HMOE_BF16) || (w_dtype != HMOE_F16 && w_dtype != HMOE_BF16))
+        return fail(HMOE_E_ARG, "hmoe_router_decode: x and wt must be fp16 or bf16");
+    if (!x || !wt || !sel || !rw || !ws) return fail(HMOE_E_ARG, "hmoe_router_decode: null pointer");
+    if (ws_bytes < router_ws_bytes(R, E)) return fail(HMOE_E_WS, "hmoe_router_decode: router workspace too small");
+    const int hc = H < HC ? H : HC;
+    size_t smem = (size_t) RR * (hc > 512 ? hc : 512) * 4 + (size_t) RW * hc * 2;
+    const size_t need = (size_t) RW * 512 * 4 + sizeof(RouteSmem);            // the selection's scratch, then the Route builder's
+    if (smem < need) smem = need;
+    const dim3 grid((E + RW - 1) / RW + 1, (R + RR - 1) / RR);                // + 1: the block that rewrites the group's rows
+    unsigned* status = (unsigned*) ws;
+    float* logits = (float*) ((char*) ws + 256);
+    const uint16_t* xp = (const uint16_t*) x; const uint16_t* wp = (const uint16_t*) wt;
+    const int slot = (int) (g_router_calls.fetch_add(1, std::memory_order_relaxed) % CTR_SLOTS);
+    const bool xb = x_dtype == HMOE_BF16, wb = w_dtype == HMOE_BF16;
+    if (!xb && !wb) launch_logits_prep<false, false>(grid, smem, st, xp, wp, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot, status, pa);
+    else if (!xb && wb) launch_logits_prep<false, true>(grid, smem, st, xp, wp, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot, status, pa);
+    else if (xb && !wb) launch_logits_prep<true, false>(grid, smem, st, xp, wp, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot, status, pa);
+    else launch_logits_prep<true, true>(grid, smem, st, xp, wp, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot, status, pa);
+    count_launches(1);
     const cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) return fail(HMOE_E_CUDA, cudaGetErrorString(err));
     return HMOE_OK;

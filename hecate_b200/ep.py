@@ -73,8 +73,11 @@ class PeerBuffers:
 class EpDecoder:
     """One rank's side of an expert-parallel decode layer."""
 
-    def __init__(self, rank, world, tables, n_experts, device, dist, use_peer=True):
+    def __init__(self, rank, world, tables, n_experts, device, dist, use_peer=True, fused_tail=True):
         self.rank, self.world, self.tabs, self.dev, self.dist = rank, world, tables, device, dist
+        # fused_tail: the combine runs as the tail of the down launch (hmoe_decode_ep_combine) instead of as a kernel of its own;
+        # it needs the register-resident decode kernels (H <= 6144, I <= 2048)
+        self.fused_tail = fused_tail and tables.H <= 6144 and tables.I <= 2048
         self.plan = shard_plan(rank, world, n_experts)
         assert tables.n == self.plan["n_local"]
         self.ws = moe.decode_workspace(tables.H, tables.I, device)
@@ -92,7 +95,9 @@ class EpDecoder:
         st = C.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)
         pl = self.plan
         struct = self.struct if tables is None else tables.struct()
-        if self.use_peer:
+        if self.use_peer and self.fused_tail:
+            self._decode_combine(struct, vp(x), moe._dt(x), vp(sel), vp(rw), R, f, 0, st)
+        elif self.use_peer:
             check(lib().hmoe_decode_ep(C.byref(struct), vp(x), C.c_int(moe._dt(x)), vp(sel), vp(rw), C.c_int(R), C.c_int(pl["lo"]),
                                        C.c_int(pl["n_local"]), C.c_int(0), C.c_void_p(self.peer.own), vp(self.ws),
                                        C.c_size_t(self.ws.numel()), C.c_int(pl["shared_mod"]), C.c_int(pl["shared_rem"]),
@@ -108,6 +113,13 @@ class EpDecoder:
                 self.dist.all_reduce(y)
             moe.moe4_combine(f, 0, y, R, 0)
         return f
+
+    def _decode_combine(self, struct, x, x_dt, sel, rw, R, f, own_rows, st):
+        pl, pb = self.plan, self.peer
+        check(lib().hmoe_decode_ep_combine(C.byref(struct), x, C.c_int(x_dt), sel, rw, C.c_int(R), C.c_int(pl["lo"]), C.c_int(pl["n_local"]),
+                                           C.c_int(0), vp(self.ws), C.c_size_t(self.ws.numel()), C.c_int(pl["shared_mod"]),
+                                           C.c_int(pl["shared_rem"]), C.c_void_p(pb.gen_ptr), C.c_size_t(pb.slot_floats), C.c_int(self.rank),
+                                           C.c_int(self.world), pb.slots, pb.flags, vp(f), C.c_int(own_rows), vp(pb.status), st))
 
     def own_rows(self, R):
         """Rows of a step that this rank holds when the tokens are data-parallel: rank, rank + world, ..."""
@@ -127,6 +139,9 @@ class EpDecoder:
         H, topk = self.tabs.H, self.tabs.topk
         check(lib().hmoe_ep_dispatch(C.c_int(self.rank), C.c_int(self.world), pb.stage, vp(x_own), vp(sel_own), vp(rw_own), C.c_int(R), C.c_int(H),
                                      C.c_int(topk), vp(pb.status), st))
+        if self.fused_tail:
+            self._decode_combine(struct, C.c_void_p(pb.stage_x), moe._dt(x_own), C.c_void_p(pb.stage_sel), C.c_void_p(pb.stage_rw), R, f_own, 1, st)
+            return f_own
         check(lib().hmoe_decode_ep(C.byref(struct), C.c_void_p(pb.stage_x), C.c_int(moe._dt(x_own)), C.c_void_p(pb.stage_sel), C.c_void_p(pb.stage_rw),
                                    C.c_int(R), C.c_int(pl["lo"]), C.c_int(pl["n_local"]), C.c_int(0), C.c_void_p(pb.own), vp(self.ws),
                                    C.c_size_t(self.ws.numel()), C.c_int(pl["shared_mod"]), C.c_int(pl["shared_rem"]), C.c_void_p(pb.gen_ptr),

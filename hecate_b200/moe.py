@@ -271,6 +271,27 @@ def router_fused(x, wt, bias, logits, ctr, sel, rw, topk, scale):
     return sel, rw
 
 
+def router_decode(tables, x, wt, bias, sel, rw, scale, y, ws, lo=0, n_local=None, act_quant=False):
+    """router_fused followed by decode on its output, in three launches instead of four (hmoe_router_decode): what the
+    reference's hooks do back to back per layer (routing_fn, then cpu_split_submit). sel / rw are written; y += experts(x)."""
+    R, H = x.shape
+    E = wt.shape[0]
+    need = lib().hmoe_router_ws_bytes(C.c_int(R), C.c_int(E))
+    rws = _router_ws.get((x.device, ))
+    if rws is None or rws.numel() < need:
+        rws = _router_ws[(x.device, )] = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=x.device)
+    if not (x.is_contiguous() and wt.is_contiguous() and sel.is_contiguous() and rw.is_contiguous() and y.is_contiguous()):
+        raise HmoeError("router_decode: tensors must be contiguous")
+    if sel.dtype != torch.int64 or rw.dtype != torch.float16 or y.dtype != torch.float32 or H != tables.H or sel.shape[1] != tables.topk:
+        raise HmoeError("router_decode: sel int64 [R][topk], rw fp16, y fp32 required")
+    st = tables.struct()
+    check(lib().hmoe_router_decode(C.byref(st), vp(x), C.c_int(_dt(x)), vp(wt), C.c_int(_dt(wt)), vp(bias), C.c_int(R), C.c_int(E),
+                                   C.c_float(float(scale)), vp(sel), vp(rw), vp(rws), C.c_size_t(rws.numel()), C.c_int(lo),
+                                   C.c_int(tables.n if n_local is None else n_local), C.c_int(int(act_quant)), vp(y), vp(ws),
+                                   C.c_size_t(ws.numel()), _stream(x.device)))
+    return y
+
+
 def norm_route(y, r, w, xn, wt, bias, sel, rw, topk, scale, eps, cbias=0.0, cscale=1.0, r_out=None):
     """Residual add + input norm + router in one launch (the reference's norm_route, runtime/core/exl3_normroute.py:16-65, without
     its hand-off arguments): r' = r + y (y may be None) -> r_out (or dropped), xn = fp16 norm of r', (sel, rw) = router(xn)."""

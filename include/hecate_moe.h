@@ -79,6 +79,17 @@ size_t hmoe_decode_ws_bytes(int H, int I);
 int hmoe_decode(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
                 int act_quant, float* y, void* ws, size_t ws_bytes, void* stream);
 
+/* hmoe_router followed by hmoe_decode on the router's own output, as three launches instead of four: the router's launch also
+ * does the decode call's set-up step (the rows rewritten for the MMAs by one more block per row group while the logits are
+ * computed; the work list built by the block that completes the last selection), so no separate set-up kernel sits between
+ * the router and the expert kernels. This is what the reference's hooks do back to back per layer: routing_fn, then
+ * cpu_split_submit with the selection it returned (docker/patches/exllamav3/block_sparse_mlp_routing.py:253-301,
+ * runtime/tier/tier_split.py:520-574). Arguments as in the two calls; H and topk are the layer's; R <= 16; sel and rw are outputs.
+ * A wait that gives up inside the router sets bit 0 of the decode workspace's status word and the call computes nothing. */
+int hmoe_router_decode(const hmoe_layer* layer, const void* x, int x_dtype, const void* wt, int w_dtype, const float* bias, int R, int E, float scale,
+                       int64_t* sel, void* rw, void* router_ws, size_t router_ws_bytes, int lo, int n_local, int act_quant, float* y, void* ws,
+                       size_t ws_bytes, void* stream);
+
 /* Expert-parallel decode over the GPUs of one box (no reference counterpart as such: the reference splits a layer's experts
  * over unlike processors that all receive every row and ignore foreign ids, runtime/tier/tier_split.py:3-11, moe4.cu:93, and
  * adds their fp32 partials in a fixed order, moe4.cu:702-717; these entry points do the same over NVLink peer memory).
@@ -113,6 +124,13 @@ int hmoe_ep_combine(int rank, int world, void* const* slots, void* const* flags,
  * the offsets hmoe_ep_stage_offsets returns: the inputs of hmoe_decode_ep. All ranks must make the same sequence of steps, each
  * followed by a combine (which is what makes a single staging area enough).
  * hmoe_ep_combine_own: hmoe_ep_combine for data-parallel tokens: f_own [n][H] += the sums of this rank's rows only. */
+/* hmoe_decode_ep followed by hmoe_ep_combine (own_rows = 0) or hmoe_ep_combine_own (own_rows = 1) as one call without the
+ * combine's launch: the down kernel's blocks do the combine when they run out of weights to stream (the block that finishes last
+ * raises the flags, every block waits, bounded, for the peers and sums its slice of the peers' partials into f). Same buffers and
+ * protocol as the separate calls, so ranks using either form interoperate step by step. Needs H <= 6144 and I <= 2048. */
+int hmoe_decode_ep_combine(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
+                           int act_quant, void* ws, size_t ws_bytes, int shared_mod, int shared_rem, uint32_t* gen, size_t slot_floats, int rank,
+                           int world, void* const* slots, void* const* flags, float* f, int own_rows, uint32_t* status, void* stream);
 size_t hmoe_ep_stage_bytes(int H, int topk);
 int hmoe_ep_stage_offsets(int H, int topk, size_t* x_off, size_t* sel_off, size_t* rw_off);
 int hmoe_ep_dispatch(int rank, int world, void* const* stage, const void* x_own, const int64_t* sel_own, const void* rw_own, int R, int H, int topk,

@@ -143,6 +143,39 @@ def test_shapes_beyond_the_register_resident_path(oracle, dev, H, I):
     assert int8_close(errors(got, ref)), errors(got, ref)
 
 
+@pytest.mark.parametrize("R,H,I,E,aq", [(16, 6144, 2048, 32, False), (5, 6144, 2048, 32, True), (1, 512, 256, 32, True), (13, 1024, 256, 64, False)])
+def test_router_decode_in_one_call_equals_the_two_calls(oracle, dev, R, H, I, E, aq):
+    """hmoe_router_decode (the router's launch also does the decode call's set-up step) against hmoe_router followed by
+    hmoe_decode: the same selection and weights bit for bit, the same output up to the order of the fp32 atomic additions; and
+    against the CPU checker."""
+    import torch
+    from hecate_b200 import moe
+    hl = HostLayer(9, 0, H, I, range(E), 128, True)
+    tabs = hl.upload(dev)
+    x = synth.activations(40 + R, 0, R, H)
+    xt = torch.from_numpy(x).to(dev).to(torch.bfloat16)
+    wt = torch.from_numpy(synth.router_weight(41, 0, E, H)).to(dev).to(torch.bfloat16)
+    bias = torch.from_numpy(synth.router_bias(41, 0, E, 0.05)).to(dev)
+    ws = moe.decode_workspace(H, I, dev)
+    sel1 = torch.empty(R, 8, dtype=torch.int64, device=dev); rw1 = torch.empty(R, 8, dtype=torch.float16, device=dev)
+    y1 = torch.zeros(R, H, device=dev)
+    moe.router_fused(xt, wt, bias, None, None, sel1, rw1, 8, 1.5)
+    moe.decode(tabs, xt, sel1, rw1, y1, ws, act_quant=aq)
+    ws2 = moe.decode_workspace(H, I, dev)
+    for _ in range(2):                                        # twice: the counters inside the library return to zero
+        sel2 = torch.full((R, 8), -7, dtype=torch.int64, device=dev); rw2 = torch.zeros(R, 8, dtype=torch.float16, device=dev)
+        y2 = torch.zeros(R, H, device=dev)
+        moe.router_decode(tabs, xt, wt, bias, sel2, rw2, 1.5, y2, ws2, act_quant=aq)
+        assert torch.equal(sel1, sel2) and torch.equal(rw1.view(torch.int16), rw2.view(torch.int16))
+        assert moe.ws_status(ws2) == 0
+        e = errors(y2.cpu().numpy(), y1.cpu().numpy())
+        assert int8_close(e) if aq else e[2] < 1e-3, e
+    ex, sh = hl.oracle_experts(oracle)
+    ref = oracle.moe_forward(H, I, 128, x.astype(np.float16), sel2.cpu().numpy(), rw2.cpu().numpy(), 0, ex, sh, mode=0 if aq else 1)
+    e = errors(y2.cpu().numpy(), ref)
+    assert (e[0] < MAX_REL and e[1] < MEAN_ABS) if aq else e[2] < NORM_REL_EXACT, e
+
+
 def test_accumulates_into_y_and_combine(oracle, dev):
     import torch
     from hecate_b200 import moe

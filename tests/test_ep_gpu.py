@@ -61,8 +61,8 @@ def _rank_main(rank, world, port, out_path):
     local = HostLayer(0, 0, H, I, range(p["lo"], p["lo"] + p["n_local"]), 128, True).upload(dev)
     x = torch.from_numpy(synth.activations(1, 0, R, H)).to(dev).half()
     res = {}
-    for mode in (True, False):
-        dec = EpDecoder(rank, world, local, E, dev, dist, use_peer=mode)
+    for mode in (True, "separate", False):                  # peer combine as the down launch's tail, as its own kernel, NCCL all-reduce
+        dec = EpDecoder(rank, world, local, E, dev, dist, use_peer=bool(mode), fused_tail=(mode is True))
         outs = []
         for stepi in range(4):                                # several steps: both slots and the generation logic get used
             sel, rw = synth.zipf_routing(10 + stepi, 0, R, E, 8, 0.0)
@@ -74,19 +74,24 @@ def _rank_main(rank, world, port, out_path):
         if dec.peer is not None:
             dist.barrier(); dec.peer.close()
     # data-parallel tokens: every rank passes only its own rows (rank, rank + world, ...); dispatch and combine over peer memory
-    dec = EpDecoder(rank, world, local, E, dev, dist, use_peer=True)
-    own = dec.own_rows(R)
-    outs = []
-    for stepi in range(4):
-        sel, rw = synth.zipf_routing(10 + stepi, 0, R, E, 8, 0.0)
-        f_own = torch.zeros(len(own), H, device=dev)
-        dec.step_dp(x[own].contiguous(), torch.from_numpy(sel[own]).to(dev), torch.from_numpy(rw[own]).to(dev), f_own, R)
-        outs.append(f_own)
-    assert dec.status() == 0 and dec.dispatch_bytes(R) == (world - 1) * len(own) * (H * 2 + 80)
-    dp = torch.stack(outs)
-    dist.barrier(); dec.peer.close()
-    dp_err = torch.tensor([float((dp - res[True][:, own]).abs().max() / res[True].abs().max())], device=dev)
+    dp_err = torch.zeros(1, device=dev)
+    for fused in (True, False):
+        dec = EpDecoder(rank, world, local, E, dev, dist, use_peer=True, fused_tail=fused)
+        own = dec.own_rows(R)
+        outs = []
+        for stepi in range(4):
+            sel, rw = synth.zipf_routing(10 + stepi, 0, R, E, 8, 0.0)
+            f_own = torch.zeros(len(own), H, device=dev)
+            dec.step_dp(x[own].contiguous(), torch.from_numpy(sel[own]).to(dev), torch.from_numpy(rw[own]).to(dev), f_own, R)
+            outs.append(f_own)
+        assert dec.status() == 0 and dec.dispatch_bytes(R) == (world - 1) * len(own) * (H * 2 + 80)
+        dp = torch.stack(outs)
+        dist.barrier(); dec.peer.close()
+        dp_err = torch.maximum(dp_err, torch.tensor([float((dp - res[True][:, own]).abs().max() / res[True].abs().max())], device=dev))
     dist.all_reduce(dp_err, op=dist.ReduceOp.MAX)
+    sep_err = torch.tensor([float((res["separate"] - res[True]).abs().max() / res[True].abs().max())], device=dev)
+    dist.all_reduce(sep_err, op=dist.ReduceOp.MAX)
+    dp_err = torch.maximum(dp_err, sep_err)
     # all ranks hold the same bits after the peer combine (fixed rank order)
     mine = res[True].clone()
     others = [torch.zeros_like(mine) for _ in range(world)]

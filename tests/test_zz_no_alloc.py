@@ -10,7 +10,7 @@ import ctypes as C
 import numpy as np
 import pytest
 
-from helpers import HostLayer, errors, random_routing
+from helpers import HostLayer, errors, int8_close, random_routing
 from hecate_b200 import synth
 
 pytestmark = pytest.mark.gpu
@@ -53,12 +53,15 @@ def test_noalloc_matches_workspace_entry_point_twice(H, I, E, group, act_quant):
         torch.cuda.synchronize()
         assert int(status_dev.item()) == 0
         # Same kernels, same inputs: the results differ only through the order of the fp32 atomic additions inside the
-        # kernels. In the int8 mode that stays at the 1e-7 level (held to the decode tests' 1e-4). With fp16 activations a
-        # last-bit difference of a gate/up sum can flip the fp16 rounding of one intermediate value, which at these small
-        # shapes shows up as up to ~2e-4 of the largest output (measured over repeated runs of hmoe_decode itself), so that
-        # mode is held to 1e-3, inside the 2e-3 gate the decode tests apply to it.
+        # kernels. With fp16 activations a last-bit difference of a gate/up sum can flip the fp16 rounding of one intermediate
+        # value, which at these small shapes shows up as up to ~2e-4 of the largest output (measured over repeated runs of
+        # hmoe_decode itself), so that mode is held to 1e-3, inside the 2e-3 gate the decode tests apply to it. In the int8 mode
+        # the typical difference is 1e-7, but the same last-bit difference can move one intermediate value across a rounding
+        # boundary of its int8 code (1/127 of its group's maximum), which shifts that row by up to ~2e-3 of the output range:
+        # the gate is the one the decode tests use for the int8 mode on small layers (helpers.int8_close).
         e = errors(got.cpu().numpy(), want.cpu().numpy())
-        assert e[0] < (1e-4 if act_quant else 1e-3) and e[2] < (1e-4 if act_quant else 1e-3), (call, e)
+        print(f"noalloc H={H} I={I} call {call}: max-rel {e[0]:.2e} mean-abs {e[1]:.2e} norm-rel {e[2]:.2e}")
+        assert int8_close(e) if act_quant else (e[0] < 1e-3 and e[2] < 1e-3), (call, e)
         assert float(want.abs().max()) > 0
 
 
