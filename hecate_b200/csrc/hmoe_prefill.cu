@@ -12,13 +12,18 @@
 // row block (<= 256, one expert) the N operand, fp32 accumulators in tensor memory. Per 64-column stage:
 //   warps 0-15 read the packed codes of the tile straight from global memory (16 bytes per lane, the stored fragment order),
 //              turn them into fp16 (times the bf16 group scale in the group format) and store them as a K-major,
-//              128-byte-swizzled operand tile (4-byte stores, conflict free);
+//              128-byte-swizzled operand tile (4-byte stores, conflict free); they do nothing else and run ahead of the MMAs
+//              from tile to tile as far as the ring allows;
 //   warp 16    one thread loads the row block's 256 x 64 input tile with one 2-D TMA copy (128-byte swizzle, rows beyond the
 //              array zero-filled);
 //   warp 17    one thread issues tcgen05.mma (M 128, N = picks rounded up to 16, K 16) four times per matrix and commits the
-//              stage back to the producers.
-// gate_up keeps two accumulators (gate, up: 2 x 256 columns) over the same input tile and its epilogue writes
-// act = SiLU(g) * u * routing weight in fp16; down adds scale * sum into out[token] with coalesced fp32 reductions.
+//              stage back to the producers;
+//   warps 18-21 read the finished sums out of tensor memory (one quarter of the lanes = 32 channels each).
+// gate_up keeps two accumulators (gate, up: 2 x 256 columns) over the same input tile and its read-out writes
+// act = SiLU(g) * u * routing weight in fp16; down adds scale * sum into out[token] with coalesced fp32 reductions and keeps two
+// accumulator sets, so a tile's read-out runs under the next tile's MMAs. (Measured on the benchmark with parts of the kernel
+// switched off: the MMA / TMA pipeline alone needs 4.5 ms of a 7.7 ms step, the dequantisation 1.5 ms and the read-outs 1.7 ms
+// when the same warps do both in turn, as an earlier version did; hence the separate warps.)
 // Blocks are persistent (one per SM) over (row block, channel tile) items, channel tile fastest, so the blocks working at
 // the same time share one input tile and one expert's weights through L2.
 // Every wait is bounded (see mbar_wait); tensor memory is released by the warp that allocated it on every path.
@@ -30,8 +35,9 @@ namespace hmoe {
 namespace {
 
 constexpr int TM = 128, TN = 256, TK = 64;
-constexpr int NDQ = 16;                         // dequantise / epilogue warps
-constexpr int PF_THREADS = (NDQ + 2) * 32;      // + warp NDQ: TMA, warp NDQ + 1: MMA
+constexpr int NDQ = 16;                         // dequantising warps
+constexpr int NEPI = 4;                         // read-out warps, one per quarter of the tensor-memory lanes
+constexpr int PF_THREADS = (NDQ + 2 + NEPI) * 32;      // warp NDQ: TMA, warp NDQ + 1: MMA, warps NDQ + 2 ..: read-out
 constexpr int CHUNK = 1024;                     // picks per permutation block (one warp)
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -323,7 +329,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
     if (threadIdx.x == 0)
     {
         for (int i = 0; i < L::STAGES; ++i) { mbar_init(full_a + i * 8, NMAT == 2 ? NDQ : NDQ / 2); mbar_init(full_b + i * 8, 1); mbar_init(empty + i * 8, 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(done + i * 8, 1); mbar_init(tmem_free + i * 8, NDQ); }
+        for (int i = 0; i < 2; ++i) { mbar_init(done + i * 8, 1); mbar_init(tmem_free + i * 8, NEPI); }
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -344,109 +350,22 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
     {
         // ---- dequantise: one 16-row strip of one 64-row unit per warp and stage. gate_up: 2 matrices x 2 units x 4 strips =
         // 16 strip-blocks per stage, one per warp. down: 8 strip-blocks per stage; warps 0-7 take the even stages, warps
-        // 8-15 the odd ones. The packed words are fetched NPF of the warp's stages ahead. The warps also read out the
-        // finished sums (epilogue), but LEAD of their stages late: by then the ring holds the first stages of the next tile, so
-        // the MMA thread has work (down, second accumulator set) or can restart at once (gate_up) while the sums are read.
+        // 8-15 the odd ones. The packed words are fetched NPF of the warp's stages ahead. These warps do nothing else: they
+        // stream from tile to tile and stop only when the ring is full, so the MMA thread always finds its next stages.
         const int g = lane >> 2, q = lane & 3;
         const int strip = warp & 3, unit = (warp >> 2) & 1, mat = NMAT == 2 ? warp >> 3 : 0;
         const int kb0 = NMAT == 2 ? 0 : warp >> 3, kstep = NMAT == 2 ? 1 : 2;
         constexpr int NPF = 4;
-        // own stages of the next tile produced before the epilogue: gate_up fills its whole ring (all three slots held the
-        // finished tile's last stages, so none of them waits for the next tile's MMAs); down, whose warps take alternate stages and
-        // whose MMAs are not held back by the read-out, does best with one (measured: 3/1 7.42 ms, 2/1 7.60, 3/2 7.84)
-        constexpr int LEAD = NMAT == 2 ? PfSmem<2>::STAGES : 1;
-        struct Tile { int e, pos0, n, ct; uint32_t tile_n; };
-        Tile pend; bool have_pend = false;
         bool ok = true;
-        auto epilogue = [&](const Tile& t) {
-
-            // warp w reads tensor-memory lanes 32 (w % 4) .. + 31 (channels), columns 64 (w / 4) .. + 63 (picks)
-            const uint32_t acc = (uint32_t) (t.tile_n % NACC);
-            if (!mbar_wait(done + acc * 8, (t.tile_n / NACC) & 1, abort_flag, a.status)) { ok = false; return; }
-            tc_fence_after();
-            const uint32_t n16 = (uint32_t) ((t.n + 15) & ~15);
-            const int lq = warp & 3, cq = warp >> 2;
-            const int ch = t.ct * TM + lq * 32 + lane;
-            const uint32_t tacc = tmem + acc * 256 + ((uint32_t) (lq * 32) << 16);
-            float sc0 = 1.f, sc1 = 1.f;
-            if (!a.grouped)
-            {
-                const void* s0p = t.e < a.n_local ? (const void*) a.s0[t.e] : a.sh_s0;
-                sc0 = __ldg((const float*) s0p + ch);
-                if (NMAT == 2) { const void* s1p = t.e < a.n_local ? (const void*) a.s1[t.e] : a.sh_s1; sc1 = __ldg((const float*) s1p + ch); }
-            }
-            for (int c0 = cq * 64; c0 < cq * 64 + 64 && c0 < (int) n16; c0 += 16)
-            {
-                uint32_t r0[16], r1[16];                 // 16 columns at a time: the streaming loop's prefetched words stay in registers
-                tmem_ld16(tacc + c0, r0);
-                if (NMAT == 2) tmem_ld16(tacc + 256 + c0, r1);
-                tmem_ld_wait();
-                if (NMAT == 2)
-                {
-                    #pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                    {
-                        const int p = c0 + j;
-                        if (p < t.n)
-                        {
-                            const float gg = __uint_as_float(r0[j]) * sc0, uu = __uint_as_float(r1[j]) * sc1;
-                            float v = gg / (1.f + expf(-gg)) * uu * a.wt[t.pos0 + p];
-                            if (a.act_quant)
-                            {
-                                // second int8 round trip of the CPU engine: 32 consecutive channels = this warp
-                                float m = fabsf(v);
-                                #pragma unroll
-                                for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-                                const float sq8 = m > 0.f ? __fdiv_rn(m, 127.f) : 1.f;
-                                v = __fmul_rn((float) __float2int_rn(__fmul_rn(v, __fdiv_rn(1.f, sq8))), sq8);
-                                // code x scale does not fit fp16: keep it as hi + lo halves, the down GEMM walks both
-                                const __half hi = __float2half_rn(v);
-                                a.act[(size_t) (t.pos0 + p) * (2 * a.N) + ch] = hi;
-                                a.act[(size_t) (t.pos0 + p) * (2 * a.N) + a.N + ch] = __float2half_rn(v - __half2float(hi));
-                            }
-                            else
-                                a.act[(size_t) (t.pos0 + p) * a.N + ch] = __float2half_rn(v);
-                        }
-                    }
-                }
-                else
-                {
-                    #pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                    {
-                        const int p = c0 + j;
-                        if (p < t.n)
-                        {
-                            const int tk = a.tok[t.pos0 + p];
-                            const float v = __uint_as_float(r0[j]) * sc0;
-                            if (a.rows_per_rank)
-                            {
-                                // the row's owner may be another GPU, and up to eight GPUs add into the same addresses: the
-                                // reduction has to be atomic at system scope (a gpu-scope one is only atomic among this GPU's threads)
-                                const int pr = tk / a.rows_per_rank;
-                                red_add_sys(a.out_peer[pr] + (size_t) (tk - pr * a.rows_per_rank) * a.N + ch, v);
-                            }
-                            else atomicAdd(a.out + (size_t) tk * a.N + ch, v);
-                        }
-                    }
-                }
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(tmem_free + acc * 8);
-        };
-
         uint32_t tile_n = 0;
         for (int item = blockIdx.x; item < nitems && ok; item += gridDim.x, ++tile_n)
         {
             if (*abort_flag) { ok = false; break; }
-            const int rb = item / NCT;
-            Tile cur;
-            cur.ct = item % NCT; cur.e = a.rbt[4 * rb]; cur.pos0 = a.rbt[4 * rb + 1]; cur.n = a.rbt[4 * rb + 2]; cur.tile_n = tile_n;
-            const void* wp = cur.e < a.n_local ? (const void*) (mat ? a.w1[cur.e] : a.w0[cur.e]) : (mat ? a.sh_w1 : a.sh_w0);
-            const void* sp = cur.e < a.n_local ? (const void*) (mat ? a.s1[cur.e] : a.s0[cur.e]) : (mat ? a.sh_s1 : a.sh_s0);
-            const char* wbase = (const char*) wp + ((size_t) (2 * cur.ct + unit) * KB * 4 + strip) * 512 + lane * 16;
-            const char* sbase_p = (const char*) sp + ((size_t) (2 * cur.ct + unit) * (a.K / 128) * 64 + g * 8 + 2 * strip) * 2;
+            const int rb = item / NCT, ct = item % NCT, e = a.rbt[4 * rb];
+            const void* wp = e < a.n_local ? (const void*) (mat ? a.w1[e] : a.w0[e]) : (mat ? a.sh_w1 : a.sh_w0);
+            const void* sp = e < a.n_local ? (const void*) (mat ? a.s1[e] : a.s0[e]) : (mat ? a.sh_s1 : a.sh_s0);
+            const char* wbase = (const char*) wp + ((size_t) (2 * ct + unit) * KB * 4 + strip) * 512 + lane * 16;
+            const char* sbase_p = (const char*) sp + ((size_t) (2 * ct + unit) * (a.K / 128) * 64 + g * 8 + 2 * strip) * 2;
             // packed words and scale pairs of the next NPF of this warp's stages, in flight while the current one is converted
             uint4 wq[NPF]; uint32_t sq[NPF];
             #pragma unroll
@@ -458,7 +377,6 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
                 sq[i] = (a.grouped && kbi < KBT) ? __ldg((const uint32_t*) (sbase_p + (size_t) (kbw >> 1) * 128)) : 0u;
             }
             const uint32_t it0 = tile_n * (uint32_t) KBT;
-            int produced = 0;
             for (int kb = kb0; kb < KBT; kb += kstep)
             {
                 const uint32_t gi = it0 + kb, s = gi % L::STAGES;
@@ -478,13 +396,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
                 fence_proxy_async();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(full_a + s * 8);
-                if (++produced == LEAD && have_pend) { epilogue(pend); have_pend = false; if (!ok) break; }
             }
-            if (!ok) break;
-            if (have_pend) { epilogue(pend); have_pend = false; }       // tiles with fewer than LEAD stages per warp
-            pend = cur; have_pend = true;
         }
-        if (ok && have_pend) epilogue(pend);
     }
     else if (warp == NDQ)
     {
@@ -505,7 +418,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
             }
         }
     }
-    else
+    else if (warp == NDQ + 1)
     {
         if (lane == 0)
         {
@@ -537,6 +450,105 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
                 }
                 if (ok) tc_commit(done + acc * 8);
             }
+        }
+    }
+    else
+    {
+        // ---- read-out: warp NDQ + 2 + i reads the tensor-memory lanes of quarter (warp % 4) (a warp may only touch the quarter
+        // that matches its number), i.e. 32 output channels, for all picks of the tile, 16 columns at a time. gate_up: SiLU(gate)
+        // * up * routing weight -> fp16 activations; down: out[token] += scale * sum, one fp32 reduction per element (32 lanes =
+        // 32 consecutive channels = 128 contiguous bytes). Because these warps do nothing else, the read-out of a tile overlaps
+        // the dequantisation and (down: second accumulator set) the MMAs of the next one.
+        const int lq = warp & 3;
+        uint32_t tile_n = 0;
+        bool ok = true;
+        for (int item = blockIdx.x; item < nitems && ok; item += gridDim.x, ++tile_n)
+        {
+            if (*abort_flag) break;
+            const int rb = item / NCT, ct = item % NCT;
+            const int e = a.rbt[4 * rb], pos0 = a.rbt[4 * rb + 1], n = a.rbt[4 * rb + 2];
+            const uint32_t acc = (uint32_t) (tile_n % NACC);
+            if (!mbar_wait(done + acc * 8, (tile_n / NACC) & 1, abort_flag, a.status)) break;
+            tc_fence_after();
+            const uint32_t n16 = (uint32_t) ((n + 15) & ~15);
+            const int ch = ct * TM + lq * 32 + lane;
+            const uint32_t tacc = tmem + acc * 256 + ((uint32_t) (lq * 32) << 16);
+            float sc0 = 1.f, sc1 = 1.f;
+            if (!a.grouped)
+            {
+                const void* s0p = e < a.n_local ? (const void*) a.s0[e] : a.sh_s0;
+                sc0 = __ldg((const float*) s0p + ch);
+                if (NMAT == 2) { const void* s1p = e < a.n_local ? (const void*) a.s1[e] : a.sh_s1; sc1 = __ldg((const float*) s1p + ch); }
+            }
+            for (int c0 = 0; c0 < (int) n16; c0 += 16)
+            {
+                uint32_t r0[16], r1[16];
+                tmem_ld16(tacc + c0, r0);
+                if (NMAT == 2) tmem_ld16(tacc + 256 + c0, r1);
+                // the picks' routing weights (gate_up) or tokens (down): lane j of the first 16 loads pick c0 + j, handed out by shuffles
+                const int pj = c0 + (lane & 15);
+                float wj = 0.f; int tj = 0;
+                if (pj < n) { if (NMAT == 2) wj = __ldg(a.wt + pos0 + pj); else tj = __ldg(a.tok + pos0 + pj); }
+                tmem_ld_wait();
+                if (NMAT == 2)
+                {
+                    #pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                    {
+                        const int p = c0 + j;
+                        const float w = __shfl_sync(0xffffffffu, wj, j);
+                        if (p < n)
+                        {
+                            const float gg = __uint_as_float(r0[j]) * sc0, uu = __uint_as_float(r1[j]) * sc1;
+                            if (a.act_quant)
+                            {
+                                float v = gg / (1.f + expf(-gg)) * uu * w;
+                                // second int8 round trip of the CPU engine: 32 consecutive channels = this warp
+                                float m = fabsf(v);
+                                #pragma unroll
+                                for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+                                const float sq8 = m > 0.f ? __fdiv_rn(m, 127.f) : 1.f;
+                                v = __fmul_rn((float) __float2int_rn(__fmul_rn(v, __fdiv_rn(1.f, sq8))), sq8);
+                                // code x scale does not fit fp16: keep it as hi + lo halves, the down GEMM walks both
+                                const __half hi = __float2half_rn(v);
+                                a.act[(size_t) (pos0 + p) * (2 * a.N) + ch] = hi;
+                                a.act[(size_t) (pos0 + p) * (2 * a.N) + a.N + ch] = __float2half_rn(v - __half2float(hi));
+                            }
+                            else
+                            {
+                                // fp16 result: the fast exponential and division are far inside its rounding (the reference's
+                                // kernels make the same choice, runtime/tier/moe4/moe4t.cu:404-425 built with fast-math)
+                                const float v = __fdividef(gg, 1.f + __expf(-gg)) * uu * w;
+                                a.act[(size_t) (pos0 + p) * a.N + ch] = __float2half_rn(v);
+                            }
+                        }
+                    }
+                }
+                else
+                {
+                    #pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                    {
+                        const int p = c0 + j;
+                        const int tk = __shfl_sync(0xffffffffu, tj, j);
+                        if (p < n)
+                        {
+                            const float v = __uint_as_float(r0[j]) * sc0;
+                            if (a.rows_per_rank)
+                            {
+                                // the row's owner may be another GPU, and up to eight GPUs add into the same addresses: the
+                                // reduction has to be atomic at system scope (a gpu-scope one is only atomic among this GPU's threads)
+                                const int pr = tk / a.rows_per_rank;
+                                red_add_sys(a.out_peer[pr] + (size_t) (tk - pr * a.rows_per_rank) * a.N + ch, v);
+                            }
+                            else atomicAdd(a.out + (size_t) tk * a.N + ch, v);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tmem_free + acc * 8);
         }
     }
     tc_fence_before();
