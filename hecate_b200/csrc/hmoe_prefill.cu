@@ -270,17 +270,15 @@ struct GemmArgs
 
 // One 16-row x 64-column strip of packed codes (one 16-byte word per lane) -> 16 fp16x2 values stored into the K-major
 // 128-byte-swizzled operand tile. r8 = index of the strip's first 8-row group in the tile; the lane's rows are g and g + 8.
-// NW = 4: the whole word (16-column steps 0..3); NW = 2: its half `t0 / 2` (steps t0, t0 + 1; ww holds just those two words).
-template <int NW>
-__device__ __forceinline__ void store_strip(uint32_t tile, int r8, int g, int q, const uint32_t (&ww)[NW], int t0, uint32_t s_lo, uint32_t s_hi, bool scaled)
+__device__ __forceinline__ void store_strip(uint32_t tile, int r8, int g, int q, const uint4& w, uint32_t s_lo, uint32_t s_hi, bool scaled)
 {
+    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
     const uint32_t row0 = tile + r8 * 1024 + g * 128 + 4 * q, row1 = row0 + 1024;
     #pragma unroll
-    for (int i = 0; i < NW; ++i)
+    for (int t = 0; t < 4; ++t)
     {
-        const int t = t0 + i;
         uint32_t a[4];
-        frag_from_codes(ww[i], a);
+        frag_from_codes(ww[t], a);
         if (scaled)
         {
             asm("mul.f16x2 %0, %0, %1;" : "+r"(a[0]) : "r"(s_lo)); asm("mul.f16x2 %0, %0, %1;" : "+r"(a[2]) : "r"(s_lo));
@@ -301,18 +299,12 @@ __device__ __forceinline__ void scale_pair(uint32_t bf2, uint32_t& s_lo, uint32_
 template <int NMAT>
 struct PfSmem
 {
-    // Two rings with their own depths. A slot of dequantised weights is refilled a few hundred cycles after the MMAs release it
-    // (its packed codes wait in registers): two slots suffice. A slot of inputs is refilled by a TMA copy that takes well over a
-    // microsecond from request to arrival, longer than the MMAs of a stage run (0.5 us gate_up, 0.25 us down at full rate), so the
-    // inputs get all the remaining shared memory: the deeper this ring, the less the tensor core waits for operands.
-    static constexpr int SA = 2;
-    static constexpr int SB = NMAT == 2 ? 4 : 5;
+    static constexpr int STAGES = NMAT == 2 ? 3 : 4;
     static constexpr int A_BYTES = TM * TK * 2;             // 16 KB per matrix
     static constexpr int B_BYTES = TN * TK * 2;             // 32 KB
-    static constexpr int A_SLOT = NMAT * A_BYTES;
-    static constexpr int b0 = SA * A_SLOT;                  // the input ring starts here
-    static constexpr int bars = b0 + SB * B_BYTES;          // full_a[SA], empty_a[SA], full_b[SB], empty_b[SB], done[2], tmem_free[2]
-    static constexpr int misc = bars + (2 * SA + 2 * SB + 4) * 8;
+    static constexpr int STAGE = NMAT * A_BYTES + B_BYTES;
+    static constexpr int bars = STAGES * STAGE;             // full_a[S], full_b[S], empty[S], done[2], tmem_free[2]
+    static constexpr int misc = bars + (3 * STAGES + 4) * 8;
     static constexpr int total = misc + 32 + 1024;          // + slack to align the base to 1024
 };
 
@@ -325,8 +317,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t sbase = (raw + 1023u) & ~1023u;
     unsigned char* smem = smem_raw + (sbase - raw);
-    const uint32_t full_a = sbase + L::bars, empty_a = full_a + L::SA * 8, full_b = empty_a + L::SA * 8, empty_b = full_b + L::SB * 8,
-                   done = empty_b + L::SB * 8, tmem_free = done + 2 * 8;      // done[NACC], tmem_free[NACC]
+    const uint32_t full_a = sbase + L::bars, full_b = full_a + L::STAGES * 8, empty = full_b + L::STAGES * 8,
+                   done = empty + L::STAGES * 8, tmem_free = done + 2 * 8;      // done[NACC], tmem_free[NACC]
     uint32_t* tmem_slot = (uint32_t*) (smem + L::misc);
     volatile int* abort_flag = (volatile int*) (smem + L::misc + 8);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -336,8 +328,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
 
     if (threadIdx.x == 0)
     {
-        for (int i = 0; i < L::SA; ++i) { mbar_init(full_a + i * 8, NDQ); mbar_init(empty_a + i * 8, 1); }
-        for (int i = 0; i < L::SB; ++i) { mbar_init(full_b + i * 8, 1); mbar_init(empty_b + i * 8, 1); }
+        for (int i = 0; i < L::STAGES; ++i) { mbar_init(full_a + i * 8, NMAT == 2 ? NDQ : NDQ / 2); mbar_init(full_b + i * 8, 1); mbar_init(empty + i * 8, 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(done + i * 8, 1); mbar_init(tmem_free + i * 8, NEPI); }
         *abort_flag = 0;
         fence_barrier_init();
@@ -357,15 +348,14 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
 
     if (warp < NDQ)
     {
-        // ---- dequantise. gate_up: 2 matrices x 2 units x 4 strips = 16 strips of 16 rows x 64 columns per stage, one per warp (a
-        // 16-byte word per lane). down: 8 strips per stage, two warps each: one takes the first 32 columns (8 bytes per lane), the
-        // other the last 32. Every warp works on every stage, so a slot is refilled in the time of one strip. The packed words
-        // are fetched NPF stages ahead. These warps do nothing else: they stream from tile to tile and stop only when the ring
-        // is full, so the MMA thread always finds its next stages.
+        // ---- dequantise: one 16-row strip of one 64-row unit per warp and stage. gate_up: 2 matrices x 2 units x 4 strips =
+        // 16 strip-blocks per stage, one per warp. down: 8 strip-blocks per stage; warps 0-7 take the even stages, warps
+        // 8-15 the odd ones. The packed words are fetched NPF of the warp's stages ahead. These warps do nothing else: they
+        // stream from tile to tile and stop only when the ring is full, so the MMA thread always finds its next stages.
         const int g = lane >> 2, q = lane & 3;
-        const int strip = warp & 3, unit = (warp >> 2) & 1, mat = NMAT == 2 ? warp >> 3 : 0, khalf = NMAT == 2 ? 0 : warp >> 3;
-        constexpr int NW = NMAT == 2 ? 4 : 2;                 // 32-bit words per lane and stage
-        constexpr int NPF = NMAT == 2 ? 4 : 6;
+        const int strip = warp & 3, unit = (warp >> 2) & 1, mat = NMAT == 2 ? warp >> 3 : 0;
+        const int kb0 = NMAT == 2 ? 0 : warp >> 3, kstep = NMAT == 2 ? 1 : 2;
+        constexpr int NPF = 4;
         bool ok = true;
         uint32_t tile_n = 0;
         for (int item = blockIdx.x; item < nitems && ok; item += gridDim.x, ++tile_n)
@@ -374,42 +364,35 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
             const int rb = item / NCT, ct = item % NCT, e = a.rbt[4 * rb];
             const void* wp = e < a.n_local ? (const void*) (mat ? a.w1[e] : a.w0[e]) : (mat ? a.sh_w1 : a.sh_w0);
             const void* sp = e < a.n_local ? (const void*) (mat ? a.s1[e] : a.s0[e]) : (mat ? a.sh_s1 : a.sh_s0);
-            const char* wbase = (const char*) wp + ((size_t) (2 * ct + unit) * KB * 4 + strip) * 512 + lane * 16 + khalf * 8;
+            const char* wbase = (const char*) wp + ((size_t) (2 * ct + unit) * KB * 4 + strip) * 512 + lane * 16;
             const char* sbase_p = (const char*) sp + ((size_t) (2 * ct + unit) * (a.K / 128) * 64 + g * 8 + 2 * strip) * 2;
-            // packed words and scale pairs of the next NPF stages, in flight while the current one is converted
-            uint32_t wq[NPF][NW]; uint32_t sq[NPF];
-            auto fetch = [&](int kbi, uint32_t (&w)[NW], uint32_t& sc) {
-                const int kbw = kbi >= KB ? kbi - KB : kbi;            // second pass over the weights for the lo halves
-                if (kbi < KBT)
-                {
-                    if (NW == 4) { const uint4 v = ldg128_nc(wbase + (size_t) kbw * 2048); w[0] = v.x; w[1] = v.y; w[NW - 2] = v.z; w[NW - 1] = v.w; }
-                    else { const uint2 v = __ldg((const uint2*) (wbase + (size_t) kbw * 2048)); w[0] = v.x; w[1] = v.y; }
-                }
-                else { for (int i = 0; i < NW; ++i) w[i] = 0u; }
-                sc = (a.grouped && kbi < KBT) ? __ldg((const uint32_t*) (sbase_p + (size_t) (kbw >> 1) * 128)) : 0u;
-            };
+            // packed words and scale pairs of the next NPF of this warp's stages, in flight while the current one is converted
+            uint4 wq[NPF]; uint32_t sq[NPF];
             #pragma unroll
-            for (int i = 0; i < NPF; ++i) fetch(i, wq[i], sq[i]);
-            const uint32_t it0 = tile_n * (uint32_t) KBT;
-            for (int kb = 0; kb < KBT; ++kb)
+            for (int i = 0; i < NPF; ++i)
             {
-                const uint32_t gi = it0 + kb, s = gi % L::SA;
-                uint32_t wc[NW];
-                #pragma unroll
-                for (int i = 0; i < NW; ++i) wc[i] = wq[0][i];
+                const int kbi = kb0 + i * kstep;
+                const int kbw = kbi >= KB ? kbi - KB : kbi;            // second pass over the weights for the lo halves
+                wq[i] = kbi < KBT ? ldg128_nc(wbase + (size_t) kbw * 2048) : make_uint4(0, 0, 0, 0);
+                sq[i] = (a.grouped && kbi < KBT) ? __ldg((const uint32_t*) (sbase_p + (size_t) (kbw >> 1) * 128)) : 0u;
+            }
+            const uint32_t it0 = tile_n * (uint32_t) KBT;
+            for (int kb = kb0; kb < KBT; kb += kstep)
+            {
+                const uint32_t gi = it0 + kb, s = gi % L::STAGES;
+                const uint4 wc = wq[0];
                 const uint32_t sc = sq[0];
                 #pragma unroll
-                for (int i = 0; i + 1 < NPF; ++i)
+                for (int i = 0; i + 1 < NPF; ++i) { wq[i] = wq[i + 1]; sq[i] = sq[i + 1]; }
                 {
-                    #pragma unroll
-                    for (int j = 0; j < NW; ++j) wq[i][j] = wq[i + 1][j];
-                    sq[i] = sq[i + 1];
+                    const int kbn = kb + NPF * kstep, kbw = kbn >= KB ? kbn - KB : kbn;
+                    wq[NPF - 1] = kbn < KBT ? ldg128_nc(wbase + (size_t) kbw * 2048) : make_uint4(0, 0, 0, 0);
+                    sq[NPF - 1] = (a.grouped && kbn < KBT) ? __ldg((const uint32_t*) (sbase_p + (size_t) (kbw >> 1) * 128)) : 0u;
                 }
-                fetch(kb + NPF, wq[NPF - 1], sq[NPF - 1]);
-                if (gi >= (uint32_t) L::SA && !mbar_wait(empty_a + s * 8, ((gi / L::SA) - 1) & 1, abort_flag, a.status)) { ok = false; break; }
+                if (gi >= (uint32_t) L::STAGES && !mbar_wait(empty + s * 8, ((gi / L::STAGES) - 1) & 1, abort_flag, a.status)) { ok = false; break; }
                 uint32_t s_lo = 0, s_hi = 0;
                 if (a.grouped) scale_pair(sc, s_lo, s_hi);
-                store_strip<NW>(sbase + s * L::A_SLOT + mat * L::A_BYTES, unit * 8 + strip * 2, g, q, wc, 2 * khalf, s_lo, s_hi, a.grouped != 0);
+                store_strip(sbase + s * L::STAGE + mat * L::A_BYTES, unit * 8 + strip * 2, g, q, wc, s_lo, s_hi, a.grouped != 0);
                 fence_proxy_async();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(full_a + s * 8);
@@ -427,10 +410,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
                 const int pos0 = a.rbt[4 * (item / NCT) + 1];
                 for (int kb = 0; kb < KBT; ++kb)
                 {
-                    const uint32_t it = tile_n * (uint32_t) KBT + kb, s = it % L::SB;
-                    if (it >= (uint32_t) L::SB && !mbar_wait(empty_b + s * 8, ((it / L::SB) - 1) & 1, abort_flag, a.status)) { ok = false; break; }
+                    const uint32_t it = tile_n * (uint32_t) KBT + kb, s = it % L::STAGES;
+                    if (it >= (uint32_t) L::STAGES && !mbar_wait(empty + s * 8, ((it / L::STAGES) - 1) & 1, abort_flag, a.status)) { ok = false; break; }
                     mbar_expect_tx(full_b + s * 8, L::B_BYTES);
-                    tma_load_2d(sbase + L::b0 + s * L::B_BYTES, &tmap, kb * 64, pos0, full_b + s * 8);
+                    tma_load_2d(sbase + s * L::STAGE + NMAT * L::A_BYTES, &tmap, kb * 64, pos0, full_b + s * 8);
                 }
             }
         }
@@ -452,10 +435,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
                 tc_fence_after();
                 for (int kb = 0; kb < KBT && ok; ++kb)
                 {
-                    const uint32_t it = tile_n * (uint32_t) KBT + kb, sa = it % L::SA, sb = it % L::SB;
-                    if (!mbar_wait(full_a + sa * 8, (it / L::SA) & 1, abort_flag, a.status) || !mbar_wait(full_b + sb * 8, (it / L::SB) & 1, abort_flag, a.status)) { ok = false; break; }
+                    const uint32_t it = tile_n * (uint32_t) KBT + kb, s = it % L::STAGES, ph = (it / L::STAGES) & 1;
+                    if (!mbar_wait(full_a + s * 8, ph, abort_flag, a.status) || !mbar_wait(full_b + s * 8, ph, abort_flag, a.status)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t at = sbase + sa * L::A_SLOT, bt = sbase + L::b0 + sb * L::B_BYTES;
+                    const uint32_t at = sbase + s * L::STAGE, bt = at + NMAT * L::A_BYTES;
                     #pragma unroll
                     for (int k = 0; k < 4; ++k)
                     {
@@ -463,8 +446,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
                         mma_f16_ss(tacc, smem_desc_sw128(at + k * 32), bd, idesc, (kb | k) != 0);
                         if (NMAT == 2) mma_f16_ss(tacc + 256, smem_desc_sw128(at + L::A_BYTES + k * 32), bd, idesc, (kb | k) != 0);
                     }
-                    tc_commit(empty_a + sa * 8);         // both arrive when the MMAs issued so far have read their operands
-                    tc_commit(empty_b + sb * 8);
+                    tc_commit(empty + s * 8);
                 }
                 if (ok) tc_commit(done + acc * 8);
             }
