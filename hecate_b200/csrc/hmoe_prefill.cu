@@ -184,23 +184,25 @@ __global__ void __launch_bounds__(192) gather_kernel(const void* __restrict__ x,
             for (int k = 0; k < 32; ++k) v[k] = __fmul_rn((float) __float2int_rn(__fmul_rn(v[k], inv)), s);
         }
         const size_t rowlen = act_quant ? 2 * (size_t) H : (size_t) H;       // int8 mode: [hi | lo] halves, code x scale kept to ~22 bits
-        uint4* d = (uint4*) (xg + (size_t) pos * rowlen + gi * 32);
-        uint4* dl = (uint4*) (xg + (size_t) pos * rowlen + H + gi * 32);
+        // The 64 columns of a block are stored in the order the weight tiles use (operand_pos): the thread's 32 columns (16-column
+        // steps 2j, 2j + 1 of the block) become, for each q, eight consecutive values = one 16-byte store.
+        const int kb = gi >> 1, j8 = (gi & 1) * 8;
         #pragma unroll
-        for (int j = 0; j < 4; ++j)
+        for (int q = 0; q < 4; ++q)
         {
             uint32_t w[4], wl[4];
             #pragma unroll
-            for (int k = 0; k < 4; ++k)
+            for (int i = 0; i < 4; ++i)
             {
-                const __half2 h = __floats2half2_rn(v[j * 8 + 2 * k], v[j * 8 + 2 * k + 1]);
-                w[k] = *(const uint32_t*) &h;
+                const int c = (i >> 1) * 16 + (i & 1) * 8 + 2 * q;           // step (i / 2), half (i % 2), columns 2q, 2q + 1
+                const __half2 h = __floats2half2_rn(v[c], v[c + 1]);
+                w[i] = *(const uint32_t*) &h;
                 const float2 f = __half22float2(h);
-                const __half2 l = __floats2half2_rn(v[j * 8 + 2 * k] - f.x, v[j * 8 + 2 * k + 1] - f.y);
-                wl[k] = *(const uint32_t*) &l;
+                const __half2 l = __floats2half2_rn(v[c] - f.x, v[c + 1] - f.y);
+                wl[i] = *(const uint32_t*) &l;
             }
-            d[j] = make_uint4(w[0], w[1], w[2], w[3]);
-            if (act_quant) dl[j] = make_uint4(wl[0], wl[1], wl[2], wl[3]);
+            *(uint4*) (xg + (size_t) pos * rowlen + kb * 64 + q * 16 + j8) = make_uint4(w[0], w[1], w[2], w[3]);
+            if (act_quant) *(uint4*) (xg + (size_t) pos * rowlen + H + kb * 64 + q * 16 + j8) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
         }
     }
 }
@@ -268,25 +270,44 @@ struct GemmArgs
     unsigned* status;
 };
 
-// One 16-row x 64-column strip of packed codes (one 16-byte word per lane) -> 16 fp16x2 values stored into the K-major
-// 128-byte-swizzled operand tile. r8 = index of the strip's first 8-row group in the tile; the lane's rows are g and g + 8.
-__device__ __forceinline__ void store_strip(uint32_t tile, int r8, int g, int q, const uint4& w, uint32_t s_lo, uint32_t s_hi, bool scaled)
+// Column order of the GEMM operands inside every block of 64 columns. The tensor core only needs both operands to agree on
+// which stored position holds which column, so the order is chosen for the weights: a lane (g, q) of the dequantising warps holds,
+// of rows g and g + 8, the columns 16 t + 8 h + 2 q + cc (t = 0..3, h, cc = 0..1) of the block, and these go to positions
+// 16 q + 4 t + 2 h + cc: the lane's sixteen values of a row are contiguous (32 bytes, two 16-byte stores). The gathered inputs
+// and the intermediate activations are written in the same order (gather_kernel, the gate_up read-out).
+__host__ __device__ __forceinline__ int operand_pos(int k) { return ((k >> 1) & 3) * 16 + (k >> 4) * 4 + ((k >> 3) & 1) * 2 + (k & 1); }
+
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
+{
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+// One 16-row x 64-column strip of packed codes (one 16-byte word per lane) -> 32 fp16 values per lane (a[t] = the four registers
+// of 16-column step t, times the group scale), and their store into the K-major 128-byte-swizzled operand tile as four 16-byte
+// words (conflict free: the eight lanes of a quarter warp hit eight different 16-byte columns). The two halves are separate
+// functions because the conversion is done BEFORE the warp waits for its ring slot: when the slot is released only the four
+// stores stand between the release and the MMA thread's wake-up.
+__device__ __forceinline__ void convert_strip(const uint4& w, uint32_t s_lo, uint32_t s_hi, bool scaled, uint32_t (&a)[4][4])
 {
     const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-    const uint32_t row0 = tile + r8 * 1024 + g * 128 + 4 * q, row1 = row0 + 1024;
     #pragma unroll
     for (int t = 0; t < 4; ++t)
     {
-        uint32_t a[4];
-        frag_from_codes(ww[t], a);
+        frag_from_codes(ww[t], a[t]);
         if (scaled)
         {
-            asm("mul.f16x2 %0, %0, %1;" : "+r"(a[0]) : "r"(s_lo)); asm("mul.f16x2 %0, %0, %1;" : "+r"(a[2]) : "r"(s_lo));
-            asm("mul.f16x2 %0, %0, %1;" : "+r"(a[1]) : "r"(s_hi)); asm("mul.f16x2 %0, %0, %1;" : "+r"(a[3]) : "r"(s_hi));
+            asm("mul.f16x2 %0, %0, %1;" : "+r"(a[t][0]) : "r"(s_lo)); asm("mul.f16x2 %0, %0, %1;" : "+r"(a[t][2]) : "r"(s_lo));
+            asm("mul.f16x2 %0, %0, %1;" : "+r"(a[t][1]) : "r"(s_hi)); asm("mul.f16x2 %0, %0, %1;" : "+r"(a[t][3]) : "r"(s_hi));
         }
-        const uint32_t c0 = (uint32_t) (((2 * t) ^ g) << 4), c1 = (uint32_t) (((2 * t + 1) ^ g) << 4);
-        sts32(row0 + c0, a[0]); sts32(row1 + c0, a[1]); sts32(row0 + c1, a[2]); sts32(row1 + c1, a[3]);
     }
+}
+// row0 = shared address of the lane's row g in the strip's first 8-row group; c0, c1 = byte offsets of its two 16-byte columns
+__device__ __forceinline__ void store_strip(uint32_t row0, uint32_t c0, uint32_t c1, const uint32_t (&a)[4][4])
+{
+    sts128(row0 + c0, a[0][0], a[0][2], a[1][0], a[1][2]);
+    sts128(row0 + c1, a[2][0], a[2][2], a[3][0], a[3][2]);
+    sts128(row0 + 1024 + c0, a[0][1], a[0][3], a[1][1], a[1][3]);
+    sts128(row0 + 1024 + c1, a[2][1], a[2][3], a[3][1], a[3][3]);
 }
 
 // bf16 pair (rows g, g + 8 of a strip) -> two fp16x2 broadcast registers
@@ -355,7 +376,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
         const int g = lane >> 2, q = lane & 3;
         const int strip = warp & 3, unit = (warp >> 2) & 1, mat = NMAT == 2 ? warp >> 3 : 0;
         const int kb0 = NMAT == 2 ? 0 : warp >> 3, kstep = NMAT == 2 ? 1 : 2;
-        constexpr int NPF = 4;
+        constexpr int NPF = 3;
+        // shared address of this lane's row g in slot 0, and its two 16-byte columns under the 128-byte swizzle
+        const uint32_t row_off = sbase + mat * L::A_BYTES + (unit * 8 + strip * 2) * 1024 + g * 128;
+        const uint32_t c0 = (uint32_t) (((2 * q) ^ g) << 4), c1 = (uint32_t) (((2 * q + 1) ^ g) << 4);
         bool ok = true;
         uint32_t tile_n = 0;
         for (int item = blockIdx.x; item < nitems && ok; item += gridDim.x, ++tile_n)
@@ -366,36 +390,41 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
             const void* sp = e < a.n_local ? (const void*) (mat ? a.s1[e] : a.s0[e]) : (mat ? a.sh_s1 : a.sh_s0);
             const char* wbase = (const char*) wp + ((size_t) (2 * ct + unit) * KB * 4 + strip) * 512 + lane * 16;
             const char* sbase_p = (const char*) sp + ((size_t) (2 * ct + unit) * (a.K / 128) * 64 + g * 8 + 2 * strip) * 2;
-            // packed words and scale pairs of the next NPF of this warp's stages, in flight while the current one is converted
+            // packed words and scale pairs of the next NPF of this warp's stages, in flight while earlier ones are converted
+            // (the queue is indexed with compile-time positions: the loop over the stages is unrolled NPF times)
             uint4 wq[NPF]; uint32_t sq[NPF];
-            #pragma unroll
-            for (int i = 0; i < NPF; ++i)
-            {
-                const int kbi = kb0 + i * kstep;
+            auto fetch = [&](int kbi, uint4& w, uint32_t& sc) {
                 const int kbw = kbi >= KB ? kbi - KB : kbi;            // second pass over the weights for the lo halves
-                wq[i] = kbi < KBT ? ldg128_nc(wbase + (size_t) kbw * 2048) : make_uint4(0, 0, 0, 0);
-                sq[i] = (a.grouped && kbi < KBT) ? __ldg((const uint32_t*) (sbase_p + (size_t) (kbw >> 1) * 128)) : 0u;
-            }
-            const uint32_t it0 = tile_n * (uint32_t) KBT;
-            for (int kb = kb0; kb < KBT; kb += kstep)
-            {
-                const uint32_t gi = it0 + kb, s = gi % L::STAGES;
-                const uint4 wc = wq[0];
-                const uint32_t sc = sq[0];
-                #pragma unroll
-                for (int i = 0; i + 1 < NPF; ++i) { wq[i] = wq[i + 1]; sq[i] = sq[i + 1]; }
-                {
-                    const int kbn = kb + NPF * kstep, kbw = kbn >= KB ? kbn - KB : kbn;
-                    wq[NPF - 1] = kbn < KBT ? ldg128_nc(wbase + (size_t) kbw * 2048) : make_uint4(0, 0, 0, 0);
-                    sq[NPF - 1] = (a.grouped && kbn < KBT) ? __ldg((const uint32_t*) (sbase_p + (size_t) (kbw >> 1) * 128)) : 0u;
-                }
-                if (gi >= (uint32_t) L::STAGES && !mbar_wait(empty + s * 8, ((gi / L::STAGES) - 1) & 1, abort_flag, a.status)) { ok = false; break; }
+                w = kbi < KBT ? ldg128_nc(wbase + (size_t) kbw * 2048) : make_uint4(0, 0, 0, 0);
+                sc = (a.grouped && kbi < KBT) ? __ldg((const uint32_t*) (sbase_p + (size_t) (kbw >> 1) * 128)) : 0u;
+            };
+            auto convert = [&](const uint4& w, uint32_t sc, uint32_t (&cv)[4][4]) {
                 uint32_t s_lo = 0, s_hi = 0;
                 if (a.grouped) scale_pair(sc, s_lo, s_hi);
-                store_strip(sbase + s * L::STAGE + mat * L::A_BYTES, unit * 8 + strip * 2, g, q, wc, s_lo, s_hi, a.grouped != 0);
-                fence_proxy_async();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(full_a + s * 8);
+                convert_strip(w, s_lo, s_hi, a.grouped != 0, cv);
+            };
+            #pragma unroll
+            for (int i = 0; i < NPF; ++i) fetch(kb0 + i * kstep, wq[i], sq[i]);
+            uint32_t cv[4][4];                                 // the converted strip of the warp's next stage
+            convert(wq[0], sq[0], cv);
+            const uint32_t it0 = tile_n * (uint32_t) KBT;
+            for (int kbase = kb0; kbase < KBT && ok; kbase += NPF * kstep)
+            {
+                #pragma unroll
+                for (int u = 0; u < NPF; ++u)
+                {
+                    const int kb = kbase + u * kstep;
+                    if (kb >= KBT || !ok) continue;
+                    const uint32_t gi = it0 + kb, s = gi % L::STAGES;
+                    if (gi >= (uint32_t) L::STAGES && !mbar_wait(empty + s * 8, ((gi / L::STAGES) - 1) & 1, abort_flag, a.status)) { ok = false; continue; }
+                    store_strip(row_off + s * L::STAGE, c0, c1, cv);
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(full_a + s * 8);
+                    // off the critical path: refill the queue position just used and convert the next stage's words
+                    fetch(kb + NPF * kstep, wq[u], sq[u]);
+                    convert(wq[(u + 1) % NPF], sq[(u + 1) % NPF], cv);
+                }
             }
         }
     }
@@ -472,6 +501,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
             tc_fence_after();
             const uint32_t n16 = (uint32_t) ((n + 15) & ~15);
             const int ch = ct * TM + lq * 32 + lane;
+            const int chp = (ch & ~63) + operand_pos(ch & 63);       // where the down GEMM expects this channel of the activations
             const uint32_t tacc = tmem + acc * 256 + ((uint32_t) (lq * 32) << 16);
             float sc0 = 1.f, sc1 = 1.f;
             if (!a.grouped)
@@ -511,15 +541,15 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
                                 v = __fmul_rn((float) __float2int_rn(__fmul_rn(v, __fdiv_rn(1.f, sq8))), sq8);
                                 // code x scale does not fit fp16: keep it as hi + lo halves, the down GEMM walks both
                                 const __half hi = __float2half_rn(v);
-                                a.act[(size_t) (pos0 + p) * (2 * a.N) + ch] = hi;
-                                a.act[(size_t) (pos0 + p) * (2 * a.N) + a.N + ch] = __float2half_rn(v - __half2float(hi));
+                                a.act[(size_t) (pos0 + p) * (2 * a.N) + chp] = hi;
+                                a.act[(size_t) (pos0 + p) * (2 * a.N) + a.N + chp] = __float2half_rn(v - __half2float(hi));
                             }
                             else
                             {
                                 // fp16 result: the fast exponential and division are far inside its rounding (the reference's
                                 // kernels make the same choice, runtime/tier/moe4/moe4t.cu:404-425 built with fast-math)
                                 const float v = __fdividef(gg, 1.f + __expf(-gg)) * uu * w;
-                                a.act[(size_t) (pos0 + p) * a.N + ch] = __float2half_rn(v);
+                                a.act[(size_t) (pos0 + p) * a.N + chp] = __float2half_rn(v);
                             }
                         }
                     }
