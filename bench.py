@@ -627,8 +627,8 @@ def run_ep(args, world, rank, dev):
 def stack_arm(args, world, rank, dev, L, torch, dist, ep, moe, synth):
     """The expert stack of a whole model: L MoE layers with per-layer weights and router (layer index in the seed), the experts
     of every layer split over the GPUs, decode batch of 8 tokens x (1 + 1 draft) = 16 rows that are data-parallel (rank r holds
-    rows r, r + world, ...). Per layer and rank: router on the rank's rows -> dispatch (all-gather of rows, selections, weights over
-    peer memory) -> expert kernels -> combine of the rank's rows over peer memory. One CUDA graph replays all L layers of a step.
+    rows r, r + world, ...). Per layer and rank: dispatch of the rank's rows over peer memory + router + set-up (one launch) ->
+    expert kernels -> combine of the rank's rows over peer memory. One CUDA graph replays all L layers of a step.
     Successive layers use different input batches, so every layer routes differently."""
     pl = ep.shard_plan(rank, world, E)
     layers = [Layer(dev, 1000 + 16 * l + rank, pl["n_local"]) for l in range(L)]
@@ -649,10 +649,7 @@ def stack_arm(args, world, rank, dev, L, torch, dist, ep, moe, synth):
     def step(b):
         for l in range(L):
             if world > 1:
-                x = xo[(b + l) % (NB + 1)]
-                if n_own:
-                    moe.router_fused(x, wts[l], bias, None, None, sel, rw, TOPK, 1.0)
-                dec.step_dp(x, sel, rw, f_own, ROWS, tables=layers[l].tabs)
+                dec.step_dp_fused(xo[(b + l) % (NB + 1)], wts[l], bias, 1.0, sel16, rw16, f_own, ROWS, tables=layers[l].tabs)
             else:
                 x = xs[(b + l) % (NB + 1)]
                 moe.router_fused(x, wts[l], bias, None, None, sel16, rw16, TOPK, 1.0)
@@ -683,7 +680,7 @@ def stack_arm(args, world, rank, dev, L, torch, dist, ep, moe, synth):
     return {"metric": "moe_stack_decode_us_per_layer", "value": t * 1e3 / L, "unit": "us/layer", "layers": L, "ms_per_step": t, "steps": steps,
             "warmup": warmup, "tokens_per_s": 8 / (t * 1e-3), "rows_per_s": ROWS / (t * 1e-3), "experts_per_gpu_per_layer": pl["n_local"],
             "resident_gb_per_gpu": resident / 1e9, "launch": "eager" if args.no_graph else "one cuda graph per step over all layers",
-            "dispatch_bytes_per_rank_per_layer": (world - 1) * n_own * (H * 2 + TOPK * 10) if world > 1 else 0,
+            "dispatch_bytes_per_rank_per_layer": (world - 1) * n_own * H * 2 if world > 1 else 0,
             "combine_bytes_per_rank_per_layer": (world - 1) * n_own * H * 4 if world > 1 else 0,
             "config": {"workload": f"{L} MoE layers (per-layer random weights and routing from seed), decode M=8 tokens x 2 rows, experts "
                                    f"split over {world} GPUs, data-parallel tokens with dispatch + combine over NVLink peer memory every layer"},
@@ -692,9 +689,9 @@ def stack_arm(args, world, rank, dev, L, torch, dist, ep, moe, synth):
 
 def ep_decode_arm(args, world, rank, dev, tabs, pl, torch, dist, ep, moe, synth):
     """Two arms. "peer" (the headline): the 16 rows are data-parallel (rank r holds rows r, r + world, ...); per step every rank
-    routes its own rows, dispatches them (rows, selections, weights: an all-gather over NVLink peer memory), runs its experts on
-    all rows and brings its own rows' sums back over peer memory. "nccl" (the baseline): rows replicated, router replicated,
-    NCCL all-reduce of the fp32 partials."""
+    dispatches its rows (an all-gather over NVLink peer memory, done by the router's own launch), routes all rows, runs its experts
+    on them and brings its own rows' sums back over peer memory: four launches (hmoe_decode_ep_dp). "nccl" (the baseline): rows
+    replicated, router replicated, NCCL all-reduce of the fp32 partials."""
     steps, warmup = args.steps, max(3, args.warmup)
     wt = torch.from_numpy(synth.router_weight(0, 0, E, H)).to(dev).to(torch.bfloat16)
     bias = torch.zeros(E, dtype=torch.float32, device=dev)
@@ -717,12 +714,10 @@ def ep_decode_arm(args, world, rank, dev, tabs, pl, torch, dist, ep, moe, synth)
     for mode in ("nccl", "peer"):
         dec = ep.EpDecoder(rank, world, tabs, E, dev, dist, use_peer=(mode == "peer"))
         if mode == "peer":
-            disp_bytes = dec.dispatch_bytes(ROWS)
+            disp_bytes = dec.dispatch_bytes(ROWS, with_routing=False)
 
-            def step(x):                        # x: this rank's rows
-                if n_own:
-                    moe.router_fused(x, wt, bias, None, None, sel_o, rw_o, TOPK, 1.0)
-                dec.step_dp(x, sel_o, rw_o, f_o, ROWS)
+            def step(x):                        # x: this rank's rows; one launch dispatches them, routes all rows and sets up
+                dec.step_dp_fused(x, wt, bias, 1.0, sel, rw, f_o, ROWS)
             inputs, hosts, x_dev, out_dev = xo, xo_host, xo_in, f_o
         else:
             def step(x):                        # x: all rows

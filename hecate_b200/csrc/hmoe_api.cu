@@ -257,6 +257,36 @@ int hmoe_decode_ep_combine(const hmoe_layer* layer, const void* x, int x_dtype, 
                          shared_rem, gen, slot_floats, false, &e);
 }
 
+int hmoe_decode_ep_dp(const hmoe_layer* layer, const void* x_own, int x_dtype, const void* wt, int w_dtype, const float* bias, int R, int E,
+                      float scale, int64_t* sel, void* rw, void* router_ws, size_t router_ws_bytes, int lo, int n_local, int act_quant, void* ws,
+                      size_t ws_bytes, int rank, int world, void* const* stage, void* const* slots, void* const* flags, uint32_t* gen,
+                      size_t slot_floats, float* f_own, uint32_t* status, int fused_tail, void* stream)
+{
+    if (!layer) return fail(HMOE_E_ARG, "hmoe_decode_ep_dp: null layer");
+    if (world < 1 || world > 8 || rank < 0 || rank >= world || !stage || !slots || !flags || !gen || !status || !f_own)
+        return fail(HMOE_E_ARG, "hmoe_decode_ep_dp: world 1..8, buffers");
+    if (R < 1 || R > MAXR || layer->H % 8) return fail(HMOE_E_ARG, "hmoe_decode_ep_dp: rows 1..16");
+    const int n_own = R > rank ? (R - rank + world - 1) / world : 0;
+    if (n_own > 0 && !x_own) return fail(HMOE_E_ARG, "hmoe_decode_ep_dp: null rows");
+    const StageLayout SL(layer->H, layer->topk);
+    const void* x_all = (const char*) stage[rank] + SL.x;          // after the launch below: all rows, in the local staging area
+    PrepArgs pa;
+    int rc = decode_prep_args(layer, x_all, x_dtype, R, lo, n_local, act_quant, ws, ws_bytes, world, rank, gen, &pa);
+    if (rc) return rc;
+    DispArgs da;
+    da.rank = rank; da.world = world; da.n_own = n_own; da.words = layer->H / 8; da.x_own = (const uint4*) x_own;
+    da.x_off = SL.x; da.flags_off = SL.flags; da.ctl_off = SL.ctl;
+    for (int p = 0; p < 8; ++p) da.stage[p] = p < world ? (char*) stage[p] : nullptr;
+    cudaStream_t st = (cudaStream_t) stream;
+    rc = router_prepare_launch(x_all, x_dtype, wt, w_dtype, bias, R, layer->H, E, layer->topk, scale, sel, rw, router_ws, router_ws_bytes, pa, st, &da);
+    if (rc) return rc;
+    EpCombineArgs e = {rank, world, 1, slots, flags, f_own, status};
+    rc = decode_launch(layer, x_all, x_dtype, sel, rw, R, lo, n_local, act_quant, (float*) slots[rank], ws, ws_bytes, st, world, rank, gen, slot_floats, true,
+                       fused_tail ? &e : nullptr);
+    if (rc || fused_tail) return rc;
+    return ep_combine_launch(rank, world, slots, flags, gen, f_own, R, layer->H, slot_floats, status, st, 1);
+}
+
 int hmoe_combine(float* f, const float* o, float* y, int64_t n, const float* o2, void* stream)
 {
     if (!f || !y || n < 0 || n % 4) return fail(HMOE_E_ARG, "hmoe_combine: f, y and n % 4 == 0 required");

@@ -163,6 +163,26 @@ __device__ __forceinline__ float det_expf(float x)
     return __fmul_rn(p, __int_as_float(((int) n + 127) << 23));
 }
 
+// ---- expert-parallel exchange over peer memory: flag stores / loads at system scope, and the staging area every rank keeps
+// for the decode dispatch (the step's rows, selections and weights at their global row positions, one flag per sending rank,
+// two control words)
+__device__ __forceinline__ void sys_st_release(unsigned* p, unsigned v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ unsigned sys_ld_acquire(const unsigned* p)
+{
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+struct StageLayout
+{
+    size_t x, sel, rw, flags, ctl, total;
+    __host__ __device__ StageLayout(int H, int topk)
+    {
+        x = 0; sel = x + (size_t) MAXR * H * 2; rw = sel + (size_t) MAXR * topk * 8; flags = (rw + (size_t) MAXR * topk * 2 + 255) / 256 * 256;
+        ctl = flags + 256; total = ctl + 256;
+    }
+};
+
 // ---- pieces of the residual + RMS-norm kernels (hmoe_combine_norm, hmoe_norm_router): 4-wide column arithmetic in the order
 // the bit-identity contract with the reference norm kernels fixes (see sum_norm_kernel)
 __device__ __forceinline__ float4 vec_add(float4 a, const float4 b) { a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w; return a; }

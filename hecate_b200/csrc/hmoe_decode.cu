@@ -134,12 +134,16 @@ __device__ __forceinline__ void ep_tail_combine(const EpTail& e, unsigned gen, s
             if (r % e.world != e.rank) continue;
             o = (r / e.world) * H + (i - r * H);
         }
+        // all peers' loads are issued before the first sum (a warp issues in order: a sum between two loads would serialise
+        // the NVLink round trips); the sums then run in rank order
+        float4 v[8];
+        #pragma unroll
+        for (int p = 0; p < 8; ++p)
+            if (p < e.world) v[p] = ep_ld_peer((const float4*) (e.slots[p] + (size_t) parity * slot_floats + i));
         float4 acc = *(float4*) (e.f + o);
-        for (int p = 0; p < e.world; ++p)
-        {
-            const float4 v = ep_ld_peer((const float4*) (e.slots[p] + (size_t) parity * slot_floats + i));
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-        }
+        #pragma unroll
+        for (int p = 0; p < 8; ++p)
+            if (p < e.world) { acc.x += v[p].x; acc.y += v[p].y; acc.z += v[p].z; acc.w += v[p].w; }
         *(float4*) (e.f + o) = acc;
     }
 }

@@ -74,12 +74,16 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(const EpArgs a, const u
             if (r % a.world != a.rank) continue;
             o = (r / a.world) * H + (i - r * H);
         }
+        // all peers' loads are issued before the first sum (a warp issues in order: a sum between two loads would serialise
+        // the NVLink round trips); the sums then run in rank order
+        float4 v[8];
+        #pragma unroll
+        for (int p = 0; p < 8; ++p)
+            if (p < a.world) v[p] = ld_peer((const float4*) (a.slots[p] + (size_t) parity * slot_floats + i));
         float4 acc = *(float4*) (f + o);
-        for (int p = 0; p < a.world; ++p)
-        {
-            const float4 v = ld_peer((const float4*) (a.slots[p] + (size_t) parity * slot_floats + i));
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-        }
+        #pragma unroll
+        for (int p = 0; p < 8; ++p)
+            if (p < a.world) { acc.x += v[p].x; acc.y += v[p].y; acc.z += v[p].z; acc.w += v[p].w; }
         *(float4*) (f + o) = acc;
     }
 }
@@ -97,17 +101,9 @@ struct StageArgs
     int rank, world;
     char* stage[8];
 };
-struct StageLayout
-{
-    size_t x, sel, rw, flags, ctl, total;
-    __host__ __device__ StageLayout(int H, int topk)
-    {
-        x = 0; sel = x + (size_t) MAXR * H * 2; rw = sel + (size_t) MAXR * topk * 8; flags = (rw + (size_t) MAXR * topk * 2 + 255) / 256 * 256;
-        ctl = flags + 256; total = ctl + 256;
-    }
-};
+constexpr int DISPATCH_THREADS = 1024;
 
-__global__ void __launch_bounds__(256) ep_dispatch_kernel(const StageArgs a, const uint4* __restrict__ x_own, const int64_t* __restrict__ sel_own,
+__global__ void __launch_bounds__(DISPATCH_THREADS) ep_dispatch_kernel(const StageArgs a, const uint4* __restrict__ x_own, const int64_t* __restrict__ sel_own,
                                                           const uint16_t* __restrict__ rw_own, int R, int H, int topk, unsigned* __restrict__ status)
 {
     const StageLayout L(H, topk);
@@ -118,10 +114,19 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const StageArgs a, con
     const unsigned g = *(volatile unsigned*) ctl + 1u;            // advanced only after every block of this launch has read it
     const int n_own = R > a.rank ? (R - a.rank + a.world - 1) / a.world : 0;
     const int words = H / 8;                                       // 16-byte words per row
-    for (int i = tid; i < n_own * words; i += blockDim.x)
+    // all of a thread's loads are issued before its first store: the copy costs one load latency, not one per word
+    constexpr int U = 8;
+    for (int base = tid; base < n_own * words; base += DISPATCH_THREADS * U)
     {
-        const int j = i / words, c = i - j * words;
-        ((uint4*) (dst + L.x))[(size_t) (a.rank + j * a.world) * words + c] = x_own[(size_t) j * words + c];
+        uint4 v[U];
+        #pragma unroll
+        for (int u = 0; u < U; ++u) { const int i = base + u * DISPATCH_THREADS; if (i < n_own * words) v[u] = x_own[i]; }
+        #pragma unroll
+        for (int u = 0; u < U; ++u)
+        {
+            const int i = base + u * DISPATCH_THREADS;
+            if (i < n_own * words) { const int j = i / words, c = i - j * words; ((uint4*) (dst + L.x))[(size_t) (a.rank + j * a.world) * words + c] = v[u]; }
+        }
     }
     for (int i = tid; i < n_own * topk; i += blockDim.x)
     {
@@ -183,7 +188,7 @@ int ep_dispatch_launch(int rank, int world, void* const* stage, const void* x_ow
     StageArgs a;
     a.rank = rank; a.world = world;
     for (int p = 0; p < 8; ++p) a.stage[p] = p < world ? (char*) stage[p] : nullptr;
-    ep_dispatch_kernel<<<world, 256, 0, st>>>(a, (const uint4*) x_own, sel_own, (const uint16_t*) rw_own, R, H, topk, status);
+    ep_dispatch_kernel<<<world, DISPATCH_THREADS, 0, st>>>(a, (const uint4*) x_own, sel_own, (const uint16_t*) rw_own, R, H, topk, status);
     count_launches(1);
     const cudaError_t err = cudaGetLastError();
     return err == cudaSuccess ? HMOE_OK : fail(HMOE_E_CUDA, cudaGetErrorString(err));

@@ -46,10 +46,13 @@ int decode_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t
                   int act_quant, float* y, void* ws, size_t ws_bytes, cudaStream_t st, int sh_mod = 1, int sh_rem = 0,
                   unsigned* gen_ptr = nullptr, size_t slot_stride = 0, bool prepared = false, const struct EpCombineArgs* epc = nullptr);
 struct PrepArgs;
+struct DispArgs;
 int decode_prep_args(const hmoe_layer* L, const void* x, int x_dtype, int R, int lo, int n_local, int act_quant, void* ws, size_t ws_bytes,
                      int sh_mod, int sh_rem, unsigned* gen_ptr, PrepArgs* pa);
 int router_prepare_launch(const void* x, int x_dtype, const void* wt, int w_dtype, const float* bias, int R, int H, int E, int topk, float scale,
-                          int64_t* sel, void* rw, void* ws, size_t ws_bytes, const PrepArgs& pa, cudaStream_t st);
+                          int64_t* sel, void* rw, void* ws, size_t ws_bytes, const PrepArgs& pa, cudaStream_t st, const DispArgs* da = nullptr);
+int ep_combine_launch(int rank, int world, void* const* slots, void* const* flags, const unsigned* gen, float* f, int rows, int H, size_t slot_floats,
+                      unsigned* status, cudaStream_t st, int own_rows);
 
 int shared_i8_launch(const hmoe_layer* L, int R, int sh_mod, int sh_rem, const __half* xf, float* gs, float* y, const unsigned* gen_ptr,
                      size_t slot_stride, int sms, cudaStream_t st);

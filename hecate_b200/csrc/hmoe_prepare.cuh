@@ -8,6 +8,8 @@ namespace hmoe {
 
 // Row r of x rewritten as fp16 in the column order the MMAs read (in the int8 mode: the CPU engine's int8 codes as fp16 integers
 // plus a scale per 32 columns), and the row's share of the per-pick gate / up sums cleared. Called by `nthreads` threads of a block.
+// FRESH: the row arrived from another GPU during this launch (read it past L1).
+template <bool FRESH = false>
 __device__ __forceinline__ void prepare_row(const void* __restrict__ x, int x_kind /* 0 fp16, 1 bf16, 2 fp16 in MMA column order */, int r, int H,
                                             int act_quant, __half* __restrict__ xf, float* __restrict__ xscale, float4* __restrict__ gzero,
                                             int gzero_n, int tid, int nthreads)
@@ -36,7 +38,7 @@ __device__ __forceinline__ void prepare_row(const void* __restrict__ x, int x_ki
             #pragma unroll
             for (int j = 0; j < 4; ++j)
             {
-                const uint4 u = p[j];
+                const uint4 u = FRESH ? __ldcg(p + j) : p[j];
                 const uint32_t w[4] = {u.x, u.y, u.z, u.w};
                 #pragma unroll
                 for (int k = 0; k < 4; ++k)
@@ -81,6 +83,16 @@ struct PrepArgs
     unsigned* gen_bump;
     int I, nblocks;
     unsigned* status;          // the decode workspace's status word
+};
+
+// Expert parallelism with data-parallel tokens: what the router's launch needs to do the dispatch itself (push this rank's rows
+// into every rank's staging area, wait for the rows of its row group). stage[p] = rank p's staging area as seen from here.
+struct DispArgs
+{
+    int rank, world, n_own, words;      // rows this rank owns (rank, rank + world, ...), 16-byte words per row
+    char* stage[8];
+    const uint4* x_own;                 // [n_own][H] 2-byte elements
+    size_t x_off, flags_off, ctl_off;   // StageLayout offsets
 };
 
 // Shared memory of build_route (17 KB).

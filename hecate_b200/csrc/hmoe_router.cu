@@ -115,12 +115,17 @@ struct NormArgs
 // no separate prepare kernel sits between the router and the expert kernels: one more block per row group (blockIdx.x ==
 // gridDim.x - 1) rewrites the group's rows for the MMAs while the other blocks compute logits, and the block that completes the
 // last row group's selection builds the Route from the selections of all rows.
-template <bool XBF, bool WBF, bool FUSED, bool NORM, bool PREP = false>
+// DISP (with PREP): expert parallelism with data-parallel tokens. The launch is also the dispatch: blocks (p, 0) for p < world first
+// store this rank's rows into rank p's staging area and raise this rank's flag there (release, system scope); every block then
+// waits, bounded, for the flags of the ranks that own its four rows before it reads them from the local staging area. So the
+// exchange costs one NVLink round trip at the head of the router instead of a kernel of its own, and every rank routes all rows
+// (the router is latency-bound: four rows or sixteen cost the same).
+template <bool XBF, bool WBF, bool FUSED, bool NORM, bool PREP = false, bool DISP = false>
 __global__ void __launch_bounds__(RW * 32) router_logits_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ wt,
                                                                 int R, int H, int E, float* __restrict__ logits,
                                                                 const float* __restrict__ bias, int topk, float scale,
                                                                 int64_t* __restrict__ sel, __half* __restrict__ rw, int slot, const NormArgs na,
-                                                                unsigned* __restrict__ status, const PrepArgs pa)
+                                                                unsigned* __restrict__ status, const PrepArgs pa, const DispArgs da)
 {
     extern __shared__ __align__(128) unsigned char rsm[];
     __shared__ int s_last;
@@ -131,12 +136,53 @@ __global__ void __launch_bounds__(RW * 32) router_logits_kernel(const uint16_t* 
     if (PREP)
     {
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");    // the expert kernels' blocks may set up while this one runs
-        if ((int) blockIdx.x == nrouter)
+    }
+    unsigned dgen = 0;                                   // DISP: this step's dispatch generation
+    bool rows_ok = true;
+    if (DISP)
+    {
+        __shared__ int s_rows_ok;
+        unsigned* ctl = (unsigned*) (da.stage[da.rank] + da.ctl_off);      // [0] generation of the last step, [1] blocks of this launch that have read it
+        dgen = *(volatile unsigned*) ctl + 1u;
+        if (threadIdx.x == 0) s_rows_ok = 1;
+        __syncthreads();
+        if (threadIdx.x == 0) atomicAdd(ctl + 1, 1u);
+        if (blockIdx.y == 0 && (int) blockIdx.x < da.world)
         {
-            for (int r = blockIdx.y * RR; r < R && r < (int) (blockIdx.y + 1) * RR; ++r)
-                prepare_row(pa.x, pa.x_kind, r, H, pa.act_quant, pa.xf, pa.xscale, pa.gzero, pa.gzero_n, threadIdx.x, RW * 32);
-            return;
+            char* dst = da.stage[blockIdx.x];
+            const int total = da.n_own * da.words;
+            constexpr int U = 8;                            // all of a thread's loads are issued before its first store
+            for (int base = threadIdx.x; base < total; base += RW * 32 * U)
+            {
+                uint4 v[U];
+                #pragma unroll
+                for (int u = 0; u < U; ++u) { const int i = base + u * RW * 32; if (i < total) v[u] = da.x_own[i]; }
+                #pragma unroll
+                for (int u = 0; u < U; ++u)
+                {
+                    const int i = base + u * RW * 32;
+                    if (i < total) { const int j = i / da.words, c = i - j * da.words; ((uint4*) (dst + da.x_off))[(size_t) (da.rank + j * da.world) * da.words + c] = v[u]; }
+                }
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) { __threadfence_system(); sys_st_release((unsigned*) (dst + da.flags_off) + da.rank, dgen); }
         }
+        if ((int) threadIdx.x < RR && (int) (blockIdx.y * RR + threadIdx.x) < R)
+        {
+            const unsigned* fl = (const unsigned*) (da.stage[da.rank] + da.flags_off) + (blockIdx.y * RR + threadIdx.x) % da.world;
+            const unsigned long long t0 = globaltimer_ns();
+            while ((int) (sys_ld_acquire(fl) - dgen) < 0)
+                if (globaltimer_ns() - t0 > 2000000000ull) { atomicOr(pa.status, ST_WAIT_TIMEOUT); s_rows_ok = 0; break; }
+        }
+        __syncthreads();
+        rows_ok = s_rows_ok != 0;
+    }
+    if (PREP && (int) blockIdx.x == nrouter)
+    {
+        if (rows_ok)
+            for (int r = blockIdx.y * RR; r < R && r < (int) (blockIdx.y + 1) * RR; ++r)
+                prepare_row<DISP>(pa.x, pa.x_kind, r, H, pa.act_quant, pa.xf, pa.xscale, pa.gzero, pa.gzero_n, threadIdx.x, RW * 32);
+        return;
     }
     const int hc = H < HC ? H : HC;                              // chunk length, a multiple of 256
     float* xs = (float*) rsm;                                    // [RR][hc] fp32, see above
@@ -226,7 +272,8 @@ __global__ void __launch_bounds__(RW * 32) router_logits_kernel(const uint16_t* 
             for (int u = 0; u < 6; ++u)
             {
                 const int i = i0 + u * RW * 32 * 8, r = i / cl, c = i - r * cl;
-                v[u] = (i < RR * cl && r < nr) ? *(const uint4*) (x + (size_t) (r0 + r) * H + c0 + c) : make_uint4(0, 0, 0, 0);
+                v[u] = (i < RR * cl && r < nr) ? (DISP ? __ldcg((const uint4*) (x + (size_t) (r0 + r) * H + c0 + c)) : *(const uint4*) (x + (size_t) (r0 + r) * H + c0 + c))
+                                               : make_uint4(0, 0, 0, 0);
             }
             #pragma unroll
             for (int u = 0; u < 6; ++u)
@@ -245,7 +292,7 @@ __global__ void __launch_bounds__(RW * 32) router_logits_kernel(const uint16_t* 
         __syncthreads();
         // A wait that gives up raises the status bit; the block skips the sums but still takes part in the arrival count
         // below, so the call's counter slot returns to zero and later calls that reuse it are not affected.
-        const bool got = mbar_wait(bar, par, &s_abort, status);
+        const bool got = mbar_wait(bar, par, &s_abort, status) && rows_ok;
         if (FUSED && !got && lane == 0) atomicOr(&g_router_bad[slot][blockIdx.y], 1u);
         #pragma unroll 2
         for (int k = 0; got && k < cl; k += 256)
@@ -314,8 +361,19 @@ __global__ void __launch_bounds__(RW * 32) router_logits_kernel(const uint16_t* 
         // nothing) and tell the host through the decode workspace's status word.
         if (threadIdx.x == 0) { g_router_anybad[slot] = 0u; atomicOr(pa.status, ST_WAIT_TIMEOUT); pa.route->m = 0; pa.route->ntiles = 0; }
         for (int i = threadIdx.x; i < 2 * (MAXB + 1); i += RW * 32) pa.route->split[i / (MAXB + 1)][i % (MAXB + 1)] = 0;
-        return;
     }
+    if (DISP && threadIdx.x == 0)
+    {
+        // this block is the last to work: once every block of the launch has read the generation, advance it (bounded wait)
+        unsigned* ctl = (unsigned*) (da.stage[da.rank] + da.ctl_off);
+        const unsigned nblk = gridDim.x * gridDim.y;
+        const unsigned long long t0 = globaltimer_ns();
+        while (*(volatile unsigned*) (ctl + 1) < nblk)
+            if (globaltimer_ns() - t0 > 1000000000ull) { atomicOr(pa.status, ST_WAIT_TIMEOUT); break; }
+        ctl[1] = 0u;
+        *(volatile unsigned*) ctl = dgen;
+    }
+    if (anybad) return;
     build_route<true>(*(RouteSmem*) (rsm + RW * 512 * 4), sel, rw, R, H, pa.I, topk, pa.lo, pa.n_local, pa.has_shared, pa.sh_mod, pa.sh_rem,
                       pa.gen_bump, pa.route, pa.nblocks, threadIdx.x);
 }
@@ -339,8 +397,8 @@ void launch_logits(dim3 grid, size_t smem, cudaStream_t st, bool fused, const ui
         cudaFuncSetAttribute(router_logits_kernel<XBF, WBF, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     }
     const NormArgs na = {};
-    if (fused) router_logits_kernel<XBF, WBF, true, false><<<grid, RW * 32, smem, st>>>(x, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot, na, status, PrepArgs());
-    else router_logits_kernel<XBF, WBF, false, false><<<grid, RW * 32, smem, st>>>(x, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot, na, status, PrepArgs());
+    if (fused) router_logits_kernel<XBF, WBF, true, false><<<grid, RW * 32, smem, st>>>(x, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot, na, status, PrepArgs(), DispArgs());
+    else router_logits_kernel<XBF, WBF, false, false><<<grid, RW * 32, smem, st>>>(x, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot, na, status, PrepArgs(), DispArgs());
 }
 
 template <bool WBF>
@@ -353,8 +411,8 @@ void launch_norm_router(dim3 grid, size_t smem, cudaStream_t st, bool fused, con
         cudaFuncSetAttribute(router_logits_kernel<false, WBF, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         cudaFuncSetAttribute(router_logits_kernel<false, WBF, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     }
-    if (fused) router_logits_kernel<false, WBF, true, true><<<grid, RW * 32, smem, st>>>(nullptr, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot, na, status, PrepArgs());
-    else router_logits_kernel<false, WBF, false, true><<<grid, RW * 32, smem, st>>>(nullptr, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot, na, status, PrepArgs());
+    if (fused) router_logits_kernel<false, WBF, true, true><<<grid, RW * 32, smem, st>>>(nullptr, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot, na, status, PrepArgs(), DispArgs());
+    else router_logits_kernel<false, WBF, false, true><<<grid, RW * 32, smem, st>>>(nullptr, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot, na, status, PrepArgs(), DispArgs());
 }
 
 // Both entry points share the counter sets, so they also share the rotation that hands them out.
@@ -362,12 +420,18 @@ std::atomic<unsigned> g_router_calls{0};
 
 template <bool XBF, bool WBF>
 void launch_logits_prep(dim3 grid, size_t smem, cudaStream_t st, const uint16_t* x, const uint16_t* wt, int R, int H, int E, float* logits,
-                        const float* bias, int topk, float scale, int64_t* sel, __half* rw, int slot, unsigned* status, const PrepArgs& pa)
+                        const float* bias, int topk, float scale, int64_t* sel, __half* rw, int slot, unsigned* status, const PrepArgs& pa,
+                        const DispArgs* da)
 {
     static DeviceOnce once;
-    if (once.first()) cudaFuncSetAttribute(router_logits_kernel<XBF, WBF, true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (once.first())
+    {
+        cudaFuncSetAttribute(router_logits_kernel<XBF, WBF, true, false, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(router_logits_kernel<XBF, WBF, true, false, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    }
     const NormArgs na = {};
-    router_logits_kernel<XBF, WBF, true, false, true><<<grid, RW * 32, smem, st>>>(x, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot, na, status, pa);
+    if (da) router_logits_kernel<XBF, WBF, true, false, true, true><<<grid, RW * 32, smem, st>>>(x, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot, na, status, pa, *da);
+    else router_logits_kernel<XBF, WBF, true, false, true, false><<<grid, RW * 32, smem, st>>>(x, wt, R, H, E, logits, bias, topk, scale, sel, rw, slot, na, status, pa, DispArgs());
 }
 
 }  // namespace
@@ -408,7 +472,7 @@ int router_launch(const void* x, int x_dtype, const void* wt, int w_dtype, const
 
 // The router with the decode call's set-up step inside its launch: `pa` comes from decode_prep_args.
 int router_prepare_launch(const void* x, int x_dtype, const void* wt, int w_dtype, const float* bias, int R, int H, int E, int topk, float scale,
-                          int64_t* sel, void* rw, void* ws, size_t ws_bytes, const PrepArgs& pa, cudaStream_t st)
+                          int64_t* sel, void* rw, void* ws, size_t ws_bytes, const PrepArgs& pa, cudaStream_t st, const DispArgs* da)
 {
     if (R < 1 || R > MAXR || E < 32 || E > 256 || E % 32 || H % 256 || H < 256 || topk < 1 || topk > TOPK_MAX || topk > E)
         return fail(HMOE_E_ARG, "hmoe_router_decode: needs 1 <= R <= 16, E % 32 == 0, E <= 256, H % 256 == 0, topk <= 8");
@@ -426,10 +490,10 @@ int router_prepare_launch(const void* x, int x_dtype, const void* wt, int w_dtyp
     const uint16_t* xp = (const uint16_t*) x; const uint16_t* wp = (const uint16_t*) wt;
     const int slot = (int) (g_router_calls.fetch_add(1, std::memory_order_relaxed) % CTR_SLOTS);
     const bool xb = x_dtype == HMOE_BF16, wb = w_dtype == HMOE_BF16;
-    if (!xb && !wb) launch_logits_prep<false, false>(grid, smem, st, xp, wp, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot, status, pa);
-    else if (!xb && wb) launch_logits_prep<false, true>(grid, smem, st, xp, wp, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot, status, pa);
-    else if (xb && !wb) launch_logits_prep<true, false>(grid, smem, st, xp, wp, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot, status, pa);
-    else launch_logits_prep<true, true>(grid, smem, st, xp, wp, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot, status, pa);
+    if (!xb && !wb) launch_logits_prep<false, false>(grid, smem, st, xp, wp, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot, status, pa, da);
+    else if (!xb && wb) launch_logits_prep<false, true>(grid, smem, st, xp, wp, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot, status, pa, da);
+    else if (xb && !wb) launch_logits_prep<true, false>(grid, smem, st, xp, wp, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot, status, pa, da);
+    else launch_logits_prep<true, true>(grid, smem, st, xp, wp, R, H, E, logits, bias, topk, scale, sel, (__half*) rw, slot, status, pa, da);
     count_launches(1);
     const cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) return fail(HMOE_E_CUDA, cudaGetErrorString(err));

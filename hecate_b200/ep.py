@@ -73,10 +73,11 @@ class PeerBuffers:
 class EpDecoder:
     """One rank's side of an expert-parallel decode layer."""
 
-    def __init__(self, rank, world, tables, n_experts, device, dist, use_peer=True, fused_tail=True):
+    def __init__(self, rank, world, tables, n_experts, device, dist, use_peer=True, fused_tail=False):
         self.rank, self.world, self.tabs, self.dev, self.dist = rank, world, tables, device, dist
         # fused_tail: the combine runs as the tail of the down launch (hmoe_decode_ep_combine) instead of as a kernel of its own;
-        # it needs the register-resident decode kernels (H <= 6144, I <= 2048)
+        # it needs the register-resident decode kernels (H <= 6144, I <= 2048). Measured at 2 GPUs it is 2-3 us slower than the
+        # separate kernel (148 blocks poll the flags instead of one thread), so it is off by default.
         self.fused_tail = fused_tail and tables.H <= 6144 and tables.I <= 2048
         self.plan = shard_plan(rank, world, n_experts)
         assert tables.n == self.plan["n_local"]
@@ -150,9 +151,30 @@ class EpDecoder:
                                         C.c_int(H), C.c_size_t(pb.slot_floats), vp(pb.status), st))
         return f_own
 
-    def dispatch_bytes(self, R, itemsize=2):
-        """Bytes this rank sends to other ranks per step in step_dp (rows, selections, weights)."""
-        return (self.world - 1) * len(self.own_rows(R)) * (self.tabs.H * itemsize + self.tabs.topk * 10)
+    def step_dp_fused(self, x_own, wt, bias, scale, sel, rw, f_own, R, tables=None):
+        """Data-parallel tokens in four launches (hmoe_decode_ep_dp): the router's launch is also the dispatch of the rows and the
+        expert kernels' set-up; every rank routes all R rows (sel, rw [R][topk] are outputs). x_own [n][H]: this rank's rows;
+        f_own [n][H] (fp32) += their layer output."""
+        import torch
+        if not self.use_peer:
+            raise RuntimeError("step_dp_fused needs the peer-memory buffers")
+        st = C.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)
+        pl, pb = self.plan, self.peer
+        struct = self.struct if tables is None else tables.struct()
+        E = wt.shape[0]
+        need = lib().hmoe_router_ws_bytes(C.c_int(R), C.c_int(E))
+        if getattr(self, "_rws", None) is None or self._rws.numel() < need:
+            self._rws = torch.zeros(max(need, 1 << 16), dtype=torch.uint8, device=self.dev)
+        check(lib().hmoe_decode_ep_dp(C.byref(struct), vp(x_own), C.c_int(moe._dt(x_own)), vp(wt), C.c_int(moe._dt(wt)), vp(bias), C.c_int(R),
+                                      C.c_int(E), C.c_float(float(scale)), vp(sel), vp(rw), vp(self._rws), C.c_size_t(self._rws.numel()),
+                                      C.c_int(pl["lo"]), C.c_int(pl["n_local"]), C.c_int(0), vp(self.ws), C.c_size_t(self.ws.numel()),
+                                      C.c_int(self.rank), C.c_int(self.world), pb.stage, pb.slots, pb.flags, C.c_void_p(pb.gen_ptr),
+                                      C.c_size_t(pb.slot_floats), vp(f_own), vp(pb.status), C.c_int(int(self.fused_tail)), st))
+        return f_own
+
+    def dispatch_bytes(self, R, itemsize=2, with_routing=True):
+        """Bytes this rank sends to other ranks per step: its rows and (step_dp) their selections and weights."""
+        return (self.world - 1) * len(self.own_rows(R)) * (self.tabs.H * itemsize + (self.tabs.topk * 10 if with_routing else 0))
 
     def status(self):
         import torch

@@ -131,6 +131,17 @@ int hmoe_ep_combine(int rank, int world, void* const* slots, void* const* flags,
 int hmoe_decode_ep_combine(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
                            int act_quant, void* ws, size_t ws_bytes, int shared_mod, int shared_rem, uint32_t* gen, size_t slot_floats, int rank,
                            int world, void* const* slots, void* const* flags, float* f, int own_rows, uint32_t* status, void* stream);
+/* One expert-parallel decode layer call with data-parallel tokens, end to end, in four launches: dispatch + router + set-up (one
+ * kernel: blocks (p, 0) store this rank's rows x_own [n][H] into rank p's staging area and raise the flag there; every block waits,
+ * bounded, for the owners of the rows it needs; every rank then routes all R rows, which costs what routing its own would, and
+ * builds its work list), gate_up, down, and the combine of the rank's own rows (fused_tail != 0: inside the down launch).
+ * sel int64 [R][topk] and rw fp16 [R][topk] receive the routing of all rows; f_own [n][H] += the layer output of this rank's rows
+ * (rows rank, rank + world, ...). Buffers as in hmoe_ep_dispatch / hmoe_decode_ep / hmoe_ep_combine_own, with which it can be mixed
+ * step by step. A wait that gives up sets bit 0 of the decode workspace's status word or of *status. */
+int hmoe_decode_ep_dp(const hmoe_layer* layer, const void* x_own, int x_dtype, const void* wt, int w_dtype, const float* bias, int R, int E,
+                      float scale, int64_t* sel, void* rw, void* router_ws, size_t router_ws_bytes, int lo, int n_local, int act_quant, void* ws,
+                      size_t ws_bytes, int rank, int world, void* const* stage, void* const* slots, void* const* flags, uint32_t* gen,
+                      size_t slot_floats, float* f_own, uint32_t* status, int fused_tail, void* stream);
 size_t hmoe_ep_stage_bytes(int H, int topk);
 int hmoe_ep_stage_offsets(int H, int topk, size_t* x_off, size_t* sel_off, size_t* rw_off);
 int hmoe_ep_dispatch(int rank, int world, void* const* stage, const void* x_own, const int64_t* sel_own, const void* rw_own, int R, int H, int topk,

@@ -88,6 +88,25 @@ def _rank_main(rank, world, port, out_path):
         dp = torch.stack(outs)
         dist.barrier(); dec.peer.close()
         dp_err = torch.maximum(dp_err, torch.tensor([float((dp - res[True][:, own]).abs().max() / res[True].abs().max())], device=dev))
+    # the same in four launches: the router's launch is the dispatch and the set-up (every rank routes all rows itself)
+    wt = torch.from_numpy(synth.router_weight(7, 0, 32, H)).to(dev).to(torch.float16)
+    for fused in (False, True):
+        dec = EpDecoder(rank, world, local, E, dev, dist, use_peer=True, fused_tail=fused)
+        own = dec.own_rows(R)
+        for stepi in range(3):
+            xs = torch.from_numpy(synth.activations(30 + stepi, 0, R, H)).to(dev).half()
+            sel_f = torch.empty(R, 8, dtype=torch.int64, device=dev); rw_f = torch.empty(R, 8, dtype=torch.float16, device=dev)
+            f_own = torch.zeros(len(own), H, device=dev)
+            dec.step_dp_fused(xs[own].contiguous(), wt, None, 1.0, sel_f, rw_f, f_own, R)      # 32 router rows, 16 experts: ids >= 16 are foreign to every rank
+            # reference: the separate router on all rows, then the replicated-rows step
+            sel_r = torch.empty(R, 8, dtype=torch.int64, device=dev); rw_r = torch.empty(R, 8, dtype=torch.float16, device=dev)
+            moe.router_fused(xs, wt, None, None, None, sel_r, rw_r, 8, 1.0)
+            f_all = torch.zeros(R, H, device=dev)
+            dec.step(xs, sel_r, rw_r, f_all)
+            assert torch.equal(sel_f, sel_r) and torch.equal(rw_f.view(torch.int16), rw_r.view(torch.int16))
+            dp_err = torch.maximum(dp_err, torch.tensor([float((f_own - f_all[own]).abs().max() / f_all.abs().max())], device=dev))
+        assert dec.status() == 0
+        dist.barrier(); dec.peer.close()
     dist.all_reduce(dp_err, op=dist.ReduceOp.MAX)
     sep_err = torch.tensor([float((res["separate"] - res[True]).abs().max() / res[True].abs().max())], device=dev)
     dist.all_reduce(sep_err, op=dist.ReduceOp.MAX)
