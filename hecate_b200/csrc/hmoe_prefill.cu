@@ -18,7 +18,8 @@
 //              array zero-filled);
 //   warp 17    one thread issues tcgen05.mma (M 128, N = picks rounded up to 16, K 16) four times per matrix and commits the
 //              stage back to the producers;
-//   warps 18-21 read the finished sums out of tensor memory (one quarter of the lanes = 32 channels each).
+//   warps 18-21 (down) / 18-25 (gate_up) read the finished sums out of tensor memory (one quarter of the lanes = 32 channels each;
+//              gate_up: two warps per quarter, half the columns each).
 // gate_up keeps two accumulators (gate, up: 2 x 256 columns) over the same input tile and its read-out writes
 // act = SiLU(g) * u * routing weight in fp16; down adds scale * sum into out[token] with coalesced fp32 reductions and keeps two
 // accumulator sets, so a tile's read-out runs under the next tile's MMAs. (Measured on the benchmark with parts of the kernel
@@ -36,8 +37,10 @@ namespace {
 
 constexpr int TM = 128, TN = 256, TK = 64;
 constexpr int NDQ = 16;                         // dequantising warps
-constexpr int NEPI = 4;                         // read-out warps, one per quarter of the tensor-memory lanes
-constexpr int PF_THREADS = (NDQ + 2 + NEPI) * 32;      // warp NDQ: TMA, warp NDQ + 1: MMA, warps NDQ + 2 ..: read-out
+// read-out warps: one per quarter of the tensor-memory lanes in down (whose read-out runs under the next tile's MMAs), two per
+// quarter in gate_up (whose single accumulator set keeps the tensor core waiting until the read-out is done: half the columns each)
+__host__ __device__ constexpr int nepi(int nmat) { return nmat == 2 ? 8 : 4; }
+__host__ __device__ constexpr int pf_threads(int nmat) { return (NDQ + 2 + nepi(nmat)) * 32; }      // warp NDQ: TMA, warp NDQ + 1: MMA, warps NDQ + 2 ..: read-out
 constexpr int CHUNK = 1024;                     // picks per permutation block (one warp)
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -331,7 +334,7 @@ struct PfSmem
 
 // NMAT = 2: gate and up over one input tile, SiLU epilogue. NMAT = 1: down, scatter-add epilogue.
 template <int NMAT>
-__global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap, const GemmArgs a)
+__global__ void __launch_bounds__(pf_threads(NMAT), 1) prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap, const GemmArgs a)
 {
     using L = PfSmem<NMAT>;
     extern __shared__ unsigned char smem_raw[];
@@ -350,7 +353,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
     if (threadIdx.x == 0)
     {
         for (int i = 0; i < L::STAGES; ++i) { mbar_init(full_a + i * 8, NMAT == 2 ? NDQ : NDQ / 2); mbar_init(full_b + i * 8, 1); mbar_init(empty + i * 8, 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(done + i * 8, 1); mbar_init(tmem_free + i * 8, NEPI); }
+        for (int i = 0; i < 2; ++i) { mbar_init(done + i * 8, 1); mbar_init(tmem_free + i * 8, nepi(NMAT)); }
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -488,7 +491,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
         // * up * routing weight -> fp16 activations; down: out[token] += scale * sum, one fp32 reduction per element (32 lanes =
         // 32 consecutive channels = 128 contiguous bytes). Because these warps do nothing else, the read-out of a tile overlaps
         // the dequantisation and (down: second accumulator set) the MMAs of the next one.
-        const int lq = warp & 3;
+        const int lq = warp & 3, chalf = (warp - (NDQ + 2)) >> 2;        // lane quarter; gate_up: which half of the columns
         uint32_t tile_n = 0;
         bool ok = true;
         for (int item = blockIdx.x; item < nitems && ok; item += gridDim.x, ++tile_n)
@@ -496,6 +499,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
             if (*abort_flag) break;
             const int rb = item / NCT, ct = item % NCT;
             const int e = a.rbt[4 * rb], pos0 = a.rbt[4 * rb + 1], n = a.rbt[4 * rb + 2];
+            (void) chalf;
             const uint32_t acc = (uint32_t) (tile_n % NACC);
             if (!mbar_wait(done + acc * 8, (tile_n / NACC) & 1, abort_flag, a.status)) break;
             tc_fence_after();
@@ -510,7 +514,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(const __gri
                 sc0 = __ldg((const float*) s0p + ch);
                 if (NMAT == 2) { const void* s1p = e < a.n_local ? (const void*) a.s1[e] : a.sh_s1; sc1 = __ldg((const float*) s1p + ch); }
             }
-            for (int c0 = 0; c0 < (int) n16; c0 += 16)
+            const int csplit = NMAT == 2 ? (((int) n16 + 31) >> 5) << 4 : (int) n16;      // gate_up: columns [0, csplit) and [csplit, n16)
+            for (int c0 = chalf ? csplit : 0; c0 < (chalf ? (int) n16 : csplit); c0 += 16)
             {
                 uint32_t r0[16], r1[16];
                 tmem_ld16(tacc + c0, r0);
@@ -717,10 +722,10 @@ int prefill_sorted_launch(const hmoe_layer* L, const void* x, int x_dtype, const
     for (int p = 0; p < 8; ++p) g.out_peer[p] = nullptr;
     g.K = H; g.N = I; g.w0 = L->gate_w; g.w1 = L->up_w; g.s0 = L->gate_s; g.s1 = L->up_s;
     g.sh_w0 = L->sh_gate_w; g.sh_w1 = L->sh_up_w; g.sh_s0 = L->sh_gate_s; g.sh_s1 = L->sh_up_s;
-    prefill_gemm_kernel<2><<<sms, PF_THREADS, PfSmem<2>::total, st>>>(mx, g);
+    prefill_gemm_kernel<2><<<sms, pf_threads(2), PfSmem<2>::total, st>>>(mx, g);
     g.K = I; g.N = H; g.w0 = L->down_w; g.w1 = nullptr; g.s0 = L->down_s; g.s1 = nullptr;
     g.sh_w0 = L->sh_down_w; g.sh_w1 = nullptr; g.sh_s0 = L->sh_down_s; g.sh_s1 = nullptr;
-    prefill_gemm_kernel<1><<<sms, PF_THREADS, PfSmem<1>::total, st>>>(ma, g);
+    prefill_gemm_kernel<1><<<sms, pf_threads(1), PfSmem<1>::total, st>>>(ma, g);
     count_launches(4);
     const cudaError_t err = cudaGetLastError();
     return err == cudaSuccess ? HMOE_OK : fail(HMOE_E_CUDA, cudaGetErrorString(err));
@@ -793,10 +798,10 @@ int prefill_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_
     for (int p = 0; p < 8; ++p) g.out_peer[p] = (out_peer && p < world) ? (float*) out_peer[p] : nullptr;
     g.K = H; g.N = I; g.w0 = L->gate_w; g.w1 = L->up_w; g.s0 = L->gate_s; g.s1 = L->up_s;
     g.sh_w0 = L->sh_gate_w; g.sh_w1 = L->sh_up_w; g.sh_s0 = L->sh_gate_s; g.sh_s1 = L->sh_up_s;
-    prefill_gemm_kernel<2><<<sms, PF_THREADS, PfSmem<2>::total, st>>>(mx, g);
+    prefill_gemm_kernel<2><<<sms, pf_threads(2), PfSmem<2>::total, st>>>(mx, g);
     g.K = I; g.N = H; g.w0 = L->down_w; g.w1 = nullptr; g.s0 = L->down_s; g.s1 = nullptr;
     g.sh_w0 = L->sh_down_w; g.sh_w1 = nullptr; g.sh_s0 = L->sh_down_s; g.sh_s1 = nullptr;
-    prefill_gemm_kernel<1><<<sms, PF_THREADS, PfSmem<1>::total, st>>>(ma, g);
+    prefill_gemm_kernel<1><<<sms, pf_threads(1), PfSmem<1>::total, st>>>(ma, g);
     count_launches(3);
     const cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) return fail(HMOE_E_CUDA, cudaGetErrorString(err));
