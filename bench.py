@@ -268,10 +268,14 @@ def make_graphed(step, xs, torch, moe, use_graph):
     return (lambda b: graphs[b].replay()), per_step
 
 
-def timed(torch, run, steps, nb):
-    """ms per step over `steps` calls of run(i % nb), CUDA events on the current stream, synchronised on both sides."""
+def timed(torch, run, steps, nb, lead=0):
+    """ms per step over `steps` calls of run(i % nb), CUDA events on the current stream, synchronised on both sides. lead: that
+    many further warm-up steps are queued directly in front of the start event (multi-GPU arms: the ranks leave the host-side
+    barrier tens of microseconds apart, and without them the first timed step would measure that skew, not the step)."""
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
+    for i in range(lead):
+        run((nb - lead + i) % nb)
     ev0.record()
     for i in range(steps):
         run(i % nb)
@@ -665,7 +669,7 @@ def stack_arm(args, world, rank, dev, L, torch, dist, ep, moe, synth):
     torch.cuda.synchronize(); dist.barrier()
     with ClockSampler(dev.index) as cs:
         dist.barrier()
-        t = timed(torch, run_step, steps, NB)
+        t = timed(torch, run_step, steps, NB, lead=1)
         dist.barrier()
     ms = torch.tensor([t], device=dev)
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
@@ -738,11 +742,29 @@ def ep_decode_arm(args, world, rank, dev, tabs, pl, torch, dist, ep, moe, synth)
         torch.cuda.synchronize(); dist.barrier()
         with ClockSampler(dev.index) as cs:
             dist.barrier()
-            t = timed(torch, run_step, steps, NBATCH)
+            t = timed(torch, run_step, steps, NBATCH, lead=3)
             dist.barrier()
         ms = torch.tensor([t], device=dev)
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         launches = per_step * steps
+        if mode == "peer":
+            # for comparison: the same buffers with the rows already replicated on every rank (no dispatch; e.g. behind a
+            # tensor-parallel attention), combine of all rows over peer memory
+            def step_rep(x):
+                moe.router_fused(x, wt, bias, None, None, sel, rw, TOPK, 1.0)
+                dec.step(x, sel, rw, f)
+            for i in range(3):
+                step_rep(xs[i])
+            torch.cuda.synchronize(); dist.barrier()
+            run_rep, _ = make_graphed(step_rep, xs, torch, moe, graph)
+            for i in range(3):
+                run_rep(i)
+            torch.cuda.synchronize(); dist.barrier()
+            t_rep = torch.tensor([timed(torch, run_rep, steps, NBATCH, lead=3)], device=dev)
+            dist.all_reduce(t_rep, op=dist.ReduceOp.MAX)
+            rep_us = float(t_rep.item()) * 1e3
+            del run_rep
+            dist.barrier()
 
         def e2e_step(b):
             x_dev.copy_(hosts[b], non_blocking=True); step(x_dev); f_host[:out_dev.shape[0]].copy_(out_dev, non_blocking=True)
@@ -782,6 +804,7 @@ def ep_decode_arm(args, world, rank, dev, tabs, pl, torch, dist, ep, moe, synth)
                                           "dispatch and combine as an all-to-all over NVLink peer memory",
                    "l2": "inputs larger than L2: 8 input batches in a ring, each step streams different experts"},
         "us_per_layer": r["ms"] * 1e3, "nccl_allreduce_us_per_layer": results["nccl"]["ms"] * 1e3,
+        "replicated_rows_us_per_layer": rep_us,
         "distinct_local_experts_last_step": dl, "load_imbalance_max_over_mean": max(dl) / (sum(dl) / len(dl)),
         "combine_bytes_per_rank": (world - 1) * n_own * H * 4, "dispatch_bytes_per_rank": disp_bytes,
         "roofline": {"bound": "hbm", "kernel": "decode kernels of the most loaded rank (whole call)", "achieved": bytes_rank_max / (r["ms"] * 1e-3) / 1e9,
@@ -824,7 +847,7 @@ def ep_prefill_arm(args, world, rank, dev, tabs, R, zipf, torch, dist, ep, moe, 
         l0 = moe.launch_count()
         with ClockSampler(dev.index) as cs:
             dist.barrier()
-            t = timed(torch, lambda i: p.step(x, sel, rw, out), steps, 1)
+            t = timed(torch, lambda i: p.step(x, sel, rw, out), steps, 1, lead=1)
             dist.barrier()
         ms = torch.tensor([t], device=dev)
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)

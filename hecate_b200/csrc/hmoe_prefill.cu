@@ -243,6 +243,11 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r)
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
                    "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]) : "r"(taddr));
 }
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t* r)
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "r"(taddr));
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar)
 {
@@ -515,26 +520,21 @@ __global__ void __launch_bounds__(pf_threads(NMAT), 1) prefill_gemm_kernel(const
                 if (NMAT == 2) { const void* s1p = e < a.n_local ? (const void*) a.s1[e] : a.sh_s1; sc1 = __ldg((const float*) s1p + ch); }
             }
             const int csplit = NMAT == 2 ? (((int) n16 + 31) >> 5) << 4 : (int) n16;      // gate_up: columns [0, csplit) and [csplit, n16)
-            for (int c0 = chalf ? csplit : 0; c0 < (chalf ? (int) n16 : csplit); c0 += 16)
+            const int cbeg = chalf ? csplit : 0, cend = chalf ? (int) n16 : csplit;
+            if (NMAT == 2)
             {
-                uint32_t r0[16], r1[16];
-                tmem_ld16(tacc + c0, r0);
-                if (NMAT == 2) tmem_ld16(tacc + 256 + c0, r1);
-                // the picks' routing weights (gate_up) or tokens (down): lane j of the first 16 loads pick c0 + j, handed out by shuffles
-                const int pj = c0 + (lane & 15);
-                float wj = 0.f; int tj = 0;
-                if (pj < n) { if (NMAT == 2) wj = __ldg(a.wt + pos0 + pj); else tj = __ldg(a.tok + pos0 + pj); }
-                tmem_ld_wait();
-                if (NMAT == 2)
-                {
+                // Eight columns at a time, two register sets in turn: the tensor-memory loads of the next eight columns are in
+                // flight while the current eight are turned into activations (the tensor core waits for this read-out).
+                uint32_t g0[8], u0[8], g1[8], u1[8];
+                auto emit = [&](const uint32_t (&gr)[8], const uint32_t (&ur)[8], int c0, float wj) {
                     #pragma unroll
-                    for (int j = 0; j < 16; ++j)
+                    for (int j = 0; j < 8; ++j)
                     {
                         const int p = c0 + j;
                         const float w = __shfl_sync(0xffffffffu, wj, j);
                         if (p < n)
                         {
-                            const float gg = __uint_as_float(r0[j]) * sc0, uu = __uint_as_float(r1[j]) * sc1;
+                            const float gg = __uint_as_float(gr[j]) * sc0, uu = __uint_as_float(ur[j]) * sc1;
                             if (a.act_quant)
                             {
                                 float v = gg / (1.f + expf(-gg)) * uu * w;
@@ -558,26 +558,49 @@ __global__ void __launch_bounds__(pf_threads(NMAT), 1) prefill_gemm_kernel(const
                             }
                         }
                     }
-                }
-                else
+                };
+                auto weight_of = [&](int c0) { const int pj = c0 + (lane & 7); return pj < n ? __ldg(a.wt + pos0 + pj) : 0.f; };   // lane j: pick c0 + j
+                if (cbeg < cend) { tmem_ld8(tacc + cbeg, g0); tmem_ld8(tacc + 256 + cbeg, u0); }
+                for (int c0 = cbeg; c0 < cend; c0 += 16)
                 {
-                    #pragma unroll
-                    for (int j = 0; j < 16; ++j)
+                    const float wa = weight_of(c0), wb = weight_of(c0 + 8);
+                    tmem_ld_wait();
+                    if (c0 + 8 < cend) { tmem_ld8(tacc + c0 + 8, g1); tmem_ld8(tacc + 256 + c0 + 8, u1); }
+                    emit(g0, u0, c0, wa);
+                    if (c0 + 8 < cend)
                     {
-                        const int p = c0 + j;
-                        const int tk = __shfl_sync(0xffffffffu, tj, j);
-                        if (p < n)
+                        tmem_ld_wait();
+                        if (c0 + 16 < cend) { tmem_ld8(tacc + c0 + 16, g0); tmem_ld8(tacc + 256 + c0 + 16, u0); }
+                        emit(g1, u1, c0 + 8, wb);
+                    }
+                }
+            }
+            else
+            for (int c0 = cbeg; c0 < cend; c0 += 16)
+            {
+                uint32_t r0[16];
+                tmem_ld16(tacc + c0, r0);
+                // the picks' tokens: lane j of the first 16 loads pick c0 + j, handed out by shuffles
+                const int pj = c0 + (lane & 15);
+                int tj = 0;
+                if (pj < n) tj = __ldg(a.tok + pos0 + pj);
+                tmem_ld_wait();
+                #pragma unroll
+                for (int j = 0; j < 16; ++j)
+                {
+                    const int p = c0 + j;
+                    const int tk = __shfl_sync(0xffffffffu, tj, j);
+                    if (p < n)
+                    {
+                        const float v = __uint_as_float(r0[j]) * sc0;
+                        if (a.rows_per_rank)
                         {
-                            const float v = __uint_as_float(r0[j]) * sc0;
-                            if (a.rows_per_rank)
-                            {
-                                // the row's owner may be another GPU, and up to eight GPUs add into the same addresses: the
-                                // reduction has to be atomic at system scope (a gpu-scope one is only atomic among this GPU's threads)
-                                const int pr = tk / a.rows_per_rank;
-                                red_add_sys(a.out_peer[pr] + (size_t) (tk - pr * a.rows_per_rank) * a.N + ch, v);
-                            }
-                            else atomicAdd(a.out + (size_t) tk * a.N + ch, v);
+                            // the row's owner may be another GPU, and up to eight GPUs add into the same addresses: the
+                            // reduction has to be atomic at system scope (a gpu-scope one is only atomic among this GPU's threads)
+                            const int pr = tk / a.rows_per_rank;
+                            red_add_sys(a.out_peer[pr] + (size_t) (tk - pr * a.rows_per_rank) * a.N + ch, v);
                         }
+                        else atomicAdd(a.out + (size_t) tk * a.N + ch, v);
                     }
                 }
             }
