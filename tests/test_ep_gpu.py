@@ -111,6 +111,35 @@ def _rank_main(rank, world, port, out_path):
     sep_err = torch.tensor([float((res["separate"] - res[True]).abs().max() / res[True].abs().max())], device=dev)
     dist.all_reduce(sep_err, op=dist.ReduceOp.MAX)
     dp_err = torch.maximum(dp_err, sep_err)
+    # The reference's int8 shared expert beside the int4 routed experts, at a shape whose two small kernels leave most blocks
+    # without work: the programmatic launch chain must still order the step counter and the partial slot (every rank adds its
+    # share of the shared expert's rows into the slot of THIS step).
+    from hecate_b200 import layout as LY
+    mk8 = lambda s_, N, K: (synth.rand_bytes(13, s_, N * K).reshape(N, K).astype(np.uint8), np.exp(synth.normal(13, s_ + 50, N) * 0.5 - 7.5).astype(np.float32))
+    ex8 = (mk8(1, I, H), mk8(2, I, H), mk8(3, H, I))
+    up = lambda a_: torch.from_numpy(np.ascontiguousarray(a_)).to(dev)
+    sh8 = tuple(up(LY.pack_i8(c)) for c, _ in ex8) + tuple(up(s_) for _, s_ in ex8)
+    base = HostLayer(0, 0, H, I, range(p["lo"], p["lo"] + p["n_local"]), 128, False).upload(dev)
+    t8 = moe.ExpertTables(H, I, 8, *[base.keep[i] for i in range(6)], group=128, shared=sh8, device=dev, shared_i8=True)
+    i8_err = torch.zeros(1, device=dev)
+    dec = EpDecoder(rank, world, t8, E, dev, dist, use_peer=True)
+    outs8 = []
+    for stepi in range(4):
+        sel, rw = synth.zipf_routing(10 + stepi, 0, R, E, 8, 0.0)
+        f = torch.zeros(R, H, device=dev)
+        dec.step(x, torch.from_numpy(sel).to(dev), torch.from_numpy(rw).to(dev), f)
+        outs8.append(f)
+    assert dec.status() == 0
+    dist.barrier(); dec.peer.close()
+    if rank == 0:
+        full8 = HostLayer(0, 0, H, I, range(E), 128, False).upload(dev)
+        tf8 = moe.ExpertTables(H, I, 8, *[full8.keep[i] for i in range(6)], group=128, shared=sh8, device=dev, shared_i8=True)
+        ws8 = moe.decode_workspace(H, I, dev)
+        for stepi in range(4):
+            sel, rw = synth.zipf_routing(10 + stepi, 0, R, E, 8, 0.0)
+            y = torch.zeros(R, H, device=dev)
+            moe.decode(tf8, x, torch.from_numpy(sel).to(dev), torch.from_numpy(rw).to(dev), y, ws8)
+            i8_err = torch.maximum(i8_err, ((outs8[stepi] - y).norm() / y.norm()).reshape(1))
     # all ranks hold the same bits after the peer combine (fixed rank order)
     mine = res[True].clone()
     others = [torch.zeros_like(mine) for _ in range(world)]
@@ -127,7 +156,7 @@ def _rank_main(rank, world, port, out_path):
             refs.append(y)
         ref = torch.stack(refs)
         np.save(out_path, np.array([float(same), float((res[True] - ref).norm() / ref.norm()), float((res[False] - ref).norm() / ref.norm()),
-                                    float(dp_err.item())]))
+                                    float(dp_err.item()), float(i8_err.item())]))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -139,10 +168,11 @@ def test_two_gpu_peer_combine_matches_single_gpu(tmp_path):
     import torch.multiprocessing as mp
     out = str(tmp_path / "ep.npy")
     mp.spawn(_rank_main, args=(2, 29600 + os.getpid() % 2000, out), nprocs=2, join=True)
-    same, err_peer, err_nccl, err_dp = np.load(out)
+    same, err_peer, err_nccl, err_dp, err_i8 = np.load(out)
     assert same == 1.0
     assert err_peer < 1e-3 and err_nccl < 1e-3
     assert err_dp < 1e-3                 # dispatched rows give what replicated rows give (the sums differ only in their atomic order)
+    assert err_i8 < 1e-3                 # int8 shared expert under expert parallelism = the single-GPU result
 
 
 def _prefill_rank_main(rank, world, port, out_path):
