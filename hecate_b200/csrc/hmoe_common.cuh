@@ -136,6 +136,18 @@ __device__ __forceinline__ void frag_from_codes(uint32_t w, uint32_t* a)
     asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(a[3]) : "r"(hi1), "r"(0x2c002c00u), "r"(0xd480d480u));
 }
 
+// The reference's int8 format (its shared expert and dense linears, runtime/core/hecate_runtime.py:38-48): value = code - 128.
+// 4 bytes (c0 rh0, c0 rh1, c1 rh0, c1 rh1) -> fp16x2 (row g: c0, c1) and (row g + 8: c0, c1), value code - 128, exactly
+// (the same magic-number step as the reference uses for these bytes, runtime/tier/moe4/moe4.cu:48-55: 1024 + code is exact in fp16)
+__device__ __forceinline__ void dec_i8(uint32_t w, uint32_t& lo, uint32_t& hi)
+{
+    uint32_t h0, h1;
+    asm("lop3.b32 %0, %1, 0x00ff00ff, 0x64006400, 0xea;" : "=r"(h0) : "r"(w));
+    asm("lop3.b32 %0, %1, 0x00ff00ff, 0x64006400, 0xea;" : "=r"(h1) : "r"(w >> 8));
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(lo) : "r"(h0), "r"(0x64806480u));
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(hi) : "r"(h1), "r"(0x64806480u));
+}
+
 // position of two-value word p (columns 2p, 2p+1 of a 64-column block) in the activation row order the kernels read:
 // t = p / 8 (16-column step), h = (p % 8) / 4, q = p % 4  ->  q * 8 + t * 2 + h (the B-fragment order the reference's norm +
 // router kernel may pre-write for moe4, frag_word, runtime/tier/moe4/moe4.cu:72)

@@ -269,6 +269,7 @@ struct GemmArgs
     const int64_t* w0; const int64_t* w1;     // pointer tables of the matrix (gate, up) or (down, -)
     const int64_t* s0; const int64_t* s1;     // scale tables
     const void* sh_w0; const void* sh_w1; const void* sh_s0; const void* sh_s1;   // shared expert (expert id n_local)
+    int sh_i8;                // the shared expert is in the reference's int8 format (dense GEMV fragment order, fp32 scale per row)
     int n_local;
     const Plan* plan; const int* rbt; const int* tok; const float* wt;
     __half* act;              // gate_up: output [pos][I]
@@ -396,6 +397,30 @@ __global__ void __launch_bounds__(pf_threads(NMAT), 1) prefill_gemm_kernel(const
             const int rb = item / NCT, ct = item % NCT, e = a.rbt[4 * rb];
             const void* wp = e < a.n_local ? (const void*) (mat ? a.w1[e] : a.w0[e]) : (mat ? a.sh_w1 : a.sh_w0);
             const void* sp = e < a.n_local ? (const void*) (mat ? a.s1[e] : a.s0[e]) : (mat ? a.sh_s1 : a.sh_s0);
+            if (a.sh_i8 && e >= a.n_local)
+            {
+                // The shared expert in the reference's int8 format (runtime/tier/tier_split.py:495-514): 2 KB units of 64 rows x 32
+                // columns, 16 bytes per lane and strip = the fragments of two 16-column steps; a stage takes two units. One ninth
+                // of the work at most, so no prefetch queue: the two loads of a stage are issued, converted and stored in turn.
+                // Its fp32 row scales are applied by the read-out.
+                const char* w8 = (const char*) wp + ((size_t) (2 * ct + unit) * (a.K / 32) * 4 + strip) * 512 + lane * 16;
+                const uint32_t it0 = tile_n * (uint32_t) KBT;
+                for (int kb = kb0; kb < KBT && ok; kb += kstep)
+                {
+                    const int kbw = kb >= KB ? kb - KB : kb;
+                    const uint4 wa = ldg128_nc(w8 + (size_t) (2 * kbw) * 2048), wb = ldg128_nc(w8 + (size_t) (2 * kbw + 1) * 2048);
+                    uint32_t cv[4][4];
+                    dec_i8(wa.x, cv[0][0], cv[0][1]); dec_i8(wa.y, cv[0][2], cv[0][3]); dec_i8(wa.z, cv[1][0], cv[1][1]); dec_i8(wa.w, cv[1][2], cv[1][3]);
+                    dec_i8(wb.x, cv[2][0], cv[2][1]); dec_i8(wb.y, cv[2][2], cv[2][3]); dec_i8(wb.z, cv[3][0], cv[3][1]); dec_i8(wb.w, cv[3][2], cv[3][3]);
+                    const uint32_t gi = it0 + kb, s = gi % L::STAGES;
+                    if (gi >= (uint32_t) L::STAGES && !mbar_wait(empty + s * 8, ((gi / L::STAGES) - 1) & 1, abort_flag, a.status)) { ok = false; break; }
+                    store_strip(row_off + s * L::STAGE, c0, c1, cv);
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(full_a + s * 8);
+                }
+                continue;
+            }
             const char* wbase = (const char*) wp + ((size_t) (2 * ct + unit) * KB * 4 + strip) * 512 + lane * 16;
             const char* sbase_p = (const char*) sp + ((size_t) (2 * ct + unit) * (a.K / 128) * 64 + g * 8 + 2 * strip) * 2;
             // packed words and scale pairs of the next NPF of this warp's stages, in flight while earlier ones are converted
@@ -513,7 +538,7 @@ __global__ void __launch_bounds__(pf_threads(NMAT), 1) prefill_gemm_kernel(const
             const int chp = (ch & ~63) + operand_pos(ch & 63);       // where the down GEMM expects this channel of the activations
             const uint32_t tacc = tmem + acc * 256 + ((uint32_t) (lq * 32) << 16);
             float sc0 = 1.f, sc1 = 1.f;
-            if (!a.grouped)
+            if (!a.grouped || (a.sh_i8 && e >= a.n_local))      // one fp32 scale per output row: applied here, not in the operand
             {
                 const void* s0p = e < a.n_local ? (const void*) a.s0[e] : a.sh_s0;
                 sc0 = __ldg((const float*) s0p + ch);
@@ -740,6 +765,7 @@ int prefill_sorted_launch(const hmoe_layer* L, const void* x, int x_dtype, const
     if (!make_map(&mx, xg, H * kf, (size_t) npos) || !make_map(&ma, act, I * kf, (size_t) npos)) return fail(HMOE_E_CUDA, "hmoe_prefill_sorted: cuTensorMapEncodeTiled failed");
     GemmArgs g;
     g.grouped = L->group != 0; g.act_quant = act_quant; g.n_local = n_local; g.kfold = kf;
+    g.sh_i8 = L->shared_format == 1 && L->sh_gate_w != nullptr;
     g.plan = plan; g.rbt = rbt; g.tok = tok; g.wt = wt; g.act = act; g.out = out; g.status = status;
     g.rows_per_rank = 0;
     for (int p = 0; p < 8; ++p) g.out_peer[p] = nullptr;
@@ -792,7 +818,6 @@ int prefill_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_
     if (!(L->group == 0 && L->scale_dtype == HMOE_F32) && !(L->group == 128 && L->scale_dtype == HMOE_BF16))
         return fail(HMOE_E_ARG, "hmoe_prefill: scales must be fp32 per row (group 0) or bf16 per 128 columns");
     if (x_dtype != HMOE_F16 && x_dtype != HMOE_BF16) return fail(HMOE_E_ARG, "hmoe_prefill: x must be fp16 or bf16");
-    if (L->shared_format != 0 && L->sh_gate_w) return fail(HMOE_E_UNSUPPORTED, "hmoe_prefill: the int8 shared expert is served by the decode path only");
     if (!x || !sel || !rw || (!out && !out_peer) || !ws) return fail(HMOE_E_ARG, "hmoe_prefill: null pointer");
     const int kf = act_quant ? 2 : 1;
     const WsLayout w = ws_layout(R, L->topk, n_local, H, I, TN, kf);
@@ -816,6 +841,7 @@ int prefill_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_
     if (!make_map(&mx, xg, H * kf, (size_t) w.rows_cap) || !make_map(&ma, act, I * kf, (size_t) w.rows_cap)) return fail(HMOE_E_CUDA, "hmoe_prefill: cuTensorMapEncodeTiled failed");
     GemmArgs g;
     g.grouped = L->group != 0; g.act_quant = act_quant; g.n_local = n_local; g.kfold = kf;
+    g.sh_i8 = L->shared_format == 1 && L->sh_gate_w != nullptr;
     g.plan = plan; g.rbt = rbt; g.tok = tok; g.wt = wt; g.act = act; g.out = out; g.status = status;
     g.rows_per_rank = out_peer ? rows_per_rank : 0;
     for (int p = 0; p < 8; ++p) g.out_peer[p] = (out_peer && p < world) ? (float*) out_peer[p] : nullptr;

@@ -23,16 +23,6 @@ namespace {
 
 constexpr int SW = 16, STHREADS = SW * 32, PART = 16 * 65;
 
-// 4 bytes (c0 rh0, c0 rh1, c1 rh0, c1 rh1) -> fp16x2 (row g: c0, c1) and (row g + 8: c0, c1), value code - 128, exactly
-// (the same magic-number step as the reference uses for these bytes, runtime/tier/moe4/moe4.cu:48-55: 1024 + code is exact in fp16)
-__device__ __forceinline__ void dec_i8(uint32_t w, uint32_t& lo, uint32_t& hi)
-{
-    uint32_t h0, h1;
-    asm("lop3.b32 %0, %1, 0x00ff00ff, 0x64006400, 0xea;" : "=r"(h0) : "r"(w));
-    asm("lop3.b32 %0, %1, 0x00ff00ff, 0x64006400, 0xea;" : "=r"(h1) : "r"(w >> 8));
-    asm("sub.f16x2 %0, %1, %2;" : "=r"(lo) : "r"(h0), "r"(0x64806480u));
-    asm("sub.f16x2 %0, %1, %2;" : "=r"(hi) : "r"(h1), "r"(0x64806480u));
-}
 // programmatic dependent launch: let the next kernel's blocks start as this one's retire / wait for the kernel before
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }

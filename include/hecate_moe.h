@@ -41,7 +41,7 @@ typedef struct hmoe_layer
     const void* sh_gate_s; const void* sh_up_s; const void* sh_down_s;
     int32_t shared_format; /* 0: the shared expert is stored like a routed expert (int4, the layer's scale format);
                               1: the reference's own shared expert (runtime/tier/tier_split.py:495-514): int8 codes (value = code - 128)
-                              in its dense GEMV fragment order with one fp32 scale per output row (decode only) */
+                              in its dense GEMV fragment order with one fp32 scale per output row (decode and prefill) */
 } hmoe_layer;
 
 int hmoe_version(void);

@@ -1,5 +1,5 @@
 """The shared expert in the reference's int8 format (dense GEMV fragment order, one fp32 scale per row) beside int4 routed
-experts: the decode result equals the routed experts' result plus an exact evaluation of the int8 expert."""
+experts: the decode and the prefill result equal the routed experts' result plus an exact evaluation of the int8 expert."""
 import numpy as np
 import pytest
 
@@ -46,19 +46,32 @@ def test_int8_shared_expert(oracle, H, I, R, group):
         assert errors(y.cpu().numpy(), ref)[2] < NORM_REL_EXACT, (call, errors(y.cpu().numpy(), ref))
 
 
-def test_int8_shared_expert_is_decode_only(oracle):
+@pytest.mark.parametrize("H,I,R,group", [(256, 128, 40, 128), (512, 256, 300, 0), (6144, 2048, 200, 128)])
+def test_int8_shared_expert_in_prefill(oracle, H, I, R, group):
+    """The grouped GEMMs take the same int8 shared expert: its tiles are staged from the int8 fragment order and scaled per row in
+    the read-out, beside routed experts of either scale format."""
     import torch
     from hecate_b200 import moe
-    from hecate_b200._lib import HmoeError
     dev = torch.device("cuda:0")
-    H, I, E, R = 256, 128, 8, 40
-    hl = HostLayer(9, 0, H, I, range(E), 128, False)
+    E = 8
+    hl = HostLayer(9, 0, H, I, range(E), group, False)
     base = hl.upload(dev)
     ex8 = _int8_expert(13, H, I)
     up = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
     shared = tuple(up(layout.pack_i8(c)) for c, _ in ex8) + tuple(up(s) for _, s in ex8)
-    tabs = moe.ExpertTables(H, I, 8, *[base.keep[i] for i in range(6)], group=128, shared=shared, device=dev, shared_i8=True)
+    tabs = moe.ExpertTables(H, I, 8, *[base.keep[i] for i in range(6)], group=group, shared=shared, device=dev, shared_i8=True)
     x = synth.activations(3, 0, R, H).astype(np.float16); sel, rw = random_routing(4, R, E)
+    ex, _ = hl.oracle_experts(oracle)
+    rows = np.unique(np.concatenate([np.arange(min(R, 6)), [R // 2, R - 1]]))
+    ref = oracle.moe_forward(H, I, group, x[rows], sel[rows], rw[rows], 0, ex, None, mode=1).astype(np.float64) + _shared_exact(x[rows], ex8)
     ws = moe.prefill_workspace(R, 8, E, H, I, dev)
-    with pytest.raises(HmoeError):
-        moe.prefill(tabs, up(x), up(sel), up(rw), torch.zeros(R, H, device=dev), ws)
+    for call in range(2):
+        y = torch.zeros(R, H, device=dev)
+        moe.prefill(tabs, up(x), up(sel), up(rw), y, ws)
+        assert moe.ws_status(ws) == 0
+        got = y.cpu().numpy()
+        assert errors(got[rows], ref)[2] < NORM_REL_EXACT, (call, errors(got[rows], ref))
+    # and the decode kernels agree with the grouped GEMMs on the first 16 rows
+    yd = torch.zeros(16 if R >= 16 else R, H, device=dev); n = yd.shape[0]
+    moe.decode(tabs, up(x[:n]), up(sel[:n]), up(rw[:n]), yd, moe.decode_workspace(H, I, dev))
+    assert errors(got[:n], yd.cpu().numpy().astype(np.float64))[2] < NORM_REL_EXACT
