@@ -29,6 +29,7 @@
 // the same time share one input tile and one expert's weights through L2.
 // Every wait is bounded (see mbar_wait); tensor memory is released by the warp that allocated it on every path.
 #include <cuda.h>
+#include <type_traits>
 #include "hmoe_common.cuh"
 #include "hmoe_internal.h"
 
@@ -379,13 +380,13 @@ __global__ void __launch_bounds__(pf_threads(NMAT), 1) prefill_gemm_kernel(const
     if (warp < NDQ)
     {
         // ---- dequantise: one 16-row strip of one 64-row unit per warp and stage. gate_up: 2 matrices x 2 units x 4 strips =
-        // 16 strip-blocks per stage, one per warp. down: 8 strip-blocks per stage; warps 0-7 take the even stages, warps
-        // 8-15 the odd ones. The packed words are fetched NPF of the warp's stages ahead. These warps do nothing else: they
-        // stream from tile to tile and stop only when the ring is full, so the MMA thread always finds its next stages.
+        // 16 strip-blocks per stage, one per warp. down: 8 strip-blocks per stage; warps 0-7 take the even pairs of stages, warps
+        // 8-15 the odd ones (in pairs of stages, see below). The packed words are fetched two of the warp's steps ahead. These warps
+        // do nothing else: they stream from tile to tile and stop only when the ring is full, so the MMA thread always finds its
+        // next stages.
         const int g = lane >> 2, q = lane & 3;
         const int strip = warp & 3, unit = (warp >> 2) & 1, mat = NMAT == 2 ? warp >> 3 : 0;
         const int kb0 = NMAT == 2 ? 0 : warp >> 3, kstep = NMAT == 2 ? 1 : 2;
-        constexpr int NPF = 3;
         // shared address of this lane's row g in slot 0, and its two 16-byte columns under the 128-byte swizzle
         const uint32_t row_off = sbase + mat * L::A_BYTES + (unit * 8 + strip * 2) * 1024 + g * 128;
         const uint32_t c0 = (uint32_t) (((2 * q) ^ g) << 4), c1 = (uint32_t) (((2 * q + 1) ^ g) << 4);
@@ -421,44 +422,61 @@ __global__ void __launch_bounds__(pf_threads(NMAT), 1) prefill_gemm_kernel(const
                 }
                 continue;
             }
+            // One step of a warp = one 128-column scale group = two consecutive ring stages: two 16-byte code words and one scale
+            // word per lane. gate_up: every warp takes every pair of stages; down: warps 0-7 the even pairs, warps 8-15 the odd ones.
+            const int NPW = KB >> 1, NP = KBT >> 1;                  // pairs in one pass over the weights / in the tile
+            const int j0 = NMAT == 2 ? 0 : warp >> 3;
+            constexpr int JSTEP = NMAT == 2 ? 1 : 2;
             const char* wbase = (const char*) wp + ((size_t) (2 * ct + unit) * KB * 4 + strip) * 512 + lane * 16;
             const char* sbase_p = (const char*) sp + ((size_t) (2 * ct + unit) * (a.K / 128) * 64 + g * 8 + 2 * strip) * 2;
-            // packed words and scale pairs of the next NPF of this warp's stages, in flight while earlier ones are converted
-            // (the queue is indexed with compile-time positions: the loop over the stages is unrolled NPF times)
-            uint4 wq[NPF]; uint32_t sq[NPF];
-            auto fetch = [&](int kbi, uint4& w, uint32_t& sc) {
-                const int kbw = kbi >= KB ? kbi - KB : kbi;            // second pass over the weights for the lo halves
-                w = kbi < KBT ? ldg128_nc(wbase + (size_t) kbw * 2048) : make_uint4(0, 0, 0, 0);
-                sc = (a.grouped && kbi < KBT) ? __ldg((const uint32_t*) (sbase_p + (size_t) (kbw >> 1) * 128)) : 0u;
-            };
-            auto convert = [&](const uint4& w, uint32_t sc, uint32_t (&cv)[4][4]) {
-                uint32_t s_lo = 0, s_hi = 0;
-                if (a.grouped) scale_pair(sc, s_lo, s_hi);
-                convert_strip(w, s_lo, s_hi, a.grouped != 0, cv);
-            };
-            #pragma unroll
-            for (int i = 0; i < NPF; ++i) fetch(kb0 + i * kstep, wq[i], sq[i]);
-            uint32_t cv[4][4];                                 // the converted strip of the warp's next stage
-            convert(wq[0], sq[0], cv);
-            const uint32_t it0 = tile_n * (uint32_t) KBT;
-            for (int kbase = kb0; kbase < KBT && ok; kbase += NPF * kstep)
-            {
-                #pragma unroll
-                for (int u = 0; u < NPF; ++u)
-                {
-                    const int kb = kbase + u * kstep;
-                    if (kb >= KBT || !ok) continue;
-                    const uint32_t gi = it0 + kb, s = gi % L::STAGES;
-                    if (gi >= (uint32_t) L::STAGES && !mbar_wait(empty + s * 8, ((gi / L::STAGES) - 1) & 1, abort_flag, a.status)) { ok = false; continue; }
+            // the warp's ring slot and the parity of the slot's current use, stepped from stage to stage (no division per stage)
+            const uint32_t gi0 = tile_n * (uint32_t) KBT + 2 * j0;
+            uint32_t s = gi0 % L::STAGES, ph = (gi0 / L::STAGES) & 1;
+            auto run = [&](auto grouped_tag) {
+                constexpr bool GROUPED = decltype(grouped_tag)::value;
+                // the code words and scale pairs of the warp's next two steps, in flight while the current step is converted
+                uint4 qa[2] = {}, qb[2] = {}; uint32_t qs[2] = {};
+                auto fetch = [&](int pj, uint4& wa, uint4& wb, uint32_t& sc) {
+                    if (pj >= NP) return;
+                    const int jw = pj >= NPW ? pj - NPW : pj;               // second pass over the weights for the lo halves
+                    const char* p = wbase + (size_t) jw * 4096;
+                    wa = ldg128_nc(p); wb = ldg128_nc(p + 2048);
+                    if (GROUPED) sc = __ldg((const uint32_t*) (sbase_p + (size_t) jw * 128));
+                };
+                // the converted strip into ring slot s (a fresh slot passes at once: its barrier's preceding phase counts as
+                // complete), the slot handed to the MMA thread, s stepped
+                auto put = [&](const uint32_t (&cv)[4][4]) -> bool {
+                    if (!mbar_wait(empty + s * 8, ph ^ 1, abort_flag, a.status)) return false;
                     store_strip(row_off + s * L::STAGE, c0, c1, cv);
                     fence_proxy_async();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(full_a + s * 8);
-                    // off the critical path: refill the queue position just used and convert the next stage's words
-                    fetch(kb + NPF * kstep, wq[u], sq[u]);
-                    convert(wq[(u + 1) % NPF], sq[(u + 1) % NPF], cv);
+                    if (++s == (uint32_t) L::STAGES) { s = 0; ph ^= 1; }
+                    return true;
+                };
+                fetch(j0, qa[0], qb[0], qs[0]);
+                fetch(j0 + JSTEP, qa[1], qb[1], qs[1]);
+                uint32_t cv[4][4], s_lo = 0, s_hi = 0;                      // the converted strip of the warp's next stage
+                if (GROUPED) scale_pair(qs[0], s_lo, s_hi);
+                convert_strip(qa[0], s_lo, s_hi, GROUPED, cv);
+                for (int j = j0; j < NP && ok; j += 2 * JSTEP)
+                {
+                    #pragma unroll
+                    for (int u = 0; u < 2; ++u)
+                    {
+                        const int jj = j + u * JSTEP;
+                        if (jj >= NP) break;
+                        if (!put(cv)) { ok = false; break; }
+                        convert_strip(qb[u], s_lo, s_hi, GROUPED, cv);      // before the wait for the second slot
+                        if (!put(cv)) { ok = false; break; }
+                        if (JSTEP == 2) { s += 2; if (s >= (uint32_t) L::STAGES) { s -= L::STAGES; ph ^= 1; } }     // the other warps' pair
+                        fetch(jj + 2 * JSTEP, qa[u], qb[u], qs[u]);
+                        if (GROUPED) scale_pair(qs[u ^ 1], s_lo, s_hi);     // the next pair's first stage, converted before its slot is waited for
+                        convert_strip(qa[u ^ 1], s_lo, s_hi, GROUPED, cv);
+                    }
                 }
-            }
+            };
+            if (a.grouped) run(std::true_type()); else run(std::false_type());
         }
     }
     else if (warp == NDQ)
