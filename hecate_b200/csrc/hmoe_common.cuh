@@ -63,9 +63,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     for (uint32_t i = 0;; ++i)
     {
         if (mbar_try_hint(bar, parity, 20000u)) return true;
-#ifdef HMOE_WAIT_SLEEP
-        __nanosleep(HMOE_WAIT_SLEEP);
-#endif
         if ((i & 63u) == 63u)
         {
             if (*abort_flag) return false;

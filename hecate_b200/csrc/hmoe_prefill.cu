@@ -36,6 +36,21 @@
 namespace hmoe {
 namespace {
 
+// Diagnostic build (-DHMOE_PROBE_WAITS): every role adds up the cycles it spends in each of its waits (in registers, one atomic
+// per thread at the end of the kernel); hmoe_probe_read() returns the sums. 32 counters per kernel: 0 / 1 / 2 MMA thread waiting
+// for the weights / the inputs / a free accumulator set, 4 and 10 dequantising warps 0 and 15 waiting for a ring slot, 9 warp 0's
+// stores + fence + arrive, 6 TMA thread waiting for a slot, 7 / 8 first read-out warp waiting for a tile / reading it out, 15
+// the block's lifetime. Not part of the normal build.
+#ifdef HMOE_PROBE_WAITS
+__device__ unsigned long long g_probe[64];
+#define PROBE_T0() const long long pt0_ = clock64()
+#define PROBE_ADD(i) pacc_[i] += (unsigned long long) (clock64() - pt0_)
+#define PROBE_ON(c) (c)
+#else
+#define PROBE_T0()
+#define PROBE_ADD(i)
+#define PROBE_ON(c) false
+#endif
 constexpr int TM = 128, TN = 256, TK = 64;
 constexpr int NDQ = 16;                         // dequantising warps
 // read-out warps: one per quarter of the tensor-memory lanes in down (whose read-out runs under the next tile's MMAs), two per
@@ -238,6 +253,11 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r)
                    "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
                    "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]) : "r"(taddr));
 }
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t* r)
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63]) : "r"(taddr));
+}
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r)
 {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
@@ -355,7 +375,7 @@ __global__ void __launch_bounds__(pf_threads(NMAT), 1) prefill_gemm_kernel(const
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // Accumulators in tensor memory: gate + up fill all 512 columns; down needs 256 and keeps two sets, so the MMAs of the
     // next tile run while this tile's sums are read out.
-    constexpr int TMEM_COLS = 512, NACC = NMAT == 2 ? 1 : 2;
+        constexpr int TMEM_COLS = 512, NACC = NMAT == 2 ? 1 : 2;
 
     if (threadIdx.x == 0)
     {
@@ -375,6 +395,10 @@ __global__ void __launch_bounds__(pf_threads(NMAT), 1) prefill_gemm_kernel(const
     const uint32_t tmem = *tmem_slot;
 
     const int KB = a.K / 64, KBT = KB * a.kfold, NCT = a.N / TM;     // KB 64-column blocks of the weights, KBT ring stages per tile
+#ifdef HMOE_PROBE_WAITS
+    unsigned long long pacc_[16] = {};
+#endif
+    PROBE_T0();
     const int nitems = a.plan->nrb * NCT;
 
     if (warp < NDQ)
@@ -446,11 +470,13 @@ __global__ void __launch_bounds__(pf_threads(NMAT), 1) prefill_gemm_kernel(const
                 // the converted strip into ring slot s (a fresh slot passes at once: its barrier's preceding phase counts as
                 // complete), the slot handed to the MMA thread, s stepped
                 auto put = [&](const uint32_t (&cv)[4][4]) -> bool {
-                    if (!mbar_wait(empty + s * 8, ph ^ 1, abort_flag, a.status)) return false;
+                    { PROBE_T0(); const bool w_ = mbar_wait(empty + s * 8, ph ^ 1, abort_flag, a.status); if (PROBE_ON(threadIdx.x == 0)) PROBE_ADD(4); if (PROBE_ON(threadIdx.x == 15 * 32)) PROBE_ADD(10); if (!w_) return false; }
+                    PROBE_T0();
                     store_strip(row_off + s * L::STAGE, c0, c1, cv);
                     fence_proxy_async();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(full_a + s * 8);
+                    if (PROBE_ON(threadIdx.x == 0)) PROBE_ADD(9);
                     if (++s == (uint32_t) L::STAGES) { s = 0; ph ^= 1; }
                     return true;
                 };
@@ -491,7 +517,7 @@ __global__ void __launch_bounds__(pf_threads(NMAT), 1) prefill_gemm_kernel(const
                 for (int kb = 0; kb < KBT; ++kb)
                 {
                     const uint32_t it = tile_n * (uint32_t) KBT + kb, s = it % L::STAGES;
-                    if (it >= (uint32_t) L::STAGES && !mbar_wait(empty + s * 8, ((it / L::STAGES) - 1) & 1, abort_flag, a.status)) { ok = false; break; }
+                    { PROBE_T0(); const bool w_ = it < (uint32_t) L::STAGES || mbar_wait(empty + s * 8, ((it / L::STAGES) - 1) & 1, abort_flag, a.status); PROBE_ADD(6); if (!w_) { ok = false; break; } }
                     mbar_expect_tx(full_b + s * 8, L::B_BYTES);
                     tma_load_2d(sbase + s * L::STAGE + NMAT * L::A_BYTES, &tmap, kb * 64, pos0, full_b + s * 8);
                 }
@@ -511,12 +537,13 @@ __global__ void __launch_bounds__(pf_threads(NMAT), 1) prefill_gemm_kernel(const
                 const uint32_t idesc = (1u << 4) | ((n16 >> 3) << 17) | ((uint32_t) (TM >> 4) << 24);
                 const uint32_t acc = tile_n % NACC, tacc = tmem + acc * 256;
                 // the accumulator set is free once the tile that used it last has been read out
-                if (tile_n >= (uint32_t) NACC && !mbar_wait(tmem_free + acc * 8, ((tile_n / NACC) - 1) & 1, abort_flag, a.status)) break;
+                { PROBE_T0(); const bool w_ = tile_n < (uint32_t) NACC || mbar_wait(tmem_free + acc * 8, ((tile_n / NACC) - 1) & 1, abort_flag, a.status); PROBE_ADD(2); if (!w_) break; }
                 tc_fence_after();
                 for (int kb = 0; kb < KBT && ok; ++kb)
                 {
                     const uint32_t it = tile_n * (uint32_t) KBT + kb, s = it % L::STAGES, ph = (it / L::STAGES) & 1;
-                    if (!mbar_wait(full_a + s * 8, ph, abort_flag, a.status) || !mbar_wait(full_b + s * 8, ph, abort_flag, a.status)) { ok = false; break; }
+                    { PROBE_T0(); const bool w_ = mbar_wait(full_a + s * 8, ph, abort_flag, a.status); PROBE_ADD(0); if (!w_) { ok = false; break; } }
+                    { PROBE_T0(); const bool w_ = mbar_wait(full_b + s * 8, ph, abort_flag, a.status); PROBE_ADD(1); if (!w_) { ok = false; break; } }
                     tc_fence_after();
                     const uint32_t at = sbase + s * L::STAGE, bt = at + NMAT * L::A_BYTES;
                     #pragma unroll
@@ -549,12 +576,15 @@ __global__ void __launch_bounds__(pf_threads(NMAT), 1) prefill_gemm_kernel(const
             const int e = a.rbt[4 * rb], pos0 = a.rbt[4 * rb + 1], n = a.rbt[4 * rb + 2];
             (void) chalf;
             const uint32_t acc = (uint32_t) (tile_n % NACC);
-            if (!mbar_wait(done + acc * 8, (tile_n / NACC) & 1, abort_flag, a.status)) break;
-            tc_fence_after();
             const uint32_t n16 = (uint32_t) ((n + 15) & ~15);
             const int ch = ct * TM + lq * 32 + lane;
             const int chp = (ch & ~63) + operand_pos(ch & 63);       // where the down GEMM expects this channel of the activations
             const uint32_t tacc = tmem + acc * 256 + ((uint32_t) (lq * 32) << 16);
+            const int csplit = NMAT == 2 ? (((int) n16 + 31) >> 5) << 4 : (int) n16;      // gate_up: columns [0, csplit) and [csplit, n16)
+            const int cbeg = chalf ? csplit : 0, cend = chalf ? (int) n16 : csplit;
+            // Everything the read-out needs besides the sums is fetched BEFORE the wait for the tile's last MMA, so that no global
+            // load stands between that MMA and the release of the accumulators: the row scales, and in gate_up the
+            // routing weights of the warp's columns (lane l holds picks cbeg + 32 i + l).
             float sc0 = 1.f, sc1 = 1.f;
             if (!a.grouped || (a.sh_i8 && e >= a.n_local))      // one fp32 scale per output row: applied here, not in the operand
             {
@@ -562,23 +592,38 @@ __global__ void __launch_bounds__(pf_threads(NMAT), 1) prefill_gemm_kernel(const
                 sc0 = __ldg((const float*) s0p + ch);
                 if (NMAT == 2) { const void* s1p = e < a.n_local ? (const void*) a.s1[e] : a.sh_s1; sc1 = __ldg((const float*) s1p + ch); }
             }
-            const int csplit = NMAT == 2 ? (((int) n16 + 31) >> 5) << 4 : (int) n16;      // gate_up: columns [0, csplit) and [csplit, n16)
-            const int cbeg = chalf ? csplit : 0, cend = chalf ? (int) n16 : csplit;
-            if (NMAT == 2)
+            float wv[4] = {0.f, 0.f, 0.f, 0.f};
+            if constexpr (NMAT == 2)
+            {
+                #pragma unroll
+                for (int i = 0; i < 4; ++i) { const int pj = cbeg + 32 * i + lane; if (pj < n) wv[i] = __ldg(a.wt + pos0 + pj); }
+            }
+            { PROBE_T0(); const bool w_ = mbar_wait(done + acc * 8, (tile_n / NACC) & 1, abort_flag, a.status); if (PROBE_ON(threadIdx.x == (NDQ + 2) * 32)) PROBE_ADD(7); if (!w_) break; }
+            PROBE_T0();
+            tc_fence_after();
+            if constexpr (NMAT == 2)
             {
                 // Eight columns at a time, two register sets in turn: the tensor-memory loads of the next eight columns are in
                 // flight while the current eight are turned into activations (the tensor core waits for this read-out).
+                // The loops carry no branch per column: a conditional region per column costs convergence-barrier instructions that
+                // run one after the other (measured: ~70 cycles per column); the arithmetic runs for the padding columns too and
+                // only the store is predicated; the int8 mode is a compile-time variant of the whole loop.
                 uint32_t g0[8], u0[8], g1[8], u1[8];
-                auto emit = [&](const uint32_t (&gr)[8], const uint32_t (&ur)[8], int c0, float wj) {
-                    #pragma unroll
-                    for (int j = 0; j < 8; ++j)
-                    {
-                        const int p = c0 + j;
-                        const float w = __shfl_sync(0xffffffffu, wj, j);
-                        if (p < n)
+                auto read_out = [&](auto aq_tag) {
+                    constexpr bool AQ = decltype(aq_tag)::value;
+                    auto emit = [&](const uint32_t (&gr)[8], const uint32_t (&ur)[8], int c0) {
+                        const int rel = c0 - cbeg, wi = rel >> 5, lb = rel & 31;
+                        const float wsel = wi == 0 ? wv[0] : wi == 1 ? wv[1] : wi == 2 ? wv[2] : wv[3];
+                        float ws[8];
+                        #pragma unroll
+                        for (int j = 0; j < 8; ++j) ws[j] = __shfl_sync(0xffffffffu, wsel, lb + j);
+                        #pragma unroll
+                        for (int j = 0; j < 8; ++j)
                         {
+                            const int p = c0 + j;
+                            const float w = ws[j];
                             const float gg = __uint_as_float(gr[j]) * sc0, uu = __uint_as_float(ur[j]) * sc1;
-                            if (a.act_quant)
+                            if (AQ)
                             {
                                 float v = gg / (1.f + expf(-gg)) * uu * w;
                                 // second int8 round trip of the CPU engine: 32 consecutive channels = this warp
@@ -588,70 +633,92 @@ __global__ void __launch_bounds__(pf_threads(NMAT), 1) prefill_gemm_kernel(const
                                 const float sq8 = m > 0.f ? __fdiv_rn(m, 127.f) : 1.f;
                                 v = __fmul_rn((float) __float2int_rn(__fmul_rn(v, __fdiv_rn(1.f, sq8))), sq8);
                                 // code x scale does not fit fp16: keep it as hi + lo halves, the down GEMM walks both
-                                const __half hi = __float2half_rn(v);
-                                a.act[(size_t) (pos0 + p) * (2 * a.N) + chp] = hi;
-                                a.act[(size_t) (pos0 + p) * (2 * a.N) + a.N + chp] = __float2half_rn(v - __half2float(hi));
+                                const __half hi = __float2half_rn(v), lo = __float2half_rn(v - __half2float(hi));
+                                __half* dst = a.act + (size_t) (pos0 + p) * (2 * a.N) + chp;
+                                if (p < n) { dst[0] = hi; dst[a.N] = lo; }
                             }
                             else
                             {
                                 // fp16 result: the fast exponential and division are far inside its rounding (the reference's
                                 // kernels make the same choice, runtime/tier/moe4/moe4t.cu:404-425 built with fast-math)
-                                const float v = __fdividef(gg, 1.f + __expf(-gg)) * uu * w;
-                                a.act[(size_t) (pos0 + p) * a.N + chp] = __float2half_rn(v);
+                                const __half v = __float2half_rn(__fdividef(gg, 1.f + __expf(-gg)) * uu * w);
+                                if (p < n) a.act[(size_t) (pos0 + p) * a.N + chp] = v;
                             }
+                        }
+                    };
+                    if (cbeg < cend) { tmem_ld8(tacc + cbeg, g0); tmem_ld8(tacc + 256 + cbeg, u0); }
+                    for (int c0 = cbeg; c0 < cend; c0 += 16)
+                    {
+                        tmem_ld_wait();
+                        if (c0 + 8 < cend) { tmem_ld8(tacc + c0 + 8, g1); tmem_ld8(tacc + 256 + c0 + 8, u1); }
+                        emit(g0, u0, c0);
+                        if (c0 + 8 < cend)
+                        {
+                            tmem_ld_wait();
+                            if (c0 + 16 < cend) { tmem_ld8(tacc + c0 + 16, g0); tmem_ld8(tacc + 256 + c0 + 16, u0); }
+                            emit(g1, u1, c0 + 8);
                         }
                     }
                 };
-                auto weight_of = [&](int c0) { const int pj = c0 + (lane & 7); return pj < n ? __ldg(a.wt + pos0 + pj) : 0.f; };   // lane j: pick c0 + j
-                if (cbeg < cend) { tmem_ld8(tacc + cbeg, g0); tmem_ld8(tacc + 256 + cbeg, u0); }
-                for (int c0 = cbeg; c0 < cend; c0 += 16)
-                {
-                    const float wa = weight_of(c0), wb = weight_of(c0 + 8);
-                    tmem_ld_wait();
-                    if (c0 + 8 < cend) { tmem_ld8(tacc + c0 + 8, g1); tmem_ld8(tacc + 256 + c0 + 8, u1); }
-                    emit(g0, u0, c0, wa);
-                    if (c0 + 8 < cend)
-                    {
-                        tmem_ld_wait();
-                        if (c0 + 16 < cend) { tmem_ld8(tacc + c0 + 16, g0); tmem_ld8(tacc + 256 + c0 + 16, u0); }
-                        emit(g1, u1, c0 + 8, wb);
-                    }
-                }
+                if (a.act_quant) read_out(std::true_type()); else read_out(std::false_type());
             }
             else
-            for (int c0 = cbeg; c0 < cend; c0 += 16)
             {
-                uint32_t r0[16];
-                tmem_ld16(tacc + c0, r0);
-                // the picks' tokens: lane j of the first 16 loads pick c0 + j, handed out by shuffles
-                const int pj = c0 + (lane & 15);
-                int tj = 0;
-                if (pj < n) tj = __ldg(a.tok + pos0 + pj);
-                tmem_ld_wait();
-                #pragma unroll
-                for (int j = 0; j < 16; ++j)
-                {
-                    const int p = c0 + j;
-                    const int tk = __shfl_sync(0xffffffffu, tj, j);
-                    if (p < n)
-                    {
-                        const float v = __uint_as_float(r0[j]) * sc0;
-                        if (a.rows_per_rank)
+                // Sixteen columns at a time, two register sets in turn: the tensor-memory load of the next sixteen columns is in
+                // flight while the current sixteen go out as reductions. No branch per column here either: the padding columns
+                // add 0 to the row of the block's last pick.
+                uint32_t r0[16], r1[16];
+                auto read_out = [&](auto peer_tag) {
+                    constexpr bool PEER = decltype(peer_tag)::value;
+                    auto emit = [&](const uint32_t (&r)[16], int c0, int tj) {
+                        int tks[16];
+                        #pragma unroll
+                        for (int j = 0; j < 16; ++j) tks[j] = __shfl_sync(0xffffffffu, tj, j);
+                        #pragma unroll
+                        for (int j = 0; j < 16; ++j)
                         {
-                            // the row's owner may be another GPU, and up to eight GPUs add into the same addresses: the
-                            // reduction has to be atomic at system scope (a gpu-scope one is only atomic among this GPU's threads)
-                            const int pr = tk / a.rows_per_rank;
-                            red_add_sys(a.out_peer[pr] + (size_t) (tk - pr * a.rows_per_rank) * a.N + ch, v);
+                            const int tk = tks[j];
+                            const float v = c0 + j < n ? __uint_as_float(r[j]) * sc0 : 0.f;
+                            if (PEER)
+                            {
+                                // the row's owner may be another GPU, and up to eight GPUs add into the same addresses: the
+                                // reduction has to be atomic at system scope (a gpu-scope one is only atomic among this GPU's threads)
+                                const int pr = tk / a.rows_per_rank;
+                                red_add_sys(a.out_peer[pr] + (size_t) (tk - pr * a.rows_per_rank) * a.N + ch, v);
+                            }
+                            else atomicAdd(a.out + (size_t) tk * a.N + ch, v);
                         }
-                        else atomicAdd(a.out + (size_t) tk * a.N + ch, v);
+                    };
+                    // lane j (and j + 16) fetches the token of pick c0 + j while the tensor-memory load is in flight
+                    auto token_of = [&](int c0) { return __ldg(a.tok + pos0 + min(c0 + (lane & 15), n - 1)); };
+                    if (cbeg < cend) tmem_ld16(tacc + cbeg, r0);
+                    for (int c0 = cbeg; c0 < cend; c0 += 32)
+                    {
+                        const int ta = token_of(c0), tb = token_of(c0 + 16);
+                        tmem_ld_wait();
+                        if (c0 + 16 < cend) tmem_ld16(tacc + c0 + 16, r1);
+                        emit(r0, c0, ta);
+                        if (c0 + 16 < cend)
+                        {
+                            tmem_ld_wait();
+                            if (c0 + 32 < cend) tmem_ld16(tacc + c0 + 32, r0);
+                            emit(r1, c0 + 16, tb);
+                        }
                     }
-                }
+                };
+                if (a.rows_per_rank) read_out(std::true_type()); else read_out(std::false_type());
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tmem_free + acc * 8);
+            if (PROBE_ON(threadIdx.x == (NDQ + 2) * 32)) PROBE_ADD(8);
         }
     }
+#ifdef HMOE_PROBE_WAITS
+    if (threadIdx.x == 0) PROBE_ADD(15);
+    #pragma unroll
+    for (int i = 0; i < 16; ++i) if (pacc_[i]) atomicAdd(&g_probe[(NMAT - 1) * 32 + i], pacc_[i]);
+#endif
     tc_fence_before();
     __syncthreads();
     if (warp == NDQ + 1)
@@ -876,3 +943,13 @@ int prefill_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_
 }
 
 }  // namespace hmoe
+
+#ifdef HMOE_PROBE_WAITS
+extern "C" int hmoe_probe_read(unsigned long long* out, int clear)
+{
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, hmoe::g_probe, sizeof(unsigned long long) * 64);
+    if (clear) { unsigned long long z[64] = {}; cudaMemcpyToSymbol(hmoe::g_probe, z, sizeof(z)); }
+    return 0;
+}
+#endif
