@@ -12,10 +12,10 @@
 // row block (<= 256, one expert) the N operand, fp32 accumulators in tensor memory. Per 64-column stage:
 //   warps 0-15 read the packed codes of the tile straight from global memory (16 bytes per lane, the stored fragment order),
 //              turn them into fp16 (times the bf16 group scale in the group format) and store them as a K-major,
-//              128-byte-swizzled operand tile (4-byte stores, conflict free); they do nothing else and run ahead of the MMAs
+//              128-byte-swizzled operand tile (16-byte stores, conflict free); they do nothing else and run ahead of the MMAs
 //              from tile to tile as far as the ring allows;
-//   warp 16    one thread loads the row block's 256 x 64 input tile with one 2-D TMA copy (128-byte swizzle, rows beyond the
-//              array zero-filled);
+//   warp 16    one thread loads the row block's input tile (picks x 64 columns) as 2-D TMA boxes of 64 rows, as many as the block
+//              has picks (128-byte swizzle, rows beyond the array zero-filled);
 //   warp 17    one thread issues tcgen05.mma (M 128, N = picks rounded up to 16, K 16) four times per matrix and commits the
 //              stage back to the producers;
 //   warps 18-21 (down) / 18-25 (gate_up) read the finished sums out of tensor memory (one quarter of the lanes = 32 channels each;
@@ -52,6 +52,7 @@ __device__ unsigned long long g_probe[64];
 #define PROBE_ON(c) false
 #endif
 constexpr int TM = 128, TN = 256, TK = 64;
+constexpr int TB = 64;                          // rows per TMA box of the input tile
 constexpr int NDQ = 16;                         // dequantising warps
 // read-out warps: one per quarter of the tensor-memory lanes in down (whose read-out runs under the next tile's MMAs), two per
 // quarter in gate_up (whose single accumulator set keeps the tensor core waiting until the read-out is done: half the columns each)
@@ -442,7 +443,7 @@ __global__ void __launch_bounds__(pf_threads(NMAT), 1) prefill_gemm_kernel(const
                     store_strip(row_off + s * L::STAGE, c0, c1, cv);
                     fence_proxy_async();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(full_a + s * 8);
+                    mbar_arrive_if(full_a + s * 8, lane == 0);
                 }
                 continue;
             }
@@ -475,7 +476,7 @@ __global__ void __launch_bounds__(pf_threads(NMAT), 1) prefill_gemm_kernel(const
                     store_strip(row_off + s * L::STAGE, c0, c1, cv);
                     fence_proxy_async();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(full_a + s * 8);
+                    mbar_arrive_if(full_a + s * 8, lane == 0);
                     if (PROBE_ON(threadIdx.x == 0)) PROBE_ADD(9);
                     if (++s == (uint32_t) L::STAGES) { s = 0; ph ^= 1; }
                     return true;
@@ -513,13 +514,16 @@ __global__ void __launch_bounds__(pf_threads(NMAT), 1) prefill_gemm_kernel(const
             bool ok = true;
             for (int item = blockIdx.x; item < nitems && ok; item += gridDim.x, ++tile_n)
             {
-                const int pos0 = a.rbt[4 * (item / NCT) + 1];
+                const int pos0 = a.rbt[4 * (item / NCT) + 1], n = a.rbt[4 * (item / NCT) + 2];
+                // boxes of 64 rows: a row block with few picks brings in only the rows the MMA reads (n rounded up to 16 <= 64 nb)
+                const int nb = (n + 63) >> 6;
                 for (int kb = 0; kb < KBT; ++kb)
                 {
                     const uint32_t it = tile_n * (uint32_t) KBT + kb, s = it % L::STAGES;
                     { PROBE_T0(); const bool w_ = it < (uint32_t) L::STAGES || mbar_wait(empty + s * 8, ((it / L::STAGES) - 1) & 1, abort_flag, a.status); PROBE_ADD(6); if (!w_) { ok = false; break; } }
-                    mbar_expect_tx(full_b + s * 8, L::B_BYTES);
-                    tma_load_2d(sbase + s * L::STAGE + NMAT * L::A_BYTES, &tmap, kb * 64, pos0, full_b + s * 8);
+                    mbar_expect_tx(full_b + s * 8, (uint32_t) nb * (TB * TK * 2));
+                    for (int b = 0; b < nb; ++b)
+                        tma_load_2d(sbase + s * L::STAGE + NMAT * L::A_BYTES + b * (TB * TK * 2), &tmap, kb * 64, pos0 + b * TB, full_b + s * 8);
                 }
             }
         }
@@ -710,7 +714,7 @@ __global__ void __launch_bounds__(pf_threads(NMAT), 1) prefill_gemm_kernel(const
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(tmem_free + acc * 8);
+            mbar_arrive_if(tmem_free + acc * 8, lane == 0);
             if (PROBE_ON(threadIdx.x == (NDQ + 2) * 32)) PROBE_ADD(8);
         }
     }
@@ -742,14 +746,14 @@ encode_fn_t encode_fn()
     return f;
 }
 
-// row-major fp16 [rows][K] in tiles of 64 columns x 256 rows, 128-byte swizzle
+// row-major fp16 [rows][K] in boxes of 64 columns x 64 rows, 128-byte swizzle
 bool make_map(CUtensorMap* m, const void* ptr, int K, size_t rows)
 {
     encode_fn_t f = encode_fn();
     if (!f) return false;
     cuuint64_t dims[2] = {(cuuint64_t) K, (cuuint64_t) rows};
     cuuint64_t strides[1] = {(cuuint64_t) K * 2};
-    cuuint32_t box[2] = {TK, TN}, es[2] = {1, 1};
+    cuuint32_t box[2] = {TK, TB}, es[2] = {1, 1};
     return f(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*) ptr, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
