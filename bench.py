@@ -374,6 +374,28 @@ def decode_arm(args, dev, layer, torch, moe, synth, O):
     ms_q = timed(torch, run_q, steps, NBATCH)
     aq[0] = False
 
+    # smaller batches through the same call (1 row = the reference's single-token decode step): latency per layer call and the
+    # share of the HBM rate its algorithmic bytes reach
+    small = {}
+    for r in (1, 2, 4, 8):
+        xr = [x[:r].contiguous() for x in xs]
+        sel_r, rw_r = sel[:r].clone(), rw[:r].clone()
+        y_r, f_r = torch.zeros(r, H, dtype=torch.float32, device=dev), torch.zeros(r, H, dtype=torch.float32, device=dev)
+
+        def step_r(x):
+            moe.router_decode(tabs, x, wt, bias, sel_r, rw_r, 1.0, y_r, ws)
+            moe.moe4_combine(f_r, 0, y_r, r, 0)
+        d_r = []
+        for b in range(NBATCH):
+            step_r(xr[b]); d_r.append(int(torch.unique(sel_r).numel()))
+        run_r, _ = make_graphed(step_r, xr, torch, moe, not args.no_graph)
+        for i in range(3):
+            run_r(i % NBATCH)
+        ms_r = timed(torch, run_r, max(8, min(steps, 64)), NBATCH)
+        bytes_r = (float(np.mean(d_r)) + 1) * EXPERT_BYTES + n_exp * H * 2 + r * H * 6
+        small[str(r)] = {"us_per_layer": ms_r * 1e3, "distinct_experts": float(np.mean(d_r)),
+                         "layer_hbm_frac": bytes_r / (ms_r * 1e-3) / 1e9 / peaks()["hbm"]}
+
     # parity on this very layer, outside the timed regions: the router's selection bit for bit, two rows of batch 0 in both modes
     parity = {}
     if O is not None:
@@ -409,6 +431,7 @@ def decode_arm(args, dev, layer, torch, moe, synth, O):
         "e2e": {"value": ROWS / e2e_s, "unit": UNIT, "h2d_bytes_per_step": ROWS * H * 2, "d2h_bytes_per_step": ROWS * H * 4,
                 "us_per_layer": e2e_s * 1e6},
         "act_quant": {"decode_us_per_layer": ms_q * 1e3, "decode_vs_default": ms_q / ms_per_step},
+        "small_batches": small,
         "parity_check": {"decode": parity},
         "gpu_launches": int(launches), "device_status": int(status), "clocks": cs.summary(),
     }
@@ -820,8 +843,9 @@ def ep_prefill_arm(args, world, rank, dev, tabs, R, zipf, torch, dist, ep, moe, 
     """R tokens in total, split over the ranks; uniform or Zipf routing. Placement: contiguous ids for uniform routing; under
     skew the experts are dealt to the GPUs by load (hecate_b200.placement.balance) from the pick counts of ANOTHER sample of the
     same popularity (the routing log of an earlier chunk), and the selection is expressed in router positions, as a router with
-    permuted weight rows would emit it. Both combines (NCCL reduce-scatter, fused into the down GEMM over peer memory) are timed
-    and cross-checked; the line reports the faster."""
+    permuted weight rows would emit it. Both dispatches (NCCL all-gather; all-to-all-v over NVLink peer memory, a row only to the
+    ranks that hold one of its experts) and both combines (NCCL reduce-scatter; fused into the down GEMM over peer memory) are
+    timed and cross-checked; the line reports the fastest pair and names it."""
     rpr = R // world
     steps, warmup = max(1, min(args.steps, 20)), max(3, min(args.warmup, 5))
     sel_all, rw_all = synth.zipf_routing(10, 0, R, E, TOPK, zipf)
@@ -838,12 +862,16 @@ def ep_prefill_arm(args, world, rank, dev, tabs, R, zipf, torch, dist, ep, moe, 
     out = torch.empty(rpr, H, dtype=torch.float32, device=dev)
     times, outs = {}, {}
     st_all = launches = 0
-    for mode in ("nccl", "peer"):
-        p = ep.EpPrefill(rank, world, tabs, E, rpr, dev, dist, use_peer=(mode == "peer"))
+    sent_rows = 0
+    for mode in ("nccl", "peer", "a2a+nccl", "a2a+peer"):            # [dispatch +] combine
+        a2a = mode.startswith("a2a")
+        p = ep.EpPrefill(rank, world, tabs, E, rpr, dev, dist, use_peer=mode.endswith("peer"), dispatch="peer" if a2a else "nccl")
         for _ in range(warmup):
             p.step(x, sel, rw, out)
         torch.cuda.synchronize(); dist.barrier()
         outs[mode] = out[::256].clone()
+        if a2a:
+            sent_rows = int(p.sent.item()) // warmup
         l0 = moe.launch_count()
         with ClockSampler(dev.index) as cs:
             dist.barrier()
@@ -858,9 +886,13 @@ def ep_prefill_arm(args, world, rank, dev, tabs, R, zipf, torch, dist, ep, moe, 
         if p.peer is not None:
             dist.barrier(); p.peer.close()
         del p
-    best = min(times, key=times.get)               # both arms are timed; the line reports the faster one and names it
+    best = min(times, key=times.get)               # all arms are timed; the line reports the fastest one and names it
     e = torch.tensor(list(errors(outs["peer"].cpu().numpy(), outs["nccl"].cpu().numpy())), device=dev, dtype=torch.float64)
     dist.all_reduce(e, op=dist.ReduceOp.MAX)
+    e2 = torch.tensor(list(errors(outs["a2a+peer"].cpu().numpy(), outs["nccl"].cpu().numpy())), device=dev, dtype=torch.float64)
+    dist.all_reduce(e2, op=dist.ReduceOp.MAX)
+    sr = torch.tensor([sent_rows], device=dev); dist.all_reduce(sr, op=dist.ReduceOp.MAX)
+    sent_rows = int(sr.item())
     picks = np.array([int(((sel_all >= r * pl["n_local"]) & (sel_all < (r + 1) * pl["n_local"])).sum()) for r in range(world)])
     if rank != 0:
         return None
@@ -872,17 +904,24 @@ def ep_prefill_arm(args, world, rank, dev, tabs, R, zipf, torch, dist, ep, moe, 
         "ms_per_step": t * 1e3, "dtype": "int4 -> fp16 x fp16 -> fp32 (tcgen05)",
         "config": {"workload": f"prefill M={R} tokens over {world} GPUs ({rpr} each), Zipf({zipf}) top-8 over {E} experts + shared, "
                                f"{pl['n_local']} experts per GPU ({'placed by load from a calibration sample' if use_plan else 'contiguous ids'}), "
-                               f"all-gather dispatch (NCCL), combine: " + ("fused into the down GEMM over NVLink peer memory" if best == "peer" else "NCCL reduce-scatter"),
+                               + ("dispatch: all-to-all-v over NVLink peer memory" if best.startswith("a2a") else "dispatch: all-gather (NCCL)")
+                               + ", combine: " + ("fused into the down GEMM over NVLink peer memory" if best.endswith("peer") else "NCCL reduce-scatter"),
                    "l2": "inputs larger than L2"},
         "tokens_per_s": R / t, "nccl_reduce_scatter_ms_per_step": times["nccl"], "peer_combine_ms_per_step": times["peer"],
-        "dispatch_bytes_per_rank": (world - 1) * rpr * (H * 2 + TOPK * 10), "combine_bytes_per_rank": (world - 1) * rpr * H * 4,
+        "peer_dispatch_nccl_combine_ms_per_step": times["a2a+nccl"], "peer_dispatch_peer_combine_ms_per_step": times["a2a+peer"],
+        "dispatch_bytes_per_rank": (world - 1) * rpr * (H * 2 + TOPK * 10) if not best.startswith("a2a") else sent_rows * H * 2 + (world - 1) * rpr * TOPK * 10,
+        "dispatch_bytes_per_rank_all_gather": (world - 1) * rpr * (H * 2 + TOPK * 10),
+        "dispatch_bytes_per_rank_all_to_all_v": sent_rows * H * 2 + (world - 1) * rpr * TOPK * 10,
+        "combine_bytes_per_rank": (world - 1) * rpr * H * 4,
         "picks_per_rank": picks.tolist(), "load_imbalance_max_over_mean": float(picks.max() / picks.mean()),
         "load_imbalance_contiguous_placement": base_imb,
         "roofline": {"bound": "tensor", "kernel": "whole step incl. collectives", "achieved": flop / t / 1e12, "peak": pk["bf16"] * world, "unit": "TFLOP/s",
                      "frac": flop / t / 1e12 / (pk["bf16"] * world), "peak_kind": pk["kind"] + " burst (bf16_tflops) x n_gpus",
                      "frac_sustained": flop / t / 1e12 / (pk["bf16_sustained"] * world), "traffic": None},
         "parity_check": {"peer_combine_vs_nccl_reduce_scatter": {"max_rel": float(e[0]), "mean_abs": float(e[1]), "norm_rel": float(e[2]),
-                                                                 "ok": bool(float(e[2]) < 1e-5)}},
+                                                                 "ok": bool(float(e[2]) < 1e-5)},
+                         "peer_dispatch_and_combine_vs_nccl": {"max_rel": float(e2[0]), "mean_abs": float(e2[1]), "norm_rel": float(e2[2]),
+                                                               "ok": bool(float(e2[2]) < 1e-5)}},
         "gpu_launches": int(launches), "device_status": int(st_all), "clocks": cs.summary()}
 
 

@@ -147,6 +147,67 @@ __global__ void __launch_bounds__(DISPATCH_THREADS) ep_dispatch_kernel(const Sta
     }
 }
 
+// Prefill dispatch as an all-to-all-v over peer memory: one warp per row of the rank's slice. The row goes, at its global position,
+// into the staging area of every rank that holds one of its selected experts (position e belongs to rank e / n_per_rank) and into
+// the rank's own (the shared expert runs where the row lives); the selections and weights go to every rank (a row costs 80 bytes
+// there, 12 KB here). A rank that does not need a row keeps whatever its staging area held at that position and never reads it:
+// its permutation only lists rows with a local expert. The flag barrier that follows (ep_barrier_kernel, next launch of the stream)
+// publishes the stores.
+struct PrefillStage
+{
+    size_t sel, rw, total;          // x at 0: [R][H] 16-bit; sel int64 [R][topk]; rw 16-bit [R][topk]
+    __host__ __device__ PrefillStage(int R, int H, int topk)
+    {
+        sel = ((size_t) R * H * 2 + 255) / 256 * 256;
+        rw = sel + ((size_t) R * topk * 8 + 255) / 256 * 256;
+        total = rw + ((size_t) R * topk * 2 + 255) / 256 * 256;
+    }
+};
+
+__global__ void __launch_bounds__(256) prefill_dispatch_kernel(const StageArgs a, const uint4* __restrict__ x_own, const int64_t* __restrict__ sel_own,
+                                                               const uint16_t* __restrict__ rw_own, int rpr, int H, int topk, int n_per_rank,
+                                                               unsigned long long* __restrict__ sent_rows)
+{
+    const PrefillStage L(rpr * a.world, H, topk);
+    const int lane = threadIdx.x & 31, warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
+    const int words = H / 8;
+    unsigned long long sent = 0;
+    for (int row = warp; row < rpr; row += nwarps)
+    {
+        const size_t grow = (size_t) a.rank * rpr + row;
+        unsigned m = 0;
+        if (lane < topk)
+        {
+            const int64_t e = sel_own[(size_t) row * topk + lane];
+            const uint16_t w = rw_own[(size_t) row * topk + lane];
+            if (e >= 0 && e < (int64_t) a.world * n_per_rank) m = 1u << (int) (e / n_per_rank);
+            for (int p = 0; p < a.world; ++p)
+            {
+                ((int64_t*) (a.stage[p] + L.sel))[grow * topk + lane] = e;
+                ((uint16_t*) (a.stage[p] + L.rw))[grow * topk + lane] = w;
+            }
+        }
+        m = __reduce_or_sync(0xffffffffu, m) | (1u << a.rank);
+        sent += __popc(m & ~(1u << a.rank));
+        const uint4* src = x_own + (size_t) row * words;
+        constexpr int U = 4;                       // a lane's loads of a pass are issued before its first store
+        for (int c0 = lane; c0 < words; c0 += 32 * U)
+        {
+            uint4 v[U];
+            #pragma unroll
+            for (int u = 0; u < U; ++u) if (c0 + 32 * u < words) v[u] = src[c0 + 32 * u];
+            for (int p = 0; p < a.world; ++p)
+            {
+                if (!((m >> p) & 1u)) continue;
+                uint4* dst = (uint4*) a.stage[p] + grow * words;
+                #pragma unroll
+                for (int u = 0; u < U; ++u) if (c0 + 32 * u < words) dst[c0 + 32 * u] = v[u];
+            }
+        }
+    }
+    if (sent_rows && lane == 0 && sent) atomicAdd(sent_rows, sent);
+}
+
 // Barrier over the ranks through the same flags: raise generation `gen` in every peer's memory, wait (bounded) until every
 // peer has raised it here. What a rank wrote into peer memory before this kernel (in stream order) is complete when the
 // peers pass the barrier: the flag is stored with release semantics at system scope after a system-wide fence.
@@ -206,6 +267,25 @@ int ep_combine_launch(int rank, int world, void* const* slots, void* const* flag
     const int blocks = (n / 4 + 255) / 256 < 96 ? (n / 4 + 255) / 256 : 96;
     if (H % 4) return fail(HMOE_E_ARG, "hmoe_ep_combine: H must be a multiple of 4");
     ep_combine_kernel<<<blocks, 256, 0, st>>>(a, gen, f, n, slot_floats, status, own_rows, H);
+    count_launches(1);
+    const cudaError_t err = cudaGetLastError();
+    return err == cudaSuccess ? HMOE_OK : fail(HMOE_E_CUDA, cudaGetErrorString(err));
+}
+
+size_t prefill_stage_bytes(int R, int H, int topk) { return PrefillStage(R, H, topk).total; }
+void prefill_stage_offsets(int R, int H, int topk, size_t* sel_off, size_t* rw_off) { const PrefillStage L(R, H, topk); *sel_off = L.sel; *rw_off = L.rw; }
+
+int prefill_dispatch_launch(int rank, int world, void* const* stage, const void* x_own, const int64_t* sel_own, const void* rw_own, int rpr, int H,
+                            int topk, int n_per_rank, unsigned long long* sent_rows, cudaStream_t st)
+{
+    if (world < 1 || world > 8 || rank < 0 || rank >= world) return fail(HMOE_E_ARG, "hmoe_prefill_ep_dispatch: world must be 1..8");
+    if (!stage || !x_own || !sel_own || !rw_own || rpr < 1 || H % 8 || topk < 1 || topk > 32 || n_per_rank < 1)
+        return fail(HMOE_E_ARG, "hmoe_prefill_ep_dispatch: arguments");
+    StageArgs a;
+    a.rank = rank; a.world = world;
+    for (int p = 0; p < 8; ++p) a.stage[p] = p < world ? (char*) stage[p] : nullptr;
+    const int blocks = 2 * device_sms();
+    prefill_dispatch_kernel<<<blocks, 256, 0, st>>>(a, (const uint4*) x_own, sel_own, (const uint16_t*) rw_own, rpr, H, topk, n_per_rank, sent_rows);
     count_launches(1);
     const cudaError_t err = cudaGetLastError();
     return err == cudaSuccess ? HMOE_OK : fail(HMOE_E_CUDA, cudaGetErrorString(err));
@@ -292,6 +372,19 @@ int hmoe_ep_copy(void* dst, const void* src, size_t bytes, void* stream)
 int hmoe_ep_barrier(int rank, int world, void* const* flags, uint32_t gen, uint32_t* status, void* stream)
 {
     return ep_barrier_launch(rank, world, flags, gen, status, (cudaStream_t) stream);
+}
+
+size_t hmoe_prefill_ep_stage_bytes(int rows_total, int H, int topk) { return prefill_stage_bytes(rows_total, H, topk); }
+int hmoe_prefill_ep_stage_offsets(int rows_total, int H, int topk, size_t* sel_off, size_t* rw_off)
+{
+    if (!sel_off || !rw_off) return fail(HMOE_E_ARG, "hmoe_prefill_ep_stage_offsets: null pointer");
+    prefill_stage_offsets(rows_total, H, topk, sel_off, rw_off);
+    return HMOE_OK;
+}
+int hmoe_prefill_ep_dispatch(int rank, int world, void* const* stage, const void* x_own, const int64_t* sel_own, const void* rw_own, int rows_per_rank,
+                             int H, int topk, int n_per_rank, unsigned long long* sent_rows, void* stream)
+{
+    return prefill_dispatch_launch(rank, world, stage, x_own, sel_own, rw_own, rows_per_rank, H, topk, n_per_rank, sent_rows, (cudaStream_t) stream);
 }
 
 }  // extern "C"

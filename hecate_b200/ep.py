@@ -29,7 +29,7 @@ class PeerBuffers:
     """Symmetric buffers of the combine: per rank two fp32 partial slots [MAX_ROWS * H] and `world` generation flags,
     allocated with cudaMalloc by the library, exported with CUDA IPC and opened by every peer."""
 
-    def __init__(self, rank, world, H, device, dist, slot_floats=None, stage_topk=0):
+    def __init__(self, rank, world, H, device, dist, slot_floats=None, stage_topk=0, prefill_stage=None):
         import torch
         self.rank, self.world, self.H = rank, world, H
         self.slot_floats = MAX_ROWS * H if slot_floats is None else (slot_floats + 63) // 64 * 64
@@ -37,6 +37,10 @@ class PeerBuffers:
         self.stage_off = self.bytes                          # optional: the staging area of the decode dispatch
         if stage_topk:
             self.bytes += lib().hmoe_ep_stage_bytes(C.c_int(H), C.c_int(stage_topk))
+        if prefill_stage:                                    # (rows of all ranks, topk): the staging area of the prefill dispatch
+            self.bytes = (self.bytes + 255) // 256 * 256
+            self.pstage_off = self.bytes
+            self.bytes += lib().hmoe_prefill_ep_stage_bytes(C.c_int(prefill_stage[0]), C.c_int(H), C.c_int(prefill_stage[1]))
         p = C.c_void_p()
         check(lib().hmoe_ep_alloc(C.c_size_t(self.bytes), C.byref(p)))
         self.own = p.value
@@ -61,6 +65,11 @@ class PeerBuffers:
             offs = [C.c_size_t() for _ in range(3)]
             check(lib().hmoe_ep_stage_offsets(C.c_int(H), C.c_int(stage_topk), *[C.byref(o) for o in offs]))
             self.stage_x, self.stage_sel, self.stage_rw = (self.own + self.stage_off + o.value for o in offs)
+        if prefill_stage:
+            self.pstage = (C.c_void_p * world)(*[b + self.pstage_off for b in self.base])
+            so, ro = C.c_size_t(), C.c_size_t()
+            check(lib().hmoe_prefill_ep_stage_offsets(C.c_int(prefill_stage[0]), C.c_int(H), C.c_int(prefill_stage[1]), C.byref(so), C.byref(ro)))
+            self.pstage_x, self.pstage_sel, self.pstage_rw = self.own + self.pstage_off, self.own + self.pstage_off + so.value, self.own + self.pstage_off + ro.value
         dist.barrier()
 
     def close(self):
@@ -186,14 +195,16 @@ class EpDecoder:
 
 
 class EpPrefill:
-    """Expert-parallel prefill. Dispatch: the ranks' token slices are all-gathered (NCCL); every rank runs the grouped GEMMs
-    for its experts over all tokens (ids outside [lo, lo + n_local) are dropped by the permutation) plus the shared expert
-    for its own tokens. Combine, use_peer = True: the down GEMM adds every row's sums straight into the output of the rank
+    """Expert-parallel prefill. Dispatch: the ranks' token slices are all-gathered (NCCL), or, dispatch="peer", sent as an
+    all-to-all-v over NVLink peer memory (hmoe_prefill_ep_dispatch: a row goes only to the ranks that hold one of its experts);
+    every rank runs the grouped GEMMs for its experts over all tokens (ids outside [lo, lo + n_local) are dropped by the
+    permutation) plus the shared expert for its own tokens. Combine, use_peer = True: the down GEMM adds every row's sums straight into the output of the rank
     that owns the row, over NVLink peer memory, and a flag barrier ends the step. use_peer = False (the baseline): a local
     full-size partial and an NCCL reduce-scatter."""
 
-    def __init__(self, rank, world, tables, n_experts, rows_per_rank, device, dist, use_peer=None):
+    def __init__(self, rank, world, tables, n_experts, rows_per_rank, device, dist, use_peer=None, dispatch="nccl"):
         import torch
+        assert dispatch in ("nccl", "peer")
         if use_peer is None:
             # measured at 2 GPUs (32768 rows): the fused combine is 5 % slower than the reduce-scatter it replaces, because every
             # pick of a remote token crosses the link (up to 8 per token) where the reduce-scatter sends one sum per token; the
@@ -204,18 +215,23 @@ class EpPrefill:
         R = rows_per_rank * world
         self.R = R
         self.ws = moe.prefill_workspace(R, tables.topk, tables.n, tables.H, tables.I, device)
-        self.x_all = torch.empty(R, tables.H, dtype=torch.bfloat16, device=device)
-        self.sel_all = torch.empty(R, tables.topk, dtype=torch.int64, device=device)
-        self.rw_all = torch.empty(R, tables.topk, dtype=torch.float16, device=device)
+        if not (dispatch == "peer" and world > 1):
+            self.x_all = torch.empty(R, tables.H, dtype=torch.bfloat16, device=device)
+            self.sel_all = torch.empty(R, tables.topk, dtype=torch.int64, device=device)
+            self.rw_all = torch.empty(R, tables.topk, dtype=torch.float16, device=device)
         self.use_peer = use_peer and world > 1
+        self.peer_dispatch = dispatch == "peer" and world > 1
         self.struct = tables.struct()
         self.gen = 0
-        if self.use_peer:
-            # one slot of the symmetric buffer is this rank's output [rows_per_rank][H]; the flags serve the barrier
-            self.peer = PeerBuffers(rank, world, tables.H, device, dist, slot_floats=rows_per_rank * tables.H)
+        self.peer = None
+        if self.use_peer or self.peer_dispatch:
+            # one slot of the symmetric buffer is this rank's output [rows_per_rank][H]; the flags serve the barriers
+            self.peer = PeerBuffers(rank, world, tables.H, device, dist, slot_floats=rows_per_rank * tables.H if self.use_peer else 64,
+                                    prefill_stage=(R, tables.topk) if self.peer_dispatch else None)
             self.out_tab = (C.c_void_p * world)(*self.peer.base)
-        else:
-            self.peer = None
+        if self.peer_dispatch:
+            self.sent = torch.zeros(1, dtype=torch.int64, device=device)       # (row, remote rank) pairs stored so far
+        if not self.use_peer:
             self.partial = torch.empty(R, tables.H, dtype=torch.float32, device=device)
 
     def step(self, x, sel, rw, out):
@@ -227,13 +243,22 @@ class EpPrefill:
         if self.use_peer:
             # own output cleared before the step's first collective: when the all-gather returns on a peer, this rank has passed it
             check(lib().hmoe_ep_memset(C.c_void_p(self.peer.own), C.c_int(0), C.c_size_t(nbytes), st))
-        if self.world > 1:
-            d.all_gather_into_tensor(self.x_all, x); d.all_gather_into_tensor(self.sel_all, sel); d.all_gather_into_tensor(self.rw_all, rw)
+        if self.peer_dispatch:
+            # the previous step's readers are done: every rank passed the barrier / reduce-scatter that ended it
+            self.gen += 1
+            check(lib().hmoe_prefill_ep_dispatch(C.c_int(self.rank), C.c_int(self.world), self.peer.pstage, vp(x), vp(sel), vp(rw), C.c_int(self.rpr),
+                                                 C.c_int(self.tabs.H), C.c_int(self.tabs.topk), C.c_int(pl["n_local"]), vp(self.sent), st))
+            check(lib().hmoe_ep_barrier(C.c_int(self.rank), C.c_int(self.world), self.peer.flags, C.c_uint32(self.gen), vp(self.peer.status), st))
+            xa, sa, ra = C.c_void_p(self.peer.pstage_x), C.c_void_p(self.peer.pstage_sel), C.c_void_p(self.peer.pstage_rw)
         else:
-            self.x_all.copy_(x); self.sel_all.copy_(sel); self.rw_all.copy_(rw)
+            if self.world > 1:
+                d.all_gather_into_tensor(self.x_all, x); d.all_gather_into_tensor(self.sel_all, sel); d.all_gather_into_tensor(self.rw_all, rw)
+            else:
+                self.x_all.copy_(x); self.sel_all.copy_(sel); self.rw_all.copy_(rw)
+            xa, sa, ra = vp(self.x_all), vp(self.sel_all), vp(self.rw_all)
         if self.use_peer:
             self.gen += 1
-            check(lib().hmoe_prefill_ep_peer(C.byref(self.struct), vp(self.x_all), C.c_int(moe._dt(self.x_all)), vp(self.sel_all), vp(self.rw_all),
+            check(lib().hmoe_prefill_ep_peer(C.byref(self.struct), xa, C.c_int(moe._dt(x)), sa, ra,
                                              C.c_int(self.R), C.c_int(pl["lo"]), C.c_int(pl["n_local"]), C.c_int(0), self.out_tab,
                                              C.c_int(self.world), C.c_int(self.rpr), vp(self.ws), C.c_size_t(self.ws.numel()),
                                              C.c_int(self.rank * self.rpr), C.c_int(self.rpr), st))
@@ -241,7 +266,7 @@ class EpPrefill:
             check(lib().hmoe_ep_copy(vp(out), C.c_void_p(self.peer.own), C.c_size_t(nbytes), st))
             return out
         self.partial.zero_()
-        check(lib().hmoe_prefill_ep(C.byref(self.struct), vp(self.x_all), C.c_int(moe._dt(self.x_all)), vp(self.sel_all), vp(self.rw_all),
+        check(lib().hmoe_prefill_ep(C.byref(self.struct), xa, C.c_int(moe._dt(x)), sa, ra,
                                     C.c_int(self.R), C.c_int(pl["lo"]), C.c_int(pl["n_local"]), C.c_int(0), vp(self.partial), vp(self.ws),
                                     C.c_size_t(self.ws.numel()), C.c_int(self.rank * self.rpr), C.c_int(self.rpr), st))
         if self.world > 1:

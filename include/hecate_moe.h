@@ -191,6 +191,21 @@ int hmoe_prefill_ep_peer(const hmoe_layer* layer, const void* x, int x_dtype, co
                          int act_quant, void* const* out_peer, int world, int rows_per_rank, void* ws, size_t ws_bytes, int shared_row0,
                          int shared_rows, void* stream);
 int hmoe_ep_barrier(int rank, int world, void* const* flags, uint32_t gen, uint32_t* status, void* stream);
+/* Prefill dispatch as an all-to-all-v over NVLink peer memory (no reference counterpart; the mailbox of runtime/tier/moe4/moe4.cu:719-738
+ * is its template: payload stored into the consumer's memory, then a flag). Every rank holds rows_per_rank rows (rank r the global
+ * rows [r * rows_per_rank, (r + 1) * rows_per_rank)) and stores each of them, at its global position, into the staging area of every
+ * rank that holds one of the row's selected experts (router position e belongs to rank e / n_per_rank; ids outside
+ * [0, world * n_per_rank) select no rank) and into its own; selections and weights go to every rank. stage[p] = rank p's staging area
+ * as seen from this process (hmoe_prefill_ep_stage_bytes from hmoe_ep_alloc): x [R][H] 16-bit at offset 0, sel int64 [R][topk] and
+ * rw 16-bit [R][topk] at the offsets hmoe_prefill_ep_stage_offsets returns; these are then the x / sel / rw of hmoe_prefill_ep(_peer)
+ * with R = world * rows_per_rank. A rank never reads rows it was not sent: its permutation lists only rows with a local expert, and
+ * the shared expert is applied to the rank's own rows. Call hmoe_ep_barrier after it (it publishes the stores); the next step's
+ * dispatch may start once every rank has finished reading its staging area (e.g. after the barrier that ends the peer combine, or
+ * after the reduce-scatter). sent_rows (device counter, may be null) is increased by the number of (row, remote rank) pairs stored. */
+size_t hmoe_prefill_ep_stage_bytes(int rows_total, int H, int topk);
+int hmoe_prefill_ep_stage_offsets(int rows_total, int H, int topk, size_t* sel_off, size_t* rw_off);
+int hmoe_prefill_ep_dispatch(int rank, int world, void* const* stage, const void* x_own, const int64_t* sel_own, const void* rw_own, int rows_per_rank,
+                             int H, int topk, int n_per_rank, unsigned long long* sent_rows, void* stream);
 /* Stream-ordered memset / device-to-device copy for memory obtained from hmoe_ep_alloc (which the host language may have no
  * tensor for). */
 int hmoe_ep_memset(void* ptr, int value, size_t bytes, void* stream);

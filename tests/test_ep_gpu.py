@@ -215,6 +215,30 @@ def _prefill_rank_main(rank, world, port, out_path):
     assert ep.status() == 0
     gathered_placed = [torch.empty_like(out_p) for _ in range(world)]
     dist.all_gather(gathered_placed, out_p)
+    # Dispatch as an all-to-all-v over peer memory. A routing in which two rows of three select experts of their own rank only
+    # (the other rank's picks replaced by ids no rank holds): those rows must not travel, and the rank that does not get them
+    # must not read them. The first step sends every row everywhere with large values, which stay in the staging areas
+    # where the second step stores nothing.
+    sel_v = sel.copy()
+    owner = np.arange(R) // rpr
+    keep_home = (np.arange(R) % 3 != 0)[:, None] & (sel_v // p["n_local"] != owner[:, None])
+    sel_v[keep_home] = 1000
+    outs_v = {}
+    sent_ok = True
+    for use_peer in (False, True):
+        ep = EpPrefill(rank, world, local, E, rpr, dev, dist, use_peer=use_peer, dispatch="peer")
+        out_v = torch.empty(rpr, H, device=dev)
+        ep.step(torch.from_numpy(xa[sl] * 50).to(dev).to(torch.bfloat16), torch.from_numpy(sel[sl]).to(dev), torch.from_numpy(rw[sl]).to(dev), out_v)
+        s0 = int(ep.sent.item())
+        ep.step(torch.from_numpy(xa[sl]).to(dev).to(torch.bfloat16), torch.from_numpy(sel_v[sl]).to(dev), torch.from_numpy(rw[sl]).to(dev), out_v)
+        assert ep.status() == 0
+        want = int(((sel_v[sl] < E) & (sel_v[sl] // p["n_local"] != rank)).any(axis=1).sum())
+        sent_ok &= s0 == rpr * (world - 1) and int(ep.sent.item()) - s0 == want and want < rpr
+        outs_v[use_peer] = out_v
+    assert sent_ok
+    gathered_v = {k: [torch.empty_like(v) for _ in range(world)] for k, v in outs_v.items()}
+    for k in outs_v:
+        dist.all_gather(gathered_v[k], outs_v[k])
     gathered = [torch.empty_like(out) for _ in range(world)]
     dist.all_gather(gathered, outs[True])
     gathered_nccl = [torch.empty_like(out) for _ in range(world)]
@@ -225,8 +249,11 @@ def _prefill_rank_main(rank, world, port, out_path):
         ref = torch.zeros(R, H, device=dev)
         moe.prefill(full, torch.from_numpy(xa).to(dev).to(torch.bfloat16), torch.from_numpy(sel).to(dev), torch.from_numpy(rw).to(dev), ref, ws)
         got = torch.cat(gathered); got_nccl = torch.cat(gathered_nccl); got_placed = torch.cat(gathered_placed)
+        ref_v = torch.zeros(R, H, device=dev)
+        moe.prefill(full, torch.from_numpy(xa).to(dev).to(torch.bfloat16), torch.from_numpy(sel_v).to(dev), torch.from_numpy(rw).to(dev), ref_v, ws)
+        ev = [float((torch.cat(gathered_v[k]) - ref_v).norm() / ref_v.norm()) for k in (False, True)]
         np.save(out_path, np.array([float((got - ref).norm() / ref.norm()), float((got_nccl - ref).norm() / ref.norm()),
-                                    float((got_placed - ref).norm() / ref.norm())]))
+                                    float((got_placed - ref).norm() / ref.norm())] + ev))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -241,3 +268,4 @@ def test_two_gpu_prefill_matches_single_gpu(tmp_path):
     e = np.load(out)
     assert e[0] < 1e-3 and e[1] < 1e-3, e        # peer-memory combine, NCCL reduce-scatter combine
     assert e[2] < 1e-3, e                         # experts placed by load with copies: same result as contiguous ids
+    assert e[3] < 1e-3 and e[4] < 1e-3, e        # peer-memory all-to-all-v dispatch, with either combine
