@@ -273,6 +273,12 @@ int hmoe_decode_ep_dp(const hmoe_layer* layer, const void* x_own, int x_dtype, c
     PrepArgs pa;
     int rc = decode_prep_args(layer, x_all, x_dtype, R, lo, n_local, act_quant, ws, ws_bytes, world, rank, gen, &pa);
     if (rc) return rc;
+    if (world > 1 && E % world == 0 && n_local == 2 * (E / world))
+    {
+        // every expert on two ranks: this rank's tables hold the bands rank and rank + 1 (mod world) of E / world router positions
+        if (E > 256 || lo != rank * (E / world)) return fail(HMOE_E_ARG, "hmoe_decode_ep_dp: two bands per rank need lo = rank * E / world and E <= 256");
+        pa.n_total = E; pa.bal_world = world; pa.bal_rank = rank;
+    }
     DispArgs da;
     da.rank = rank; da.world = world; da.n_own = n_own; da.words = layer->H / 8; da.x_own = (const uint4*) x_own;
     da.x_off = SL.x; da.flags_off = SL.flags; da.ctl_off = SL.ctl;

@@ -375,7 +375,7 @@ __global__ void __launch_bounds__(RW * 32) router_logits_kernel(const uint16_t* 
     }
     if (anybad) return;
     build_route<true>(*(RouteSmem*) (rsm + RW * 512 * 4), sel, rw, R, H, pa.I, topk, pa.lo, pa.n_local, pa.has_shared, pa.sh_mod, pa.sh_rem,
-                      pa.gen_bump, pa.route, pa.nblocks, threadIdx.x);
+                      pa.gen_bump, pa.route, pa.nblocks, threadIdx.x, pa.n_total, pa.bal_world, pa.bal_rank);
 }
 
 __global__ void __launch_bounds__(256) router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int R, int E,

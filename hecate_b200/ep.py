@@ -25,6 +25,30 @@ def shard_plan(rank, world, n_experts):
     return dict(lo=rank * n_local, n_local=n_local, shared_mod=world, shared_rem=rank)
 
 
+def replica_owners(sel, n_experts, world):
+    """Host mirror of the device's choice with every expert on two ranks (EpDecoder(replicas=2)): rank r holds the bands r and r + 1
+    (mod world) of n_experts / world router positions, so position e of band p is held by ranks p and p - 1; the bands walk their
+    positions side by side and give each picked position to the holder with fewer experts so far (ties: rank p).
+    Returns {position: rank} for the picked positions of `sel` (any integer array)."""
+    import numpy as np
+    npr = n_experts // world
+    picked = np.zeros(n_experts, dtype=bool)
+    ids = np.asarray(sel).reshape(-1)
+    picked[ids[(ids >= 0) & (ids < n_experts)]] = True
+    load = [0] * world
+    owner = {}
+    for i in range(npr):
+        new = list(load)
+        for p in range(world):
+            if picked[p * npr + i]:
+                q = (p - 1) % world
+                o = q if load[q] < load[p] else p
+                owner[p * npr + i] = o
+                new[o] += 1
+        load = new
+    return owner
+
+
 class PeerBuffers:
     """Symmetric buffers of the combine: per rank two fp32 partial slots [MAX_ROWS * H] and `world` generation flags,
     allocated with cudaMalloc by the library, exported with CUDA IPC and opened by every peer."""
@@ -82,13 +106,20 @@ class PeerBuffers:
 class EpDecoder:
     """One rank's side of an expert-parallel decode layer."""
 
-    def __init__(self, rank, world, tables, n_experts, device, dist, use_peer=True, fused_tail=False):
+    def __init__(self, rank, world, tables, n_experts, device, dist, use_peer=True, fused_tail=False, replicas=1):
+        """replicas = 2: every expert is held by two ranks (the tables of rank r hold the bands r and r + 1 (mod world) of
+        n_experts / world router positions each, in this order) and every step gives each picked expert to the less loaded of its
+        two holders, the same choice on every rank (step_dp_fused only; twice the weight memory)."""
         self.rank, self.world, self.tabs, self.dev, self.dist = rank, world, tables, device, dist
+        assert replicas in (1, 2) and (replicas == 1 or world > 1)
+        self.replicas = replicas
         # fused_tail: the combine runs as the tail of the down launch (hmoe_decode_ep_combine) instead of as a kernel of its own;
         # it needs the register-resident decode kernels (H <= 6144, I <= 2048). Measured at 2 GPUs it is 2-3 us slower than the
         # separate kernel (148 blocks poll the flags instead of one thread), so it is off by default.
         self.fused_tail = fused_tail and tables.H <= 6144 and tables.I <= 2048
         self.plan = shard_plan(rank, world, n_experts)
+        if replicas == 2:
+            self.plan["n_local"] *= 2
         assert tables.n == self.plan["n_local"]
         self.ws = moe.decode_workspace(tables.H, tables.I, device)
         self.use_peer = use_peer and world > 1
@@ -101,6 +132,8 @@ class EpDecoder:
         """f[R][H] (fp32) += the layer's output for rows x with global routing (sel, rw); identical on every rank. The rows are
         replicated (every rank passes all of them)."""
         import torch
+        if self.replicas != 1:
+            raise RuntimeError("experts held by two ranks are served by step_dp_fused only")
         R = x.shape[0]
         st = C.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)
         pl = self.plan
@@ -141,8 +174,8 @@ class EpDecoder:
         the two halves of an all-to-all over NVLink peer memory (hmoe_ep_dispatch, hmoe_ep_combine_own). `tables`: another layer's
         experts through the same buffers (a stack of layers shares one set)."""
         import torch
-        if not self.use_peer:
-            raise RuntimeError("step_dp needs the peer-memory buffers")
+        if not self.use_peer or self.replicas != 1:
+            raise RuntimeError("step_dp needs the peer-memory buffers and one holder per expert")
         st = C.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)
         pl, pb = self.plan, self.peer
         struct = self.struct if tables is None else tables.struct()

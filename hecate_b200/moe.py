@@ -180,6 +180,14 @@ def ws_status(ws):
     return out.value
 
 
+def route_distinct(ws):
+    """Diagnostic: the number of distinct routed experts the last decode call on workspace `ws` served on this device (the first
+    word of the work list, which follows the 256-byte status block). Synchronises."""
+    import torch
+    torch.cuda.synchronize(ws.device)
+    return int(ws[256:260].view(torch.int32).item())
+
+
 # ----------------------------------------------------------------------------------------------------------------------
 # reference-named entry points
 

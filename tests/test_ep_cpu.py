@@ -23,6 +23,29 @@ def test_shard_plan_covers_everything_once():
         shard_plan(0, 3, 256)
 
 
+def test_replica_owners_serve_every_pick_once_and_level_the_load():
+    """Every expert on two ranks: each picked position gets one of its two holders, and the most loaded rank serves fewer experts
+    than under the one-holder split (averaged over routings; never more than one above the mean at 2 ranks)."""
+    from hecate_b200 import synth
+    from hecate_b200.ep import replica_owners
+    for world in (2, 4, 8):
+        npr = 256 // world
+        worst_one, worst_two = [], []
+        for seed in range(20):
+            sel, _ = synth.zipf_routing(seed, 0, 16, 256, 8, 0.0)
+            own = replica_owners(sel, 256, world)
+            ids = np.unique(sel)
+            assert sorted(own) == list(ids)
+            for e, r in own.items():
+                assert r in (e // npr, (e // npr - 1) % world)
+            load = np.bincount(list(own.values()), minlength=world)
+            worst_two.append(load.max()); worst_one.append(np.bincount(ids // npr, minlength=world).max())
+            if world == 2:
+                assert load.max() - load.min() <= 1
+        assert np.mean(worst_two) <= np.mean(worst_one) - (0 if world == 2 else 1.5)
+    assert replica_owners(np.array([[300, -1]]), 256, 4) == {}
+
+
 def _rank_main(rank, world, port, out_path):
     sys.path.insert(0, ROOT); sys.path.insert(0, os.path.join(ROOT, "tests"))
     import torch

@@ -107,6 +107,34 @@ def _rank_main(rank, world, port, out_path):
             dp_err = torch.maximum(dp_err, torch.tensor([float((f_own - f_all[own]).abs().max() / f_all.abs().max())], device=dev))
         assert dec.status() == 0
         dist.barrier(); dec.peer.close()
+    # Every expert on two ranks (at 2 ranks: both hold all of them, rank 1 in the order band 1, band 0): each step gives every
+    # picked expert to one of its holders by the same rule on both ranks, so the combined result is the single-GPU one and the
+    # two ranks' work lists together hold every picked expert exactly once.
+    from hecate_b200.ep import replica_owners
+    E2 = 32
+    wt2 = torch.from_numpy(synth.router_weight(8, 0, E2, H)).to(dev).to(torch.float16)
+    npr2 = E2 // world
+    ids2 = [(rank * npr2 + i) % E2 for i in range(2 * npr2)]
+    both = HostLayer(0, 0, H, I, ids2, 128, True).upload(dev)
+    full2 = HostLayer(0, 0, H, I, range(E2), 128, True).upload(dev)
+    dec = EpDecoder(rank, world, both, E2, dev, dist, use_peer=True, replicas=2)
+    own = dec.own_rows(R)
+    ws2 = moe.decode_workspace(H, I, dev)
+    for stepi in range(3):
+        xs = torch.from_numpy(synth.activations(40 + stepi, 0, R, H)).to(dev).half()
+        sel_f = torch.empty(R, 8, dtype=torch.int64, device=dev); rw_f = torch.empty(R, 8, dtype=torch.float16, device=dev)
+        f_own = torch.zeros(len(own), H, device=dev)
+        dec.step_dp_fused(xs[own].contiguous(), wt2, None, 1.0, sel_f, rw_f, f_own, R)
+        y_ref = torch.zeros(R, H, device=dev)
+        moe.decode(full2, xs, sel_f, rw_f, y_ref, ws2)
+        dp_err = torch.maximum(dp_err, torch.tensor([float((f_own - y_ref[own]).abs().max() / y_ref.abs().max())], device=dev))
+        owners = replica_owners(sel_f.cpu().numpy(), E2, world)
+        m_dev = torch.tensor([float(moe.route_distinct(dec.ws))], device=dev)
+        m_all = [torch.zeros_like(m_dev) for _ in range(world)]
+        dist.all_gather(m_all, m_dev)
+        assert [int(t.item()) for t in m_all] == [sum(1 for o in owners.values() if o == r) for r in range(world)]
+    assert dec.status() == 0
+    dist.barrier(); dec.peer.close()
     dist.all_reduce(dp_err, op=dist.ReduceOp.MAX)
     sep_err = torch.tensor([float((res["separate"] - res[True]).abs().max() / res[True].abs().max())], device=dev)
     dist.all_reduce(sep_err, op=dist.ReduceOp.MAX)
