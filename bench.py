@@ -284,6 +284,28 @@ def timed(torch, run, steps, nb, lead=0):
     return ev0.elapsed_time(ev1) / steps
 
 
+def wait_probe(moe, steps):
+    """With the diagnostic build of the library: steps = None clears the prefill GEMMs' wait counters and returns {} (None with the
+    normal build); otherwise returns, per kernel, the share of the blocks' lifetime each role spent in each of its waits."""
+    import ctypes as C
+    from hecate_b200 import _lib
+    L = _lib.lib()
+    if not hasattr(L, "hmoe_probe_read"):
+        return None
+    buf = (C.c_ulonglong * 64)()
+    L.hmoe_probe_read(buf, 1)
+    if steps is None:
+        return {}
+    names = {0: "mma_thread_waits_for_weights", 1: "mma_thread_waits_for_inputs", 2: "mma_thread_waits_for_free_accumulators",
+             4: "dequant_warp0_waits_for_ring_slot", 10: "dequant_warp15_waits_for_ring_slot", 9: "dequant_warp0_store_fence_arrive",
+             6: "tma_thread_waits_for_ring_slot", 7: "readout_warp_waits_for_tile", 8: "readout_warp_reads_out"}
+    out = {}
+    for k, kernel in ((1, "gate_up"), (0, "down")):
+        tot = buf[32 * k + 15]
+        out[kernel] = dict({"block_lifetime_cycles_all_sms_per_step": tot / steps}, **{n: buf[32 * k + i] / max(tot, 1) for i, n in names.items()})
+    return out
+
+
 def oracle_rows(O, layer, x_rows, sel_rows, rw_rows, mode):
     """The CPU checker's output for a few rows of THIS layer (weights copied back from the device). x_rows float32 (bf16 values)."""
     ids = sorted(set(int(e) for e in sel_rows.reshape(-1)))
@@ -462,10 +484,12 @@ def prefill_arm(args, dev, layer, torch, moe, synth, O, R=8192, zipf=1.1):
 
     for i in range(warmup):
         step(i)
+    probe = wait_probe(moe, None)                # diagnostic library only (python -m hecate_b200.csrc.build --probe-waits): clears its counters
     l0 = moe.launch_count()
     with ClockSampler(dev.index) as cs:
         ms = timed(torch, step, steps, NB)
     launches = moe.launch_count() - l0
+    probe = wait_probe(moe, steps) if probe is not None else None
     n2 = max(1, min(steps, 10))
     torch.cuda.synchronize()
     t0 = time.perf_counter()
@@ -480,7 +504,7 @@ def prefill_arm(args, dev, layer, torch, moe, synth, O, R=8192, zipf=1.1):
     tf = flop / (ms * 1e-3) / 1e12
     res = {
         "metric": "moe_prefill_expert_gemm_tflops", "value": tf, "unit": "TFLOP/s", "ms_per_step": ms, "steps": steps, "warmup": warmup,
-        "tokens_per_s": R / (ms * 1e-3), "dtype": "int4 -> fp16 x fp16 -> fp32 (tcgen05)",
+        "tokens_per_s": R / (ms * 1e-3), "dtype": "int4 -> fp16 x fp16 -> fp32 (tcgen05)", **({"wait_shares": probe} if probe else {}),
         "config": {"workload": f"prefill M={R} tokens, Zipf({zipf}) top-8 over {n_exp} experts + shared, H=6144, int4 g128 bf16 scales",
                    "l2": "inputs larger than L2 (4.85 GB of weights, 0.9 GB gathered inputs)", "max_picks_per_expert": int(counts.max()),
                    "min_picks_per_expert": int(counts.min())},

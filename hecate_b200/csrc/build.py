@@ -1,6 +1,8 @@
 """Builds libhecate_moe_b200.so in-tree with nvcc for sm_100a (no torch headers, links cudart only).
 
     python -m hecate_b200.csrc.build [--force] [--verbose]
+    python -m hecate_b200.csrc.build --probe-waits      # diagnostic build libhecate_moe_b200_probe.so: the prefill GEMMs count the cycles
+                                                        # every role spends in its waits (select it with HECATE_MOE_LIB; bench.py reports them)
 """
 import glob
 import os
@@ -18,7 +20,8 @@ def sources():
     return sorted(glob.glob(os.path.join(HERE, "*.cu")))
 
 
-def build(force=False, verbose=False):
+def build(force=False, verbose=False, defines=(), lib=None, obj_suffix=".o"):
+    LIB = lib or globals()["LIB"]
     deps = sources() + glob.glob(os.path.join(HERE, "*.cuh")) + glob.glob(os.path.join(HERE, "*.h")) + \
         [os.path.join(HERE, "..", "..", "include", "hecate_moe.h")]
     if not force and os.path.exists(LIB) and all(os.path.getmtime(LIB) >= os.path.getmtime(d) for d in deps):
@@ -26,8 +29,8 @@ def build(force=False, verbose=False):
     objs = []
     procs = []
     for src in sources():
-        obj = src[:-3] + ".o"
-        cmd = [NVCC, *[f for f in FLAGS if f != "--shared"], "-c", src, "-o", obj] + (["-Xptxas", "-v"] if verbose else [])
+        obj = src[:-3] + obj_suffix
+        cmd = [NVCC, *[f for f in FLAGS if f != "--shared"], *defines, "-c", src, "-o", obj] + (["-Xptxas", "-v"] if verbose else [])
         procs.append((subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT), src))
         objs.append(obj)
     bad = False
@@ -43,4 +46,8 @@ def build(force=False, verbose=False):
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    if "--probe-waits" in sys.argv:
+        print(build(force=True, verbose="--verbose" in sys.argv, defines=["-DHMOE_PROBE_WAITS"],
+                    lib=os.path.join(HERE, "libhecate_moe_b200_probe.so"), obj_suffix=".probe.o"))
+    else:
+        print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
