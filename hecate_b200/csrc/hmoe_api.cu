@@ -43,6 +43,8 @@ namespace {
 __global__ void __launch_bounds__(256) combine_kernel(float* __restrict__ f, const float* __restrict__ o, float* __restrict__ y,
                                                       int64_t n, const float* __restrict__ o2)
 {
+    // launched with programmatic stream serialization: the blocks may be resident before the kernel that produced y has finished
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int64_t i = ((int64_t) blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i >= n) return;
     float4 a = *(float4*) (f + i);
@@ -297,7 +299,16 @@ int hmoe_combine(float* f, const float* o, float* y, int64_t n, const float* o2,
 {
     if (!f || !y || n < 0 || n % 4) return fail(HMOE_E_ARG, "hmoe_combine: f, y and n % 4 == 0 required");
     if (n == 0) return HMOE_OK;
-    combine_kernel<<<(unsigned) ((n / 4 + 255) / 256), 256, 0, (cudaStream_t) stream>>>(f, o, y, n, o2);
+    {
+        // behind the decode kernels (which release their dependents early) the launch latency overlaps the down kernel's tail
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned) ((n / 4 + 255) / 256)); cfg.blockDim = dim3(256); cfg.stream = (cudaStream_t) stream;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = at; cfg.numAttrs = 1;
+        cudaLaunchKernelEx(&cfg, combine_kernel, f, o, y, n, o2);
+    }
     count_launches(1);
     const cudaError_t err = cudaGetLastError();
     return err == cudaSuccess ? HMOE_OK : fail(HMOE_E_CUDA, cudaGetErrorString(err));

@@ -132,6 +132,10 @@ __global__ void __launch_bounds__(RW * 32) router_logits_kernel(const uint16_t* 
     __shared__ int s_abort;
     __shared__ __align__(8) unsigned long long s_bar[RW];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // The expert kernels that follow are launched with programmatic stream serialization: let their blocks be scheduled as this
+    // kernel's blocks leave (they wait for this grid's completion before they read anything it wrote), so that their launch
+    // latency and prologue overlap the selection in this kernel's last block.
+    if (PREP) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int nrouter = PREP ? (int) gridDim.x - 1 : (int) gridDim.x;       // blocks per row group that compute logits
     if (PREP)
     {
