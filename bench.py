@@ -465,7 +465,7 @@ def prefill_arm(args, dev, layer, torch, moe, synth, O, R=8192, zipf=1.1):
     A step = permute -> gather -> grouped gate_up GEMM (+ SiLU epilogue) -> grouped down GEMM (+ scatter-add epilogue).
     value = TFLOP/s over the algorithmic flops 2 * (8 R + R) * 37,748,736 (padding columns not counted)."""
     n_exp, tabs = layer.n, layer.tabs
-    steps, warmup = max(1, min(args.steps, 50)), max(3, min(args.warmup, 5))
+    steps, warmup = max(1, min(args.steps, 20)), max(3, min(args.warmup, 5))
     NB = 2
     xs_np = [synth.activations(20 + b, 0, R, H) for b in range(NB)]
     xs = [torch.from_numpy(x).to(torch.bfloat16).to(dev) for x in xs_np]
