@@ -222,30 +222,40 @@ __device__ __forceinline__ void build_route(RouteSmem& S, const int64_t* __restr
     // +20 % in down, under +1 % in gate_up); the blocks' item ranges are cut at equal cost so that the blocks that get the
     // 16-row shared expert do not finish last.
     const int J0 = 2 * (I / 64), J1 = H / 64;
+    // inclusive prefix sums of the four columns over the 256 threads: shuffles inside the warps, the eight warp totals through
+    // shared memory (two barriers)
+    int incl[4];
     {
         const int n = tid < ns ? __popc(S.s_mask[tid]) : 0, full = n >> 3, rest = n & 7;
-        S.s_scan[0][tid] = (n + 7) >> 3;
-        S.s_scan[1][tid] = n;
-        S.s_scan[2][tid] = J0 * (full * (400 + 8) + (rest ? 400 + rest : 0));
-        S.s_scan[3][tid] = J1 * (full * (100 + 3 * 8) + (rest ? 100 + 3 * rest : 0));
+        incl[0] = (n + 7) >> 3;
+        incl[1] = n;
+        incl[2] = J0 * (full * (400 + 8) + (rest ? 400 + rest : 0));
+        incl[3] = J1 * (full * (100 + 3 * 8) + (rest ? 100 + 3 * rest : 0));
     }
+    const int lane_ = tid & 31, warp_ = tid >> 5;
+    #pragma unroll
+    for (int o = 1; o < 32; o <<= 1)
+        #pragma unroll
+        for (int c = 0; c < 4; ++c) { const int t = __shfl_up_sync(0xffffffffu, incl[c], o); if (lane_ >= o) incl[c] += t; }
+    if (lane_ == 31)
+        #pragma unroll
+        for (int c = 0; c < 4; ++c) S.s_scan[c][warp_] = incl[c];
     __syncthreads();
-    int incl[4];
-    #pragma unroll 1
-    for (int o = 1; o < 256; o <<= 1)                      // inclusive prefix sums of the four columns
+    int tot[4];
+    #pragma unroll
+    for (int c = 0; c < 4; ++c)
     {
+        int before = 0, all = 0;
         #pragma unroll
-        for (int c = 0; c < 4; ++c) incl[c] = S.s_scan[c][tid] + (tid >= o ? S.s_scan[c][tid - o] : 0);
-        __syncthreads();
-        #pragma unroll
-        for (int c = 0; c < 4; ++c) S.s_scan[c][tid] = incl[c];
-        __syncthreads();
+        for (int w = 0; w < 8; ++w) { const int x = S.s_scan[c][w]; all += x; if (w < warp_) before += x; }
+        incl[c] += before; tot[c] = all;
     }
-    const int nt = S.s_scan[0][255];
+    __syncthreads();                                       // s_scan is reused below
+    const int nt = tot[0];
     if (tid == 0)
     {
         route->m = m; route->ntiles = nt; route->pad[0] = route->pad[1] = 0;
-        S.s_cum[0][nt] = S.s_scan[2][255]; S.s_cum[1][nt] = S.s_scan[3][255];
+        S.s_cum[0][nt] = tot[2]; S.s_cum[1][nt] = tot[3];
         if (gen_bump) *gen_bump += 1;          // expert-parallel step counter: selects the partial slot and the combine's generation
     }
     if (tid < ns)

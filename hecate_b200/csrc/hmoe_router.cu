@@ -43,13 +43,16 @@ static __device__ unsigned g_router_groups[CTR_SLOTS], g_router_anybad[CTR_SLOTS
 // These kernels run once per layer on a handful of warps per SM: their duration is a chain of memory latencies, so every
 // group of loads is issued before its first use.
 
-// One warp selects one row: keys and activations of the E <= 256 experts in shared memory (512 words at `scratch`),
-// top-k rounds (max key, then lowest index holding it), weights. fresh: the logits were written by other blocks of the
-// same launch (read them past L1).
+// One warp selects one row of E <= 256 experts: top-k rounds (max key, then lowest index holding it), weights. fresh: the logits
+// were written by other blocks of the same launch (read them past L1).
 __device__ __noinline__ void topk_row(const float* __restrict__ logits, const float* __restrict__ bias, int r, int E, int topk, float scale,
                                       int64_t* __restrict__ sel, __half* __restrict__ rw, int lane, bool fresh, float* scratch)
 {
-    float* s_act = scratch; unsigned* s_key = (unsigned*) (scratch + 256);
+    // Lane L keeps experts L, L + 32, ... (eight of them) in registers: activation and order-preserving key. A round is seven
+    // compares per lane, one warp-wide maximum of the keys and one warp-wide minimum of the indices holding it; the winner's
+    // activation is broadcast from its lane and its key cleared there. (scratch is not needed any more.)
+    (void) scratch;
+    float act[8]; unsigned key[8];
     {
         // all of the row's logits and biases are requested before the first is used
         float l[8], bb[8];
@@ -61,30 +64,28 @@ __device__ __noinline__ void topk_row(const float* __restrict__ logits, const fl
             bb[i] = (e < E && bias) ? __ldg(bias + e) : 0.f;
         }
         #pragma unroll
-        for (int i = 0; i < 8; ++i) { s_act[lane + 32 * i] = l[i]; s_key[lane + 32 * i] = __float_as_uint(bb[i]); }
+        for (int i = 0; i < 8; ++i)
+        {
+            act[i] = __fdiv_rn(1.f, __fadd_rn(1.f, det_expf(-l[i])));
+            const unsigned u = __float_as_uint(__fadd_rn(act[i], bb[i]));
+            key[i] = lane + 32 * i < E ? ((u & 0x80000000u) ? ~u : (u | 0x80000000u)) : 0u;
+        }
     }
-    __syncwarp();
-    #pragma unroll 1
-    for (int e = lane; e < E; e += 32)
-    {
-        const float act = __fdiv_rn(1.f, __fadd_rn(1.f, det_expf(-s_act[e])));
-        const unsigned u = __float_as_uint(__fadd_rn(act, __uint_as_float(s_key[e])));
-        s_act[e] = act; s_key[e] = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-    }
-    __syncwarp();
     float sum = 0.f, mine_w = 0.f; int mine_id = 0;
     #pragma unroll 1
     for (int k = 0; k < topk; ++k)
     {
         unsigned lk = 0u; int li = lane;
-        #pragma unroll 1
-        for (int e = lane; e < E; e += 32) { const unsigned key = s_key[e]; if (key > lk) { lk = key; li = e; } }
+        #pragma unroll
+        for (int i = 0; i < 8; ++i) if (key[i] > lk) { lk = key[i]; li = lane + 32 * i; }       // ascending index: the lowest index wins a tie
         const unsigned m = __reduce_max_sync(0xffffffffu, lk);
         const unsigned bi = __reduce_min_sync(0xffffffffu, lk == m ? (unsigned) li : 0xffffffffu);
-        const float a = s_act[bi];
-        __syncwarp();
-        if (lane == 0) s_key[bi] = 0u;
-        __syncwarp();
+        float a = 0.f;
+        #pragma unroll
+        for (int i = 0; i < 8; ++i) if ((int) (bi >> 5) == i) a = act[i];
+        a = __shfl_sync(0xffffffffu, a, (int) (bi & 31u));
+        #pragma unroll
+        for (int i = 0; i < 8; ++i) if ((int) bi == lane + 32 * i) key[i] = 0u;
         sum = __fadd_rn(sum, a);
         if (lane == k) { mine_w = a; mine_id = (int) bi; }
     }
