@@ -306,6 +306,32 @@ def wait_probe(moe, steps):
     return out
 
 
+def decode_timeline(torch, run_step, nbatch, reps=24):
+    """With the diagnostic build of the library: the decode chain's kernels stamp the global timer (earliest / latest over their
+    blocks); returns the median time of every stamp after the router's entry, in microseconds, over single replayed steps."""
+    import ctypes as C
+    from hecate_b200 import _lib
+    L = _lib.lib()
+    if not hasattr(L, "hmoe_tl_router"):
+        return None
+    bufs = {n: (C.c_ulonglong * 16)() for n in ("router", "decode", "combine")}
+
+    def read(clear):
+        for n, b in bufs.items():
+            getattr(L, "hmoe_tl_" + n)(b, clear)
+    rows = []
+    for it in range(reps):
+        run_step(it % nbatch); torch.cuda.synchronize(); read(1)        # a step before keeps the caches and clocks as in a run
+        run_step((it + 1) % nbatch); torch.cuda.synchronize(); read(0)
+        r, d, c = bufs["router"], bufs["decode"], bufs["combine"]
+        ev = {"router_logits_done": r[1], "selection_done": r[3], "work_list_done": r[5], "gate_up_first_block_resident": d[0],
+              "gate_up_wait_returned": d[2], "gate_up_first_weights_in": d[4], "gate_up_end": d[1], "down_first_block_resident": d[8],
+              "down_wait_returned": d[10], "down_first_weights_in": d[12], "down_end": d[9], "combine_wait_returned": c[0]}
+        rows.append([(v - r[0]) / 1e3 for v in ev.values()])
+    med = np.median(np.array(rows), axis=0)
+    return {k: float(v) for k, v in zip(ev.keys(), med)}
+
+
 def oracle_rows(O, layer, x_rows, sel_rows, rw_rows, mode):
     """The CPU checker's output for a few rows of THIS layer (weights copied back from the device). x_rows float32 (bf16 values)."""
     ids = sorted(set(int(e) for e in sel_rows.reshape(-1)))
@@ -359,6 +385,7 @@ def decode_arm(args, dev, layer, torch, moe, synth, O):
             while time.time() < t_end:
                 run_step(0); torch.cuda.synchronize()
     launches = launches_per_step * steps
+    timeline = decode_timeline(torch, run_step, NBATCH)              # diagnostic library only
     # kernel durations: a second pass over the same steps launched eagerly back to back, CUDA events around each kernel on
     # its stream (recorded by the library into a ring); read after the pass
     moe.set_profiling(True)
@@ -414,9 +441,10 @@ def decode_arm(args, dev, layer, torch, moe, synth, O):
         for i in range(3):
             run_r(i % NBATCH)
         ms_r = timed(torch, run_r, max(8, min(steps, 64)), NBATCH)
+        tl_r = decode_timeline(torch, run_r, NBATCH) if r == 1 else None
         bytes_r = (float(np.mean(d_r)) + 1) * EXPERT_BYTES + n_exp * H * 2 + r * H * 6
         small[str(r)] = {"us_per_layer": ms_r * 1e3, "distinct_experts": float(np.mean(d_r)),
-                         "layer_hbm_frac": bytes_r / (ms_r * 1e-3) / 1e9 / peaks()["hbm"]}
+                         "layer_hbm_frac": bytes_r / (ms_r * 1e-3) / 1e9 / peaks()["hbm"], **({"timeline_us": tl_r} if tl_r else {})}
 
     # parity on this very layer, outside the timed regions: the router's selection bit for bit, two rows of batch 0 in both modes
     parity = {}
@@ -453,7 +481,7 @@ def decode_arm(args, dev, layer, torch, moe, synth, O):
         "e2e": {"value": ROWS / e2e_s, "unit": UNIT, "h2d_bytes_per_step": ROWS * H * 2, "d2h_bytes_per_step": ROWS * H * 4,
                 "us_per_layer": e2e_s * 1e6},
         "act_quant": {"decode_us_per_layer": ms_q * 1e3, "decode_vs_default": ms_q / ms_per_step},
-        "small_batches": small,
+        "small_batches": small, **({"timeline_us": timeline} if timeline else {}),
         "parity_check": {"decode": parity},
         "gpu_launches": int(launches), "device_status": int(status), "clocks": cs.summary(),
     }

@@ -2,7 +2,8 @@
 
     python -m hecate_b200.csrc.build [--force] [--verbose]
     python -m hecate_b200.csrc.build --probe-waits      # diagnostic build libhecate_moe_b200_probe.so: the prefill GEMMs count the cycles
-                                                        # every role spends in its waits (select it with HECATE_MOE_LIB; bench.py reports them)
+                                                        # every role spends in its waits, and the decode chain's kernels stamp the global
+                                                        # timer at a few points (select it with HECATE_MOE_LIB; bench.py reports both)
 """
 import glob
 import os
@@ -47,7 +48,7 @@ def build(force=False, verbose=False, defines=(), lib=None, obj_suffix=".o"):
 
 if __name__ == "__main__":
     if "--probe-waits" in sys.argv:
-        print(build(force=True, verbose="--verbose" in sys.argv, defines=["-DHMOE_PROBE_WAITS"],
+        print(build(force=True, verbose="--verbose" in sys.argv, defines=["-DHMOE_PROBE_WAITS", "-DHMOE_PROBE_TIMELINE"],
                     lib=os.path.join(HERE, "libhecate_moe_b200_probe.so"), obj_suffix=".probe.o"))
     else:
         print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

@@ -80,6 +80,20 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (status) atomicOr(status, ST_WAIT_TIMEOUT);
     return false;
 }
+// Diagnostic build (-DHMOE_PROBE_TIMELINE): kernels of the decode chain stamp the global timer at a few points (earliest and latest
+// over the blocks); every source file has its own table and reader. Not part of the normal build.
+#ifdef HMOE_PROBE_TIMELINE
+static __device__ unsigned long long g_tl[16];
+#define TL_MIN(i) do { if (threadIdx.x == 0) atomicMin(&g_tl[i], globaltimer_ns()); } while (0)
+#define TL_MAX(i) do { if (threadIdx.x == 0) atomicMax(&g_tl[i], globaltimer_ns()); } while (0)
+#define TL_READER(name) extern "C" int name(unsigned long long* out, int clear) { \
+    cudaDeviceSynchronize(); cudaMemcpyFromSymbol(out, g_tl, sizeof(unsigned long long) * 16); \
+    if (clear) { unsigned long long z[16]; for (int i = 0; i < 16; ++i) z[i] = (i & 1) ? 0ull : ~0ull; cudaMemcpyToSymbol(g_tl, z, sizeof(z)); } return 0; }
+#else
+#define TL_MIN(i)
+#define TL_MAX(i)
+#define TL_READER(name)
+#endif
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 

@@ -638,7 +638,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_stream_kernel(const Decode
     // kernel before it has completed with its memory visible. So whatever a dependent reads before ITS wait (down: the route,
     // the step counter) was written at least two kernels back and is complete, whatever the occupancy. Blocks without work
     // wait too, so that a grid with nothing to do cannot release its dependents early.
-    if (!DOWN) { pdl_wait(); pdl_launch_dependents(); }
+    TL_MIN(DOWN ? 8 : 0);
+    if (!DOWN) { pdl_wait(); pdl_launch_dependents(); TL_MIN(2); }
     const Route* rt = a.route;
     const int K = DOWN ? a.I : a.H, N = DOWN ? a.H : a.I;          // input columns and output rows of one matrix
     const int KB = K / 64, NG = N / 64, J = DOWN ? NG : 2 * NG;
@@ -787,7 +788,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_stream_kernel(const Decode
         for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
         uint32_t st = 0, par = 0;
         int tile = p0 / J, j = p0 % J;
-        if (DOWN) { pdl_wait(); pdl_launch_dependents(); }
+        if (DOWN) { pdl_wait(); pdl_launch_dependents(); TL_MIN(10); }
         enter_tile(tile);
         if (!GROUPED) load_row_scales(j, sd);
         bool alive = true;
@@ -804,6 +805,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_stream_kernel(const Decode
                 if (kc * 32 + 2 * warp < KB)
                 {
                     if (!mbar_wait(full0 + st * CW * 8, par, abort_flag, a.status)) { alive = false; break; }
+                    TL_MIN(DOWN ? 12 : 4);
                     const uint32_t slot = ring + st * CW * SLOT;
                     uint4 sc = make_uint4(0, 0, 0, 0);
                     if (GROUPED) sc = lds128(slot + 4096 + g * 16);
@@ -847,6 +849,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_stream_kernel(const Decode
     }
     else if (DOWN) { pdl_wait(); pdl_launch_dependents(); }
     __syncthreads();
+    TL_MAX(DOWN ? 9 : 1);
     if (DOWN && a.ep.world > 0) ep_tail_combine(a.ep, *a.gen_ptr, a.slot_stride, a.H);
 }
 
@@ -1099,3 +1102,8 @@ extern "C" int hmoe_decode_noalloc(const hmoe_layer* layer, const void* x, int x
         return fail(HMOE_E_CUDA, "hmoe_decode_noalloc: copying the status word failed");
     return HMOE_OK;
 }
+
+#ifdef HMOE_PROBE_TIMELINE
+using namespace hmoe;
+TL_READER(hmoe_tl_decode)
+#endif

@@ -111,13 +111,15 @@ struct RouteSmem
     int wcount[8];
     int m_sh;
     unsigned char gflag[256];                  // replicated experts: router position -> 1 picked by some row, 2 picked and served here
-};
+    int raw_sel[MAXR * TOPK_MAX];              // SRC = 2: the selections (router positions) and, in s_rw, the weights, left here by the
+};                                             // block's own selection step instead of being read back from global memory
 
 // routing block: slot = distinct expert (ascending id), then the shared expert; tiles of <= 8 rows per slot.
 // Everything is done in parallel with block-wide prefix sums: this block is the critical path of the call (the
 // streaming kernel's blocks are already resident and wait for it).
-// Called by all 256 threads of one block. FRESH: sel / rw were written by other blocks of the same launch (read them past L1).
-template <bool FRESH>
+// Called by all 256 threads of one block. SRC = 1: sel / rw were written by other blocks of the same launch (read them past L1);
+// SRC = 2: they are in S.raw_sel / S.s_rw already (written by this block's own selection step, visible after a barrier).
+template <int SRC>
 __device__ __forceinline__ void build_route(RouteSmem& S, const int64_t* __restrict__ sel, const __half* __restrict__ rw, int R, int H, int I, int topk,
                                             int lo, int n_local, int has_shared, int sh_mod, int sh_rem, unsigned* gen_bump,
                                             Route* __restrict__ route, int nblocks, int tid, int n_total = 0, int bal_world = 0, int bal_rank = 0)
@@ -125,6 +127,7 @@ __device__ __forceinline__ void build_route(RouteSmem& S, const int64_t* __restr
     const int NP = R * topk;
     S.slot_of[tid] = 0;                                      // used as the picked flag first
     if (tid < MAXS) S.s_mask[tid] = 0u;
+    if (bal_world <= 1) __syncthreads();                     // (the other path has its own barriers before the flags are set)
     if (bal_world > 1)
     {
         // Every expert held by two ranks (rank r holds the bands r and r + 1 of n_total / world positions each, so position e is
@@ -136,7 +139,7 @@ __device__ __forceinline__ void build_route(RouteSmem& S, const int64_t* __restr
         __syncthreads();
         if (tid < NP)
         {
-            const int64_t e = FRESH ? (int64_t) __ldcg((const long long*) sel + tid) : sel[tid];
+            const int64_t e = SRC == 2 ? (int64_t) S.raw_sel[tid] : SRC == 1 ? (int64_t) __ldcg((const long long*) sel + tid) : sel[tid];
             if (e >= 0 && e < n_total) S.gflag[(int) e] = 1;
         }
         __syncthreads();
@@ -161,7 +164,7 @@ __device__ __forceinline__ void build_route(RouteSmem& S, const int64_t* __restr
     }
     if (tid < NP)
     {
-        int64_t e = FRESH ? (int64_t) __ldcg((const long long*) sel + tid) : sel[tid];
+        int64_t e = SRC == 2 ? (int64_t) S.raw_sel[tid] : SRC == 1 ? (int64_t) __ldcg((const long long*) sel + tid) : sel[tid];
         bool in;
         if (bal_world > 1)
         {
@@ -171,10 +174,11 @@ __device__ __forceinline__ void build_route(RouteSmem& S, const int64_t* __restr
         }
         else { e -= lo; in = e >= 0 && e < n_local; }
         S.s_sel[tid] = in ? (short) e : (short) -1;
-        S.s_rw[tid] = __half2float(FRESH ? __ushort_as_half(__ldcg((const unsigned short*) rw + tid)) : rw[tid]);
+        if (SRC != 2) S.s_rw[tid] = __half2float(SRC == 1 ? __ushort_as_half(__ldcg((const unsigned short*) rw + tid)) : rw[tid]);
         if (in) S.slot_of[(int) e] = 1;
     }
     __syncthreads();
+    TL_MAX(7);
     {
         // distinct experts in ascending order: one flag per thread, ballots per warp, prefix over the eight warps
         const bool picked = S.slot_of[tid] != 0;
@@ -222,6 +226,7 @@ __device__ __forceinline__ void build_route(RouteSmem& S, const int64_t* __restr
     // +20 % in down, under +1 % in gate_up); the blocks' item ranges are cut at equal cost so that the blocks that get the
     // 16-row shared expert do not finish last.
     const int J0 = 2 * (I / 64), J1 = H / 64;
+    TL_MAX(9);
     // inclusive prefix sums of the four columns over the 256 threads: shuffles inside the warps, the eight warp totals through
     // shared memory (two barriers)
     int incl[4];
@@ -278,6 +283,7 @@ __device__ __forceinline__ void build_route(RouteSmem& S, const int64_t* __restr
         }
     }
     __syncthreads();
+    TL_MAX(11);
     for (int i = tid; i < 2 * (nblocks + 1); i += 256)
     {
         const int k = i / (nblocks + 1), b = i % (nblocks + 1), J = k ? J1 : J0;

@@ -36,64 +36,90 @@ constexpr int CTR_SLOTS = 16, CTR_GROUPS = 256;
 static __device__ unsigned g_router_ctr[CTR_SLOTS][CTR_GROUPS];
 // Set by a block of the row group whose bounded wait gave up; read and cleared by the group's last block.
 static __device__ unsigned g_router_bad[CTR_SLOTS][CTR_GROUPS];
-// PREP: row groups whose selection is complete (the block that completes the last one builds the decode call's Route), and
-// whether any of them failed.
-static __device__ unsigned g_router_groups[CTR_SLOTS], g_router_anybad[CTR_SLOTS];
+// PREP: one count over all blocks of the launch in g_router_ctr[slot][0] (low half: arrivals, high half: blocks whose wait gave up).
 
 // These kernels run once per layer on a handful of warps per SM: their duration is a chain of memory latencies, so every
 // group of loads is issued before its first use.
 
-// One warp selects one row of E <= 256 experts: top-k rounds (max key, then lowest index holding it), weights. fresh: the logits
-// were written by other blocks of the same launch (read them past L1).
-__device__ __noinline__ void topk_row(const float* __restrict__ logits, const float* __restrict__ bias, int r, int E, int topk, float scale,
-                                      int64_t* __restrict__ sel, __half* __restrict__ rw, int lane, bool fresh, float* scratch)
+// One warp selects NR rows (r, r + rstep, ...) of E <= 256 experts side by side: top-k rounds (max key, then lowest index holding
+// it), weights. fresh: the logits were written by other blocks of the same launch (read them past L1). The rows' rounds are
+// independent chains of warp-wide reductions, so two rows take little longer than one.
+// Lane L keeps experts L, L + 32, ... (eight of them) of every row in registers: activation and order-preserving key. A round is
+// seven compares per lane, one warp-wide maximum of the keys and one warp-wide minimum of the indices holding it; the winner's
+// activation is broadcast from its lane and its key cleared there.
+template <int NR>
+__device__ __forceinline__ void topk_rows(const float* __restrict__ logits, const float* __restrict__ bias, int r, int rstep, int R, int E, int topk,
+                                          float scale, int64_t* __restrict__ sel, __half* __restrict__ rw, int lane, bool fresh,
+                                          int* s_sel_out = nullptr, float* s_rw_out = nullptr)
 {
-    // Lane L keeps experts L, L + 32, ... (eight of them) in registers: activation and order-preserving key. A round is seven
-    // compares per lane, one warp-wide maximum of the keys and one warp-wide minimum of the indices holding it; the winner's
-    // activation is broadcast from its lane and its key cleared there. (scratch is not needed any more.)
-    (void) scratch;
-    float act[8]; unsigned key[8];
+    float act[NR][8]; unsigned key[NR][8];
     {
-        // all of the row's logits and biases are requested before the first is used
-        float l[8], bb[8];
+        // all of the rows' logits and biases are requested before the first is used
+        float l[NR][8], bb[8];
         #pragma unroll
         for (int i = 0; i < 8; ++i)
         {
             const int e = lane + 32 * i;
-            l[i] = e < E ? (fresh ? __ldcg(logits + (size_t) r * E + e) : logits[(size_t) r * E + e]) : 0.f;
+            #pragma unroll
+            for (int n = 0; n < NR; ++n)
+            {
+                const int rr = r + n * rstep;
+                l[n][i] = (e < E && rr < R) ? (fresh ? __ldcg(logits + (size_t) rr * E + e) : logits[(size_t) rr * E + e]) : 0.f;
+            }
             bb[i] = (e < E && bias) ? __ldg(bias + e) : 0.f;
         }
         #pragma unroll
-        for (int i = 0; i < 8; ++i)
-        {
-            act[i] = __fdiv_rn(1.f, __fadd_rn(1.f, det_expf(-l[i])));
-            const unsigned u = __float_as_uint(__fadd_rn(act[i], bb[i]));
-            key[i] = lane + 32 * i < E ? ((u & 0x80000000u) ? ~u : (u | 0x80000000u)) : 0u;
-        }
+        for (int n = 0; n < NR; ++n)
+            #pragma unroll
+            for (int i = 0; i < 8; ++i)
+            {
+                act[n][i] = __fdiv_rn(1.f, __fadd_rn(1.f, det_expf(-l[n][i])));
+                const unsigned u = __float_as_uint(__fadd_rn(act[n][i], bb[i]));
+                key[n][i] = lane + 32 * i < E ? ((u & 0x80000000u) ? ~u : (u | 0x80000000u)) : 0u;
+            }
     }
-    float sum = 0.f, mine_w = 0.f; int mine_id = 0;
+    float sum[NR], mine_w[NR]; int mine_id[NR];
+    #pragma unroll
+    for (int n = 0; n < NR; ++n) { sum[n] = 0.f; mine_w[n] = 0.f; mine_id[n] = 0; }
     #pragma unroll 1
     for (int k = 0; k < topk; ++k)
     {
-        unsigned lk = 0u; int li = lane;
         #pragma unroll
-        for (int i = 0; i < 8; ++i) if (key[i] > lk) { lk = key[i]; li = lane + 32 * i; }       // ascending index: the lowest index wins a tie
-        const unsigned m = __reduce_max_sync(0xffffffffu, lk);
-        const unsigned bi = __reduce_min_sync(0xffffffffu, lk == m ? (unsigned) li : 0xffffffffu);
-        float a = 0.f;
-        #pragma unroll
-        for (int i = 0; i < 8; ++i) if ((int) (bi >> 5) == i) a = act[i];
-        a = __shfl_sync(0xffffffffu, a, (int) (bi & 31u));
-        #pragma unroll
-        for (int i = 0; i < 8; ++i) if ((int) bi == lane + 32 * i) key[i] = 0u;
-        sum = __fadd_rn(sum, a);
-        if (lane == k) { mine_w = a; mine_id = (int) bi; }
+        for (int n = 0; n < NR; ++n)
+        {
+            unsigned lk = 0u; int li = lane;
+            #pragma unroll
+            for (int i = 0; i < 8; ++i) if (key[n][i] > lk) { lk = key[n][i]; li = lane + 32 * i; }     // ascending index: the lowest index wins a tie
+            const unsigned m = __reduce_max_sync(0xffffffffu, lk);
+            const unsigned bi = __reduce_min_sync(0xffffffffu, lk == m ? (unsigned) li : 0xffffffffu);
+            float a = 0.f;
+            #pragma unroll
+            for (int i = 0; i < 8; ++i) if ((int) (bi >> 5) == i) a = act[n][i];
+            a = __shfl_sync(0xffffffffu, a, (int) (bi & 31u));
+            #pragma unroll
+            for (int i = 0; i < 8; ++i) if ((int) bi == lane + 32 * i) key[n][i] = 0u;
+            sum[n] = __fadd_rn(sum[n], a);
+            if (lane == k) { mine_w[n] = a; mine_id[n] = (int) bi; }
+        }
     }
-    if (lane < topk)
+    #pragma unroll
+    for (int n = 0; n < NR; ++n)
     {
-        sel[(size_t) r * topk + lane] = mine_id;
-        rw[(size_t) r * topk + lane] = __float2half_rn(__fdiv_rn(__fmul_rn(mine_w, scale), __fadd_rn(sum, 1e-20f)));
+        const int rr = r + n * rstep;
+        if (lane < topk && rr < R)
+        {
+            const __half h = __float2half_rn(__fdiv_rn(__fmul_rn(mine_w[n], scale), __fadd_rn(sum[n], 1e-20f)));
+            sel[(size_t) rr * topk + lane] = mine_id[n];
+            rw[(size_t) rr * topk + lane] = h;
+            if (s_sel_out) { s_sel_out[rr * topk + lane] = mine_id[n]; s_rw_out[rr * topk + lane] = __half2float(h); }     // for a work list built by the same block
+        }
     }
+}
+__device__ __noinline__ void topk_row(const float* __restrict__ logits, const float* __restrict__ bias, int r, int E, int topk, float scale,
+                                      int64_t* __restrict__ sel, __half* __restrict__ rw, int lane, bool fresh, float* scratch)
+{
+    (void) scratch;
+    topk_rows<1>(logits, bias, r, 0, r + 1, E, topk, scale, sel, rw, lane, fresh);
 }
 
 // Block (bx, by): experts 8 bx .. 8 bx + 7 (one per warp) x rows 4 by .. 4 by + 3, the columns in chunks of at most HC.
@@ -114,8 +140,8 @@ struct NormArgs
 
 // PREP (with FUSED, without NORM): the launch also does the set-up step of the decode call that follows (hmoe_prepare.cuh), so that
 // no separate prepare kernel sits between the router and the expert kernels: one more block per row group (blockIdx.x ==
-// gridDim.x - 1) rewrites the group's rows for the MMAs while the other blocks compute logits, and the block that completes the
-// last row group's selection builds the Route from the selections of all rows.
+// gridDim.x - 1) rewrites the group's rows for the MMAs while the other blocks compute logits, and the block that finishes last in
+// the whole launch selects the experts of all rows and builds the Route.
 // DISP (with PREP): expert parallelism with data-parallel tokens. The launch is also the dispatch: blocks (p, 0) for p < world first
 // store this rank's rows into rank p's staging area and raise this rank's flag there (release, system scope); every block then
 // waits, bounded, for the flags of the ranks that own its four rows before it reads them from the local staging area. So the
@@ -131,8 +157,10 @@ __global__ void __launch_bounds__(RW * 32) router_logits_kernel(const uint16_t* 
     extern __shared__ __align__(128) unsigned char rsm[];
     __shared__ int s_last;
     __shared__ int s_abort;
+    __shared__ int s_blockbad;
     __shared__ __align__(8) unsigned long long s_bar[RW];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    TL_MIN(0);
     // The expert kernels that follow are launched with programmatic stream serialization: let their blocks be scheduled as this
     // kernel's blocks leave (they wait for this grid's completion before they read anything it wrote), so that their launch
     // latency and prologue overlap the selection in this kernel's last block.
@@ -196,7 +224,7 @@ __global__ void __launch_bounds__(RW * 32) router_logits_kernel(const uint16_t* 
     const int e = blockIdx.x * RW + warp;
     const uint16_t* w = wt + (size_t) (e < E ? e : 0) * H;
     if (lane == 0) { mbar_init(bar, 1); fence_barrier_init(); }
-    if (threadIdx.x == 0) s_abort = 0;
+    if (threadIdx.x == 0) { s_abort = 0; s_blockbad = 0; }
     __syncthreads();
     float acc[RR];
     #pragma unroll
@@ -298,7 +326,7 @@ __global__ void __launch_bounds__(RW * 32) router_logits_kernel(const uint16_t* 
         // A wait that gives up raises the status bit; the block skips the sums but still takes part in the arrival count
         // below, so the call's counter slot returns to zero and later calls that reuse it are not affected.
         const bool got = mbar_wait(bar, par, &s_abort, status) && rows_ok;
-        if (FUSED && !got && lane == 0) atomicOr(&g_router_bad[slot][blockIdx.y], 1u);
+        if (FUSED && !got && lane == 0) { if (PREP) atomicOr(&s_blockbad, 1); else atomicOr(&g_router_bad[slot][blockIdx.y], 1u); }
         #pragma unroll 2
         for (int k = 0; got && k < cl; k += 256)
         {
@@ -325,8 +353,62 @@ __global__ void __launch_bounds__(RW * 32) router_logits_kernel(const uint16_t* 
         if (lane == 0 && r < nr && e < E) logits[(size_t) (r0 + r) * E + e] = a;
     }
     if (!FUSED) return;
+    TL_MAX(1);
     __threadfence();
     __syncthreads();
+    if (PREP)
+    {
+        // One level: the block that finishes LAST IN THE WHOLE LAUNCH selects the experts of all rows (two rows per warp at sixteen
+        // rows) and builds the work list from its own shared memory. Every hand-off through global memory costs about a
+        // microsecond of latency on this chain (measured: logits 6.7 us after the kernel's entry, work list 17.5 us with the
+        // group-wise scheme of the stand-alone router: an arrival count per row group, then one over the groups, each followed by a
+        // flag load and a reload of what the previous step had written); here it is one arrival count, whose upper half carries
+        // the "a wait gave up" flags, and one load of the logits.
+        __shared__ unsigned s_old;
+        if (threadIdx.x == 0)
+        {
+            unsigned* c = &g_router_ctr[slot][0];
+            const unsigned old = atomicAdd(c, 1u + (s_blockbad ? 0x10000u : 0u));
+            s_last = (old & 0xffffu) == (unsigned) nrouter * gridDim.y - 1u;
+            s_old = old + (s_blockbad ? 0x10000u : 0u);
+            if (s_last) *c = 0u;
+        }
+        __syncthreads();
+        if (!s_last) return;
+        __threadfence();
+        const bool anybad = (s_old >> 16) != 0u;
+        RouteSmem& S = *(RouteSmem*) (rsm + RW * 512 * 4);
+        if (anybad)
+        {
+            // a wait gave up somewhere in this call: the logits are incomplete. Leave an empty Route (the expert kernels then do
+            // nothing) and tell the host through the decode workspace's status word.
+            if (threadIdx.x == 0) { atomicOr(pa.status, ST_WAIT_TIMEOUT); pa.route->m = 0; pa.route->ntiles = 0; }
+            for (int i = threadIdx.x; i < 2 * (MAXB + 1); i += RW * 32) pa.route->split[i / (MAXB + 1)][i % (MAXB + 1)] = 0;
+        }
+        else
+        {
+            // R <= 16: rows warp and warp + 8 (one instance of the code whatever R is: this block runs it once, from a cold instruction cache)
+            if (warp < R) topk_rows<2>(logits, bias, warp, RW, R, E, topk, scale, sel, rw, lane, true, S.raw_sel, S.s_rw);
+        }
+        TL_MAX(3);
+        if (DISP && threadIdx.x == 0)
+        {
+            // this block is the last to work: once every block of the launch has read the generation, advance it (bounded wait)
+            unsigned* ctl = (unsigned*) (da.stage[da.rank] + da.ctl_off);
+            const unsigned nblk = gridDim.x * gridDim.y;
+            const unsigned long long t0 = globaltimer_ns();
+            while (*(volatile unsigned*) (ctl + 1) < nblk)
+                if (globaltimer_ns() - t0 > 1000000000ull) { atomicOr(pa.status, ST_WAIT_TIMEOUT); break; }
+            ctl[1] = 0u;
+            *(volatile unsigned*) ctl = dgen;
+        }
+        __syncthreads();
+        if (anybad) return;
+        build_route<2>(S, sel, rw, R, H, pa.I, topk, pa.lo, pa.n_local, pa.has_shared, pa.sh_mod, pa.sh_rem,
+                       pa.gen_bump, pa.route, pa.nblocks, threadIdx.x, pa.n_total, pa.bal_world, pa.bal_rank);
+        TL_MAX(5);
+        return;
+    }
     if (threadIdx.x == 0)
     {
         unsigned* c = &g_router_ctr[slot][blockIdx.y];
@@ -341,46 +423,10 @@ __global__ void __launch_bounds__(RW * 32) router_logits_kernel(const uint16_t* 
         // after a failed wait the logits are incomplete: select nothing (the status word tells the host)
         const unsigned bad = *(volatile unsigned*) &g_router_bad[slot][blockIdx.y];
         __syncthreads();
-        if (threadIdx.x == 0 && bad) { g_router_bad[slot][blockIdx.y] = 0u; if (PREP) atomicOr(&g_router_anybad[slot], 1u); }
-        if (bad && !PREP) return;
-        if (!bad && warp < nr) topk_row(logits, bias, r0 + warp, E, topk, scale, sel, rw, lane, true, xs + warp * 512);
+        if (threadIdx.x == 0 && bad) g_router_bad[slot][blockIdx.y] = 0u;
+        if (bad) return;
+        if (warp < nr) topk_row(logits, bias, r0 + warp, E, topk, scale, sel, rw, lane, true, xs + warp * 512);
     }
-    if (!PREP) return;
-    // the selections of this row group are written: count the group; the block that completes the last group builds the Route
-    __syncthreads();
-    if (threadIdx.x == 0)
-    {
-        __threadfence();
-        const unsigned old = atomicAdd(&g_router_groups[slot], 1u);
-        s_last = old == gridDim.y - 1;
-        if (s_last) g_router_groups[slot] = 0u;
-    }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    const unsigned anybad = *(volatile unsigned*) &g_router_anybad[slot];
-    __syncthreads();
-    if (anybad)
-    {
-        // a wait gave up somewhere in this call: the selections are incomplete. Leave an empty Route (the expert kernels then do
-        // nothing) and tell the host through the decode workspace's status word.
-        if (threadIdx.x == 0) { g_router_anybad[slot] = 0u; atomicOr(pa.status, ST_WAIT_TIMEOUT); pa.route->m = 0; pa.route->ntiles = 0; }
-        for (int i = threadIdx.x; i < 2 * (MAXB + 1); i += RW * 32) pa.route->split[i / (MAXB + 1)][i % (MAXB + 1)] = 0;
-    }
-    if (DISP && threadIdx.x == 0)
-    {
-        // this block is the last to work: once every block of the launch has read the generation, advance it (bounded wait)
-        unsigned* ctl = (unsigned*) (da.stage[da.rank] + da.ctl_off);
-        const unsigned nblk = gridDim.x * gridDim.y;
-        const unsigned long long t0 = globaltimer_ns();
-        while (*(volatile unsigned*) (ctl + 1) < nblk)
-            if (globaltimer_ns() - t0 > 1000000000ull) { atomicOr(pa.status, ST_WAIT_TIMEOUT); break; }
-        ctl[1] = 0u;
-        *(volatile unsigned*) ctl = dgen;
-    }
-    if (anybad) return;
-    build_route<true>(*(RouteSmem*) (rsm + RW * 512 * 4), sel, rw, R, H, pa.I, topk, pa.lo, pa.n_local, pa.has_shared, pa.sh_mod, pa.sh_rem,
-                      pa.gen_bump, pa.route, pa.nblocks, threadIdx.x, pa.n_total, pa.bal_world, pa.bal_rank);
 }
 
 __global__ void __launch_bounds__(256) router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int R, int E,
@@ -534,3 +580,8 @@ int norm_router_launch(const float* y, const float* r, float* r_out, const void*
 }
 
 }  // namespace hmoe
+
+#ifdef HMOE_PROBE_TIMELINE
+using namespace hmoe;
+TL_READER(hmoe_tl_router)
+#endif
