@@ -199,6 +199,7 @@ __global__ void __launch_bounds__(RW * 32) router_logits_kernel(const uint16_t* 
             }
             __syncthreads();
             if (threadIdx.x == 0) { __threadfence_system(); sys_st_release((unsigned*) (dst + da.flags_off) + da.rank, dgen); }
+            TL_MAX(13);
         }
         if ((int) threadIdx.x < RR && (int) (blockIdx.y * RR + threadIdx.x) < R)
         {
@@ -208,6 +209,7 @@ __global__ void __launch_bounds__(RW * 32) router_logits_kernel(const uint16_t* 
                 if (globaltimer_ns() - t0 > 2000000000ull) { atomicOr(pa.status, ST_WAIT_TIMEOUT); s_rows_ok = 0; break; }
         }
         __syncthreads();
+        TL_MAX(15);
         rows_ok = s_rows_ok != 0;
     }
     if (PREP && (int) blockIdx.x == nrouter)
