@@ -607,12 +607,14 @@ __global__ void __launch_bounds__(pf_threads(NMAT), 1) prefill_gemm_kernel(const
             tc_fence_after();
             if constexpr (NMAT == 2)
             {
-                // Eight columns at a time, two register sets in turn: the tensor-memory loads of the next eight columns are in
-                // flight while the current eight are turned into activations (the tensor core waits for this read-out).
+                // Eight columns at a time, one register set: with 72 registers per thread a second set in flight (the next eight columns'
+                // tensor-memory loads under the current eight's arithmetic) left the compiler too few registers to run the eight columns'
+                // exp / reciprocal / product chains side by side, and the read-out took twice as long (measured: 127 M against 62 M
+                // cycles per step over all SMs; the loads alone are 17 M). The tensor core waits for this read-out.
                 // The loops carry no branch per column: a conditional region per column costs convergence-barrier instructions that
                 // run one after the other (measured: ~70 cycles per column); the arithmetic runs for the padding columns too and
                 // only the store is predicated; the int8 mode is a compile-time variant of the whole loop.
-                uint32_t g0[8], u0[8], g1[8], u1[8];
+                uint32_t g0[8], u0[8];
                 auto read_out = [&](auto aq_tag) {
                     constexpr bool AQ = decltype(aq_tag)::value;
                     auto emit = [&](const uint32_t (&gr)[8], const uint32_t (&ur)[8], int c0) {
@@ -650,18 +652,11 @@ __global__ void __launch_bounds__(pf_threads(NMAT), 1) prefill_gemm_kernel(const
                             }
                         }
                     };
-                    if (cbeg < cend) { tmem_ld8(tacc + cbeg, g0); tmem_ld8(tacc + 256 + cbeg, u0); }
-                    for (int c0 = cbeg; c0 < cend; c0 += 16)
+                    for (int c0 = cbeg; c0 < cend; c0 += 8)
                     {
+                        tmem_ld8(tacc + c0, g0); tmem_ld8(tacc + 256 + c0, u0);
                         tmem_ld_wait();
-                        if (c0 + 8 < cend) { tmem_ld8(tacc + c0 + 8, g1); tmem_ld8(tacc + 256 + c0 + 8, u1); }
                         emit(g0, u0, c0);
-                        if (c0 + 8 < cend)
-                        {
-                            tmem_ld_wait();
-                            if (c0 + 16 < cend) { tmem_ld8(tacc + c0 + 16, g0); tmem_ld8(tacc + 256 + c0 + 16, u0); }
-                            emit(g1, u1, c0 + 8);
-                        }
                     }
                 };
                 if (a.act_quant) read_out(std::true_type()); else read_out(std::false_type());
