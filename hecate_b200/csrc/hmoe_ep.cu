@@ -50,6 +50,9 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(const EpArgs a, const u
                                                          size_t slot_floats, unsigned* __restrict__ status, int own_rows, int H)
 {
     __shared__ int ok_sh;
+    // launched with programmatic stream serialization behind the down kernel (which releases its dependents early): the blocks are
+    // resident when down ends; nothing is read, and above all no flag raised, before down has completed with its sums visible
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const unsigned gen = *gen_ptr;            // bumped by this step's prepare kernel, stable for the rest of the step
     const int parity = gen & 1;
     if (blockIdx.x == 0 && threadIdx.x < a.world) st_release_sys(a.flags[threadIdx.x] + a.rank, gen);
@@ -266,7 +269,15 @@ int ep_combine_launch(int rank, int world, void* const* slots, void* const* flag
     for (int p = 0; p < 8; ++p) { a.slots[p] = p < world ? (float*) slots[p] : nullptr; a.flags[p] = p < world ? (unsigned*) flags[p] : nullptr; }
     const int blocks = (n / 4 + 255) / 256 < 96 ? (n / 4 + 255) / 256 : 96;
     if (H % 4) return fail(HMOE_E_ARG, "hmoe_ep_combine: H must be a multiple of 4");
-    ep_combine_kernel<<<blocks, 256, 0, st>>>(a, gen, f, n, slot_floats, status, own_rows, H);
+    {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(blocks); cfg.blockDim = dim3(256); cfg.stream = st;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = at; cfg.numAttrs = 1;
+        cudaLaunchKernelEx(&cfg, ep_combine_kernel, a, gen, f, n, slot_floats, status, own_rows, H);
+    }
     count_launches(1);
     const cudaError_t err = cudaGetLastError();
     return err == cudaSuccess ? HMOE_OK : fail(HMOE_E_CUDA, cudaGetErrorString(err));
