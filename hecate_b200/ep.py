@@ -49,6 +49,17 @@ def replica_owners(sel, n_experts, world):
     return owner
 
 
+def prefill_destinations(sel, n_per_rank, world):
+    """Host mirror of hmoe_prefill_ep_dispatch's routing of rows: a boolean array [rows][world], entry (i, p) set when rank p holds
+    one of row i's selected router positions (position e belongs to rank e // n_per_rank; ids outside [0, world * n_per_rank)
+    select no rank). The row's own rank always receives it as well; that is not included here."""
+    import numpy as np
+    sel = np.asarray(sel)
+    valid = (sel >= 0) & (sel < world * n_per_rank)
+    owner = np.where(valid, sel // n_per_rank, -1)
+    return (owner[:, :, None] == np.arange(world)[None, None, :]).any(axis=1)
+
+
 class PeerBuffers:
     """Symmetric buffers of the combine: per rank two fp32 partial slots [MAX_ROWS * H] and `world` generation flags,
     allocated with cudaMalloc by the library, exported with CUDA IPC and opened by every peer."""

@@ -46,6 +46,20 @@ def test_replica_owners_serve_every_pick_once_and_level_the_load():
     assert replica_owners(np.array([[300, -1]]), 256, 4) == {}
 
 
+def test_prefill_destinations_mask():
+    """The all-to-all-v's row routing: a row goes to the ranks that hold one of its experts; foreign ids go nowhere; the share of
+    (row, rank) pairs skipped under uniform top-8 routing is (1 - 1/W)^8."""
+    from hecate_b200 import synth
+    from hecate_b200.ep import prefill_destinations
+    sel = np.array([[0, 1, 2, 3, 4, 5, 6, 7], [0, 64, 128, 192, 1, 65, 129, 193], [255, 255, 255, 255, 255, 255, 255, 999], [-1, 300, 400, 500, 600, 700, 800, 900]])
+    m = prefill_destinations(sel, 64, 4)
+    assert m.tolist() == [[True, False, False, False], [True, True, True, True], [False, False, False, True], [False, False, False, False]]
+    for world in (2, 4, 8):
+        s, _ = synth.zipf_routing(5, 0, 4096, 256, 8, 0.0)
+        frac = 1.0 - prefill_destinations(s, 256 // world, world).mean()
+        assert abs(frac - (1 - 1 / world) ** 8) < 0.02, (world, frac)
+
+
 def _rank_main(rank, world, port, out_path):
     sys.path.insert(0, ROOT); sys.path.insert(0, os.path.join(ROOT, "tests"))
     import torch
