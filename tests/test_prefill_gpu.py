@@ -121,6 +121,30 @@ def test_prefill_row_block_edges(oracle, dev):
     assert errors(out.cpu().numpy(), ref)[2] < NORM_REL_EXACT
 
 
+@pytest.mark.parametrize("n", [1, 15, 16, 17, 63, 64, 65, 127, 128, 129, 191, 192, 193, 255])
+def test_prefill_pick_counts_around_the_input_box_size(oracle, dev, n):
+    """One expert with exactly n picks (the input tile is loaded as boxes of 64 rows, the MMA runs over n rounded up to 16): the
+    rows behind the block belong to another expert's block and must neither be read into the result nor written."""
+    import torch
+    from hecate_b200 import moe
+    H, I, E = 256, 128, 8
+    R = 300
+    sel = np.full((R, 8), 1000, dtype=np.int64)             # ids no expert holds
+    sel[:n, 0] = 2                                          # expert 2: n picks
+    sel[:, 1] = 5                                           # expert 5: every row (its blocks follow expert 2's in the gathered order)
+    rw = (synth.uniform(6, 1, R * 8).reshape(R, 8) * 0.3 + 0.05).astype(np.float16)
+    hl = HostLayer(0, 0, H, I, range(E), 128, False)
+    tabs = hl.upload(dev)
+    x = synth.activations(2, 0, R, H).astype(np.float16)
+    ex, _ = hl.oracle_experts(oracle)
+    ref = oracle.moe_forward(H, I, 128, x, sel, rw, 0, ex, None, mode=1)
+    ws = moe.prefill_workspace(R, 8, E, H, I, dev)
+    out = torch.zeros(R, H, device=dev)
+    moe.prefill(tabs, torch.from_numpy(x).to(dev), torch.from_numpy(sel).to(dev), torch.from_numpy(rw).to(dev), out, ws)
+    assert moe.ws_status(ws) == 0
+    assert errors(out.cpu().numpy(), ref)[2] < NORM_REL_EXACT
+
+
 def test_prefill_adds_into_out_and_is_linear_in_weights(dev):
     """out is added into; doubling every routing weight doubles the routed part (the shared expert's part stays)."""
     import torch
