@@ -691,7 +691,10 @@ def run_ep(args, world, rank, dev):
     if L > 0:
         del layer, tabs
         torch.cuda.empty_cache()
-        res = stack_arm(args, world, rank, dev, L, torch, dist, ep, moe, synth)
+        try:
+            res = stack_arm(args, world, rank, dev, L, torch, dist, ep, moe, synth)
+        except Exception as exc:                    # the headline arms above are measured already: report the failure, keep the line
+            res = {"metric": "moe_stack_decode_us_per_layer", "error": f"{type(exc).__name__}: {exc}"[:300], "layers": L}
         if rank == 0:
             if line is None:
                 line = dict(res, n_gpus=world, higher_is_better=True, scaling="strong", vs_baseline=None, data="synthetic")
