@@ -124,6 +124,9 @@ __global__ void __launch_bounds__(STHREADS, 1) shared_i8_kernel(const SharedArgs
         const int row = (int) (seg0 / KB);
         const long long seg1 = (long long) (row + 1) * KB < U1 ? (long long) (row + 1) * KB : U1;
         long long u = seg0 + warp;
+        // the segment's row scale of this thread's output column (the same for all of its outputs: they are 512 apart), requested
+        // now so that its latency is spent under the units and not in front of the reductions
+        const float sc_n = __ldg((DOWN ? a.down_s : (row >= NG ? a.up_s : a.gate_s)) + (row % NG) * 64 + (threadIdx.x & 63));
         uint4 w[4], wn[4];
         uint32_t b[2][4], bn[2][4];
         if (u < seg1) load_w(u, w);              // weights do not depend on the kernel before: requested while it drains
@@ -163,7 +166,6 @@ __global__ void __launch_bounds__(STHREADS, 1) shared_i8_kernel(const SharedArgs
             }
         __syncthreads();
         const int mat = row >= NG ? 1 : 0, gr = row % NG;
-        const float* sc = (DOWN ? a.down_s : (mat ? a.up_s : a.gate_s)) + gr * 64;
         for (int i = threadIdx.x; i < 1024; i += STHREADS)
         {
             const int r = i >> 6, n = i & 63;                        // tile column (row of the step), row of the group: consecutive n per warp
@@ -173,7 +175,7 @@ __global__ void __launch_bounds__(STHREADS, 1) shared_i8_kernel(const SharedArgs
                 #pragma unroll
                 for (int ww = 0; ww < SW; ++ww) v += part[ww * PART + r * 65 + n];
                 float* dst = DOWN ? yout + (size_t) r * a.H + gr * 64 + n : a.gs + (size_t) r * 2 * a.I + (size_t) mat * a.I + gr * 64 + n;
-                red_add_f32(dst, v * __ldg(sc + n));
+                red_add_f32(dst, v * sc_n);
             }
         }
         __syncthreads();
