@@ -36,7 +36,7 @@ def lib():
         L.hmoe_last_error.restype = C.c_char_p
         L.hmoe_launch_count.restype = C.c_int64
         for n in ("hmoe_router_ws_bytes", "hmoe_decode_ws_bytes", "hmoe_prefill_ws_bytes", "hmoe_permute_ws_bytes", "hmoe_prefill_sorted_ws_bytes",
-                  "hmoe_ep_stage_bytes", "hmoe_prefill_ep_stage_bytes"):
+                  "hmoe_ep_stage_bytes", "hmoe_prefill_ep_stage_bytes", "hmoe_short_prefill_ws_bytes", "hmoe_forward_ws_bytes"):
             getattr(L, n).restype = C.c_size_t
         _lib = L
     return _lib

@@ -246,18 +246,32 @@ __device__ __forceinline__ uint2 norm_pack4(const float4 v, float4 w, float cbia
 // runtime/tier/moe4/moe4.cu:86-110), followed by the shared expert if there is one. Each expert's rows are cut into
 // tiles of <= 8 rows: a tile is the unit the expert kernels work on (its rows are the 8 columns of the MMAs). An expert
 // picked by more than 8 rows therefore appears as two tiles and is streamed twice (the second pass hits L2).
-struct Route
+template <int NT>
+struct RouteT
 {
     int m;                          // distinct routed experts
     int ntiles;
     int pad[2];
-    short expert[MAXT];             // local expert id of the tile (-1 = shared)
-    unsigned char nrows[MAXT];      // rows in the tile (1..8)
-    unsigned char rows[MAXT][8];    // their row numbers, ascending; entries >= nrows repeat the first row
-    float w[MAXT][8];               // routing weight per listed row (summed over repeated picks), 0 beyond nrows
-    short rowbase[MAXT];            // number of real rows in the tiles before this one (row index of the tile's first row in
+    short expert[NT];               // local expert id of the tile (-1 = shared)
+    unsigned char nrows[NT];        // rows in the tile (1..8)
+    unsigned char rows[NT][8];      // their row numbers, ascending; entries >= nrows repeat the first row
+    float w[NT][8];                 // routing weight per listed row (summed over repeated picks), 0 beyond nrows
+    short rowbase[NT];              // number of real rows in the tiles before this one (row index of the tile's first row in
                                     // the per-pick buffers; at most rows * (topk + 1) real rows per call)
     int split[2][MAXB + 1];         // streaming kernels (0 gate_up, 1 down): block b works on items [split[b], split[b + 1])
 };
+using Route = RouteT<MAXT>;
+
+// Short prefill: more rows than a decode call takes, still so few that most experts see fewer than eight of them, so the
+// streaming kernels (every distinct expert read once at memory speed) beat the grouped tensor-core GEMMs (whose weight
+// conversion costs the same for a 3-pick row block as for a 256-pick one). The reference has the same range between its
+// decode and its grouped-GEMM paths (runtime/tier/tier_split.py:341-355: 9..64 rows through the moe4 decode kernels in 8-row
+// chunks, each chunk streaming its experts again); here the whole call is one tile list, so an expert is streamed once per
+// eight of its picks. A pick is one tile column (an expert picked twice by a row gets two columns of that row).
+constexpr int SHORT_MAXR = 255;               // row numbers are bytes
+// tiles: one partial tile per local expert and for the shared expert, plus the full ones
+constexpr int SHORT_MAXT = 256 + 1 + (SHORT_MAXR * TOPK_MAX) / 8 + SHORT_MAXR / 8 + 2;
+using RouteShort = RouteT<SHORT_MAXT>;
+constexpr int FORWARD_SHORT_ROWS = 255;     // hmoe_forward: calls of up to this many rows take the short path
 
 }  // namespace hmoe

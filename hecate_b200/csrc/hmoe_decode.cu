@@ -60,6 +60,105 @@ __global__ void __launch_bounds__(256) decode_prepare_kernel(const void* __restr
     else build_route<false>(S, sel, rw, R, H, I, topk, lo, n_local, has_shared, sh_mod, sh_rem, gen_bump, route, nblocks, threadIdx.x);
 }
 
+// Set-up step of a short-prefill call: blocks 0 .. R-1 rewrite one row each exactly like the decode set-up; the last block
+// builds the tile list from the selections. One thread per local expert (and one for the shared expert) walks the picks in
+// order (they sit in shared memory and all threads read the same entry, a broadcast): once to count its picks, then,
+// knowing from a prefix sum where its tiles and its rows of the per-pick buffer start, once more to write its tiles. Tiles
+// therefore come in ascending expert order with their picks in row order, the shared expert last, as in a decode call.
+constexpr int SHORT_THREADS = 288;          // >= 256 local experts + the shared expert
+__global__ void __launch_bounds__(SHORT_THREADS) short_prepare_kernel(const void* __restrict__ x, int x_kind, const int64_t* __restrict__ sel,
+    const __half* __restrict__ rw, int R, int H, int topk, int lo, int n_local, int has_shared, int act_quant,
+    __half* __restrict__ xf, float* __restrict__ xscale, RouteShort* __restrict__ route, int sh_mod, int sh_rem,
+    float4* __restrict__ gzero, int gzero_n, int I, int nblocks)
+{
+    __shared__ short s_sel[SHORT_MAXR * TOPK_MAX];
+    __shared__ int s_n[SHORT_THREADS], s_t0[SHORT_THREADS], s_rb[SHORT_THREADS];
+    __shared__ int s_cum[2][SHORT_MAXT + 1];
+    __shared__ unsigned char s_nn[SHORT_MAXT];
+    __shared__ int s_nt;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // the next kernel's blocks may set up while this one runs
+    if ((int) blockIdx.x < R) { prepare_row(x, x_kind, blockIdx.x, H, act_quant, xf, xscale, gzero, gzero_n, threadIdx.x, blockDim.x); return; }
+    const int tid = threadIdx.x, P = R * topk, ns = n_local + (has_shared ? 1 : 0);
+    for (int i = tid; i < P; i += SHORT_THREADS)
+    {
+        const int64_t e = sel[i] - lo;
+        s_sel[i] = (e >= 0 && e < n_local) ? (short) e : (short) -1;
+    }
+    __syncthreads();
+    const bool routed = tid < n_local, shared = has_shared && tid == n_local;
+    int n = 0;
+    if (routed)
+        for (int i = 0; i < P; ++i) n += s_sel[i] == tid ? 1 : 0;
+    else if (shared)
+        for (int r = 0; r < R; ++r) n += r % sh_mod == sh_rem ? 1 : 0;
+    s_n[tid] = n;
+    __syncthreads();
+    if (tid == 0)
+    {
+        int t = 0, rb = 0, m = 0;
+        for (int e = 0; e < ns; ++e) { s_t0[e] = t; s_rb[e] = rb; t += (s_n[e] + 7) >> 3; rb += s_n[e]; m += (e < n_local && s_n[e] > 0) ? 1 : 0; }
+        s_nt = t;
+        route->m = m; route->ntiles = t; route->pad[0] = route->pad[1] = 0;
+    }
+    __syncthreads();
+    const int nt = s_nt;
+    if (n > 0)
+    {
+        const int t0 = s_t0[tid], rb = s_rb[tid];
+        for (int b8 = 0, t = t0; b8 < n; b8 += 8, ++t)
+        {
+            const int nn = n - b8 < 8 ? n - b8 : 8;
+            route->expert[t] = routed ? (short) tid : (short) -1; route->nrows[t] = (unsigned char) nn; route->rowbase[t] = (short) (rb + b8);
+            s_nn[t] = (unsigned char) nn;
+        }
+        int pos = 0, first = 0;
+        auto put = [&](int row, float wgt) {
+            const int t = t0 + (pos >> 3), c = pos & 7;
+            if (c == 0) first = row;
+            route->rows[t][c] = (unsigned char) row; route->w[t][c] = wgt;
+            ++pos;
+        };
+        if (routed)
+        {
+            int i = 0;
+            for (int r = 0; r < R; ++r)
+                for (int k = 0; k < topk; ++k, ++i)
+                    if (s_sel[i] == tid) put(r, __half2float(rw[i]));
+        }
+        else
+            for (int r = 0; r < R; ++r)
+                if (r % sh_mod == sh_rem) put(r, 1.f);
+        // columns beyond the picks of the last tile: the tile's first row again, weight 0 (computed, never written out)
+        for (int c = n & 7; c != 0 && c < 8; ++c) { route->rows[t0 + (n >> 3)][c] = (unsigned char) first; route->w[t0 + (n >> 3)][c] = 0.f; }
+    }
+    __syncthreads();
+    // the blocks' item ranges, cut at equal cost (the cost model of the decode set-up: an item of a tile with more real rows
+    // issues more reductions)
+    const int J0 = 2 * (I / 64), J1 = H / 64;
+    if (tid == 0)
+    {
+        int c0 = 0, c1 = 0;
+        for (int t = 0; t < nt; ++t) { s_cum[0][t] = c0; s_cum[1][t] = c1; c0 += J0 * (400 + s_nn[t]); c1 += J1 * (100 + 3 * s_nn[t]); }
+        s_cum[0][nt] = c0; s_cum[1][nt] = c1;
+    }
+    __syncthreads();
+    for (int i = tid; i < 2 * (nblocks + 1); i += SHORT_THREADS)
+    {
+        const int k = i / (nblocks + 1), b = i % (nblocks + 1), J = k ? J1 : J0;
+        int p = nt * J;
+        if (b < nblocks && nt > 0)
+        {
+            const int target = (int) ((long long) s_cum[k][nt] * b / nblocks);
+            int lo2 = 0, hi = nt - 1;                    // last tile whose start is <= target
+            while (lo2 < hi) { const int mid = (lo2 + hi + 1) >> 1; if (s_cum[k][mid] <= target) lo2 = mid; else hi = mid - 1; }
+            const int item = k ? 100 + 3 * s_nn[lo2] : 400 + s_nn[lo2];
+            const int off = (target - s_cum[k][lo2]) / item;
+            p = lo2 * J + (off < J ? off : J);
+        }
+        route->split[k][b] = p;
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------------------------
 // What a warp needs from global memory for its two 64-column blocks (one 128-column scale group) of a ring stage,
 // fetched one stage ahead.
@@ -616,7 +715,7 @@ struct StreamSmem
     static constexpr int total = flags + 16;
 };
 
-template <bool GROUPED, bool Q8, bool DOWN, int KC>
+template <bool GROUPED, bool Q8, bool DOWN, int KC, typename RT = Route>
 __global__ void __launch_bounds__(NTHREADS, 1) decode_stream_kernel(const DecodeArgs a)
 {
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -640,7 +739,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_stream_kernel(const Decode
     // wait too, so that a grid with nothing to do cannot release its dependents early.
     TL_MIN(DOWN ? 8 : 0);
     if (!DOWN) { pdl_wait(); pdl_launch_dependents(); TL_MIN(2); }
-    const Route* rt = a.route;
+    const RT* rt = reinterpret_cast<const RT*>(a.route);          // RT = RouteShort: the same fields with room for more tiles
     const int K = DOWN ? a.I : a.H, N = DOWN ? a.H : a.I;          // input columns and output rows of one matrix
     const int KB = K / 64, NG = N / 64, J = DOWN ? NG : 2 * NG;
     const int p0 = rt->split[DOWN][blockIdx.x], p1 = rt->split[DOWN][blockIdx.x + 1];      // cut at equal cost by the prepare kernel
@@ -1040,6 +1139,82 @@ int decode_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t
     else if (v == 2) launch_pair<true, false>(grid, a, R, st);
     else launch_pair<true, true>(grid, a, R, st);
     count_launches(prepared ? 2 : 3);
+    const cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) return fail(HMOE_E_CUDA, cudaGetErrorString(err));
+    return HMOE_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Short prefill (1 .. SHORT_MAXR rows): set-up kernel + the two streaming kernels over one tile list for the whole call.
+size_t short_ws_bytes(int R, int H, int I, int topk)
+{
+    size_t b = 256;                                      // status word + padding
+    b += up256(sizeof(RouteShort));
+    b += up256((size_t) R * H * 2);                      // xf
+    b += up256((size_t) R * (H / 32) * 4);               // xscale
+    b += up256((size_t) R * (topk + 1) * 2 * I * 4);     // per-pick gate / up sums
+    return b;
+}
+
+template <bool G, bool Q, int KC>
+static void launch_short_gate_up(int grid, const DecodeArgs& a, cudaStream_t st)
+{
+    static DeviceOnce once;
+    if (once.first()) cudaFuncSetAttribute(decode_stream_kernel<G, Q, false, KC, RouteShort>, cudaFuncAttributeMaxDynamicSharedMemorySize, StreamSmem::total);
+    launch_dependent(decode_stream_kernel<G, Q, false, KC, RouteShort>, grid, a, st);
+}
+
+template <bool G, bool Q>
+static void launch_short_pair(int grid, const DecodeArgs& a, cudaStream_t st)
+{
+    static DeviceOnce once;
+    if (once.first()) cudaFuncSetAttribute(decode_stream_kernel<G, Q, true, 1, RouteShort>, cudaFuncAttributeMaxDynamicSharedMemorySize, StreamSmem::total);
+    if (a.H <= 2048) launch_short_gate_up<G, Q, 1>(grid, a, st);
+    else if (a.H <= 4096) launch_short_gate_up<G, Q, 2>(grid, a, st);
+    else launch_short_gate_up<G, Q, 3>(grid, a, st);
+    launch_dependent(decode_stream_kernel<G, Q, true, 1, RouteShort>, grid, a, st);
+}
+
+int short_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
+                 int act_quant, float* y, void* ws, size_t ws_bytes, cudaStream_t st)
+{
+    const int H = L->H, I = L->I;
+    if (R < 1 || R > SHORT_MAXR) return fail(HMOE_E_ARG, "hmoe_short_prefill: rows must be 1..255");
+    if (L->topk < 1 || L->topk > TOPK_MAX) return fail(HMOE_E_ARG, "hmoe_short_prefill: topk must be 1..8");
+    if (H % 128 || I % 128 || H < 128 || I < 128) return fail(HMOE_E_ARG, "hmoe_short_prefill: H and I must be multiples of 128");
+    if (!(I <= 2048 && H <= 6144)) return fail(HMOE_E_UNSUPPORTED, "hmoe_short_prefill: needs H <= 6144 and I <= 2048");
+    if (L->shared_format == 1 && L->sh_gate_w != nullptr) return fail(HMOE_E_UNSUPPORTED, "hmoe_short_prefill: the int8 shared expert is served by hmoe_decode and hmoe_prefill");
+    if (n_local < 0 || n_local > 256) return fail(HMOE_E_ARG, "hmoe_short_prefill: at most 256 local experts");
+    if (!(L->group == 0 && L->scale_dtype == HMOE_F32) && !(L->group == 128 && L->scale_dtype == HMOE_BF16))
+        return fail(HMOE_E_ARG, "hmoe_short_prefill: scales must be fp32 per row (group 0) or bf16 per 128 columns");
+    if (x_dtype != HMOE_F16 && x_dtype != HMOE_BF16) return fail(HMOE_E_ARG, "hmoe_short_prefill: x must be fp16 or bf16");
+    if (!x || !sel || !rw || !y || !ws) return fail(HMOE_E_ARG, "hmoe_short_prefill: null pointer");
+    if (ws_bytes < short_ws_bytes(R, H, I, L->topk)) return fail(HMOE_E_WS, "hmoe_short_prefill: workspace too small");
+    const int g_sms = device_sms();
+    if (g_sms <= 0) return fail(HMOE_E_CUDA, "hmoe_short_prefill: no current CUDA device");
+    char* w = (char*) ws;
+    unsigned* status = (unsigned*) w; w += 256;
+    RouteShort* route = (RouteShort*) w; w += up256(sizeof(RouteShort));
+    __half* xf = (__half*) w; w += up256((size_t) R * H * 2);
+    float* xscale = (float*) w; w += up256((size_t) R * (H / 32) * 4);
+    float* G = (float*) w;
+    const int has_shared = L->sh_gate_w != nullptr;
+    const int grid = g_sms < MAXB ? g_sms : MAXB;
+    short_prepare_kernel<<<R + 1, SHORT_THREADS, 0, st>>>(x, x_dtype == HMOE_BF16 ? 1 : 0, sel, (const __half*) rw, R, H, L->topk, lo, n_local, has_shared,
+                                                          act_quant, xf, xscale, route, 1, 0, (float4*) G, (L->topk + 1) * 2 * I / 4, I, grid);
+    DecodeArgs a;
+    a.H = H; a.I = I;
+    a.gate_w = L->gate_w; a.up_w = L->up_w; a.down_w = L->down_w; a.gate_s = L->gate_s; a.up_s = L->up_s; a.down_s = L->down_s;
+    a.sh_gw = L->sh_gate_w; a.sh_uw = L->sh_up_w; a.sh_dw = L->sh_down_w; a.sh_gs = L->sh_gate_s; a.sh_us = L->sh_up_s; a.sh_ds = L->sh_down_s;
+    a.route = reinterpret_cast<const Route*>(route); a.xf = xf; a.xscale = xscale; a.act = nullptr; a.ascale = nullptr; a.G = G; a.y = y; a.status = status;
+    a.gen_ptr = nullptr; a.slot_stride = 0;
+    a.ep = EpTail();
+    const int v = (L->group ? 2 : 0) + (act_quant ? 1 : 0);
+    if (v == 0) launch_short_pair<false, false>(grid, a, st);
+    else if (v == 1) launch_short_pair<false, true>(grid, a, st);
+    else if (v == 2) launch_short_pair<true, false>(grid, a, st);
+    else launch_short_pair<true, true>(grid, a, st);
+    count_launches(3);
     const cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) return fail(HMOE_E_CUDA, cudaGetErrorString(err));
     return HMOE_OK;

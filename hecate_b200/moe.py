@@ -108,6 +108,53 @@ def prefill(tables, x, sel, rw, out, ws, lo=0, n_local=None, act_quant=False):
     return out
 
 
+def _rows_call(fn, name, tables, x, sel, rw, out, ws, lo, n_local, act_quant):
+    R = x.shape[0]
+    if not (x.is_contiguous() and sel.is_contiguous() and rw.is_contiguous() and out.is_contiguous()):
+        raise HmoeError(name + ": tensors must be contiguous")
+    if sel.dtype != torch.int64 or rw.dtype != torch.float16 or out.dtype != torch.float32:
+        raise HmoeError(name + ": sel int64, rw fp16, out fp32 required")
+    if x.shape[1] != tables.H or sel.shape[1] != tables.topk or out.shape[-1] != tables.H:
+        raise HmoeError(name + ": shape")
+    st = tables.struct()
+    check(fn(C.byref(st), vp(x), C.c_int(_dt(x)), vp(sel), vp(rw), C.c_int(R), C.c_int(lo),
+             C.c_int(tables.n if n_local is None else n_local), C.c_int(int(act_quant)), vp(out), vp(ws),
+             C.c_size_t(ws.numel()), _stream(x.device)))
+    return out
+
+
+def short_prefill_workspace(R, H, I, topk, device):
+    n = lib().hmoe_short_prefill_ws_bytes(C.c_int(R), C.c_int(H), C.c_int(I), C.c_int(topk))
+    if n == 0:
+        raise HmoeError("short_prefill_workspace: rows must be 1..255")
+    return torch.zeros(n, dtype=torch.uint8, device=device)
+
+
+def short_prefill(tables, x, sel, rw, out, ws, lo=0, n_local=None, act_quant=False):
+    """out[R][H] (fp32) += experts(x) for 1..255 rows through the decode streaming kernels, the whole call as one tile list
+    (the counterpart of tier_split._hot_prefill's 8-row chunks of moe4.forward, tier_split.py:341-355)."""
+    return _rows_call(lib().hmoe_short_prefill, "short_prefill", tables, x, sel, rw, out, ws, lo, n_local, act_quant)
+
+
+def forward_short_rows():
+    """Calls of 17 .. this many rows take the short path in `forward`."""
+    return int(lib().hmoe_forward_short_rows())
+
+
+def forward_workspace(R, topk, n_local, H, I, device, act_quant=False):
+    n = lib().hmoe_forward_ws_bytes(C.c_int(R), C.c_int(topk), C.c_int(n_local), C.c_int(H), C.c_int(I), C.c_int(int(act_quant)))
+    if n == 0:
+        raise HmoeError("forward_workspace: rows >= 1, topk 1..8")
+    return torch.zeros(n, dtype=torch.uint8, device=device)
+
+
+def forward(tables, x, sel, rw, out, ws, lo=0, n_local=None, act_quant=False):
+    """out[R][H] (fp32) += experts(x) for any number of rows; the library picks decode, short prefill or the grouped GEMMs
+    by the row count, as tier_submit / _hot_prefill do among the reference's kernels (tier_split.py:341-364,543-546).
+    ws: forward_workspace(R_max, ...), good for every call of up to R_max rows."""
+    return _rows_call(lib().hmoe_forward, "forward", tables, x, sel, rw, out, ws, lo, n_local, act_quant)
+
+
 def moe4t_scratch(device, npos, H=6144, I=2048, act_quant=False):
     """moe4t.scratch(device, npos) -> [gu, ar, d] (moe4t.cu:490-495). Here one workspace tensor stands for all three (it holds
     the gathered inputs and the intermediate activations); the other two entries keep call sites that unpack three working."""

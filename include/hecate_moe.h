@@ -179,6 +179,25 @@ size_t hmoe_prefill_ws_bytes(int R, int topk, int n_local, int H, int I, int act
 int hmoe_prefill(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
                  int act_quant, float* out, void* ws, size_t ws_bytes, void* stream);
 
+/* Short prefill: the range between a decode call and the grouped GEMMs, 1..255 rows (replaces the branch of _hot_prefill,
+ * runtime/tier/tier_split.py:341-355, that runs 9..64 rows through moe4.forward in 8-row chunks, each chunk streaming its
+ * experts again). The whole call is one list of (expert, <= 8 picks) tiles for the decode streaming kernels, so a distinct
+ * expert is read from memory once per eight of its picks; the grouped GEMMs convert every expert's weights whatever its row
+ * count and only win from about a hundred rows up. Arguments as hmoe_prefill (out is added into). Needs H <= 6144, I <= 2048
+ * and the int4 shared expert (else HMOE_E_UNSUPPORTED). ws: hmoe_short_prefill_ws_bytes(R, ...) bytes, 0 for R outside 1..255. */
+size_t hmoe_short_prefill_ws_bytes(int R, int H, int I, int topk);
+int hmoe_short_prefill(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
+                       int act_quant, float* out, void* ws, size_t ws_bytes, void* stream);
+
+/* One entry point for any number of rows, as tier_submit / _hot_prefill choose among the reference's kernels by row count
+ * (runtime/tier/tier_split.py:341-364,543-546): R <= 16 -> hmoe_decode, R <= hmoe_forward_short_rows() -> hmoe_short_prefill
+ * (when the layer's shapes and shared-expert format allow it), else hmoe_prefill. One workspace serves every row count up to
+ * the R it was sized for: hmoe_forward_ws_bytes(R_max, ...) bytes, zero-filled once. */
+int hmoe_forward_short_rows(void);
+size_t hmoe_forward_ws_bytes(int R, int topk, int n_local, int H, int I, int act_quant);
+int hmoe_forward(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
+                 int act_quant, float* out, void* ws, size_t ws_bytes, void* stream);
+
 /* hmoe_prefill for one rank of an expert-parallel group (no reference counterpart): experts split by lo / n_local as above;
  * the shared expert is applied to rows [shared_row0, shared_row0 + shared_rows) only (the rank's own tokens). */
 int hmoe_prefill_ep(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
