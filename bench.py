@@ -446,6 +446,35 @@ def decode_arm(args, dev, layer, torch, moe, synth, O):
         small[str(r)] = {"us_per_layer": ms_r * 1e3, "distinct_experts": float(np.mean(d_r)),
                          "layer_hbm_frac": bytes_r / (ms_r * 1e-3) / 1e9 / peaks()["hbm"], **({"timeline_us": tl_r} if tl_r else {})}
 
+    # larger batches than a decode call takes (the range the reference serves with 8-row chunks of its decode kernels,
+    # tier_split.py:341-355): the short-prefill call (routing given) next to the grouped GEMMs on the same inputs, and the share
+    # of the HBM rate the distinct experts' bytes reach
+    short = {}
+    for r in (32, 64, 128):
+        xm = [torch.from_numpy(synth.activations(40 + b, 0, r, H)).to(torch.bfloat16).to(dev) for b in range(2)]
+        rm = [synth.zipf_routing(50 + b, 0, r, n_exp, TOPK, 0.0) for b in range(2)]
+        sm = [torch.from_numpy(q[0]).to(dev) for q in rm]; wm = [torch.from_numpy(q[1]).to(dev) for q in rm]
+        o_s, o_g = torch.zeros(r, H, dtype=torch.float32, device=dev), torch.zeros(r, H, dtype=torch.float32, device=dev)
+        ws_s, ws_g = moe.short_prefill_workspace(r, H, I, TOPK, dev), moe.prefill_workspace(r, TOPK, n_exp, H, I, dev)
+
+        def step_s(b):
+            o_s.zero_(); moe.short_prefill(tabs, xm[b], sm[b], wm[b], o_s, ws_s)
+
+        def step_g(b):
+            o_g.zero_(); moe.prefill(tabs, xm[b], sm[b], wm[b], o_g, ws_g)
+        step_s(0); step_g(0)
+        agree = float(((o_s - o_g).norm() / o_g.norm().clamp_min(1e-30)).item())
+        run_s, _ = make_graphed(step_s, [0, 1], torch, moe, not args.no_graph)
+        run_g, _ = make_graphed(step_g, [0, 1], torch, moe, not args.no_graph)
+        for i in range(3):
+            run_s(i % 2); run_g(i % 2)
+        ms_s, ms_g = timed(torch, run_s, 8, 2), timed(torch, run_g, 8, 2)
+        d_m = float(np.mean([len(np.unique(q[0])) for q in rm]))
+        short[str(r)] = {"us_per_layer": ms_s * 1e3, "grouped_gemms_us_per_layer": ms_g * 1e3, "distinct_experts": d_m,
+                         "layer_hbm_frac": (d_m + 1) * EXPERT_BYTES / (ms_s * 1e-3) / 1e9 / peaks()["hbm"],
+                         "norm_rel_short_vs_grouped_gemms": agree, "device_status": int(moe.ws_status(ws_s))}
+        del ws_s, ws_g
+
     # parity on this very layer, outside the timed regions: the router's selection bit for bit, two rows of batch 0 in both modes
     parity = {}
     if O is not None:
@@ -481,7 +510,7 @@ def decode_arm(args, dev, layer, torch, moe, synth, O):
         "e2e": {"value": ROWS / e2e_s, "unit": UNIT, "h2d_bytes_per_step": ROWS * H * 2, "d2h_bytes_per_step": ROWS * H * 4,
                 "us_per_layer": e2e_s * 1e6},
         "act_quant": {"decode_us_per_layer": ms_q * 1e3, "decode_vs_default": ms_q / ms_per_step},
-        "small_batches": small, **({"timeline_us": timeline} if timeline else {}),
+        "small_batches": small, "short_prefill": short, **({"timeline_us": timeline} if timeline else {}),
         "parity_check": {"decode": parity},
         "gpu_launches": int(launches), "device_status": int(status), "clocks": cs.summary(),
     }
