@@ -61,87 +61,124 @@ __global__ void __launch_bounds__(256) decode_prepare_kernel(const void* __restr
 }
 
 // Set-up step of a short-prefill call: blocks 0 .. R-1 rewrite one row each exactly like the decode set-up; the last block
-// builds the tile list from the selections. One thread per local expert (and one for the shared expert) walks the picks in
-// order (they sit in shared memory and all threads read the same entry, a broadcast): once to count its picks, then,
-// knowing from a prefix sum where its tiles and its rows of the per-pick buffer start, once more to write its tiles. Tiles
-// therefore come in ascending expert order with their picks in row order, the shared expert last, as in a decode call.
-constexpr int SHORT_THREADS = 288;          // >= 256 local experts + the shared expert
+// builds the tile list from the selections. The picks are counted per expert with shared-memory atomics; one warp turns the
+// counts into prefix sums (first tile, first row of the per-pick buffer, cost before the expert's items); every expert's
+// thread writes the headers of its tiles; one warp then walks the picks in order, 32 at a time (lanes with the same expert
+// find each other with a match, the expert's fill count moves on by the size of the group), and writes every pick into its
+// tile column. Tiles therefore come in ascending expert order with their picks in row order, the shared expert last, as in
+// a decode call.
+constexpr int SHORT_THREADS = 288;          // >= 256 local experts + the shared expert; nine slots per lane in the prefix warp
 __global__ void __launch_bounds__(SHORT_THREADS) short_prepare_kernel(const void* __restrict__ x, int x_kind, const int64_t* __restrict__ sel,
     const __half* __restrict__ rw, int R, int H, int topk, int lo, int n_local, int has_shared, int act_quant,
     __half* __restrict__ xf, float* __restrict__ xscale, RouteShort* __restrict__ route, int sh_mod, int sh_rem,
     float4* __restrict__ gzero, int gzero_n, int I, int nblocks)
 {
     __shared__ short s_sel[SHORT_MAXR * TOPK_MAX];
-    __shared__ int s_n[SHORT_THREADS], s_t0[SHORT_THREADS], s_rb[SHORT_THREADS];
+    __shared__ int s_n[SHORT_THREADS], s_fill[SHORT_THREADS], s_pre[4][SHORT_THREADS];      // s_pre: tiles, rows, cost in gate_up, cost in down before the slot
     __shared__ int s_cum[2][SHORT_MAXT + 1];
     __shared__ unsigned char s_nn[SHORT_MAXT];
-    __shared__ int s_nt;
+    __shared__ int s_tot[4];
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // the next kernel's blocks may set up while this one runs
     if ((int) blockIdx.x < R) { prepare_row(x, x_kind, blockIdx.x, H, act_quant, xf, xscale, gzero, gzero_n, threadIdx.x, blockDim.x); return; }
-    const int tid = threadIdx.x, P = R * topk, ns = n_local + (has_shared ? 1 : 0);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, P = R * topk, ns = n_local + (has_shared ? 1 : 0);
+    const int J0 = 2 * (I / 64), J1 = H / 64;
+    // the cost model of the decode set-up: an item of a tile with more real rows issues more reductions
+    auto cost0 = [&](int n) { return J0 * ((n >> 3) * 408 + ((n & 7) ? 400 + (n & 7) : 0)); };
+    auto cost1 = [&](int n) { return J1 * ((n >> 3) * 124 + ((n & 7) ? 100 + 3 * (n & 7) : 0)); };
+    s_n[tid] = 0; s_fill[tid] = 0;
+    __syncthreads();
     for (int i = tid; i < P; i += SHORT_THREADS)
     {
         const int64_t e = sel[i] - lo;
-        s_sel[i] = (e >= 0 && e < n_local) ? (short) e : (short) -1;
+        const bool mine = e >= 0 && e < n_local;
+        s_sel[i] = mine ? (short) e : (short) -1;
+        if (mine) atomicAdd(&s_n[(int) e], 1);
+    }
+    if (has_shared && tid == 0) s_n[n_local] = (R + sh_mod - 1 - sh_rem) / sh_mod;       // rows r < R with r % sh_mod == sh_rem
+    __syncthreads();
+    const int n = tid < ns ? s_n[tid] : 0;
+    const int m = __syncthreads_count(tid < n_local && n > 0);
+    if (warp == 0)
+    {
+        constexpr int PER = SHORT_THREADS / 32;
+        int v[4] = {0, 0, 0, 0};
+        #pragma unroll
+        for (int k = 0; k < PER; ++k)
+        {
+            const int e = lane * PER + k, ne = e < ns ? s_n[e] : 0;
+            v[0] += (ne + 7) >> 3; v[1] += ne; v[2] += cost0(ne); v[3] += cost1(ne);
+        }
+        int incl[4] = {v[0], v[1], v[2], v[3]};
+        #pragma unroll
+        for (int o = 1; o < 32; o <<= 1)
+            #pragma unroll
+            for (int c = 0; c < 4; ++c) { const int t = __shfl_up_sync(0xffffffffu, incl[c], o); if (lane >= o) incl[c] += t; }
+        int run[4] = {incl[0] - v[0], incl[1] - v[1], incl[2] - v[2], incl[3] - v[3]};
+        #pragma unroll
+        for (int k = 0; k < PER; ++k)
+        {
+            const int e = lane * PER + k, ne = e < ns ? s_n[e] : 0;
+            #pragma unroll
+            for (int c = 0; c < 4; ++c) s_pre[c][e] = run[c];
+            run[0] += (ne + 7) >> 3; run[1] += ne; run[2] += cost0(ne); run[3] += cost1(ne);
+        }
+        if (lane == 31)
+            #pragma unroll
+            for (int c = 0; c < 4; ++c) s_tot[c] = incl[c];
     }
     __syncthreads();
-    const bool routed = tid < n_local, shared = has_shared && tid == n_local;
-    int n = 0;
-    if (routed)
-        for (int i = 0; i < P; ++i) n += s_sel[i] == tid ? 1 : 0;
-    else if (shared)
-        for (int r = 0; r < R; ++r) n += r % sh_mod == sh_rem ? 1 : 0;
-    s_n[tid] = n;
-    __syncthreads();
+    const int nt = s_tot[0], t0 = s_pre[0][tid];
     if (tid == 0)
     {
-        int t = 0, rb = 0, m = 0;
-        for (int e = 0; e < ns; ++e) { s_t0[e] = t; s_rb[e] = rb; t += (s_n[e] + 7) >> 3; rb += s_n[e]; m += (e < n_local && s_n[e] > 0) ? 1 : 0; }
-        s_nt = t;
-        route->m = m; route->ntiles = t; route->pad[0] = route->pad[1] = 0;
+        route->m = m; route->ntiles = nt; route->pad[0] = route->pad[1] = 0;
+        s_cum[0][nt] = s_tot[2]; s_cum[1][nt] = s_tot[3];
     }
-    __syncthreads();
-    const int nt = s_nt;
     if (n > 0)
     {
-        const int t0 = s_t0[tid], rb = s_rb[tid];
+        int c0 = s_pre[2][tid], c1 = s_pre[3][tid];
+        const int rb = s_pre[1][tid];
         for (int b8 = 0, t = t0; b8 < n; b8 += 8, ++t)
         {
             const int nn = n - b8 < 8 ? n - b8 : 8;
-            route->expert[t] = routed ? (short) tid : (short) -1; route->nrows[t] = (unsigned char) nn; route->rowbase[t] = (short) (rb + b8);
-            s_nn[t] = (unsigned char) nn;
+            route->expert[t] = tid < n_local ? (short) tid : (short) -1; route->nrows[t] = (unsigned char) nn; route->rowbase[t] = (short) (rb + b8);
+            s_nn[t] = (unsigned char) nn; s_cum[0][t] = c0; s_cum[1][t] = c1;
+            c0 += J0 * (400 + nn); c1 += J1 * (100 + 3 * nn);
         }
-        int pos = 0, first = 0;
-        auto put = [&](int row, float wgt) {
-            const int t = t0 + (pos >> 3), c = pos & 7;
-            if (c == 0) first = row;
-            route->rows[t][c] = (unsigned char) row; route->w[t][c] = wgt;
-            ++pos;
-        };
-        if (routed)
-        {
-            int i = 0;
-            for (int r = 0; r < R; ++r)
-                for (int k = 0; k < topk; ++k, ++i)
-                    if (s_sel[i] == tid) put(r, __half2float(rw[i]));
-        }
-        else
-            for (int r = 0; r < R; ++r)
-                if (r % sh_mod == sh_rem) put(r, 1.f);
-        // columns beyond the picks of the last tile: the tile's first row again, weight 0 (computed, never written out)
-        for (int c = n & 7; c != 0 && c < 8; ++c) { route->rows[t0 + (n >> 3)][c] = (unsigned char) first; route->w[t0 + (n >> 3)][c] = 0.f; }
     }
-    __syncthreads();
-    // the blocks' item ranges, cut at equal cost (the cost model of the decode set-up: an item of a tile with more real rows
-    // issues more reductions)
-    const int J0 = 2 * (I / 64), J1 = H / 64;
-    if (tid == 0)
+    if (warp == 1)
     {
-        int c0 = 0, c1 = 0;
-        for (int t = 0; t < nt; ++t) { s_cum[0][t] = c0; s_cum[1][t] = c1; c0 += J0 * (400 + s_nn[t]); c1 += J1 * (100 + 3 * s_nn[t]); }
-        s_cum[0][nt] = c0; s_cum[1][nt] = c1;
+        for (int base = 0; base < P; base += 32)
+        {
+            const int i = base + lane, e = i < P ? (int) s_sel[i] : -1;
+            const unsigned peers = __match_any_sync(0xffffffffu, e), before = peers & ((1u << lane) - 1u);
+            if (e >= 0)
+            {
+                const int pos = s_fill[e] + __popc(before), t = s_pre[0][e] + (pos >> 3), c = pos & 7;
+                route->rows[t][c] = (unsigned char) (i / topk); route->w[t][c] = __half2float(rw[i]);
+            }
+            __syncwarp();
+            if (e >= 0 && before == 0) s_fill[e] += __popc(peers);        // the first lane of every group moves the expert's fill count on
+            __syncwarp();
+        }
+    }
+    else if (warp == 2 && has_shared)
+    {
+        for (int r = lane; r < R; r += 32)
+            if (r % sh_mod == sh_rem)
+            {
+                const int pos = (r + sh_mod - 1 - sh_rem) / sh_mod, t = s_pre[0][n_local] + (pos >> 3), c = pos & 7;
+                route->rows[t][c] = (unsigned char) r; route->w[t][c] = 1.f;
+            }
     }
     __syncthreads();
+    // columns beyond the picks of an expert's last tile: the tile's first row again, weight 0 (computed, never written out)
+    if (n & 7)
+    {
+        const int t = t0 + (n >> 3);
+        const unsigned char first = route->rows[t][0];
+        for (int c = n & 7; c < 8; ++c) { route->rows[t][c] = first; route->w[t][c] = 0.f; }
+    }
+    // the blocks' item ranges, cut at equal cost
     for (int i = tid; i < 2 * (nblocks + 1); i += SHORT_THREADS)
     {
         const int k = i / (nblocks + 1), b = i % (nblocks + 1), J = k ? J1 : J0;
