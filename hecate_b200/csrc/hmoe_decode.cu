@@ -154,7 +154,7 @@ __global__ void __launch_bounds__(SHORT_THREADS) short_prepare_kernel(const void
             if (e >= 0)
             {
                 const int pos = s_fill[e] + __popc(before), t = s_pre[0][e] + (pos >> 3), c = pos & 7;
-                route->rows[t][c] = (unsigned char) (i / topk); route->w[t][c] = __half2float(rw[i]);
+                route->rows[t][c] = (unsigned short) (i / topk); route->w[t][c] = __half2float(rw[i]);
             }
             __syncwarp();
             if (e >= 0 && before == 0) s_fill[e] += __popc(peers);        // the first lane of every group moves the expert's fill count on
@@ -167,7 +167,7 @@ __global__ void __launch_bounds__(SHORT_THREADS) short_prepare_kernel(const void
             if (r % sh_mod == sh_rem)
             {
                 const int pos = (r + sh_mod - 1 - sh_rem) / sh_mod, t = s_pre[0][n_local] + (pos >> 3), c = pos & 7;
-                route->rows[t][c] = (unsigned char) r; route->w[t][c] = 1.f;
+                route->rows[t][c] = (unsigned short) r; route->w[t][c] = 1.f;
             }
     }
     __syncthreads();
@@ -175,7 +175,7 @@ __global__ void __launch_bounds__(SHORT_THREADS) short_prepare_kernel(const void
     if (n & 7)
     {
         const int t = t0 + (n >> 3);
-        const unsigned char first = route->rows[t][0];
+        const unsigned short first = route->rows[t][0];
         for (int c = n & 7; c < 8; ++c) { route->rows[t][c] = first; route->w[t][c] = 0.f; }
     }
     // the blocks' item ranges, cut at equal cost
@@ -1216,7 +1216,7 @@ int short_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t*
                  int act_quant, float* y, void* ws, size_t ws_bytes, cudaStream_t st)
 {
     const int H = L->H, I = L->I;
-    if (R < 1 || R > SHORT_MAXR) return fail(HMOE_E_ARG, "hmoe_short_prefill: rows must be 1..255");
+    if (R < 1 || R > SHORT_MAXR) return fail(HMOE_E_ARG, "hmoe_short_prefill: rows must be 1..640");
     if (L->topk < 1 || L->topk > TOPK_MAX) return fail(HMOE_E_ARG, "hmoe_short_prefill: topk must be 1..8");
     if (H % 128 || I % 128 || H < 128 || I < 128) return fail(HMOE_E_ARG, "hmoe_short_prefill: H and I must be multiples of 128");
     if (!(I <= 2048 && H <= 6144)) return fail(HMOE_E_UNSUPPORTED, "hmoe_short_prefill: needs H <= 6144 and I <= 2048");

@@ -126,12 +126,12 @@ def _rows_call(fn, name, tables, x, sel, rw, out, ws, lo, n_local, act_quant):
 def short_prefill_workspace(R, H, I, topk, device):
     n = lib().hmoe_short_prefill_ws_bytes(C.c_int(R), C.c_int(H), C.c_int(I), C.c_int(topk))
     if n == 0:
-        raise HmoeError("short_prefill_workspace: rows must be 1..255")
+        raise HmoeError("short_prefill_workspace: rows must be 1..640")
     return torch.zeros(n, dtype=torch.uint8, device=device)
 
 
 def short_prefill(tables, x, sel, rw, out, ws, lo=0, n_local=None, act_quant=False):
-    """out[R][H] (fp32) += experts(x) for 1..255 rows through the decode streaming kernels, the whole call as one tile list
+    """out[R][H] (fp32) += experts(x) for 1..640 rows through the decode streaming kernels, the whole call as one tile list
     (the counterpart of tier_split._hot_prefill's 8-row chunks of moe4.forward, tier_split.py:341-355)."""
     return _rows_call(lib().hmoe_short_prefill, "short_prefill", tables, x, sel, rw, out, ws, lo, n_local, act_quant)
 

@@ -179,12 +179,12 @@ size_t hmoe_prefill_ws_bytes(int R, int topk, int n_local, int H, int I, int act
 int hmoe_prefill(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
                  int act_quant, float* out, void* ws, size_t ws_bytes, void* stream);
 
-/* Short prefill: the range between a decode call and the grouped GEMMs, 1..255 rows (replaces the branch of _hot_prefill,
+/* Short prefill: the range between a decode call and the grouped GEMMs, 1..640 rows (replaces the branch of _hot_prefill,
  * runtime/tier/tier_split.py:341-355, that runs 9..64 rows through moe4.forward in 8-row chunks, each chunk streaming its
  * experts again). The whole call is one list of (expert, <= 8 picks) tiles for the decode streaming kernels, so a distinct
  * expert is read from memory once per eight of its picks; the grouped GEMMs convert every expert's weights whatever its row
- * count and only win from about a hundred rows up. Arguments as hmoe_prefill (out is added into). Needs H <= 6144, I <= 2048
- * and the int4 shared expert (else HMOE_E_UNSUPPORTED). ws: hmoe_short_prefill_ws_bytes(R, ...) bytes, 0 for R outside 1..255. */
+ * count and only win from several hundred rows up (level at about 640 rows of uniform routing over 256 experts). Arguments as hmoe_prefill (out is added into). Needs H <= 6144, I <= 2048
+ * and the int4 shared expert (else HMOE_E_UNSUPPORTED). ws: hmoe_short_prefill_ws_bytes(R, ...) bytes, 0 for R outside 1..640. */
 size_t hmoe_short_prefill_ws_bytes(int R, int H, int I, int topk);
 int hmoe_short_prefill(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
                        int act_quant, float* out, void* ws, size_t ws_bytes, void* stream);

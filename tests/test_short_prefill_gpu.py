@@ -1,4 +1,4 @@
-"""Short prefill on the GPU (1..255 rows as one tile list for the streaming kernels) against the CPU checker, against the
+"""Short prefill on the GPU (1..640 rows as one tile list for the streaming kernels) against the CPU checker, against the
 grouped GEMMs at the benchmark's widths, and the row-count dispatch of `forward`."""
 import numpy as np
 import pytest
@@ -37,16 +37,17 @@ def _short(oracle, dev, H, I, E, R, group, shared, aq, zipf, seed=0, lo=0, n_loc
         ws = moe.short_prefill_workspace(R, H, I, 8, dev)
         moe.short_prefill(*args, ws, lo=lo, n_local=n_local, act_quant=aq)
     else:
-        ws = moe.forward_workspace(max(R, 400), 8, n_local, H, I, dev, act_quant=aq)      # one workspace for every row count
+        ws = moe.forward_workspace(max(R, 800), 8, n_local, H, I, dev, act_quant=aq)      # one workspace for every row count
         moe.forward(*args, ws, lo=lo, n_local=n_local, act_quant=aq)
     assert moe.ws_status(ws) == 0
     return errors(out.cpu().numpy(), ref)
 
 
 @pytest.mark.parametrize("group", [0, 128])
-@pytest.mark.parametrize("R,zipf,shared", [(1, 0.0, False), (17, 0.0, True), (40, 1.1, True), (100, 0.0, False), (255, 1.3, True)])
+@pytest.mark.parametrize("R,zipf,shared", [(1, 0.0, False), (17, 0.0, True), (40, 1.1, True), (100, 0.0, False), (255, 1.3, True), (257, 0.0, True), (640, 1.1, True)])
 def test_short_prefill_exact_mode_small(oracle, dev, group, R, zipf, shared):
-    """Few experts, so every expert gets many 8-pick tiles (255 rows over 8 experts: 32 tiles each, 32 of the shared expert)."""
+    """Few experts, so every expert gets many 8-pick tiles (640 rows over 8 experts: 80 tiles each under uniform routing, 80 of
+    the shared expert; row numbers beyond 255)."""
     e = _short(oracle, dev, 256, 128, 8, R, group, shared, False, zipf)
     assert e[2] < NORM_REL_EXACT, e
 
@@ -103,7 +104,7 @@ def test_short_prefill_argument_errors(dev):
     H, I, E = 256, 128, 8
     tabs = HostLayer(0, 0, H, I, range(E), 128, False).upload(dev)
     with pytest.raises(moe.HmoeError):
-        moe.short_prefill_workspace(256, H, I, 8, dev)
+        moe.short_prefill_workspace(641, H, I, 8, dev)
     R = 40
     x = torch.zeros(R, H, dtype=torch.float16, device=dev)
     sel = torch.zeros(R, 8, dtype=torch.int64, device=dev); rw = torch.zeros(R, 8, dtype=torch.float16, device=dev)
@@ -113,11 +114,11 @@ def test_short_prefill_argument_errors(dev):
         moe.short_prefill(tabs, x, sel, rw, out, small)
 
 
-@pytest.mark.parametrize("R", [8, 16, 17, 64, 300])
+@pytest.mark.parametrize("R", [8, 16, 17, 64, 300, 384, 385, 700])
 def test_forward_picks_a_path_by_row_count(oracle, dev, R):
     """decode (<= 16 rows), short prefill, grouped GEMMs (> forward_short_rows()): one entry point, one workspace, the same result."""
     from hecate_b200 import moe
-    assert 16 < moe.forward_short_rows() <= 255
+    assert 16 < moe.forward_short_rows() <= 640
     e = _short(oracle, dev, 256, 128, 8, R, 128, True, False, 1.1, call="forward")
     assert e[2] < NORM_REL_EXACT, e
 
