@@ -212,6 +212,14 @@ int hmoe_short_prefill(const hmoe_layer* layer, const void* x, int x_dtype, cons
     return short_launch(layer, x, x_dtype, sel, rw, R, lo, n_local, act_quant, out, ws, ws_bytes, (cudaStream_t) stream);
 }
 
+int hmoe_short_prefill_ep(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
+                          int act_quant, float* out, void* ws, size_t ws_bytes, int shared_row0, int shared_rows, void* stream)
+{
+    if (!layer) return fail(HMOE_E_ARG, "hmoe_short_prefill_ep: null layer");
+    if (shared_rows < 0) return fail(HMOE_E_ARG, "hmoe_short_prefill_ep: shared_rows must be >= 0");
+    return short_launch(layer, x, x_dtype, sel, rw, R, lo, n_local, act_quant, out, ws, ws_bytes, (cudaStream_t) stream, shared_row0, shared_rows);
+}
+
 // Which path serves a call of R rows: 0 decode, 1 short prefill, 2 grouped GEMMs. The short path needs the shapes whose tile
 // activations fit in registers and the int4 shared expert; FORWARD_SHORT_ROWS is where the grouped GEMMs become faster
 // (measured on the benchmark layer: they cost the same from about 100 rows up because every expert's weights are converted

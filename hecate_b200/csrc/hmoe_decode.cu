@@ -70,7 +70,7 @@ __global__ void __launch_bounds__(256) decode_prepare_kernel(const void* __restr
 constexpr int SHORT_THREADS = 288;          // >= 256 local experts + the shared expert; nine slots per lane in the prefix warp
 __global__ void __launch_bounds__(SHORT_THREADS) short_prepare_kernel(const void* __restrict__ x, int x_kind, const int64_t* __restrict__ sel,
     const __half* __restrict__ rw, int R, int H, int topk, int lo, int n_local, int has_shared, int act_quant,
-    __half* __restrict__ xf, float* __restrict__ xscale, RouteShort* __restrict__ route, int sh_mod, int sh_rem,
+    __half* __restrict__ xf, float* __restrict__ xscale, RouteShort* __restrict__ route, int sh_row0, int sh_rows,
     float4* __restrict__ gzero, int gzero_n, int I, int nblocks)
 {
     __shared__ short s_sel[SHORT_MAXR * TOPK_MAX];
@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(SHORT_THREADS) short_prepare_kernel(const void
         s_sel[i] = mine ? (short) e : (short) -1;
         if (mine) atomicAdd(&s_n[(int) e], 1);
     }
-    if (has_shared && tid == 0) s_n[n_local] = (R + sh_mod - 1 - sh_rem) / sh_mod;       // rows r < R with r % sh_mod == sh_rem
+    if (has_shared && tid == 0) s_n[n_local] = sh_rows;                  // the shared expert serves rows [sh_row0, sh_row0 + sh_rows)
     __syncthreads();
     const int n = tid < ns ? s_n[tid] : 0;
     const int m = __syncthreads_count(tid < n_local && n > 0);
@@ -163,12 +163,11 @@ __global__ void __launch_bounds__(SHORT_THREADS) short_prepare_kernel(const void
     }
     else if (warp == 2 && has_shared)
     {
-        for (int r = lane; r < R; r += 32)
-            if (r % sh_mod == sh_rem)
-            {
-                const int pos = (r + sh_mod - 1 - sh_rem) / sh_mod, t = s_pre[0][n_local] + (pos >> 3), c = pos & 7;
-                route->rows[t][c] = (unsigned short) r; route->w[t][c] = 1.f;
-            }
+        for (int pos = lane; pos < sh_rows; pos += 32)
+        {
+            const int t = s_pre[0][n_local] + (pos >> 3), c = pos & 7;
+            route->rows[t][c] = (unsigned short) (sh_row0 + pos); route->w[t][c] = 1.f;
+        }
     }
     __syncthreads();
     // columns beyond the picks of an expert's last tile: the tile's first row again, weight 0 (computed, never written out)
@@ -1213,9 +1212,11 @@ static void launch_short_pair(int grid, const DecodeArgs& a, cudaStream_t st)
 }
 
 int short_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
-                 int act_quant, float* y, void* ws, size_t ws_bytes, cudaStream_t st)
+                 int act_quant, float* y, void* ws, size_t ws_bytes, cudaStream_t st, int shared_row0, int shared_rows)
 {
     const int H = L->H, I = L->I;
+    if (shared_rows < 0) { shared_row0 = 0; shared_rows = R; }
+    if (shared_row0 < 0 || shared_row0 + shared_rows > R) return fail(HMOE_E_ARG, "hmoe_short_prefill: the shared expert's rows must lie inside the call's rows");
     if (R < 1 || R > SHORT_MAXR) return fail(HMOE_E_ARG, "hmoe_short_prefill: rows must be 1..640");
     if (L->topk < 1 || L->topk > TOPK_MAX) return fail(HMOE_E_ARG, "hmoe_short_prefill: topk must be 1..8");
     if (H % 128 || I % 128 || H < 128 || I < 128) return fail(HMOE_E_ARG, "hmoe_short_prefill: H and I must be multiples of 128");
@@ -1235,10 +1236,10 @@ int short_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t*
     __half* xf = (__half*) w; w += up256((size_t) R * H * 2);
     float* xscale = (float*) w; w += up256((size_t) R * (H / 32) * 4);
     float* G = (float*) w;
-    const int has_shared = L->sh_gate_w != nullptr;
+    const int has_shared = L->sh_gate_w != nullptr && shared_rows > 0;
     const int grid = g_sms < MAXB ? g_sms : MAXB;
     short_prepare_kernel<<<R + 1, SHORT_THREADS, 0, st>>>(x, x_dtype == HMOE_BF16 ? 1 : 0, sel, (const __half*) rw, R, H, L->topk, lo, n_local, has_shared,
-                                                          act_quant, xf, xscale, route, 1, 0, (float4*) G, (L->topk + 1) * 2 * I / 4, I, grid);
+                                                          act_quant, xf, xscale, route, shared_row0, shared_rows, (float4*) G, (L->topk + 1) * 2 * I / 4, I, grid);
     DecodeArgs a;
     a.H = H; a.I = I;
     a.gate_w = L->gate_w; a.up_w = L->up_w; a.down_w = L->down_w; a.gate_s = L->gate_s; a.up_s = L->up_s; a.down_s = L->down_s;

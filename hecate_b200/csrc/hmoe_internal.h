@@ -44,7 +44,7 @@ struct EpCombineArgs
 size_t decode_ws_bytes(int H, int I);
 size_t short_ws_bytes(int R, int H, int I, int topk);
 int short_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
-                 int act_quant, float* y, void* ws, size_t ws_bytes, cudaStream_t st);
+                 int act_quant, float* y, void* ws, size_t ws_bytes, cudaStream_t st, int shared_row0 = 0, int shared_rows = -1);
 int decode_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
                   int act_quant, float* y, void* ws, size_t ws_bytes, cudaStream_t st, int sh_mod = 1, int sh_rem = 0,
                   unsigned* gen_ptr = nullptr, size_t slot_stride = 0, bool prepared = false, const struct EpCombineArgs* epc = nullptr);

@@ -244,9 +244,11 @@ class EpPrefill:
     every rank runs the grouped GEMMs for its experts over all tokens (ids outside [lo, lo + n_local) are dropped by the
     permutation) plus the shared expert for its own tokens. Combine, use_peer = True: the down GEMM adds every row's sums straight into the output of the rank
     that owns the row, over NVLink peer memory, and a flag barrier ends the step. use_peer = False (the baseline): a local
-    full-size partial and an NCCL reduce-scatter."""
+    full-size partial and an NCCL reduce-scatter. short: with the reduce-scatter combine, steps of few rows in total (up to
+    moe.forward_short_rows(), e.g. a decode step of many sequences) run the local experts through the streaming kernels
+    (hmoe_short_prefill_ep) instead of the grouped GEMMs; None = whenever the layer allows it."""
 
-    def __init__(self, rank, world, tables, n_experts, rows_per_rank, device, dist, use_peer=None, dispatch="nccl"):
+    def __init__(self, rank, world, tables, n_experts, rows_per_rank, device, dist, use_peer=None, dispatch="nccl", short=None):
         import torch
         assert dispatch in ("nccl", "peer")
         if use_peer is None:
@@ -259,6 +261,13 @@ class EpPrefill:
         R = rows_per_rank * world
         self.R = R
         self.ws = moe.prefill_workspace(R, tables.topk, tables.n, tables.H, tables.I, device)
+        can_short = (R <= moe.forward_short_rows() and tables.H <= 6144 and tables.I <= 2048 and not (tables.shared is not None and tables.shared_i8)
+                     and not (use_peer and world > 1))
+        if short and not can_short:
+            raise moe.HmoeError("EpPrefill: short needs <= forward_short_rows() rows in total, H <= 6144, I <= 2048, the int4 shared expert and the reduce-scatter combine")
+        self.short = can_short if short is None else bool(short)
+        if self.short:
+            self.ws_short = moe.short_prefill_workspace(R, tables.H, tables.I, tables.topk, device)
         if not (dispatch == "peer" and world > 1):
             self.x_all = torch.empty(R, tables.H, dtype=torch.bfloat16, device=device)
             self.sel_all = torch.empty(R, tables.topk, dtype=torch.int64, device=device)
@@ -310,9 +319,10 @@ class EpPrefill:
             check(lib().hmoe_ep_copy(vp(out), C.c_void_p(self.peer.own), C.c_size_t(nbytes), st))
             return out
         self.partial.zero_()
-        check(lib().hmoe_prefill_ep(C.byref(self.struct), xa, C.c_int(moe._dt(x)), sa, ra,
-                                    C.c_int(self.R), C.c_int(pl["lo"]), C.c_int(pl["n_local"]), C.c_int(0), vp(self.partial), vp(self.ws),
-                                    C.c_size_t(self.ws.numel()), C.c_int(self.rank * self.rpr), C.c_int(self.rpr), st))
+        fn, ws = (lib().hmoe_short_prefill_ep, self.ws_short) if self.short else (lib().hmoe_prefill_ep, self.ws)
+        check(fn(C.byref(self.struct), xa, C.c_int(moe._dt(x)), sa, ra,
+                 C.c_int(self.R), C.c_int(pl["lo"]), C.c_int(pl["n_local"]), C.c_int(0), vp(self.partial), vp(ws),
+                 C.c_size_t(ws.numel()), C.c_int(self.rank * self.rpr), C.c_int(self.rpr), st))
         if self.world > 1:
             d.reduce_scatter_tensor(out, self.partial)
         else:
@@ -323,6 +333,8 @@ class EpPrefill:
         import torch
         torch.cuda.synchronize(self.dev)
         s = moe.ws_status(self.ws)
+        if self.short:
+            s |= moe.ws_status(self.ws_short)
         if self.peer is not None:
             s |= int(self.peer.status.item())
         return s

@@ -189,6 +189,11 @@ size_t hmoe_short_prefill_ws_bytes(int R, int H, int I, int topk);
 int hmoe_short_prefill(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
                        int act_quant, float* out, void* ws, size_t ws_bytes, void* stream);
 
+/* hmoe_short_prefill for one rank of an expert-parallel group (no reference counterpart), as hmoe_prefill_ep: experts split by
+ * lo / n_local, the shared expert applied to rows [shared_row0, shared_row0 + shared_rows) only (the rank's own tokens). */
+int hmoe_short_prefill_ep(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
+                          int act_quant, float* out, void* ws, size_t ws_bytes, int shared_row0, int shared_rows, void* stream);
+
 /* One entry point for any number of rows, as tier_submit / _hot_prefill choose among the reference's kernels by row count
  * (runtime/tier/tier_split.py:341-364,543-546): R <= 16 -> hmoe_decode, R <= hmoe_forward_short_rows() -> hmoe_short_prefill
  * (when the layer's shapes and shared-expert format allow it), else hmoe_prefill. One workspace serves every row count up to

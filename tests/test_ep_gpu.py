@@ -222,8 +222,11 @@ def _prefill_rank_main(rank, world, port, out_path):
     sl = slice(rank * rpr, (rank + 1) * rpr)
     errs = []
     outs = {}
-    for use_peer in (False, True):
-        ep = EpPrefill(rank, world, local, E, rpr, dev, dist, use_peer=use_peer)
+    for use_peer in (False, True, "short"):
+        # 320 rows in total: few enough for the streaming kernels ("short": hmoe_short_prefill_ep + reduce-scatter); the other two arms
+        # keep the grouped GEMMs
+        ep = EpPrefill(rank, world, local, E, rpr, dev, dist, use_peer=use_peer is True, short=use_peer == "short")
+        assert ep.short == (use_peer == "short")
         out = torch.empty(rpr, H, device=dev)
         for _ in range(2):                     # twice: the second step reuses the zeroed peer buffer and the next barrier generation
             ep.step(torch.from_numpy(xa[sl]).to(dev).to(torch.bfloat16), torch.from_numpy(sel[sl]).to(dev), torch.from_numpy(rw[sl]).to(dev), out)
@@ -254,7 +257,7 @@ def _prefill_rank_main(rank, world, port, out_path):
     outs_v = {}
     sent_ok = True
     for use_peer in (False, True):
-        ep = EpPrefill(rank, world, local, E, rpr, dev, dist, use_peer=use_peer, dispatch="peer")
+        ep = EpPrefill(rank, world, local, E, rpr, dev, dist, use_peer=use_peer, dispatch="peer", short=False)
         out_v = torch.empty(rpr, H, device=dev)
         ep.step(torch.from_numpy(xa[sl] * 50).to(dev).to(torch.bfloat16), torch.from_numpy(sel[sl]).to(dev), torch.from_numpy(rw[sl]).to(dev), out_v)
         s0 = int(ep.sent.item())
@@ -271,6 +274,8 @@ def _prefill_rank_main(rank, world, port, out_path):
     dist.all_gather(gathered, outs[True])
     gathered_nccl = [torch.empty_like(out) for _ in range(world)]
     dist.all_gather(gathered_nccl, outs[False])
+    gathered_short = [torch.empty_like(out) for _ in range(world)]
+    dist.all_gather(gathered_short, outs["short"])
     if rank == 0:
         full = HostLayer(0, 0, H, I, range(E), 128, True).upload(dev)
         ws = moe.prefill_workspace(R, 8, E, H, I, dev)
@@ -281,7 +286,7 @@ def _prefill_rank_main(rank, world, port, out_path):
         moe.prefill(full, torch.from_numpy(xa).to(dev).to(torch.bfloat16), torch.from_numpy(sel_v).to(dev), torch.from_numpy(rw).to(dev), ref_v, ws)
         ev = [float((torch.cat(gathered_v[k]) - ref_v).norm() / ref_v.norm()) for k in (False, True)]
         np.save(out_path, np.array([float((got - ref).norm() / ref.norm()), float((got_nccl - ref).norm() / ref.norm()),
-                                    float((got_placed - ref).norm() / ref.norm())] + ev))
+                                    float((got_placed - ref).norm() / ref.norm())] + ev + [float((torch.cat(gathered_short) - ref).norm() / ref.norm())]))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -297,3 +302,4 @@ def test_two_gpu_prefill_matches_single_gpu(tmp_path):
     assert e[0] < 1e-3 and e[1] < 1e-3, e        # peer-memory combine, NCCL reduce-scatter combine
     assert e[2] < 1e-3, e                         # experts placed by load with copies: same result as contiguous ids
     assert e[3] < 1e-3 and e[4] < 1e-3, e        # peer-memory all-to-all-v dispatch, with either combine
+    assert e[5] < 1e-3, e                         # local experts through the streaming kernels (short prefill), reduce-scatter combine
