@@ -221,14 +221,15 @@ int hmoe_short_prefill_ep(const hmoe_layer* layer, const void* x, int x_dtype, c
 }
 
 // Which path serves a call of R rows: 0 decode, 1 short prefill, 2 grouped GEMMs. The short path needs the shapes whose tile
-// activations fit in registers and the int4 shared expert; FORWARD_SHORT_ROWS is where the grouped GEMMs become faster
+// activations fit in registers; FORWARD_SHORT_ROWS is where the grouped GEMMs become faster
 // (measured on the benchmark layer: they cost the same from about 100 rows up because every expert's weights are converted
 // whatever its row count, the short path grows with the number of 8-pick tiles).
-static int forward_path(const hmoe_layer* L, int R)
+static int forward_path(const hmoe_layer* L, int R, int act_quant)
 {
     const bool sh8 = L->shared_format == 1 && L->sh_gate_w != nullptr;
+    if (sh8 && act_quant) return 2;           // the int8 shared expert in the int8 activation mode: only the grouped GEMMs serve it
     if (R <= MAXR) return 0;
-    if (R <= FORWARD_SHORT_ROWS && L->I <= 2048 && L->H <= 6144 && !sh8) return 1;
+    if (R <= FORWARD_SHORT_ROWS && L->I <= 2048 && L->H <= 6144) return 1;
     return 2;
 }
 int hmoe_forward_short_rows(void) { return FORWARD_SHORT_ROWS; }
@@ -238,7 +239,7 @@ size_t hmoe_forward_ws_bytes(int R, int topk, int n_local, int H, int I, int act
     size_t b = decode_ws_bytes(H, I);
     const int rs = R < FORWARD_SHORT_ROWS ? R : FORWARD_SHORT_ROWS;
     if (R > MAXR) { const size_t s = short_ws_bytes(rs, H, I, topk); b = s > b ? s : b; }
-    if (R > MAXR) { const size_t p = prefill_ws_bytes(R, topk, n_local, H, I, act_quant); b = p > b ? p : b; }
+    { const size_t p = prefill_ws_bytes(R, topk, n_local, H, I, act_quant); b = p > b ? p : b; }      // any R can end up there (see forward_path)
     return b;
 }
 int hmoe_forward(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
@@ -247,7 +248,7 @@ int hmoe_forward(const hmoe_layer* layer, const void* x, int x_dtype, const int6
     if (!layer) return fail(HMOE_E_ARG, "hmoe_forward: null layer");
     if (R < 1) return fail(HMOE_E_ARG, "hmoe_forward: rows must be >= 1");
     if (ws_bytes < hmoe_forward_ws_bytes(R, layer->topk, n_local, layer->H, layer->I, act_quant)) return fail(HMOE_E_WS, "hmoe_forward: workspace too small");
-    switch (forward_path(layer, R))
+    switch (forward_path(layer, R, act_quant))
     {
     case 0: return decode_launch(layer, x, x_dtype, sel, rw, R, lo, n_local, act_quant, out, ws, ws_bytes, (cudaStream_t) stream);
     case 1: return short_launch(layer, x, x_dtype, sel, rw, R, lo, n_local, act_quant, out, ws, ws_bytes, (cudaStream_t) stream);

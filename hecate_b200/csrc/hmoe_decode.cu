@@ -1137,6 +1137,8 @@ int decode_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t
     float* ascale = (float*) w;
     const bool sh8 = L->shared_format == 1 && L->sh_gate_w != nullptr;       // the reference's int8 shared expert: its own kernels
     if (sh8 && !(I <= 2048 && H <= 6144)) return fail(HMOE_E_UNSUPPORTED, "hmoe_decode: the int8 shared expert needs H <= 6144 and I <= 2048");
+    // its kernels read the prepared rows as values; in the int8 activation mode those hold codes with their scales apart
+    if (sh8 && act_quant) return fail(HMOE_E_UNSUPPORTED, "hmoe_decode: the int8 shared expert is not available in the int8 activation mode (hmoe_prefill serves it)");
     const int has_shared = L->sh_gate_w != nullptr && !sh8;
     if (g_prof) cudaEventRecord(g_ev[g_prof_calls % PROF_RING][0], st);
     // prepared: the router's launch has done the set-up step (hmoe_router_decode)
@@ -1221,7 +1223,8 @@ int short_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t*
     if (L->topk < 1 || L->topk > TOPK_MAX) return fail(HMOE_E_ARG, "hmoe_short_prefill: topk must be 1..8");
     if (H % 128 || I % 128 || H < 128 || I < 128) return fail(HMOE_E_ARG, "hmoe_short_prefill: H and I must be multiples of 128");
     if (!(I <= 2048 && H <= 6144)) return fail(HMOE_E_UNSUPPORTED, "hmoe_short_prefill: needs H <= 6144 and I <= 2048");
-    if (L->shared_format == 1 && L->sh_gate_w != nullptr) return fail(HMOE_E_UNSUPPORTED, "hmoe_short_prefill: the int8 shared expert is served by hmoe_decode and hmoe_prefill");
+    const bool sh8 = L->shared_format == 1 && L->sh_gate_w != nullptr;       // the reference's int8 shared expert: its own kernels, 16 rows at a time
+    if (sh8 && act_quant) return fail(HMOE_E_UNSUPPORTED, "hmoe_short_prefill: the int8 shared expert is not available in the int8 activation mode (hmoe_prefill serves it)");
     if (n_local < 0 || n_local > 256) return fail(HMOE_E_ARG, "hmoe_short_prefill: at most 256 local experts");
     if (!(L->group == 0 && L->scale_dtype == HMOE_F32) && !(L->group == 128 && L->scale_dtype == HMOE_BF16))
         return fail(HMOE_E_ARG, "hmoe_short_prefill: scales must be fp32 per row (group 0) or bf16 per 128 columns");
@@ -1236,14 +1239,26 @@ int short_launch(const hmoe_layer* L, const void* x, int x_dtype, const int64_t*
     __half* xf = (__half*) w; w += up256((size_t) R * H * 2);
     float* xscale = (float*) w; w += up256((size_t) R * (H / 32) * 4);
     float* G = (float*) w;
-    const int has_shared = L->sh_gate_w != nullptr && shared_rows > 0;
+    const int has_shared = L->sh_gate_w != nullptr && shared_rows > 0 && !sh8;
     const int grid = g_sms < MAXB ? g_sms : MAXB;
     short_prepare_kernel<<<R + 1, SHORT_THREADS, 0, st>>>(x, x_dtype == HMOE_BF16 ? 1 : 0, sel, (const __half*) rw, R, H, L->topk, lo, n_local, has_shared,
                                                           act_quant, xf, xscale, route, shared_row0, shared_rows, (float4*) G, (L->topk + 1) * 2 * I / 4, I, grid);
+    if (sh8)
+    {
+        // The shared expert's rows in groups of sixteen through the decode path's pair of int8 kernels; a group's gate / up sums go to
+        // sixteen rows of the per-pick buffer behind the routed picks (cleared by the set-up kernel with the rest).
+        for (int c = 0; c < shared_rows; c += MAXR)
+        {
+            const int n = shared_rows - c < MAXR ? shared_rows - c : MAXR, r0 = shared_row0 + c;
+            const int rc = shared_i8_launch(L, n, 1, 0, xf + (size_t) r0 * H, G + ((size_t) R * L->topk + c) * 2 * I, y + (size_t) r0 * H, nullptr, 0, grid, st);
+            if (rc) return rc;
+        }
+    }
     DecodeArgs a;
     a.H = H; a.I = I;
     a.gate_w = L->gate_w; a.up_w = L->up_w; a.down_w = L->down_w; a.gate_s = L->gate_s; a.up_s = L->up_s; a.down_s = L->down_s;
-    a.sh_gw = L->sh_gate_w; a.sh_uw = L->sh_up_w; a.sh_dw = L->sh_down_w; a.sh_gs = L->sh_gate_s; a.sh_us = L->sh_up_s; a.sh_ds = L->sh_down_s;
+    a.sh_gw = sh8 ? nullptr : L->sh_gate_w; a.sh_uw = sh8 ? nullptr : L->sh_up_w; a.sh_dw = sh8 ? nullptr : L->sh_down_w;
+    a.sh_gs = sh8 ? nullptr : L->sh_gate_s; a.sh_us = sh8 ? nullptr : L->sh_up_s; a.sh_ds = sh8 ? nullptr : L->sh_down_s;
     a.route = reinterpret_cast<const Route*>(route); a.xf = xf; a.xscale = xscale; a.act = nullptr; a.ascale = nullptr; a.G = G; a.y = y; a.status = status;
     a.gen_ptr = nullptr; a.slot_stride = 0;
     a.ep = EpTail();

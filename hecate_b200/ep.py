@@ -261,10 +261,9 @@ class EpPrefill:
         R = rows_per_rank * world
         self.R = R
         self.ws = moe.prefill_workspace(R, tables.topk, tables.n, tables.H, tables.I, device)
-        can_short = (R <= moe.forward_short_rows() and tables.H <= 6144 and tables.I <= 2048 and not (tables.shared is not None and tables.shared_i8)
-                     and not (use_peer and world > 1))
+        can_short = R <= moe.forward_short_rows() and tables.H <= 6144 and tables.I <= 2048 and not (use_peer and world > 1)
         if short and not can_short:
-            raise moe.HmoeError("EpPrefill: short needs <= forward_short_rows() rows in total, H <= 6144, I <= 2048, the int4 shared expert and the reduce-scatter combine")
+            raise moe.HmoeError("EpPrefill: short needs <= forward_short_rows() rows in total, H <= 6144, I <= 2048 and the reduce-scatter combine")
         self.short = can_short if short is None else bool(short)
         if self.short:
             self.ws_short = moe.short_prefill_workspace(R, tables.H, tables.I, tables.topk, device)

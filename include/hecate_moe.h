@@ -184,7 +184,8 @@ int hmoe_prefill(const hmoe_layer* layer, const void* x, int x_dtype, const int6
  * experts again). The whole call is one list of (expert, <= 8 picks) tiles for the decode streaming kernels, so a distinct
  * expert is read from memory once per eight of its picks; the grouped GEMMs convert every expert's weights whatever its row
  * count and only win from several hundred rows up (level at about 640 rows of uniform routing over 256 experts). Arguments as hmoe_prefill (out is added into). Needs H <= 6144, I <= 2048
- * and the int4 shared expert (else HMOE_E_UNSUPPORTED). ws: hmoe_short_prefill_ws_bytes(R, ...) bytes, 0 for R outside 1..640. */
+ * (else HMOE_E_UNSUPPORTED); the int8 shared expert runs sixteen rows at a time through the decode path's kernels and is not
+ * available with act_quant = 1 (nor in hmoe_decode; hmoe_prefill and hmoe_forward serve that combination). ws: hmoe_short_prefill_ws_bytes(R, ...) bytes, 0 for R outside 1..640. */
 size_t hmoe_short_prefill_ws_bytes(int R, int H, int I, int topk);
 int hmoe_short_prefill(const hmoe_layer* layer, const void* x, int x_dtype, const int64_t* sel, const void* rw, int R, int lo, int n_local,
                        int act_quant, float* out, void* ws, size_t ws_bytes, void* stream);
@@ -196,7 +197,7 @@ int hmoe_short_prefill_ep(const hmoe_layer* layer, const void* x, int x_dtype, c
 
 /* One entry point for any number of rows, as tier_submit / _hot_prefill choose among the reference's kernels by row count
  * (runtime/tier/tier_split.py:341-364,543-546): R <= 16 -> hmoe_decode, R <= hmoe_forward_short_rows() -> hmoe_short_prefill
- * (when the layer's shapes and shared-expert format allow it), else hmoe_prefill. One workspace serves every row count up to
+ * (when the layer's shapes allow it), else hmoe_prefill; the int8 shared expert with act_quant = 1 always takes hmoe_prefill. One workspace serves every row count up to
  * the R it was sized for: hmoe_forward_ws_bytes(R_max, ...) bytes, zero-filled once. */
 int hmoe_forward_short_rows(void);
 size_t hmoe_forward_ws_bytes(int R, int topk, int n_local, int H, int I, int act_quant);

@@ -75,3 +75,22 @@ def test_int8_shared_expert_in_prefill(oracle, H, I, R, group):
     yd = torch.zeros(16 if R >= 16 else R, H, device=dev); n = yd.shape[0]
     moe.decode(tabs, up(x[:n]), up(sel[:n]), up(rw[:n]), yd, moe.decode_workspace(H, I, dev))
     assert errors(got[:n], yd.cpu().numpy().astype(np.float64))[2] < NORM_REL_EXACT
+    # and so does the short path, which runs the int8 shared expert sixteen rows at a time (37 rows: 16 + 16 + 5)
+    ns = min(R, 37)
+    ys = torch.zeros(ns, H, device=dev)
+    wss = moe.short_prefill_workspace(ns, H, I, 8, dev)
+    for call in range(2):
+        ys.zero_()
+        moe.short_prefill(tabs, up(x[:ns]), up(sel[:ns]), up(rw[:ns]), ys, wss)
+        assert moe.ws_status(wss) == 0
+        assert errors(ys.cpu().numpy().astype(np.float64), got[:ns])[2] < NORM_REL_EXACT, call
+    # in the int8 activation mode the streaming kernels do not take the int8 shared expert; `forward` sends such a call to the grouped GEMMs
+    with pytest.raises(moe.HmoeError):
+        moe.short_prefill(tabs, up(x[:ns]), up(sel[:ns]), up(rw[:ns]), ys, wss, act_quant=True)
+    with pytest.raises(moe.HmoeError):
+        moe.decode(tabs, up(x[:n]), up(sel[:n]), up(rw[:n]), yd, moe.decode_workspace(H, I, dev), act_quant=True)
+    wsf = moe.forward_workspace(ns, 8, E, H, I, dev, act_quant=True)
+    yq = torch.zeros(ns, H, device=dev); yp = torch.zeros(ns, H, device=dev)
+    moe.forward(tabs, up(x[:ns]), up(sel[:ns]), up(rw[:ns]), yq, wsf, act_quant=True)
+    moe.prefill(tabs, up(x[:ns]), up(sel[:ns]), up(rw[:ns]), yp, moe.prefill_workspace(ns, 8, E, H, I, dev, act_quant=True), act_quant=True)
+    assert moe.ws_status(wsf) == 0 and errors(yq.cpu().numpy(), yp.cpu().numpy())[2] < 1e-5       # the same kernels; the sums' order differs
