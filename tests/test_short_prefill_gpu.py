@@ -148,3 +148,44 @@ def test_short_prefill_matches_grouped_gemms_at_full_shape(dev):
     moe.short_prefill(tabs, x, st, rt, b, wss)
     assert moe.ws_status(wsp) == 0 and moe.ws_status(wss) == 0
     assert errors(b.cpu().numpy(), a.cpu().numpy())[2] < 1e-3
+
+
+def test_short_prefill_random_against_decode_chunks(dev):
+    """Random row counts, expert counts, bands, scale formats and routings (repeated picks inside a row, a few very hot experts):
+    the short path equals the decode call in 16-row chunks, which shares its streaming kernels but not its set-up code."""
+    import torch
+    from hecate_b200 import moe
+    rng = np.random.default_rng(7)
+    H, I = 256, 128
+    layers = {}
+    for it in range(60):
+        E = int(rng.choice([8, 32, 256])); shared = bool(rng.integers(2)); group = int(rng.choice([0, 128]))
+        key = (E, shared, group)
+        if key not in layers:
+            layers[key] = HostLayer(3, 0, H, I, range(E), group, shared).upload(dev)
+        tabs = layers[key]
+        R = int(rng.integers(1, 641))
+        lo = int(rng.integers(0, E)) if rng.integers(3) == 0 else 0
+        n_local = int(rng.integers(1, E - lo + 1)) if lo or rng.integers(3) == 0 else E
+        mode = int(rng.integers(3))
+        if mode == 0:
+            sel = rng.integers(0, E, size=(R, 8))
+        elif mode == 1:
+            sel = np.stack([rng.permutation(E)[:8] for _ in range(R)])
+        else:
+            sel = np.minimum((rng.pareto(1.0, size=(R, 8)) * 2).astype(np.int64), E - 1)
+        sel = sel.astype(np.int64)
+        rw = (rng.random((R, 8)) * 0.3 + 0.02).astype(np.float16)
+        aq = bool(rng.integers(2)) and mode == 1      # repeated picks: decode sums their weights before the int8 round trip, the short path after
+        x = torch.from_numpy(synth.activations(100 + it, 0, R, H)).to(dev).half()
+        st, rt = torch.from_numpy(sel).to(dev), torch.from_numpy(rw).to(dev)
+        a = torch.zeros(R, H, device=dev); b = torch.zeros(R, H, device=dev)
+        ws = moe.short_prefill_workspace(R, H, I, 8, dev)
+        moe.short_prefill(tabs, x, st, rt, a, ws, lo=lo, n_local=n_local, act_quant=aq)
+        wsd = moe.decode_workspace(H, I, dev)
+        for c in range(0, R, 16):
+            n = min(16, R - c)
+            moe.decode(tabs, x[c:c + n], st[c:c + n], rt[c:c + n], b[c:c + n], wsd, lo=lo, n_local=n_local, act_quant=aq)
+        assert moe.ws_status(ws) == 0
+        err = float((a - b).norm()) / (float(b.norm()) or 1.0)
+        assert err < 2e-3, (it, E, shared, group, R, lo, n_local, mode, aq, err)
