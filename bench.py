@@ -980,9 +980,12 @@ def ep_prefill_arm(args, world, rank, dev, tabs, R, zipf, torch, dist, ep, moe, 
     times, outs = {}, {}
     st_all = launches = 0
     sent_rows = 0
-    for mode in ("nccl", "peer", "a2a+nccl", "a2a+peer"):            # [dispatch +] combine
+    # [dispatch +] combine through the grouped GEMMs; steps of few rows in total also through the streaming kernels ("short": the
+    # local experts via hmoe_short_prefill_ep, NCCL all-gather and reduce-scatter around them)
+    modes = ("nccl", "peer", "a2a+nccl", "a2a+peer") + (("short",) if R <= moe.forward_short_rows() else ())
+    for mode in modes:
         a2a = mode.startswith("a2a")
-        p = ep.EpPrefill(rank, world, tabs, E, rpr, dev, dist, use_peer=mode.endswith("peer"), dispatch="peer" if a2a else "nccl")
+        p = ep.EpPrefill(rank, world, tabs, E, rpr, dev, dist, use_peer=mode.endswith("peer"), dispatch="peer" if a2a else "nccl", short=mode == "short")
         for _ in range(warmup):
             p.step(x, sel, rw, out)
         torch.cuda.synchronize(); dist.barrier()
@@ -1004,6 +1007,10 @@ def ep_prefill_arm(args, world, rank, dev, tabs, R, zipf, torch, dist, ep, moe, 
             dist.barrier(); p.peer.close()
         del p
     best = min(times, key=times.get)               # all arms are timed; the line reports the fastest one and names it
+    e3 = None
+    if "short" in outs:
+        e3 = torch.tensor(list(errors(outs["short"].cpu().numpy(), outs["nccl"].cpu().numpy())), device=dev, dtype=torch.float64)
+        dist.all_reduce(e3, op=dist.ReduceOp.MAX)
     e = torch.tensor(list(errors(outs["peer"].cpu().numpy(), outs["nccl"].cpu().numpy())), device=dev, dtype=torch.float64)
     dist.all_reduce(e, op=dist.ReduceOp.MAX)
     e2 = torch.tensor(list(errors(outs["a2a+peer"].cpu().numpy(), outs["nccl"].cpu().numpy())), device=dev, dtype=torch.float64)
@@ -1022,10 +1029,12 @@ def ep_prefill_arm(args, world, rank, dev, tabs, R, zipf, torch, dist, ep, moe, 
         "config": {"workload": f"prefill M={R} tokens over {world} GPUs ({rpr} each), Zipf({zipf}) top-8 over {E} experts + shared, "
                                f"{pl['n_local']} experts per GPU ({'placed by load from a calibration sample' if use_plan else 'contiguous ids'}), "
                                + ("dispatch: all-to-all-v over NVLink peer memory" if best.startswith("a2a") else "dispatch: all-gather (NCCL)")
-                               + ", combine: " + ("fused into the down GEMM over NVLink peer memory" if best.endswith("peer") else "NCCL reduce-scatter"),
+                               + ", combine: " + ("fused into the down GEMM over NVLink peer memory" if best.endswith("peer") else "NCCL reduce-scatter")
+                               + (", local experts through the streaming kernels (short prefill)" if best == "short" else ""),
                    "l2": "inputs larger than L2"},
         "tokens_per_s": R / t, "nccl_reduce_scatter_ms_per_step": times["nccl"], "peer_combine_ms_per_step": times["peer"],
         "peer_dispatch_nccl_combine_ms_per_step": times["a2a+nccl"], "peer_dispatch_peer_combine_ms_per_step": times["a2a+peer"],
+        **({"short_prefill_ms_per_step": times["short"]} if "short" in times else {}),
         "dispatch_bytes_per_rank": (world - 1) * rpr * (H * 2 + TOPK * 10) if not best.startswith("a2a") else sent_rows * H * 2 + (world - 1) * rpr * TOPK * 10,
         "dispatch_bytes_per_rank_all_gather": (world - 1) * rpr * (H * 2 + TOPK * 10),
         "dispatch_bytes_per_rank_all_to_all_v": sent_rows * H * 2 + (world - 1) * rpr * TOPK * 10,
@@ -1038,7 +1047,9 @@ def ep_prefill_arm(args, world, rank, dev, tabs, R, zipf, torch, dist, ep, moe, 
         "parity_check": {"peer_combine_vs_nccl_reduce_scatter": {"max_rel": float(e[0]), "mean_abs": float(e[1]), "norm_rel": float(e[2]),
                                                                  "ok": bool(float(e[2]) < 1e-5)},
                          "peer_dispatch_and_combine_vs_nccl": {"max_rel": float(e2[0]), "mean_abs": float(e2[1]), "norm_rel": float(e2[2]),
-                                                               "ok": bool(float(e2[2]) < 1e-5)}},
+                                                               "ok": bool(float(e2[2]) < 1e-5)},
+                         **({"short_prefill_vs_grouped_gemms": {"max_rel": float(e3[0]), "mean_abs": float(e3[1]), "norm_rel": float(e3[2]),
+                                                                "ok": bool(float(e3[2]) < 1e-3)}} if e3 is not None else {})},
         "gpu_launches": int(launches), "device_status": int(st_all), "clocks": cs.summary()}
 
 
