@@ -268,7 +268,8 @@ using Route = RouteT<MAXT>;
 // decode and its grouped-GEMM paths (runtime/tier/tier_split.py:341-355: 9..64 rows through the moe4 decode kernels in 8-row
 // chunks, each chunk streaming its experts again); here the whole call is one tile list, so an expert is streamed once per
 // eight of its picks. A pick is one tile column (an expert picked twice by a row gets two columns of that row).
-constexpr int SHORT_MAXR = 640;               // beyond this the grouped GEMMs are faster on any layer (16-bit row numbers, 16-bit rows of the per-pick buffer)
+constexpr int SHORT_MAXR = 640;               // where the grouped GEMMs catch up on a 256-expert layer under uniform routing (row numbers and the rows
+                                              // of the per-pick buffer are 16-bit in the route)
 // tiles: one partial tile per local expert and for the shared expert, plus the full ones
 constexpr int SHORT_MAXT = 256 + 1 + (SHORT_MAXR * TOPK_MAX) / 8 + SHORT_MAXR / 8 + 2;
 using RouteShort = RouteT<SHORT_MAXT, unsigned short>;
