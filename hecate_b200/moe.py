@@ -235,6 +235,15 @@ def route_distinct(ws):
     return int(ws[256:260].view(torch.int32).item())
 
 
+def route_tiles(ws):
+    """Diagnostic: (distinct routed experts, 8-pick tiles) of the work list the last decode or short-prefill call left in `ws`.
+    Synchronises."""
+    import torch
+    torch.cuda.synchronize(ws.device)
+    m, nt = ws[256:264].view(torch.int32).tolist()
+    return int(m), int(nt)
+
+
 # ----------------------------------------------------------------------------------------------------------------------
 # reference-named entry points
 

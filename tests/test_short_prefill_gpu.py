@@ -187,5 +187,10 @@ def test_short_prefill_random_against_decode_chunks(dev):
             n = min(16, R - c)
             moe.decode(tabs, x[c:c + n], st[c:c + n], rt[c:c + n], b[c:c + n], wsd, lo=lo, n_local=n_local, act_quant=aq)
         assert moe.ws_status(ws) == 0
+        # the work list: one tile per eight picks of a local expert (a repeated pick counts twice), the shared expert's rows behind them
+        local = sel[(sel >= lo) & (sel < lo + n_local)] - lo
+        counts = np.bincount(local, minlength=n_local)
+        want_tiles = int(((counts + 7) // 8).sum()) + ((R + 7) // 8 if shared else 0)
+        assert moe.route_tiles(ws) == (int((counts > 0).sum()), want_tiles), (it, moe.route_tiles(ws), want_tiles)
         err = float((a - b).norm()) / (float(b.norm()) or 1.0)
         assert err < 2e-3, (it, E, shared, group, R, lo, n_local, mode, aq, err)
