@@ -194,3 +194,25 @@ def test_short_prefill_random_against_decode_chunks(dev):
         assert moe.route_tiles(ws) == (int((counts > 0).sum()), want_tiles), (it, moe.route_tiles(ws), want_tiles)
         err = float((a - b).norm()) / (float(b.norm()) or 1.0)
         assert err < 2e-3, (it, E, shared, group, R, lo, n_local, mode, aq, err)
+
+
+def test_forward_reuses_one_workspace_across_paths(oracle, dev):
+    """Calls of different sizes, alternating among the three paths, on ONE workspace sized for the largest: what one path leaves
+    behind in the shared scratch must not matter to the next (both activation modes)."""
+    import torch
+    from hecate_b200 import moe
+    H, I, E = 256, 128, 8
+    hl = HostLayer(0, 0, H, I, range(E), 128, True)
+    tabs = hl.upload(dev)
+    ex, sh = hl.oracle_experts(oracle)
+    for aq in (False, True):
+        ws = moe.forward_workspace(700, 8, E, H, I, dev, act_quant=aq)
+        for k, R in enumerate([300, 8, 700, 64, 16, 500, 17, 1, 384, 385]):
+            x = synth.activations(30 + k, 0, R, H).astype(np.float16)
+            sel, rw = synth.zipf_routing(40 + k, 0, R, E, 8, 1.1)
+            ref = oracle.moe_forward(H, I, 128, x, sel, rw, 0, ex, sh, mode=0 if aq else 1)
+            out = torch.zeros(R, H, device=dev)
+            moe.forward(tabs, torch.from_numpy(x).to(dev), torch.from_numpy(sel).to(dev), torch.from_numpy(rw).to(dev), out, ws, act_quant=aq)
+            assert moe.ws_status(ws) == 0
+            e = errors(out.cpu().numpy(), ref)
+            assert (e[0] < MAX_REL and e[1] < MEAN_ABS) if aq else e[2] < NORM_REL_EXACT, (aq, R, e)
