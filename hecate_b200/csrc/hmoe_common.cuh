@@ -276,4 +276,6 @@ using RouteShort = RouteT<SHORT_MAXT, unsigned short>;
 constexpr int FORWARD_SHORT_ROWS = 384;     // hmoe_forward: calls of up to this many rows take the short path (uniform routing over 256
                                             // experts: level with the grouped GEMMs at 640 rows, 1.4 x faster at 384; skewed routing moves the crossing down)
 
+constexpr int FORWARD_SHORT_ROWS_SH8 = 256; // the same with the reference's int8 shared expert (measured: 1.69 ms against 2.2 - 2.7 ms at 256 rows, level near 384)
+
 }  // namespace hmoe

@@ -261,7 +261,8 @@ class EpPrefill:
         R = rows_per_rank * world
         self.R = R
         self.ws = moe.prefill_workspace(R, tables.topk, tables.n, tables.H, tables.I, device)
-        can_short = R <= moe.forward_short_rows() and tables.H <= 6144 and tables.I <= 2048 and not (use_peer and world > 1)
+        sh8 = tables.shared is not None and tables.shared_i8          # the int8 shared expert hands over to the grouped GEMMs earlier (see hmoe_forward)
+        can_short = R <= (min(256, moe.forward_short_rows()) if sh8 else moe.forward_short_rows()) and tables.H <= 6144 and tables.I <= 2048 and not (use_peer and world > 1)
         if short and not can_short:
             raise moe.HmoeError("EpPrefill: short needs <= forward_short_rows() rows in total, H <= 6144, I <= 2048 and the reduce-scatter combine")
         self.short = can_short if short is None else bool(short)

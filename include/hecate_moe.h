@@ -197,7 +197,7 @@ int hmoe_short_prefill_ep(const hmoe_layer* layer, const void* x, int x_dtype, c
 
 /* One entry point for any number of rows, as tier_submit / _hot_prefill choose among the reference's kernels by row count
  * (runtime/tier/tier_split.py:341-364,543-546): R <= 16 -> hmoe_decode, R <= hmoe_forward_short_rows() -> hmoe_short_prefill
- * (when the layer's shapes allow it), else hmoe_prefill; the int8 shared expert with act_quant = 1 always takes hmoe_prefill. One workspace serves every row count up to
+ * (256 with the int8 shared expert; when the layer's shapes allow it), else hmoe_prefill; the int8 shared expert with act_quant = 1 always takes hmoe_prefill. One workspace serves every row count up to
  * the R it was sized for: hmoe_forward_ws_bytes(R_max, ...) bytes, zero-filled once. */
 int hmoe_forward_short_rows(void);
 size_t hmoe_forward_ws_bytes(int R, int topk, int n_local, int H, int I, int act_quant);
